@@ -1,0 +1,49 @@
+"""TEST INFRASTRUCTURE.  The reference's greedy decode loop over token ids.
+
+Restates ``tests/models/orchestrator/causal_lm/generation.py:41-85`` without the
+tokenizer: walk the prompt one token per step, then sample greedily
+(``torch.argmax``, lowest index on ties) ``max_new`` times.  Returns the token ids,
+per-step logits if asked, and the decode-only seconds.
+"""
+from __future__ import annotations
+
+from time import perf_counter
+
+import torch
+
+
+def greedy(logits) -> int:
+    return int(torch.argmax(logits).item())
+
+
+def decode_ids(loaded, prompt_ids, max_new, device="cpu", keep_logits=False, prompt_limit=None):
+    prompt_ids = torch.as_tensor(prompt_ids, dtype=torch.int64)
+    n_prompt = prompt_ids.numel()
+    input_ids = torch.empty(n_prompt + max_new, dtype=torch.int64)
+    input_ids[:n_prompt] = prompt_ids
+    caches = loaded.init_caches(device=device)
+    kept = []
+    logits = None
+    t_prompt = perf_counter()
+    for step in range(n_prompt):
+        args = loaded.prepare_inputs_for_generation(input_ids[: step + 1], step, caches, device=device)
+        logits, fresh = loaded.forward(*args)
+        caches = loaded.append_cache(caches, fresh)
+        if keep_logits:
+            kept.append(logits)
+    t_prompt = perf_counter() - t_prompt
+    out = []
+    started = perf_counter()
+    for step in range(max_new):
+        token = greedy(logits)
+        out.append(token)
+        input_ids[n_prompt + step] = token
+        pos = n_prompt + step
+        args = loaded.prepare_inputs_for_generation(input_ids[: pos + 1], pos, caches, device=device)
+        logits, fresh = loaded.forward(*args)
+        caches = loaded.append_cache(caches, fresh)
+        if keep_logits:
+            kept.append(logits)
+    seconds = perf_counter() - started
+    return {"tokens": out, "seconds": seconds, "prompt_seconds": t_prompt, "logits": kept,
+            "caches": caches}

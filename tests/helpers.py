@@ -1,0 +1,29 @@
+"""Shared test helpers: tolerances the reference's own tests use."""
+import torch
+
+
+def one_ulp_at(reference: torch.Tensor) -> float:
+    """One representable step at the tensor's largest magnitude
+    (reference ``tests/models/decode_oracle.py:42-54``)."""
+    scale = reference.abs().max()
+    up = torch.nextafter(scale, torch.full_like(scale, float("inf")))
+    down = torch.nextafter(scale, torch.full_like(scale, float("-inf")))
+    return max(abs((up - scale).item()), abs((scale - down).item()))
+
+
+def assert_ulps(got, want, ulps, msg=""):
+    assert got.dtype == want.dtype and got.shape == want.shape, (got.dtype, want.dtype, got.shape, want.shape)
+    err = (got.float() - want.float()).abs().max().item()
+    bound = ulps * one_ulp_at(want)
+    assert err <= bound, f"{msg}: max err {err:.4g} > {ulps} ulp-at-scale = {bound:.4g}"
+
+
+# BASELINE tolerance for bf16 hidden states and logits
+RTOL = 2e-2
+ATOL = 2e-2
+
+
+def assert_close_bf16(got, want, msg="", rtol=RTOL, atol=ATOL):
+    g, w = got.float().cpu(), want.float().cpu()
+    viol = ((g - w).abs() - (atol + rtol * w.abs())).max().item()
+    assert viol <= 0, f"{msg}: allclose(rtol={rtol}, atol={atol}) violated by {viol:.4g}"

@@ -1,0 +1,66 @@
+"""The CPU oracle against the committed Hugging Face vectors (CPU only).
+
+The reference pins each authored model against a seeded Hugging Face module at
+"3 roundings at the output's scale" per fused function
+(``tests/models/decode_oracle.py:69-83``).  The same bound is applied per layer
+here; logits after the whole (3-layer) stack get a proportionally wider bound.
+"""
+import torch
+
+from oracle import evaluator, generation, qwen3_1_7b as oq
+from tests.helpers import assert_ulps
+from tilefoundry_b200.authored import qwen3_1_7b as q
+from tilefoundry_b200.authored.weights import random_weights
+from tilefoundry_b200.runtime import DictResource
+
+
+def _load(golden_dir):
+    fx = torch.load(golden_dir / "qwen3_tiny_hf.pt")
+    cfg = q.Qwen3Config(**fx["config"])
+    mod = q.build(cfg)
+    weights = q.tie_head(random_weights(mod, seed=fx["seed_w"], std=fx["std"]))
+    chk = int(sum(int(t.view(torch.int16).to(torch.int64).sum()) for t in weights.values()) & 0x7FFFFFFF)
+    assert chk == fx["weights_checksum"], "seeded weights differ from the ones the fixture was made with"
+    return fx, cfg, evaluator.load(mod, DictResource(weights), oq.make(cfg))
+
+
+def test_layers_match_hf_hidden_states(golden_dir):
+    fx, cfg, loaded = _load(golden_dir)
+    hs = fx["hidden_states"]            # [L+1, T, H]; hs[0] = embeddings, hs[L] = after final norm
+    T = hs.shape[1]
+    cos, sin = q.rope_tables(cfg)
+    scale = torch.full((1, 1, 1, 1), cfg.head_dim ** -0.5, dtype=torch.bfloat16)
+    # embedding is an exact gather
+    emb = torch.stack([loaded.embed(fx["ids"][t].reshape(1))[0, 0] for t in range(T)])
+    assert torch.equal(emb, hs[0])
+    for li, layer in enumerate(loaded.modules[:-1]):
+        kc = torch.zeros(1, 0, cfg.num_key_value_heads, cfg.head_dim, dtype=torch.bfloat16)
+        vc = kc.clone()
+        for t in range(T):
+            x = hs[li, t].reshape(1, 1, -1)
+            out, kn, vn = layer(x, cos, sin, torch.tensor([t], dtype=torch.int32), kc, vc, scale)
+            kc, vc = torch.cat([kc, kn], 1), torch.cat([vc, vn], 1)
+            assert_ulps(out[0, 0], hs[li + 1, t], 3, f"layer {li} position {t}")
+
+
+def test_logits_and_greedy_tokens_match_hf(golden_dir):
+    fx, cfg, loaded = _load(golden_dir)
+    n_new = fx["new_tokens"].numel()
+    run = generation.decode_ids(loaded, fx["ids"], n_new, keep_logits=True)
+    got = torch.cat(run["logits"][: fx["ids"].numel()])
+    assert_ulps(got, fx["logits"], 3 * (cfg.num_hidden_layers + 1), "prompt logits")
+    assert run["tokens"] == fx["new_tokens"].tolist()
+    full = torch.cat(run["logits"][: fx["final_logits"].shape[0]])
+    assert_ulps(full, fx["final_logits"], 3 * (cfg.num_hidden_layers + 1), "continuation logits")
+
+
+def test_zero_length_context_is_a_first_step(golden_dir):
+    # ctx_len admits 0: the step attends only the position it brings itself.
+    fx, cfg, loaded = _load(golden_dir)
+    caches = loaded.init_caches()
+    assert caches[0][0].shape == (1, 0, cfg.num_key_value_heads, cfg.head_dim)
+    args = loaded.prepare_inputs_for_generation(fx["ids"][:1], 0, caches)
+    logits, fresh = loaded.forward(*args)
+    assert logits.shape == (1, cfg.vocab_size) and logits.dtype == torch.bfloat16
+    assert_ulps(logits[0], fx["logits"][0], 3 * (cfg.num_hidden_layers + 1), "first step")
+    assert fresh[0][0].shape == (1, 1, cfg.num_key_value_heads, cfg.head_dim)
