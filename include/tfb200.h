@@ -1,0 +1,237 @@
+/* tfb200 -- C ABI of the B200 decode-step kernel library (libtfb200.so).
+ *
+ * Every entry point takes raw DEVICE pointers, sizes and a CUDA stream, validates
+ * its arguments on the host, enqueues work on that stream and returns a status
+ * (TFB_OK = 0).  Nothing here allocates device memory, synchronises or touches
+ * torch types; buffers are the caller's.  All matrices are bf16 unless a comment
+ * says otherwise.
+ *
+ * The entry points are what a TileFoundry runtime twin binds in place of its own
+ * kernel library: the reference examples call per-function kernel launchers with
+ * caller-owned outputs and no allocation or synchronisation
+ * (examples/granite_4_0_h_small-cuda/kernels/granite.cu:804-808), selected through
+ * @runtime_func bodies (src/tilefoundry/runtime/decorator.py:53-77).  Each
+ * declaration cites the authored function or reference kernel it stands in for.
+ */
+#ifndef TFB200_H
+#define TFB200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define TFB_API __attribute__((visibility("default")))
+#else
+#define TFB_API
+#endif
+
+typedef void* tfb_stream_t; /* cudaStream_t */
+
+enum {
+    TFB_OK = 0,
+    TFB_EINVAL = 1,      /* bad size, null pointer, unsupported combination */
+    TFB_EALIGN = 2,      /* pointer or row stride not 16-byte aligned */
+    TFB_ECAPACITY = 3,   /* position / context exceeds the cache or scratch capacity */
+    TFB_ELAUNCH = 4,     /* the CUDA runtime refused the launch */
+    TFB_ENODEVICE = 5    /* no sm_100 device is current */
+};
+
+TFB_API int tfb_version(void);
+TFB_API const char* tfb_status_string(int status);
+/* Text of the last CUDA runtime error a launch returned on this thread ("" if none). */
+TFB_API const char* tfb_last_error(void);
+
+/* ---- embedding row gather -------------------------------------------------
+ * out[r, :] = table[ids[r], :] * scale (scale == 1 copies bits).
+ * Stands in for `embed`: tests/models/qwen3_1_7b/model.py:311-318 (scale 1),
+ * tests/models/minicpm3_4b/model.py:359 and
+ * examples/granite_4_0_h_small-cuda/model.py:615 (scale 12, a bf16 multiply). */
+TFB_API int tfb_embed(const void* table, const int64_t* ids, void* out, int32_t rows, int32_t hidden,
+              int64_t vocab, float scale, tfb_stream_t stream);
+
+/* ---- RMSNorm --------------------------------------------------------------
+ * mode TFB_NORM_F32GAIN: y = bf16(x32 * rsqrt(mean(x32^2)+eps) * gamma32)      (tf.rms_norm,
+ *      src/tilefoundry/ir/hir/nn/rms_norm.py:103-110)
+ * mode TFB_NORM_CAST_THEN_GAIN: y = bf16(bf16(x32 * rsqrt(..)) * gamma)          (the spelled-out
+ *      Qwen3RMSNorm, tests/models/qwen3_1_7b/model.py:127-138, :321-329) */
+enum { TFB_NORM_NONE = 0, TFB_NORM_F32GAIN = 1, TFB_NORM_CAST_THEN_GAIN = 2 };
+TFB_API int tfb_rmsnorm(const void* x, const void* gamma, void* y, int32_t rows, int32_t width, float eps,
+                int32_t mode, tfb_stream_t stream);
+
+/* ---- weight-streaming projection (batch-1 GEMV) ----------------------------
+ * y = epilogue( W . prologue(x) ),  W stored [n, k] row-major ("out, in": one
+ * output's weights contiguous), x a length-k vector.
+ *
+ * prologue: TFB_NORM_* applied to x with `gamma`/`eps` (fused RMSNorm), then
+ *           multiplied by x_scale if x_scale != 1 (bf16 multiply).
+ * epilogue: TFB_EPI_STORE     y[i] = bf16(acc)
+ *           TFB_EPI_RESIDUAL  y[i] = bf16(residual[i] + bf16(bf16(acc) * res_scale))
+ *           TFB_EPI_SWIGLU    y[i] = bf16(bf16(silu(bf16(acc_gate))) * bf16(acc_up)), gate rows
+ *                             from w, up rows from w2, both [n, k]
+ *           TFB_EPI_STORE_F32 y[i] = acc * out_scale (f32 output)
+ * Accumulation is f32.  `prefetch`/`prefetch_bytes` name a byte range (the next
+ * projection's weights) that this launch asks the L2 to fetch while it runs.
+ * pdl != 0 launches with programmatic stream serialisation: the kernel starts its
+ * weight loads before the preceding kernel in the stream has finished and waits
+ * for it only before reading x / residual.
+ *
+ * Stands in for the matmuls of self_attention / mlp (tests/models/qwen3_1_7b/
+ * model.py:161-172,214-216,231-235) and their fused norms; reference kernels:
+ * examples/qwen3_1_7b-tilelang/fast/kernels.py:124-260,
+ * examples/granite_4_0_h_small-cuda/kernels/granite.cu:81-157. */
+enum { TFB_EPI_STORE = 0, TFB_EPI_RESIDUAL = 1, TFB_EPI_SWIGLU = 2, TFB_EPI_STORE_F32 = 3 };
+typedef struct {
+    const void* w;
+    const void* w2;
+    const void* x;
+    const void* gamma;
+    const void* residual;
+    void* y;
+    int32_t n, k;
+    int32_t prologue;
+    int32_t epilogue;
+    float eps, x_scale, res_scale, out_scale;
+    const void* prefetch;
+    uint64_t prefetch_bytes;
+    int32_t pdl;
+    int32_t reserved;
+} tfb_gemv_args;
+TFB_API int tfb_gemv(const tfb_gemv_args* args, tfb_stream_t stream);
+
+/* ---- lm_head + greedy pick -------------------------------------------------
+ * logits[i] = bf16( W[i,:] . prologue(x) * out_scale ), token = argmax over the bf16
+ * logits with the lowest index winning ties (torch.argmax), all in one launch.
+ * scratch_val/scratch_idx hold one (max, index) pair per CTA; `counter` is a
+ * zero-initialised uint32 the kernel returns to zero.  Capacity needed:
+ * tfb_lm_head_scratch_entries(n).  `logits` may be NULL to skip the store.
+ * Stands in for lm_head + greedy: tests/models/qwen3_1_7b/model.py:332-336,
+ * tests/models/orchestrator/causal_lm/generation.py:24-26; reference kernel
+ * examples/qwen3_1_7b-tilelang/fast/kernels.py:261-328. */
+typedef struct {
+    const void* w;          /* [n, k] */
+    const void* x;          /* [k] bf16 */
+    const void* gamma;      /* [k] or NULL */
+    void* logits;           /* [n] bf16 or NULL */
+    int64_t* token_out;     /* [1] */
+    float* scratch_val;
+    int32_t* scratch_idx;
+    uint32_t* counter;
+    int32_t n, k;
+    int32_t prologue;
+    float eps, x_scale, out_scale;
+    int32_t pdl;
+    /* optional generation bookkeeping done by the same launch (all may be NULL):
+     * tokens[pos+1] = (pos+1 < n_prompt) ? tokens[pos+1] : token;  pos += 1 */
+    int64_t* tokens;
+    int32_t* pos;
+    int32_t n_prompt;
+    int32_t max_tokens;
+} tfb_lm_head_args;
+TFB_API int32_t tfb_lm_head_scratch_entries(int32_t n);
+TFB_API int tfb_lm_head_argmax(const tfb_lm_head_args* args, tfb_stream_t stream);
+
+/* ---- GQA decode attention over a paged KV cache ----------------------------
+ * One launch: per-head q/k RMSNorm (optional) -> RoPE on the first rotary_dim
+ * dims (rotate-half; 0 = none) -> append this token's K,V at position *pos ->
+ * split-KV online-softmax attention over positions [0, *pos] -> merged bf16
+ * output [hq*d].  Cache layout per layer: pool[page][slot][hkv][d], page_size
+ * slots per page; logical position p lives in page block_table[p / page_size],
+ * slot p % page_size.  k_new_out/v_new_out (optional) receive this token's entry
+ * [hkv*d] as the authored function returns it.
+ * q is scaled as the authored step does: q_s = bf16(q_rope * scale).
+ * Scratch: part_o f32 [hq][splits][d], part_ml f32 [hq][splits][2], counters
+ * uint32 [hkv] zero-initialised (returned to zero), where
+ * splits = tfb_attn_splits(max_ctx).
+ * Stands in for self_attention between the projections:
+ * tests/models/qwen3_1_7b/model.py:173-213; reference kernels
+ * examples/qwen3_1_7b-tilelang/fast/kernels.py:329-547. */
+typedef struct {
+    const void* qkv;        /* [hq*d | hkv*d | hkv*d] bf16, this token */
+    const void* gamma_q;    /* [d] or NULL */
+    const void* gamma_k;    /* [d] or NULL */
+    const void* cos_table;  /* [max_pos, rotary_dim] bf16 (NULL if rotary_dim == 0) */
+    const void* sin_table;
+    const int32_t* pos;     /* device scalar: position of this token == prior context length */
+    const int32_t* rope_pos;/* device scalar: row of the rotary tables to use; NULL = *pos */
+    void* k_pool;
+    void* v_pool;
+    const int32_t* block_table;
+    void* out;              /* [hq*d] bf16 */
+    void* k_new_out;        /* optional [hkv*d] */
+    void* v_new_out;        /* optional [hkv*d] */
+    float* part_o;
+    float* part_ml;
+    uint32_t* counters;
+    int32_t hq, hkv, d, rotary_dim;
+    int32_t page_size, table_len, max_ctx, max_pos;
+    float eps, scale;
+    int32_t norm_mode;      /* TFB_NORM_NONE or TFB_NORM_CAST_THEN_GAIN */
+    int32_t pdl;
+    const void* prefetch;
+    uint64_t prefetch_bytes;
+} tfb_attn_gqa_args;
+TFB_API int32_t tfb_attn_splits(int32_t max_ctx);
+TFB_API int tfb_attn_gqa_decode(const tfb_attn_gqa_args* args, tfb_stream_t stream);
+
+/* ---- a whole Qwen3-architecture decode step --------------------------------
+ * embed -> layers x [norm+qkv, attention, o+residual, norm+gate/up+SwiGLU,
+ * down+residual] -> final norm + lm_head + greedy pick + position advance, enqueued
+ * back to back with programmatic dependent launch.  The caller owns every buffer
+ * (weights packed [out, in]; w_qkv = q|k|v rows, w_gate / w_up separate).
+ * Reads tokens[*pos]; leaves the picked token in tokens[*pos + 1] unless that slot
+ * is still inside the prompt, and advances *pos.  Capturable in a CUDA graph.
+ * Stands in for Qwen3_1_7B.forward + append_cache + greedy
+ * (tests/models/qwen3_1_7b/model.py:338-383); reference driver
+ * examples/qwen3_1_7b-tilelang/fast/engine.py:189-271. */
+typedef struct {
+    const void* gamma_in;
+    const void* w_qkv;      /* [(hq+2hkv)*d, hidden] */
+    const void* gamma_q;
+    const void* gamma_k;
+    const void* w_o;        /* [hidden, hq*d] */
+    const void* gamma_post;
+    const void* w_gate;     /* [inter, hidden] */
+    const void* w_up;       /* [inter, hidden] */
+    const void* w_down;     /* [hidden, inter] */
+    void* k_pool;
+    void* v_pool;
+} tfb_qwen3_layer;
+typedef struct {
+    const tfb_qwen3_layer* layers; /* host array [n_layers] */
+    int32_t n_layers, hidden, hq, hkv, d, inter;
+    int64_t vocab;
+    float eps, scale;
+    const void* w_embed;    /* [vocab, hidden] */
+    const void* gamma_final;
+    const void* w_head;     /* [vocab, hidden] (may equal w_embed when tied) */
+    const void* cos_table;
+    const void* sin_table;
+    int32_t max_pos, page_size, table_len, max_ctx;
+    const int32_t* block_table;
+    int64_t* tokens;
+    int32_t* pos;
+    int32_t n_prompt, max_tokens;
+    /* activations and scratch */
+    void* hidden_buf;       /* [hidden] bf16 residual stream */
+    void* qkv_buf;          /* [(hq+2hkv)*d] */
+    void* attn_buf;         /* [hq*d] */
+    void* act_buf;          /* [inter] */
+    void* logits;           /* [vocab] bf16 or NULL */
+    float* part_o;
+    float* part_ml;
+    uint32_t* counters;     /* [hkv + 1] zero-initialised: attention + lm_head */
+    float* head_val;
+    int32_t* head_idx;
+    void* hidden_trace;     /* optional [n_layers+1][hidden] bf16: residual stream after each layer, then final-normed */
+    int32_t pdl;
+    int32_t l2_prefetch;
+} tfb_qwen3_step_args;
+TFB_API int tfb_qwen3_decode_step(const tfb_qwen3_step_args* args, tfb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TFB200_H */

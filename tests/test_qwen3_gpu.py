@@ -1,0 +1,221 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU oracle -- Qwen3 architecture.
+
+Bars: integer outputs (token ids, page table) bit-exact; bf16 hidden states, cache
+entries and logits within rtol 2e-2 / atol 2e-2.
+"""
+import pytest
+import torch
+
+from oracle import evaluator, generation, ops as tf, qwen3_1_7b as oq
+from tests.helpers import ATOL, RTOL, assert_close_bf16
+from tilefoundry_b200.authored import qwen3_1_7b as q
+from tilefoundry_b200.authored.weights import random_weights
+from tilefoundry_b200.runtime import AllClose, DictResource, Equal, NanInf, check
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from tilefoundry_b200 import lib
+    lib.load()
+    return torch.device("cuda:0")
+
+
+def _cuda(weights, dev):
+    return {k: v.to(dev) for k, v in weights.items()}
+
+
+# ---- single kernels ---------------------------------------------------------------
+
+@pytest.mark.parametrize("n,k", [(4096, 2048), (2048, 2048), (2048, 6144), (1000, 768), (7, 256), (288, 2560)])
+def test_gemv_store_and_residual(dev, n, k):
+    from tilefoundry_b200 import lib
+    g = torch.Generator().manual_seed(n * 7 + k)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(BF)
+    x = torch.randn(k, generator=g).to(BF)
+    res = torch.randn(n, generator=g).to(BF)
+    want = tf.matmul(x[None], w.t())[0]
+    got = lib.gemv(w.to(dev), x.to(dev), torch.empty(n, device=dev, dtype=BF))
+    assert_close_bf16(got, want, f"gemv {n}x{k}")
+    got = lib.gemv(w.to(dev), x.to(dev), torch.empty(n, device=dev, dtype=BF), residual=res.to(dev),
+                   epilogue=lib.EPI_RESIDUAL)
+    assert_close_bf16(got, res + want, f"gemv+residual {n}x{k}")
+    got32 = lib.gemv(w.to(dev), x.to(dev), torch.empty(n, device=dev, dtype=torch.float32),
+                     epilogue=lib.EPI_STORE_F32)
+    torch.testing.assert_close(got32.cpu(), x.float() @ w.float().t(), rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_gemv_norm_prologue_and_swiglu(dev, mode):
+    from tilefoundry_b200 import lib
+    n, k, eps = 1536, 2048, 1e-6
+    g = torch.Generator().manual_seed(5)
+    wg = (torch.randn(n, k, generator=g) / k ** 0.5).to(BF)
+    wu = (torch.randn(n, k, generator=g) / k ** 0.5).to(BF)
+    x = torch.randn(k, generator=g).to(BF)
+    gamma = (1 + 0.1 * torch.randn(k, generator=g)).to(BF)
+    if mode == 2:
+        x32 = x.float()
+        xn = (x32 * torch.rsqrt((x32 * x32).mean(-1, keepdim=True) + eps)).to(BF) * gamma
+    else:
+        xn = tf.rms_norm(x, gamma, eps)
+    want = tf.silu(tf.matmul(xn[None], wg.t())) * tf.matmul(xn[None], wu.t())
+    got = lib.gemv(wg.to(dev), x.to(dev), torch.empty(n, device=dev, dtype=BF), w2=wu.to(dev),
+                   gamma=gamma.to(dev), prologue=mode, epilogue=lib.EPI_SWIGLU, eps=eps)
+    assert_close_bf16(got, want[0], f"norm{mode}+swiglu")
+    normed = lib.rmsnorm(x.to(dev), gamma.to(dev), torch.empty(k, device=dev, dtype=BF), eps, mode)
+    assert_close_bf16(normed, xn, f"rmsnorm mode {mode}", rtol=1e-2, atol=1e-2)
+
+
+def test_gemv_rejects_bad_arguments(dev):
+    from tilefoundry_b200 import lib
+    w = torch.zeros(8, 100, device=dev, dtype=BF)          # k not a multiple of 256
+    with pytest.raises(RuntimeError, match="invalid argument"):
+        lib.gemv(w, torch.zeros(100, device=dev, dtype=BF), torch.zeros(8, device=dev, dtype=BF))
+    with pytest.raises(ValueError, match="CUDA tensors"):
+        lib.gemv(torch.zeros(8, 256, dtype=BF), torch.zeros(256, dtype=BF), torch.zeros(8, dtype=BF))
+
+
+# ---- functions through the twin boundary, judged by check() ---------------------------
+
+def _sides(cfg, dev, seed=3, std=0.05):
+    from tilefoundry_b200.twins.qwen3_1_7b import make_twin
+    mod = q.build(cfg)
+    weights = q.tie_head(random_weights(mod, seed=seed, std=std))
+    ref = evaluator.load(mod, DictResource(weights), oq.make(cfg))
+    twin = make_twin(cfg)()
+    twin.load(DictResource(_cuda(weights, dev)))
+    return ref, twin
+
+
+def _on_cpu(fn):
+    def run(*args):
+        out = fn(*[a.cpu() if isinstance(a, torch.Tensor) else a for a in args])
+        return out
+    return run
+
+
+def _to_cpu(x):
+    return tuple(_to_cpu(i) for i in x) if isinstance(x, tuple) else x.cpu()
+
+
+def _layer_inputs(cfg, ctx, dev, seed=1):
+    g = torch.Generator().manual_seed(seed)
+    cos, sin = q.rope_tables(cfg)
+    hidden = (torch.randn(1, 1, cfg.hidden_size, generator=g)).to(BF)
+    kc = (torch.randn(1, ctx, cfg.num_key_value_heads, cfg.head_dim, generator=g)).to(BF)
+    vc = (torch.randn(1, ctx, cfg.num_key_value_heads, cfg.head_dim, generator=g)).to(BF)
+    pos = torch.tensor([ctx], dtype=torch.int32)
+    scale = torch.full((1, 1, 1, 1), cfg.head_dim ** -0.5, dtype=BF)
+    return tuple(t.to(dev) for t in (hidden, cos, sin, pos, kc, vc, scale))
+
+
+CLOSE = [AllClose(atol=ATOL, rtol=RTOL), NanInf()]
+
+
+@pytest.mark.parametrize("ctx", [0, 1, 24, 127, 128, 129, 300])
+def test_decoder_layer_against_evaluator_tiny(dev, ctx):
+    cfg = q.QWEN3_TINY
+    ref, twin = _sides(cfg, dev)
+    inputs = _layer_inputs(cfg, ctx, dev)
+    for fn in ("self_attention", "decoder_layer"):
+        report = check(lambda *a: _to_cpu(getattr(twin.layer0, fn)(*a)), _on_cpu(getattr(ref.layer0, fn)),
+                       inputs, expect={"output[0]": CLOSE, "output[1]": CLOSE, "output[2]": [Equal()]})
+        assert report.passed, f"{fn} ctx={ctx}\n{report.render()}"
+    h = inputs[0]
+    for fn in ("mlp", "placed_mlp", "input_rms_norm"):
+        report = check(lambda *a: _to_cpu(getattr(twin.layer0, fn)(*a)), _on_cpu(getattr(ref.layer0, fn)),
+                       (h,), expect={"output": CLOSE})
+        assert report.passed, f"{fn}\n{report.render()}"
+
+
+def test_full_size_layer_against_evaluator(dev):
+    # one layer at the 1.7B dimensions, ctx of a few hundred positions
+    cfg = q.Qwen3Config(num_hidden_layers=1, vocab_size=4096)
+    ref, twin = _sides(cfg, dev, std=0.02)
+    inputs = _layer_inputs(cfg, 333, dev)
+    report = check(lambda *a: _to_cpu(twin.layer0.decoder_layer(*a)), _on_cpu(ref.layer0.decoder_layer),
+                   inputs, expect={"output[0]": CLOSE, "output[1]": CLOSE, "output[2]": [Equal()]})
+    assert report.passed, report.render()
+    ids = torch.tensor([17], dtype=torch.int64)
+    report = check(lambda i: twin.embed(i.to(dev)).cpu(), ref.embed, (ids,), expect={"output": [Equal()]})
+    assert report.passed
+    hidden = inputs[0]
+    report = check(lambda h: twin.lm_head(twin.final_rms_norm(h)).cpu(),
+                   lambda h: ref.lm_head(ref.final_rms_norm(h.cpu())), (hidden,), expect={"output": CLOSE})
+    assert report.passed, report.render()
+    want_tok = int(torch.argmax(ref.lm_head(ref.final_rms_norm(hidden.cpu()))))
+    got_logits = twin.lm_head(twin.final_rms_norm(hidden))
+    # the kernel's own pick must be the lowest-index maximum of the bf16 logits it wrote
+    assert int(twin.last_token) == int(torch.argmax(got_logits.cpu()))
+    if float(torch.topk(got_logits.float().flatten(), 2).values.diff().abs()) > 0.03:
+        assert int(twin.last_token) == want_tok
+
+
+# ---- the whole model: session (captured step) vs the evaluator's greedy loop ----------------
+
+def _session_vs_oracle(cfg, dev, n_prompt, n_new, seed, std, use_graph):
+    from tilefoundry_b200.engine.qwen3 import Qwen3Session
+    from tilefoundry_b200.engine import paged_kv
+    mod = q.build(cfg)
+    weights = q.tie_head(random_weights(mod, seed=seed, std=std))
+    ref = evaluator.load(mod, DictResource(weights), oq.make(cfg))
+    g = torch.Generator().manual_seed(seed + 100)
+    prompt = torch.randint(0, cfg.vocab_size, (n_prompt,), generator=g)
+    want = generation.decode_ids(ref, prompt, n_new, keep_logits=True)
+
+    sess = Qwen3Session(cfg, DictResource(_cuda(weights, dev)), max_ctx=n_prompt + n_new + 5, device=dev,
+                        keep_logits=True, trace_hidden=True)
+    sess.reset(prompt)
+    if use_graph:
+        sess.capture()
+    got_logits = []
+    for _ in range(n_prompt + n_new - 1):
+        sess.run(1, use_graph)
+        got_logits.append(sess.logits.clone())
+    torch.cuda.synchronize()
+    return ref, want, sess, got_logits, prompt
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_session_matches_evaluator_tiny(dev, use_graph):
+    cfg = q.QWEN3_TINY
+    n_prompt, n_new = 24, 140          # crosses the 128-position split and the 64-slot page boundaries
+    ref, want, sess, got_logits, prompt = _session_vs_oracle(cfg, dev, n_prompt, n_new, 11, 0.05, use_graph)
+    total = n_prompt + n_new - 1
+    # token ids: bit-exact
+    got_tokens = sess.tokens[n_prompt: n_prompt + n_new].cpu().tolist()
+    assert got_tokens == want["tokens"], (got_tokens, want["tokens"])
+    assert int(sess.pos) == total
+    # logits at every step
+    for step in range(total):
+        assert_close_bf16(got_logits[step], want["logits"][step][0], f"logits step {step}")
+    # the cache the session built equals the evaluator's appended caches
+    from tilefoundry_b200.engine import paged_kv
+    assert torch.equal(sess.table.cpu(), paged_kv.block_table(1, sess.max_ctx))
+    for li, (k_ref, v_ref) in enumerate(want["caches"]):
+        k_got = paged_kv.logical_view(sess.layers[li]["k_pool"], sess.table[0], total)
+        v_got = paged_kv.logical_view(sess.layers[li]["v_pool"], sess.table[0], total)
+        assert_close_bf16(k_got, k_ref[:, :total], f"layer {li} K cache")
+        assert_close_bf16(v_got, v_ref[:, :total], f"layer {li} V cache")
+
+
+def test_generate_equals_stepwise_and_is_idempotent(dev):
+    from tilefoundry_b200.engine.qwen3 import Qwen3Session
+    cfg = q.QWEN3_TINY
+    mod = q.build(cfg)
+    weights = q.tie_head(random_weights(mod, seed=2, std=0.05))
+    sess = Qwen3Session(cfg, DictResource(_cuda(weights, dev)), max_ctx=200, device=dev)
+    prompt = torch.arange(5, 25)
+    a = sess.generate(prompt, 100).tokens
+    b = sess.generate(prompt, 100, use_graph=False).tokens
+    c = sess.generate(prompt, 100).tokens
+    assert a == b == c
+    with pytest.raises(ValueError, match="exceed capacity"):
+        sess.generate(prompt, 500)
+    with pytest.raises(ValueError, match="at least one token"):
+        sess.generate([], 4)

@@ -1,0 +1,267 @@
+// extern "C" entry points: host-side validation, then enqueue.  See include/tfb200.h.
+#include "../../include/tfb200.h"
+#include "kernels.h"
+
+#include <cstdio>
+#include <cstring>
+
+namespace {
+
+thread_local char g_last_error[256] = "";
+
+int fail_launch(cudaError_t e) {
+    std::snprintf(g_last_error, sizeof g_last_error, "%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
+    cudaGetLastError();  // clear the sticky-free error so later launches report their own
+    return TFB_ELAUNCH;
+}
+inline int done(cudaError_t e) { return e == cudaSuccess ? TFB_OK : fail_launch(e); }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline cudaStream_t S(tfb_stream_t s) { return static_cast<cudaStream_t>(s); }
+
+#define TFB_REQUIRE(cond, code)      \
+    do {                             \
+        if (!(cond)) return (code);  \
+    } while (0)
+
+}  // namespace
+
+extern "C" {
+
+int tfb_version(void) { return 100; }
+
+const char* tfb_status_string(int status) {
+    switch (status) {
+        case TFB_OK: return "ok";
+        case TFB_EINVAL: return "invalid argument (size, null pointer or unsupported combination)";
+        case TFB_EALIGN: return "pointer or row stride is not 16-byte aligned";
+        case TFB_ECAPACITY: return "position or context exceeds the capacity given";
+        case TFB_ELAUNCH: return "the CUDA runtime refused the launch (see tfb_last_error)";
+        case TFB_ENODEVICE: return "no sm_100 device is current";
+        default: return "unknown status";
+    }
+}
+
+const char* tfb_last_error(void) { return g_last_error; }
+
+int tfb_embed(const void* table, const int64_t* ids, void* out, int32_t rows, int32_t hidden,
+              int64_t vocab, float scale, tfb_stream_t stream) {
+    TFB_REQUIRE(table && ids && out, TFB_EINVAL);
+    TFB_REQUIRE(rows >= 0 && hidden > 0 && vocab > 0 && hidden % 8 == 0, TFB_EINVAL);
+    TFB_REQUIRE(aligned16(table) && aligned16(out), TFB_EALIGN);
+    if (rows == 0) return TFB_OK;
+    return done(tfb::embed_launch(static_cast<const uint16_t*>(table),
+                                  reinterpret_cast<const long long*>(ids), nullptr, nullptr,
+                                  static_cast<uint16_t*>(out), rows, hidden, vocab, scale, S(stream), false));
+}
+
+int tfb_rmsnorm(const void* x, const void* gamma, void* y, int32_t rows, int32_t width, float eps,
+                int32_t mode, tfb_stream_t stream) {
+    TFB_REQUIRE(x && gamma && y, TFB_EINVAL);
+    TFB_REQUIRE(rows >= 0 && width > 0, TFB_EINVAL);
+    TFB_REQUIRE(mode == TFB_NORM_F32GAIN || mode == TFB_NORM_CAST_THEN_GAIN, TFB_EINVAL);
+    if (rows == 0) return TFB_OK;
+    return done(tfb::rmsnorm_launch(static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(gamma),
+                                    static_cast<uint16_t*>(y), rows, width, eps, mode, S(stream), false));
+}
+
+static int gemv_checked(const tfb_gemv_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->w && a->x && a->y, TFB_EINVAL);
+    TFB_REQUIRE(a->n > 0 && a->k > 0 && a->k % 256 == 0 && a->k <= 16384, TFB_EINVAL);
+    TFB_REQUIRE(a->prologue >= TFB_NORM_NONE && a->prologue <= TFB_NORM_CAST_THEN_GAIN, TFB_EINVAL);
+    TFB_REQUIRE(a->epilogue >= TFB_EPI_STORE && a->epilogue <= TFB_EPI_STORE_F32, TFB_EINVAL);
+    TFB_REQUIRE(a->prologue == TFB_NORM_NONE || a->gamma, TFB_EINVAL);
+    TFB_REQUIRE(a->epilogue != TFB_EPI_RESIDUAL || a->residual, TFB_EINVAL);
+    TFB_REQUIRE(a->epilogue != TFB_EPI_SWIGLU || a->w2, TFB_EINVAL);
+    TFB_REQUIRE(aligned16(a->w) && aligned16(a->x) && (!a->w2 || aligned16(a->w2)) &&
+                    (!a->gamma || aligned16(a->gamma)), TFB_EALIGN);
+    TFB_REQUIRE(!a->prefetch || (aligned16(a->prefetch) && a->prefetch_bytes % 16 == 0), TFB_EALIGN);
+    tfb::GemvParams p;
+    p.w = static_cast<const uint4*>(a->w);
+    p.w2 = static_cast<const uint4*>(a->w2);
+    p.x = static_cast<const uint16_t*>(a->x);
+    p.gamma = static_cast<const uint16_t*>(a->gamma);
+    p.residual = static_cast<const uint16_t*>(a->residual);
+    p.y = a->y;
+    p.n = a->n;
+    p.k = a->k;
+    p.eps = a->eps;
+    p.x_scale = a->x_scale;
+    p.res_scale = a->res_scale;
+    p.out_scale = a->out_scale;
+    p.prefetch = a->prefetch;
+    p.prefetch_bytes = a->prefetch_bytes;
+    return done(tfb::gemv_dispatch(p, a->prologue, a->epilogue, S(stream), a->pdl != 0));
+}
+
+int tfb_gemv(const tfb_gemv_args* args, tfb_stream_t stream) { return gemv_checked(args, stream); }
+
+int32_t tfb_lm_head_scratch_entries(int32_t n) { return n > 0 ? tfb::lm_head_ctas(n) : 0; }
+
+int tfb_lm_head_argmax(const tfb_lm_head_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->w && a->x && a->scratch_val && a->scratch_idx && a->counter, TFB_EINVAL);
+    TFB_REQUIRE(a->token_out || (a->tokens && a->pos), TFB_EINVAL);
+    TFB_REQUIRE(a->n > 0 && a->k > 0 && a->k % 256 == 0 && a->k <= 8192, TFB_EINVAL);
+    TFB_REQUIRE(a->prologue >= TFB_NORM_NONE && a->prologue <= TFB_NORM_CAST_THEN_GAIN, TFB_EINVAL);
+    TFB_REQUIRE(a->prologue == TFB_NORM_NONE || a->gamma, TFB_EINVAL);
+    TFB_REQUIRE(aligned16(a->w) && aligned16(a->x) && (!a->gamma || aligned16(a->gamma)), TFB_EALIGN);
+    tfb::HeadParams p;
+    p.w = static_cast<const uint4*>(a->w);
+    p.x = static_cast<const uint16_t*>(a->x);
+    p.gamma = static_cast<const uint16_t*>(a->gamma);
+    p.logits = static_cast<uint16_t*>(a->logits);
+    p.token_out = reinterpret_cast<long long*>(a->token_out);
+    p.scratch_val = a->scratch_val;
+    p.scratch_idx = a->scratch_idx;
+    p.counter = a->counter;
+    p.n = a->n;
+    p.k = a->k;
+    p.eps = a->eps;
+    p.x_scale = a->x_scale;
+    p.out_scale = a->out_scale;
+    p.tokens = reinterpret_cast<long long*>(a->tokens);
+    p.pos = a->pos;
+    p.n_prompt = a->n_prompt;
+    p.max_tokens = a->max_tokens;
+    return done(tfb::lm_head_dispatch(p, a->prologue, S(stream), a->pdl != 0));
+}
+
+int32_t tfb_attn_splits(int32_t max_ctx) { return max_ctx > 0 ? tfb::attn_splits(max_ctx) : 0; }
+
+int tfb_attn_gqa_decode(const tfb_attn_gqa_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->qkv && a->pos && a->k_pool && a->v_pool && a->block_table && a->out, TFB_EINVAL);
+    TFB_REQUIRE(a->part_o && a->part_ml && a->counters, TFB_EINVAL);
+    TFB_REQUIRE(a->hq > 0 && a->hkv > 0 && a->hq % a->hkv == 0, TFB_EINVAL);
+    TFB_REQUIRE(a->d == 64 || a->d == 128, TFB_EINVAL);
+    TFB_REQUIRE(a->rotary_dim >= 0 && a->rotary_dim <= a->d && a->rotary_dim % 2 == 0, TFB_EINVAL);
+    TFB_REQUIRE(a->rotary_dim == 0 || (a->cos_table && a->sin_table), TFB_EINVAL);
+    TFB_REQUIRE(a->page_size > 0 && a->table_len > 0 && a->max_ctx > 0, TFB_EINVAL);
+    TFB_REQUIRE(a->norm_mode == TFB_NORM_NONE || a->norm_mode == TFB_NORM_CAST_THEN_GAIN, TFB_EINVAL);
+    TFB_REQUIRE(a->norm_mode == TFB_NORM_NONE || (a->gamma_q && a->gamma_k), TFB_EINVAL);
+    TFB_REQUIRE((long long)a->page_size * a->table_len >= a->max_ctx, TFB_ECAPACITY);
+    TFB_REQUIRE(a->rotary_dim == 0 || a->max_pos >= a->max_ctx, TFB_ECAPACITY);
+    TFB_REQUIRE(aligned16(a->k_pool) && aligned16(a->v_pool) && aligned16(a->qkv), TFB_EALIGN);
+    tfb::AttnParams p;
+    p.qkv = static_cast<const uint16_t*>(a->qkv);
+    p.gamma_q = static_cast<const uint16_t*>(a->gamma_q);
+    p.gamma_k = static_cast<const uint16_t*>(a->gamma_k);
+    p.cos_table = static_cast<const uint16_t*>(a->cos_table);
+    p.sin_table = static_cast<const uint16_t*>(a->sin_table);
+    p.pos = a->pos;
+    p.rope_pos = a->rope_pos;
+    p.k_pool = static_cast<uint16_t*>(a->k_pool);
+    p.v_pool = static_cast<uint16_t*>(a->v_pool);
+    p.block_table = a->block_table;
+    p.out = static_cast<uint16_t*>(a->out);
+    p.k_new_out = static_cast<uint16_t*>(a->k_new_out);
+    p.v_new_out = static_cast<uint16_t*>(a->v_new_out);
+    p.part_o = a->part_o;
+    p.part_ml = a->part_ml;
+    p.counters = a->counters;
+    p.hq = a->hq;
+    p.hkv = a->hkv;
+    p.d = a->d;
+    p.rotary_dim = a->rotary_dim;
+    p.page_size = a->page_size;
+    p.max_ctx = a->max_ctx;
+    p.nsplit = tfb::attn_splits(a->max_ctx);
+    p.eps = a->eps;
+    p.scale = a->scale;
+    p.norm_mode = a->norm_mode;
+    p.prefetch = a->prefetch;
+    p.prefetch_bytes = a->prefetch_bytes;
+    const int G = a->hq / a->hkv;
+    TFB_REQUIRE(G == 1 || G == 2 || (G == 4 && a->d == 128), TFB_EINVAL);
+    return done(tfb::attn_gqa_dispatch(p, S(stream), a->pdl != 0));
+}
+
+int tfb_qwen3_decode_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->layers && a->n_layers > 0, TFB_EINVAL);
+    TFB_REQUIRE(a->w_embed && a->gamma_final && a->w_head && a->tokens && a->pos, TFB_EINVAL);
+    TFB_REQUIRE(a->hidden_buf && a->qkv_buf && a->attn_buf && a->act_buf, TFB_EINVAL);
+    TFB_REQUIRE(a->part_o && a->part_ml && a->counters && a->head_val && a->head_idx, TFB_EINVAL);
+    TFB_REQUIRE(a->hidden % 256 == 0 && a->inter % 256 == 0 && (a->hq * a->d) % 256 == 0, TFB_EINVAL);
+    TFB_REQUIRE((long long)a->page_size * a->table_len >= a->max_ctx, TFB_ECAPACITY);
+    TFB_REQUIRE(a->max_pos >= a->max_ctx && a->max_tokens <= a->max_ctx + 1, TFB_ECAPACITY);
+    const bool pdl = a->pdl != 0;
+    const bool pf = a->l2_prefetch != 0;
+    const int H = a->hidden, QP = a->hq * a->d, KVP = a->hkv * a->d, I = a->inter;
+    const int NQKV = QP + 2 * KVP;
+    cudaStream_t st = S(stream);
+    uint16_t* hid = static_cast<uint16_t*>(a->hidden_buf);
+    uint16_t* trace = static_cast<uint16_t*>(a->hidden_trace);
+
+    cudaError_t e = tfb::embed_launch(static_cast<const uint16_t*>(a->w_embed), nullptr,
+                                      reinterpret_cast<const long long*>(a->tokens), a->pos, hid, 1, H,
+                                      a->vocab, 1.f, st, pdl);
+    if (e != cudaSuccess) return fail_launch(e);
+
+    for (int l = 0; l < a->n_layers; ++l) {
+        const tfb_qwen3_layer& L = a->layers[l];
+        const tfb_qwen3_layer* next = (l + 1 < a->n_layers) ? &a->layers[l + 1] : nullptr;
+        tfb_gemv_args g;
+        // 1. input norm + q|k|v projection
+        std::memset(&g, 0, sizeof g);
+        g.w = L.w_qkv; g.x = hid; g.gamma = L.gamma_in; g.y = a->qkv_buf;
+        g.n = NQKV; g.k = H; g.prologue = TFB_NORM_CAST_THEN_GAIN; g.epilogue = TFB_EPI_STORE;
+        g.eps = a->eps; g.x_scale = 1.f; g.res_scale = 1.f; g.out_scale = 1.f; g.pdl = pdl;
+        if (pf) { g.prefetch = L.w_o; g.prefetch_bytes = 2ull * H * QP; }
+        int rc = gemv_checked(&g, stream);
+        if (rc) return rc;
+        // 2. q/k norm, RoPE, KV append, attention
+        tfb_attn_gqa_args t;
+        std::memset(&t, 0, sizeof t);
+        t.qkv = a->qkv_buf; t.gamma_q = L.gamma_q; t.gamma_k = L.gamma_k;
+        t.cos_table = a->cos_table; t.sin_table = a->sin_table; t.pos = a->pos;
+        t.k_pool = L.k_pool; t.v_pool = L.v_pool; t.block_table = a->block_table; t.out = a->attn_buf;
+        t.part_o = a->part_o; t.part_ml = a->part_ml; t.counters = a->counters;
+        t.hq = a->hq; t.hkv = a->hkv; t.d = a->d; t.rotary_dim = a->d;
+        t.page_size = a->page_size; t.table_len = a->table_len; t.max_ctx = a->max_ctx; t.max_pos = a->max_pos;
+        t.eps = a->eps; t.scale = a->scale; t.norm_mode = TFB_NORM_CAST_THEN_GAIN; t.pdl = pdl;
+        if (pf) { t.prefetch = L.w_gate; t.prefetch_bytes = 2ull * I * H; }
+        rc = tfb_attn_gqa_decode(&t, stream);
+        if (rc) return rc;
+        // 3. output projection + residual
+        std::memset(&g, 0, sizeof g);
+        g.w = L.w_o; g.x = a->attn_buf; g.residual = hid; g.y = hid;
+        g.n = H; g.k = QP; g.prologue = TFB_NORM_NONE; g.epilogue = TFB_EPI_RESIDUAL;
+        g.eps = a->eps; g.x_scale = 1.f; g.res_scale = 1.f; g.out_scale = 1.f; g.pdl = pdl;
+        if (pf) { g.prefetch = L.w_up; g.prefetch_bytes = 2ull * I * H; }
+        rc = gemv_checked(&g, stream);
+        if (rc) return rc;
+        // 4. post-attention norm + gate/up + SwiGLU
+        std::memset(&g, 0, sizeof g);
+        g.w = L.w_gate; g.w2 = L.w_up; g.x = hid; g.gamma = L.gamma_post; g.y = a->act_buf;
+        g.n = I; g.k = H; g.prologue = TFB_NORM_CAST_THEN_GAIN; g.epilogue = TFB_EPI_SWIGLU;
+        g.eps = a->eps; g.x_scale = 1.f; g.res_scale = 1.f; g.out_scale = 1.f; g.pdl = pdl;
+        if (pf) { g.prefetch = L.w_down; g.prefetch_bytes = 2ull * I * H; }
+        rc = gemv_checked(&g, stream);
+        if (rc) return rc;
+        // 5. down projection + residual
+        std::memset(&g, 0, sizeof g);
+        g.w = L.w_down; g.x = a->act_buf; g.residual = hid; g.y = hid;
+        g.n = H; g.k = I; g.prologue = TFB_NORM_NONE; g.epilogue = TFB_EPI_RESIDUAL;
+        g.eps = a->eps; g.x_scale = 1.f; g.res_scale = 1.f; g.out_scale = 1.f; g.pdl = pdl;
+        if (pf && next) { g.prefetch = next->w_qkv; g.prefetch_bytes = 2ull * NQKV * H; }
+        rc = gemv_checked(&g, stream);
+        if (rc) return rc;
+        if (trace) {
+            e = tfb::copy_launch(hid, trace + size_t(l) * H, H * 2, st, pdl);
+            if (e != cudaSuccess) return fail_launch(e);
+        }
+    }
+    if (trace) {
+        e = tfb::rmsnorm_launch(hid, static_cast<const uint16_t*>(a->gamma_final),
+                                trace + size_t(a->n_layers) * H, 1, H, a->eps, TFB_NORM_CAST_THEN_GAIN, st, pdl);
+        if (e != cudaSuccess) return fail_launch(e);
+    }
+    tfb_lm_head_args h;
+    std::memset(&h, 0, sizeof h);
+    h.w = a->w_head; h.x = hid; h.gamma = a->gamma_final; h.logits = a->logits;
+    h.scratch_val = a->head_val; h.scratch_idx = a->head_idx; h.counter = a->counters + a->hkv;
+    h.n = int(a->vocab); h.k = H; h.prologue = TFB_NORM_CAST_THEN_GAIN; h.eps = a->eps;
+    h.x_scale = 1.f; h.out_scale = 1.f; h.pdl = pdl;
+    h.tokens = a->tokens; h.pos = a->pos; h.n_prompt = a->n_prompt; h.max_tokens = a->max_tokens;
+    return tfb_lm_head_argmax(&h, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,153 @@
+// Batch-1 weight-streaming projections: y = epilogue(W . prologue(x)).
+//
+// HBM-bound: per output row the kernel reads 2k bytes of weights once and does 2k
+// flops.  Algorithmic bytes per launch = n*k*2 (x2 for SwiGLU) -- activations are
+// a few KB and stay in L2.
+#include "gemv.cuh"
+#include "kernels.h"
+#include "launch.h"
+
+namespace tfb {
+
+
+// WARPS warps per CTA; KSPLIT of them share one group of ROWS rows, each taking a
+// contiguous slice of K.  EPI: 0 store bf16, 1 residual, 2 SwiGLU, 3 store f32.
+template <int ROWS, int KSPLIT, int WARPS, int UNROLL, int NORM_MODE, int EPI>
+__global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
+    extern __shared__ __align__(16) float smem[];
+    float* xs = smem;                         // k floats
+    float* red = smem + p.k;                  // 32 floats
+    float* part = red + 32;                   // (WARPS/KSPLIT) * KSPLIT * ROWS * (EPI==2 ? 2 : 1)
+
+    constexpr int GROUPS = WARPS / KSPLIT;
+    constexpr int NMAT = (EPI == 2) ? 2 : 1;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int group = warp / KSPLIT, ks = warp % KSPLIT;
+    const int row0 = (blockIdx.x * GROUPS + group) * ROWS;
+    const int rows_valid = min(ROWS, p.n - row0);
+    const int row_stride = p.k >> 3;                       // uint4 per row
+    const int its = p.k >> 8;                              // 256 elements per warp iteration
+    const int it_per = (its + KSPLIT - 1) / KSPLIT;
+    const int it_begin = ks * it_per, it_end = min(its, it_begin + it_per);
+
+    // Weights do not depend on the preceding kernel: start streaming them now.
+    RowsDot<ROWS, UNROLL> a, b;
+    const uint4* wrow = p.w + size_t(max(row0, 0)) * row_stride;
+    const uint4* w2row = (EPI == 2) ? p.w2 + size_t(row0) * row_stride : nullptr;
+    a.load(wrow, row_stride, rows_valid, it_begin, it_end, lane);
+    if (EPI == 2) b.load(w2row, row_stride, rows_valid, it_begin, it_end, lane);
+    if (threadIdx.x == 0) l2_prefetch_slice(p.prefetch, p.prefetch_bytes, blockIdx.x, gridDim.x);
+
+    pdl_trigger();
+    pdl_wait();
+
+    stage_activation<NORM_MODE>(p.x, p.gamma, xs, red, p.k, p.eps, p.x_scale);
+    __syncthreads();
+
+    float acc[ROWS], acc2[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) { acc[r] = 0.f; acc2[r] = 0.f; }
+
+    for (int it0 = it_begin; it0 < it_end; it0 += UNROLL) {
+        a.fma(xs, it0, it_end, lane, acc);
+        if (EPI == 2) b.fma(xs, it0, it_end, lane, acc2);
+        if (it0 + UNROLL < it_end) {
+            a.load(wrow, row_stride, rows_valid, it0 + UNROLL, it_end, lane);
+            if (EPI == 2) b.load(w2row, row_stride, rows_valid, it0 + UNROLL, it_end, lane);
+        }
+    }
+
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        acc[r] = warp_sum(acc[r]);
+        if (EPI == 2) acc2[r] = warp_sum(acc2[r]);
+    }
+
+    if (KSPLIT > 1) {
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                part[((group * KSPLIT + ks) * ROWS + r) * NMAT] = acc[r];
+                if (EPI == 2) part[((group * KSPLIT + ks) * ROWS + r) * NMAT + 1] = acc2[r];
+            }
+        }
+        __syncthreads();
+        if (ks != 0) return;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            float s = 0.f, s2 = 0.f;
+#pragma unroll
+            for (int q = 0; q < KSPLIT; ++q) {         // fixed order: deterministic
+                s += part[((group * KSPLIT + q) * ROWS + r) * NMAT];
+                if (EPI == 2) s2 += part[((group * KSPLIT + q) * ROWS + r) * NMAT + 1];
+            }
+            acc[r] = s;
+            acc2[r] = s2;
+        }
+    }
+
+    if (lane < rows_valid) {
+        float v = 0.f, v2 = 0.f;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r)
+            if (lane == r) { v = acc[r]; v2 = acc2[r]; }
+        const int row = row0 + lane;
+        if (EPI == 0) {
+            static_cast<uint16_t*>(p.y)[row] = f32_to_bf16_bits(v);
+        } else if (EPI == 1) {
+            float o = round_bf16(v);
+            if (p.res_scale != 1.f) o = round_bf16(o * p.res_scale);
+            static_cast<uint16_t*>(p.y)[row] = f32_to_bf16_bits(bf16_bits_to_f32(p.residual[row]) + o);
+        } else if (EPI == 2) {
+            const float g = round_bf16(v), u = round_bf16(v2);
+            static_cast<uint16_t*>(p.y)[row] = f32_to_bf16_bits(round_bf16(silu_f32(g)) * u);
+        } else {
+            static_cast<float*>(p.y)[row] = v * p.out_scale;
+        }
+    }
+}
+
+template <int ROWS, int KSPLIT, int WARPS, int UNROLL, int NORM_MODE, int EPI>
+static cudaError_t launch_cfg(const GemvParams& p, cudaStream_t stream, bool pdl) {
+    constexpr int GROUPS = WARPS / KSPLIT;
+    constexpr int NMAT = (EPI == 2) ? 2 : 1;
+    const int rows_per_cta = GROUPS * ROWS;
+    const unsigned grid = (p.n + rows_per_cta - 1) / rows_per_cta;
+    const size_t smem = (size_t(p.k) + 32 + GROUPS * KSPLIT * ROWS * NMAT) * sizeof(float);
+    auto kern = gemv_kernel<ROWS, KSPLIT, WARPS, UNROLL, NORM_MODE, EPI>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return e;
+    }
+    return launch_kernel(kern, dim3(grid), dim3(WARPS * 32), smem, stream, pdl, p);
+}
+
+template <int NORM_MODE, int EPI>
+static cudaError_t pick_shape(const GemvParams& p, cudaStream_t stream, bool pdl) {
+    // Shape choice: enough warps to cover 148 SMs several times over, rows per warp
+    // and K-split chosen so one warp streams 4-8 KB.
+    const long long bytes = 2ll * p.n * p.k * (EPI == 2 ? 2 : 1);
+    if (EPI == 2) {
+        return launch_cfg<1, 1, 4, 4, NORM_MODE, EPI>(p, stream, pdl);
+    }
+    if (p.k >= 4096) {
+        return launch_cfg<2, 4, 8, 4, NORM_MODE, EPI>(p, stream, pdl);
+    }
+    if (bytes <= (12ll << 20)) {
+        return launch_cfg<2, 2, 4, 4, NORM_MODE, EPI>(p, stream, pdl);
+    }
+    return launch_cfg<2, 1, 4, 4, NORM_MODE, EPI>(p, stream, pdl);
+}
+
+cudaError_t gemv_dispatch(const GemvParams& p, int norm_mode, int epi, cudaStream_t stream, bool pdl) {
+#define TFB_CASE(NM, EP) \
+    if (norm_mode == NM && epi == EP) return pick_shape<NM, EP>(p, stream, pdl);
+    TFB_CASE(0, 0) TFB_CASE(1, 0) TFB_CASE(2, 0)
+    TFB_CASE(0, 1) TFB_CASE(1, 1) TFB_CASE(2, 1)
+    TFB_CASE(0, 2) TFB_CASE(1, 2) TFB_CASE(2, 2)
+    TFB_CASE(0, 3) TFB_CASE(1, 3) TFB_CASE(2, 3)
+#undef TFB_CASE
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace tfb

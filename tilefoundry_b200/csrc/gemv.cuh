@@ -1,0 +1,116 @@
+// Weight-streaming GEMV building blocks shared by the projection and lm_head kernels.
+//
+// Data layout: W is [n, k] bf16 row-major, so one output's weights are one
+// contiguous run of 2k bytes.  A warp owns ROWS consecutive outputs (times a
+// K-slice when KSPLIT > 1); lane l reads the 16-byte pieces l, l+32, l+64, ... of
+// each row, so every warp-wide load is 512 contiguous bytes.  The activation
+// vector is staged once per CTA in shared memory as f32, permuted so that the two
+// float4 a lane needs for one 16-byte weight piece are each a conflict-free
+// warp-wide float4 read.
+#pragma once
+#include "common.cuh"
+
+namespace tfb {
+
+// Shared-memory float index of activation element k under the staging permutation:
+// piece c = k/8 belongs to (iteration it = c/32, lane = c%32); its first 4 floats go
+// to float4 slot (it*2+0)*32+lane, the last 4 to (it*2+1)*32+lane.
+__device__ __forceinline__ int xs_index(int k) {
+    const int c = k >> 3, j = k & 7;
+    const int it = c >> 5, lane = c & 31;
+    return (((it * 2 + (j >> 2)) * 32 + lane) << 2) + (j & 3);
+}
+
+// Stage x[0..k) (bf16) into xs (f32, permuted) applying the fused prologue.
+// All threads of the CTA take part.  `red` is >= 32 floats of shared scratch.
+template <int NORM_MODE>
+__device__ __forceinline__ void stage_activation(const uint16_t* __restrict__ x,
+                                                 const uint16_t* __restrict__ gamma, float* xs,
+                                                 float* red, int k, float eps, float x_scale) {
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    float rstd = 1.f;
+    if (NORM_MODE != 0) {
+        float ss = 0.f;
+        for (int c = tid; c < (k >> 3); c += nthr) {
+            const uint4 v = *reinterpret_cast<const uint4*>(x + (c << 3));
+            const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float a = bf16_lo(u[i]), b = bf16_hi(u[i]);
+                ss = fmaf(a, a, ss);
+                ss = fmaf(b, b, ss);
+            }
+        }
+        ss = block_sum(ss, red);
+        rstd = rsqrtf(ss / float(k) + eps);
+    }
+    for (int c = tid; c < (k >> 3); c += nthr) {
+        const uint4 v = *reinterpret_cast<const uint4*>(x + (c << 3));
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { f[2 * i] = bf16_lo(u[i]); f[2 * i + 1] = bf16_hi(u[i]); }
+        if (NORM_MODE != 0) {
+            const uint4 gv = *reinterpret_cast<const uint4*>(gamma + (c << 3));
+            const uint32_t g[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float g0 = bf16_lo(g[i]), g1 = bf16_hi(g[i]);
+                if (NORM_MODE == 2) {          // round, then gain (a bf16 multiply)
+                    f[2 * i] = round_bf16(round_bf16(f[2 * i] * rstd) * g0);
+                    f[2 * i + 1] = round_bf16(round_bf16(f[2 * i + 1] * rstd) * g1);
+                } else {                       // f32 through the gain, one rounding
+                    f[2 * i] = round_bf16(f[2 * i] * rstd * g0);
+                    f[2 * i + 1] = round_bf16(f[2 * i + 1] * rstd * g1);
+                }
+            }
+        }
+        if (x_scale != 1.f) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = round_bf16(f[i] * x_scale);
+        }
+        const int it = c >> 5, lane = c & 31;
+        float4* dst = reinterpret_cast<float4*>(xs);
+        dst[(it * 2) * 32 + lane] = make_float4(f[0], f[1], f[2], f[3]);
+        dst[(it * 2 + 1) * 32 + lane] = make_float4(f[4], f[5], f[6], f[7]);
+    }
+}
+
+// Dot products of ROWS weight rows with the staged activation over the 16-byte
+// pieces [it_begin, it_end) x 32 lanes.  `w` points at row 0, `row_stride` in
+// uint4 units; rows at or beyond `rows_valid` are skipped (their acc stays 0).
+// `first` holds pieces loaded ahead of time for iterations it_begin..it_begin+UNROLL-1.
+template <int ROWS, int UNROLL>
+struct RowsDot {
+    uint4 buf[ROWS][UNROLL];
+
+    __device__ __forceinline__ void load(const uint4* __restrict__ w, int row_stride, int rows_valid,
+                                         int it0, int it_end, int lane) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int it = it0 + u;
+                if (r < rows_valid && it < it_end)
+                    buf[r][u] = ld_stream16(w + size_t(r) * row_stride + it * 32 + lane);
+                else
+                    buf[r][u] = make_uint4(0, 0, 0, 0);
+            }
+    }
+
+    __device__ __forceinline__ void fma(const float* xs, int it0, int it_end, int lane, float (&acc)[ROWS]) {
+        const float4* x4 = reinterpret_cast<const float4*>(xs);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int it = it0 + u;
+            if (it < it_end) {
+                const float4 xa = x4[(it * 2) * 32 + lane];
+                const float4 xb = x4[(it * 2 + 1) * 32 + lane];
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) acc[r] = dot8(buf[r][u], xa, xb, acc[r]);
+            }
+        }
+    }
+};
+
+}  // namespace tfb

@@ -1,0 +1,73 @@
+// Internal interface between the kernel translation units and the C ABI.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tfb {
+
+struct GemvParams {
+    const uint4* w;
+    const uint4* w2;
+    const uint16_t* x;
+    const uint16_t* gamma;
+    const uint16_t* residual;
+    void* y;
+    int n, k;
+    float eps, x_scale, res_scale, out_scale;
+    const void* prefetch;
+    unsigned long long prefetch_bytes;
+};
+cudaError_t gemv_dispatch(const GemvParams& p, int norm_mode, int epi, cudaStream_t stream, bool pdl);
+
+struct AttnParams {
+    const uint16_t* qkv;
+    const uint16_t* gamma_q;
+    const uint16_t* gamma_k;
+    const uint16_t* cos_table;
+    const uint16_t* sin_table;
+    const int* pos;
+    const int* rope_pos;
+    uint16_t* k_pool;
+    uint16_t* v_pool;
+    const int* block_table;
+    uint16_t* out;
+    uint16_t* k_new_out;
+    uint16_t* v_new_out;
+    float* part_o;
+    float* part_ml;
+    unsigned* counters;
+    int hq, hkv, d, rotary_dim, page_size, max_ctx, nsplit;
+    float eps, scale;
+    int norm_mode;
+    const void* prefetch;
+    unsigned long long prefetch_bytes;
+};
+int attn_splits(int max_ctx);
+cudaError_t attn_gqa_dispatch(const AttnParams& p, cudaStream_t stream, bool pdl);
+
+struct HeadParams {
+    const uint4* w;
+    const uint16_t* x;
+    const uint16_t* gamma;
+    uint16_t* logits;
+    long long* token_out;
+    float* scratch_val;
+    int* scratch_idx;
+    unsigned* counter;
+    int n, k;
+    float eps, x_scale, out_scale;
+    long long* tokens;
+    int* pos;
+    int n_prompt, max_tokens;
+};
+int lm_head_ctas(int n);
+cudaError_t lm_head_dispatch(const HeadParams& p, int norm_mode, cudaStream_t stream, bool pdl);
+
+cudaError_t embed_launch(const uint16_t* table, const long long* ids, const long long* ids_base,
+                         const int* pos, uint16_t* out, int rows, int hidden, long long vocab,
+                         float scale, cudaStream_t stream, bool pdl);
+cudaError_t rmsnorm_launch(const uint16_t* x, const uint16_t* gamma, uint16_t* y, int rows, int width,
+                           float eps, int mode, cudaStream_t stream, bool pdl);
+cudaError_t copy_launch(const void* src, void* dst, int bytes, cudaStream_t stream, bool pdl);
+
+}  // namespace tfb

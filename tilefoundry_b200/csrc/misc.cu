@@ -1,0 +1,184 @@
+// Small kernels around the projections: embedding gather, stand-alone RMSNorm,
+// and the lm_head projection fused with the greedy pick.
+#include "gemv.cuh"
+#include "kernels.h"
+#include "launch.h"
+
+namespace tfb {
+
+// ---- embedding ---------------------------------------------------------------
+// Row r reads table[id] where id = ids[r], or tokens[*pos] when `tokens` is given
+// (the generation loop keeps its token history and position on the device).
+__global__ void embed_kernel(const uint16_t* __restrict__ table, const long long* __restrict__ ids,
+                             const long long* __restrict__ tokens, const int* __restrict__ pos,
+                             uint16_t* __restrict__ out, int hidden, long long vocab, float scale) {
+    pdl_trigger();
+    pdl_wait();
+    long long id = tokens ? tokens[*pos] : ids[blockIdx.x];
+    if (id < 0) id = 0;
+    if (id >= vocab) id = vocab - 1;
+    const uint4* src = reinterpret_cast<const uint4*>(table + size_t(id) * hidden);
+    uint4* dst = reinterpret_cast<uint4*>(out + size_t(blockIdx.x) * hidden);
+    for (int c = threadIdx.x; c < (hidden >> 3); c += blockDim.x) {
+        uint4 v = src[c];
+        if (scale != 1.f) {
+            uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t lo = f32_to_bf16_bits(bf16_lo(u[i]) * scale);
+                const uint32_t hi = f32_to_bf16_bits(bf16_hi(u[i]) * scale);
+                u[i] = lo | (hi << 16);
+            }
+            v = make_uint4(u[0], u[1], u[2], u[3]);
+        }
+        dst[c] = v;
+    }
+}
+
+cudaError_t embed_launch(const uint16_t* table, const long long* ids, const long long* tokens,
+                         const int* pos, uint16_t* out, int rows, int hidden, long long vocab,
+                         float scale, cudaStream_t stream, bool pdl) {
+    return launch_kernel(embed_kernel, dim3(rows), dim3(256), 0, stream, pdl, table, ids, tokens, pos,
+                         out, hidden, vocab, scale);
+}
+
+// ---- RMSNorm -------------------------------------------------------------------
+template <int MODE>
+__global__ void rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gamma,
+                               uint16_t* __restrict__ y, int width, float eps) {
+    __shared__ float red[32];
+    pdl_trigger();
+    pdl_wait();
+    const uint16_t* xr = x + size_t(blockIdx.x) * width;
+    uint16_t* yr = y + size_t(blockIdx.x) * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = bf16_bits_to_f32(xr[i]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float rstd = rsqrtf(ss / float(width) + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = bf16_bits_to_f32(xr[i]), g = bf16_bits_to_f32(gamma[i]);
+        const float o = (MODE == 2) ? round_bf16(v * rstd) * g : v * rstd * g;
+        yr[i] = f32_to_bf16_bits(o);
+    }
+}
+
+cudaError_t rmsnorm_launch(const uint16_t* x, const uint16_t* gamma, uint16_t* y, int rows, int width,
+                           float eps, int mode, cudaStream_t stream, bool pdl) {
+    if (mode == 2)
+        return launch_kernel(rmsnorm_kernel<2>, dim3(rows), dim3(256), 0, stream, pdl, x, gamma, y, width, eps);
+    return launch_kernel(rmsnorm_kernel<1>, dim3(rows), dim3(256), 0, stream, pdl, x, gamma, y, width, eps);
+}
+
+__global__ void copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int n16) {
+    pdl_trigger();
+    pdl_wait();
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += gridDim.x * blockDim.x) dst[i] = src[i];
+}
+cudaError_t copy_launch(const void* src, void* dst, int bytes, cudaStream_t stream, bool pdl) {
+    return launch_kernel(copy_kernel, dim3(1), dim3(256), 0, stream, pdl,
+                         static_cast<const uint4*>(src), static_cast<uint4*>(dst), bytes / 16);
+}
+
+// ---- lm_head + greedy pick -----------------------------------------------------
+// Algorithmic bytes per launch = n*k*2 (the head matrix, read once).  Each CTA
+// reduces its rows' bf16-rounded logits to one (max, lowest index) pair; the last
+// CTA to finish (atomic ticket) reduces the pairs, writes the token and advances
+// the generation state.  Ties resolve to the lowest index, as torch.argmax does.
+constexpr int kHeadRows = 4, kHeadWarps = 8, kHeadUnroll = 2;
+int lm_head_ctas(int n) { return (n + kHeadRows * kHeadWarps - 1) / (kHeadRows * kHeadWarps); }
+
+__device__ __forceinline__ void argmax_merge(float& v, int& i, float ov, int oi) {
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+}
+
+template <int NORM_MODE>
+__global__ void __launch_bounds__(kHeadWarps * 32) lm_head_kernel(const HeadParams p) {
+    extern __shared__ __align__(16) float smem[];
+    float* xs = smem;
+    float* red = smem + p.k;
+    __shared__ float wv[kHeadWarps];
+    __shared__ int wi[kHeadWarps];
+    __shared__ int s_last;
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row0 = (blockIdx.x * kHeadWarps + warp) * kHeadRows;
+    const int rows_valid = min(kHeadRows, p.n - row0);
+    const int row_stride = p.k >> 3, its = p.k >> 8;
+
+    RowsDot<kHeadRows, kHeadUnroll> a;
+    const uint4* wrow = p.w + size_t(row0) * row_stride;
+    a.load(wrow, row_stride, rows_valid, 0, its, lane);
+    pdl_trigger();
+    pdl_wait();
+    stage_activation<NORM_MODE>(p.x, p.gamma, xs, red, p.k, p.eps, p.x_scale);
+    __syncthreads();
+
+    float acc[kHeadRows];
+#pragma unroll
+    for (int r = 0; r < kHeadRows; ++r) acc[r] = 0.f;
+    for (int it0 = 0; it0 < its; it0 += kHeadUnroll) {
+        a.fma(xs, it0, its, lane, acc);
+        if (it0 + kHeadUnroll < its) a.load(wrow, row_stride, rows_valid, it0 + kHeadUnroll, its, lane);
+    }
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+#pragma unroll
+    for (int r = 0; r < kHeadRows; ++r) {
+        const float s = round_bf16(warp_sum(acc[r]) * p.out_scale);
+        if (r < rows_valid) {
+            if (lane == 0 && p.logits) p.logits[row0 + r] = f32_to_bf16_bits(s);
+            argmax_merge(best, best_i, s, row0 + r);
+        }
+    }
+    if (lane == 0) { wv[warp] = best; wi[warp] = best_i; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < kHeadWarps; ++w) argmax_merge(best, best_i, wv[w], wi[w]);
+        p.scratch_val[blockIdx.x] = best;
+        p.scratch_idx[blockIdx.x] = best_i;
+        __threadfence();
+        const unsigned ticket = atomicAdd(p.counter, 1u);
+        s_last = (ticket == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    best = -INFINITY;
+    best_i = 0x7fffffff;
+    for (int c = threadIdx.x; c < int(gridDim.x); c += blockDim.x)
+        argmax_merge(best, best_i, __ldcg(p.scratch_val + c), __ldcg(p.scratch_idx + c));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        argmax_merge(best, best_i, ov, oi);
+    }
+    if (lane == 0) { wv[warp] = best; wi[warp] = best_i; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < kHeadWarps; ++w) argmax_merge(best, best_i, wv[w], wi[w]);
+        if (p.token_out) *p.token_out = best_i;
+        if (p.tokens && p.pos) {
+            const int cur = *p.pos;
+            if (cur + 1 < p.max_tokens) {
+                if (cur + 1 >= p.n_prompt) p.tokens[cur + 1] = best_i;
+                *p.pos = cur + 1;
+            }
+        }
+        *p.counter = 0;
+    }
+}
+
+cudaError_t lm_head_dispatch(const HeadParams& p, int norm_mode, cudaStream_t stream, bool pdl) {
+    const size_t smem = (size_t(p.k) + 32) * sizeof(float);
+    const dim3 grid(lm_head_ctas(p.n)), block(kHeadWarps * 32);
+    if (norm_mode == 0) return launch_kernel(lm_head_kernel<0>, grid, block, smem, stream, pdl, p);
+    if (norm_mode == 1) return launch_kernel(lm_head_kernel<1>, grid, block, smem, stream, pdl, p);
+    if (norm_mode == 2) return launch_kernel(lm_head_kernel<2>, grid, block, smem, stream, pdl, p);
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace tfb

@@ -1,0 +1,150 @@
+"""ctypes binding of ``libtfb200.so`` (declarations: ``include/tfb200.h``).
+
+There is no CPU or PyTorch fallback: if the library is missing or a call returns a
+non-zero status, a ``RuntimeError`` is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from functools import lru_cache
+from pathlib import Path
+
+import torch
+
+LIB_PATH = Path(__file__).resolve().parent / "csrc" / "libtfb200.so"
+
+NORM_NONE, NORM_F32GAIN, NORM_CAST_THEN_GAIN = 0, 1, 2
+EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU, EPI_STORE_F32 = 0, 1, 2, 3
+
+_vp, _i32, _i64, _u64, _f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_uint64, C.c_float
+
+
+class GemvArgs(C.Structure):
+    _fields_ = [("w", _vp), ("w2", _vp), ("x", _vp), ("gamma", _vp), ("residual", _vp), ("y", _vp),
+                ("n", _i32), ("k", _i32), ("prologue", _i32), ("epilogue", _i32),
+                ("eps", _f32), ("x_scale", _f32), ("res_scale", _f32), ("out_scale", _f32),
+                ("prefetch", _vp), ("prefetch_bytes", _u64), ("pdl", _i32), ("reserved", _i32)]
+
+
+class LmHeadArgs(C.Structure):
+    _fields_ = [("w", _vp), ("x", _vp), ("gamma", _vp), ("logits", _vp), ("token_out", _vp),
+                ("scratch_val", _vp), ("scratch_idx", _vp), ("counter", _vp),
+                ("n", _i32), ("k", _i32), ("prologue", _i32),
+                ("eps", _f32), ("x_scale", _f32), ("out_scale", _f32), ("pdl", _i32),
+                ("tokens", _vp), ("pos", _vp), ("n_prompt", _i32), ("max_tokens", _i32)]
+
+
+class AttnGqaArgs(C.Structure):
+    _fields_ = [("qkv", _vp), ("gamma_q", _vp), ("gamma_k", _vp), ("cos_table", _vp), ("sin_table", _vp),
+                ("pos", _vp), ("rope_pos", _vp), ("k_pool", _vp), ("v_pool", _vp), ("block_table", _vp), ("out", _vp),
+                ("k_new_out", _vp), ("v_new_out", _vp), ("part_o", _vp), ("part_ml", _vp), ("counters", _vp),
+                ("hq", _i32), ("hkv", _i32), ("d", _i32), ("rotary_dim", _i32),
+                ("page_size", _i32), ("table_len", _i32), ("max_ctx", _i32), ("max_pos", _i32),
+                ("eps", _f32), ("scale", _f32), ("norm_mode", _i32), ("pdl", _i32),
+                ("prefetch", _vp), ("prefetch_bytes", _u64)]
+
+
+class Qwen3Layer(C.Structure):
+    _fields_ = [(n, _vp) for n in ("gamma_in", "w_qkv", "gamma_q", "gamma_k", "w_o", "gamma_post",
+                                   "w_gate", "w_up", "w_down", "k_pool", "v_pool")]
+
+
+class Qwen3StepArgs(C.Structure):
+    _fields_ = [("layers", C.POINTER(Qwen3Layer)),
+                ("n_layers", _i32), ("hidden", _i32), ("hq", _i32), ("hkv", _i32), ("d", _i32), ("inter", _i32),
+                ("vocab", _i64), ("eps", _f32), ("scale", _f32),
+                ("w_embed", _vp), ("gamma_final", _vp), ("w_head", _vp), ("cos_table", _vp), ("sin_table", _vp),
+                ("max_pos", _i32), ("page_size", _i32), ("table_len", _i32), ("max_ctx", _i32),
+                ("block_table", _vp), ("tokens", _vp), ("pos", _vp), ("n_prompt", _i32), ("max_tokens", _i32),
+                ("hidden_buf", _vp), ("qkv_buf", _vp), ("attn_buf", _vp), ("act_buf", _vp), ("logits", _vp),
+                ("part_o", _vp), ("part_ml", _vp), ("counters", _vp), ("head_val", _vp), ("head_idx", _vp),
+                ("hidden_trace", _vp), ("pdl", _i32), ("l2_prefetch", _i32)]
+
+
+#: every symbol ``include/tfb200.h`` declares: name -> (restype, argtypes)
+SYMBOLS = {
+    "tfb_version": (_i32, []),
+    "tfb_status_string": (C.c_char_p, [_i32]),
+    "tfb_last_error": (C.c_char_p, []),
+    "tfb_embed": (_i32, [_vp, _vp, _vp, _i32, _i32, _i64, _f32, _vp]),
+    "tfb_rmsnorm": (_i32, [_vp, _vp, _vp, _i32, _i32, _f32, _i32, _vp]),
+    "tfb_gemv": (_i32, [C.POINTER(GemvArgs), _vp]),
+    "tfb_lm_head_scratch_entries": (_i32, [_i32]),
+    "tfb_lm_head_argmax": (_i32, [C.POINTER(LmHeadArgs), _vp]),
+    "tfb_attn_splits": (_i32, [_i32]),
+    "tfb_attn_gqa_decode": (_i32, [C.POINTER(AttnGqaArgs), _vp]),
+    "tfb_qwen3_decode_step": (_i32, [C.POINTER(Qwen3StepArgs), _vp]),
+}
+
+
+@lru_cache(maxsize=1)
+def load() -> C.CDLL:
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m tilefoundry_b200.build` "
+            "(needs nvcc). There is no fallback path."
+        )
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (res, args) in SYMBOLS.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
+    return lib
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        lib = load()
+        msg = lib.tfb_status_string(status).decode()
+        detail = lib.tfb_last_error().decode()
+        raise RuntimeError(f"{what}: status {status} ({msg})" + (f" [{detail}]" if detail else ""))
+
+
+def ptr(t: "torch.Tensor | None") -> int | None:
+    """Device address of a contiguous CUDA tensor (``None`` stays NULL)."""
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError("kernel arguments must be CUDA tensors; there is no CPU path")
+    if not t.is_contiguous():
+        raise ValueError("kernel arguments must be contiguous")
+    return t.data_ptr()
+
+
+def stream() -> int:
+    """torch's current stream, so launches order with the caller's work and can be graph-captured."""
+    return torch.cuda.current_stream().cuda_stream
+
+
+# ---- thin per-op helpers (all enqueue on the current stream) ----------------------
+
+def embed(table, ids, out, scale=1.0):
+    check(load().tfb_embed(ptr(table), ptr(ids), ptr(out), ids.numel(), table.shape[1], table.shape[0],
+                           scale, stream()), "tfb_embed")
+    return out
+
+
+def rmsnorm(x, gamma, out, eps, mode):
+    width = x.shape[-1]
+    check(load().tfb_rmsnorm(ptr(x), ptr(gamma), ptr(out), x.numel() // width, width, eps, mode, stream()),
+          "tfb_rmsnorm")
+    return out
+
+
+def gemv(w, x, y, *, w2=None, gamma=None, residual=None, prologue=NORM_NONE, epilogue=EPI_STORE,
+         eps=0.0, x_scale=1.0, res_scale=1.0, out_scale=1.0, prefetch=None, pdl=False):
+    n, k = w.shape
+    a = GemvArgs(w=ptr(w), w2=ptr(w2), x=ptr(x), gamma=ptr(gamma), residual=ptr(residual), y=ptr(y),
+                 n=n, k=k, prologue=prologue, epilogue=epilogue, eps=eps, x_scale=x_scale,
+                 res_scale=res_scale, out_scale=out_scale,
+                 prefetch=ptr(prefetch), prefetch_bytes=0 if prefetch is None else prefetch.numel() * prefetch.element_size(),
+                 pdl=int(pdl))
+    check(load().tfb_gemv(C.byref(a), stream()), "tfb_gemv")
+    return y
+
+
+def attn_splits(max_ctx: int) -> int:
+    return load().tfb_attn_splits(max_ctx)
+
+
+def lm_head_scratch_entries(n: int) -> int:
+    return load().tfb_lm_head_scratch_entries(n)
