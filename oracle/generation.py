@@ -16,18 +16,32 @@ def greedy(logits) -> int:
     return int(torch.argmax(logits).item())
 
 
-def decode_ids(loaded, prompt_ids, max_new, device="cpu", keep_logits=False, prompt_limit=None):
+def _forward_traced(loaded, token_ids, cos, sin, pos_ids, scale, caches, trace):
+    """`forward` with the residual stream after every layer recorded (same calls, same order)."""
+    hidden = loaded.embed(token_ids)
+    entries, rows = [], []
+    for layer, (k_cache, v_cache) in zip(loaded.modules, caches):
+        hidden, k_new, v_new = layer(hidden, cos, sin, pos_ids, k_cache, v_cache, scale)
+        entries.append((k_new, v_new))
+        rows.append(hidden.reshape(-1))
+    normed = loaded.final_rms_norm(hidden)
+    rows.append(normed.reshape(-1))
+    trace.append(torch.stack(rows))
+    return loaded.lm_head(normed), tuple(entries)
+
+
+def decode_ids(loaded, prompt_ids, max_new, device="cpu", keep_logits=False, keep_hidden=False):
     prompt_ids = torch.as_tensor(prompt_ids, dtype=torch.int64)
     n_prompt = prompt_ids.numel()
     input_ids = torch.empty(n_prompt + max_new, dtype=torch.int64)
     input_ids[:n_prompt] = prompt_ids
     caches = loaded.init_caches(device=device)
-    kept = []
+    kept, trace = [], []
     logits = None
     t_prompt = perf_counter()
     for step in range(n_prompt):
         args = loaded.prepare_inputs_for_generation(input_ids[: step + 1], step, caches, device=device)
-        logits, fresh = loaded.forward(*args)
+        logits, fresh = _forward_traced(loaded, *args, trace) if keep_hidden else loaded.forward(*args)
         caches = loaded.append_cache(caches, fresh)
         if keep_logits:
             kept.append(logits)
@@ -40,10 +54,10 @@ def decode_ids(loaded, prompt_ids, max_new, device="cpu", keep_logits=False, pro
         input_ids[n_prompt + step] = token
         pos = n_prompt + step
         args = loaded.prepare_inputs_for_generation(input_ids[: pos + 1], pos, caches, device=device)
-        logits, fresh = loaded.forward(*args)
+        logits, fresh = _forward_traced(loaded, *args, trace) if keep_hidden else loaded.forward(*args)
         caches = loaded.append_cache(caches, fresh)
         if keep_logits:
             kept.append(logits)
     seconds = perf_counter() - started
     return {"tokens": out, "seconds": seconds, "prompt_seconds": t_prompt, "logits": kept,
-            "caches": caches}
+            "caches": caches, "hidden": trace}

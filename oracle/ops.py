@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
-DT = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32,
+DT = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32, "f64": torch.float64,
       "i32": torch.int32, "i64": torch.int64}
 
 

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from oracle import evaluator, generation, ops as tf, qwen3_1_7b as oq
-from tests.helpers import ATOL, RTOL, assert_close_bf16
+from tests.helpers import ATOL, RTOL, assert_close_at_scale, assert_close_bf16
 from tilefoundry_b200.authored import qwen3_1_7b as q
 from tilefoundry_b200.authored.weights import random_weights
 from tilefoundry_b200.runtime import AllClose, DictResource, Equal, NanInf, check
@@ -166,26 +166,27 @@ def _session_vs_oracle(cfg, dev, n_prompt, n_new, seed, std, use_graph):
     ref = evaluator.load(mod, DictResource(weights), oq.make(cfg))
     g = torch.Generator().manual_seed(seed + 100)
     prompt = torch.randint(0, cfg.vocab_size, (n_prompt,), generator=g)
-    want = generation.decode_ids(ref, prompt, n_new, keep_logits=True)
+    want = generation.decode_ids(ref, prompt, n_new, keep_logits=True, keep_hidden=True)
 
     sess = Qwen3Session(cfg, DictResource(_cuda(weights, dev)), max_ctx=n_prompt + n_new + 5, device=dev,
                         keep_logits=True, trace_hidden=True)
     sess.reset(prompt)
     if use_graph:
         sess.capture()
-    got_logits = []
+    got_logits, got_hidden = [], []
     for _ in range(n_prompt + n_new - 1):
         sess.run(1, use_graph)
         got_logits.append(sess.logits.clone())
+        got_hidden.append(sess.trace.clone())
     torch.cuda.synchronize()
-    return ref, want, sess, got_logits, prompt
+    return ref, want, sess, got_logits, got_hidden, prompt
 
 
 @pytest.mark.parametrize("use_graph", [False, True])
 def test_session_matches_evaluator_tiny(dev, use_graph):
     cfg = q.QWEN3_TINY
     n_prompt, n_new = 24, 140          # crosses the 128-position split and the 64-slot page boundaries
-    ref, want, sess, got_logits, prompt = _session_vs_oracle(cfg, dev, n_prompt, n_new, 11, 0.05, use_graph)
+    ref, want, sess, got_logits, got_hidden, prompt = _session_vs_oracle(cfg, dev, n_prompt, n_new, 11, 0.05, use_graph)
     total = n_prompt + n_new - 1
     # token ids: bit-exact
     got_tokens = sess.tokens[n_prompt: n_prompt + n_new].cpu().tolist()
@@ -193,15 +194,40 @@ def test_session_matches_evaluator_tiny(dev, use_graph):
     assert int(sess.pos) == total
     # logits at every step
     for step in range(total):
-        assert_close_bf16(got_logits[step], want["logits"][step][0], f"logits step {step}")
+        assert_close_at_scale(got_logits[step], want["logits"][step][0], f"logits step {step}")
+        for li in range(cfg.num_hidden_layers + 1):
+            assert_close_at_scale(got_hidden[step][li], want["hidden"][step][li], f"hidden step {step} layer {li}")
     # the cache the session built equals the evaluator's appended caches
     from tilefoundry_b200.engine import paged_kv
     assert torch.equal(sess.table.cpu(), paged_kv.block_table(1, sess.max_ctx))
     for li, (k_ref, v_ref) in enumerate(want["caches"]):
         k_got = paged_kv.logical_view(sess.layers[li]["k_pool"], sess.table[0], total)
         v_got = paged_kv.logical_view(sess.layers[li]["v_pool"], sess.table[0], total)
-        assert_close_bf16(k_got, k_ref[:, :total], f"layer {li} K cache")
-        assert_close_bf16(v_got, v_ref[:, :total], f"layer {li} V cache")
+        assert_close_at_scale(k_got, k_ref[:, :total], f"layer {li} K cache")
+        assert_close_at_scale(v_got, v_ref[:, :total], f"layer {li} V cache")
+
+
+def test_config0_full_model_first_32_tokens(dev):
+    """The CPU-runnable configuration: Qwen3-1.7B architecture, N(0, 0.02) weights, 64 random prompt
+    ids, 32 greedy tokens.  Token ids must be bit-exact (a mismatch is excused only where the
+    oracle's own top-2 logits are within one bf16 ulp of each other); logits and every layer's
+    hidden state within the end-to-end bound."""
+    cfg = q.QWEN3_1_7B
+    n_prompt, n_new = 64, 32
+    ref, want, sess, got_logits, got_hidden, prompt = _session_vs_oracle(cfg, dev, n_prompt, n_new, 0, 0.02, True)
+    got_tokens = sess.tokens[n_prompt: n_prompt + n_new].cpu().tolist()
+    for i, (g, w) in enumerate(zip(got_tokens, want["tokens"])):
+        if g != w:
+            lg = want["logits"][n_prompt - 1 + i][0].float()
+            top = torch.topk(lg, 2).values
+            ulp = 2.0 ** (torch.floor(torch.log2(top[0].abs())) - 7)
+            assert (top[0] - top[1]) <= ulp, f"token {i}: got {g}, want {w}, oracle margin {float(top[0]-top[1])}"
+            pytest.skip(f"oracle tie at token {i}; sequences diverge after it")
+    assert got_tokens == want["tokens"]
+    for step in range(n_prompt + n_new - 1):
+        assert_close_at_scale(got_logits[step], want["logits"][step][0], f"logits step {step}")
+        for li in range(cfg.num_hidden_layers + 1):
+            assert_close_at_scale(got_hidden[step][li], want["hidden"][step][li], f"hidden step {step} layer {li}")
 
 
 def test_generate_equals_stepwise_and_is_idempotent(dev):

@@ -126,10 +126,13 @@ def make_twin(cfg: authored.Qwen3Config = authored.QWEN3_1_7B):
         logits = _new((1, V), hidden)
         n = lib.lm_head_scratch_entries(V)
         token = torch.zeros(1, device=hidden.device, dtype=torch.int64)
+        # scratch must stay referenced until the launch is enqueued: two unnamed temporaries
+        # would be handed the same block by the caching allocator
+        val, idx = _new(n, hidden, torch.float32), _new(n, hidden, torch.int32)
+        counter = torch.zeros(1, device=hidden.device, dtype=torch.int32)
         a = lib.LmHeadArgs(w=lib.ptr(self._head), x=lib.ptr(hidden.reshape(-1)), logits=lib.ptr(logits),
-                           token_out=lib.ptr(token), scratch_val=lib.ptr(_new(n, hidden, torch.float32)),
-                           scratch_idx=lib.ptr(_new(n, hidden, torch.int32)),
-                           counter=lib.ptr(torch.zeros(1, device=hidden.device, dtype=torch.int32)),
+                           token_out=lib.ptr(token), scratch_val=lib.ptr(val), scratch_idx=lib.ptr(idx),
+                           counter=lib.ptr(counter),
                            n=V, k=H, prologue=lib.NORM_NONE, eps=EPS, x_scale=1.0, out_scale=1.0, pdl=0)
         lib.check(lib.load().tfb_lm_head_argmax(C.byref(a), lib.stream()), "tfb_lm_head_argmax")
         self.last_token = token
