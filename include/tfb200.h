@@ -43,6 +43,11 @@ TFB_API int tfb_version(void);
 TFB_API const char* tfb_status_string(int status);
 /* Text of the last CUDA runtime error a launch returned on this thread ("" if none). */
 TFB_API const char* tfb_last_error(void);
+/* Debug timeline.  While a device buffer of capacity*4 uint64 is registered, each projection,
+ * attention and lm_head launch is given the next 4-word record and writes, in %globaltimer ns:
+ * earliest CTA start, earliest and latest return from the dependency wait, latest exit.  The
+ * caller presets the words to (~0, ~0, 0, 0).  Pass NULL to stop.  Not for production use. */
+TFB_API int tfb_debug_trace(void* device_buffer, int32_t capacity);
 
 /* ---- embedding row gather -------------------------------------------------
  * out[r, :] = table[ids[r], :] * scale (scale == 1 copies bits).
@@ -83,6 +88,11 @@ TFB_API int tfb_rmsnorm(const void* x, const void* gamma, void* y, int32_t rows,
  * examples/qwen3_1_7b-tilelang/fast/kernels.py:124-260,
  * examples/granite_4_0_h_small-cuda/kernels/granite.cu:81-157. */
 enum { TFB_EPI_STORE = 0, TFB_EPI_RESIDUAL = 1, TFB_EPI_SWIGLU = 2, TFB_EPI_STORE_F32 = 3 };
+/* Two implementations compute the same thing: a warp-per-row kernel with direct 128-bit
+ * streaming loads (what AUTO picks: it measured faster at every decode shape on B200), and a
+ * persistent one-CTA-per-SM kernel that streams weights through a shared-memory ring filled by
+ * bulk async copies (cp.async.bulk + mbarrier), kept selectable for A/B measurement. */
+enum { TFB_KERNEL_AUTO = 0, TFB_KERNEL_ROWS = 1, TFB_KERNEL_RING = 2 };
 typedef struct {
     const void* w;
     const void* w2;
@@ -97,6 +107,8 @@ typedef struct {
     const void* prefetch;
     uint64_t prefetch_bytes;
     int32_t pdl;
+    int32_t kernel;  /* TFB_KERNEL_AUTO, or force one implementation (for A/B measurement) */
+    int32_t self_prefetch; /* streaming kernel: once its ring is full, ask the L2 for the rest of its own rows */
     int32_t reserved;
 } tfb_gemv_args;
 TFB_API int tfb_gemv(const tfb_gemv_args* args, tfb_stream_t stream);
@@ -129,6 +141,8 @@ typedef struct {
     int32_t* pos;
     int32_t n_prompt;
     int32_t max_tokens;
+    int32_t kernel;         /* TFB_KERNEL_* */
+    int32_t self_prefetch;  /* as in tfb_gemv_args */
 } tfb_lm_head_args;
 TFB_API int32_t tfb_lm_head_scratch_entries(int32_t n);
 TFB_API int tfb_lm_head_argmax(const tfb_lm_head_args* args, tfb_stream_t stream);
@@ -227,7 +241,9 @@ typedef struct {
     int32_t* head_idx;
     void* hidden_trace;     /* optional [n_layers+1][hidden] bf16: residual stream after each layer, then final-normed */
     int32_t pdl;
-    int32_t l2_prefetch;
+    int32_t l2_prefetch;    /* bit 0: each projection prefetches its own remaining rows; bit 1: the next projection's */
+    int32_t kernel;         /* TFB_KERNEL_* for every projection of the step */
+    int64_t* picked;        /* optional [1]: the token this step picked, whatever the prompt says */
 } tfb_qwen3_step_args;
 TFB_API int tfb_qwen3_decode_step(const tfb_qwen3_step_args* args, tfb_stream_t stream);
 

@@ -9,6 +9,14 @@ namespace {
 
 thread_local char g_last_error[256] = "";
 
+// debug timeline: 4 words per launch, handed out in launch order
+unsigned long long* g_trace_buf = nullptr;
+int g_trace_cap = 0, g_trace_next = 0;
+unsigned long long* next_trace() {
+    if (!g_trace_buf || g_trace_next >= g_trace_cap) return nullptr;
+    return g_trace_buf + 8 * size_t(g_trace_next++);
+}
+
 int fail_launch(cudaError_t e) {
     std::snprintf(g_last_error, sizeof g_last_error, "%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
     cudaGetLastError();  // clear the sticky-free error so later launches report their own
@@ -28,6 +36,13 @@ inline cudaStream_t S(tfb_stream_t s) { return static_cast<cudaStream_t>(s); }
 extern "C" {
 
 int tfb_version(void) { return 100; }
+
+int tfb_debug_trace(void* device_buffer, int32_t capacity) {
+    g_trace_buf = static_cast<unsigned long long*>(device_buffer);
+    g_trace_cap = device_buffer ? capacity : 0;
+    g_trace_next = 0;
+    return TFB_OK;
+}
 
 const char* tfb_status_string(int status) {
     switch (status) {
@@ -75,7 +90,7 @@ static int gemv_checked(const tfb_gemv_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(aligned16(a->w) && aligned16(a->x) && (!a->w2 || aligned16(a->w2)) &&
                     (!a->gamma || aligned16(a->gamma)), TFB_EALIGN);
     TFB_REQUIRE(!a->prefetch || (aligned16(a->prefetch) && a->prefetch_bytes % 16 == 0), TFB_EALIGN);
-    tfb::GemvParams p;
+    tfb::GemvParams p = {};
     p.w = static_cast<const uint4*>(a->w);
     p.w2 = static_cast<const uint4*>(a->w2);
     p.x = static_cast<const uint16_t*>(a->x);
@@ -90,12 +105,20 @@ static int gemv_checked(const tfb_gemv_args* a, tfb_stream_t stream) {
     p.out_scale = a->out_scale;
     p.prefetch = a->prefetch;
     p.prefetch_bytes = a->prefetch_bytes;
+    p.self_prefetch = a->self_prefetch;
+    p.trace = next_trace();
+    if (a->kernel == TFB_KERNEL_RING && tfb::gemv_stream_supported(a->n, a->k))
+        return done(tfb::gemv_stream_dispatch(p, a->prologue, a->epilogue, S(stream), a->pdl != 0));
     return done(tfb::gemv_dispatch(p, a->prologue, a->epilogue, S(stream), a->pdl != 0));
 }
 
 int tfb_gemv(const tfb_gemv_args* args, tfb_stream_t stream) { return gemv_checked(args, stream); }
 
-int32_t tfb_lm_head_scratch_entries(int32_t n) { return n > 0 ? tfb::lm_head_ctas(n) : 0; }
+int32_t tfb_lm_head_scratch_entries(int32_t n) {
+    if (n <= 0) return 0;
+    const int a = tfb::lm_head_ctas(n), b = tfb::lm_head_stream_ctas();
+    return a > b ? a : b;
+}
 
 int tfb_lm_head_argmax(const tfb_lm_head_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->w && a->x && a->scratch_val && a->scratch_idx && a->counter, TFB_EINVAL);
@@ -104,6 +127,19 @@ int tfb_lm_head_argmax(const tfb_lm_head_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a->prologue >= TFB_NORM_NONE && a->prologue <= TFB_NORM_CAST_THEN_GAIN, TFB_EINVAL);
     TFB_REQUIRE(a->prologue == TFB_NORM_NONE || a->gamma, TFB_EINVAL);
     TFB_REQUIRE(aligned16(a->w) && aligned16(a->x) && (!a->gamma || aligned16(a->gamma)), TFB_EALIGN);
+    if (a->kernel == TFB_KERNEL_RING && tfb::gemv_stream_supported(a->n, a->k)) {
+        tfb::GemvParams g = {};
+        g.w = static_cast<const uint4*>(a->w);
+        g.x = static_cast<const uint16_t*>(a->x);
+        g.gamma = static_cast<const uint16_t*>(a->gamma);
+        g.y = a->logits;
+        g.n = a->n; g.k = a->k; g.eps = a->eps; g.x_scale = a->x_scale; g.res_scale = 1.f; g.out_scale = a->out_scale;
+        g.scratch_val = a->scratch_val; g.scratch_idx = a->scratch_idx; g.counter = a->counter;
+        g.token_out = reinterpret_cast<long long*>(a->token_out);
+        g.tokens = reinterpret_cast<long long*>(a->tokens); g.pos = a->pos;
+        g.n_prompt = a->n_prompt; g.max_tokens = a->max_tokens; g.self_prefetch = a->self_prefetch;
+        return done(tfb::gemv_stream_dispatch(g, a->prologue, 4, S(stream), a->pdl != 0));
+    }
     tfb::HeadParams p;
     p.w = static_cast<const uint4*>(a->w);
     p.x = static_cast<const uint16_t*>(a->x);
@@ -122,6 +158,7 @@ int tfb_lm_head_argmax(const tfb_lm_head_args* a, tfb_stream_t stream) {
     p.pos = a->pos;
     p.n_prompt = a->n_prompt;
     p.max_tokens = a->max_tokens;
+    p.trace = next_trace();
     return done(tfb::lm_head_dispatch(p, a->prologue, S(stream), a->pdl != 0));
 }
 
@@ -132,7 +169,7 @@ int tfb_attn_gqa_decode(const tfb_attn_gqa_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a->part_o && a->part_ml && a->counters, TFB_EINVAL);
     TFB_REQUIRE(a->hq > 0 && a->hkv > 0 && a->hq % a->hkv == 0, TFB_EINVAL);
     TFB_REQUIRE(a->d == 64 || a->d == 128, TFB_EINVAL);
-    TFB_REQUIRE(a->rotary_dim >= 0 && a->rotary_dim <= a->d && a->rotary_dim % 2 == 0, TFB_EINVAL);
+    TFB_REQUIRE(a->rotary_dim >= 0 && a->rotary_dim <= a->d && a->rotary_dim % 64 == 0, TFB_EINVAL);
     TFB_REQUIRE(a->rotary_dim == 0 || (a->cos_table && a->sin_table), TFB_EINVAL);
     TFB_REQUIRE(a->page_size > 0 && a->table_len > 0 && a->max_ctx > 0, TFB_EINVAL);
     TFB_REQUIRE(a->norm_mode == TFB_NORM_NONE || a->norm_mode == TFB_NORM_CAST_THEN_GAIN, TFB_EINVAL);
@@ -169,6 +206,7 @@ int tfb_attn_gqa_decode(const tfb_attn_gqa_args* a, tfb_stream_t stream) {
     p.norm_mode = a->norm_mode;
     p.prefetch = a->prefetch;
     p.prefetch_bytes = a->prefetch_bytes;
+    p.trace = next_trace();
     const int G = a->hq / a->hkv;
     TFB_REQUIRE(G == 1 || G == 2 || (G == 4 && a->d == 128), TFB_EINVAL);
     return done(tfb::attn_gqa_dispatch(p, S(stream), a->pdl != 0));
@@ -183,7 +221,8 @@ int tfb_qwen3_decode_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
     TFB_REQUIRE((long long)a->page_size * a->table_len >= a->max_ctx, TFB_ECAPACITY);
     TFB_REQUIRE(a->max_pos >= a->max_ctx && a->max_tokens <= a->max_ctx + 1, TFB_ECAPACITY);
     const bool pdl = a->pdl != 0;
-    const bool pf = a->l2_prefetch != 0;
+    const bool pf = (a->l2_prefetch & 2) != 0;
+    const int spf = a->l2_prefetch & 1;
     const int H = a->hidden, QP = a->hq * a->d, KVP = a->hkv * a->d, I = a->inter;
     const int NQKV = QP + 2 * KVP;
     cudaStream_t st = S(stream);
@@ -203,7 +242,7 @@ int tfb_qwen3_decode_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
         std::memset(&g, 0, sizeof g);
         g.w = L.w_qkv; g.x = hid; g.gamma = L.gamma_in; g.y = a->qkv_buf;
         g.n = NQKV; g.k = H; g.prologue = TFB_NORM_CAST_THEN_GAIN; g.epilogue = TFB_EPI_STORE;
-        g.eps = a->eps; g.x_scale = 1.f; g.res_scale = 1.f; g.out_scale = 1.f; g.pdl = pdl;
+        g.eps = a->eps; g.x_scale = 1.f; g.res_scale = 1.f; g.out_scale = 1.f; g.pdl = pdl; g.kernel = a->kernel; g.self_prefetch = spf;
         if (pf) { g.prefetch = L.w_o; g.prefetch_bytes = 2ull * H * QP; }
         int rc = gemv_checked(&g, stream);
         if (rc) return rc;
@@ -224,7 +263,7 @@ int tfb_qwen3_decode_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
         std::memset(&g, 0, sizeof g);
         g.w = L.w_o; g.x = a->attn_buf; g.residual = hid; g.y = hid;
         g.n = H; g.k = QP; g.prologue = TFB_NORM_NONE; g.epilogue = TFB_EPI_RESIDUAL;
-        g.eps = a->eps; g.x_scale = 1.f; g.res_scale = 1.f; g.out_scale = 1.f; g.pdl = pdl;
+        g.eps = a->eps; g.x_scale = 1.f; g.res_scale = 1.f; g.out_scale = 1.f; g.pdl = pdl; g.kernel = a->kernel; g.self_prefetch = spf;
         if (pf) { g.prefetch = L.w_up; g.prefetch_bytes = 2ull * I * H; }
         rc = gemv_checked(&g, stream);
         if (rc) return rc;
@@ -232,7 +271,7 @@ int tfb_qwen3_decode_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
         std::memset(&g, 0, sizeof g);
         g.w = L.w_gate; g.w2 = L.w_up; g.x = hid; g.gamma = L.gamma_post; g.y = a->act_buf;
         g.n = I; g.k = H; g.prologue = TFB_NORM_CAST_THEN_GAIN; g.epilogue = TFB_EPI_SWIGLU;
-        g.eps = a->eps; g.x_scale = 1.f; g.res_scale = 1.f; g.out_scale = 1.f; g.pdl = pdl;
+        g.eps = a->eps; g.x_scale = 1.f; g.res_scale = 1.f; g.out_scale = 1.f; g.pdl = pdl; g.kernel = a->kernel; g.self_prefetch = spf;
         if (pf) { g.prefetch = L.w_down; g.prefetch_bytes = 2ull * I * H; }
         rc = gemv_checked(&g, stream);
         if (rc) return rc;
@@ -240,7 +279,7 @@ int tfb_qwen3_decode_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
         std::memset(&g, 0, sizeof g);
         g.w = L.w_down; g.x = a->act_buf; g.residual = hid; g.y = hid;
         g.n = H; g.k = I; g.prologue = TFB_NORM_NONE; g.epilogue = TFB_EPI_RESIDUAL;
-        g.eps = a->eps; g.x_scale = 1.f; g.res_scale = 1.f; g.out_scale = 1.f; g.pdl = pdl;
+        g.eps = a->eps; g.x_scale = 1.f; g.res_scale = 1.f; g.out_scale = 1.f; g.pdl = pdl; g.kernel = a->kernel; g.self_prefetch = spf;
         if (pf && next) { g.prefetch = next->w_qkv; g.prefetch_bytes = 2ull * NQKV * H; }
         rc = gemv_checked(&g, stream);
         if (rc) return rc;
@@ -259,7 +298,8 @@ int tfb_qwen3_decode_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
     h.w = a->w_head; h.x = hid; h.gamma = a->gamma_final; h.logits = a->logits;
     h.scratch_val = a->head_val; h.scratch_idx = a->head_idx; h.counter = a->counters + a->hkv;
     h.n = int(a->vocab); h.k = H; h.prologue = TFB_NORM_CAST_THEN_GAIN; h.eps = a->eps;
-    h.x_scale = 1.f; h.out_scale = 1.f; h.pdl = pdl;
+    h.x_scale = 1.f; h.out_scale = 1.f; h.pdl = pdl; h.kernel = a->kernel; h.self_prefetch = spf;
+    h.token_out = a->picked;
     h.tokens = a->tokens; h.pos = a->pos; h.n_prompt = a->n_prompt; h.max_tokens = a->max_tokens;
     return tfb_lm_head_argmax(&h, stream);
 }

@@ -1,21 +1,31 @@
 // GQA decode attention over a paged bf16 KV cache, one launch per layer:
-// per-head q/k RMSNorm -> RoPE -> KV append -> split-KV online softmax -> merge.
+// per-head q/k RMSNorm -> RoPE -> KV append -> split-KV softmax -> merge.
 //
-// HBM-bound on the cache: algorithmic bytes per launch = (ctx+1) * hkv * d * 2 (K and V)
-// * 2 bytes.  Grid = (hkv, splits): one CTA owns one KV head and SPLIT_LEN
-// consecutive positions, and serves all G = hq/hkv query heads that share the KV
-// head so each cache line is read once.  A sub-group of d/8 lanes reads one
-// position's 2d-byte row with one 16-byte load per lane.  Partial (max, sum,
-// weighted V) triples go to scratch; the last CTA of a KV head to finish (an atomic
-// ticket, no spinning) merges them.
+// HBM/L2-bound on the cache: algorithmic bytes per launch = (ctx+1) * hkv * d * 2 (K and V)
+// * 2 bytes.  Grid = (hkv, splits): one CTA owns one KV head and kSplitLen (= one
+// page of) consecutive positions, and serves all G = hq/hkv query heads that share
+// the KV head, so each cache row is read once.
+//
+// Latency is what matters at batch 1, so the kernel is built around one round trip:
+//  * cached rows are immutable, so the CTA starts copying its K and V rows into
+//    shared memory (16-byte cp.async, all in flight at once) BEFORE
+//    griddepcontrol.wait, while the q|k|v projection before it is still running.
+//    The position word may still be the previous step's at that moment; it can only
+//    be smaller, and the rows it leaves out are fetched after the wait.
+//  * after the wait: this token's q/k/v are normalised, rotated, and the new K/V row
+//    is dropped into the same shared tile, so the score and PV loops have no special
+//    case.
+//  * PV gives each thread whole output elements (no cross-thread reduction).
+//  * partial (max, sum, weighted V) go to scratch; the last CTA of a KV head to
+//    finish (an atomic ticket, no spinning) merges them with all loads independent.
 #include "common.cuh"
 #include "kernels.h"
 #include "launch.h"
 
 namespace tfb {
 
-constexpr int kSplitLen = 128;
-constexpr int kAttnThreads = 128;
+constexpr int kSplitLen = 64;
+constexpr int kAttnThreads = 256;
 
 int attn_splits(int max_ctx) { return (max_ctx + kSplitLen - 1) / kSplitLen; }
 
@@ -23,130 +33,192 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
     f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x); f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
     f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
 }
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                 :: "r"(uint32_t(__cvta_generic_to_shared(smem_dst))), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 template <int D, int G>
 __global__ void __launch_bounds__(kAttnThreads) attn_gqa_kernel(const AttnParams p) {
-    constexpr int LPP = D / 8;                 // lanes that share one position's row
-    constexpr int PPW = 32 / LPP;              // positions a warp reads per load
+    constexpr int LPP = D / 8;                 // lanes that share one position's row (16 B each)
+    constexpr int NSG = kAttnThreads / LPP;    // position sub-groups in the CTA
     constexpr int NWARP = kAttnThreads / 32;
-    constexpr int NG = NWARP * PPW;            // position sub-groups in the CTA
     constexpr int NV = G + 1;                  // vectors normalised + rotated: G queries and the key
+    constexpr int OUT_PER_THREAD = (G * D + kAttnThreads - 1) / kAttnThreads;
 
-    __shared__ __align__(16) float vec[NV + 1][D];       // q_0..q_{G-1}, k_new, v_new
-    __shared__ __align__(16) float tmp[NV][D];
+    __shared__ __align__(16) uint16_t kbuf[kSplitLen][D];
+    __shared__ __align__(16) uint16_t vbuf[kSplitLen][D];
+    __shared__ __align__(16) float vec[NV + 1][D];       // q_0..q_{G-1} (scaled), k_new, v_new
+    __shared__ float gain[2][D];                         // q and k norm gains
+    __shared__ float rot[2][D];                          // cos / sin row of this position
     __shared__ float sc[G][kSplitLen];
-    __shared__ __align__(16) float red[NG][G][D];
     __shared__ float stat_m[G], stat_l[G];
+    __shared__ float mrg_w[G][64];                       // merge weights per split (64 splits per pass)
     __shared__ int s_last;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = blockIdx.x, split = blockIdx.y;
+    const int p0 = split * kSplitLen;
 
-    if (tid == 0)
-        l2_prefetch_slice(p.prefetch, p.prefetch_bytes, blockIdx.y * gridDim.x + blockIdx.x,
-                          gridDim.x * gridDim.y);
+    trace_start(p.trace);
+    // ---- before the dependency wait: start fetching the cached rows ---------------------
+    // Rows below the position word are final whatever step wrote that word last.
+    int pre_end = p0, rot_pos = -1;
+    {
+        const int pos_early = *reinterpret_cast<const volatile int*>(p.pos);
+        if (pos_early >= 0 && pos_early < p.max_ctx) {
+            pre_end = max(p0, min(p0 + kSplitLen, pos_early));
+            const int rows = pre_end - p0;
+            for (int c = tid; c < rows * LPP; c += kAttnThreads) {
+                const int r = c / LPP, piece = c % LPP;
+                const int pp = p0 + r;
+                const int page = p.block_table[pp / p.page_size];
+                const size_t off = ((size_t(page) * p.page_size + (pp % p.page_size)) * p.hkv + g) * D + piece * 8;
+                cp_async16(&kbuf[r][piece * 8], p.k_pool + off);
+                cp_async16(&vbuf[r][piece * 8], p.v_pool + off);
+            }
+        }
+        if (tid == 0)
+            l2_prefetch_slice(p.prefetch, p.prefetch_bytes, blockIdx.y * gridDim.x + blockIdx.x,
+                              gridDim.x * gridDim.y);
+        // weights and (most likely) the rotary row do not depend on the previous kernel either
+        if (tid < D) {
+            gain[0][tid] = p.norm_mode ? bf16_bits_to_f32(p.gamma_q[tid]) : 1.f;
+            gain[1][tid] = p.norm_mode ? bf16_bits_to_f32(p.gamma_k[tid]) : 1.f;
+        }
+        rot_pos = (p.rope_pos == nullptr && pos_early >= 0 && pos_early < p.max_ctx) ? pos_early : -1;
+        if (rot_pos >= 0 && tid < p.rotary_dim) {
+            rot[0][tid] = bf16_bits_to_f32(p.cos_table[size_t(rot_pos) * p.rotary_dim + tid]);
+            rot[1][tid] = bf16_bits_to_f32(p.sin_table[size_t(rot_pos) * p.rotary_dim + tid]);
+        }
+    }
     pdl_trigger();
     pdl_wait();
+    trace_waited(p.trace);
 
     const int pos = *p.pos;
-    if (pos < 0 || pos >= p.max_ctx) return;
     const int total = pos + 1;
     const int n_active = (total + kSplitLen - 1) / kSplitLen;
-    if (split >= n_active) return;
+    if (pos < 0 || pos >= p.max_ctx || split >= n_active) {
+        cp_async_wait_all();                   // nothing may still be landing in smem when the CTA exits
+        return;
+    }
     const bool owner = (split == n_active - 1);
-    const int p0 = split * kSplitLen;
     const int p1 = min(p0 + kSplitLen, total);
-    const int pend = min(p1, pos);             // cache positions; the new token is handled from smem
+    const int pend = min(p1, pos);             // cached rows of this split are [p0, pend)
+    for (int c = tid; c < max(pend - pre_end, 0) * LPP; c += kAttnThreads) {   // rows the early look missed
+        const int r = (pre_end - p0) + c / LPP, piece = c % LPP;
+        const int pp = p0 + r;
+        const int page = p.block_table[pp / p.page_size];
+        const size_t off = ((size_t(page) * p.page_size + (pp % p.page_size)) * p.hkv + g) * D + piece * 8;
+        cp_async16(&kbuf[r][piece * 8], p.k_pool + off);
+        cp_async16(&vbuf[r][piece * 8], p.v_pool + off);
+    }
 
-    // ---- this token's q (G heads), k, v for KV head g -------------------------
-    for (int vi = warp; vi < NV + 1; vi += NWARP) {
-        const uint16_t* src;
-        if (vi < G) src = p.qkv + size_t(g * G + vi) * D;
-        else if (vi == G) src = p.qkv + size_t(p.hq) * D + size_t(g) * D;
-        else src = p.qkv + size_t(p.hq + p.hkv) * D + size_t(g) * D;
-        float x[D / 32];
-        float ss = 0.f;
+    // ---- this token's q (G heads), k, v for KV head g -------------------------------------
+    // One warp per vector, everything in registers: lane l holds elements l, l+32, ...; the
+    // rotate-half partner of element i is i +- rotary_dim/2, a multiple of 32 away, so it sits in
+    // the same lane and norm -> RoPE -> scale needs no shared-memory round trip.
+    const int rd = p.rotary_dim, half = rd >> 1;
+    const int rpos = p.rope_pos ? *p.rope_pos : pos;
+    if (rpos != rot_pos && tid < rd) {            // the early look was a step behind (or not allowed)
+        rot[0][tid] = bf16_bits_to_f32(p.cos_table[size_t(rpos) * rd + tid]);
+        rot[1][tid] = bf16_bits_to_f32(p.sin_table[size_t(rpos) * rd + tid]);
+    }
+    float xv[2][D / 32];                         // up to two vectors per warp (NV + 1 <= 2 * NWARP)
+    int vis[2] = {warp, warp + NWARP};
 #pragma unroll
-        for (int i = 0; i < D / 32; ++i) {
-            x[i] = bf16_bits_to_f32(src[lane + 32 * i]);
-            ss = fmaf(x[i], x[i], ss);
+    for (int s2 = 0; s2 < 2; ++s2) {
+        const int vi = vis[s2];
+        if (vi < NV + 1) {
+            const uint16_t* src;
+            if (vi < G) src = p.qkv + size_t(g * G + vi) * D;
+            else if (vi == G) src = p.qkv + size_t(p.hq) * D + size_t(g) * D;
+            else src = p.qkv + size_t(p.hq + p.hkv) * D + size_t(g) * D;
+#pragma unroll
+            for (int i = 0; i < D / 32; ++i) xv[s2][i] = bf16_bits_to_f32(src[lane + 32 * i]);
         }
-        if (vi == G + 1) {                     // v: no norm, no rotation
+    }
+    __syncthreads();                             // rot[] / gain[] visible
+#pragma unroll
+    for (int s2 = 0; s2 < 2; ++s2) {
+        const int vi = vis[s2];
+        if (vi >= NV + 1) continue;
+        float* x = xv[s2];
+        if (vi == G + 1) {                       // v: no norm, no rotation
 #pragma unroll
             for (int i = 0; i < D / 32; ++i) vec[vi][lane + 32 * i] = x[i];
             continue;
         }
-        float rstd = 1.f;
-        const uint16_t* gam = (vi < G) ? p.gamma_q : p.gamma_k;
         if (p.norm_mode != 0) {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < D / 32; ++i) ss = fmaf(x[i], x[i], ss);
             ss = warp_sum(ss);
-            rstd = rsqrtf(ss / float(D) + p.eps);
+            const float rstd = rsqrtf(ss / float(D) + p.eps);
+            const float* gm = gain[vi < G ? 0 : 1];
+#pragma unroll
+            for (int i = 0; i < D / 32; ++i) x[i] = round_bf16(round_bf16(x[i] * rstd) * gm[lane + 32 * i]);
         }
+        float r[D / 32];
 #pragma unroll
         for (int i = 0; i < D / 32; ++i) {
-            float n = x[i];
-            if (p.norm_mode != 0) n = round_bf16(round_bf16(n * rstd) * bf16_bits_to_f32(gam[lane + 32 * i]));
-            tmp[vi][lane + 32 * i] = n;
+            const int e = lane + 32 * i;
+            r[i] = x[i];
+            if (e < rd) {
+                // partner index e +- half; half is a multiple of 32, so it is register i +- half/32
+                const int pi = (e < half) ? i + half / 32 : i - half / 32;
+                float partner = 0.f;
+#pragma unroll
+                for (int k2 = 0; k2 < D / 32; ++k2) if (k2 == pi) partner = x[k2];
+                if (e < half) partner = -partner;
+                r[i] = round_bf16(__fadd_rn(__fmul_rn(x[i], rot[0][e]), __fmul_rn(partner, rot[1][e])));
+            }
+            if (vi < G) r[i] = round_bf16(r[i] * p.scale);
+            vec[vi][e] = r[i];
         }
     }
     __syncthreads();
-    const int rd = p.rotary_dim, half = rd >> 1;
-    const int rpos = p.rope_pos ? *p.rope_pos : pos;
-    for (int e = tid; e < NV * D; e += kAttnThreads) {
-        const int vi = e / D, i = e % D;
-        float r = tmp[vi][i];
-        if (i < rd) {
-            const float c = bf16_bits_to_f32(p.cos_table[size_t(rpos) * rd + i]);
-            const float s = bf16_bits_to_f32(p.sin_table[size_t(rpos) * rd + i]);
-            const float partner = (i < half) ? -tmp[vi][i + half] : tmp[vi][i - half];
-            r = round_bf16(__fadd_rn(__fmul_rn(r, c), __fmul_rn(partner, s)));
-        }
-        if (vi < G) r = round_bf16(r * p.scale);
-        vec[vi][i] = r;
-    }
-    __syncthreads();
+    trace_mark(p.trace, 0);
 
-    if (owner) {                                // append this token's entry to the cache
+    if (owner) {                                // append this token's entry: cache, outputs, shared tile
         const int page = p.block_table[pos / p.page_size];
         const size_t base = ((size_t(page) * p.page_size + (pos % p.page_size)) * p.hkv + g) * D;
         for (int i = tid; i < D; i += kAttnThreads) {
             const uint16_t kb = f32_to_bf16_bits(vec[G][i]), vb = f32_to_bf16_bits(vec[G + 1][i]);
             p.k_pool[base + i] = kb;
             p.v_pool[base + i] = vb;
+            kbuf[pos - p0][i] = kb;
+            vbuf[pos - p0][i] = vb;
             if (p.k_new_out) p.k_new_out[size_t(g) * D + i] = kb;
             if (p.v_new_out) p.v_new_out[size_t(g) * D + i] = vb;
         }
     }
+    cp_async_wait_all();
+    __syncthreads();
+    trace_mark(p.trace, 1);
 
-    // ---- pass 1: scores ----------------------------------------------------------
-    const int sg = warp * PPW + lane / LPP, sl = lane % LPP;
-    float q[G][8];
+    // ---- scores --------------------------------------------------------------------------------
+    const int n = p1 - p0;                      // rows in the shared tile, the new one included
+    {
+        const int sg = tid / LPP, sl = tid % LPP;
+        float q[G][8];
 #pragma unroll
-    for (int j = 0; j < G; ++j)
+        for (int j = 0; j < G; ++j)
 #pragma unroll
-        for (int i = 0; i < 8; ++i) q[j][i] = vec[j][sl * 8 + i];
-
-    constexpr int U = 4;
-    // Every lane of a warp runs the same trip count (the shuffles below need the
-    // full warp); only loads and stores are guarded by the position bound.
-    for (int pb = p0; pb < pend; pb += NG * U) {
-        uint4 kv[U];
+            for (int i = 0; i < 8; ++i) q[j][i] = vec[j][sl * 8 + i];
+        // every lane runs the same trip count (the shuffles need the full warp)
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int pp = pb + u * NG + sg;
-            if (pp < pend) {
-                const int page = p.block_table[pp / p.page_size];
-                const size_t off = ((size_t(page) * p.page_size + (pp % p.page_size)) * p.hkv + g) * D + sl * 8;
-                kv[u] = *reinterpret_cast<const uint4*>(p.k_pool + off);
-            } else {
-                kv[u] = make_uint4(0, 0, 0, 0);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int pp = pb + u * NG + sg;
+        for (int r0 = 0; r0 < kSplitLen; r0 += NSG) {
+            const int r = r0 + sg;
             float kf[8];
-            unpack8(kv[u], kf);
+            if (r < n) {
+                unpack8(*reinterpret_cast<const uint4*>(&kbuf[r][sl * 8]), kf);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) kf[i] = 0.f;
+            }
 #pragma unroll
             for (int j = 0; j < G; ++j) {
                 float s = 0.f;
@@ -154,23 +226,13 @@ __global__ void __launch_bounds__(kAttnThreads) attn_gqa_kernel(const AttnParams
                 for (int i = 0; i < 8; ++i) s = fmaf(q[j][i], kf[i], s);
 #pragma unroll
                 for (int o = LPP / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                if (sl == 0 && pp < pend) sc[j][pp - p0] = s;
+                if (sl == 0 && r < n) sc[j][r] = s;
             }
-        }
-    }
-    if (owner && warp == 0) {                   // the token attends itself
-#pragma unroll
-        for (int j = 0; j < G; ++j) {
-            float s = 0.f;
-            for (int i = lane; i < D; i += 32) s = fmaf(vec[j][i], vec[G][i], s);
-            s = warp_sum(s);
-            if (lane == 0) sc[j][pos - p0] = s;
         }
     }
     __syncthreads();
 
-    // ---- softmax statistics of this split ----------------------------------------
-    const int n = p1 - p0;
+    // ---- softmax statistics of this split ----------------------------------------------------
     for (int j = warp; j < G; j += NWARP) {
         float m = -INFINITY;
         for (int i = lane; i < n; i += 32) m = fmaxf(m, sc[j][i]);
@@ -186,68 +248,35 @@ __global__ void __launch_bounds__(kAttnThreads) attn_gqa_kernel(const AttnParams
     }
     __syncthreads();
 
-    // ---- pass 2: probability-weighted V --------------------------------------------
-    float acc[G][8];
-#pragma unroll
-    for (int j = 0; j < G; ++j)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
-    for (int pb = p0; pb < pend; pb += NG * U) {
-        uint4 vv[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int pp = pb + u * NG + sg;
-            if (pp < pend) {
-                const int page = p.block_table[pp / p.page_size];
-                const size_t off = ((size_t(page) * p.page_size + (pp % p.page_size)) * p.hkv + g) * D + sl * 8;
-                vv[u] = *reinterpret_cast<const uint4*>(p.v_pool + off);
-            } else {
-                vv[u] = make_uint4(0, 0, 0, 0);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int pp = pb + u * NG + sg;
-            if (pp < pend) {
-                float vf[8];
-                unpack8(vv[u], vf);
-#pragma unroll
-                for (int j = 0; j < G; ++j) {
-                    const float pr = sc[j][pp - p0];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) acc[j][i] = fmaf(pr, vf[i], acc[j][i]);
-                }
-            }
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < G; ++j)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) red[sg][j][sl * 8 + i] = acc[j][i];
-    __syncthreads();
-
+    // ---- probability-weighted V: each thread owns whole output elements -----------------------
     const int nsplit = p.nsplit;
-    for (int e = tid; e < G * D; e += kAttnThreads) {
-        const int j = e / D, d = e % D;
-        float o = 0.f;
 #pragma unroll
-        for (int s = 0; s < NG; ++s) o += red[s][j][d];
-        if (owner) o = fmaf(sc[j][pos - p0], vec[G + 1][d], o);
-        const int head = g * G + j;
-        if (n_active == 1) {
-            p.out[size_t(head) * D + d] = f32_to_bf16_bits(o / stat_l[j]);
-        } else {
-            p.part_o[(size_t(head) * nsplit + split) * D + d] = o;
+    for (int t = 0; t < OUT_PER_THREAD; ++t) {
+        const int e = tid + t * kAttnThreads;
+        if (e < G * D) {
+            const int j = e / D, d = e % D;
+            float o0 = 0.f, o1 = 0.f;
+            int r = 0;
+            for (; r + 1 < n; r += 2) {
+                o0 = fmaf(sc[j][r], bf16_bits_to_f32(vbuf[r][d]), o0);
+                o1 = fmaf(sc[j][r + 1], bf16_bits_to_f32(vbuf[r + 1][d]), o1);
+            }
+            if (r < n) o0 = fmaf(sc[j][r], bf16_bits_to_f32(vbuf[r][d]), o0);
+            const float o = o0 + o1;
+            const int head = g * G + j;
+            if (n_active == 1) p.out[size_t(head) * D + d] = f32_to_bf16_bits(o / stat_l[j]);
+            else p.part_o[(size_t(head) * nsplit + split) * D + d] = o;
         }
     }
-    if (n_active == 1) return;
+    if (n_active == 1) { trace_end(p.trace); return; }
     if (tid < G) {
         const int head = g * G + tid;
         p.part_ml[(size_t(head) * nsplit + split) * 2] = stat_m[tid];
         p.part_ml[(size_t(head) * nsplit + split) * 2 + 1] = stat_l[tid];
     }
 
-    // ---- merge by the last CTA of this KV head ---------------------------------------
+    trace_mark(p.trace, 2);
+    // ---- merge by the last CTA of this KV head ---------------------------------------------------
     __threadfence();
     __syncthreads();
     if (tid == 0) {
@@ -255,30 +284,87 @@ __global__ void __launch_bounds__(kAttnThreads) attn_gqa_kernel(const AttnParams
         s_last = (ticket == unsigned(n_active - 1));
     }
     __syncthreads();
-    if (!s_last) return;
+    trace_mark(p.trace, 3);
+    if (!s_last) { trace_end(p.trace); return; }
     __threadfence();
-    for (int e = tid; e < G * D; e += kAttnThreads) {
-        const int j = e / D, d = e % D;
-        const int head = g * G + j;
-        const float* ml = p.part_ml + size_t(head) * nsplit * 2;
-        float M = -INFINITY;
-        for (int s = 0; s < n_active; ++s) M = fmaxf(M, __ldcg(ml + 2 * s));
-        float num = 0.f, den = 0.f;
-        for (int s = 0; s < n_active; ++s) {
-            const float w = __expf(__ldcg(ml + 2 * s) - M);
-            num = fmaf(w, __ldcg(p.part_o + (size_t(head) * nsplit + s) * D + d), num);
-            den = fmaf(w, __ldcg(ml + 2 * s + 1), den);
+
+    float num[OUT_PER_THREAD], den[OUT_PER_THREAD], run_m[OUT_PER_THREAD];
+#pragma unroll
+    for (int t = 0; t < OUT_PER_THREAD; ++t) { num[t] = 0.f; den[t] = 0.f; run_m[t] = -INFINITY; }
+    for (int s0 = 0; s0 < n_active; s0 += 64) {              // 64 splits per pass (4096 positions)
+        const int ns = min(64, n_active - s0);
+        __syncthreads();
+        // per head: max over this pass, weights exp(m_s - M) into shared
+        for (int j = warp; j < G; j += NWARP) {
+            const float* ml = p.part_ml + (size_t(g * G + j) * nsplit + s0) * 2;
+            const float m0 = lane < ns ? __ldcg(ml + 2 * lane) : -INFINITY;
+            const float m1 = lane + 32 < ns ? __ldcg(ml + 2 * (lane + 32)) : -INFINITY;
+            const float M = warp_max(fmaxf(m0, m1));
+            if (lane < ns) mrg_w[j][lane] = __expf(m0 - M);
+            if (lane + 32 < ns) mrg_w[j][lane + 32] = __expf(m1 - M);
+            if (lane == 0) stat_m[j] = M;
         }
-        p.out[size_t(head) * D + d] = f32_to_bf16_bits(num / den);
+        __syncthreads();
+#pragma unroll
+        for (int t = 0; t < OUT_PER_THREAD; ++t) {
+            const int e = tid + t * kAttnThreads;
+            if (e < G * D) {
+                const int j = e / D, d = e % D;
+                const int head = g * G + j;
+                const float* po = p.part_o + (size_t(head) * nsplit + s0) * D + d;
+                const float* ml = p.part_ml + (size_t(head) * nsplit + s0) * 2;
+                float a = 0.f, b = 0.f;
+                int s = 0;
+                for (; s + 4 <= ns; s += 4) {                  // independent loads, four in flight
+                    const float v0 = __ldcg(po + size_t(s) * D), v1 = __ldcg(po + size_t(s + 1) * D);
+                    const float v2 = __ldcg(po + size_t(s + 2) * D), v3 = __ldcg(po + size_t(s + 3) * D);
+                    const float l0 = __ldcg(ml + 2 * s + 1), l1 = __ldcg(ml + 2 * s + 3);
+                    const float l2 = __ldcg(ml + 2 * s + 5), l3 = __ldcg(ml + 2 * s + 7);
+                    a = fmaf(mrg_w[j][s], v0, a); a = fmaf(mrg_w[j][s + 1], v1, a);
+                    a = fmaf(mrg_w[j][s + 2], v2, a); a = fmaf(mrg_w[j][s + 3], v3, a);
+                    b = fmaf(mrg_w[j][s], l0, b); b = fmaf(mrg_w[j][s + 1], l1, b);
+                    b = fmaf(mrg_w[j][s + 2], l2, b); b = fmaf(mrg_w[j][s + 3], l3, b);
+                }
+                for (; s < ns; ++s) {
+                    a = fmaf(mrg_w[j][s], __ldcg(po + size_t(s) * D), a);
+                    b = fmaf(mrg_w[j][s], __ldcg(ml + 2 * s + 1), b);
+                }
+                // fold this pass into the running (max, num, den)
+                const float M = stat_m[j];
+                const float newm = fmaxf(run_m[t], M);
+                const float c_old = run_m[t] == -INFINITY ? 0.f : __expf(run_m[t] - newm);
+                const float c_new = __expf(M - newm);
+                num[t] = num[t] * c_old + a * c_new;
+                den[t] = den[t] * c_old + b * c_new;
+                run_m[t] = newm;
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < OUT_PER_THREAD; ++t) {
+        const int e = tid + t * kAttnThreads;
+        if (e < G * D) {
+            const int j = e / D, d = e % D;
+            p.out[size_t(g * G + j) * D + d] = f32_to_bf16_bits(num[t] / den[t]);
+        }
     }
     if (tid == 0) p.counters[g] = 0;
+    trace_end(p.trace);
 }
 
 cudaError_t attn_gqa_dispatch(const AttnParams& p, cudaStream_t stream, bool pdl) {
     const int G = p.hq / p.hkv;
     const dim3 grid(p.hkv, p.nsplit), block(kAttnThreads);
-#define TFB_ATTN(DD, GG) \
-    if (p.d == DD && G == GG) return launch_kernel(attn_gqa_kernel<DD, GG>, grid, block, 0, stream, pdl, p);
+#define TFB_ATTN(DD, GG)                                                                                  \
+    if (p.d == DD && G == GG) {                                                                           \
+        static bool once = false;                                                                         \
+        if (!once) {                                                                                      \
+            cudaFuncSetAttribute(attn_gqa_kernel<DD, GG>, cudaFuncAttributePreferredSharedMemoryCarveout, \
+                                 cudaSharedmemCarveoutMaxShared);                                         \
+            once = true;                                                                                  \
+        }                                                                                                 \
+        return launch_kernel(attn_gqa_kernel<DD, GG>, grid, block, 0, stream, pdl, p);                    \
+    }
     TFB_ATTN(128, 1) TFB_ATTN(128, 2) TFB_ATTN(128, 4) TFB_ATTN(64, 2) TFB_ATTN(64, 1)
 #undef TFB_ATTN
     return cudaErrorInvalidValue;

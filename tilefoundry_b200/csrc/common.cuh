@@ -59,6 +59,27 @@ __device__ __forceinline__ void l2_prefetch_slice(const void* base, unsigned lon
     }
 }
 
+// ---- optional timeline trace (debug): 8 words per launch -------------------------------
+// [0] earliest CTA start, [1] earliest / [2] latest return from the dependency wait, [3] latest exit
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void trace_start(unsigned long long* t) {
+    if (t && threadIdx.x == 0) atomicMin(t, global_ns());
+}
+__device__ __forceinline__ void trace_waited(unsigned long long* t) {
+    if (t && threadIdx.x == 0) { const unsigned long long g = global_ns(); atomicMin(t + 1, g); atomicMax(t + 2, g); }
+}
+// words 4..7: latest time any CTA passed an interior mark
+__device__ __forceinline__ void trace_mark(unsigned long long* t, int which) {
+    if (t && threadIdx.x == 0) atomicMax(t + 4 + which, global_ns());
+}
+__device__ __forceinline__ void trace_end(unsigned long long* t) {
+    if (t && threadIdx.x == 0) atomicMax(t + 3, global_ns());
+}
+
 // ---- reductions -----------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

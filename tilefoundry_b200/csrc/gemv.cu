@@ -7,6 +7,9 @@
 #include "kernels.h"
 #include "launch.h"
 
+#include <cstdio>
+#include <cstdlib>
+
 namespace tfb {
 
 
@@ -30,6 +33,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
     const int it_per = (its + KSPLIT - 1) / KSPLIT;
     const int it_begin = ks * it_per, it_end = min(its, it_begin + it_per);
 
+    trace_start(p.trace);
     // Weights do not depend on the preceding kernel: start streaming them now.
     RowsDot<ROWS, UNROLL> a, b;
     const uint4* wrow = p.w + size_t(max(row0, 0)) * row_stride;
@@ -37,12 +41,24 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
     a.load(wrow, row_stride, rows_valid, it_begin, it_end, lane);
     if (EPI == 2) b.load(w2row, row_stride, rows_valid, it_begin, it_end, lane);
     if (threadIdx.x == 0) l2_prefetch_slice(p.prefetch, p.prefetch_bytes, blockIdx.x, gridDim.x);
+    constexpr int MAXC = 4;
+    const bool fast_stage = (p.k >> 3) <= MAXC * WARPS * 32;
+    StagedGain<MAXC> sg;
+    if (fast_stage) sg.template preload<NORM_MODE>(p.gamma, p.k);
 
     pdl_trigger();
     pdl_wait();
+    trace_waited(p.trace);
 
-    stage_activation<NORM_MODE>(p.x, p.gamma, xs, red, p.k, p.eps, p.x_scale);
+    // the residual is needed last but its load is issued first: one round trip less at the end
+    float res_early = 0.f;
+    if (EPI == 1 && KSPLIT == 1 && lane < rows_valid) res_early = bf16_bits_to_f32(p.residual[row0 + lane]);
+    if (EPI == 1 && KSPLIT > 1 && ks == 0 && lane < rows_valid) res_early = bf16_bits_to_f32(p.residual[row0 + lane]);
+
+    if (fast_stage) sg.template stage<NORM_MODE>(p.x, xs, red, p.k, p.eps, p.x_scale);
+    else stage_activation<NORM_MODE>(p.x, p.gamma, xs, red, p.k, p.eps, p.x_scale);
     __syncthreads();
+    trace_mark(p.trace, 0);
 
     float acc[ROWS], acc2[ROWS];
 #pragma unroll
@@ -97,7 +113,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
         } else if (EPI == 1) {
             float o = round_bf16(v);
             if (p.res_scale != 1.f) o = round_bf16(o * p.res_scale);
-            static_cast<uint16_t*>(p.y)[row] = f32_to_bf16_bits(bf16_bits_to_f32(p.residual[row]) + o);
+            static_cast<uint16_t*>(p.y)[row] = f32_to_bf16_bits(res_early + o);
         } else if (EPI == 2) {
             const float g = round_bf16(v), u = round_bf16(v2);
             static_cast<uint16_t*>(p.y)[row] = f32_to_bf16_bits(round_bf16(silu_f32(g)) * u);
@@ -105,6 +121,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
             static_cast<float*>(p.y)[row] = v * p.out_scale;
         }
     }
+    trace_end(p.trace);
 }
 
 template <int ROWS, int KSPLIT, int WARPS, int UNROLL, int NORM_MODE, int EPI>
@@ -127,25 +144,46 @@ static cudaError_t pick_shape(const GemvParams& p, cudaStream_t stream, bool pdl
     // Shape choice: enough warps to cover 148 SMs several times over, rows per warp
     // and K-split chosen so one warp streams 4-8 KB.
     const long long bytes = 2ll * p.n * p.k * (EPI == 2 ? 2 : 1);
+#ifdef TFB_TUNE
+    if (const char* e = getenv("TFB_GEMV_CFG")) {
+        int r = 0, ks = 0, w = 0, u = 0;
+        if (sscanf(e, "%d,%d,%d,%d", &r, &ks, &w, &u) == 4) {
+#define TFB_TRY(R, KS, W, U) \
+    if (r == R && ks == KS && w == W && u == U) return launch_cfg<R, KS, W, U, NORM_MODE, EPI>(p, stream, pdl);
+            TFB_TRY(1, 1, 4, 8) TFB_TRY(1, 2, 4, 4) TFB_TRY(1, 1, 8, 8) TFB_TRY(1, 2, 8, 4) TFB_TRY(1, 1, 2, 8)
+            TFB_TRY(1, 3, 6, 8) TFB_TRY(1, 3, 3, 8) TFB_TRY(1, 6, 6, 4) TFB_TRY(2, 3, 6, 4) TFB_TRY(1, 4, 4, 2)
+            TFB_TRY(1, 1, 4, 4) TFB_TRY(2, 1, 4, 4) TFB_TRY(2, 2, 4, 4) TFB_TRY(2, 4, 8, 4) TFB_TRY(2, 1, 4, 8)
+#undef TFB_TRY
+        }
+    }
+#endif
+    // Measured on B200 (graph of 28 back-to-back launches, one per layer's weights): for k <= 2048
+    // the whole row in flight in one batch (UNROLL 8) with 8-warp CTAs is fastest; the wide
+    // SwiGLU and k >= 4096 shapes prefer two rows per warp with an in-CTA K split.
+    (void)bytes;
     if (EPI == 2) {
-        return launch_cfg<1, 1, 4, 4, NORM_MODE, EPI>(p, stream, pdl);
+        return launch_cfg<2, 2, 4, 4, NORM_MODE, EPI>(p, stream, pdl);
     }
     if (p.k >= 4096) {
         return launch_cfg<2, 4, 8, 4, NORM_MODE, EPI>(p, stream, pdl);
     }
-    if (bytes <= (12ll << 20)) {
+    if (p.k > 2048) {
         return launch_cfg<2, 2, 4, 4, NORM_MODE, EPI>(p, stream, pdl);
     }
-    return launch_cfg<2, 1, 4, 4, NORM_MODE, EPI>(p, stream, pdl);
+    return launch_cfg<1, 1, 8, 8, NORM_MODE, EPI>(p, stream, pdl);
 }
 
 cudaError_t gemv_dispatch(const GemvParams& p, int norm_mode, int epi, cudaStream_t stream, bool pdl) {
 #define TFB_CASE(NM, EP) \
     if (norm_mode == NM && epi == EP) return pick_shape<NM, EP>(p, stream, pdl);
+#ifdef TFB_TUNE
+    TFB_CASE(0, 0) TFB_CASE(2, 0) TFB_CASE(0, 1) TFB_CASE(2, 2)
+#else
     TFB_CASE(0, 0) TFB_CASE(1, 0) TFB_CASE(2, 0)
     TFB_CASE(0, 1) TFB_CASE(1, 1) TFB_CASE(2, 1)
     TFB_CASE(0, 2) TFB_CASE(1, 2) TFB_CASE(2, 2)
     TFB_CASE(0, 3) TFB_CASE(1, 3) TFB_CASE(2, 3)
+#endif
 #undef TFB_CASE
     return cudaErrorInvalidValue;
 }

@@ -76,6 +76,78 @@ __device__ __forceinline__ void stage_activation(const uint16_t* __restrict__ x,
     }
 }
 
+// Same staging with the norm gains fetched ahead of time (they are weights, so they can be read
+// before the dependency wait) and x read from global memory exactly once: one memory round trip
+// between the wait and the first dot product instead of three.  Each thread owns up to MAXC
+// 8-element pieces; callers fall back to stage_activation when k/8 > MAXC * blockDim.x.
+template <int MAXC>
+struct StagedGain {
+    uint4 g[MAXC];
+    template <int NORM_MODE>
+    __device__ __forceinline__ void preload(const uint16_t* __restrict__ gamma, int k) {
+        if (NORM_MODE == 0) return;
+#pragma unroll
+        for (int m = 0; m < MAXC; ++m) {
+            const int c = threadIdx.x + m * blockDim.x;
+            g[m] = (c < (k >> 3)) ? *reinterpret_cast<const uint4*>(gamma + (c << 3)) : make_uint4(0, 0, 0, 0);
+        }
+    }
+    template <int NORM_MODE>
+    __device__ __forceinline__ void stage(const uint16_t* __restrict__ x, float* xs, float* red, int k,
+                                          float eps, float x_scale) {
+        uint4 xv[MAXC];
+#pragma unroll
+        for (int m = 0; m < MAXC; ++m) {
+            const int c = threadIdx.x + m * blockDim.x;
+            xv[m] = (c < (k >> 3)) ? *reinterpret_cast<const uint4*>(x + (c << 3)) : make_uint4(0, 0, 0, 0);
+        }
+        float rstd = 1.f;
+        if (NORM_MODE != 0) {
+            float ss = 0.f;
+#pragma unroll
+            for (int m = 0; m < MAXC; ++m) {
+                const uint32_t u[4] = {xv[m].x, xv[m].y, xv[m].z, xv[m].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float a = bf16_lo(u[i]), b = bf16_hi(u[i]);
+                    ss = fmaf(a, a, ss);
+                    ss = fmaf(b, b, ss);
+                }
+            }
+            ss = block_sum(ss, red);
+            rstd = rsqrtf(ss / float(k) + eps);
+        }
+#pragma unroll
+        for (int m = 0; m < MAXC; ++m) {
+            const int c = threadIdx.x + m * blockDim.x;
+            if (c >= (k >> 3)) continue;
+            const uint32_t u[4] = {xv[m].x, xv[m].y, xv[m].z, xv[m].w};
+            const uint32_t gg[4] = {g[m].x, g[m].y, g[m].z, g[m].w};
+            float f[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                f[2 * i] = bf16_lo(u[i]);
+                f[2 * i + 1] = bf16_hi(u[i]);
+                if (NORM_MODE == 2) {
+                    f[2 * i] = round_bf16(round_bf16(f[2 * i] * rstd) * bf16_lo(gg[i]));
+                    f[2 * i + 1] = round_bf16(round_bf16(f[2 * i + 1] * rstd) * bf16_hi(gg[i]));
+                } else if (NORM_MODE == 1) {
+                    f[2 * i] = round_bf16(f[2 * i] * rstd * bf16_lo(gg[i]));
+                    f[2 * i + 1] = round_bf16(f[2 * i + 1] * rstd * bf16_hi(gg[i]));
+                }
+            }
+            if (x_scale != 1.f) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] = round_bf16(f[i] * x_scale);
+            }
+            const int it = c >> 5, lane = c & 31;
+            float4* dst = reinterpret_cast<float4*>(xs);
+            dst[(it * 2) * 32 + lane] = make_float4(f[0], f[1], f[2], f[3]);
+            dst[(it * 2 + 1) * 32 + lane] = make_float4(f[4], f[5], f[6], f[7]);
+        }
+    }
+};
+
 // Dot products of ROWS weight rows with the staged activation over the 16-byte
 // pieces [it_begin, it_end) x 32 lanes.  `w` points at row 0, `row_stride` in
 // uint4 units; rows at or beyond `rows_valid` are skipped (their acc stays 0).

@@ -16,7 +16,22 @@ struct GemvParams {
     float eps, x_scale, res_scale, out_scale;
     const void* prefetch;
     unsigned long long prefetch_bytes;
+    unsigned long long* trace;
+    // streaming kernel only
+    int kc, nstages, self_prefetch;
+    unsigned* status;
+    // lm_head mode (epilogue 4) of the streaming kernel
+    float* scratch_val;
+    int* scratch_idx;
+    unsigned* counter;
+    long long* token_out;
+    long long* tokens;
+    int* pos;
+    int n_prompt, max_tokens;
 };
+bool gemv_stream_supported(int n, int k);
+cudaError_t gemv_stream_dispatch(const GemvParams& p, int norm_mode, int epi, cudaStream_t stream, bool pdl);
+int lm_head_stream_ctas();
 cudaError_t gemv_dispatch(const GemvParams& p, int norm_mode, int epi, cudaStream_t stream, bool pdl);
 
 struct AttnParams {
@@ -41,6 +56,7 @@ struct AttnParams {
     int norm_mode;
     const void* prefetch;
     unsigned long long prefetch_bytes;
+    unsigned long long* trace;
 };
 int attn_splits(int max_ctx);
 cudaError_t attn_gqa_dispatch(const AttnParams& p, cudaStream_t stream, bool pdl);
@@ -59,6 +75,7 @@ struct HeadParams {
     long long* tokens;
     int* pos;
     int n_prompt, max_tokens;
+    unsigned long long* trace;
 };
 int lm_head_ctas(int n);
 cudaError_t lm_head_dispatch(const HeadParams& p, int norm_mode, cudaStream_t stream, bool pdl);

@@ -108,11 +108,13 @@ __global__ void __launch_bounds__(kHeadWarps * 32) lm_head_kernel(const HeadPara
     const int rows_valid = min(kHeadRows, p.n - row0);
     const int row_stride = p.k >> 3, its = p.k >> 8;
 
+    trace_start(p.trace);
     RowsDot<kHeadRows, kHeadUnroll> a;
     const uint4* wrow = p.w + size_t(row0) * row_stride;
     a.load(wrow, row_stride, rows_valid, 0, its, lane);
     pdl_trigger();
     pdl_wait();
+    trace_waited(p.trace);
     stage_activation<NORM_MODE>(p.x, p.gamma, xs, red, p.k, p.eps, p.x_scale);
     __syncthreads();
 
@@ -144,7 +146,7 @@ __global__ void __launch_bounds__(kHeadWarps * 32) lm_head_kernel(const HeadPara
         s_last = (ticket == gridDim.x - 1);
     }
     __syncthreads();
-    if (!s_last) return;
+    if (!s_last) { trace_end(p.trace); return; }
     __threadfence();
     best = -INFINITY;
     best_i = 0x7fffffff;
@@ -170,6 +172,7 @@ __global__ void __launch_bounds__(kHeadWarps * 32) lm_head_kernel(const HeadPara
         }
         *p.counter = 0;
     }
+    trace_end(p.trace);
 }
 
 cudaError_t lm_head_dispatch(const HeadParams& p, int norm_mode, cudaStream_t stream, bool pdl) {

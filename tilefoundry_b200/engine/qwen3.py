@@ -46,7 +46,7 @@ def pack_layer(w: dict) -> dict:
 class Qwen3Session:
     def __init__(self, cfg: Qwen3Config, resource, *, max_ctx: int = 2176, device="cuda:0",
                  keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True,
-                 l2_prefetch: bool = True):
+                 l2_prefetch: int = 0, kernel: int = 0):
         if not torch.cuda.is_available():
             raise RuntimeError("Qwen3Session needs a CUDA device; there is no CPU path")
         lib.load()
@@ -96,6 +96,7 @@ class Qwen3Session:
         self.head_val = z(n_head, dtype=f32)
         self.head_idx = z(n_head, dtype=torch.int32)
         self.trace = z(cfg.num_hidden_layers + 1, H) if trace_hidden else None
+        self.picked = z(1, dtype=torch.int64)
 
         self._layer_structs = (lib.Qwen3Layer * len(self.layers))()
         for s, layer in zip(self._layer_structs, self.layers):
@@ -114,7 +115,7 @@ class Qwen3Session:
             act_buf=lib.ptr(self.act), logits=lib.ptr(self.logits), part_o=lib.ptr(self.part_o),
             part_ml=lib.ptr(self.part_ml), counters=lib.ptr(self.counters), head_val=lib.ptr(self.head_val),
             head_idx=lib.ptr(self.head_idx), hidden_trace=lib.ptr(self.trace),
-            pdl=int(pdl), l2_prefetch=int(l2_prefetch))
+            pdl=int(pdl), l2_prefetch=int(l2_prefetch), kernel=int(kernel), picked=lib.ptr(self.picked))
         self.graph = None
         self._graph_prompt = None
         #: kernels one step enqueues (embed + 5 per layer + lm_head [+ trace copies and final norm])

@@ -11,7 +11,9 @@ from pathlib import Path
 
 import torch
 
-LIB_PATH = Path(__file__).resolve().parent / "csrc" / "libtfb200.so"
+import os
+
+LIB_PATH = Path(os.environ.get("TFB200_LIB") or Path(__file__).resolve().parent / "csrc" / "libtfb200.so")
 
 NORM_NONE, NORM_F32GAIN, NORM_CAST_THEN_GAIN = 0, 1, 2
 EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU, EPI_STORE_F32 = 0, 1, 2, 3
@@ -23,7 +25,7 @@ class GemvArgs(C.Structure):
     _fields_ = [("w", _vp), ("w2", _vp), ("x", _vp), ("gamma", _vp), ("residual", _vp), ("y", _vp),
                 ("n", _i32), ("k", _i32), ("prologue", _i32), ("epilogue", _i32),
                 ("eps", _f32), ("x_scale", _f32), ("res_scale", _f32), ("out_scale", _f32),
-                ("prefetch", _vp), ("prefetch_bytes", _u64), ("pdl", _i32), ("reserved", _i32)]
+                ("prefetch", _vp), ("prefetch_bytes", _u64), ("pdl", _i32), ("kernel", _i32), ("self_prefetch", _i32), ("reserved", _i32)]
 
 
 class LmHeadArgs(C.Structure):
@@ -31,7 +33,7 @@ class LmHeadArgs(C.Structure):
                 ("scratch_val", _vp), ("scratch_idx", _vp), ("counter", _vp),
                 ("n", _i32), ("k", _i32), ("prologue", _i32),
                 ("eps", _f32), ("x_scale", _f32), ("out_scale", _f32), ("pdl", _i32),
-                ("tokens", _vp), ("pos", _vp), ("n_prompt", _i32), ("max_tokens", _i32)]
+                ("tokens", _vp), ("pos", _vp), ("n_prompt", _i32), ("max_tokens", _i32), ("kernel", _i32), ("self_prefetch", _i32)]
 
 
 class AttnGqaArgs(C.Structure):
@@ -58,7 +60,7 @@ class Qwen3StepArgs(C.Structure):
                 ("block_table", _vp), ("tokens", _vp), ("pos", _vp), ("n_prompt", _i32), ("max_tokens", _i32),
                 ("hidden_buf", _vp), ("qkv_buf", _vp), ("attn_buf", _vp), ("act_buf", _vp), ("logits", _vp),
                 ("part_o", _vp), ("part_ml", _vp), ("counters", _vp), ("head_val", _vp), ("head_idx", _vp),
-                ("hidden_trace", _vp), ("pdl", _i32), ("l2_prefetch", _i32)]
+                ("hidden_trace", _vp), ("pdl", _i32), ("l2_prefetch", _i32), ("kernel", _i32), ("picked", _vp)]
 
 
 #: every symbol ``include/tfb200.h`` declares: name -> (restype, argtypes)
@@ -66,6 +68,7 @@ SYMBOLS = {
     "tfb_version": (_i32, []),
     "tfb_status_string": (C.c_char_p, [_i32]),
     "tfb_last_error": (C.c_char_p, []),
+    "tfb_debug_trace": (_i32, [_vp, _i32]),
     "tfb_embed": (_i32, [_vp, _vp, _vp, _i32, _i32, _i64, _f32, _vp]),
     "tfb_rmsnorm": (_i32, [_vp, _vp, _vp, _i32, _i32, _f32, _i32, _vp]),
     "tfb_gemv": (_i32, [C.POINTER(GemvArgs), _vp]),
@@ -131,13 +134,13 @@ def rmsnorm(x, gamma, out, eps, mode):
 
 
 def gemv(w, x, y, *, w2=None, gamma=None, residual=None, prologue=NORM_NONE, epilogue=EPI_STORE,
-         eps=0.0, x_scale=1.0, res_scale=1.0, out_scale=1.0, prefetch=None, pdl=False):
+         eps=0.0, x_scale=1.0, res_scale=1.0, out_scale=1.0, prefetch=None, pdl=False, kernel=0, self_prefetch=False):
     n, k = w.shape
     a = GemvArgs(w=ptr(w), w2=ptr(w2), x=ptr(x), gamma=ptr(gamma), residual=ptr(residual), y=ptr(y),
                  n=n, k=k, prologue=prologue, epilogue=epilogue, eps=eps, x_scale=x_scale,
                  res_scale=res_scale, out_scale=out_scale,
                  prefetch=ptr(prefetch), prefetch_bytes=0 if prefetch is None else prefetch.numel() * prefetch.element_size(),
-                 pdl=int(pdl))
+                 pdl=int(pdl), kernel=kernel, self_prefetch=int(self_prefetch))
     check(load().tfb_gemv(C.byref(a), stream()), "tfb_gemv")
     return y
 
