@@ -71,7 +71,8 @@ TFB_API int tfb_rmsnorm(const void* x, const void* gamma, void* y, int32_t rows,
  * output's weights contiguous), x a length-k vector.
  *
  * prologue: TFB_NORM_* applied to x with `gamma`/`eps` (fused RMSNorm), then
- *           multiplied by x_scale if x_scale != 1 (bf16 multiply).
+ *           multiplied by x_scale if x_scale != 1 (bf16 multiply); a NEGATIVE x_scale divides
+ *           by its magnitude instead (IEEE division, e.g. -10 for MiniCPM3's hidden / 10).
  * epilogue: TFB_EPI_STORE     y[i] = bf16(acc)
  *           TFB_EPI_RESIDUAL  y[i] = bf16(residual[i] + bf16(bf16(acc) * res_scale))
  *           TFB_EPI_SWIGLU    y[i] = bf16(bf16(silu(bf16(acc_gate))) * bf16(acc_up)), gate rows
@@ -246,6 +247,93 @@ typedef struct {
     int64_t* picked;        /* optional [1]: the token this step picked, whatever the prompt says */
 } tfb_qwen3_step_args;
 TFB_API int tfb_qwen3_decode_step(const tfb_qwen3_step_args* args, tfb_stream_t stream);
+
+/* ---- multi-head latent attention decode (MiniCPM3) ------------------------------
+ * One launch: RoPE on the rotary slice of q and on the shared rotary key slice,
+ * key = [k_nope | k_rope] and value assembly per head, append at position *pos, then
+ * split-KV softmax attention over positions [0, *pos] of a paged cache of assembled
+ * keys pool[page][slot][heads][nope+rope] and values pool[page][slot][heads][v].
+ * q_s = bf16(query * scale) as the authored step does.  Scratch as for
+ * tfb_attn_gqa_decode with hq = heads, d = v; counters uint32 [heads].
+ * Stands in for steps 4-7 of mla_attention: examples/minicpm3_4b-cutedsl/model.py:250-290;
+ * reference kernel examples/minicpm3_4b-cutedsl/kernels/cute_attention.py:60-200. */
+typedef struct {
+    const void* q_up;       /* [heads*(nope+rope)] bf16 */
+    const void* kv_up;      /* [heads*(nope+v)] bf16: k_nope | v per head */
+    const void* k_rope;     /* [rope] bf16 */
+    const void* cos_table;  /* [max_pos, rope] */
+    const void* sin_table;
+    const int32_t* pos;
+    const int32_t* rope_pos;
+    void* k_pool;
+    void* v_pool;
+    const int32_t* block_table;
+    void* out;              /* [heads*v] */
+    void* k_new_out;        /* optional [heads*(nope+rope)] */
+    void* v_new_out;        /* optional [heads*v] */
+    float* part_o;
+    float* part_ml;
+    uint32_t* counters;
+    int32_t heads, nope, rope, v;
+    int32_t page_size, table_len, max_ctx, max_pos;
+    float scale;
+    int32_t pdl;
+} tfb_attn_mla_args;
+TFB_API int tfb_attn_mla_decode(const tfb_attn_mla_args* args, tfb_stream_t stream);
+
+/* ---- a whole MiniCPM3-architecture decode step ----------------------------------
+ * embed*scale_emb -> layers x [norm + (q_a|kv_a), q_b, kv_b, MLA attention, o + scaled
+ * residual, norm + gate/up + SwiGLU, down + scaled residual] -> final norm, hidden /
+ * logits_scaling, lm_head, greedy pick, position advance.  Weights packed [out, in];
+ * w_qkv_a = q_a rows then kv_a rows.  Stands in for MiniCPM3_4B.forward + append_cache
+ * + greedy (examples/minicpm3_4b-cutedsl/model.py:396-470). */
+typedef struct {
+    const void* gamma_in;
+    const void* w_qkv_a;    /* [q_lora + kv_lora + rope, hidden] */
+    const void* gamma_q_a;
+    const void* w_q_b;      /* [heads*(nope+rope), q_lora] */
+    const void* gamma_kv_a;
+    const void* w_kv_b;     /* [heads*(nope+v), kv_lora] */
+    const void* w_o;        /* [hidden, heads*v] */
+    const void* gamma_post;
+    const void* w_gate;
+    const void* w_up;
+    const void* w_down;
+    void* k_pool;
+    void* v_pool;
+} tfb_minicpm3_layer;
+typedef struct {
+    const tfb_minicpm3_layer* layers;
+    int32_t n_layers, hidden, heads, q_lora, kv_lora, nope, rope, v, inter;
+    int64_t vocab;
+    float eps, lora_eps, scale, embed_scale, residual_scale, logits_div;
+    const void* w_embed;
+    const void* gamma_final;
+    const void* w_head;
+    const void* cos_table;
+    const void* sin_table;
+    int32_t max_pos, page_size, table_len, max_ctx;
+    const int32_t* block_table;
+    int64_t* tokens;
+    int32_t* pos;
+    int32_t n_prompt, max_tokens;
+    void* hidden_buf;       /* [hidden] */
+    void* qkv_a_buf;        /* [q_lora + kv_lora + rope] */
+    void* q_up_buf;         /* [heads*(nope+rope)] */
+    void* kv_up_buf;        /* [heads*(nope+v)] */
+    void* attn_buf;         /* [heads*v] */
+    void* act_buf;          /* [inter] */
+    void* logits;
+    float* part_o;
+    float* part_ml;
+    uint32_t* counters;     /* [heads + 1] */
+    float* head_val;
+    int32_t* head_idx;
+    void* hidden_trace;     /* optional [n_layers+1][hidden] */
+    int64_t* picked;
+    int32_t pdl;
+} tfb_minicpm3_step_args;
+TFB_API int tfb_minicpm3_decode_step(const tfb_minicpm3_step_args* args, tfb_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -71,3 +71,15 @@ def load(module, resource, impl_for):
         consts[name] = value
     kids = [load(c, resource.subtree(c.name), impl_for) for c in module.modules]
     return Loaded(module, consts, kids, impl_for(module))
+
+
+def load_as(module, resource, impl_for, dtype):
+    """Like ``load`` but with every floating weight cast to *dtype* and no dtype validation: used to
+    run the same function bodies at f32/f64 as an arbiter between two bf16 implementations (the
+    reference keeps such an arbiter too, ``examples/qwen3_1_7b-tilelang/fast/arbitrate.py``)."""
+    consts = {}
+    for name in module.weights:
+        value = resource.load(name)
+        consts[name] = value.to(dtype) if value.is_floating_point() else value
+    kids = [load_as(c, resource.subtree(c.name), impl_for, dtype) for c in module.modules]
+    return Loaded(module, consts, kids, impl_for(module))

@@ -1,11 +1,12 @@
 // extern "C" entry points: host-side validation, then enqueue.  See include/tfb200.h.
 #include "../../include/tfb200.h"
 #include "kernels.h"
+#include "api_internal.h"
 
 #include <cstdio>
 #include <cstring>
 
-namespace {
+namespace tfb { namespace host {
 
 thread_local char g_last_error[256] = "";
 
@@ -22,16 +23,10 @@ int fail_launch(cudaError_t e) {
     cudaGetLastError();  // clear the sticky-free error so later launches report their own
     return TFB_ELAUNCH;
 }
-inline int done(cudaError_t e) { return e == cudaSuccess ? TFB_OK : fail_launch(e); }
-inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-inline cudaStream_t S(tfb_stream_t s) { return static_cast<cudaStream_t>(s); }
 
-#define TFB_REQUIRE(cond, code)      \
-    do {                             \
-        if (!(cond)) return (code);  \
-    } while (0)
+} }  // namespace tfb::host
 
-}  // namespace
+using namespace tfb::host;
 
 extern "C" {
 
@@ -79,7 +74,8 @@ int tfb_rmsnorm(const void* x, const void* gamma, void* y, int32_t rows, int32_t
                                     static_cast<uint16_t*>(y), rows, width, eps, mode, S(stream), false));
 }
 
-static int gemv_checked(const tfb_gemv_args* a, tfb_stream_t stream) {
+}  // extern "C"
+int tfb::host::gemv_checked(const tfb_gemv_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->w && a->x && a->y, TFB_EINVAL);
     TFB_REQUIRE(a->n > 0 && a->k > 0 && a->k % 256 == 0 && a->k <= 16384, TFB_EINVAL);
     TFB_REQUIRE(a->prologue >= TFB_NORM_NONE && a->prologue <= TFB_NORM_CAST_THEN_GAIN, TFB_EINVAL);
@@ -112,6 +108,7 @@ static int gemv_checked(const tfb_gemv_args* a, tfb_stream_t stream) {
     return done(tfb::gemv_dispatch(p, a->prologue, a->epilogue, S(stream), a->pdl != 0));
 }
 
+extern "C" {
 int tfb_gemv(const tfb_gemv_args* args, tfb_stream_t stream) { return gemv_checked(args, stream); }
 
 int32_t tfb_lm_head_scratch_entries(int32_t n) {

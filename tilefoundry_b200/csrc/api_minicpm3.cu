@@ -1,0 +1,128 @@
+// C ABI: MLA attention and the MiniCPM3-architecture decode step.  See include/tfb200.h.
+#include "api_internal.h"
+#include "kernels.h"
+
+#include <cstring>
+
+using namespace tfb::host;
+
+extern "C" {
+
+int tfb_attn_mla_decode(const tfb_attn_mla_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->q_up && a->kv_up && a->k_rope && a->cos_table && a->sin_table && a->pos, TFB_EINVAL);
+    TFB_REQUIRE(a->k_pool && a->v_pool && a->block_table && a->out, TFB_EINVAL);
+    TFB_REQUIRE(a->part_o && a->part_ml && a->counters, TFB_EINVAL);
+    TFB_REQUIRE(a->heads > 0 && a->nope == 64 && a->rope == 32 && a->v == 64, TFB_EINVAL);
+    TFB_REQUIRE(a->page_size > 0 && a->table_len > 0 && a->max_ctx > 0, TFB_EINVAL);
+    TFB_REQUIRE((long long)a->page_size * a->table_len >= a->max_ctx && a->max_pos >= a->max_ctx, TFB_ECAPACITY);
+    TFB_REQUIRE(aligned16(a->k_pool) && aligned16(a->v_pool), TFB_EALIGN);
+    tfb::MlaParams p = {};
+    p.q_up = static_cast<const uint16_t*>(a->q_up);
+    p.kv_up = static_cast<const uint16_t*>(a->kv_up);
+    p.k_rope = static_cast<const uint16_t*>(a->k_rope);
+    p.cos_table = static_cast<const uint16_t*>(a->cos_table);
+    p.sin_table = static_cast<const uint16_t*>(a->sin_table);
+    p.pos = a->pos;
+    p.rope_pos = a->rope_pos;
+    p.k_pool = static_cast<uint16_t*>(a->k_pool);
+    p.v_pool = static_cast<uint16_t*>(a->v_pool);
+    p.block_table = a->block_table;
+    p.out = static_cast<uint16_t*>(a->out);
+    p.k_new_out = static_cast<uint16_t*>(a->k_new_out);
+    p.v_new_out = static_cast<uint16_t*>(a->v_new_out);
+    p.part_o = a->part_o;
+    p.part_ml = a->part_ml;
+    p.counters = a->counters;
+    p.heads = a->heads; p.nope = a->nope; p.rope = a->rope; p.vd = a->v;
+    p.page_size = a->page_size; p.max_ctx = a->max_ctx; p.nsplit = tfb::mla_splits(a->max_ctx);
+    p.scale = a->scale;
+    p.trace = next_trace();
+    return done(tfb::attn_mla_dispatch(p, S(stream), a->pdl != 0));
+}
+
+int tfb_minicpm3_decode_step(const tfb_minicpm3_step_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->layers && a->n_layers > 0, TFB_EINVAL);
+    TFB_REQUIRE(a->w_embed && a->gamma_final && a->w_head && a->tokens && a->pos, TFB_EINVAL);
+    TFB_REQUIRE(a->hidden_buf && a->qkv_a_buf && a->q_up_buf && a->kv_up_buf && a->attn_buf && a->act_buf, TFB_EINVAL);
+    TFB_REQUIRE(a->part_o && a->part_ml && a->counters && a->head_val && a->head_idx, TFB_EINVAL);
+    TFB_REQUIRE(a->hidden % 256 == 0 && a->inter % 256 == 0 && a->q_lora % 256 == 0 && a->kv_lora % 256 == 0, TFB_EINVAL);
+    TFB_REQUIRE((a->heads * a->v) % 256 == 0, TFB_EINVAL);
+    TFB_REQUIRE(a->max_tokens <= a->max_ctx + 1, TFB_ECAPACITY);
+    const bool pdl = a->pdl != 0;
+    const int H = a->hidden, I = a->inter, NH = a->heads;
+    const int NA = a->q_lora + a->kv_lora + a->rope, NQ = NH * (a->nope + a->rope), NKV = NH * (a->nope + a->v);
+    const int NO = NH * a->v;
+    cudaStream_t st = S(stream);
+    uint16_t* hid = static_cast<uint16_t*>(a->hidden_buf);
+    uint16_t* qkv_a = static_cast<uint16_t*>(a->qkv_a_buf);
+    uint16_t* trace = static_cast<uint16_t*>(a->hidden_trace);
+
+    cudaError_t e = tfb::embed_launch(static_cast<const uint16_t*>(a->w_embed), nullptr,
+                                      reinterpret_cast<const long long*>(a->tokens), a->pos, hid, 1, H,
+                                      a->vocab, a->embed_scale, st, pdl);
+    if (e != cudaSuccess) return fail_launch(e);
+
+    auto gemv = [&](const void* w, const void* w2, const void* x, const void* gamma, const void* res, void* y,
+                    int n, int k, int pro, int epi, float eps, float res_scale) {
+        tfb_gemv_args g;
+        std::memset(&g, 0, sizeof g);
+        g.w = w; g.w2 = w2; g.x = x; g.gamma = gamma; g.residual = res; g.y = y; g.n = n; g.k = k;
+        g.prologue = pro; g.epilogue = epi; g.eps = eps; g.x_scale = 1.f; g.res_scale = res_scale; g.out_scale = 1.f;
+        g.pdl = pdl;
+        return gemv_checked(&g, stream);
+    };
+
+    for (int l = 0; l < a->n_layers; ++l) {
+        const tfb_minicpm3_layer& L = a->layers[l];
+        int rc;
+        // 1. input norm + q down-projection | kv compression (one fused projection)
+        if ((rc = gemv(L.w_qkv_a, nullptr, hid, L.gamma_in, nullptr, qkv_a, NA, H, TFB_NORM_CAST_THEN_GAIN,
+                       TFB_EPI_STORE, a->eps, 1.f))) return rc;
+        // 2. low-rank norm + q up-projection
+        if ((rc = gemv(L.w_q_b, nullptr, qkv_a, L.gamma_q_a, nullptr, a->q_up_buf, NQ, a->q_lora,
+                       TFB_NORM_CAST_THEN_GAIN, TFB_EPI_STORE, a->lora_eps, 1.f))) return rc;
+        // 3. low-rank norm + kv up-projection (k_nope | v per head)
+        if ((rc = gemv(L.w_kv_b, nullptr, qkv_a + a->q_lora, L.gamma_kv_a, nullptr, a->kv_up_buf, NKV, a->kv_lora,
+                       TFB_NORM_CAST_THEN_GAIN, TFB_EPI_STORE, a->lora_eps, 1.f))) return rc;
+        // 4. RoPE, assembly, cache append, attention
+        tfb_attn_mla_args t;
+        std::memset(&t, 0, sizeof t);
+        t.q_up = a->q_up_buf; t.kv_up = a->kv_up_buf; t.k_rope = qkv_a + a->q_lora + a->kv_lora;
+        t.cos_table = a->cos_table; t.sin_table = a->sin_table; t.pos = a->pos;
+        t.k_pool = L.k_pool; t.v_pool = L.v_pool; t.block_table = a->block_table; t.out = a->attn_buf;
+        t.part_o = a->part_o; t.part_ml = a->part_ml; t.counters = a->counters;
+        t.heads = NH; t.nope = a->nope; t.rope = a->rope; t.v = a->v;
+        t.page_size = a->page_size; t.table_len = a->table_len; t.max_ctx = a->max_ctx; t.max_pos = a->max_pos;
+        t.scale = a->scale; t.pdl = pdl;
+        if ((rc = tfb_attn_mla_decode(&t, stream))) return rc;
+        // 5. output projection + scaled residual
+        if ((rc = gemv(L.w_o, nullptr, a->attn_buf, nullptr, hid, hid, H, NO, TFB_NORM_NONE, TFB_EPI_RESIDUAL,
+                       a->eps, a->residual_scale))) return rc;
+        // 6. post-attention norm + gate/up + SwiGLU
+        if ((rc = gemv(L.w_gate, L.w_up, hid, L.gamma_post, nullptr, a->act_buf, I, H, TFB_NORM_CAST_THEN_GAIN,
+                       TFB_EPI_SWIGLU, a->eps, 1.f))) return rc;
+        // 7. down projection + scaled residual
+        if ((rc = gemv(L.w_down, nullptr, a->act_buf, nullptr, hid, hid, H, I, TFB_NORM_NONE, TFB_EPI_RESIDUAL,
+                       a->eps, a->residual_scale))) return rc;
+        if (trace) {
+            e = tfb::copy_launch(hid, trace + size_t(l) * H, H * 2, st, pdl);
+            if (e != cudaSuccess) return fail_launch(e);
+        }
+    }
+    if (trace) {
+        e = tfb::rmsnorm_launch(hid, static_cast<const uint16_t*>(a->gamma_final),
+                                trace + size_t(a->n_layers) * H, 1, H, a->eps, TFB_NORM_CAST_THEN_GAIN, st, pdl);
+        if (e != cudaSuccess) return fail_launch(e);
+    }
+    tfb_lm_head_args h;
+    std::memset(&h, 0, sizeof h);
+    h.w = a->w_head; h.x = hid; h.gamma = a->gamma_final; h.logits = a->logits;
+    h.scratch_val = a->head_val; h.scratch_idx = a->head_idx; h.counter = a->counters + NH;
+    h.n = int(a->vocab); h.k = H; h.prologue = TFB_NORM_CAST_THEN_GAIN; h.eps = a->eps;
+    h.x_scale = -a->logits_div; h.out_scale = 1.f; h.pdl = pdl;
+    h.token_out = a->picked;
+    h.tokens = a->tokens; h.pos = a->pos; h.n_prompt = a->n_prompt; h.max_tokens = a->max_tokens;
+    return tfb_lm_head_argmax(&h, stream);
+}
+
+}  // extern "C"

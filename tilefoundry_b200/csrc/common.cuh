@@ -116,6 +116,12 @@ __device__ __forceinline__ float dot8(const uint4& w, const float4& xa, const fl
     return acc;
 }
 
+// Activation pre-scale of the projections: a positive factor multiplies, a negative one divides by
+// its magnitude (IEEE division: "hidden / 10" is not "hidden * 0.1" in the last bit).
+__device__ __forceinline__ float apply_scale(float x, float s) {
+    return s < 0.f ? __fdiv_rn(x, -s) : x * s;
+}
+
 __device__ __forceinline__ float silu_f32(float x) { return x / (1.f + __expf(-x)); }
 
 }  // namespace tfb

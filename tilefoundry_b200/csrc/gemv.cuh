@@ -67,7 +67,7 @@ __device__ __forceinline__ void stage_activation(const uint16_t* __restrict__ x,
         }
         if (x_scale != 1.f) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) f[i] = round_bf16(f[i] * x_scale);
+            for (int i = 0; i < 8; ++i) f[i] = round_bf16(apply_scale(f[i], x_scale));
         }
         const int it = c >> 5, lane = c & 31;
         float4* dst = reinterpret_cast<float4*>(xs);
@@ -138,7 +138,7 @@ struct StagedGain {
             }
             if (x_scale != 1.f) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) f[i] = round_bf16(f[i] * x_scale);
+                for (int i = 0; i < 8; ++i) f[i] = round_bf16(apply_scale(f[i], x_scale));
             }
             const int it = c >> 5, lane = c & 31;
             float4* dst = reinterpret_cast<float4*>(xs);

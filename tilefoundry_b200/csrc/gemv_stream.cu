@@ -116,7 +116,7 @@ __device__ __forceinline__ void stage_activation_group(const uint16_t* __restric
         }
         if (x_scale != 1.f) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) f[i] = round_bf16(f[i] * x_scale);
+            for (int i = 0; i < 8; ++i) f[i] = round_bf16(apply_scale(f[i], x_scale));
         }
         const int it = c >> 5, ln = c & 31;
         float4* dst = reinterpret_cast<float4*>(xs);

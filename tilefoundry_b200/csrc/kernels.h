@@ -87,4 +87,28 @@ cudaError_t rmsnorm_launch(const uint16_t* x, const uint16_t* gamma, uint16_t* y
                            float eps, int mode, cudaStream_t stream, bool pdl);
 cudaError_t copy_launch(const void* src, void* dst, int bytes, cudaStream_t stream, bool pdl);
 
+struct MlaParams {
+    const uint16_t* q_up;      // [heads][nope+rope]
+    const uint16_t* kv_up;     // [heads][nope+v]
+    const uint16_t* k_rope;    // [rope] shared rotary key slice
+    const uint16_t* cos_table;
+    const uint16_t* sin_table;
+    const int* pos;
+    const int* rope_pos;
+    uint16_t* k_pool;          // [page][slot][heads][nope+rope]
+    uint16_t* v_pool;          // [page][slot][heads][v]
+    const int* block_table;
+    uint16_t* out;             // [heads][v]
+    uint16_t* k_new_out;
+    uint16_t* v_new_out;
+    float* part_o;
+    float* part_ml;
+    unsigned* counters;        // [heads]
+    int heads, nope, rope, vd, page_size, max_ctx, nsplit;
+    float scale;
+    unsigned long long* trace;
+};
+int mla_splits(int max_ctx);
+cudaError_t attn_mla_dispatch(const MlaParams& p, cudaStream_t stream, bool pdl);
+
 }  // namespace tfb

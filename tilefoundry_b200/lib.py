@@ -63,6 +63,34 @@ class Qwen3StepArgs(C.Structure):
                 ("hidden_trace", _vp), ("pdl", _i32), ("l2_prefetch", _i32), ("kernel", _i32), ("picked", _vp)]
 
 
+class AttnMlaArgs(C.Structure):
+    _fields_ = [("q_up", _vp), ("kv_up", _vp), ("k_rope", _vp), ("cos_table", _vp), ("sin_table", _vp),
+                ("pos", _vp), ("rope_pos", _vp), ("k_pool", _vp), ("v_pool", _vp), ("block_table", _vp),
+                ("out", _vp), ("k_new_out", _vp), ("v_new_out", _vp), ("part_o", _vp), ("part_ml", _vp),
+                ("counters", _vp), ("heads", _i32), ("nope", _i32), ("rope", _i32), ("v", _i32),
+                ("page_size", _i32), ("table_len", _i32), ("max_ctx", _i32), ("max_pos", _i32),
+                ("scale", _f32), ("pdl", _i32)]
+
+
+class MiniCPM3Layer(C.Structure):
+    _fields_ = [(n, _vp) for n in ("gamma_in", "w_qkv_a", "gamma_q_a", "w_q_b", "gamma_kv_a", "w_kv_b", "w_o",
+                                   "gamma_post", "w_gate", "w_up", "w_down", "k_pool", "v_pool")]
+
+
+class MiniCPM3StepArgs(C.Structure):
+    _fields_ = [("layers", C.POINTER(MiniCPM3Layer)),
+                ("n_layers", _i32), ("hidden", _i32), ("heads", _i32), ("q_lora", _i32), ("kv_lora", _i32),
+                ("nope", _i32), ("rope", _i32), ("v", _i32), ("inter", _i32), ("vocab", _i64),
+                ("eps", _f32), ("lora_eps", _f32), ("scale", _f32), ("embed_scale", _f32),
+                ("residual_scale", _f32), ("logits_div", _f32),
+                ("w_embed", _vp), ("gamma_final", _vp), ("w_head", _vp), ("cos_table", _vp), ("sin_table", _vp),
+                ("max_pos", _i32), ("page_size", _i32), ("table_len", _i32), ("max_ctx", _i32),
+                ("block_table", _vp), ("tokens", _vp), ("pos", _vp), ("n_prompt", _i32), ("max_tokens", _i32),
+                ("hidden_buf", _vp), ("qkv_a_buf", _vp), ("q_up_buf", _vp), ("kv_up_buf", _vp), ("attn_buf", _vp),
+                ("act_buf", _vp), ("logits", _vp), ("part_o", _vp), ("part_ml", _vp), ("counters", _vp),
+                ("head_val", _vp), ("head_idx", _vp), ("hidden_trace", _vp), ("picked", _vp), ("pdl", _i32)]
+
+
 #: every symbol ``include/tfb200.h`` declares: name -> (restype, argtypes)
 SYMBOLS = {
     "tfb_version": (_i32, []),
@@ -77,6 +105,8 @@ SYMBOLS = {
     "tfb_attn_splits": (_i32, [_i32]),
     "tfb_attn_gqa_decode": (_i32, [C.POINTER(AttnGqaArgs), _vp]),
     "tfb_qwen3_decode_step": (_i32, [C.POINTER(Qwen3StepArgs), _vp]),
+    "tfb_attn_mla_decode": (_i32, [C.POINTER(AttnMlaArgs), _vp]),
+    "tfb_minicpm3_decode_step": (_i32, [C.POINTER(MiniCPM3StepArgs), _vp]),
 }
 
 
