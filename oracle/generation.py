@@ -16,12 +16,15 @@ def greedy(logits) -> int:
     return int(torch.argmax(logits).item())
 
 
-def _forward_traced(loaded, token_ids, cos, sin, pos_ids, scale, caches, trace):
-    """`forward` with the residual stream after every layer recorded (same calls, same order)."""
+def _forward_traced(loaded, trace, token_ids, cos, sin, pos_ids, *rest):
+    """``forward`` with the residual stream after every layer recorded (same calls, same order).
+    Covers the attention-cache models, whose step takes ``(token, cos, sin, pos, *scalars, caches)``
+    and whose layers take ``(hidden, cos, sin, pos, k_cache, v_cache, *scalars)``."""
+    *scalars, caches = rest
     hidden = loaded.embed(token_ids)
     entries, rows = [], []
     for layer, (k_cache, v_cache) in zip(loaded.modules, caches):
-        hidden, k_new, v_new = layer(hidden, cos, sin, pos_ids, k_cache, v_cache, scale)
+        hidden, k_new, v_new = layer(hidden, cos, sin, pos_ids, k_cache, v_cache, *scalars)
         entries.append((k_new, v_new))
         rows.append(hidden.reshape(-1))
     normed = loaded.final_rms_norm(hidden)
@@ -41,7 +44,7 @@ def decode_ids(loaded, prompt_ids, max_new, device="cpu", keep_logits=False, kee
     t_prompt = perf_counter()
     for step in range(n_prompt):
         args = loaded.prepare_inputs_for_generation(input_ids[: step + 1], step, caches, device=device)
-        logits, fresh = _forward_traced(loaded, *args, trace) if keep_hidden else loaded.forward(*args)
+        logits, fresh = _forward_traced(loaded, trace, *args) if keep_hidden else loaded.forward(*args)
         caches = loaded.append_cache(caches, fresh)
         if keep_logits:
             kept.append(logits)
@@ -54,7 +57,7 @@ def decode_ids(loaded, prompt_ids, max_new, device="cpu", keep_logits=False, kee
         input_ids[n_prompt + step] = token
         pos = n_prompt + step
         args = loaded.prepare_inputs_for_generation(input_ids[: pos + 1], pos, caches, device=device)
-        logits, fresh = _forward_traced(loaded, *args, trace) if keep_hidden else loaded.forward(*args)
+        logits, fresh = _forward_traced(loaded, trace, *args) if keep_hidden else loaded.forward(*args)
         caches = loaded.append_cache(caches, fresh)
         if keep_logits:
             kept.append(logits)

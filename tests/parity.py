@@ -1,0 +1,71 @@
+"""Shared parity drivers: a session walking the evaluator's own token sequence, compared step by step."""
+import torch
+
+from oracle import generation
+from tests.helpers import assert_close_at_scale
+
+
+def cuda_weights(weights, dev):
+    return {k: v.to(dev) for k, v in weights.items()}
+
+
+def on_cpu(fn):
+    return lambda *args: fn(*[a.cpu() if isinstance(a, torch.Tensor) else a for a in args])
+
+
+def to_cpu(x):
+    return tuple(to_cpu(i) for i in x) if isinstance(x, tuple) else x.cpu()
+
+
+def teacher_forced(ref, make_session, vocab, n_prompt, n_new, seed, use_graph):
+    """The evaluator decodes greedily on the CPU; the session then walks the very same token sequence
+    (given to it as its prompt), so a near-tie in one step cannot make the two sides diverge."""
+    g = torch.Generator().manual_seed(seed + 100)
+    prompt = torch.randint(0, vocab, (n_prompt,), generator=g)
+    want = generation.decode_ids(ref, prompt, n_new, keep_logits=True, keep_hidden=True)
+    forced = torch.cat([prompt, torch.tensor(want["tokens"], dtype=torch.int64)])
+    sess = make_session(n_prompt + n_new + 5)
+    sess.reset(forced)
+    if use_graph:
+        sess.capture()
+    got = {"logits": [], "hidden": [], "picked": []}
+    for _ in range(n_prompt + n_new - 1):
+        sess.run(1, use_graph)
+        got["logits"].append(sess.logits.clone())
+        got["hidden"].append(sess.trace.clone())
+        got["picked"].append(sess.picked.clone())
+    torch.cuda.synchronize()
+    return want, sess, got
+
+
+def compare_run(n_layers, want, sess, got, n_prompt, n_new):
+    """Logits and hidden states within the end-to-end bound at every step; greedy picks bit-exact
+    except where the evaluator's top-2 margin is inside twice the measured logit difference."""
+    total = n_prompt + n_new - 1
+    assert int(sess.pos) == total
+    excused = 0
+    for step in range(total):
+        ref_logits = want["logits"][step][0]
+        assert_close_at_scale(got["logits"][step], ref_logits, f"logits step {step}")
+        for li in range(n_layers + 1):
+            assert_close_at_scale(got["hidden"][step][li], want["hidden"][step][li], f"hidden step {step} layer {li}")
+        pick, ref_pick = int(got["picked"][step]), int(torch.argmax(ref_logits))
+        assert pick == int(torch.argmax(got["logits"][step].cpu())), f"step {step}: pick is not argmax"
+        if pick != ref_pick:
+            top = torch.topk(ref_logits.float(), 2).values
+            noise = (got["logits"][step].float().cpu() - ref_logits.float()).abs().max()
+            assert float(top[0] - top[1]) <= 2 * float(noise), (
+                f"step {step}: picked {pick}, evaluator {ref_pick}, margin {float(top[0] - top[1]):.4g}, "
+                f"noise {float(noise):.4g}")
+            excused += 1
+    return excused
+
+
+def compare_caches(want, sess, total):
+    from tilefoundry_b200.engine import paged_kv
+    assert torch.equal(sess.table.cpu(), paged_kv.block_table(1, sess.max_ctx))
+    for li, (k_ref, v_ref) in enumerate(want["caches"]):
+        k_got = paged_kv.logical_view(sess.layers[li]["k_pool"], sess.table[0], total)
+        v_got = paged_kv.logical_view(sess.layers[li]["v_pool"], sess.table[0], total)
+        assert_close_at_scale(k_got, k_ref[:, :total], f"layer {li} K cache")
+        assert_close_at_scale(v_got, v_ref[:, :total], f"layer {li} V cache")

@@ -1,0 +1,96 @@
+"""Parity of the CUDA path against the CPU oracle -- MiniCPM3 architecture (multi-head latent attention)."""
+import pytest
+import torch
+
+from oracle import evaluator, minicpm3_4b as om
+from tests import parity
+from tests.helpers import ATOL, RTOL
+from tilefoundry_b200.authored import minicpm3_4b as m
+from tilefoundry_b200.authored.weights import random_weights
+from tilefoundry_b200.runtime import AllClose, DictResource, Equal, NanInf, check
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+CLOSE = [AllClose(atol=ATOL, rtol=RTOL), NanInf()]
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from tilefoundry_b200 import lib
+    lib.load()
+    return torch.device("cuda:0")
+
+
+def _sides(cfg, dev, seed=3, std=0.05):
+    from tilefoundry_b200.twins.minicpm3_4b import make_twin
+    mod = m.build(cfg)
+    weights = m.tie_head(random_weights(mod, seed=seed, std=std))
+    ref = evaluator.load(mod, DictResource(weights), om.make(cfg))
+    twin = make_twin(cfg)()
+    twin.load(DictResource(parity.cuda_weights(weights, dev)))
+    return ref, twin, weights
+
+
+def _layer_inputs(cfg, ctx, dev, seed=1):
+    g = torch.Generator().manual_seed(seed)
+    cos, sin = m.rope_tables(cfg)
+    NH = cfg.num_attention_heads
+    hidden = torch.randn(1, 1, cfg.hidden_size, generator=g).to(BF)
+    kc = torch.randn(1, ctx, NH, cfg.qk_head_dim, generator=g).to(BF)
+    vc = torch.randn(1, ctx, NH, cfg.v_head_dim, generator=g).to(BF)
+    pos = torch.tensor([ctx], dtype=torch.int32)
+    scale = torch.full((1, 1, 1, 1), cfg.qk_head_dim ** -0.5, dtype=BF)
+    rs = torch.full((1, 1, 1), cfg.residual_scale, dtype=BF)
+    return tuple(t.to(dev) for t in (hidden, cos, sin, pos, kc, vc, scale, rs))
+
+
+@pytest.mark.parametrize("ctx", [0, 1, 63, 64, 65, 200])
+def test_layer_functions_against_evaluator_tiny(dev, ctx):
+    cfg = m.MINICPM3_TINY
+    ref, twin, _ = _sides(cfg, dev)
+    inputs = _layer_inputs(cfg, ctx, dev)
+    expect = {"output[0]": CLOSE, "output[1]": CLOSE, "output[2]": [Equal()]}
+    rep = check(lambda *a: parity.to_cpu(twin.layer0.mla_attention(*a)), parity.on_cpu(ref.layer0.mla_attention),
+                inputs[:-1], expect=expect)
+    assert rep.passed, f"mla_attention ctx={ctx}\n{rep.render()}"
+    rep = check(lambda *a: parity.to_cpu(twin.layer0.decoder_layer(*a)), parity.on_cpu(ref.layer0.decoder_layer),
+                inputs, expect=expect)
+    assert rep.passed, f"decoder_layer ctx={ctx}\n{rep.render()}"
+    for fn in ("mlp", "input_rms_norm"):
+        rep = check(lambda *a: parity.to_cpu(getattr(twin.layer0, fn)(*a)), parity.on_cpu(getattr(ref.layer0, fn)),
+                    (inputs[0],), expect={"output": CLOSE})
+        assert rep.passed, f"{fn}\n{rep.render()}"
+
+
+def test_full_size_layer_and_root_functions(dev):
+    cfg = m.MiniCPM3Config(num_hidden_layers=1, vocab_size=4096)
+    ref, twin, _ = _sides(cfg, dev, std=0.02)
+    inputs = _layer_inputs(cfg, 333, dev)
+    rep = check(lambda *a: parity.to_cpu(twin.layer0.decoder_layer(*a)), parity.on_cpu(ref.layer0.decoder_layer),
+                inputs, expect={"output[0]": CLOSE, "output[1]": CLOSE, "output[2]": [Equal()]})
+    assert rep.passed, rep.render()
+    ids = torch.tensor([17], dtype=torch.int64)
+    rep = check(lambda i: twin.embed(i.to(dev)).cpu(), ref.embed, (ids,), expect={"output": [Equal()]})
+    assert rep.passed, rep.render()               # scaled by 12 with one bf16 rounding on both sides
+    hidden = inputs[0]
+    rep = check(lambda h: twin.lm_head(twin.final_rms_norm(h)).cpu(),
+                lambda h: ref.lm_head(ref.final_rms_norm(h.cpu())), (hidden,), expect={"output": CLOSE})
+    assert rep.passed, rep.render()
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_session_matches_evaluator_tiny(dev, use_graph):
+    from tilefoundry_b200.engine.minicpm3 import MiniCPM3Session
+    cfg = m.MINICPM3_TINY
+    mod = m.build(cfg)
+    weights = m.tie_head(random_weights(mod, seed=11, std=0.05))
+    ref = evaluator.load(mod, DictResource(weights), om.make(cfg))
+    make = lambda cap: MiniCPM3Session(cfg, DictResource(parity.cuda_weights(weights, dev)), max_ctx=cap, device=dev,
+                                       keep_logits=True, trace_hidden=True)
+    n_prompt, n_new = 24, 120
+    want, sess, got = parity.teacher_forced(ref, make, cfg.vocab_size, n_prompt, n_new, 11, use_graph)
+    excused = parity.compare_run(cfg.num_hidden_layers, want, sess, got, n_prompt, n_new)
+    assert excused <= 8
+    parity.compare_caches(want, sess, n_prompt + n_new - 1)

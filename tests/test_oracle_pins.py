@@ -64,3 +64,34 @@ def test_zero_length_context_is_a_first_step(golden_dir):
     assert logits.shape == (1, cfg.vocab_size) and logits.dtype == torch.bfloat16
     assert_ulps(logits[0], fx["logits"][0], 3 * (cfg.num_hidden_layers + 1), "first step")
     assert fresh[0][0].shape == (1, 1, cfg.num_key_value_heads, cfg.head_dim)
+
+
+# ---- MiniCPM3: pinned by the reference's own torch statement of its decode path ------------------------
+
+def test_minicpm3_layer_matches_reference_ops_vectors(golden_dir):
+    """`tests/golden/minicpm3_tiny_refops.pt` was produced by importing the reference's
+    ``examples/minicpm3_4b-cutedsl/kernels/reference_ops.py``.  It rotates in bf16 and keeps the
+    attention in f32 where the evaluator rotates in f32 and rounds attention intermediates to bf16,
+    so the two agree to a few roundings at the output's scale, not bit for bit."""
+    from oracle import minicpm3_4b as om
+    from tilefoundry_b200.authored import minicpm3_4b as m
+
+    fx = torch.load(golden_dir / "minicpm3_tiny_refops.pt")
+    cfg = m.MiniCPM3Config(**{**fx["config"], "short_factor": tuple(fx["config"]["short_factor"])})
+    mod = m.build(cfg)
+    weights = m.tie_head(random_weights(mod, seed=fx["seed_w"], std=fx["std"]))
+    loaded = evaluator.load(mod, DictResource(weights), om.make(cfg))
+    cos, sin = m.rope_tables(cfg)
+    scale = torch.full((1, 1, 1, 1), cfg.qk_head_dim ** -0.5, dtype=torch.bfloat16)
+    alpha = torch.full((1, 1, 1), cfg.residual_scale, dtype=torch.bfloat16)
+    NH = cfg.num_attention_heads
+    for case in fx["cases"]:
+        pos = torch.tensor([case["ctx"]], dtype=torch.int32)
+        out, k_new, v_new = loaded.layer0(case["hidden"], cos, sin, pos, case["k_cache"], case["v_cache"], scale, alpha)
+        assert_ulps(out.reshape(-1), case["out"], 3, f"layer out ctx {case['ctx']}")
+        assert_ulps(k_new.reshape(-1), case["k_new"], 1, f"k_new ctx {case['ctx']}")
+        assert torch.equal(v_new.reshape(-1), case["v_new"])
+    assert torch.equal(loaded.embed(torch.tensor([17])).reshape(-1), fx["embed"])
+    normed = loaded.final_rms_norm(fx["cases"][-1]["out"].reshape(1, 1, -1))
+    assert torch.equal(normed.reshape(-1), fx["final_norm"])
+    assert_ulps(loaded.lm_head(normed).reshape(-1), fx["logits"], 1, "logits")

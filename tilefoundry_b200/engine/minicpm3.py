@@ -1,0 +1,103 @@
+"""MiniCPM3-architecture (MLA) decode session: packed weights, paged cache of assembled keys and
+values, one captured step.  Same trade as the Qwen3 session; the reference's own fast driver for this
+model makes it too (``examples/minicpm3_4b-cutedsl/runtime_model.py:248-320`` repacks at load)."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from .. import lib
+from ..authored.minicpm3_4b import MiniCPM3Config, rope_tables
+from . import paged_kv
+from .session import DecodeSession
+
+
+def pack_layer(w: dict) -> dict:
+    """Authored ``(1, in, out)`` -> ``[out, in]``; q_a and kv_a fused along the output axis."""
+    t = lambda name: w[name][0].t().contiguous()
+    out = {n: w[n].contiguous() for n in ("gamma_in", "gamma_q_a", "gamma_kv_a", "gamma_post")}
+    out.update(w_qkv_a=torch.cat([t("w_q_a"), t("w_kv_a")], dim=0).contiguous(), w_q_b=t("w_q_b"),
+               w_kv_b=t("w_kv_b"), w_o=t("w_o"), w_gate=t("w_gate"), w_up=t("w_up"), w_down=t("w_down"))
+    return out
+
+
+LAYER_WEIGHTS = ("gamma_in", "w_q_a", "gamma_q_a", "w_q_b", "w_kv_a", "gamma_kv_a", "w_kv_b", "w_o",
+                 "gamma_post", "w_gate", "w_up", "w_down")
+
+
+class MiniCPM3Session(DecodeSession):
+    def __init__(self, cfg: MiniCPM3Config, resource, *, max_ctx: int = 2176, device="cuda:0",
+                 keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True):
+        if not torch.cuda.is_available():
+            raise RuntimeError("MiniCPM3Session needs a CUDA device; there is no CPU path")
+        lib.load()
+        self.cfg, self.device, self.max_ctx = cfg, torch.device(device), int(max_ctx)
+        dev = self.device
+        to = lambda t: t.to(dev)
+        self.w_embed = to(resource.load("w_embed")).contiguous()
+        head = to(resource.load("w_head")).t().contiguous()
+        self.w_head = self.w_embed if torch.equal(head, self.w_embed) else head
+        self.gamma_final = to(resource.load("gamma_final")).contiguous()
+        self.layers = []
+        for i in range(cfg.num_hidden_layers):
+            sub = resource.subtree(f"layer{i}")
+            self.layers.append(pack_layer({n: to(sub.load(n)) for n in LAYER_WEIGHTS}))
+
+        cos, sin = rope_tables(cfg, "cpu")
+        self.max_pos = min(cfg.max_position_embeddings, self.max_ctx)
+        self.cos, self.sin = cos[: self.max_pos].contiguous().to(dev), sin[: self.max_pos].contiguous().to(dev)
+        NH, QK, VD, H, I, V = (cfg.num_attention_heads, cfg.qk_head_dim, cfg.v_head_dim, cfg.hidden_size,
+                               cfg.intermediate_size, cfg.vocab_size)
+        self.table = paged_kv.block_table(1, self.max_ctx, device=dev)
+        for layer in self.layers:
+            layer["k_pool"] = paged_kv.new_pool(1, self.max_ctx, NH, QK, device=dev)
+            layer["v_pool"] = paged_kv.new_pool(1, self.max_ctx, NH, VD, device=dev)
+        bf, f32 = torch.bfloat16, torch.float32
+        z = lambda *s, dtype=bf: torch.zeros(*s, device=dev, dtype=dtype)
+        nsplit = lib.attn_splits(self.max_ctx)
+        self.tokens, self.pos = z(self.max_ctx + 1, dtype=torch.int64), z(1, dtype=torch.int32)
+        self.hidden = z(H)
+        self.qkv_a = z(cfg.q_lora_rank + cfg.kv_lora_rank + cfg.qk_rope_head_dim)
+        self.q_up, self.kv_up = z(NH * QK), z(NH * (cfg.qk_nope_head_dim + VD))
+        self.attn, self.act = z(NH * VD), z(I)
+        self.logits = z(V) if keep_logits else None
+        self.part_o, self.part_ml = z(NH * nsplit * VD, dtype=f32), z(NH * nsplit * 2, dtype=f32)
+        self.counters = z(NH + 1, dtype=torch.int32)
+        n_head = lib.lm_head_scratch_entries(V)
+        self.head_val, self.head_idx = z(n_head, dtype=f32), z(n_head, dtype=torch.int32)
+        self.trace = z(cfg.num_hidden_layers + 1, H) if trace_hidden else None
+        self.picked = z(1, dtype=torch.int64)
+
+        self._layer_structs = (lib.MiniCPM3Layer * len(self.layers))()
+        for s, layer in zip(self._layer_structs, self.layers):
+            for name, _ in lib.MiniCPM3Layer._fields_:
+                setattr(s, name, lib.ptr(layer[name]))
+        as_bf16 = lambda v: float(torch.tensor(v, dtype=bf))    # the authored step holds these as bf16 tensors
+        self.args = lib.MiniCPM3StepArgs(
+            layers=self._layer_structs, n_layers=len(self.layers), hidden=H, heads=NH, q_lora=cfg.q_lora_rank,
+            kv_lora=cfg.kv_lora_rank, nope=cfg.qk_nope_head_dim, rope=cfg.qk_rope_head_dim, v=VD, inter=I, vocab=V,
+            eps=cfg.rms_norm_eps, lora_eps=cfg.lora_eps, scale=as_bf16(QK ** -0.5), embed_scale=cfg.scale_emb,
+            residual_scale=as_bf16(cfg.residual_scale), logits_div=cfg.logits_scaling,
+            w_embed=lib.ptr(self.w_embed), gamma_final=lib.ptr(self.gamma_final), w_head=lib.ptr(self.w_head),
+            cos_table=lib.ptr(self.cos), sin_table=lib.ptr(self.sin), max_pos=self.max_pos,
+            page_size=paged_kv.PAGE_SIZE, table_len=self.table.shape[1], max_ctx=self.max_ctx,
+            block_table=lib.ptr(self.table), tokens=lib.ptr(self.tokens), pos=lib.ptr(self.pos), n_prompt=0,
+            max_tokens=self.max_ctx + 1, hidden_buf=lib.ptr(self.hidden), qkv_a_buf=lib.ptr(self.qkv_a),
+            q_up_buf=lib.ptr(self.q_up), kv_up_buf=lib.ptr(self.kv_up), attn_buf=lib.ptr(self.attn),
+            act_buf=lib.ptr(self.act), logits=lib.ptr(self.logits), part_o=lib.ptr(self.part_o),
+            part_ml=lib.ptr(self.part_ml), counters=lib.ptr(self.counters), head_val=lib.ptr(self.head_val),
+            head_idx=lib.ptr(self.head_idx), hidden_trace=lib.ptr(self.trace), picked=lib.ptr(self.picked),
+            pdl=int(pdl))
+        self.launches_per_step = 2 + 7 * len(self.layers) + (len(self.layers) + 1 if trace_hidden else 0)
+
+    def weight_bytes(self) -> int:
+        names = ("w_qkv_a", "w_q_b", "w_kv_b", "w_o", "w_gate", "w_up", "w_down")
+        return sum(self.layers[0][n].numel() * 2 for n in names) * len(self.layers) + self.w_head.numel() * 2
+
+    def kv_bytes_per_position(self) -> int:
+        c = self.cfg
+        return c.num_attention_heads * (c.qk_head_dim + c.v_head_dim) * 2 * c.num_hidden_layers
+
+    def step(self) -> None:
+        lib.check(lib.load().tfb_minicpm3_decode_step(C.byref(self.args), lib.stream()), "tfb_minicpm3_decode_step")

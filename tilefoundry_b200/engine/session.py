@@ -1,0 +1,90 @@
+"""What every fixed-address decode session shares: token history and position on the device,
+one captured step, and the generate loop."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+
+@dataclass
+class Generated:
+    tokens: list
+    seconds: float
+    prompt_seconds: float
+    prompt_steps: int
+
+    @property
+    def tokens_per_second(self) -> float:
+        return len(self.tokens) / self.seconds
+
+
+class DecodeSession:
+    """Subclasses set ``device, max_ctx, tokens, pos, counters, args`` (a ctypes step-args struct with
+    an ``n_prompt`` field) and implement ``step()``."""
+
+    graph = None
+    n_prompt = 0
+
+    def step(self) -> None:
+        raise NotImplementedError
+
+    def reset(self, prompt_ids) -> None:
+        """Start a sequence: token history = prompt, position 0.  The cache needs no clearing: a step
+        only reads positions below its own."""
+        prompt = torch.as_tensor(prompt_ids, dtype=torch.int64).reshape(-1)
+        if prompt.numel() == 0:
+            raise ValueError("decode needs a prompt of at least one token")
+        if prompt.numel() > self.max_ctx:
+            raise ValueError(f"prompt of {prompt.numel()} tokens exceeds capacity {self.max_ctx}")
+        self.tokens.zero_()
+        self.tokens[: prompt.numel()] = prompt.to(self.device)
+        self.pos.zero_()
+        self.counters.zero_()
+        if self.args.n_prompt != prompt.numel():
+            self.args.n_prompt = int(prompt.numel())
+            self.graph = None                         # the prompt length is baked into the capture
+        self.n_prompt = int(prompt.numel())
+
+    def capture(self) -> None:
+        """Record one step into a CUDA graph (positions and tokens live on the device, so the same
+        graph serves every step).  Three eager warm-up steps run first and are rolled back."""
+        saved = (self.tokens.clone(), self.pos.clone())
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                self.step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.tokens.copy_(saved[0]); self.pos.copy_(saved[1])
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.step()
+        torch.cuda.synchronize()
+        self.tokens.copy_(saved[0]); self.pos.copy_(saved[1])
+        self.graph = graph
+
+    def run(self, steps: int, use_graph: bool = True) -> None:
+        if use_graph and self.graph is None:
+            self.capture()
+        for _ in range(steps):
+            self.graph.replay() if use_graph else self.step()
+
+    def generate(self, prompt_ids, max_new: int, use_graph: bool = True) -> Generated:
+        """Walk the prompt, then continue greedily for *max_new* tokens; one sync at each end."""
+        self.reset(prompt_ids)
+        n_prompt = self.n_prompt
+        if n_prompt + max_new > self.max_ctx + 1:
+            raise ValueError(f"{n_prompt}+{max_new} tokens exceed capacity {self.max_ctx}")
+        if use_graph and self.graph is None:
+            self.capture()
+        start, mid, end = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        start.record()
+        self.run(n_prompt - 1, use_graph)          # positions 0 .. n_prompt-2: no sampling needed
+        mid.record()
+        self.run(max_new, use_graph)               # step at position p writes token p+1
+        end.record()
+        torch.cuda.synchronize()
+        out = self.tokens[n_prompt: n_prompt + max_new].tolist()
+        return Generated(out, mid.elapsed_time(end) / 1e3, start.elapsed_time(mid) / 1e3, n_prompt)
