@@ -62,7 +62,10 @@ TFB_API int tfb_embed(const void* table, const int64_t* ids, void* out, int32_t 
  *      src/tilefoundry/ir/hir/nn/rms_norm.py:103-110)
  * mode TFB_NORM_CAST_THEN_GAIN: y = bf16(bf16(x32 * rsqrt(..)) * gamma)          (the spelled-out
  *      Qwen3RMSNorm, tests/models/qwen3_1_7b/model.py:127-138, :321-329) */
-enum { TFB_NORM_NONE = 0, TFB_NORM_F32GAIN = 1, TFB_NORM_CAST_THEN_GAIN = 2 };
+/* TFB_NORM_GATED (projections only): y = bf16(v * rsqrt(mean(v^2)+eps) * gamma32) with
+ * v = f32(x) * silu(f32(x_gate)) -- granite's gated output norm,
+ * examples/granite_4_0_h_small-cuda/model.py:223-236. */
+enum { TFB_NORM_NONE = 0, TFB_NORM_F32GAIN = 1, TFB_NORM_CAST_THEN_GAIN = 2, TFB_NORM_GATED = 3 };
 TFB_API int tfb_rmsnorm(const void* x, const void* gamma, void* y, int32_t rows, int32_t width, float eps,
                 int32_t mode, tfb_stream_t stream);
 
@@ -110,7 +113,10 @@ typedef struct {
     int32_t pdl;
     int32_t kernel;  /* TFB_KERNEL_AUTO, or force one implementation (for A/B measurement) */
     int32_t self_prefetch; /* streaming kernel: once its ring is full, ask the L2 for the rest of its own rows */
-    int32_t reserved;
+    int32_t rows_per_expert; /* expert mode: output rows come in slots of this many rows ... */
+    const int64_t* expert_idx; /* ... and slot s reads the rows of expert expert_idx[s] (device array) from w / w2,
+                                  which then hold [experts][rows_per_expert][k]; NULL = plain projection */
+    const void* x_gate;    /* [k] bf16 gate vector of TFB_NORM_GATED */
 } tfb_gemv_args;
 TFB_API int tfb_gemv(const tfb_gemv_args* args, tfb_stream_t stream);
 
@@ -334,6 +340,119 @@ typedef struct {
     int32_t pdl;
 } tfb_minicpm3_step_args;
 TFB_API int tfb_minicpm3_decode_step(const tfb_minicpm3_step_args* args, tfb_stream_t stream);
+
+/* out[i] = bf16(a[i] + bf16(b[i] * scale)).  Stands in for residual_add:
+ * examples/granite_4_0_h_small-cuda/model.py:502-508; reference kernel granite.cu:159. */
+TFB_API int tfb_residual_add(const void* a, const void* b, void* out, int32_t n, float scale, tfb_stream_t stream);
+
+/* ---- Mamba-2 single-token state update --------------------------------------------
+ * tfb_conv_step: depthwise causal convolution over [state | entry] (width 4), bf16 products and
+ * sum, optional bias, SiLU; the window then slides by the entry (state_out may alias state_in).
+ * tfb_ssm_step: dt = softplus(dt_raw + dt_bias); decay = exp(dt * -exp(a_log));
+ * state = state * decay + bf16(bf16(dt*B) * x) (f32); y = bf16(sum bf16(state) * C) + x * d_skip.
+ * Stand in for conv_step / ssm_step: examples/granite_4_0_h_small-cuda/model.py:154-220;
+ * reference kernels examples/granite_4_0_h_small-cuda/kernels/granite.cu:302-410. */
+TFB_API int tfb_conv_step(const void* entry, const void* state_in, void* state_out, const void* conv_w,
+                          const void* conv_b, void* mixed, void* entry_out, int32_t channels,
+                          int32_t kernel_width, int32_t pdl, tfb_stream_t stream);
+TFB_API int tfb_ssm_step(const float* state_in, float* state_out, const void* x, const void* b_vec,
+                         const void* c_vec, const void* dt_raw, const void* a_log, const void* dt_bias,
+                         const void* d_skip, void* y, int32_t n_heads, int32_t head_dim, int32_t n_state,
+                         int32_t n_groups, int32_t pdl, tfb_stream_t stream);
+
+/* ---- MoE routing and the fused down stage -------------------------------------------
+ * tfb_router_select: mode 0 = top-k of the (bf16) logits then softmax over the k (granite
+ * `routing`, model.py:376-386); mode 1 = softmax over all experts in f32, top-k, renormalise
+ * (Qwen3.5 `routing`, examples/qwen3_5_35b_a3b-tilelang/model.py:488-499).  indices int64[top_k]
+ * by value descending, ties to the lower index; weights bf16 and/or f32.
+ * tfb_moe_down: out = residual + bf16(res_scale * (sum_s weight[s] * (W_down[idx[s]] . inner[s])
+ * + W_shared . shared_act)) with the authored rounding points (routed_experts / experts /
+ * residual_add, granite model.py:406-470,502); reference kernels granite.cu:537-700. */
+TFB_API int tfb_router_select(const void* logits_bf16, const float* logits_f32, int64_t* indices,
+                              void* weights_bf16, float* weights_f32, int32_t experts, int32_t top_k,
+                              int32_t mode, int32_t pdl, tfb_stream_t stream);
+typedef struct {
+    const void* w_down;       /* [experts][hidden][inter] */
+    const void* w_shared;     /* [hidden][shared_inter] or NULL */
+    const void* inner;        /* [top_k][inter] bf16 */
+    const void* shared_act;   /* [shared_inter] bf16 */
+    const int64_t* indices;
+    const void* weights;      /* [top_k] bf16 */
+    const float* shared_gate; /* optional device scalar multiplying the shared expert's output */
+    const void* residual;     /* optional [hidden] */
+    void* out;                /* [hidden] bf16 */
+    int32_t hidden, inter, shared_inter, top_k;
+    float res_scale;
+    int32_t pdl;
+} tfb_moe_down_args;
+TFB_API int tfb_moe_down(const tfb_moe_down_args* args, tfb_stream_t stream);
+
+/* ---- a whole granite-4.0-h decode step ---------------------------------------------
+ * embed*12 -> layers x [mixer (Mamba-2: in_proj, conv, ssm, gated norm + out_proj | attention:
+ * qkv, nope GQA attention, o_proj) + 0.22 residual, MoE (router, top-10, gathered gate/up,
+ * shared gate/up, fused down + shared out) + 0.22 residual] -> final norm, lm_head / 16, greedy
+ * pick.  Recurrent and convolution state are updated in place.  Stands in for
+ * Granite4_0_H_Small.forward + append_cache + greedy (granite model.py:640-719). */
+typedef struct {
+    int32_t kind;             /* 0 = Mamba-2 mixer, 1 = attention mixer */
+    int32_t pad;
+    const void* gamma_in;
+    const void* w_in;         /* mamba: [proj, hidden]; attention: q|k|v rows [(hq+2hkv)*d, hidden] */
+    const void* conv_w;
+    const void* conv_b;
+    const void* a_log;
+    const void* dt_bias;
+    const void* d_skip;
+    const void* gamma_ssm;
+    const void* w_out;        /* mamba: [hidden, expand]; attention: w_o [hidden, hq*d] */
+    void* conv_state;         /* mamba: bf16 [conv_dim][3] */
+    float* ssm_state;         /* mamba: f32 [nh][pd][ns] */
+    void* k_pool;             /* attention */
+    void* v_pool;
+    const void* gamma_post;
+    const void* w_router;     /* [experts, hidden] */
+    const void* w_gate;       /* [experts, inter, hidden] */
+    const void* w_up;
+    const void* w_down;       /* [experts, hidden, inter] */
+    const void* w_shared_in;  /* [2*shared_inter, hidden] */
+    const void* w_shared_out; /* [hidden, shared_inter] */
+} tfb_granite_layer;
+typedef struct {
+    const tfb_granite_layer* layers;
+    int32_t n_layers, hidden;
+    int32_t nh, pd, ns, ng, conv_width;          /* mamba */
+    int32_t hq, hkv, d;                          /* attention */
+    int32_t experts, top_k, inter, shared_inter; /* MoE */
+    int64_t vocab;
+    float eps, attn_scale, embed_scale, res_scale, logits_scale;
+    const void* table;        /* [vocab, hidden]: embedding and tied head */
+    const void* gamma_final;
+    int32_t page_size, table_len, max_ctx;
+    const int32_t* block_table;
+    int64_t* tokens;
+    int32_t* pos;
+    int32_t n_prompt, max_tokens;
+    void* hidden_buf;         /* [hidden] */
+    void* proj_buf;           /* [max(proj, (hq+2hkv)*d)] */
+    void* mixed_buf;          /* [conv_dim] */
+    void* y_buf;              /* [max(expand, hq*d)] */
+    void* router_logits;      /* [experts] bf16 */
+    int64_t* router_idx;      /* [top_k] */
+    void* router_w;           /* [top_k] bf16 */
+    void* inner_buf;          /* [top_k*inter] */
+    void* shared_buf;         /* [shared_inter] */
+    void* logits;
+    float* part_o;
+    float* part_ml;
+    uint32_t* counters;       /* [hkv + 1] */
+    float* head_val;
+    int32_t* head_idx;
+    void* hidden_trace;       /* optional [n_layers+1][hidden] */
+    int64_t* idx_trace;       /* optional [n_layers][top_k]: the routing indices of every layer */
+    int64_t* picked;
+    int32_t pdl;
+} tfb_granite_step_args;
+TFB_API int tfb_granite_decode_step(const tfb_granite_step_args* args, tfb_stream_t stream);
 
 #ifdef __cplusplus
 }

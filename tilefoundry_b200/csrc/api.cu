@@ -78,7 +78,11 @@ int tfb_rmsnorm(const void* x, const void* gamma, void* y, int32_t rows, int32_t
 int tfb::host::gemv_checked(const tfb_gemv_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->w && a->x && a->y, TFB_EINVAL);
     TFB_REQUIRE(a->n > 0 && a->k > 0 && a->k % 256 == 0 && a->k <= 16384, TFB_EINVAL);
-    TFB_REQUIRE(a->prologue >= TFB_NORM_NONE && a->prologue <= TFB_NORM_CAST_THEN_GAIN, TFB_EINVAL);
+    TFB_REQUIRE(a->prologue >= TFB_NORM_NONE && a->prologue <= TFB_NORM_GATED, TFB_EINVAL);
+    TFB_REQUIRE(a->prologue != TFB_NORM_GATED || (a->x_gate && aligned16(a->x_gate) && a->k <= 8192 &&
+                                                  a->epilogue <= TFB_EPI_RESIDUAL && a->kernel != TFB_KERNEL_RING), TFB_EINVAL);
+    TFB_REQUIRE(!a->expert_idx || (a->rows_per_expert > 0 && a->rows_per_expert % 2 == 0 &&
+                                   a->n % a->rows_per_expert == 0 && a->kernel != TFB_KERNEL_RING), TFB_EINVAL);
     TFB_REQUIRE(a->epilogue >= TFB_EPI_STORE && a->epilogue <= TFB_EPI_STORE_F32, TFB_EINVAL);
     TFB_REQUIRE(a->prologue == TFB_NORM_NONE || a->gamma, TFB_EINVAL);
     TFB_REQUIRE(a->epilogue != TFB_EPI_RESIDUAL || a->residual, TFB_EINVAL);
@@ -103,6 +107,9 @@ int tfb::host::gemv_checked(const tfb_gemv_args* a, tfb_stream_t stream) {
     p.prefetch_bytes = a->prefetch_bytes;
     p.self_prefetch = a->self_prefetch;
     p.trace = next_trace();
+    p.x2 = static_cast<const uint16_t*>(a->x_gate);
+    p.expert_idx = reinterpret_cast<const long long*>(a->expert_idx);
+    p.rows_per_expert = a->rows_per_expert;
     if (a->kernel == TFB_KERNEL_RING && tfb::gemv_stream_supported(a->n, a->k))
         return done(tfb::gemv_stream_dispatch(p, a->prologue, a->epilogue, S(stream), a->pdl != 0));
     return done(tfb::gemv_dispatch(p, a->prologue, a->epilogue, S(stream), a->pdl != 0));

@@ -1,0 +1,174 @@
+// C ABI: Mamba-2 state update, MoE routing / down stage, and the granite-4.0-h decode step.
+#include "api_internal.h"
+#include "kernels.h"
+
+#include <cstring>
+
+using namespace tfb::host;
+typedef const uint16_t* cu16;
+
+extern "C" {
+
+int tfb_residual_add(const void* a, const void* b, void* out, int32_t n, float scale, tfb_stream_t stream) {
+    TFB_REQUIRE(a && b && out && n > 0, TFB_EINVAL);
+    return done(tfb::residual_add_launch(cu16(a), cu16(b), static_cast<uint16_t*>(out), n, scale, S(stream), false));
+}
+
+int tfb_conv_step(const void* entry, const void* state_in, void* state_out, const void* conv_w,
+                  const void* conv_b, void* mixed, void* entry_out, int32_t channels, int32_t kernel_width,
+                  int32_t pdl, tfb_stream_t stream) {
+    TFB_REQUIRE(entry && state_in && state_out && conv_w && mixed, TFB_EINVAL);
+    TFB_REQUIRE(channels > 0 && kernel_width == 4, TFB_EINVAL);
+    tfb::ConvParams p = {};
+    p.entry = cu16(entry); p.state_in = cu16(state_in); p.state_out = static_cast<uint16_t*>(state_out);
+    p.conv_w = cu16(conv_w); p.conv_b = cu16(conv_b); p.mixed = static_cast<uint16_t*>(mixed);
+    p.entry_out = static_cast<uint16_t*>(entry_out); p.channels = channels; p.kernel_width = kernel_width;
+    return done(tfb::conv_step_launch(p, S(stream), pdl != 0));
+}
+
+int tfb_ssm_step(const float* state_in, float* state_out, const void* x, const void* b_vec, const void* c_vec,
+                 const void* dt_raw, const void* a_log, const void* dt_bias, const void* d_skip, void* y,
+                 int32_t n_heads, int32_t head_dim, int32_t n_state, int32_t n_groups, int32_t pdl,
+                 tfb_stream_t stream) {
+    TFB_REQUIRE(state_in && state_out && x && b_vec && c_vec && dt_raw && a_log && dt_bias && d_skip && y, TFB_EINVAL);
+    TFB_REQUIRE(n_heads > 0 && head_dim > 0 && head_dim % 8 == 0 && n_state == 128, TFB_EINVAL);
+    TFB_REQUIRE(n_groups > 0 && n_heads % n_groups == 0, TFB_EINVAL);
+    TFB_REQUIRE(aligned16(state_in) && aligned16(state_out), TFB_EALIGN);
+    tfb::SsmParams p = {};
+    p.state_in = state_in; p.state_out = state_out; p.x = cu16(x); p.b_vec = cu16(b_vec); p.c_vec = cu16(c_vec);
+    p.dt_raw = cu16(dt_raw); p.a_log = cu16(a_log); p.dt_bias = cu16(dt_bias); p.d_skip = cu16(d_skip);
+    p.y = static_cast<uint16_t*>(y); p.nh = n_heads; p.pd = head_dim; p.ns = n_state; p.ng = n_groups;
+    return done(tfb::ssm_step_launch(p, S(stream), pdl != 0));
+}
+
+int tfb_router_select(const void* logits_bf16, const float* logits_f32, int64_t* indices, void* weights_bf16,
+                      float* weights_f32, int32_t experts, int32_t top_k, int32_t mode, int32_t pdl,
+                      tfb_stream_t stream) {
+    TFB_REQUIRE((logits_bf16 || logits_f32) && indices && (weights_bf16 || weights_f32), TFB_EINVAL);
+    TFB_REQUIRE(experts > 0 && experts <= 256 && top_k > 0 && top_k <= 32 && top_k <= experts, TFB_EINVAL);
+    TFB_REQUIRE(mode == 0 || mode == 1, TFB_EINVAL);
+    tfb::RouterParams p = {};
+    p.logits_bf16 = cu16(logits_bf16); p.logits_f32 = logits_f32;
+    p.indices = reinterpret_cast<long long*>(indices);
+    p.weights_bf16 = static_cast<uint16_t*>(weights_bf16); p.weights_f32 = weights_f32;
+    p.experts = experts; p.top_k = top_k; p.mode = mode;
+    return done(tfb::router_select_launch(p, S(stream), pdl != 0));
+}
+
+int tfb_moe_down(const tfb_moe_down_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->w_down && a->inner && a->indices && a->weights && a->out, TFB_EINVAL);
+    TFB_REQUIRE(a->hidden > 0 && a->inter > 0 && a->inter % 8 == 0 && a->top_k > 0 && a->top_k <= 32, TFB_EINVAL);
+    TFB_REQUIRE(!a->w_shared || (a->shared_act && a->shared_inter > 0 && a->shared_inter % 8 == 0), TFB_EINVAL);
+    TFB_REQUIRE(aligned16(a->w_down) && (!a->w_shared || aligned16(a->w_shared)), TFB_EALIGN);
+    TFB_REQUIRE((size_t(a->top_k) * a->inter + a->shared_inter) * 4 <= 96 * 1024, TFB_ECAPACITY);
+    tfb::MoeDownParams p = {};
+    p.w_down = static_cast<const uint4*>(a->w_down); p.w_shared = static_cast<const uint4*>(a->w_shared);
+    p.inner = cu16(a->inner); p.shared_act = cu16(a->shared_act);
+    p.indices = reinterpret_cast<const long long*>(a->indices); p.weights = cu16(a->weights);
+    p.shared_gate = a->shared_gate; p.residual = cu16(a->residual); p.out = static_cast<uint16_t*>(a->out);
+    p.hidden = a->hidden; p.inter = a->inter; p.shared_inter = a->w_shared ? a->shared_inter : 0; p.top_k = a->top_k;
+    p.res_scale = a->res_scale;
+    return done(tfb::moe_down_launch(p, S(stream), a->pdl != 0));
+}
+
+int tfb_granite_decode_step(const tfb_granite_step_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->layers && a->n_layers > 0 && a->table && a->gamma_final && a->tokens && a->pos, TFB_EINVAL);
+    TFB_REQUIRE(a->hidden_buf && a->proj_buf && a->mixed_buf && a->y_buf && a->router_logits && a->router_idx &&
+                    a->router_w && a->inner_buf && a->shared_buf, TFB_EINVAL);
+    TFB_REQUIRE(a->part_o && a->part_ml && a->counters && a->head_val && a->head_idx, TFB_EINVAL);
+    TFB_REQUIRE(a->max_tokens <= a->max_ctx + 1, TFB_ECAPACITY);
+    const bool pdl = a->pdl != 0;
+    const int H = a->hidden, EXP = a->nh * a->pd, BC = a->ng * a->ns, CONVD = EXP + 2 * BC, PROJ = EXP + CONVD + a->nh;
+    const int QP = a->hq * a->d, NQKV = (a->hq + 2 * a->hkv) * a->d;
+    const int E = a->experts, K = a->top_k, I = a->inter, IS = a->shared_inter;
+    cudaStream_t st = S(stream);
+    uint16_t* hid = static_cast<uint16_t*>(a->hidden_buf);
+    uint16_t* proj = static_cast<uint16_t*>(a->proj_buf);
+    uint16_t* mixed = static_cast<uint16_t*>(a->mixed_buf);
+    uint16_t* trace = static_cast<uint16_t*>(a->hidden_trace);
+
+    cudaError_t e = tfb::embed_launch(cu16(a->table), nullptr, reinterpret_cast<const long long*>(a->tokens), a->pos,
+                                      hid, 1, H, a->vocab, a->embed_scale, st, pdl);
+    if (e != cudaSuccess) return fail_launch(e);
+
+    auto base = [&](tfb_gemv_args& g) {
+        std::memset(&g, 0, sizeof g);
+        g.eps = a->eps; g.x_scale = 1.f; g.res_scale = 1.f; g.out_scale = 1.f; g.pdl = pdl;
+    };
+    int rc;
+    tfb_gemv_args g;
+    for (int l = 0; l < a->n_layers; ++l) {
+        const tfb_granite_layer& L = a->layers[l];
+        if (L.kind == 0) {
+            // in_projection: gate | conv entry | dt
+            base(g); g.w = L.w_in; g.x = hid; g.gamma = L.gamma_in; g.y = proj; g.n = PROJ; g.k = H;
+            g.prologue = TFB_NORM_F32GAIN; g.epilogue = TFB_EPI_STORE;
+            if ((rc = gemv_checked(&g, stream))) return rc;
+            if ((rc = tfb_conv_step(proj + EXP, L.conv_state, L.conv_state, L.conv_w, L.conv_b, mixed, nullptr, CONVD,
+                                    a->conv_width, pdl, stream))) return rc;
+            if ((rc = tfb_ssm_step(L.ssm_state, L.ssm_state, mixed, mixed + EXP, mixed + EXP + BC, proj + EXP + CONVD,
+                                   L.a_log, L.dt_bias, L.d_skip, a->y_buf, a->nh, a->pd, a->ns, a->ng, pdl, stream)))
+                return rc;
+            // gated norm + out_proj + scaled residual
+            base(g); g.w = L.w_out; g.x = a->y_buf; g.x_gate = proj; g.gamma = L.gamma_ssm; g.residual = hid; g.y = hid;
+            g.n = H; g.k = EXP; g.prologue = TFB_NORM_GATED; g.epilogue = TFB_EPI_RESIDUAL; g.res_scale = a->res_scale;
+            if ((rc = gemv_checked(&g, stream))) return rc;
+        } else {
+            base(g); g.w = L.w_in; g.x = hid; g.gamma = L.gamma_in; g.y = proj; g.n = NQKV; g.k = H;
+            g.prologue = TFB_NORM_F32GAIN; g.epilogue = TFB_EPI_STORE;
+            if ((rc = gemv_checked(&g, stream))) return rc;
+            tfb_attn_gqa_args t;
+            std::memset(&t, 0, sizeof t);
+            t.qkv = proj; t.pos = a->pos; t.k_pool = L.k_pool; t.v_pool = L.v_pool; t.block_table = a->block_table;
+            t.out = a->y_buf; t.part_o = a->part_o; t.part_ml = a->part_ml; t.counters = a->counters;
+            t.hq = a->hq; t.hkv = a->hkv; t.d = a->d; t.rotary_dim = 0; t.page_size = a->page_size;
+            t.table_len = a->table_len; t.max_ctx = a->max_ctx; t.max_pos = a->max_ctx; t.eps = a->eps;
+            t.scale = a->attn_scale; t.norm_mode = TFB_NORM_NONE; t.pdl = pdl;
+            if ((rc = tfb_attn_gqa_decode(&t, stream))) return rc;
+            base(g); g.w = L.w_out; g.x = a->y_buf; g.residual = hid; g.y = hid; g.n = H; g.k = QP;
+            g.prologue = TFB_NORM_NONE; g.epilogue = TFB_EPI_RESIDUAL; g.res_scale = a->res_scale;
+            if ((rc = gemv_checked(&g, stream))) return rc;
+        }
+        // ---- MoE block ----
+        base(g); g.w = L.w_router; g.x = hid; g.gamma = L.gamma_post; g.y = a->router_logits; g.n = E; g.k = H;
+        g.prologue = TFB_NORM_F32GAIN; g.epilogue = TFB_EPI_STORE;
+        if ((rc = gemv_checked(&g, stream))) return rc;
+        if ((rc = tfb_router_select(a->router_logits, nullptr, a->router_idx, a->router_w, nullptr, E, K, 0, pdl, stream)))
+            return rc;
+        if (a->idx_trace) {
+            e = tfb::copy_launch(a->router_idx, a->idx_trace + size_t(l) * K, K * 8, st, pdl);
+            if (e != cudaSuccess) return fail_launch(e);
+        }
+        base(g); g.w = L.w_gate; g.w2 = L.w_up; g.x = hid; g.gamma = L.gamma_post; g.y = a->inner_buf; g.n = K * I; g.k = H;
+        g.prologue = TFB_NORM_F32GAIN; g.epilogue = TFB_EPI_SWIGLU; g.expert_idx = a->router_idx; g.rows_per_expert = I;
+        if ((rc = gemv_checked(&g, stream))) return rc;
+        base(g); g.w = L.w_shared_in; g.w2 = cu16(L.w_shared_in) + size_t(IS) * H; g.x = hid; g.gamma = L.gamma_post;
+        g.y = a->shared_buf; g.n = IS; g.k = H; g.prologue = TFB_NORM_F32GAIN; g.epilogue = TFB_EPI_SWIGLU;
+        if ((rc = gemv_checked(&g, stream))) return rc;
+        tfb_moe_down_args d;
+        std::memset(&d, 0, sizeof d);
+        d.w_down = L.w_down; d.w_shared = L.w_shared_out; d.inner = a->inner_buf; d.shared_act = a->shared_buf;
+        d.indices = a->router_idx; d.weights = a->router_w; d.residual = hid; d.out = hid;
+        d.hidden = H; d.inter = I; d.shared_inter = IS; d.top_k = K; d.res_scale = a->res_scale; d.pdl = pdl;
+        if ((rc = tfb_moe_down(&d, stream))) return rc;
+        if (trace) {
+            e = tfb::copy_launch(hid, trace + size_t(l) * H, H * 2, st, pdl);
+            if (e != cudaSuccess) return fail_launch(e);
+        }
+    }
+    if (trace) {
+        e = tfb::rmsnorm_launch(hid, cu16(a->gamma_final), trace + size_t(a->n_layers) * H, 1, H, a->eps,
+                                TFB_NORM_F32GAIN, st, pdl);
+        if (e != cudaSuccess) return fail_launch(e);
+    }
+    tfb_lm_head_args h;
+    std::memset(&h, 0, sizeof h);
+    h.w = a->table; h.x = hid; h.gamma = a->gamma_final; h.logits = a->logits;
+    h.scratch_val = a->head_val; h.scratch_idx = a->head_idx; h.counter = a->counters + a->hkv;
+    h.n = int(a->vocab); h.k = H; h.prologue = TFB_NORM_F32GAIN; h.eps = a->eps;
+    h.x_scale = 1.f; h.out_scale = a->logits_scale; h.pdl = pdl; h.token_out = a->picked;
+    h.tokens = a->tokens; h.pos = a->pos; h.n_prompt = a->n_prompt; h.max_tokens = a->max_tokens;
+    return tfb_lm_head_argmax(&h, stream);
+}
+
+}  // extern "C"

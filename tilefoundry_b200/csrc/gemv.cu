@@ -36,10 +36,15 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
     trace_start(p.trace);
     // Weights do not depend on the preceding kernel: start streaming them now.
     RowsDot<ROWS, UNROLL> a, b;
+    // Expert mode: output rows are grouped in slots of rows_per_expert; slot s reads the rows of
+    // expert expert_idx[s] (a device array the router wrote), so its loads must follow the wait.
+    const bool routed = p.expert_idx != nullptr;
     const uint4* wrow = p.w + size_t(max(row0, 0)) * row_stride;
     const uint4* w2row = (EPI == 2) ? p.w2 + size_t(row0) * row_stride : nullptr;
-    a.load(wrow, row_stride, rows_valid, it_begin, it_end, lane);
-    if (EPI == 2) b.load(w2row, row_stride, rows_valid, it_begin, it_end, lane);
+    if (!routed) {
+        a.load(wrow, row_stride, rows_valid, it_begin, it_end, lane);
+        if (EPI == 2) b.load(w2row, row_stride, rows_valid, it_begin, it_end, lane);
+    }
     if (threadIdx.x == 0) l2_prefetch_slice(p.prefetch, p.prefetch_bytes, blockIdx.x, gridDim.x);
     constexpr int MAXC = 4;
     const bool fast_stage = (p.k >> 3) <= MAXC * WARPS * 32;
@@ -50,12 +55,20 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
     pdl_wait();
     trace_waited(p.trace);
 
+    if (routed) {
+        const int slot = max(row0, 0) / p.rows_per_expert, within = max(row0, 0) % p.rows_per_expert;
+        const size_t erow = size_t(p.expert_idx[min(slot, p.n / p.rows_per_expert - 1)]) * p.rows_per_expert + within;
+        wrow = p.w + erow * row_stride;
+        if (EPI == 2) w2row = p.w2 + erow * row_stride;
+        a.load(wrow, row_stride, rows_valid, it_begin, it_end, lane);
+        if (EPI == 2) b.load(w2row, row_stride, rows_valid, it_begin, it_end, lane);
+    }
     // the residual is needed last but its load is issued first: one round trip less at the end
     float res_early = 0.f;
     if (EPI == 1 && KSPLIT == 1 && lane < rows_valid) res_early = bf16_bits_to_f32(p.residual[row0 + lane]);
     if (EPI == 1 && KSPLIT > 1 && ks == 0 && lane < rows_valid) res_early = bf16_bits_to_f32(p.residual[row0 + lane]);
 
-    if (fast_stage) sg.template stage<NORM_MODE>(p.x, xs, red, p.k, p.eps, p.x_scale);
+    if (fast_stage) sg.template stage<NORM_MODE>(p.x, p.x2, xs, red, p.k, p.eps, p.x_scale);
     else stage_activation<NORM_MODE>(p.x, p.gamma, xs, red, p.k, p.eps, p.x_scale);
     __syncthreads();
     trace_mark(p.trace, 0);
@@ -179,8 +192,8 @@ cudaError_t gemv_dispatch(const GemvParams& p, int norm_mode, int epi, cudaStrea
 #ifdef TFB_TUNE
     TFB_CASE(0, 0) TFB_CASE(2, 0) TFB_CASE(0, 1) TFB_CASE(2, 2)
 #else
-    TFB_CASE(0, 0) TFB_CASE(1, 0) TFB_CASE(2, 0)
-    TFB_CASE(0, 1) TFB_CASE(1, 1) TFB_CASE(2, 1)
+    TFB_CASE(0, 0) TFB_CASE(1, 0) TFB_CASE(2, 0) TFB_CASE(3, 0)
+    TFB_CASE(0, 1) TFB_CASE(1, 1) TFB_CASE(2, 1) TFB_CASE(3, 1)
     TFB_CASE(0, 2) TFB_CASE(1, 2) TFB_CASE(2, 2)
     TFB_CASE(0, 3) TFB_CASE(1, 3) TFB_CASE(2, 3)
 #endif

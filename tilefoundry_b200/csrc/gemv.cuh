@@ -92,9 +92,50 @@ struct StagedGain {
             g[m] = (c < (k >> 3)) ? *reinterpret_cast<const uint4*>(gamma + (c << 3)) : make_uint4(0, 0, 0, 0);
         }
     }
+    // NORM_MODE 3 ("gated"): the vector normalised is f32(x) * silu(f32(gate)), kept in f32 through the
+    // gain and rounded once -- granite's gated output norm (rms_norm(y * silu(gate)) * gamma).
     template <int NORM_MODE>
-    __device__ __forceinline__ void stage(const uint16_t* __restrict__ x, float* xs, float* red, int k,
-                                          float eps, float x_scale) {
+    __device__ __forceinline__ void stage(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate,
+                                          float* xs, float* red, int k, float eps, float x_scale) {
+        if (NORM_MODE == 3) {
+            float f[MAXC][8];
+            float ss = 0.f;
+#pragma unroll
+            for (int m = 0; m < MAXC; ++m) {
+                const int c = threadIdx.x + m * blockDim.x;
+                if (c < (k >> 3)) {
+                    const uint4 xv = *reinterpret_cast<const uint4*>(x + (c << 3));
+                    const uint4 gv = *reinterpret_cast<const uint4*>(gate + (c << 3));
+                    const uint32_t u[4] = {xv.x, xv.y, xv.z, xv.w}, q[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        f[m][2 * i] = bf16_lo(u[i]) * silu_f32(bf16_lo(q[i]));
+                        f[m][2 * i + 1] = bf16_hi(u[i]) * silu_f32(bf16_hi(q[i]));
+                        ss = fmaf(f[m][2 * i], f[m][2 * i], ss);
+                        ss = fmaf(f[m][2 * i + 1], f[m][2 * i + 1], ss);
+                    }
+                }
+            }
+            ss = block_sum(ss, red);
+            const float rstd = rsqrtf(ss / float(k) + eps);
+#pragma unroll
+            for (int m = 0; m < MAXC; ++m) {
+                const int c = threadIdx.x + m * blockDim.x;
+                if (c >= (k >> 3)) continue;
+                const uint32_t gg[4] = {g[m].x, g[m].y, g[m].z, g[m].w};
+                float o[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    o[2 * i] = round_bf16(f[m][2 * i] * rstd * bf16_lo(gg[i]));
+                    o[2 * i + 1] = round_bf16(f[m][2 * i + 1] * rstd * bf16_hi(gg[i]));
+                }
+                const int it = c >> 5, lane = c & 31;
+                float4* dst = reinterpret_cast<float4*>(xs);
+                dst[(it * 2) * 32 + lane] = make_float4(o[0], o[1], o[2], o[3]);
+                dst[(it * 2 + 1) * 32 + lane] = make_float4(o[4], o[5], o[6], o[7]);
+            }
+            return;
+        }
         uint4 xv[MAXC];
 #pragma unroll
         for (int m = 0; m < MAXC; ++m) {

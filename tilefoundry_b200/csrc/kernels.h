@@ -17,6 +17,9 @@ struct GemvParams {
     const void* prefetch;
     unsigned long long prefetch_bytes;
     unsigned long long* trace;
+    const uint16_t* x2;              // gate vector of the gated-norm prologue (mode 3)
+    const long long* expert_idx;     // expert mode: expert of each slot of rows_per_expert output rows
+    int rows_per_expert;
     // streaming kernel only
     int kc, nstages, self_prefetch;
     unsigned* status;
@@ -86,6 +89,8 @@ cudaError_t embed_launch(const uint16_t* table, const long long* ids, const long
 cudaError_t rmsnorm_launch(const uint16_t* x, const uint16_t* gamma, uint16_t* y, int rows, int width,
                            float eps, int mode, cudaStream_t stream, bool pdl);
 cudaError_t copy_launch(const void* src, void* dst, int bytes, cudaStream_t stream, bool pdl);
+cudaError_t residual_add_launch(const uint16_t* a, const uint16_t* b, uint16_t* out, int n, float scale,
+                                cudaStream_t stream, bool pdl);
 
 struct MlaParams {
     const uint16_t* q_up;      // [heads][nope+rope]
@@ -110,5 +115,58 @@ struct MlaParams {
 };
 int mla_splits(int max_ctx);
 cudaError_t attn_mla_dispatch(const MlaParams& p, cudaStream_t stream, bool pdl);
+
+
+struct ConvParams {
+    const uint16_t* entry;      // [channels] this token's column
+    const uint16_t* state_in;   // [channels][width-1]
+    uint16_t* state_out;        // may alias state_in
+    const uint16_t* conv_w;     // [channels][width]
+    const uint16_t* conv_b;     // [channels] or null
+    uint16_t* mixed;            // [channels]
+    uint16_t* entry_out;        // optional copy of the entry
+    int channels, kernel_width;
+};
+cudaError_t conv_step_launch(const ConvParams& p, cudaStream_t stream, bool pdl);
+
+struct SsmParams {
+    const float* state_in;      // [nh][pd][ns] f32
+    float* state_out;           // may alias state_in
+    const uint16_t* x;          // [nh*pd]
+    const uint16_t* b_vec;      // [ng][ns]
+    const uint16_t* c_vec;      // [ng][ns]
+    const uint16_t* dt_raw;     // [nh]
+    const uint16_t* a_log;
+    const uint16_t* dt_bias;
+    const uint16_t* d_skip;
+    uint16_t* y;                // [nh*pd]
+    int nh, pd, ns, ng;
+};
+cudaError_t ssm_step_launch(const SsmParams& p, cudaStream_t stream, bool pdl);
+
+struct RouterParams {
+    const uint16_t* logits_bf16;
+    const float* logits_f32;
+    long long* indices;         // [top_k]
+    uint16_t* weights_bf16;
+    float* weights_f32;
+    int experts, top_k, mode;
+};
+cudaError_t router_select_launch(const RouterParams& p, cudaStream_t stream, bool pdl);
+
+struct MoeDownParams {
+    const uint4* w_down;        // [experts][hidden][inter]
+    const uint4* w_shared;      // [hidden][shared_inter] or null
+    const uint16_t* inner;      // [top_k][inter]
+    const uint16_t* shared_act; // [shared_inter]
+    const long long* indices;
+    const uint16_t* weights;    // [top_k] bf16
+    const float* shared_gate;   // optional scalar
+    const uint16_t* residual;   // optional [hidden]
+    uint16_t* out;              // [hidden]
+    int hidden, inter, shared_inter, top_k;
+    float res_scale;
+};
+cudaError_t moe_down_launch(const MoeDownParams& p, cudaStream_t stream, bool pdl);
 
 }  // namespace tfb

@@ -82,6 +82,19 @@ cudaError_t copy_launch(const void* src, void* dst, int bytes, cudaStream_t stre
                          static_cast<const uint4*>(src), static_cast<uint4*>(dst), bytes / 16);
 }
 
+// out = a + bf16(b * scale), element by element (granite's residual_add as a stand-alone function)
+__global__ void residual_add_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b,
+                                    uint16_t* __restrict__ out, int n, float scale) {
+    pdl_trigger();
+    pdl_wait();
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+        out[i] = f32_to_bf16_bits(bf16_bits_to_f32(a[i]) + round_bf16(bf16_bits_to_f32(b[i]) * scale));
+}
+cudaError_t residual_add_launch(const uint16_t* a, const uint16_t* b, uint16_t* out, int n, float scale,
+                                cudaStream_t stream, bool pdl) {
+    return launch_kernel(residual_add_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, pdl, a, b, out, n, scale);
+}
+
 // ---- lm_head + greedy pick -----------------------------------------------------
 // Algorithmic bytes per launch = n*k*2 (the head matrix, read once).  Each CTA
 // reduces its rows' bf16-rounded logits to one (max, lowest index) pair; the last

@@ -1,0 +1,170 @@
+// Mixture-of-experts pieces for batch-1 decode: router selection (top-k + softmax) and the fused
+// "down" stage (gathered expert down-projections, routing-weighted sum, shared expert, residual).
+//
+// Router select is one warp of latency.  The down kernel is HBM-bound: algorithmic bytes per
+// launch = hidden * (top_k * inter + shared_inter) * 2 (each output row reads its top_k expert rows
+// and its shared-expert row once); granite: 4096 * (10*768 + 1536) * 2 = 75.5 MB.
+#include "common.cuh"
+#include "kernels.h"
+#include "launch.h"
+
+namespace tfb {
+
+// mode 0 (granite, examples/granite_4_0_h_small-cuda/model.py:376-386): logits (already bf16) -> top-k
+//        -> softmax over the k -> bf16 weights.
+// mode 1 (Qwen3.5, examples/qwen3_5_35b_a3b-tilelang/model.py:488-499): softmax over ALL experts in
+//        f32 -> top-k -> renormalise by the sum of the k.
+// Selection order is by value descending; equal values resolve to the lower index.
+template <int MAXE>
+__global__ void __launch_bounds__(32) router_select_kernel(const RouterParams p) {
+    constexpr int PER = MAXE / 32;
+    const int lane = threadIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    float v[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int e = lane + 32 * i;
+        v[i] = -INFINITY;
+        if (e < p.experts) v[i] = p.logits_f32 ? p.logits_f32[e] : bf16_bits_to_f32(p.logits_bf16[e]);
+    }
+    if (p.mode == 1) {                         // probabilities over all experts
+        float m = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) m = fmaxf(m, v[i]);
+        m = warp_max(m);
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) { v[i] = (lane + 32 * i < p.experts) ? expf(v[i] - m) : -INFINITY; s += fmaxf(v[i], 0.f); }
+        s = warp_sum(s);
+#pragma unroll
+        for (int i = 0; i < PER; ++i) if (lane + 32 * i < p.experts) v[i] = v[i] / s;
+    }
+    float top_v = 0.f;                          // lane j keeps the j-th selection
+    int top_i = 0;
+    for (int j = 0; j < p.top_k; ++j) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int e = lane + 32 * i;
+            if (e < p.experts && (v[i] > best || (v[i] == best && e < best_e))) { best = v[i]; best_e = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+        }
+        if (lane == j) { top_v = best; top_i = best_e; }
+#pragma unroll
+        for (int i = 0; i < PER; ++i) if (lane + 32 * i == best_e) v[i] = -INFINITY;
+    }
+    const bool mine = lane < p.top_k;
+    float w;
+    if (p.mode == 0) {
+        const float m = warp_max(mine ? top_v : -INFINITY);
+        const float e = mine ? expf(top_v - m) : 0.f;
+        w = e / warp_sum(e);
+    } else {
+        w = top_v / warp_sum(mine ? top_v : 0.f);
+    }
+    if (mine) {
+        p.indices[lane] = top_i;
+        if (p.weights_bf16) p.weights_bf16[lane] = f32_to_bf16_bits(w);
+        if (p.weights_f32) p.weights_f32[lane] = w;
+    }
+}
+
+cudaError_t router_select_launch(const RouterParams& p, cudaStream_t stream, bool pdl) {
+    if (p.experts <= 128) return launch_kernel(router_select_kernel<128>, dim3(1), dim3(32), 0, stream, pdl, p);
+    if (p.experts <= 256) return launch_kernel(router_select_kernel<256>, dim3(1), dim3(32), 0, stream, pdl, p);
+    return cudaErrorInvalidValue;
+}
+
+// One warp per output row j: for each selected slot s, dot(w_down[idx[s]][j, :], inner[s, :]) rounded to
+// bf16, times the routing weight (bf16), summed over slots with one rounding; plus the shared
+// expert's row; then the layer's scaled residual.  All rounding points of routed_experts / experts /
+// residual_add (examples/granite_4_0_h_small-cuda/model.py:406-470,502) are kept.
+constexpr int kDownWarps = 8;
+__global__ void __launch_bounds__(kDownWarps * 32) moe_down_kernel(const MoeDownParams p) {
+    extern __shared__ __align__(16) float smem[];
+    float* xin = smem;                                        // [top_k][inter] then [shared_inter]
+    __shared__ long long s_idx[32];
+    __shared__ float s_w[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int j = blockIdx.x * kDownWarps + warp;
+    const int I = p.inter, IS = p.shared_inter, K = p.top_k;
+
+    // the shared expert's row does not depend on the routing: fetch it before the wait
+    const int sh_pieces = IS >> 3;                            // 16-byte pieces in a shared-expert row
+    uint4 shw[4];
+    const uint4* shrow = (p.w_shared && j < p.hidden) ? p.w_shared + size_t(j) * sh_pieces : nullptr;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) shw[u] = (shrow && lane + 32 * u < sh_pieces) ? ld_stream16(shrow + lane + 32 * u) : make_uint4(0, 0, 0, 0);
+    pdl_trigger();
+    pdl_wait();
+
+    const float res = (p.residual && j < p.hidden) ? bf16_bits_to_f32(p.residual[j]) : 0.f;
+    if (threadIdx.x < K) { s_idx[threadIdx.x] = p.indices[threadIdx.x]; s_w[threadIdx.x] = bf16_bits_to_f32(p.weights[threadIdx.x]); }
+    for (int i = threadIdx.x; i < K * I + IS; i += blockDim.x)
+        xin[i] = bf16_bits_to_f32(i < K * I ? p.inner[i] : p.shared_act[i - K * I]);
+    __syncthreads();
+    if (j >= p.hidden) return;
+
+    float routed = 0.f;
+    const int pieces = I >> 3;
+    for (int s = 0; s < K; ++s) {
+        const uint4* row = p.w_down + (size_t(s_idx[s]) * p.hidden + j) * pieces;
+        const float* x = xin + s * I;
+        float acc = 0.f;
+        for (int c = lane; c < pieces; c += 32) {
+            const uint4 w = ld_stream16(row + c);
+            const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
+            acc = dot8(w, xa, xb, acc);
+        }
+        acc = warp_sum(acc);
+        routed += round_bf16(round_bf16(acc) * s_w[s]);        // bf16 products, f32 running sum
+    }
+    float out = round_bf16(routed);                            // the reduce over slots returns bf16
+    if (shrow) {
+        const float* x = xin + K * I;
+        float acc = 0.f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int c = lane + 32 * u;
+            if (c < sh_pieces) {
+                const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
+                acc = dot8(shw[u], xa, xb, acc);
+            }
+        }
+        for (int c = lane + 128; c < sh_pieces; c += 32) {       // rows wider than 1024 elements
+            const uint4 w = ld_stream16(shrow + c);
+            const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
+            acc = dot8(w, xa, xb, acc);
+        }
+        float sh = round_bf16(warp_sum(acc));
+        if (p.shared_gate) sh = round_bf16(sh * *p.shared_gate);  // Qwen3.5: sigmoid gate on the shared expert
+        out = round_bf16(out + sh);
+    }
+    if (lane == 0) {
+        if (p.residual) out = res + round_bf16(out * p.res_scale);
+        p.out[j] = f32_to_bf16_bits(out);
+    }
+}
+
+cudaError_t moe_down_launch(const MoeDownParams& p, cudaStream_t stream, bool pdl) {
+    const size_t smem = (size_t(p.top_k) * p.inter + p.shared_inter) * sizeof(float);
+    if (smem > 48 * 1024) {
+        static bool once = false;
+        if (!once) {
+            cudaError_t e = cudaFuncSetAttribute(moe_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+            if (e != cudaSuccess) return e;
+            once = true;
+        }
+    }
+    const dim3 grid((p.hidden + kDownWarps - 1) / kDownWarps), block(kDownWarps * 32);
+    return launch_kernel(moe_down_kernel, grid, block, smem, stream, pdl, p);
+}
+
+}  // namespace tfb

@@ -1,0 +1,140 @@
+"""granite-4.0-h decode session: Mamba-2 state and convolution windows updated in place, paged KV for the
+attention layers, expert weights left in their authored ``[experts, ...]`` slabs (rows gathered on the
+device by the routing indices), one captured step."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from .. import lib
+from ..authored.granite_4_0_h_small import GraniteConfig
+from . import paged_kv
+from .session import DecodeSession
+
+MAMBA_W = ("gamma_in", "w_in", "conv_w", "conv_b", "a_log", "dt_bias", "d_skip", "gamma_ssm", "w_out")
+ATTN_W = ("gamma_in", "w_q", "w_k", "w_v", "w_o")
+MOE_W = ("gamma_post", "w_gate", "w_up", "w_down", "w_shared_in", "w_shared_out")
+
+
+def pack_mixer(kind: str, w: dict) -> dict:
+    if kind == "linear_attention":
+        return {n: w[n].contiguous() for n in MAMBA_W}
+    return {"gamma_in": w["gamma_in"].contiguous(), "w_in": torch.cat([w["w_q"], w["w_k"], w["w_v"]], 0).contiguous(),
+            "w_out": w["w_o"].contiguous()}
+
+
+class GraniteSession(DecodeSession):
+    def __init__(self, cfg: GraniteConfig, resource, *, max_ctx: int = 2176, device="cuda:0",
+                 keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True):
+        if not torch.cuda.is_available():
+            raise RuntimeError("GraniteSession needs a CUDA device; there is no CPU path")
+        lib.load()
+        self.cfg, self.device, self.max_ctx = cfg, torch.device(device), int(max_ctx)
+        dev = self.device
+        to = lambda t: t.to(dev)
+        self.table_w = to(resource.load("table")).contiguous()
+        self.gamma_final = to(resource.load("gamma_final")).contiguous()
+        bf, f32 = torch.bfloat16, torch.float32
+        z = lambda *s, dtype=bf: torch.zeros(*s, device=dev, dtype=dtype)
+        HQ, HKV, D, H = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.hidden_size
+        E, K, I, IS, V = (cfg.num_local_experts, cfg.num_experts_per_tok, cfg.intermediate_size,
+                          cfg.shared_intermediate_size, cfg.vocab_size)
+        self.table = paged_kv.block_table(1, self.max_ctx, device=dev)
+        self.layers = []
+        for i, kind in enumerate(cfg.layer_types):
+            sub = resource.subtree(f"layer{i}")
+            mix, moe = sub.subtree("mixer"), sub.subtree("moe")
+            names = MAMBA_W if kind == "linear_attention" else ATTN_W
+            layer = pack_mixer(kind, {n: to(mix.load(n)) for n in names})
+            layer.update({n: to(moe.load(n)).contiguous() for n in MOE_W})
+            layer["w_router"] = to(moe.subtree("router").load("w_router")).contiguous()
+            layer["kind"] = kind
+            if kind == "linear_attention":
+                layer["conv_state"] = z(cfg.conv_dim, cfg.mamba_d_conv - 1)
+                layer["ssm_state"] = z(cfg.mamba_n_heads, cfg.mamba_d_head, cfg.mamba_d_state, dtype=f32)
+            else:
+                layer["k_pool"] = paged_kv.new_pool(1, self.max_ctx, HKV, D, device=dev)
+                layer["v_pool"] = paged_kv.new_pool(1, self.max_ctx, HKV, D, device=dev)
+            self.layers.append(layer)
+
+        nsplit = lib.attn_splits(self.max_ctx)
+        L = len(self.layers)
+        self.tokens, self.pos = z(self.max_ctx + 1, dtype=torch.int64), z(1, dtype=torch.int32)
+        self.hidden = z(H)
+        self.proj = z(max(cfg.proj, (HQ + 2 * HKV) * D))
+        self.mixed = z(cfg.conv_dim)
+        self.y = z(max(cfg.expand, HQ * D))
+        self.router_logits, self.router_idx, self.router_w = z(E), z(K, dtype=torch.int64), z(K)
+        self.inner, self.shared = z(K * I), z(IS)
+        self.logits = z(V) if keep_logits else None
+        self.part_o, self.part_ml = z(HQ * nsplit * D, dtype=f32), z(HQ * nsplit * 2, dtype=f32)
+        self.counters = z(HKV + 1, dtype=torch.int32)
+        n_head = lib.lm_head_scratch_entries(V)
+        self.head_val, self.head_idx = z(n_head, dtype=f32), z(n_head, dtype=torch.int32)
+        self.trace = z(L + 1, H) if trace_hidden else None
+        self.idx_trace = z(L, K, dtype=torch.int64) if trace_hidden else None
+        self.picked = z(1, dtype=torch.int64)
+
+        self._layer_structs = (lib.GraniteLayer * L)()
+        for s, layer in zip(self._layer_structs, self.layers):
+            s.kind = 0 if layer["kind"] == "linear_attention" else 1
+            for name, _ in lib.GraniteLayer._fields_[2:]:
+                setattr(s, name, lib.ptr(layer.get(name)))
+        as_bf16 = lambda v: float(torch.tensor(v, dtype=bf))
+        self.args = lib.GraniteStepArgs(
+            layers=self._layer_structs, n_layers=L, hidden=H, nh=cfg.mamba_n_heads, pd=cfg.mamba_d_head,
+            ns=cfg.mamba_d_state, ng=cfg.mamba_n_groups, conv_width=cfg.mamba_d_conv, hq=HQ, hkv=HKV, d=D,
+            experts=E, top_k=K, inter=I, shared_inter=IS, vocab=V, eps=cfg.rms_norm_eps,
+            attn_scale=cfg.attention_multiplier, embed_scale=as_bf16(cfg.embedding_multiplier),
+            res_scale=as_bf16(cfg.residual_multiplier), logits_scale=1.0 / cfg.logits_scaling,
+            table=lib.ptr(self.table_w), gamma_final=lib.ptr(self.gamma_final), page_size=paged_kv.PAGE_SIZE,
+            table_len=self.table.shape[1], max_ctx=self.max_ctx, block_table=lib.ptr(self.table),
+            tokens=lib.ptr(self.tokens), pos=lib.ptr(self.pos), n_prompt=0, max_tokens=self.max_ctx + 1,
+            hidden_buf=lib.ptr(self.hidden), proj_buf=lib.ptr(self.proj), mixed_buf=lib.ptr(self.mixed),
+            y_buf=lib.ptr(self.y), router_logits=lib.ptr(self.router_logits), router_idx=lib.ptr(self.router_idx),
+            router_w=lib.ptr(self.router_w), inner_buf=lib.ptr(self.inner), shared_buf=lib.ptr(self.shared),
+            logits=lib.ptr(self.logits), part_o=lib.ptr(self.part_o), part_ml=lib.ptr(self.part_ml),
+            counters=lib.ptr(self.counters), head_val=lib.ptr(self.head_val), head_idx=lib.ptr(self.head_idx),
+            hidden_trace=lib.ptr(self.trace), idx_trace=lib.ptr(self.idx_trace), picked=lib.ptr(self.picked),
+            pdl=int(pdl))
+        n_m = sum(1 for l in self.layers if l["kind"] == "linear_attention")
+        self.launches_per_step = 2 + 9 * n_m + 8 * (L - n_m) + (2 * L + 1 if trace_hidden else 0)
+
+    def reset(self, prompt_ids) -> None:
+        super().reset(prompt_ids)
+        for layer in self.layers:                    # recurrent state starts at zero for a new sequence
+            if layer["kind"] == "linear_attention":
+                layer["conv_state"].zero_()
+                layer["ssm_state"].zero_()
+
+    def capture(self) -> None:
+        # the warm-up steps of a capture advance the recurrent state: save and restore it with the tokens
+        saved = [(l["conv_state"].clone(), l["ssm_state"].clone()) for l in self.layers if l["kind"] == "linear_attention"]
+        super().capture()
+        it = iter(saved)
+        for layer in self.layers:
+            if layer["kind"] == "linear_attention":
+                c, s = next(it)
+                layer["conv_state"].copy_(c); layer["ssm_state"].copy_(s)
+
+    def weight_bytes(self) -> int:
+        """Bytes of weights one token reads: every mixer, router and shared expert, top-k experts, the head."""
+        cfg, total = self.cfg, self.table_w.numel() * 2
+        for l in self.layers:
+            total += (l["w_in"].numel() + l["w_out"].numel() + l["w_router"].numel() + l["w_shared_in"].numel()
+                      + l["w_shared_out"].numel()) * 2
+            total += cfg.num_experts_per_tok * 3 * cfg.intermediate_size * cfg.hidden_size * 2
+        return total
+
+    def state_bytes(self) -> int:
+        n_m = sum(1 for l in self.layers if l["kind"] == "linear_attention")
+        c = self.cfg
+        return n_m * 2 * c.mamba_n_heads * c.mamba_d_head * c.mamba_d_state * 4
+
+    def kv_bytes_per_position(self) -> int:
+        c = self.cfg
+        return 2 * c.num_key_value_heads * c.head_dim * 2 * len(c.attention_layers)
+
+    def step(self) -> None:
+        lib.check(lib.load().tfb_granite_decode_step(C.byref(self.args), lib.stream()), "tfb_granite_decode_step")

@@ -15,7 +15,7 @@ import os
 
 LIB_PATH = Path(os.environ.get("TFB200_LIB") or Path(__file__).resolve().parent / "csrc" / "libtfb200.so")
 
-NORM_NONE, NORM_F32GAIN, NORM_CAST_THEN_GAIN = 0, 1, 2
+NORM_NONE, NORM_F32GAIN, NORM_CAST_THEN_GAIN, NORM_GATED = 0, 1, 2, 3
 EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU, EPI_STORE_F32 = 0, 1, 2, 3
 
 _vp, _i32, _i64, _u64, _f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_uint64, C.c_float
@@ -25,7 +25,7 @@ class GemvArgs(C.Structure):
     _fields_ = [("w", _vp), ("w2", _vp), ("x", _vp), ("gamma", _vp), ("residual", _vp), ("y", _vp),
                 ("n", _i32), ("k", _i32), ("prologue", _i32), ("epilogue", _i32),
                 ("eps", _f32), ("x_scale", _f32), ("res_scale", _f32), ("out_scale", _f32),
-                ("prefetch", _vp), ("prefetch_bytes", _u64), ("pdl", _i32), ("kernel", _i32), ("self_prefetch", _i32), ("reserved", _i32)]
+                ("prefetch", _vp), ("prefetch_bytes", _u64), ("pdl", _i32), ("kernel", _i32), ("self_prefetch", _i32), ("rows_per_expert", _i32), ("expert_idx", _vp), ("x_gate", _vp)]
 
 
 class LmHeadArgs(C.Structure):
@@ -91,6 +91,34 @@ class MiniCPM3StepArgs(C.Structure):
                 ("head_val", _vp), ("head_idx", _vp), ("hidden_trace", _vp), ("picked", _vp), ("pdl", _i32)]
 
 
+class MoeDownArgs(C.Structure):
+    _fields_ = [("w_down", _vp), ("w_shared", _vp), ("inner", _vp), ("shared_act", _vp), ("indices", _vp),
+                ("weights", _vp), ("shared_gate", _vp), ("residual", _vp), ("out", _vp),
+                ("hidden", _i32), ("inter", _i32), ("shared_inter", _i32), ("top_k", _i32),
+                ("res_scale", _f32), ("pdl", _i32)]
+
+
+class GraniteLayer(C.Structure):
+    _fields_ = [("kind", _i32), ("pad", _i32)] + [(n, _vp) for n in (
+        "gamma_in", "w_in", "conv_w", "conv_b", "a_log", "dt_bias", "d_skip", "gamma_ssm", "w_out", "conv_state",
+        "ssm_state", "k_pool", "v_pool", "gamma_post", "w_router", "w_gate", "w_up", "w_down", "w_shared_in",
+        "w_shared_out")]
+
+
+class GraniteStepArgs(C.Structure):
+    _fields_ = [("layers", C.POINTER(GraniteLayer)), ("n_layers", _i32), ("hidden", _i32),
+                ("nh", _i32), ("pd", _i32), ("ns", _i32), ("ng", _i32), ("conv_width", _i32),
+                ("hq", _i32), ("hkv", _i32), ("d", _i32),
+                ("experts", _i32), ("top_k", _i32), ("inter", _i32), ("shared_inter", _i32), ("vocab", _i64),
+                ("eps", _f32), ("attn_scale", _f32), ("embed_scale", _f32), ("res_scale", _f32), ("logits_scale", _f32),
+                ("table", _vp), ("gamma_final", _vp), ("page_size", _i32), ("table_len", _i32), ("max_ctx", _i32),
+                ("block_table", _vp), ("tokens", _vp), ("pos", _vp), ("n_prompt", _i32), ("max_tokens", _i32),
+                ("hidden_buf", _vp), ("proj_buf", _vp), ("mixed_buf", _vp), ("y_buf", _vp), ("router_logits", _vp),
+                ("router_idx", _vp), ("router_w", _vp), ("inner_buf", _vp), ("shared_buf", _vp), ("logits", _vp),
+                ("part_o", _vp), ("part_ml", _vp), ("counters", _vp), ("head_val", _vp), ("head_idx", _vp),
+                ("hidden_trace", _vp), ("idx_trace", _vp), ("picked", _vp), ("pdl", _i32)]
+
+
 #: every symbol ``include/tfb200.h`` declares: name -> (restype, argtypes)
 SYMBOLS = {
     "tfb_version": (_i32, []),
@@ -107,6 +135,12 @@ SYMBOLS = {
     "tfb_qwen3_decode_step": (_i32, [C.POINTER(Qwen3StepArgs), _vp]),
     "tfb_attn_mla_decode": (_i32, [C.POINTER(AttnMlaArgs), _vp]),
     "tfb_minicpm3_decode_step": (_i32, [C.POINTER(MiniCPM3StepArgs), _vp]),
+    "tfb_residual_add": (_i32, [_vp, _vp, _vp, _i32, _f32, _vp]),
+    "tfb_conv_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
+    "tfb_ssm_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "tfb_router_select": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
+    "tfb_moe_down": (_i32, [C.POINTER(MoeDownArgs), _vp]),
+    "tfb_granite_decode_step": (_i32, [C.POINTER(GraniteStepArgs), _vp]),
 }
 
 
@@ -164,13 +198,17 @@ def rmsnorm(x, gamma, out, eps, mode):
 
 
 def gemv(w, x, y, *, w2=None, gamma=None, residual=None, prologue=NORM_NONE, epilogue=EPI_STORE,
-         eps=0.0, x_scale=1.0, res_scale=1.0, out_scale=1.0, prefetch=None, pdl=False, kernel=0, self_prefetch=False):
-    n, k = w.shape
+         eps=0.0, x_scale=1.0, res_scale=1.0, out_scale=1.0, prefetch=None, pdl=False, kernel=0, self_prefetch=False, x_gate=None, expert_idx=None,
+         rows_per_expert=0):
+    n, k = w.shape[-2:]
+    if expert_idx is not None:
+        n = expert_idx.numel() * rows_per_expert
     a = GemvArgs(w=ptr(w), w2=ptr(w2), x=ptr(x), gamma=ptr(gamma), residual=ptr(residual), y=ptr(y),
                  n=n, k=k, prologue=prologue, epilogue=epilogue, eps=eps, x_scale=x_scale,
                  res_scale=res_scale, out_scale=out_scale,
                  prefetch=ptr(prefetch), prefetch_bytes=0 if prefetch is None else prefetch.numel() * prefetch.element_size(),
-                 pdl=int(pdl), kernel=kernel, self_prefetch=int(self_prefetch))
+                 pdl=int(pdl), kernel=kernel, self_prefetch=int(self_prefetch), rows_per_expert=rows_per_expert,
+                 expert_idx=ptr(expert_idx), x_gate=ptr(x_gate))
     check(load().tfb_gemv(C.byref(a), stream()), "tfb_gemv")
     return y
 
