@@ -197,6 +197,23 @@ typedef struct {
 TFB_API int32_t tfb_attn_splits(int32_t max_ctx);
 TFB_API int tfb_attn_gqa_decode(const tfb_attn_gqa_args* args, tfb_stream_t stream);
 
+/* The same attention with NO caller-provided scratch: a->part_o, a->part_ml and a->counters are
+ * ignored and the split partials live in a fixed array inside the library image instead.  This
+ * entry point has no counterpart in the reference.  It is for callers that cannot allocate device
+ * memory themselves: a compiled TileFoundry entry is handed exactly the tensors its ABI declares
+ * and nothing else, and a host that drives the step from inside a latency-critical loop cannot
+ * afford cudaMalloc's device-wide synchronisation.  It calls no cudaMalloc / cudaFree and no
+ * allocating library routine.
+ *   Limits: hq <= 64 query heads, max_ctx <= 4096 positions (64 splits), d <= 128; anything larger
+ * returns TFB_ECAPACITY with the reason in tfb_last_error.  The array (about 2.1 MB) is held by
+ * every GPU that loads the library until the process exits.
+ *   The first call on each device looks up the array's device address (one runtime query, no
+ * allocation); make that first call before starting any stream capture.
+ *   All calls on a device share the one array and it keeps the previous call's contents (the
+ * merge tickets are cleared on the stream at the start of every call): two calls whose kernels can
+ * overlap on the GPU -- different streams, or graph branches -- race on it.  Serialise them. */
+TFB_API int tfb_attn_gqa_decode_noalloc(const tfb_attn_gqa_args* args, tfb_stream_t stream);
+
 /* ---- a whole Qwen3-architecture decode step --------------------------------
  * embed -> layers x [norm+qkv, attention, o+residual, norm+gate/up+SwiGLU,
  * down+residual] -> final norm + lm_head + greedy pick + position advance, enqueued

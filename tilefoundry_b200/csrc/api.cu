@@ -216,6 +216,25 @@ int tfb_attn_gqa_decode(const tfb_attn_gqa_args* a, tfb_stream_t stream) {
     return done(tfb::attn_gqa_dispatch(p, S(stream), a->pdl != 0));
 }
 
+int tfb_attn_gqa_decode_noalloc(const tfb_attn_gqa_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->max_ctx > 0 && a->hq > 0, TFB_EINVAL);
+    tfb_attn_gqa_args b = *a;
+    bool fits = false;
+    const cudaError_t e = tfb::attn_static_scratch(a->hq, tfb::attn_splits(a->max_ctx), a->d, &b.part_o, &b.part_ml,
+                                                   &b.counters, &fits);
+    if (e != cudaSuccess) return fail_launch(e);
+    if (!fits) {
+        std::snprintf(g_last_error, sizeof g_last_error,
+                      "tfb_attn_gqa_decode_noalloc: %d heads x %d splits x %d dims exceeds the built-in scratch "
+                      "(64 heads, 64 splits = 4096 positions, 128 dims)", a->hq, tfb::attn_splits(a->max_ctx), a->d);
+        return TFB_ECAPACITY;
+    }
+    // the merge tickets must start at zero; everything else is written before it is read
+    const cudaError_t m = cudaMemsetAsync(b.counters, 0, size_t(a->hkv > 0 ? a->hkv : 1) * sizeof(uint32_t), S(stream));
+    if (m != cudaSuccess) return fail_launch(m);
+    return tfb_attn_gqa_decode(&b, stream);
+}
+
 int tfb_qwen3_decode_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->layers && a->n_layers > 0, TFB_EINVAL);
     TFB_REQUIRE(a->w_embed && a->gamma_final && a->w_head && a->tokens && a->pos, TFB_EINVAL);

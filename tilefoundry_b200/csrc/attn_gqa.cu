@@ -371,3 +371,42 @@ cudaError_t attn_gqa_dispatch(const AttnParams& p, cudaStream_t stream, bool pdl
 }
 
 }  // namespace tfb
+
+// ---- scratch that lives in the library image -----------------------------------------------------
+// Some callers may not call cudaMalloc at all (see tfb_attn_gqa_decode_noalloc in the header).  For
+// them the split-KV partials, their (max, sum) pairs and the merge tickets live in this file-scope
+// array: 64 query heads x 64 splits (4096 positions) x 128 dims of f32, about 2.1 MB that every GPU
+// which loads the library holds until the process exits.
+namespace tfb {
+
+constexpr int kStaticHeads = 64, kStaticSplits = 64, kStaticDim = 128;
+constexpr size_t kStaticPartO = size_t(kStaticHeads) * kStaticSplits * kStaticDim * sizeof(float);
+constexpr size_t kStaticPartMl = size_t(kStaticHeads) * kStaticSplits * 2 * sizeof(float);
+constexpr size_t kStaticCounters = 256;                       // 64 tickets, padded
+static __device__ __align__(256) unsigned char g_attn_scratch[kStaticPartO + kStaticPartMl + kStaticCounters];
+
+// In host code `g_attn_scratch` is only a handle for the runtime, not a device address, so the
+// address is asked for once per device (with that device current) and remembered.
+cudaError_t attn_static_scratch(int hq, int nsplit, int d, float** part_o, float** part_ml, unsigned** counters,
+                                bool* fits) {
+    *fits = hq <= kStaticHeads && nsplit <= kStaticSplits && d <= kStaticDim && hq > 0 && nsplit > 0 && d > 0;
+    if (!*fits) return cudaSuccess;
+    constexpr int kMaxDevices = 64;
+    static unsigned char* base[kMaxDevices] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (base[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_attn_scratch);
+        if (e != cudaSuccess) return e;
+        base[dev] = static_cast<unsigned char*>(p);
+    }
+    *part_o = reinterpret_cast<float*>(base[dev]);
+    *part_ml = reinterpret_cast<float*>(base[dev] + kStaticPartO);
+    *counters = reinterpret_cast<unsigned*>(base[dev] + kStaticPartO + kStaticPartMl);
+    return cudaSuccess;
+}
+
+}  // namespace tfb

@@ -63,6 +63,10 @@ struct AttnParams {
 };
 int attn_splits(int max_ctx);
 cudaError_t attn_gqa_dispatch(const AttnParams& p, cudaStream_t stream, bool pdl);
+// Scratch pointers inside the library's own static device array (no allocation); *fits = false when
+// the shape is beyond its fixed capacity.
+cudaError_t attn_static_scratch(int hq, int nsplit, int d, float** part_o, float** part_ml, unsigned** counters,
+                                bool* fits);
 
 struct HeadParams {
     const uint4* w;

@@ -132,6 +132,7 @@ SYMBOLS = {
     "tfb_lm_head_argmax": (_i32, [C.POINTER(LmHeadArgs), _vp]),
     "tfb_attn_splits": (_i32, [_i32]),
     "tfb_attn_gqa_decode": (_i32, [C.POINTER(AttnGqaArgs), _vp]),
+    "tfb_attn_gqa_decode_noalloc": (_i32, [C.POINTER(AttnGqaArgs), _vp]),
     "tfb_qwen3_decode_step": (_i32, [C.POINTER(Qwen3StepArgs), _vp]),
     "tfb_attn_mla_decode": (_i32, [C.POINTER(AttnMlaArgs), _vp]),
     "tfb_minicpm3_decode_step": (_i32, [C.POINTER(MiniCPM3StepArgs), _vp]),
