@@ -93,25 +93,41 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def time_kernel_gate_up(sess, reps=5):
-    """Average device time of the dominant kernel (gate/up projection + SwiGLU), launched
-    alone over every layer's weights in turn (28 x 50 MB > L2, so each launch streams from HBM)."""
+def time_kernel_gate_up(sess, reps=10):
+    """Average device time of the dominant kernel (gate/up projection + SwiGLU): one launch per layer's
+    weights (28 x 50 MB, far larger than L2, so every launch streams from HBM), recorded as a CUDA
+    graph so host launch cost does not limit it, launched the way the step launches it (programmatic
+    dependent launch), timed with CUDA events on the launching stream."""
     from tilefoundry_b200 import lib
 
     cfg = sess.cfg
-    stream = torch.cuda.current_stream()
-    times = []
-    for rep in range(reps + 1):
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record(stream)
+
+    def launches():
         for layer in sess.layers:
             lib.gemv(layer["w_gate"], sess.hidden, sess.act, w2=layer["w_up"], gamma=layer["gamma_post"],
-                     prologue=lib.NORM_CAST_THEN_GAIN, epilogue=lib.EPI_SWIGLU, eps=cfg.rms_norm_eps)
-        end.record(stream)
-        torch.cuda.synchronize()
-        if rep:
-            times.append(start.elapsed_time(end) / len(sess.layers))
-    return statistics.median(times)                      # ms per launch
+                     prologue=lib.NORM_CAST_THEN_GAIN, epilogue=lib.EPI_SWIGLU, eps=cfg.rms_norm_eps, pdl=True)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        launches()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        launches()
+    torch.cuda.synchronize()
+    for _ in range(3):
+        graph.replay()
+    stream = torch.cuda.current_stream()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record(stream)
+    for _ in range(reps):
+        graph.replay()
+    end.record(stream)
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / (reps * len(sess.layers))      # ms per launch
 
 
 def cpu_baseline(cfg, weights, prompt, steps, warm):

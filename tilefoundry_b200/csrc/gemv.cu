@@ -48,8 +48,8 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
     if (threadIdx.x == 0) l2_prefetch_slice(p.prefetch, p.prefetch_bytes, blockIdx.x, gridDim.x);
     constexpr int MAXC = 4;
     const bool fast_stage = (p.k >> 3) <= MAXC * WARPS * 32;
-    StagedGain<MAXC> sg;
-    if (fast_stage) sg.template preload<NORM_MODE>(p.gamma, p.k);
+    uint4* gs = reinterpret_cast<uint4*>(part + WARPS * ROWS * 2);     // parked norm gains
+    if (fast_stage) StagedGain<MAXC>::template preload<NORM_MODE>(p.gamma, gs, p.k);
 
     pdl_trigger();
     pdl_wait();
@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
     if (EPI == 1 && KSPLIT == 1 && lane < rows_valid) res_early = bf16_bits_to_f32(p.residual[row0 + lane]);
     if (EPI == 1 && KSPLIT > 1 && ks == 0 && lane < rows_valid) res_early = bf16_bits_to_f32(p.residual[row0 + lane]);
 
-    if (fast_stage) sg.template stage<NORM_MODE>(p.x, p.x2, xs, red, p.k, p.eps, p.x_scale);
+    if (fast_stage) StagedGain<MAXC>::template stage<NORM_MODE>(p.x, p.x2, gs, xs, red, p.k, p.eps, p.x_scale);
     else stage_activation<NORM_MODE>(p.x, p.gamma, xs, red, p.k, p.eps, p.x_scale);
     __syncthreads();
     trace_mark(p.trace, 0);
@@ -143,7 +143,8 @@ static cudaError_t launch_cfg(const GemvParams& p, cudaStream_t stream, bool pdl
     constexpr int NMAT = (EPI == 2) ? 2 : 1;
     const int rows_per_cta = GROUPS * ROWS;
     const unsigned grid = (p.n + rows_per_cta - 1) / rows_per_cta;
-    const size_t smem = (size_t(p.k) + 32 + GROUPS * KSPLIT * ROWS * NMAT) * sizeof(float);
+    // x (f32) + reduce scratch + K-split partials (padded to WARPS*ROWS*2) + parked gains (bf16)
+    const size_t smem = (size_t(p.k) + 32 + WARPS * ROWS * 2) * sizeof(float) + (NORM_MODE ? size_t(p.k) * 2 : 0);
     auto kern = gemv_kernel<ROWS, KSPLIT, WARPS, UNROLL, NORM_MODE, EPI>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));

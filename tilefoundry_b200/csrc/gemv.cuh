@@ -76,103 +76,84 @@ __device__ __forceinline__ void stage_activation(const uint16_t* __restrict__ x,
     }
 }
 
-// Same staging with the norm gains fetched ahead of time (they are weights, so they can be read
-// before the dependency wait) and x read from global memory exactly once: one memory round trip
-// between the wait and the first dot product instead of three.  Each thread owns up to MAXC
-// 8-element pieces; callers fall back to stage_activation when k/8 > MAXC * blockDim.x.
+// Same staging with one memory round trip between the dependency wait and the first dot product:
+// the norm gains (weights, so readable before the wait) are parked in shared memory ahead of time,
+// x is read from global memory exactly once, and normalisation happens in place in shared memory.
+// Nothing is held in registers across the wait, so the weight-load buffers keep the register budget.
+// Each thread owns up to MAXC 8-element pieces; callers fall back to stage_activation when
+// k/8 > MAXC * blockDim.x.  `gs` is k/8 uint4 of shared memory.
+// NORM_MODE 3 ("gated"): the vector normalised is f32(x) * silu(f32(gate)), kept in f32 through the
+// gain and rounded once -- granite's gated output norm (rms_norm(y * silu(gate)) * gamma).
 template <int MAXC>
 struct StagedGain {
-    uint4 g[MAXC];
     template <int NORM_MODE>
-    __device__ __forceinline__ void preload(const uint16_t* __restrict__ gamma, int k) {
+    static __device__ __forceinline__ void preload(const uint16_t* __restrict__ gamma, uint4* gs, int k) {
         if (NORM_MODE == 0) return;
 #pragma unroll
         for (int m = 0; m < MAXC; ++m) {
             const int c = threadIdx.x + m * blockDim.x;
-            g[m] = (c < (k >> 3)) ? *reinterpret_cast<const uint4*>(gamma + (c << 3)) : make_uint4(0, 0, 0, 0);
+            if (c < (k >> 3)) gs[c] = *reinterpret_cast<const uint4*>(gamma + (c << 3));
         }
     }
-    // NORM_MODE 3 ("gated"): the vector normalised is f32(x) * silu(f32(gate)), kept in f32 through the
-    // gain and rounded once -- granite's gated output norm (rms_norm(y * silu(gate)) * gamma).
     template <int NORM_MODE>
-    __device__ __forceinline__ void stage(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate,
-                                          float* xs, float* red, int k, float eps, float x_scale) {
-        if (NORM_MODE == 3) {
-            float f[MAXC][8];
-            float ss = 0.f;
-#pragma unroll
-            for (int m = 0; m < MAXC; ++m) {
-                const int c = threadIdx.x + m * blockDim.x;
-                if (c < (k >> 3)) {
-                    const uint4 xv = *reinterpret_cast<const uint4*>(x + (c << 3));
-                    const uint4 gv = *reinterpret_cast<const uint4*>(gate + (c << 3));
-                    const uint32_t u[4] = {xv.x, xv.y, xv.z, xv.w}, q[4] = {gv.x, gv.y, gv.z, gv.w};
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        f[m][2 * i] = bf16_lo(u[i]) * silu_f32(bf16_lo(q[i]));
-                        f[m][2 * i + 1] = bf16_hi(u[i]) * silu_f32(bf16_hi(q[i]));
-                        ss = fmaf(f[m][2 * i], f[m][2 * i], ss);
-                        ss = fmaf(f[m][2 * i + 1], f[m][2 * i + 1], ss);
-                    }
-                }
-            }
-            ss = block_sum(ss, red);
-            const float rstd = rsqrtf(ss / float(k) + eps);
-#pragma unroll
-            for (int m = 0; m < MAXC; ++m) {
-                const int c = threadIdx.x + m * blockDim.x;
-                if (c >= (k >> 3)) continue;
-                const uint32_t gg[4] = {g[m].x, g[m].y, g[m].z, g[m].w};
-                float o[8];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    o[2 * i] = round_bf16(f[m][2 * i] * rstd * bf16_lo(gg[i]));
-                    o[2 * i + 1] = round_bf16(f[m][2 * i + 1] * rstd * bf16_hi(gg[i]));
-                }
-                const int it = c >> 5, lane = c & 31;
-                float4* dst = reinterpret_cast<float4*>(xs);
-                dst[(it * 2) * 32 + lane] = make_float4(o[0], o[1], o[2], o[3]);
-                dst[(it * 2 + 1) * 32 + lane] = make_float4(o[4], o[5], o[6], o[7]);
-            }
-            return;
-        }
-        uint4 xv[MAXC];
+    static __device__ __forceinline__ void stage(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate,
+                                                 const uint4* gs, float* xs, float* red, int k, float eps,
+                                                 float x_scale) {
+        uint4 xv[MAXC], gv[NORM_MODE == 3 ? MAXC : 1];
 #pragma unroll
         for (int m = 0; m < MAXC; ++m) {
             const int c = threadIdx.x + m * blockDim.x;
             xv[m] = (c < (k >> 3)) ? *reinterpret_cast<const uint4*>(x + (c << 3)) : make_uint4(0, 0, 0, 0);
+            if (NORM_MODE == 3)
+                gv[m] = (c < (k >> 3)) ? *reinterpret_cast<const uint4*>(gate + (c << 3)) : make_uint4(0, 0, 0, 0);
         }
-        float rstd = 1.f;
-        if (NORM_MODE != 0) {
-            float ss = 0.f;
-#pragma unroll
-            for (int m = 0; m < MAXC; ++m) {
-                const uint32_t u[4] = {xv[m].x, xv[m].y, xv[m].z, xv[m].w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float a = bf16_lo(u[i]), b = bf16_hi(u[i]);
-                    ss = fmaf(a, a, ss);
-                    ss = fmaf(b, b, ss);
-                }
-            }
-            ss = block_sum(ss, red);
-            rstd = rsqrtf(ss / float(k) + eps);
-        }
+        float4* dst = reinterpret_cast<float4*>(xs);
+        float ss = 0.f;
 #pragma unroll
         for (int m = 0; m < MAXC; ++m) {
             const int c = threadIdx.x + m * blockDim.x;
             if (c >= (k >> 3)) continue;
             const uint32_t u[4] = {xv[m].x, xv[m].y, xv[m].z, xv[m].w};
-            const uint32_t gg[4] = {g[m].x, g[m].y, g[m].z, g[m].w};
             float f[8];
 #pragma unroll
+            for (int i = 0; i < 4; ++i) { f[2 * i] = bf16_lo(u[i]); f[2 * i + 1] = bf16_hi(u[i]); }
+            if (NORM_MODE == 3) {
+                const uint32_t q[4] = {gv[m].x, gv[m].y, gv[m].z, gv[m].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    f[2 * i] *= silu_f32(bf16_lo(q[i]));
+                    f[2 * i + 1] *= silu_f32(bf16_hi(q[i]));
+                }
+            }
+            if (NORM_MODE != 0) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) ss = fmaf(f[i], f[i], ss);
+            } else if (x_scale != 1.f) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] = round_bf16(apply_scale(f[i], x_scale));
+            }
+            const int it = c >> 5, lane = c & 31;
+            dst[(it * 2) * 32 + lane] = make_float4(f[0], f[1], f[2], f[3]);
+            dst[(it * 2 + 1) * 32 + lane] = make_float4(f[4], f[5], f[6], f[7]);
+        }
+        if (NORM_MODE == 0) return;
+        ss = block_sum(ss, red);
+        const float rstd = rsqrtf(ss / float(k) + eps);
+#pragma unroll
+        for (int m = 0; m < MAXC; ++m) {                 // each thread rescales the pieces it wrote itself
+            const int c = threadIdx.x + m * blockDim.x;
+            if (c >= (k >> 3)) continue;
+            const int it = c >> 5, lane = c & 31;
+            const float4 lo = dst[(it * 2) * 32 + lane], hi = dst[(it * 2 + 1) * 32 + lane];
+            float f[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+            const uint4 g = gs[c];
+            const uint32_t gg[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
             for (int i = 0; i < 4; ++i) {
-                f[2 * i] = bf16_lo(u[i]);
-                f[2 * i + 1] = bf16_hi(u[i]);
-                if (NORM_MODE == 2) {
+                if (NORM_MODE == 2) {                    // round, then gain (a bf16 multiply)
                     f[2 * i] = round_bf16(round_bf16(f[2 * i] * rstd) * bf16_lo(gg[i]));
                     f[2 * i + 1] = round_bf16(round_bf16(f[2 * i + 1] * rstd) * bf16_hi(gg[i]));
-                } else if (NORM_MODE == 1) {
+                } else {                                 // f32 through the gain, one rounding
                     f[2 * i] = round_bf16(f[2 * i] * rstd * bf16_lo(gg[i]));
                     f[2 * i + 1] = round_bf16(f[2 * i + 1] * rstd * bf16_hi(gg[i]));
                 }
@@ -181,8 +162,6 @@ struct StagedGain {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) f[i] = round_bf16(apply_scale(f[i], x_scale));
             }
-            const int it = c >> 5, lane = c & 31;
-            float4* dst = reinterpret_cast<float4*>(xs);
             dst[(it * 2) * 32 + lane] = make_float4(f[0], f[1], f[2], f[3]);
             dst[(it * 2 + 1) * 32 + lane] = make_float4(f[4], f[5], f[6], f[7]);
         }
