@@ -43,11 +43,77 @@ def peaks():
     return 6650.0, "fallback"
 
 
-def make_weights(cfg, seed=0):
-    from tilefoundry_b200.authored import qwen3_1_7b as q
-    from tilefoundry_b200.authored.weights import random_weights
+class Workload:
+    """One BASELINE.json configuration: how to build the authored Module, the session, the oracle."""
 
-    return q.tie_head(random_weights(q.build(cfg), seed=seed, std=0.02))
+    def __init__(self, key):
+        self.key = key
+        if key == "qwen3_1_7b":
+            from tilefoundry_b200.authored import qwen3_1_7b as a
+            from tilefoundry_b200.engine.qwen3 import Qwen3Session as S
+            self.authored, self.cfg, self.session_cls, self.overrides = a, a.QWEN3_1_7B, S, None
+            self.describe = ("Qwen3-1.7B architecture (28 layers, hidden 2048, 16q/8kv x128, SwiGLU 6144, vocab "
+                             "151936, tied head), batch 1, 64-token random prompt, greedy decode, paged bf16 KV "
+                             "cache (page 64)")
+            self.oracle_name, self.cpu_layers = "qwen3_1_7b", None
+        elif key == "minicpm3_4b":
+            from tilefoundry_b200.authored import minicpm3_4b as a
+            from tilefoundry_b200.engine.minicpm3 import MiniCPM3Session as S
+            self.authored, self.cfg, self.session_cls, self.overrides = a, a.MINICPM3_4B, S, None
+            self.describe = ("MiniCPM3-4B architecture (62 layers, hidden 2560, 40 heads, MLA q_lora 768 / kv_lora "
+                             "256, nope 64 + rope 32, v 64, SwiGLU 6400, vocab 73448), batch 1, 64-token random "
+                             "prompt, greedy decode, paged bf16 cache of assembled keys and values")
+            self.oracle_name, self.cpu_layers = "minicpm3_4b", 8
+        elif key == "granite_4_0_h_small":
+            from tilefoundry_b200.authored import granite_4_0_h_small as a
+            from tilefoundry_b200.engine.granite import GraniteSession as S
+            self.authored, self.cfg, self.session_cls, self.overrides = a, a.GRANITE_4_0_H_SMALL, S, a.weight_overrides
+            self.describe = ("granite-4.0-h-small architecture (36 Mamba-2 + 4 attention layers, hidden 4096, MoE 72 "
+                             "experts top-10 + shared expert, vocab 100352), batch 1, 64-token random prompt, greedy "
+                             "decode, f32 recurrent state in place, paged bf16 KV for the attention layers")
+            self.oracle_name, self.cpu_layers = "granite_4_0_h_small", 6
+        else:
+            raise SystemExit(f"unknown --config {key!r}")
+
+    def module(self, cfg=None):
+        return self.authored.build(self.cfg if cfg is None else cfg)
+
+    def host_weights(self, cfg=None, seed=0):
+        from tilefoundry_b200.authored.weights import random_weights
+
+        w = random_weights(self.module(cfg), seed=seed, std=0.02, overrides=self.overrides)
+        return self.authored.tie_head(w) if hasattr(self.authored, "tie_head") else w
+
+    def device_weights(self, dev, seed=0):
+        from tilefoundry_b200.authored.weights import random_weights_on
+
+        tied = hasattr(self.authored, "tie_head")
+        w = random_weights_on(self.module(), dev, seed=seed, std=0.02, overrides=self.overrides,
+                              skip=("w_head",) if tied else ())
+        if tied:
+            w["w_head"] = w["w_embed"].t()          # a view: the session recognises the tie and shares the table
+        return w
+
+    def oracle(self, cfg, weights):
+        import importlib
+
+        from oracle import evaluator
+        from tilefoundry_b200.runtime import DictResource
+
+        impl = importlib.import_module(f"oracle.{self.oracle_name}").make(cfg)
+        return evaluator.load(self.module(cfg), DictResource(weights), impl)
+
+    def truncated(self):
+        """The same architecture with fewer layers, for a CPU baseline that fits host memory and time."""
+        import dataclasses
+
+        if self.cpu_layers is None:
+            return self.cfg, 1.0
+        kw = {"num_hidden_layers": self.cpu_layers}
+        if self.key == "granite_4_0_h_small":
+            kw["attention_layers"] = (self.cpu_layers - 1,)
+        small = dataclasses.replace(self.cfg, **kw)
+        return small, self.cfg.num_hidden_layers / self.cpu_layers
 
 
 def prompt_ids(cfg, seed=0):
@@ -93,20 +159,9 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def time_kernel_gate_up(sess, reps=10):
-    """Average device time of the dominant kernel (gate/up projection + SwiGLU): one launch per layer's
-    weights (28 x 50 MB, far larger than L2, so every launch streams from HBM), recorded as a CUDA
-    graph so host launch cost does not limit it, launched the way the step launches it (programmatic
-    dependent launch), timed with CUDA events on the launching stream."""
-    from tilefoundry_b200 import lib
-
-    cfg = sess.cfg
-
-    def launches():
-        for layer in sess.layers:
-            lib.gemv(layer["w_gate"], sess.hidden, sess.act, w2=layer["w_up"], gamma=layer["gamma_post"],
-                     prologue=lib.NORM_CAST_THEN_GAIN, epilogue=lib.EPI_SWIGLU, eps=cfg.rms_norm_eps, pdl=True)
-
+def _graph_time(launches, n_launches, reps=10):
+    """ms per launch of *launches()* recorded as one CUDA graph (host launch cost excluded), CUDA events on
+    the launching stream."""
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
@@ -127,41 +182,74 @@ def time_kernel_gate_up(sess, reps=10):
         graph.replay()
     end.record(stream)
     torch.cuda.synchronize()
-    return start.elapsed_time(end) / (reps * len(sess.layers))      # ms per launch
+    return start.elapsed_time(end) / (reps * n_launches)
 
 
-def cpu_baseline(cfg, weights, prompt, steps, warm):
-    """The CPU oracle (a port of the reference evaluator's arithmetic) on the host cores."""
-    from oracle import evaluator, generation, qwen3_1_7b as oq
-    from tilefoundry_b200.authored import qwen3_1_7b as q
-    from tilefoundry_b200.runtime import DictResource
+#: dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from one ncu capture
+#: (profiles/gemv_kernel_gate_up_qwen3_1_7b.md); None where no capture was taken for that configuration.
+NCU_TRAFFIC = {"qwen3_1_7b": 50388736 + 7936}
+
+
+def dominant_kernel(work, sess):
+    """(name, ms per launch, algorithmic bytes per launch) of the projection that moves the most bytes per
+    layer, launched over every layer's weights in turn (far more than L2), the way the step launches it."""
+    from tilefoundry_b200 import lib
+
+    cfg = sess.cfg
+    if work.key in ("qwen3_1_7b", "minicpm3_4b"):
+        def launches():
+            for layer in sess.layers:
+                lib.gemv(layer["w_gate"], sess.hidden, sess.act, w2=layer["w_up"], gamma=layer["gamma_post"],
+                         prologue=lib.NORM_CAST_THEN_GAIN, epilogue=lib.EPI_SWIGLU, eps=cfg.rms_norm_eps, pdl=True)
+        nbytes = 2 * cfg.intermediate_size * cfg.hidden_size * 2
+        return ("gemv_kernel<SwiGLU> (post-attention norm + gate/up projection)",
+                _graph_time(launches, len(sess.layers)), nbytes)
+    mamba = [l for l in sess.layers if l["kind"] == "linear_attention"]
+
+    def launches():
+        for layer in mamba:
+            lib.gemv(layer["w_in"], sess.hidden, sess.proj, gamma=layer["gamma_in"], prologue=lib.NORM_F32GAIN,
+                     eps=cfg.rms_norm_eps, pdl=True)
+    return ("gemv_kernel<store> (input norm + Mamba-2 in_projection)", _graph_time(launches, len(mamba)),
+            cfg.proj * cfg.hidden_size * 2)
+
+
+def cpu_baseline(work, steps, warm, seed=0):
+    """The CPU oracle (a port of the reference evaluator's arithmetic) on all host cores.  Models too
+    large for a host run use a truncated layer stack and the time is scaled per layer (labelled)."""
+    from oracle import generation
 
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    ref = evaluator.load(q.build(cfg), DictResource(weights), oq.make(cfg))
-    run = generation.decode_ids(ref, prompt[:warm], steps)
-    return {"value": steps / run["seconds"], "unit": "tok/s", "cores": threads, "kind": "port",
-            "sample": f"{warm} prompt steps (untimed) then {steps} greedy decode steps of the same "
-                      f"model and seed, torch CPU bf16, {threads} threads"}, run
+    cfg, scale = work.truncated()
+    ref = work.oracle(cfg, work.host_weights(cfg, seed))
+    run = generation.decode_ids(ref, prompt_ids(cfg, 0)[:warm], steps)
+    per_token = run["seconds"] / steps
+    sample = (f"{warm} prompt steps (untimed) then {steps} greedy decode steps, same architecture and seed, "
+              f"torch CPU bf16, {threads} threads")
+    if scale != 1.0:
+        # head and embedding are not per-layer: time them once via a zero-layer estimate is not possible,
+        # so the whole truncated step is scaled, which over-counts the head slightly
+        sample += (f"; truncated to {cfg.num_hidden_layers} of {work.cfg.num_hidden_layers} layers and scaled "
+                   f"x{scale:.2f} per layer (extrapolated)")
+        per_token *= scale
+    return {"value": 1.0 / per_token, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample}
 
 
 def run_reference(args):
-    """Reference arm: the reference's own CPU implementation of the path.  The reference package
-    does not import here (isl/ortools missing), so this is the oracle port of its evaluator."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    """Reference arm: the reference's own CPU implementation of the path.  The reference package does not
+    import here (isl / ortools missing), so this is the oracle port of its evaluator."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    from tilefoundry_b200.authored import qwen3_1_7b as q
-
-    cfg = q.QWEN3_1_7B
+    work = Workload(args.config)
     steps = max(1, min(args.steps, 32))
     warm = max(1, min(args.warmup + 1, PROMPT_TOKENS))
-    base, _ = cpu_baseline(cfg, make_weights(cfg), prompt_ids(cfg), steps, warm)
+    base = cpu_baseline(work, steps, warm)
     line = {
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tok/s", "n_gpus": args.gpus,
         "steps": steps, "warmup": warm, "ms_per_step": 1e3 / base["value"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "Qwen3-1.7B architecture, batch 1, greedy decode on host cores",
+        "config": {"workload": work.describe + " -- on host cores",
                    "note": f"bounded sample: {steps} of the requested {args.steps} steps"},
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -173,8 +261,6 @@ def run_reference(args):
 def run_ours(args):
     import torch.distributed as dist
 
-    from tilefoundry_b200.authored import qwen3_1_7b as q
-    from tilefoundry_b200.engine.qwen3 import Qwen3Session
     from tilefoundry_b200.runtime import DictResource
 
     rank = int(os.environ.get("RANK", "0"))
@@ -185,12 +271,12 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device(f"cuda:{local}")
 
-    cfg = q.QWEN3_1_7B
+    work = Workload(args.config)
+    cfg = work.cfg
     K, W = args.steps, max(args.warmup, 3)
-    weights = make_weights(cfg, seed=0)                       # same model on every rank
     prompt = prompt_ids(cfg, seed=rank)                       # its own sequence per rank
     max_ctx = max(W + K + 8, PROMPT_TOKENS + 8)
-    sess = Qwen3Session(cfg, DictResource({k: v.to(dev) for k, v in weights.items()}), max_ctx=max_ctx, device=dev)
+    sess = work.session_cls(cfg, DictResource(work.device_weights(dev, seed=0)), max_ctx=max_ctx, device=dev)
     sess.reset(prompt)
     sess.capture()
 
@@ -252,34 +338,34 @@ def run_ours(args):
     peak, peak_kind = peaks()
     w_bytes = sess.weight_bytes()
     kv_pos = sess.kv_bytes_per_position()
-    # a step at position p reads the p cached positions and its weights, writes one position
-    step_bytes = [w_bytes + kv_pos * (W + i + 1) for i in range(K)]
+    state = sess.state_bytes() if hasattr(sess, "state_bytes") else 0
+    # a step at position p reads its weights, the p cached positions and the recurrent state, writes one
+    # position and the state back
+    step_bytes = [w_bytes + state + kv_pos * (W + i + 1) for i in range(K)]
     step_gbs = sum(step_bytes) / (ms * 1e-3) / 1e9
-    k_ms = time_kernel_gate_up(sess)
-    k_bytes = 2 * cfg.intermediate_size * cfg.hidden_size * 2
+    k_name, k_ms, k_bytes = dominant_kernel(work, sess)
     k_gbs = k_bytes / (k_ms * 1e-3) / 1e9
     roofline = {
-        "kernel": "gemv_kernel<SwiGLU> (post-attention norm + gate/up projection)", "bound": "hbm",
-        "achieved": k_gbs, "peak": peak, "peak_kind": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback",
-        "unit": "GB/s", "frac": k_gbs / peak, "traffic": None,
+        "kernel": k_name, "bound": "hbm", "achieved": k_gbs, "peak": peak,
+        "peak_kind": "measured (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback",
+        "unit": "GB/s", "frac": k_gbs / peak, "traffic": NCU_TRAFFIC.get(work.key),
         "algorithmic_bytes_per_launch": k_bytes, "us_per_launch": k_ms * 1e3,
-        "whole_step": {"achieved": step_gbs, "frac": step_gbs / peak,
-                       "bytes_per_token_mean": sum(step_bytes) / K, "frac_of_8TBs_nominal": step_gbs / 8000.0},
+        "whole_step": {"achieved": step_gbs, "frac": step_gbs / peak, "bytes_per_token_mean": sum(step_bytes) / K,
+                       "weights_bytes": w_bytes, "state_bytes": state, "kv_bytes_per_position": kv_pos,
+                       "frac_of_8TBs_nominal": step_gbs / 8000.0},
     }
 
     base = None
     if world == 1 and not args.no_cpu:
-        base, _ = cpu_baseline(cfg, weights, prompt, 32, PROMPT_TOKENS)
+        base = cpu_baseline(work, 32 if work.cpu_layers is None else 8, PROMPT_TOKENS if work.cpu_layers is None else 8)
 
     line = {
         "metric": METRIC, "value": world * K / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "Qwen3-1.7B architecture (28 layers, hidden 2048, 16q/8kv x128, SwiGLU 6144, "
-                               "vocab 151936, tied head), batch 1, 64-token random prompt, greedy decode, "
-                               "paged bf16 KV cache (page 64)",
-                   "timed_positions": [W, W + K], "parallelism": "replicas only" if world > 1 else "1 gpu",
-                   "l2": "inputs larger than L2: 3.44 GB of weights are streamed every step",
+        "config": {"workload": work.describe, "name": work.key, "timed_positions": [W, W + K],
+                   "parallelism": "replicas only" if world > 1 else "1 gpu",
+                   "l2": f"inputs larger than L2: {w_bytes / 1e9:.2f} GB of weights are streamed every step",
                    "first_tokens": tokens_out[:8]},
         "e2e": {"value": world * K / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 8,
                 "d2h_bytes_per_step": 8},
@@ -297,6 +383,9 @@ def main():
     ap.add_argument("--steps", type=int, default=2048)
     ap.add_argument("--warmup", type=int, default=PROMPT_TOKENS - 1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="qwen3_1_7b",
+                    choices=["qwen3_1_7b", "minicpm3_4b", "granite_4_0_h_small"],
+                    help="which BASELINE.json configuration to run (default: the one the metric is quoted on)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -32,3 +32,27 @@ def random_weights(module: Module, seed: int = 0, std: float = 0.02, *,
                 value = value + 1.0
         out[name] = value.to(to_torch_dtype(ty.dtype)).to(device)
     return out
+
+
+def random_weights_on(module: Module, device, seed: int = 0, std: float = 0.02, *, gain_prefix: str = "gamma",
+                      overrides=None, skip=()) -> dict[str, torch.Tensor]:
+    """Same distributions as ``random_weights`` but drawn directly on *device* (a 32B-parameter model
+    takes minutes to draw on the host).  The values differ from the host generator's: use it where only
+    the shapes and distributions matter (benchmarks), not where two sides must bind the same tensors."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+    cpu_gen = torch.Generator(device="cpu").manual_seed(seed)
+    out: dict[str, torch.Tensor] = {}
+    for name, ty in module.all_weights():
+        leaf = name.rsplit(".", 1)[-1]
+        if leaf in skip:
+            continue
+        value = overrides(name, ty, cpu_gen) if overrides is not None else None
+        if value is not None:
+            out[name] = value.to(to_torch_dtype(ty.dtype)).to(device)
+            continue
+        value = torch.randn(tuple(ty.shape), generator=gen, device=device, dtype=torch.float32) * std
+        if leaf.startswith(gain_prefix):
+            value += 1.0
+        out[name] = value.to(to_torch_dtype(ty.dtype))
+        del value
+    return out
