@@ -117,6 +117,8 @@ typedef struct {
     const int64_t* expert_idx; /* ... and slot s reads the rows of expert expert_idx[s] (device array) from w / w2,
                                   which then hold [experts][rows_per_expert][k]; NULL = plain projection */
     const void* x_gate;    /* [k] bf16 gate vector of TFB_NORM_GATED */
+    int32_t expert_rank;   /* expert parallel: with expert_world > 1, w / w2 hold only the experts e with */
+    int32_t expert_world;  /* e % expert_world == expert_rank, as local expert e / expert_world; other slots give 0 */
 } tfb_gemv_args;
 TFB_API int tfb_gemv(const tfb_gemv_args* args, tfb_stream_t stream);
 
@@ -150,6 +152,9 @@ typedef struct {
     int32_t max_tokens;
     int32_t kernel;         /* TFB_KERNEL_* */
     int32_t self_prefetch;  /* as in tfb_gemv_args */
+    int32_t index_offset;   /* vocabulary parallel: w is rows [index_offset, index_offset + n) of the head */
+    float* pair_out;        /* optional f32[2]: (best logit, global index) for an all-gather; suppresses the
+                               token / position update, which tfb_pick_finalize then does */
 } tfb_lm_head_args;
 TFB_API int32_t tfb_lm_head_scratch_entries(int32_t n);
 TFB_API int tfb_lm_head_argmax(const tfb_lm_head_args* args, tfb_stream_t stream);
@@ -401,8 +406,20 @@ typedef struct {
     int32_t hidden, inter, shared_inter, top_k;
     float res_scale;
     int32_t pdl;
+    int32_t expert_rank;      /* expert parallel, as in tfb_gemv_args */
+    int32_t expert_world;
+    float* partial;           /* optional f32 [2][hidden]: instead of `out`, this rank's un-rounded routed sum and
+                                 shared-expert dot, to be all-reduced and finished by tfb_moe_finalize */
 } tfb_moe_down_args;
 TFB_API int tfb_moe_down(const tfb_moe_down_args* args, tfb_stream_t stream);
+/* out = residual + bf16(res_scale * bf16(bf16(partial[0]) + bf16(partial[1]))): the roundings tfb_moe_down applies,
+ * after the ranks' partials were summed (NCCL all-reduce).  No reference counterpart (the reference is one GPU). */
+TFB_API int tfb_moe_finalize(const float* partial, const void* residual, void* out, int32_t hidden, float res_scale,
+                             int32_t has_shared, int32_t pdl, tfb_stream_t stream);
+/* Greedy pick over `world` gathered (logit, global index) pairs, lowest index on ties, then the token / position
+ * bookkeeping of tfb_lm_head_argmax.  No reference counterpart. */
+TFB_API int tfb_pick_finalize(const float* pairs, int32_t world, int64_t* tokens, int32_t* pos, int32_t n_prompt,
+                              int32_t max_tokens, int64_t* picked, int32_t pdl, tfb_stream_t stream);
 
 /* ---- a whole granite-4.0-h decode step ---------------------------------------------
  * embed*12 -> layers x [mixer (Mamba-2: in_proj, conv, ssm, gated norm + out_proj | attention:
@@ -468,8 +485,20 @@ typedef struct {
     int64_t* idx_trace;       /* optional [n_layers][top_k]: the routing indices of every layer */
     int64_t* picked;
     int32_t pdl;
+    /* expert / tensor / vocabulary parallel over ep_world GPUs (one process each).  Routed experts: expert e on
+     * rank e % ep_world; shared expert: column / row slices; head: vocabulary slices; mixers replicated.  The
+     * layer slabs then hold only this rank's shard.  The caller all-reduces `partial` between parts 1 and 2 of
+     * every layer and all-gathers `pair` into `gathered` between parts 3 and 4. */
+    int32_t ep_rank, ep_world;
+    float* partial;           /* f32 [2][hidden] */
+    float* pair;              /* f32 [2] */
+    float* gathered;          /* f32 [ep_world][2] */
 } tfb_granite_step_args;
 TFB_API int tfb_granite_decode_step(const tfb_granite_step_args* args, tfb_stream_t stream);
+/* One piece of the step, so a sharded caller can interleave its collectives: part 0 embed; 1 layer `layer` up to
+ * the MoE down stage; 2 finish layer `layer` from the summed partials; 3 final norm + head; 4 pick from the
+ * gathered pairs.  With ep_world <= 1 parts 0, 1.., 3 are the whole step (what tfb_granite_decode_step runs). */
+TFB_API int tfb_granite_step_part(const tfb_granite_step_args* args, int32_t part, int32_t layer, tfb_stream_t stream);
 
 #ifdef __cplusplus
 }

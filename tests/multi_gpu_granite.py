@@ -1,0 +1,58 @@
+"""Run under torchrun (one rank per GPU): the sharded granite session must produce the single-GPU session's
+tokens and logits.  Rank 0 prints `MULTI_GPU_OK` on success.  Used by tests/test_multi_gpu.py."""
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+
+from tilefoundry_b200.authored import granite_4_0_h_small as gr          # noqa: E402
+from tilefoundry_b200.authored.weights import random_weights            # noqa: E402
+from tilefoundry_b200.engine.granite import GraniteSession              # noqa: E402
+from tilefoundry_b200.runtime import DictResource                       # noqa: E402
+
+
+def main():
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device(f"cuda:{local}")
+    dist.init_process_group("nccl", device_id=dev)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    cfg = gr.GRANITE_TINY
+    weights = random_weights(gr.build(cfg), seed=11, std=0.05, overrides=gr.weight_overrides)
+    on_dev = {k: v.to(dev) for k, v in weights.items()}
+    prompt = torch.randint(0, cfg.vocab_size, (16,), generator=torch.Generator().manual_seed(3))
+    n_new = 70
+    single = GraniteSession(cfg, DictResource(on_dev), max_ctx=100, device=dev, keep_logits=True)
+    want = single.generate(prompt, n_new, use_graph=False).tokens
+    want_logits = single.logits.clone()
+    sharded = GraniteSession(cfg, DictResource(on_dev), max_ctx=100, device=dev, keep_logits=True, group=dist.group.WORLD)
+    for use_graph in (False, True):
+        got = sharded.generate(prompt, n_new, use_graph=use_graph).tokens
+        full = torch.zeros_like(sharded.logits)
+        per = cfg.vocab_size // world
+        full[rank * per:(rank + 1) * per] = sharded.logits[rank * per:(rank + 1) * per]
+        dist.all_reduce(full)
+        same = sum(a == b for a, b in zip(got, want))
+        err = float((full.float() - want_logits.float()).abs().max())
+        scale = float(want_logits.float().abs().max())
+        # tokens: identical unless an f32 summation-order difference flips a bf16 rounding on a near-tie
+        assert got[:8] == want[:8], (got[:8], want[:8])
+        assert same >= n_new - 2 or got == want, f"{same}/{n_new} tokens equal"
+        if got == want:
+            assert err <= 2e-2 + 2e-2 * scale, f"logits differ by {err} (scale {scale})"
+        picks = [torch.zeros(1, dtype=torch.int64, device=dev) for _ in range(world)]
+        dist.all_gather(picks, sharded.picked)
+        assert all(int(p) == int(picks[0]) for p in picks), "ranks disagree on the picked token"
+    dist.barrier()
+    if rank == 0:
+        print(f"MULTI_GPU_OK world={world} tokens_equal={same}/{n_new} logit_err={err:.4g}")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

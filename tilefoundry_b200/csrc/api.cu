@@ -110,6 +110,8 @@ int tfb::host::gemv_checked(const tfb_gemv_args* a, tfb_stream_t stream) {
     p.x2 = static_cast<const uint16_t*>(a->x_gate);
     p.expert_idx = reinterpret_cast<const long long*>(a->expert_idx);
     p.rows_per_expert = a->rows_per_expert;
+    p.expert_rank = a->expert_rank;
+    p.expert_world = a->expert_world;
     if (a->kernel == TFB_KERNEL_RING && tfb::gemv_stream_supported(a->n, a->k))
         return done(tfb::gemv_stream_dispatch(p, a->prologue, a->epilogue, S(stream), a->pdl != 0));
     return done(tfb::gemv_dispatch(p, a->prologue, a->epilogue, S(stream), a->pdl != 0));
@@ -126,12 +128,12 @@ int32_t tfb_lm_head_scratch_entries(int32_t n) {
 
 int tfb_lm_head_argmax(const tfb_lm_head_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->w && a->x && a->scratch_val && a->scratch_idx && a->counter, TFB_EINVAL);
-    TFB_REQUIRE(a->token_out || (a->tokens && a->pos), TFB_EINVAL);
+    TFB_REQUIRE(a->token_out || a->pair_out || (a->tokens && a->pos), TFB_EINVAL);
     TFB_REQUIRE(a->n > 0 && a->k > 0 && a->k % 256 == 0 && a->k <= 8192, TFB_EINVAL);
     TFB_REQUIRE(a->prologue >= TFB_NORM_NONE && a->prologue <= TFB_NORM_CAST_THEN_GAIN, TFB_EINVAL);
     TFB_REQUIRE(a->prologue == TFB_NORM_NONE || a->gamma, TFB_EINVAL);
     TFB_REQUIRE(aligned16(a->w) && aligned16(a->x) && (!a->gamma || aligned16(a->gamma)), TFB_EALIGN);
-    if (a->kernel == TFB_KERNEL_RING && tfb::gemv_stream_supported(a->n, a->k)) {
+    if (a->kernel == TFB_KERNEL_RING && !a->pair_out && tfb::gemv_stream_supported(a->n, a->k)) {
         tfb::GemvParams g = {};
         g.w = static_cast<const uint4*>(a->w);
         g.x = static_cast<const uint16_t*>(a->x);
@@ -163,6 +165,8 @@ int tfb_lm_head_argmax(const tfb_lm_head_args* a, tfb_stream_t stream) {
     p.n_prompt = a->n_prompt;
     p.max_tokens = a->max_tokens;
     p.trace = next_trace();
+    p.pair_out = a->pair_out;
+    p.index_offset = a->index_offset;
     return done(tfb::lm_head_dispatch(p, a->prologue, S(stream), a->pdl != 0));
 }
 

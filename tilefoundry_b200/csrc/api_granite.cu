@@ -68,28 +68,79 @@ int tfb_moe_down(const tfb_moe_down_args* a, tfb_stream_t stream) {
     p.shared_gate = a->shared_gate; p.residual = cu16(a->residual); p.out = static_cast<uint16_t*>(a->out);
     p.hidden = a->hidden; p.inter = a->inter; p.shared_inter = a->w_shared ? a->shared_inter : 0; p.top_k = a->top_k;
     p.res_scale = a->res_scale;
+    p.expert_rank = a->expert_rank; p.expert_world = a->expert_world; p.partial = a->partial;
+    TFB_REQUIRE(a->expert_world <= 1 || (a->expert_rank >= 0 && a->expert_rank < a->expert_world), TFB_EINVAL);
     return done(tfb::moe_down_launch(p, S(stream), a->pdl != 0));
 }
 
+int tfb_moe_finalize(const float* partial, const void* residual, void* out, int32_t hidden, float res_scale,
+                     int32_t has_shared, int32_t pdl, tfb_stream_t stream) {
+    TFB_REQUIRE(partial && out && hidden > 0, TFB_EINVAL);
+    return done(tfb::moe_finalize_launch(partial, cu16(residual), static_cast<uint16_t*>(out), hidden, res_scale,
+                                         has_shared != 0, S(stream), pdl != 0));
+}
+
+int tfb_pick_finalize(const float* pairs, int32_t world, int64_t* tokens, int32_t* pos, int32_t n_prompt,
+                      int32_t max_tokens, int64_t* picked, int32_t pdl, tfb_stream_t stream) {
+    TFB_REQUIRE(pairs && world > 0 && (picked || (tokens && pos)), TFB_EINVAL);
+    return done(tfb::pick_finalize_launch(pairs, world, reinterpret_cast<long long*>(tokens), pos, n_prompt, max_tokens,
+                                          reinterpret_cast<long long*>(picked), S(stream), pdl != 0));
+}
+
+static int granite_part(const tfb_granite_step_args* a, int part, int layer, tfb_stream_t stream);
+
+int tfb_granite_step_part(const tfb_granite_step_args* a, int32_t part, int32_t layer, tfb_stream_t stream) {
+    TFB_REQUIRE(a && part >= 0 && part <= 4, TFB_EINVAL);
+    TFB_REQUIRE((part != 1 && part != 2) || (layer >= 0 && layer < a->n_layers), TFB_EINVAL);
+    return granite_part(a, part, layer, stream);
+}
+
 int tfb_granite_decode_step(const tfb_granite_step_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->ep_world <= 1, TFB_EINVAL);        // sharded steps interleave collectives: use the parts
+    int rc = granite_part(a, 0, 0, stream);
+    for (int l = 0; !rc && l < a->n_layers; ++l) rc = granite_part(a, 1, l, stream);
+    return rc ? rc : granite_part(a, 3, 0, stream);
+}
+
+// part 0: embed.  part 1: layer `layer` up to and including the MoE down stage (complete on one GPU; on
+// several, it leaves this rank's un-rounded partial sums in a->partial for the caller to all-reduce).
+// part 2: finish layer `layer` from the summed partials.  part 3: final norm + head (one GPU: with the
+// greedy pick; several: this rank's vocabulary slice, leaving (logit, index) in a->pair for an all-gather).
+// part 4: pick from the gathered pairs.
+static int granite_part(const tfb_granite_step_args* a, int part, int layer, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->layers && a->n_layers > 0 && a->table && a->gamma_final && a->tokens && a->pos, TFB_EINVAL);
     TFB_REQUIRE(a->hidden_buf && a->proj_buf && a->mixed_buf && a->y_buf && a->router_logits && a->router_idx &&
                     a->router_w && a->inner_buf && a->shared_buf, TFB_EINVAL);
     TFB_REQUIRE(a->part_o && a->part_ml && a->counters && a->head_val && a->head_idx, TFB_EINVAL);
     TFB_REQUIRE(a->max_tokens <= a->max_ctx + 1, TFB_ECAPACITY);
+    const bool sharded = a->ep_world > 1;
+    TFB_REQUIRE(!sharded || (a->partial && a->pair && a->gathered && a->ep_rank >= 0 && a->ep_rank < a->ep_world), TFB_EINVAL);
     const bool pdl = a->pdl != 0;
     const int H = a->hidden, EXP = a->nh * a->pd, BC = a->ng * a->ns, CONVD = EXP + 2 * BC, PROJ = EXP + CONVD + a->nh;
     const int QP = a->hq * a->d, NQKV = (a->hq + 2 * a->hkv) * a->d;
-    const int E = a->experts, K = a->top_k, I = a->inter, IS = a->shared_inter;
+    const int E = a->experts, K = a->top_k, I = a->inter;
+    const int IS = sharded ? a->shared_inter / a->ep_world : a->shared_inter;   // this rank's slice of the shared expert
     cudaStream_t st = S(stream);
     uint16_t* hid = static_cast<uint16_t*>(a->hidden_buf);
     uint16_t* proj = static_cast<uint16_t*>(a->proj_buf);
     uint16_t* mixed = static_cast<uint16_t*>(a->mixed_buf);
     uint16_t* trace = static_cast<uint16_t*>(a->hidden_trace);
 
-    cudaError_t e = tfb::embed_launch(cu16(a->table), nullptr, reinterpret_cast<const long long*>(a->tokens), a->pos,
-                                      hid, 1, H, a->vocab, a->embed_scale, st, pdl);
-    if (e != cudaSuccess) return fail_launch(e);
+    cudaError_t e = cudaSuccess;
+    if (part == 0) {
+        e = tfb::embed_launch(cu16(a->table), nullptr, reinterpret_cast<const long long*>(a->tokens), a->pos, hid, 1, H,
+                              a->vocab, a->embed_scale, st, pdl);
+        return done(e);
+    }
+    if (part == 2) {
+        e = tfb::moe_finalize_launch(a->partial, hid, hid, H, a->res_scale, true, st, pdl);
+        if (e != cudaSuccess) return fail_launch(e);
+        if (trace) e = tfb::copy_launch(hid, trace + size_t(layer) * H, H * 2, st, pdl);
+        return done(e);
+    }
+    if (part == 4)
+        return done(tfb::pick_finalize_launch(a->gathered, a->ep_world, reinterpret_cast<long long*>(a->tokens), a->pos,
+                                              a->n_prompt, a->max_tokens, reinterpret_cast<long long*>(a->picked), st, pdl));
 
     auto base = [&](tfb_gemv_args& g) {
         std::memset(&g, 0, sizeof g);
@@ -97,7 +148,7 @@ int tfb_granite_decode_step(const tfb_granite_step_args* a, tfb_stream_t stream)
     };
     int rc;
     tfb_gemv_args g;
-    for (int l = 0; l < a->n_layers; ++l) {
+    for (int l = layer; part == 1 && l <= layer; ++l) {
         const tfb_granite_layer& L = a->layers[l];
         if (L.kind == 0) {
             // in_projection: gate | conv entry | dt
@@ -141,6 +192,7 @@ int tfb_granite_decode_step(const tfb_granite_step_args* a, tfb_stream_t stream)
         }
         base(g); g.w = L.w_gate; g.w2 = L.w_up; g.x = hid; g.gamma = L.gamma_post; g.y = a->inner_buf; g.n = K * I; g.k = H;
         g.prologue = TFB_NORM_F32GAIN; g.epilogue = TFB_EPI_SWIGLU; g.expert_idx = a->router_idx; g.rows_per_expert = I;
+        g.expert_rank = a->ep_rank; g.expert_world = a->ep_world;
         if ((rc = gemv_checked(&g, stream))) return rc;
         base(g); g.w = L.w_shared_in; g.w2 = cu16(L.w_shared_in) + size_t(IS) * H; g.x = hid; g.gamma = L.gamma_post;
         g.y = a->shared_buf; g.n = IS; g.k = H; g.prologue = TFB_NORM_F32GAIN; g.epilogue = TFB_EPI_SWIGLU;
@@ -150,12 +202,14 @@ int tfb_granite_decode_step(const tfb_granite_step_args* a, tfb_stream_t stream)
         d.w_down = L.w_down; d.w_shared = L.w_shared_out; d.inner = a->inner_buf; d.shared_act = a->shared_buf;
         d.indices = a->router_idx; d.weights = a->router_w; d.residual = hid; d.out = hid;
         d.hidden = H; d.inter = I; d.shared_inter = IS; d.top_k = K; d.res_scale = a->res_scale; d.pdl = pdl;
+        d.expert_rank = a->ep_rank; d.expert_world = a->ep_world; d.partial = sharded ? a->partial : nullptr;
         if ((rc = tfb_moe_down(&d, stream))) return rc;
-        if (trace) {
+        if (trace && !sharded) {
             e = tfb::copy_launch(hid, trace + size_t(l) * H, H * 2, st, pdl);
             if (e != cudaSuccess) return fail_launch(e);
         }
     }
+    if (part == 1) return TFB_OK;
     if (trace) {
         e = tfb::rmsnorm_launch(hid, cu16(a->gamma_final), trace + size_t(a->n_layers) * H, 1, H, a->eps,
                                 TFB_NORM_F32GAIN, st, pdl);
@@ -165,7 +219,13 @@ int tfb_granite_decode_step(const tfb_granite_step_args* a, tfb_stream_t stream)
     std::memset(&h, 0, sizeof h);
     h.w = a->table; h.x = hid; h.gamma = a->gamma_final; h.logits = a->logits;
     h.scratch_val = a->head_val; h.scratch_idx = a->head_idx; h.counter = a->counters + a->hkv;
-    h.n = int(a->vocab); h.k = H; h.prologue = TFB_NORM_F32GAIN; h.eps = a->eps;
+    const int vslice = sharded ? int(a->vocab / a->ep_world) : int(a->vocab);
+    if (sharded) {
+        h.w = cu16(a->table) + size_t(a->ep_rank) * vslice * H;
+        if (a->logits) h.logits = static_cast<uint16_t*>(a->logits) + size_t(a->ep_rank) * vslice;
+        h.pair_out = a->pair; h.index_offset = a->ep_rank * vslice;
+    }
+    h.n = vslice; h.k = H; h.prologue = TFB_NORM_F32GAIN; h.eps = a->eps;
     h.x_scale = 1.f; h.out_scale = a->logits_scale; h.pdl = pdl; h.token_out = a->picked;
     h.tokens = a->tokens; h.pos = a->pos; h.n_prompt = a->n_prompt; h.max_tokens = a->max_tokens;
     return tfb_lm_head_argmax(&h, stream);

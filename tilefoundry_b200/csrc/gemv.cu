@@ -55,13 +55,19 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
     pdl_wait();
     trace_waited(p.trace);
 
+    bool skip_rows = false;
     if (routed) {
         const int slot = max(row0, 0) / p.rows_per_expert, within = max(row0, 0) % p.rows_per_expert;
-        const size_t erow = size_t(p.expert_idx[min(slot, p.n / p.rows_per_expert - 1)]) * p.rows_per_expert + within;
+        long long e = p.expert_idx[min(slot, p.n / p.rows_per_expert - 1)];
+        if (p.expert_world > 1) {
+            if (e % p.expert_world != p.expert_rank) skip_rows = true;       // another rank owns this expert
+            e /= p.expert_world;
+        }
+        const size_t erow = size_t(e) * p.rows_per_expert + within;
         wrow = p.w + erow * row_stride;
         if (EPI == 2) w2row = p.w2 + erow * row_stride;
-        a.load(wrow, row_stride, rows_valid, it_begin, it_end, lane);
-        if (EPI == 2) b.load(w2row, row_stride, rows_valid, it_begin, it_end, lane);
+        a.load(wrow, row_stride, skip_rows ? 0 : rows_valid, it_begin, it_end, lane);
+        if (EPI == 2) b.load(w2row, row_stride, skip_rows ? 0 : rows_valid, it_begin, it_end, lane);
     }
     // the residual is needed last but its load is issued first: one round trip less at the end
     float res_early = 0.f;
@@ -81,8 +87,8 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
         a.fma(xs, it0, it_end, lane, acc);
         if (EPI == 2) b.fma(xs, it0, it_end, lane, acc2);
         if (it0 + UNROLL < it_end) {
-            a.load(wrow, row_stride, rows_valid, it0 + UNROLL, it_end, lane);
-            if (EPI == 2) b.load(w2row, row_stride, rows_valid, it0 + UNROLL, it_end, lane);
+            a.load(wrow, row_stride, skip_rows ? 0 : rows_valid, it0 + UNROLL, it_end, lane);
+            if (EPI == 2) b.load(w2row, row_stride, skip_rows ? 0 : rows_valid, it0 + UNROLL, it_end, lane);
         }
     }
 

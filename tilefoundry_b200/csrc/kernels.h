@@ -20,6 +20,7 @@ struct GemvParams {
     const uint16_t* x2;              // gate vector of the gated-norm prologue (mode 3)
     const long long* expert_idx;     // expert mode: expert of each slot of rows_per_expert output rows
     int rows_per_expert;
+    int expert_rank, expert_world;   // expert e lives on rank e % world as local expert e / world (world <= 1: all local)
     // streaming kernel only
     int kc, nstages, self_prefetch;
     unsigned* status;
@@ -83,6 +84,8 @@ struct HeadParams {
     int* pos;
     int n_prompt, max_tokens;
     unsigned long long* trace;
+    float* pair_out;            // optional f32[2]: (best logit, index + index_offset) instead of the token update
+    int index_offset;
 };
 int lm_head_ctas(int n);
 cudaError_t lm_head_dispatch(const HeadParams& p, int norm_mode, cudaStream_t stream, bool pdl);
@@ -93,6 +96,10 @@ cudaError_t embed_launch(const uint16_t* table, const long long* ids, const long
 cudaError_t rmsnorm_launch(const uint16_t* x, const uint16_t* gamma, uint16_t* y, int rows, int width,
                            float eps, int mode, cudaStream_t stream, bool pdl);
 cudaError_t copy_launch(const void* src, void* dst, int bytes, cudaStream_t stream, bool pdl);
+cudaError_t moe_finalize_launch(const float* partial, const uint16_t* residual, uint16_t* out, int hidden,
+                                float res_scale, bool has_shared, cudaStream_t stream, bool pdl);
+cudaError_t pick_finalize_launch(const float* pairs, int world, long long* tokens, int* pos, int n_prompt,
+                                 int max_tokens, long long* picked, cudaStream_t stream, bool pdl);
 cudaError_t residual_add_launch(const uint16_t* a, const uint16_t* b, uint16_t* out, int n, float scale,
                                 cudaStream_t stream, bool pdl);
 
@@ -170,6 +177,8 @@ struct MoeDownParams {
     uint16_t* out;              // [hidden]
     int hidden, inter, shared_inter, top_k;
     float res_scale;
+    int expert_rank, expert_world;
+    float* partial;             // optional f32 [2][hidden]: un-rounded routed sum and shared dot of this rank
 };
 cudaError_t moe_down_launch(const MoeDownParams& p, cudaStream_t stream, bool pdl);
 

@@ -175,8 +175,12 @@ __global__ void __launch_bounds__(kHeadWarps * 32) lm_head_kernel(const HeadPara
     __syncthreads();
     if (threadIdx.x == 0) {
         for (int w = 1; w < kHeadWarps; ++w) argmax_merge(best, best_i, wv[w], wi[w]);
-        if (p.token_out) *p.token_out = best_i;
-        if (p.tokens && p.pos) {
+        if (p.pair_out) {                       // vocabulary-parallel: hand (logit, global index) to the gather
+            p.pair_out[0] = best;
+            p.pair_out[1] = float(best_i + p.index_offset);
+        }
+        if (p.token_out) *p.token_out = best_i + p.index_offset;
+        if (!p.pair_out && p.tokens && p.pos) {
             const int cur = *p.pos;
             if (cur + 1 < p.max_tokens) {
                 if (cur + 1 >= p.n_prompt) p.tokens[cur + 1] = best_i;

@@ -115,7 +115,12 @@ __global__ void __launch_bounds__(kDownWarps * 32) moe_down_kernel(const MoeDown
     float routed = 0.f;
     const int pieces = I >> 3;
     for (int s = 0; s < K; ++s) {
-        const uint4* row = p.w_down + (size_t(s_idx[s]) * p.hidden + j) * pieces;
+        long long e = s_idx[s];
+        if (p.expert_world > 1) {                              // expert parallel: only this rank's experts are here
+            if (e % p.expert_world != p.expert_rank) continue;
+            e /= p.expert_world;
+        }
+        const uint4* row = p.w_down + (size_t(e) * p.hidden + j) * pieces;
         const float* x = xin + s * I;
         float acc = 0.f;
         for (int c = lane; c < pieces; c += 32) {
@@ -127,6 +132,7 @@ __global__ void __launch_bounds__(kDownWarps * 32) moe_down_kernel(const MoeDown
         routed += round_bf16(round_bf16(acc) * s_w[s]);        // bf16 products, f32 running sum
     }
     float out = round_bf16(routed);                            // the reduce over slots returns bf16
+    float sh_raw = 0.f;
     if (shrow) {
         const float* x = xin + K * I;
         float acc = 0.f;
@@ -143,14 +149,68 @@ __global__ void __launch_bounds__(kDownWarps * 32) moe_down_kernel(const MoeDown
             const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
             acc = dot8(w, xa, xb, acc);
         }
-        float sh = round_bf16(warp_sum(acc));
+        sh_raw = warp_sum(acc);
+        float sh = round_bf16(sh_raw);
         if (p.shared_gate) sh = round_bf16(sh * *p.shared_gate);  // Qwen3.5: sigmoid gate on the shared expert
         out = round_bf16(out + sh);
     }
     if (lane == 0) {
+        if (p.partial) {                                         // sharded: the ranks' sums are added before any rounding
+            p.partial[j] = routed;
+            p.partial[p.hidden + j] = sh_raw;
+            return;
+        }
         if (p.residual) out = res + round_bf16(out * p.res_scale);
         p.out[j] = f32_to_bf16_bits(out);
     }
+}
+
+// After the ranks' partials were summed: the roundings of routed_experts / experts / residual_add.
+__global__ void moe_finalize_kernel(const float* __restrict__ partial, const uint16_t* __restrict__ residual,
+                                    uint16_t* __restrict__ out, int hidden, float res_scale, int has_shared) {
+    pdl_trigger();
+    pdl_wait();
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= hidden) return;
+    float v = round_bf16(partial[j]);
+    if (has_shared) v = round_bf16(v + round_bf16(partial[hidden + j]));
+    if (residual) v = bf16_bits_to_f32(residual[j]) + round_bf16(v * res_scale);
+    out[j] = f32_to_bf16_bits(v);
+}
+cudaError_t moe_finalize_launch(const float* partial, const uint16_t* residual, uint16_t* out, int hidden,
+                                float res_scale, bool has_shared, cudaStream_t stream, bool pdl) {
+    return launch_kernel(moe_finalize_kernel, dim3((hidden + 255) / 256), dim3(256), 0, stream, pdl, partial, residual,
+                         out, hidden, res_scale, int(has_shared));
+}
+
+// Vocabulary-parallel greedy pick: every rank contributed (best logit, global index); highest logit wins,
+// equal logits resolve to the lower index (torch.argmax over the whole vocabulary), then the generation
+// bookkeeping of the single-GPU head kernel.
+__global__ void pick_finalize_kernel(const float* __restrict__ pairs, int world, long long* tokens, int* pos,
+                                     int n_prompt, int max_tokens, long long* picked) {
+    pdl_trigger();
+    pdl_wait();
+    if (threadIdx.x != 0) return;
+    float best = -INFINITY;
+    long long best_i = 0x7fffffff;
+    for (int r = 0; r < world; ++r) {
+        const float v = pairs[2 * r];
+        const long long i = (long long)pairs[2 * r + 1];
+        if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+    }
+    if (picked) *picked = best_i;
+    if (tokens && pos) {
+        const int cur = *pos;
+        if (cur + 1 < max_tokens) {
+            if (cur + 1 >= n_prompt) tokens[cur + 1] = best_i;
+            *pos = cur + 1;
+        }
+    }
+}
+cudaError_t pick_finalize_launch(const float* pairs, int world, long long* tokens, int* pos, int n_prompt,
+                                 int max_tokens, long long* picked, cudaStream_t stream, bool pdl) {
+    return launch_kernel(pick_finalize_kernel, dim3(1), dim3(32), 0, stream, pdl, pairs, world, tokens, pos, n_prompt,
+                         max_tokens, picked);
 }
 
 cudaError_t moe_down_launch(const MoeDownParams& p, cudaStream_t stream, bool pdl) {

@@ -9,7 +9,7 @@ import torch
 
 from .. import lib
 from ..authored.granite_4_0_h_small import GraniteConfig
-from . import paged_kv
+from . import paged_kv, sharding
 from .session import DecodeSession
 
 MAMBA_W = ("gamma_in", "w_in", "conv_w", "conv_b", "a_log", "dt_bias", "d_skip", "gamma_ssm", "w_out")
@@ -26,9 +26,17 @@ def pack_mixer(kind: str, w: dict) -> dict:
 
 class GraniteSession(DecodeSession):
     def __init__(self, cfg: GraniteConfig, resource, *, max_ctx: int = 2176, device="cuda:0",
-                 keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True):
+                 keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True, group=None):
+        """*group*: a ``torch.distributed`` process group (NCCL) to shard the MoE blocks and the head over;
+        ``None`` runs everything on this GPU."""
         if not torch.cuda.is_available():
             raise RuntimeError("GraniteSession needs a CUDA device; there is no CPU path")
+        self.group = group
+        if group is not None:
+            import torch.distributed as dist
+            self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        else:
+            self.rank, self.world = 0, 1
         lib.load()
         self.cfg, self.device, self.max_ctx = cfg, torch.device(device), int(max_ctx)
         dev = self.device
@@ -47,7 +55,14 @@ class GraniteSession(DecodeSession):
             mix, moe = sub.subtree("mixer"), sub.subtree("moe")
             names = MAMBA_W if kind == "linear_attention" else ATTN_W
             layer = pack_mixer(kind, {n: to(mix.load(n)) for n in names})
-            layer.update({n: to(moe.load(n)).contiguous() for n in MOE_W})
+            if self.world == 1:
+                layer.update({n: to(moe.load(n)).contiguous() for n in MOE_W})
+            else:                                     # keep only this rank's shard on the device
+                layer["gamma_post"] = to(moe.load("gamma_post")).contiguous()
+                for n in ("w_gate", "w_up", "w_down"):
+                    layer[n] = to(sharding.local_experts(moe.load(n), self.rank, self.world))
+                w_in, w_out = sharding.shared_slices(moe.load("w_shared_in"), moe.load("w_shared_out"), self.rank, self.world)
+                layer["w_shared_in"], layer["w_shared_out"] = to(w_in), to(w_out)
             layer["w_router"] = to(moe.subtree("router").load("w_router")).contiguous()
             layer["kind"] = kind
             if kind == "linear_attention":
@@ -75,6 +90,9 @@ class GraniteSession(DecodeSession):
         self.trace = z(L + 1, H) if trace_hidden else None
         self.idx_trace = z(L, K, dtype=torch.int64) if trace_hidden else None
         self.picked = z(1, dtype=torch.int64)
+        self.partial, self.pair, self.gathered = z(2, H, dtype=f32), z(2, dtype=f32), z(self.world, 2, dtype=f32)
+        if self.world > 1:
+            sharding.vocab_slice(V, self.rank, self.world)          # validates divisibility
 
         self._layer_structs = (lib.GraniteLayer * L)()
         for s, layer in zip(self._layer_structs, self.layers):
@@ -97,7 +115,8 @@ class GraniteSession(DecodeSession):
             logits=lib.ptr(self.logits), part_o=lib.ptr(self.part_o), part_ml=lib.ptr(self.part_ml),
             counters=lib.ptr(self.counters), head_val=lib.ptr(self.head_val), head_idx=lib.ptr(self.head_idx),
             hidden_trace=lib.ptr(self.trace), idx_trace=lib.ptr(self.idx_trace), picked=lib.ptr(self.picked),
-            pdl=int(pdl))
+            pdl=int(pdl), ep_rank=self.rank, ep_world=self.world, partial=lib.ptr(self.partial),
+            pair=lib.ptr(self.pair), gathered=lib.ptr(self.gathered))
         n_m = sum(1 for l in self.layers if l["kind"] == "linear_attention")
         self.launches_per_step = 2 + 9 * n_m + 8 * (L - n_m) + (2 * L + 1 if trace_hidden else 0)
 
@@ -137,4 +156,17 @@ class GraniteSession(DecodeSession):
         return 2 * c.num_key_value_heads * c.head_dim * 2 * len(c.attention_layers)
 
     def step(self) -> None:
-        lib.check(lib.load().tfb_granite_decode_step(C.byref(self.args), lib.stream()), "tfb_granite_decode_step")
+        if self.world == 1:
+            lib.check(lib.load().tfb_granite_decode_step(C.byref(self.args), lib.stream()), "tfb_granite_decode_step")
+            return
+        import torch.distributed as dist
+        part = lambda p, l=0: lib.check(lib.load().tfb_granite_step_part(C.byref(self.args), p, l, lib.stream()),
+                                        "tfb_granite_step_part")
+        part(0)
+        for l in range(len(self.layers)):
+            part(1, l)
+            dist.all_reduce(self.partial, group=self.group)          # one reduction per MoE block
+            part(2, l)
+        part(3)
+        dist.all_gather_into_tensor(self.gathered, self.pair, group=self.group)
+        part(4)

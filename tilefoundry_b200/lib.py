@@ -25,7 +25,7 @@ class GemvArgs(C.Structure):
     _fields_ = [("w", _vp), ("w2", _vp), ("x", _vp), ("gamma", _vp), ("residual", _vp), ("y", _vp),
                 ("n", _i32), ("k", _i32), ("prologue", _i32), ("epilogue", _i32),
                 ("eps", _f32), ("x_scale", _f32), ("res_scale", _f32), ("out_scale", _f32),
-                ("prefetch", _vp), ("prefetch_bytes", _u64), ("pdl", _i32), ("kernel", _i32), ("self_prefetch", _i32), ("rows_per_expert", _i32), ("expert_idx", _vp), ("x_gate", _vp)]
+                ("prefetch", _vp), ("prefetch_bytes", _u64), ("pdl", _i32), ("kernel", _i32), ("self_prefetch", _i32), ("rows_per_expert", _i32), ("expert_idx", _vp), ("x_gate", _vp), ("expert_rank", _i32), ("expert_world", _i32)]
 
 
 class LmHeadArgs(C.Structure):
@@ -33,7 +33,7 @@ class LmHeadArgs(C.Structure):
                 ("scratch_val", _vp), ("scratch_idx", _vp), ("counter", _vp),
                 ("n", _i32), ("k", _i32), ("prologue", _i32),
                 ("eps", _f32), ("x_scale", _f32), ("out_scale", _f32), ("pdl", _i32),
-                ("tokens", _vp), ("pos", _vp), ("n_prompt", _i32), ("max_tokens", _i32), ("kernel", _i32), ("self_prefetch", _i32)]
+                ("tokens", _vp), ("pos", _vp), ("n_prompt", _i32), ("max_tokens", _i32), ("kernel", _i32), ("self_prefetch", _i32), ("index_offset", _i32), ("pair_out", _vp)]
 
 
 class AttnGqaArgs(C.Structure):
@@ -95,7 +95,7 @@ class MoeDownArgs(C.Structure):
     _fields_ = [("w_down", _vp), ("w_shared", _vp), ("inner", _vp), ("shared_act", _vp), ("indices", _vp),
                 ("weights", _vp), ("shared_gate", _vp), ("residual", _vp), ("out", _vp),
                 ("hidden", _i32), ("inter", _i32), ("shared_inter", _i32), ("top_k", _i32),
-                ("res_scale", _f32), ("pdl", _i32)]
+                ("res_scale", _f32), ("pdl", _i32), ("expert_rank", _i32), ("expert_world", _i32), ("partial", _vp)]
 
 
 class GraniteLayer(C.Structure):
@@ -116,7 +116,8 @@ class GraniteStepArgs(C.Structure):
                 ("hidden_buf", _vp), ("proj_buf", _vp), ("mixed_buf", _vp), ("y_buf", _vp), ("router_logits", _vp),
                 ("router_idx", _vp), ("router_w", _vp), ("inner_buf", _vp), ("shared_buf", _vp), ("logits", _vp),
                 ("part_o", _vp), ("part_ml", _vp), ("counters", _vp), ("head_val", _vp), ("head_idx", _vp),
-                ("hidden_trace", _vp), ("idx_trace", _vp), ("picked", _vp), ("pdl", _i32)]
+                ("hidden_trace", _vp), ("idx_trace", _vp), ("picked", _vp), ("pdl", _i32),
+                ("ep_rank", _i32), ("ep_world", _i32), ("partial", _vp), ("pair", _vp), ("gathered", _vp)]
 
 
 #: every symbol ``include/tfb200.h`` declares: name -> (restype, argtypes)
@@ -142,6 +143,9 @@ SYMBOLS = {
     "tfb_router_select": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "tfb_moe_down": (_i32, [C.POINTER(MoeDownArgs), _vp]),
     "tfb_granite_decode_step": (_i32, [C.POINTER(GraniteStepArgs), _vp]),
+    "tfb_granite_step_part": (_i32, [C.POINTER(GraniteStepArgs), _i32, _i32, _vp]),
+    "tfb_moe_finalize": (_i32, [_vp, _vp, _vp, _i32, _f32, _i32, _i32, _vp]),
+    "tfb_pick_finalize": (_i32, [_vp, _i32, _vp, _vp, _i32, _i32, _vp, _i32, _vp]),
 }
 
 
