@@ -15,6 +15,10 @@ from tilefoundry_b200.engine.granite import GraniteSession              # noqa: 
 from tilefoundry_b200.runtime import DictResource                       # noqa: E402
 
 
+def say(*a):
+    print(f"[rank {os.environ.get('RANK', '?')}]", *a, file=sys.stderr, flush=True)
+
+
 def main():
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -22,6 +26,10 @@ def main():
     dev = torch.device(f"cuda:{local}")
     dist.init_process_group("nccl", device_id=dev)
     rank, world = dist.get_rank(), dist.get_world_size()
+    probe = torch.ones(4, device=dev)
+    dist.all_reduce(probe)
+    torch.cuda.synchronize()
+    say("nccl up", probe.tolist())
     cfg = gr.GRANITE_TINY
     weights = random_weights(gr.build(cfg), seed=11, std=0.05, overrides=gr.weight_overrides)
     on_dev = {k: v.to(dev) for k, v in weights.items()}
@@ -30,9 +38,12 @@ def main():
     single = GraniteSession(cfg, DictResource(on_dev), max_ctx=100, device=dev, keep_logits=True)
     want = single.generate(prompt, n_new, use_graph=False).tokens
     want_logits = single.logits.clone()
+    say("single-GPU reference done")
     sharded = GraniteSession(cfg, DictResource(on_dev), max_ctx=100, device=dev, keep_logits=True, group=dist.group.WORLD)
     for use_graph in (False, True):
+        say("sharded generate, graph =", use_graph)
         got = sharded.generate(prompt, n_new, use_graph=use_graph).tokens
+        say("done")
         full = torch.zeros_like(sharded.logits)
         per = cfg.vocab_size // world
         full[rank * per:(rank + 1) * per] = sharded.logits[rank * per:(rank + 1) * per]
@@ -48,10 +59,14 @@ def main():
         picks = [torch.zeros(1, dtype=torch.int64, device=dev) for _ in range(world)]
         dist.all_gather(picks, sharded.picked)
         assert all(int(p) == int(picks[0]) for p in picks), "ranks disagree on the picked token"
+    torch.cuda.synchronize()
     dist.barrier()
     if rank == 0:
-        print(f"MULTI_GPU_OK world={world} tokens_equal={same}/{n_new} logit_err={err:.4g}")
-    dist.destroy_process_group()
+        print(f"MULTI_GPU_OK world={world} tokens_equal={same}/{n_new} logit_err={err:.4g}", flush=True)
+    # Tearing the process group down while captured graphs still hold its collectives did not return on
+    # the 2-GPU box; the work is done and synchronised, so leave without the teardown.
+    sys.stdout.flush()
+    os._exit(0)
 
 
 if __name__ == "__main__":

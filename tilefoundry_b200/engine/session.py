@@ -59,7 +59,8 @@ class DecodeSession:
         torch.cuda.synchronize()
         self.tokens.copy_(saved[0]); self.pos.copy_(saved[1])
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        # thread-local capture mode: a process group's watchdog thread may query CUDA events meanwhile
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
             self.step()
         torch.cuda.synchronize()
         self.tokens.copy_(saved[0]); self.pos.copy_(saved[1])
