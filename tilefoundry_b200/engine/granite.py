@@ -118,7 +118,8 @@ class GraniteSession(DecodeSession):
             pdl=int(pdl), ep_rank=self.rank, ep_world=self.world, partial=lib.ptr(self.partial),
             pair=lib.ptr(self.pair), gathered=lib.ptr(self.gathered))
         n_m = sum(1 for l in self.layers if l["kind"] == "linear_attention")
-        self.launches_per_step = 2 + 9 * n_m + 8 * (L - n_m) + (2 * L + 1 if trace_hidden else 0)
+        self.launches_per_step = 2 + 9 * n_m + 8 * (L - n_m) + (2 * L + 1 if trace_hidden else 0) + (
+            L + 1 if self.world > 1 else 0)              # sharded: one finalize per layer and the final pick
 
     def reset(self, prompt_ids) -> None:
         super().reset(prompt_ids)
@@ -143,7 +144,9 @@ class GraniteSession(DecodeSession):
         for l in self.layers:
             total += (l["w_in"].numel() + l["w_out"].numel() + l["w_router"].numel() + l["w_shared_in"].numel()
                       + l["w_shared_out"].numel()) * 2
-            total += cfg.num_experts_per_tok * 3 * cfg.intermediate_size * cfg.hidden_size * 2
+            total += cfg.num_experts_per_tok * 3 * cfg.intermediate_size * cfg.hidden_size * 2 // self.world
+        if self.world > 1:                           # the head is sliced too; the table is read for one row
+            total -= self.table_w.numel() * 2 * (self.world - 1) // self.world
         return total
 
     def state_bytes(self) -> int:
