@@ -95,3 +95,60 @@ def test_minicpm3_layer_matches_reference_ops_vectors(golden_dir):
     normed = loaded.final_rms_norm(fx["cases"][-1]["out"].reshape(1, 1, -1))
     assert torch.equal(normed.reshape(-1), fx["final_norm"])
     assert_ulps(loaded.lm_head(normed).reshape(-1), fx["logits"], 1, "logits")
+
+
+# ---- Qwen3.5: pinned by the reference's own plain-torch statement of every @func ------------------------
+
+def _close_f32(got, want, msg, tol=2e-5):
+    """f32 activations: both sides round a matmul's output to bf16 at the same points, so they differ by
+    accumulation order inside f32 reductions only -- except where such a difference flips one bf16
+    rounding of a matmul output, which the bound below allows at that tensor's scale."""
+    err = (got.float().reshape(-1) - want.float().reshape(-1)).abs().max().item()
+    scale = want.float().abs().max().item()
+    assert err <= tol * scale + 2.0 ** -8 * scale * 1.01, f"{msg}: max err {err:.4g} at scale {scale:.4g}"
+
+
+def test_qwen3_5_layers_match_reference_torch_ref_vectors(golden_dir):
+    """`tests/golden/qwen3_5_tiny_torchref.pt` was produced by importing the reference's
+    ``examples/qwen3_5_35b_a3b-tilelang/kernels/torch_ref.py``."""
+    from oracle import qwen3_5_35b_a3b as oq5
+    from tilefoundry_b200.authored import qwen3_5_35b_a3b as m
+
+    fx = torch.load(golden_dir / "qwen3_5_tiny_torchref.pt")
+    cfg = m.Qwen35Config(**fx["config"])
+    mod = m.build(cfg)
+    weights = random_weights(mod, seed=fx["seed_w"], std=fx["std"], overrides=m.weight_overrides)
+    loaded = evaluator.load(mod, DictResource(weights), oq5.make(cfg))
+    cos, sin = m.rope_tables(cfg)
+    scale = torch.full((1, 1, 1, 1), cfg.head_dim ** -0.5)
+
+    for i, case in enumerate(fx["gdn_cases"]):
+        rec = (case["rec_a"][:, :, None] * case["rec_b"][:, None, :])[None]
+        mixed, entry, updated = loaded.layer0.mixer.linear_attention(case["hidden"], case["conv_state"], rec)
+        assert torch.equal(entry, case["entry"]), f"gdn case {i}: conv entry"
+        _close_f32(mixed, case["mixed"], f"gdn case {i}: mixer output")
+        if case["updated"] is not None:
+            _close_f32(updated, case["updated"], f"gdn case {i}: state", tol=1e-4)
+        _close_f32((updated[0] * case["probe_k"][None, :, None]).sum(1), case["updated_over_k"], f"gdn case {i}: state over k", tol=1e-4)
+        _close_f32((updated[0] * case["probe_v"][None, None, :]).sum(2), case["updated_over_v"], f"gdn case {i}: state over v", tol=1e-4)
+        out, _ = loaded.layer0(case["hidden"], (case["conv_state"], rec))
+        tokens = loaded.layer0.moe.post_norm(case["hidden"] + case["mixed"])
+        rw, idx = loaded.layer0.moe.router.routing(tokens)
+        assert torch.equal(idx, case["route_idx"]), f"gdn case {i}: routed experts"
+        _close_f32(rw, case["route_w"], f"gdn case {i}: routing weights")
+        _close_f32(out, case["out"], f"gdn case {i}: layer output")
+
+    layer = getattr(loaded, f"layer{fx['attn_layer']}")
+    for case in fx["attn_cases"]:
+        pos = torch.tensor([case["ctx"]], dtype=torch.int32)
+        mixed, k_new, v_new = layer.mixer.full_attention(case["hidden"], cos, sin, pos, case["k_cache"], case["v_cache"], scale)
+        assert torch.equal(v_new, case["v_new"]), f"ctx {case['ctx']}: v_new"
+        _close_f32(k_new, case["k_new"], f"ctx {case['ctx']}: k_new", tol=1e-5)
+        _close_f32(mixed, case["mixed"], f"ctx {case['ctx']}: attention output")
+        out, _ = layer(case["hidden"], (cos, sin, pos, case["k_cache"], case["v_cache"], scale))
+        _close_f32(out, case["out"], f"ctx {case['ctx']}: layer output")
+
+    assert torch.equal(loaded.embed(torch.tensor([17])), fx["embed"])
+    normed = loaded.final_rms_norm(fx["attn_cases"][-1]["out"])
+    _close_f32(normed, fx["final_norm"], "final norm", tol=1e-5)
+    _close_f32(loaded.lm_head(fx["final_norm"]), fx["logits"], "logits", tol=0)
