@@ -72,6 +72,15 @@ class Workload:
                              "experts top-10 + shared expert, vocab 100352), batch 1, 64-token random prompt, greedy "
                              "decode, f32 recurrent state in place, paged bf16 KV for the attention layers")
             self.oracle_name, self.cpu_layers = "granite_4_0_h_small", 6
+        elif key == "qwen3_5_35b_a3b":
+            from tilefoundry_b200.authored import qwen3_5_35b_a3b as a
+            from tilefoundry_b200.engine.qwen3_5 import Qwen35Session as S
+            self.authored, self.cfg, self.session_cls, self.overrides = a, a.QWEN3_5_35B_A3B, S, a.weight_overrides
+            self.describe = ("Qwen3.5-35B-A3B architecture (30 Gated DeltaNet + 10 gated-attention layers, hidden 2048, "
+                             "MoE 256 experts top-8 + gated shared expert, vocab 248320), f32 activations and state, "
+                             "bf16 contracted weights, batch 1, 64-token random prompt, greedy decode, paged f32 KV "
+                             "for the attention layers")
+            self.oracle_name, self.cpu_layers = "qwen3_5_35b_a3b", 4
         else:
             raise SystemExit(f"unknown --config {key!r}")
 
@@ -110,6 +119,8 @@ class Workload:
         if self.cpu_layers is None:
             return self.cfg, 1.0
         kw = {"num_hidden_layers": self.cpu_layers}
+        if self.key == "qwen3_5_35b_a3b":
+            kw = {"n_layers": self.cpu_layers}               # one 3 : 1 cycle of the layer pattern
         if self.key == "granite_4_0_h_small":
             kw["attention_layers"] = (self.cpu_layers - 1,)
         small = dataclasses.replace(self.cfg, **kw)
@@ -204,6 +215,19 @@ def dominant_kernel(work, sess):
         nbytes = 2 * cfg.intermediate_size * cfg.hidden_size * 2
         return ("gemv_kernel<SwiGLU> (post-attention norm + gate/up projection)",
                 _graph_time(launches, len(sess.layers)), nbytes)
+    if work.key == "qwen3_5_35b_a3b":
+        import ctypes as C
+        gdn = [l for l in sess.layers if l["kind"] == "linear_attention"]
+        n = cfg.conv_dim + cfg.val_dim + 2 * cfg.gdn_n_v_heads
+        calls = [lib.GemvF32Args(w=lib.ptr(l["w_in"]), x=lib.ptr(sess.hidden), gamma=lib.ptr(l["gamma_in"]),
+                                 y=lib.ptr(sess.proj), n=n, k=cfg.hidden, prologue=lib.NORM_F32GAIN, epilogue=lib.EPI_STORE,
+                                 eps=cfg.rms_eps, pdl=1) for l in gdn]
+
+        def launches():
+            for a in calls:
+                lib.check(lib.load().tfb_gemv_f32(C.byref(a), lib.stream()), "tfb_gemv_f32")
+        return ("gemv_f32_kernel<store> (input norm + Gated DeltaNet in-projection)", _graph_time(launches, len(gdn)),
+                n * cfg.hidden * 2)
     mamba = [l for l in sess.layers if l["kind"] == "linear_attention"]
 
     def launches():
@@ -393,7 +417,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=PROMPT_TOKENS - 1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="qwen3_1_7b",
-                    choices=["qwen3_1_7b", "minicpm3_4b", "granite_4_0_h_small"],
+                    choices=["qwen3_1_7b", "minicpm3_4b", "granite_4_0_h_small", "qwen3_5_35b_a3b"],
                     help="which BASELINE.json configuration to run (default: the one the metric is quoted on)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()

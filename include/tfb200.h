@@ -43,10 +43,11 @@ TFB_API int tfb_version(void);
 TFB_API const char* tfb_status_string(int status);
 /* Text of the last CUDA runtime error a launch returned on this thread ("" if none). */
 TFB_API const char* tfb_last_error(void);
-/* Debug timeline.  While a device buffer of capacity*4 uint64 is registered, each projection,
- * attention and lm_head launch is given the next 4-word record and writes, in %globaltimer ns:
- * earliest CTA start, earliest and latest return from the dependency wait, latest exit.  The
- * caller presets the words to (~0, ~0, 0, 0).  Pass NULL to stop.  Not for production use. */
+/* Debug timeline.  While a device buffer of capacity*8 uint64 is registered, each projection,
+ * attention and lm_head launch is given the next 8-word record and writes, in %globaltimer ns:
+ * [0] earliest CTA start, [1] earliest and [2] latest return from the dependency wait, [3] latest exit,
+ * [4..7] latest time any CTA passed each of up to four interior marks.  The caller presets the words to
+ * (~0, ~0, 0, 0, 0, 0, 0, 0).  Pass NULL to stop.  Not for production use. */
 TFB_API int tfb_debug_trace(void* device_buffer, int32_t capacity);
 
 /* ---- embedding row gather -------------------------------------------------
@@ -65,7 +66,10 @@ TFB_API int tfb_embed(const void* table, const int64_t* ids, void* out, int32_t 
 /* TFB_NORM_GATED (projections only): y = bf16(v * rsqrt(mean(v^2)+eps) * gamma32) with
  * v = f32(x) * silu(f32(x_gate)) -- granite's gated output norm,
  * examples/granite_4_0_h_small-cuda/model.py:223-236. */
-enum { TFB_NORM_NONE = 0, TFB_NORM_F32GAIN = 1, TFB_NORM_CAST_THEN_GAIN = 2, TFB_NORM_GATED = 3 };
+enum { TFB_NORM_NONE = 0, TFB_NORM_F32GAIN = 1, TFB_NORM_CAST_THEN_GAIN = 2, TFB_NORM_GATED = 3,
+       /* f32-activation family only: */
+       TFB_NORM_SEGMENT_GATED = 4, /* per segment of `seg` elements: bf16(x * rsqrt(mean_seg(x^2)+eps) * gamma32[i % seg] * silu(gate[i])) */
+       TFB_NORM_F32_INPUT = 5      /* tfb_lm_head_argmax: x and gamma are f32; y = bf16(x * rsqrt(mean(x^2)+eps) * gamma) */ };
 TFB_API int tfb_rmsnorm(const void* x, const void* gamma, void* y, int32_t rows, int32_t width, float eps,
                 int32_t mode, tfb_stream_t stream);
 
@@ -499,6 +503,143 @@ TFB_API int tfb_granite_decode_step(const tfb_granite_step_args* args, tfb_strea
  * the MoE down stage; 2 finish layer `layer` from the summed partials; 3 final norm + head; 4 pick from the
  * gathered pairs.  With ep_world <= 1 parts 0, 1.., 3 are the whole step (what tfb_granite_decode_step runs). */
 TFB_API int tfb_granite_step_part(const tfb_granite_step_args* args, int32_t part, int32_t layer, tfb_stream_t stream);
+
+/* ================= f32-activation family (Qwen3.5-35B-A3B) =================
+ * The reference's Qwen3.5 example keeps activations, recurrent state and KV cache in f32 and its contracted
+ * weights in bf16: a product casts its activation to bf16, runs at bf16 and casts the result back
+ * (examples/qwen3_5_35b_a3b-tilelang/model.py:189,214-225; kernels/torch_ref.py:134-142).  Every f32 buffer
+ * below follows that rule: values a product wrote are exactly representable in bf16. */
+
+/* y = epilogue(bf16(W . bf16(prologue(x)))); W [n,k] bf16 row-major, x/gamma/gate/residual/y f32.
+ * prologue TFB_NORM_NONE, TFB_NORM_F32GAIN (gamma [k]) or TFB_NORM_SEGMENT_GATED (gamma [seg], gate [k]);
+ * epilogue TFB_EPI_STORE, TFB_EPI_RESIDUAL (y = residual + bf16(acc)) or TFB_EPI_SWIGLU
+ * (y = bf16(silu(bf16(acc_gate)) * bf16(acc_up)), w = gate rows, w2 = up rows).
+ * Expert mode (rows_per_expert > 0): output rows come in slots of rows_per_expert; slot s < routed_slots reads
+ * the rows of expert expert_idx[s] of w (and w2), later slots read consecutive rows of w_extra (w2_extra).
+ * Replaces the projections inside linear_attention / full_attention / routing / routed_experts / shared_expert
+ * (examples/qwen3_5_35b_a3b-tilelang/model.py:214-228,380-417,488-499,540-590). */
+typedef struct {
+    const void* w; const void* w2; const void* w_extra; const void* w2_extra;
+    const float* x; const float* gamma; const float* gate; const float* residual;
+    float* y;
+    int32_t n, k, seg;
+    int32_t prologue, epilogue;
+    float eps;
+    const int64_t* expert_idx;
+    int32_t rows_per_expert, routed_slots;
+    int32_t pdl, reserved;
+} tfb_gemv_f32_args;
+TFB_API int tfb_gemv_f32(const tfb_gemv_f32_args* args, tfb_stream_t stream);
+
+/* One Gated DeltaNet token for all value heads: conv_step + SiLU, l2_normalise of q and k, the decay
+ * g = -exp(a_log) * softplus(a + dt_bias) and write strength beta = sigmoid(b), and delta_step
+ * (examples/qwen3_5_35b_a3b-tilelang/model.py:117-212).  proj = [2*hk*dk + hv*dv conv entry | hv*dv z | hv b | hv a]
+ * (z is not read here).  conv_state is TWO buffers [channels][width-1], conv_state_stride floats apart: the
+ * buffer (*pos & 1) is read and the other one receives the shifted window (pos null: read 0, write 1).
+ * state [hv][dk][dv] is updated in place; read [hv*dv] is the un-normalised read-out. dk = 128, width = 4. */
+typedef struct {
+    const float* proj;
+    float* conv_state; uint64_t conv_state_stride;
+    const int32_t* pos;
+    const float* conv_w; const float* a_log; const float* dt_bias;
+    float* state; float* read;
+    int32_t hk, hv, dk, dv, kernel_width;
+    float q_scale;
+    int32_t pdl, reserved;
+    /* delta_step alone: when direct_q is set, q [hv][dk], k [hv][dk], v [hv][dv], g [hv], beta [hv] are taken
+     * as given and proj / conv_state / conv_w / a_log / dt_bias are not read. */
+    const float* direct_q; const float* direct_k; const float* direct_v; const float* direct_g; const float* direct_beta;
+} tfb_gdn_args;
+TFB_API int tfb_gdn_step(const tfb_gdn_args* args, tfb_stream_t stream);
+/* The pieces of the mixer as functions of their own (conv_step, l2_normalise, partial_rope / partial_rope_kv;
+ * examples/qwen3_5_35b_a3b-tilelang/model.py:117-150,293-330): mixed[c] = silu(sum_j window[c][j] * conv_w[c][j]) with
+ * window = state [channels][width-1] followed by entry [channels]; y = x * rsqrt(sum(x^2) + eps) per row;
+ * rotate-half RoPE at *pos on the leading rotary_dim of each of `heads` rows of d elements. */
+TFB_API int tfb_conv_silu_f32(const float* state, const float* entry, const float* conv_w, float* mixed, int32_t channels,
+                              int32_t width, int32_t pdl, tfb_stream_t stream);
+TFB_API int tfb_l2norm_f32(const float* x, float* y, int32_t rows, int32_t width, float eps, int32_t pdl, tfb_stream_t stream);
+TFB_API int tfb_partial_rope_f32(const float* x, const float* cos_table, const float* sin_table, const int32_t* pos,
+                                 float* out, int32_t heads, int32_t d, int32_t rotary_dim, int32_t pdl, tfb_stream_t stream);
+
+/* Gated GQA decode attention over a paged f32 cache: per-head RMSNorm of q and k with f32 gains, rotate-half
+ * RoPE on the leading rotary_dim (a multiple of 64) of each head, append at *pos, softmax over positions
+ * 0..*pos, output times sigmoid(gate) (examples/qwen3_5_35b_a3b-tilelang/model.py:293-417).
+ * proj = [hq][2*d] (q then gate per head) | [hkv][d] k | [hkv][d] v.  Pools are [page][page_size][hkv][d] f32.
+ * Scratch: part_o f32 [hq * nsplit * d], part_ml f32 [hq * nsplit * 2], counters u32 [hkv] zeroed once, with
+ * nsplit = tfb_attn_gated_splits(max_ctx). */
+typedef struct {
+    const float* proj; const float* gamma_q; const float* gamma_k;
+    const float* cos_table; const float* sin_table;
+    const int32_t* pos; const int32_t* rope_pos;
+    float* k_pool; float* v_pool; const int32_t* block_table;
+    float* out; float* k_new_out; float* v_new_out;
+    float* part_o; float* part_ml; uint32_t* counters;
+    int32_t hq, hkv, d, rotary_dim, page_size, table_len, max_ctx, max_pos;
+    float eps, scale;
+    int32_t pdl, reserved;
+} tfb_attn_gated_args;
+TFB_API int32_t tfb_attn_gated_splits(int32_t max_ctx);
+TFB_API int tfb_attn_gated_decode(const tfb_attn_gated_args* args, tfb_stream_t stream);
+
+/* out[j] = residual[j] + sum_s weights[s] * bf16(w_down[indices[s]][j,:] . inner[s,:])
+ *                      + bf16(w_shared[j,:] . inner[top_k,:]) * sigmoid(*shared_gate_logit)
+ * (routed_experts + shared_expert + experts + the layer's residual_add,
+ * examples/qwen3_5_35b_a3b-tilelang/model.py:540-612,650-665). */
+typedef struct {
+    const void* w_down; const void* w_shared;
+    const float* inner; const int64_t* indices; const float* weights; const float* shared_gate_logit;
+    const float* residual; float* out;
+    int32_t hidden, inter, shared_inter, top_k;
+    int32_t pdl, reserved;
+} tfb_moe_down_f32_args;
+TFB_API int tfb_moe_down_f32(const tfb_moe_down_f32_args* args, tfb_stream_t stream);
+
+/* embed (bf16 table row widened to f32), tf.rms_norm on f32 with an f32 gain, plain f32 add
+ * (examples/qwen3_5_35b_a3b-tilelang/model.py:760-800,650-665). */
+TFB_API int tfb_embed_f32(const void* table, const int64_t* ids, float* out, int32_t rows, int32_t hidden, int64_t vocab,
+                          int32_t pdl, tfb_stream_t stream);
+TFB_API int tfb_rmsnorm_f32(const float* x, const float* gamma, float* y, int32_t rows, int32_t width, float eps,
+                            int32_t pdl, tfb_stream_t stream);
+TFB_API int tfb_residual_add_f32(const float* a, const float* b, float* out, int32_t n, int32_t pdl, tfb_stream_t stream);
+
+/* One decoder layer's weights and state.  kind 0: Gated DeltaNet mixer, kind 1: gated attention mixer.
+ * w_in  kind 0: [2*hk*dk + 2*hv*dv + 2*hv][hidden] rows of w_in_qkv | w_in_z | w_in_b | w_in_a
+ *       kind 1: [hq*2*d + 2*hkv*d][hidden]        rows of w_qg | w_k | w_v
+ * w_router [experts + 1][hidden]: the router's rows, then the shared expert's scale row. */
+typedef struct {
+    int32_t kind, reserved;
+    const float* gamma_in; const void* w_in; const void* w_out;
+    const float* conv_w; const float* a_log; const float* dt_bias; const float* gamma_gdn;
+    float* conv_state; float* state;
+    const float* gamma_q; const float* gamma_k; float* k_pool; float* v_pool;
+    const float* gamma_post; const void* w_router;
+    const void* w_gate; const void* w_up; const void* w_down;
+    const void* w_shared_gate; const void* w_shared_up; const void* w_shared_down;
+} tfb_qwen35_layer;
+
+/* The whole captured step of the reference's engine for this model (embed -> layers -> final norm -> head ->
+ * greedy pick -> bookkeeping; examples/qwen3_5_35b_a3b-tilelang/model.py:800-892 and runtime_model.py).
+ * 7 launches per layer; token history and position live on the device as in tfb_qwen3_decode_step. */
+typedef struct {
+    const tfb_qwen35_layer* layers; int32_t n_layers; int32_t pdl;
+    const void* table; const float* gamma_final; const void* w_head;
+    const float* cos_table; const float* sin_table;
+    int64_t* tokens; int32_t* pos; int32_t n_prompt, max_tokens;
+    const int32_t* block_table; int32_t page_size, table_len, max_ctx;
+    int32_t hidden; int64_t vocab;
+    int32_t hk, hv, dk, dv, conv_width;
+    int32_t hq, hkv, d, rotary_dim;
+    int32_t experts, top_k, inter, shared_inter;
+    uint64_t conv_state_stride;
+    float eps, attn_scale, q_scale;
+    float* hidden_buf; float* attended_buf; float* proj_buf; float* mixed_buf;
+    float* router_logits; int64_t* router_idx; float* router_w; float* inner_buf;
+    float* part_o; float* part_ml; uint32_t* counters; float* head_val; int32_t* head_idx;
+    void* logits; int64_t* picked;
+    float* hidden_trace;      /* optional f32 [(n_layers + 1)][hidden]: every layer's output, then the final norm */
+    int64_t* idx_trace;       /* optional [n_layers][top_k] */
+} tfb_qwen35_step_args;
+TFB_API int tfb_qwen35_decode_step(const tfb_qwen35_step_args* args, tfb_stream_t stream);
 
 #ifdef __cplusplus
 }

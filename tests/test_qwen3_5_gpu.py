@@ -1,0 +1,174 @@
+"""Parity of the CUDA path against the CPU oracle -- Qwen3.5-35B-A3B (Gated DeltaNet + gated attention hybrid,
+256-expert MoE; f32 activations and state, bf16 contracted weights)."""
+import pytest
+import torch
+
+from oracle import evaluator, generation, qwen3_5_35b_a3b as oq
+from tests import parity
+from tests.helpers import ATOL, RTOL, assert_close_at_scale
+from tilefoundry_b200.authored import qwen3_5_35b_a3b as qa
+from tilefoundry_b200.authored.weights import random_weights
+from tilefoundry_b200.runtime import AllClose, DictResource, Equal, NanInf, check
+
+pytestmark = pytest.mark.gpu
+CLOSE = [AllClose(atol=ATOL, rtol=RTOL), NanInf()]          # through a bf16 product
+F32 = [AllClose(atol=1e-3, rtol=1e-3), NanInf()]            # pure f32 arithmetic
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from tilefoundry_b200 import lib
+    lib.load()
+    return torch.device("cuda:0")
+
+
+@pytest.fixture(scope="module")
+def sides(dev):
+    from tilefoundry_b200.twins.qwen3_5_35b_a3b import make_twin
+    cfg = qa.QWEN3_5_TINY
+    mod = qa.build(cfg)
+    weights = random_weights(mod, seed=3, std=0.05, overrides=qa.weight_overrides)
+    ref = evaluator.load(mod, DictResource(weights), oq.make(cfg))
+    twin = make_twin(cfg)()
+    twin.load(DictResource(parity.cuda_weights(weights, dev)))
+    return cfg, ref, twin
+
+
+def _check(twin_fn, ref_fn, inputs, expect):
+    rep = check(lambda *a: parity.to_cpu(twin_fn(*a)), parity.on_cpu(ref_fn), inputs, expect=expect)
+    assert rep.passed, rep.render()
+
+
+def test_linear_attention_functions(dev, sides):
+    cfg, ref, twin = sides
+    g = torch.Generator().manual_seed(5)
+    r = lambda *s, scale=1.0: (torch.randn(*s, generator=g) * scale).to(dev)
+    HV, DK, DV, CONV = cfg.gdn_n_v_heads, cfg.gdn_head_k_dim, cfg.gdn_head_v_dim, cfg.conv_dim
+    rm, tm = ref.layer0.mixer, twin.layer0.mixer
+    conv_state, entry = r(1, CONV, 3, scale=0.5), r(1, CONV, 1)
+    _check(tm.conv_step, rm.conv_step, (conv_state, entry), {"output": F32})
+    _check(tm.l2_normalise, rm.l2_normalise, (r(1, 1, HV, DK),), {"output": F32})
+    state = r(1, HV, DK, DV, scale=0.1)
+    unit = lambda t: t / t.norm(dim=-1, keepdim=True)
+    step_in = (state, unit(r(1, 1, HV, DK)), unit(r(1, 1, HV, DK)), r(1, 1, HV, DV), -torch.rand(1, 1, HV, generator=g).to(dev),
+               torch.rand(1, 1, HV, generator=g).to(dev))
+    _check(tm.delta_step, rm.delta_step, step_in, {"output[0]": F32, "output[1]": F32})
+    hidden = r(1, 1, cfg.hidden)
+    _check(tm.linear_attention, rm.linear_attention, (hidden, conv_state, state),
+           {"output[0]": CLOSE, "output[1]": CLOSE, "output[2]": CLOSE})
+    assert torch.equal(state.cpu(), step_in[0].cpu())              # inputs were not mutated
+
+
+@pytest.mark.parametrize("ctx", [0, 1, 63, 64, 130])
+def test_full_attention_functions(dev, sides, ctx):
+    cfg, ref, twin = sides
+    g = torch.Generator().manual_seed(ctx)
+    HQ, HKV, D = cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim
+    ai = cfg.full_attention_every - 1
+    ra, ta = getattr(ref, f"layer{ai}").mixer, getattr(twin, f"layer{ai}").mixer
+    cos, sin = qa.rope_tables(cfg)
+    pos = torch.tensor([ctx], dtype=torch.int32)
+    on = lambda *ts: tuple(t.to(dev) for t in ts)
+    _check(ta.partial_rope, ra.partial_rope, on(torch.randn(1, 1, HQ, D, generator=g), cos, sin, pos), {"output": F32})
+    _check(ta.partial_rope_kv, ra.partial_rope_kv, on(torch.randn(1, 1, HKV, D, generator=g), cos, sin, pos), {"output": F32})
+    hidden = torch.randn(1, 1, cfg.hidden, generator=g)
+    kc = torch.randn(1, ctx, HKV, D, generator=g) * 0.5
+    vc = torch.randn(1, ctx, HKV, D, generator=g) * 0.5
+    scale = torch.full((1, 1, 1, 1), D ** -0.5)
+    _check(ta.full_attention, ra.full_attention, on(hidden, cos, sin, pos, kc, vc, scale),
+           {"output[0]": CLOSE, "output[1]": CLOSE, "output[2]": CLOSE})
+
+
+def test_moe_functions_and_routing_indices(dev, sides):
+    cfg, ref, twin = sides
+    g = torch.Generator().manual_seed(9)
+    hidden = torch.randn(1, 1, cfg.hidden, generator=g).to(dev)
+    rm, tm = ref.layer0.moe, twin.layer0.moe
+    _check(tm.post_norm, rm.post_norm, (hidden,), {"output": F32})
+    tokens = rm.post_norm(hidden.cpu())
+    _check(tm.router.routing, rm.router.routing, (tokens.to(dev),), {"output[0]": CLOSE, "output[1]": [Equal()]})
+    weights, indices = rm.router.routing(tokens)
+    args = tuple(t.to(dev) for t in (tokens, weights, indices))
+    _check(tm.routed_experts, rm.routed_experts, args, {"output": CLOSE})
+    _check(tm.shared_expert, rm.shared_expert, (tokens.to(dev),), {"output": CLOSE})
+    _check(tm.experts, rm.experts, args, {"output": CLOSE})
+    _check(tm, rm, (hidden,), {"output": CLOSE})                 # the block's own forward
+    b = torch.randn(1, 1, cfg.hidden, generator=g).to(dev)
+    _check(twin.layer0.residual_add, ref.layer0.residual_add, (hidden, b), {"output": F32})
+
+
+def test_root_functions(dev, sides):
+    cfg, ref, twin = sides
+    g = torch.Generator().manual_seed(2)
+    ids = torch.tensor([cfg.vocab - 1])
+    assert torch.equal(twin.embed(ids.to(dev)).cpu(), ref.embed(ids))
+    hidden = torch.randn(1, 1, cfg.hidden, generator=g)
+    _check(twin.final_rms_norm, ref.final_rms_norm, (hidden.to(dev),), {"output": F32})
+    normed = ref.final_rms_norm(hidden)
+    _check(twin.lm_head, ref.lm_head, (normed.to(dev),), {"output": CLOSE})
+    assert int(twin.last_token) == int(torch.argmax(twin.lm_head(normed.to(dev))))
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_session_matches_evaluator_tiny(dev, use_graph):
+    """Teacher-forced run of the whole hybrid stack: logits within the end-to-end bound at every step, greedy
+    picks equal except inside the measured noise, recurrent state, convolution windows and KV cache as the
+    evaluator left them."""
+    from tilefoundry_b200.engine.qwen3_5 import Qwen35Session
+    from tilefoundry_b200.engine import paged_kv
+    cfg = qa.QWEN3_5_TINY
+    mod = qa.build(cfg)
+    weights = random_weights(mod, seed=11, std=0.05, overrides=qa.weight_overrides)
+    ref = evaluator.load(mod, DictResource(weights), oq.make(cfg))
+    n_prompt, n_new = 16, 80
+    prompt = torch.randint(0, cfg.vocab, (n_prompt,), generator=torch.Generator().manual_seed(111))
+    want = generation.decode_ids(ref, prompt, n_new, keep_logits=True)
+    forced = torch.cat([prompt, torch.tensor(want["tokens"], dtype=torch.int64)])
+    sess = Qwen35Session(cfg, DictResource(parity.cuda_weights(weights, dev)), max_ctx=n_prompt + n_new + 5, device=dev,
+                         keep_logits=True, trace_hidden=True)
+    sess.reset(forced)
+    if use_graph:
+        sess.capture()
+    total = n_prompt + n_new - 1
+    mismatched = 0
+    for step in range(total):
+        sess.run(1, use_graph)
+        ref_logits = want["logits"][step][0]
+        assert_close_at_scale(sess.logits, ref_logits, f"logits step {step}")
+        assert int(sess.picked) == int(torch.argmax(sess.logits.float())), f"step {step}: pick is not argmax"
+        if int(sess.picked) != int(torch.argmax(ref_logits)):
+            top = torch.topk(ref_logits.float(), 2).values
+            noise = (sess.logits.float().cpu() - ref_logits.float()).abs().max()
+            assert float(top[0] - top[1]) <= 2 * float(noise), f"pick differs at step {step}"
+            mismatched += 1
+    assert mismatched <= 6
+    assert int(sess.pos) == total
+    assert torch.equal(sess.table.cpu(), paged_kv.block_table(1, sess.max_ctx))
+    for li, (kind, state) in enumerate(zip(cfg.layer_types, want["caches"])):
+        layer = sess.layers[li]
+        if kind == "linear_attention":
+            window, matrix = state
+            assert_close_at_scale(sess.conv_window(layer), window[0], f"layer {li} conv window")
+            assert_close_at_scale(layer["state"], matrix[0], f"layer {li} recurrent state after {total} steps")
+        else:
+            k_ref, v_ref = state
+            assert_close_at_scale(paged_kv.logical_view(layer["k_pool"], sess.table[0], total), k_ref[:, :total],
+                                  f"layer {li} K cache")
+            assert_close_at_scale(paged_kv.logical_view(layer["v_pool"], sess.table[0], total), v_ref[:, :total],
+                                  f"layer {li} V cache")
+
+
+def test_generate_equals_stepwise_and_replays(dev):
+    """generate() (one captured graph, device-resident token history) returns the tokens a step-by-step eager
+    walk returns, and a second sequence through the same graph starts from zeroed recurrent state."""
+    from tilefoundry_b200.engine.qwen3_5 import Qwen35Session
+    cfg = qa.QWEN3_5_TINY
+    weights = random_weights(qa.build(cfg), seed=4, std=0.05, overrides=qa.weight_overrides)
+    sess = Qwen35Session(cfg, DictResource(parity.cuda_weights(weights, dev)), max_ctx=96, device=dev)
+    prompt = torch.randint(0, cfg.vocab, (9,), generator=torch.Generator().manual_seed(8))
+    a = sess.generate(prompt, 40, use_graph=True).tokens
+    b = sess.generate(prompt, 40, use_graph=False).tokens
+    c = sess.generate(prompt, 40, use_graph=True).tokens
+    assert a == b == c

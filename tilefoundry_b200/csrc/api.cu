@@ -130,10 +130,10 @@ int tfb_lm_head_argmax(const tfb_lm_head_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->w && a->x && a->scratch_val && a->scratch_idx && a->counter, TFB_EINVAL);
     TFB_REQUIRE(a->token_out || a->pair_out || (a->tokens && a->pos), TFB_EINVAL);
     TFB_REQUIRE(a->n > 0 && a->k > 0 && a->k % 256 == 0 && a->k <= 8192, TFB_EINVAL);
-    TFB_REQUIRE(a->prologue >= TFB_NORM_NONE && a->prologue <= TFB_NORM_CAST_THEN_GAIN, TFB_EINVAL);
-    TFB_REQUIRE(a->prologue == TFB_NORM_NONE || a->gamma, TFB_EINVAL);
+    TFB_REQUIRE((a->prologue >= TFB_NORM_NONE && a->prologue <= TFB_NORM_CAST_THEN_GAIN) || a->prologue == TFB_NORM_F32_INPUT, TFB_EINVAL);
+    TFB_REQUIRE(a->prologue == TFB_NORM_NONE || a->prologue == TFB_NORM_F32_INPUT || a->gamma, TFB_EINVAL);
     TFB_REQUIRE(aligned16(a->w) && aligned16(a->x) && (!a->gamma || aligned16(a->gamma)), TFB_EALIGN);
-    if (a->kernel == TFB_KERNEL_RING && !a->pair_out && tfb::gemv_stream_supported(a->n, a->k)) {
+    if (a->kernel == TFB_KERNEL_RING && a->prologue != TFB_NORM_F32_INPUT && !a->pair_out && tfb::gemv_stream_supported(a->n, a->k)) {
         tfb::GemvParams g = {};
         g.w = static_cast<const uint4*>(a->w);
         g.x = static_cast<const uint16_t*>(a->x);

@@ -1,0 +1,229 @@
+// C ABI of the f32-activation family (Qwen3.5-35B-A3B): argument checks, then the launches.
+#include "api_internal.h"
+#include "kernels.h"
+
+#include <cstring>
+
+using namespace tfb::host;
+
+extern "C" {
+
+int tfb_gemv_f32(const tfb_gemv_f32_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->w && a->x && a->y, TFB_EINVAL);
+    TFB_REQUIRE(a->n > 0 && a->k > 0 && a->k % 256 == 0 && a->k <= 8192, TFB_EINVAL);
+    const int nm = a->prologue, ep = a->epilogue;
+    TFB_REQUIRE(nm == TFB_NORM_NONE || nm == TFB_NORM_F32GAIN || nm == TFB_NORM_SEGMENT_GATED, TFB_EINVAL);
+    TFB_REQUIRE(ep == TFB_EPI_STORE || ep == TFB_EPI_RESIDUAL || ep == TFB_EPI_SWIGLU, TFB_EINVAL);
+    TFB_REQUIRE(nm == TFB_NORM_NONE || a->gamma, TFB_EINVAL);
+    if (nm == TFB_NORM_SEGMENT_GATED) {
+        const int s = a->seg;
+        TFB_REQUIRE(a->gate && s >= 16 && s <= 256 && (s & (s - 1)) == 0 && a->k % s == 0, TFB_EINVAL);
+    }
+    TFB_REQUIRE(ep != TFB_EPI_RESIDUAL || a->residual, TFB_EINVAL);
+    TFB_REQUIRE(ep != TFB_EPI_SWIGLU || a->w2, TFB_EINVAL);
+    if (a->rows_per_expert > 0) {
+        TFB_REQUIRE(a->rows_per_expert % 8 == 0 && a->n % a->rows_per_expert == 0 && a->routed_slots >= 0, TFB_EINVAL);
+        TFB_REQUIRE(a->routed_slots == 0 || a->expert_idx, TFB_EINVAL);
+        const bool extra = a->routed_slots * a->rows_per_expert < a->n;
+        TFB_REQUIRE(!extra || (a->w_extra && (ep != TFB_EPI_SWIGLU || a->w2_extra)), TFB_EINVAL);
+    }
+    TFB_REQUIRE(aligned16(a->w) && aligned16(a->x) && aligned16(a->y) && (!a->w2 || aligned16(a->w2)) &&
+                    (!a->gamma || aligned16(a->gamma)) && (!a->gate || aligned16(a->gate)) &&
+                    (!a->w_extra || aligned16(a->w_extra)) && (!a->w2_extra || aligned16(a->w2_extra)), TFB_EALIGN);
+    tfb::GemvF32Params p = {};
+    p.w = static_cast<const uint4*>(a->w); p.w2 = static_cast<const uint4*>(a->w2);
+    p.w_extra = static_cast<const uint4*>(a->w_extra); p.w2_extra = static_cast<const uint4*>(a->w2_extra);
+    p.x = a->x; p.gamma = a->gamma; p.gate = a->gate; p.residual = a->residual; p.y = a->y;
+    p.n = a->n; p.k = a->k; p.seg = a->seg; p.eps = a->eps;
+    p.expert_idx = reinterpret_cast<const long long*>(a->expert_idx);
+    p.rows_per_expert = a->rows_per_expert; p.routed_slots = a->routed_slots;
+    p.trace = next_trace();
+    return done(tfb::gemv_f32_dispatch(p, nm, ep, S(stream), a->pdl != 0));
+}
+
+int tfb_gdn_step(const tfb_gdn_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->state && a->read, TFB_EINVAL);
+    const bool direct = a->direct_q != nullptr;
+    TFB_REQUIRE(!direct || (a->direct_k && a->direct_v && a->direct_g && a->direct_beta), TFB_EINVAL);
+    TFB_REQUIRE(direct || (a->proj && a->conv_state && a->conv_w && a->a_log && a->dt_bias), TFB_EINVAL);
+    TFB_REQUIRE(a->dk == 128 && a->kernel_width == 4 && a->hk > 0 && a->hv > 0 && a->hv % a->hk == 0 && a->dv > 0 &&
+                    a->dv % 32 == 0, TFB_EINVAL);
+    const uint64_t channels = 2ull * a->hk * a->dk + uint64_t(a->hv) * a->dv;
+    TFB_REQUIRE(direct || a->conv_state_stride >= channels * (a->kernel_width - 1), TFB_EINVAL);
+    tfb::GdnParams p = {};
+    p.proj = a->proj; p.conv_state = a->conv_state; p.conv_state_stride = a->conv_state_stride; p.pos = a->pos;
+    p.conv_w = a->conv_w; p.a_log = a->a_log; p.dt_bias = a->dt_bias; p.state = a->state; p.read = a->read;
+    p.hk = a->hk; p.hv = a->hv; p.dk = a->dk; p.dv = a->dv; p.kernel_width = a->kernel_width; p.q_scale = a->q_scale;
+    p.direct_q = a->direct_q; p.direct_k = a->direct_k; p.direct_v = a->direct_v; p.direct_g = a->direct_g;
+    p.direct_beta = a->direct_beta;
+    return done(tfb::gdn_step_launch(p, S(stream), a->pdl != 0));
+}
+
+int32_t tfb_attn_gated_splits(int32_t max_ctx) { return tfb::attn_gated_splits(max_ctx); }
+
+int tfb_attn_gated_decode(const tfb_attn_gated_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->proj && a->gamma_q && a->gamma_k && a->cos_table && a->sin_table && a->pos && a->k_pool &&
+                    a->v_pool && a->block_table && a->out && a->part_o && a->part_ml && a->counters, TFB_EINVAL);
+    TFB_REQUIRE(a->hq > 0 && a->hkv > 0 && a->hq % a->hkv == 0 && a->page_size > 0 && a->max_ctx > 0, TFB_EINVAL);
+    TFB_REQUIRE(a->rotary_dim > 0 && a->rotary_dim % 64 == 0 && a->rotary_dim <= a->d, TFB_EINVAL);
+    TFB_REQUIRE(int64_t(a->table_len) * a->page_size >= a->max_ctx && a->max_pos >= a->max_ctx, TFB_ECAPACITY);
+    const int g = a->hq / a->hkv;
+    TFB_REQUIRE((a->d == 256 && (g == 8 || g == 4)) || (a->d == 128 && (g == 2 || g == 4)), TFB_EINVAL);
+    tfb::GatedAttnParams p = {};
+    p.proj = a->proj; p.gamma_q = a->gamma_q; p.gamma_k = a->gamma_k; p.cos_table = a->cos_table; p.sin_table = a->sin_table;
+    p.pos = a->pos; p.rope_pos = a->rope_pos; p.k_pool = a->k_pool; p.v_pool = a->v_pool; p.block_table = a->block_table;
+    p.out = a->out; p.k_new_out = a->k_new_out; p.v_new_out = a->v_new_out;
+    p.part_o = a->part_o; p.part_ml = a->part_ml; p.counters = a->counters;
+    p.hq = a->hq; p.hkv = a->hkv; p.d = a->d; p.rotary_dim = a->rotary_dim; p.page_size = a->page_size;
+    p.max_ctx = a->max_ctx; p.nsplit = tfb::attn_gated_splits(a->max_ctx); p.eps = a->eps; p.scale = a->scale;
+    return done(tfb::attn_gated_dispatch(p, S(stream), a->pdl != 0));
+}
+
+int tfb_moe_down_f32(const tfb_moe_down_f32_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->inner && a->out && a->top_k >= 0 && a->top_k <= 32, TFB_EINVAL);
+    TFB_REQUIRE(a->top_k == 0 || (a->w_down && a->indices && a->weights), TFB_EINVAL);
+    TFB_REQUIRE(a->top_k > 0 || a->w_shared, TFB_EINVAL);
+    TFB_REQUIRE(a->hidden > 0 && a->inter > 0 && a->inter % 8 == 0, TFB_EINVAL);
+    TFB_REQUIRE(!a->w_shared || (a->shared_inter > 0 && a->shared_inter % 8 == 0), TFB_EINVAL);
+    TFB_REQUIRE((!a->w_down || aligned16(a->w_down)) && aligned16(a->inner) && (!a->w_shared || aligned16(a->w_shared)), TFB_EALIGN);
+    const int is = a->w_shared ? a->shared_inter : 0;
+    TFB_REQUIRE((size_t(a->top_k) * a->inter + is) * 4 <= 96 * 1024, TFB_ECAPACITY);
+    tfb::MoeDownF32Params p = {};
+    p.w_down = static_cast<const uint4*>(a->w_down); p.w_shared = static_cast<const uint4*>(a->w_shared);
+    p.inner = a->inner; p.indices = reinterpret_cast<const long long*>(a->indices); p.weights = a->weights;
+    p.shared_gate_logit = a->shared_gate_logit; p.residual = a->residual; p.out = a->out;
+    p.hidden = a->hidden; p.inter = a->inter; p.shared_inter = is; p.top_k = a->top_k;
+    return done(tfb::moe_down_f32_launch(p, S(stream), a->pdl != 0));
+}
+
+int tfb_conv_silu_f32(const float* state, const float* entry, const float* conv_w, float* mixed, int32_t channels,
+                      int32_t width, int32_t pdl, tfb_stream_t stream) {
+    TFB_REQUIRE(state && entry && conv_w && mixed && channels > 0 && width >= 2, TFB_EINVAL);
+    return done(tfb::conv_silu_f32_launch(state, entry, conv_w, mixed, channels, width, S(stream), pdl != 0));
+}
+
+int tfb_l2norm_f32(const float* x, float* y, int32_t rows, int32_t width, float eps, int32_t pdl, tfb_stream_t stream) {
+    TFB_REQUIRE(x && y && rows >= 0 && width > 0, TFB_EINVAL);
+    if (rows == 0) return TFB_OK;
+    return done(tfb::l2norm_f32_launch(x, y, rows, width, eps, S(stream), pdl != 0));
+}
+
+int tfb_partial_rope_f32(const float* x, const float* cos_table, const float* sin_table, const int32_t* pos, float* out,
+                         int32_t heads, int32_t d, int32_t rotary_dim, int32_t pdl, tfb_stream_t stream) {
+    TFB_REQUIRE(x && cos_table && sin_table && pos && out && heads > 0 && d > 0, TFB_EINVAL);
+    TFB_REQUIRE(rotary_dim > 0 && rotary_dim % 2 == 0 && rotary_dim <= d, TFB_EINVAL);
+    return done(tfb::partial_rope_f32_launch(x, cos_table, sin_table, pos, out, heads, d, rotary_dim, S(stream), pdl != 0));
+}
+
+int tfb_embed_f32(const void* table, const int64_t* ids, float* out, int32_t rows, int32_t hidden, int64_t vocab,
+                  int32_t pdl, tfb_stream_t stream) {
+    TFB_REQUIRE(table && ids && out && rows >= 0 && hidden > 0 && vocab > 0, TFB_EINVAL);
+    if (rows == 0) return TFB_OK;
+    return done(tfb::embed_f32_launch(static_cast<const uint16_t*>(table), reinterpret_cast<const long long*>(ids), nullptr,
+                                      nullptr, out, rows, hidden, vocab, S(stream), pdl != 0));
+}
+
+int tfb_rmsnorm_f32(const float* x, const float* gamma, float* y, int32_t rows, int32_t width, float eps, int32_t pdl,
+                    tfb_stream_t stream) {
+    TFB_REQUIRE(x && gamma && y && rows >= 0 && width > 0, TFB_EINVAL);
+    if (rows == 0) return TFB_OK;
+    return done(tfb::rmsnorm_f32_launch(x, gamma, y, rows, width, eps, S(stream), pdl != 0));
+}
+
+int tfb_residual_add_f32(const float* a, const float* b, float* out, int32_t n, int32_t pdl, tfb_stream_t stream) {
+    TFB_REQUIRE(a && b && out && n >= 0, TFB_EINVAL);
+    if (n == 0) return TFB_OK;
+    return done(tfb::residual_add_f32_launch(a, b, out, n, S(stream), pdl != 0));
+}
+
+int tfb_qwen35_decode_step(const tfb_qwen35_step_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->layers && a->n_layers > 0 && a->table && a->gamma_final && a->w_head && a->tokens && a->pos, TFB_EINVAL);
+    TFB_REQUIRE(a->hidden_buf && a->attended_buf && a->proj_buf && a->mixed_buf && a->router_logits && a->router_idx &&
+                    a->router_w && a->inner_buf && a->part_o && a->part_ml && a->counters && a->head_val && a->head_idx,
+                TFB_EINVAL);
+    TFB_REQUIRE(a->max_tokens <= a->max_ctx + 1, TFB_ECAPACITY);
+    TFB_REQUIRE(a->inter > 0 && a->shared_inter % a->inter == 0, TFB_EINVAL);
+    const int pdl = a->pdl;
+    const int H = a->hidden, KEY = a->hk * a->dk, VAL = a->hv * a->dv, CONV = 2 * KEY + VAL;
+    const int N_GDN = CONV + VAL + 2 * a->hv, QD = a->hq * a->d, N_ATT = 2 * QD + 2 * a->hkv * a->d;
+    const int E = a->experts, K = a->top_k, I = a->inter, IS = a->shared_inter;
+    cudaStream_t st = S(stream);
+    float* hid = a->hidden_buf;
+    float* att = a->attended_buf;
+    cudaError_t e = tfb::embed_f32_launch(static_cast<const uint16_t*>(a->table), nullptr,
+                                          reinterpret_cast<const long long*>(a->tokens), a->pos, hid, 1, H, a->vocab, st,
+                                          pdl != 0);
+    if (e != cudaSuccess) return fail_launch(e);
+    int rc;
+    tfb_gemv_f32_args g;
+    auto base = [&](tfb_gemv_f32_args& x) { std::memset(&x, 0, sizeof x); x.eps = a->eps; x.pdl = pdl; };
+    for (int l = 0; l < a->n_layers; ++l) {
+        const tfb_qwen35_layer& L = a->layers[l];
+        base(g); g.w = L.w_in; g.x = hid; g.gamma = L.gamma_in; g.y = a->proj_buf; g.k = H;
+        g.n = L.kind == 0 ? N_GDN : N_ATT; g.prologue = TFB_NORM_F32GAIN; g.epilogue = TFB_EPI_STORE;
+        if ((rc = tfb_gemv_f32(&g, stream))) return rc;
+        if (L.kind == 0) {
+            tfb_gdn_args d;
+            std::memset(&d, 0, sizeof d);
+            d.proj = a->proj_buf; d.conv_state = L.conv_state; d.conv_state_stride = a->conv_state_stride; d.pos = a->pos;
+            d.conv_w = L.conv_w; d.a_log = L.a_log; d.dt_bias = L.dt_bias; d.state = L.state; d.read = a->mixed_buf;
+            d.hk = a->hk; d.hv = a->hv; d.dk = a->dk; d.dv = a->dv; d.kernel_width = a->conv_width; d.q_scale = a->q_scale;
+            d.pdl = pdl;
+            if ((rc = tfb_gdn_step(&d, stream))) return rc;
+            base(g); g.w = L.w_out; g.x = a->mixed_buf; g.gamma = L.gamma_gdn; g.gate = a->proj_buf + CONV; g.seg = a->dv;
+            g.residual = hid; g.y = att; g.n = H; g.k = VAL; g.prologue = TFB_NORM_SEGMENT_GATED; g.epilogue = TFB_EPI_RESIDUAL;
+            if ((rc = tfb_gemv_f32(&g, stream))) return rc;
+        } else {
+            tfb_attn_gated_args t;
+            std::memset(&t, 0, sizeof t);
+            t.proj = a->proj_buf; t.gamma_q = L.gamma_q; t.gamma_k = L.gamma_k; t.cos_table = a->cos_table;
+            t.sin_table = a->sin_table; t.pos = a->pos; t.k_pool = L.k_pool; t.v_pool = L.v_pool;
+            t.block_table = a->block_table; t.out = a->mixed_buf; t.part_o = a->part_o; t.part_ml = a->part_ml;
+            t.counters = a->counters; t.hq = a->hq; t.hkv = a->hkv; t.d = a->d; t.rotary_dim = a->rotary_dim;
+            t.page_size = a->page_size; t.table_len = a->table_len; t.max_ctx = a->max_ctx; t.max_pos = a->max_ctx;
+            t.eps = a->eps; t.scale = a->attn_scale; t.pdl = pdl;
+            if ((rc = tfb_attn_gated_decode(&t, stream))) return rc;
+            base(g); g.w = L.w_out; g.x = a->mixed_buf; g.residual = hid; g.y = att; g.n = H; g.k = QD;
+            g.prologue = TFB_NORM_NONE; g.epilogue = TFB_EPI_RESIDUAL;
+            if ((rc = tfb_gemv_f32(&g, stream))) return rc;
+        }
+        // ---- MoE block: router (+ the shared expert's scale row), selection, gate/up of 8 + 1 experts, down ----
+        base(g); g.w = L.w_router; g.x = att; g.gamma = L.gamma_post; g.y = a->router_logits; g.n = E + 1; g.k = H;
+        g.prologue = TFB_NORM_F32GAIN; g.epilogue = TFB_EPI_STORE;
+        if ((rc = tfb_gemv_f32(&g, stream))) return rc;
+        if ((rc = tfb_router_select(nullptr, a->router_logits, a->router_idx, nullptr, a->router_w, E, K, 1, pdl, stream)))
+            return rc;
+        if (a->idx_trace) {
+            e = tfb::copy_launch(a->router_idx, a->idx_trace + size_t(l) * K, K * 8, st, pdl != 0);
+            if (e != cudaSuccess) return fail_launch(e);
+        }
+        base(g); g.w = L.w_gate; g.w2 = L.w_up; g.w_extra = L.w_shared_gate; g.w2_extra = L.w_shared_up; g.x = att;
+        g.gamma = L.gamma_post; g.y = a->inner_buf; g.n = K * I + IS; g.k = H; g.prologue = TFB_NORM_F32GAIN;
+        g.epilogue = TFB_EPI_SWIGLU; g.expert_idx = a->router_idx; g.rows_per_expert = I; g.routed_slots = K;
+        if ((rc = tfb_gemv_f32(&g, stream))) return rc;
+        tfb_moe_down_f32_args d;
+        std::memset(&d, 0, sizeof d);
+        d.w_down = L.w_down; d.w_shared = L.w_shared_down; d.inner = a->inner_buf; d.indices = a->router_idx;
+        d.weights = a->router_w; d.shared_gate_logit = a->router_logits + E; d.residual = att; d.out = hid;
+        d.hidden = H; d.inter = I; d.shared_inter = IS; d.top_k = K; d.pdl = pdl;
+        if ((rc = tfb_moe_down_f32(&d, stream))) return rc;
+        if (a->hidden_trace) {
+            e = tfb::copy_launch(hid, a->hidden_trace + size_t(l) * H, H * 4, st, pdl != 0);
+            if (e != cudaSuccess) return fail_launch(e);
+        }
+    }
+    if (a->hidden_trace) {
+        e = tfb::rmsnorm_f32_launch(hid, a->gamma_final, a->hidden_trace + size_t(a->n_layers) * H, 1, H, a->eps, st, pdl != 0);
+        if (e != cudaSuccess) return fail_launch(e);
+    }
+    tfb_lm_head_args h;
+    std::memset(&h, 0, sizeof h);
+    h.w = a->w_head; h.x = hid; h.gamma = a->gamma_final; h.logits = a->logits;
+    h.scratch_val = a->head_val; h.scratch_idx = a->head_idx; h.counter = a->counters + a->hkv;
+    h.n = int(a->vocab); h.k = H; h.prologue = TFB_NORM_F32_INPUT; h.eps = a->eps;
+    h.x_scale = 1.f; h.out_scale = 1.f; h.pdl = pdl; h.token_out = a->picked;
+    h.tokens = a->tokens; h.pos = a->pos; h.n_prompt = a->n_prompt; h.max_tokens = a->max_tokens;
+    return tfb_lm_head_argmax(&h, stream);
+}
+
+}  // extern "C"

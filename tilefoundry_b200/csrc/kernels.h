@@ -182,4 +182,87 @@ struct MoeDownParams {
 };
 cudaError_t moe_down_launch(const MoeDownParams& p, cudaStream_t stream, bool pdl);
 
+// ---- f32-activation family (Qwen3.5) ----
+struct GemvF32Params {
+    const uint4* w;
+    const uint4* w2;
+    const uint4* w_extra;            // expert mode: rows of the slots past the routed ones (the shared expert)
+    const uint4* w2_extra;
+    const float* x;
+    const float* gamma;
+    const float* gate;               // prologue 4: the vector whose silu multiplies the normalised x
+    const float* residual;
+    float* y;
+    int n, k, seg;
+    float eps;
+    const long long* expert_idx;
+    int rows_per_expert, routed_slots;
+    unsigned long long* trace;
+};
+cudaError_t gemv_f32_dispatch(const GemvF32Params& p, int norm_mode, int epi, cudaStream_t stream, bool pdl);
+
+struct GdnParams {
+    const float* proj;          // [2*hk*dk + hv*dv] conv entry | [hv*dv] z | [hv] b | [hv] a
+    float* conv_state;          // two buffers of [channels][width-1], conv_state_stride floats apart
+    size_t conv_state_stride;
+    const int* pos;             // parity picks the buffer read; null: read buffer 0, write buffer 1
+    const float* conv_w;        // [channels][width]
+    const float* a_log;         // [hv]
+    const float* dt_bias;       // [hv]
+    float* state;               // [hv][dk][dv], updated in place
+    float* read;                // [hv*dv]
+    int hk, hv, dk, dv, kernel_width;
+    float q_scale;
+    // optional: q [hv][dk], k [hv][dk], v [hv][dv], g [hv], beta [hv] handed in (conv, norms and scalars skipped)
+    const float* direct_q; const float* direct_k; const float* direct_v; const float* direct_g; const float* direct_beta;
+};
+cudaError_t conv_silu_f32_launch(const float* state, const float* entry, const float* conv_w, float* mixed, int channels,
+                                 int width, cudaStream_t stream, bool pdl);
+cudaError_t l2norm_f32_launch(const float* x, float* y, int rows, int width, float eps, cudaStream_t stream, bool pdl);
+cudaError_t partial_rope_f32_launch(const float* x, const float* cos_table, const float* sin_table, const int* pos,
+                                    float* out, int heads, int d, int rd, cudaStream_t stream, bool pdl);
+cudaError_t gdn_step_launch(const GdnParams& p, cudaStream_t stream, bool pdl);
+
+struct GatedAttnParams {
+    const float* proj;          // [hq][2*d] q|gate per head, then [hkv][d] k, then [hkv][d] v
+    const float* gamma_q;
+    const float* gamma_k;
+    const float* cos_table;     // [max_ctx][rotary_dim]
+    const float* sin_table;
+    const int* pos;
+    const int* rope_pos;
+    float* k_pool;              // [page][slot][hkv][d]
+    float* v_pool;
+    const int* block_table;
+    float* out;                 // [hq*d] gated attention output
+    float* k_new_out;
+    float* v_new_out;
+    float* part_o;
+    float* part_ml;
+    unsigned* counters;
+    int hq, hkv, d, rotary_dim, page_size, max_ctx, nsplit;
+    float eps, scale;
+};
+int attn_gated_splits(int max_ctx);
+cudaError_t attn_gated_dispatch(const GatedAttnParams& p, cudaStream_t stream, bool pdl);
+
+struct MoeDownF32Params {
+    const uint4* w_down;        // [experts][hidden][inter]
+    const uint4* w_shared;      // [hidden][shared_inter] or null
+    const float* inner;         // [top_k][inter] then [shared_inter]
+    const long long* indices;
+    const float* weights;       // [top_k]
+    const float* shared_gate_logit;
+    const float* residual;
+    float* out;
+    int hidden, inter, shared_inter, top_k;
+};
+cudaError_t moe_down_f32_launch(const MoeDownF32Params& p, cudaStream_t stream, bool pdl);
+
+cudaError_t embed_f32_launch(const uint16_t* table, const long long* ids, const long long* tokens, const int* pos,
+                             float* out, int rows, int hidden, long long vocab, cudaStream_t stream, bool pdl);
+cudaError_t rmsnorm_f32_launch(const float* x, const float* gamma, float* y, int rows, int width, float eps,
+                               cudaStream_t stream, bool pdl);
+cudaError_t residual_add_f32_launch(const float* a, const float* b, float* out, int n, cudaStream_t stream, bool pdl);
+
 }  // namespace tfb

@@ -107,6 +107,20 @@ __device__ __forceinline__ void argmax_merge(float& v, int& i, float ov, int oi)
     if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
 }
 
+// f32 hidden state with an f32 gain, rounded to bf16 once on its way into the product (mode 5).
+__device__ __forceinline__ void stage_head_f32(const float* __restrict__ x, const float* __restrict__ gamma, float* xs,
+                                               float* red, int k, float eps) {
+    if (gamma == nullptr) {                          // already normalised
+        for (int i = threadIdx.x; i < k; i += blockDim.x) xs[xs_index(i)] = round_bf16(x[i]);
+        return;
+    }
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < k; i += blockDim.x) { const float v = x[i]; ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, red);
+    const float rstd = rsqrtf(ss / float(k) + eps);
+    for (int i = threadIdx.x; i < k; i += blockDim.x) xs[xs_index(i)] = round_bf16(x[i] * rstd * gamma[i]);
+}
+
 template <int NORM_MODE>
 __global__ void __launch_bounds__(kHeadWarps * 32) lm_head_kernel(const HeadParams p) {
     extern __shared__ __align__(16) float smem[];
@@ -128,7 +142,10 @@ __global__ void __launch_bounds__(kHeadWarps * 32) lm_head_kernel(const HeadPara
     pdl_trigger();
     pdl_wait();
     trace_waited(p.trace);
-    stage_activation<NORM_MODE>(p.x, p.gamma, xs, red, p.k, p.eps, p.x_scale);
+    if (NORM_MODE == 5)
+        stage_head_f32(reinterpret_cast<const float*>(p.x), reinterpret_cast<const float*>(p.gamma), xs, red, p.k, p.eps);
+    else
+        stage_activation<(NORM_MODE == 5 ? 0 : NORM_MODE)>(p.x, p.gamma, xs, red, p.k, p.eps, p.x_scale);
     __syncthreads();
 
     float acc[kHeadRows];
@@ -198,7 +215,54 @@ cudaError_t lm_head_dispatch(const HeadParams& p, int norm_mode, cudaStream_t st
     if (norm_mode == 0) return launch_kernel(lm_head_kernel<0>, grid, block, smem, stream, pdl, p);
     if (norm_mode == 1) return launch_kernel(lm_head_kernel<1>, grid, block, smem, stream, pdl, p);
     if (norm_mode == 2) return launch_kernel(lm_head_kernel<2>, grid, block, smem, stream, pdl, p);
+    if (norm_mode == 5) return launch_kernel(lm_head_kernel<5>, grid, block, smem, stream, pdl, p);
     return cudaErrorInvalidValue;
+}
+
+// ---- f32-activation helpers (embedding rows widened, RMSNorm with an f32 gain, plain add) ----
+__global__ void embed_f32_kernel(const uint16_t* __restrict__ table, const long long* __restrict__ ids,
+                                 const long long* __restrict__ tokens, const int* __restrict__ pos,
+                                 float* __restrict__ out, int hidden, long long vocab) {
+    pdl_trigger();
+    pdl_wait();
+    long long id = tokens ? tokens[*pos] : ids[blockIdx.x];
+    if (id < 0) id = 0;
+    if (id >= vocab) id = vocab - 1;
+    const uint16_t* src = table + size_t(id) * hidden;
+    float* dst = out + size_t(blockIdx.x) * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = bf16_bits_to_f32(src[i]);
+}
+cudaError_t embed_f32_launch(const uint16_t* table, const long long* ids, const long long* tokens, const int* pos,
+                             float* out, int rows, int hidden, long long vocab, cudaStream_t stream, bool pdl) {
+    return launch_kernel(embed_f32_kernel, dim3(rows), dim3(256), 0, stream, pdl, table, ids, tokens, pos, out, hidden, vocab);
+}
+
+__global__ void rmsnorm_f32_kernel(const float* __restrict__ x, const float* __restrict__ gamma, float* __restrict__ y,
+                                   int width, float eps) {
+    __shared__ float red[32];
+    pdl_trigger();
+    pdl_wait();
+    const float* xr = x + size_t(blockIdx.x) * width;
+    float* yr = y + size_t(blockIdx.x) * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
+    ss = block_sum(ss, red);
+    const float rstd = rsqrtf(ss / float(width) + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) yr[i] = xr[i] * rstd * gamma[i];
+}
+cudaError_t rmsnorm_f32_launch(const float* x, const float* gamma, float* y, int rows, int width, float eps,
+                               cudaStream_t stream, bool pdl) {
+    return launch_kernel(rmsnorm_f32_kernel, dim3(rows), dim3(256), 0, stream, pdl, x, gamma, y, width, eps);
+}
+
+__global__ void residual_add_f32_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out, int n) {
+    pdl_trigger();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = a[i] + b[i];
+}
+cudaError_t residual_add_f32_launch(const float* a, const float* b, float* out, int n, cudaStream_t stream, bool pdl) {
+    return launch_kernel(residual_add_f32_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, pdl, a, b, out, n);
 }
 
 }  // namespace tfb

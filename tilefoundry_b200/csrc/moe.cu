@@ -227,4 +227,86 @@ cudaError_t moe_down_launch(const MoeDownParams& p, cudaStream_t stream, bool pd
     return launch_kernel(moe_down_kernel, grid, block, smem, stream, pdl, p);
 }
 
+// f32-activation form (examples/qwen3_5_35b_a3b-tilelang/model.py:502-612): each expert product is rounded
+// to bf16 and carried on in f32; the routing weights, the weighted sum over slots, the shared expert's
+// sigmoid gate and the residual are f32 with no further rounding.
+//   out[j] = residual[j] + sum_s w[s] * bf16(w_down[idx[s]][j,:] . bf16(inner[s,:]))
+//                        + bf16(w_shared[j,:] . bf16(inner[top_k,:])) * sigmoid(*shared_gate_logit)
+// `inner` holds top_k routed slots followed by the shared expert's slot, already rounded to bf16 values.
+__global__ void __launch_bounds__(kDownWarps * 32) moe_down_f32_kernel(const MoeDownF32Params p) {
+    extern __shared__ __align__(16) float smem[];
+    float* xin = smem;                                        // [top_k][inter] then [shared_inter]
+    __shared__ long long s_idx[32];
+    __shared__ float s_w[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int j = blockIdx.x * kDownWarps + warp;
+    const int I = p.inter, IS = p.shared_inter, K = p.top_k;
+
+    const int sh_pieces = IS >> 3;
+    uint4 shw[4];
+    const uint4* shrow = (p.w_shared && j < p.hidden) ? p.w_shared + size_t(j) * sh_pieces : nullptr;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) shw[u] = (shrow && lane + 32 * u < sh_pieces) ? ld_stream16(shrow + lane + 32 * u) : make_uint4(0, 0, 0, 0);
+    pdl_trigger();
+    pdl_wait();
+
+    const float res = (p.residual && j < p.hidden) ? p.residual[j] : 0.f;
+    if (threadIdx.x < K) { s_idx[threadIdx.x] = p.indices[threadIdx.x]; s_w[threadIdx.x] = p.weights[threadIdx.x]; }
+    for (int i = threadIdx.x * 4; i < K * I + IS; i += blockDim.x * 4)
+        *reinterpret_cast<float4*>(xin + i) = *reinterpret_cast<const float4*>(p.inner + i);
+    __syncthreads();
+    if (j >= p.hidden) return;
+
+    float routed = 0.f;
+    const int pieces = I >> 3;
+    for (int s = 0; s < K; ++s) {
+        const uint4* row = p.w_down + (size_t(s_idx[s]) * p.hidden + j) * pieces;
+        const float* x = xin + s * I;
+        float acc = 0.f;
+        for (int c = lane; c < pieces; c += 32) {
+            const uint4 w = ld_stream16(row + c);
+            const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
+            acc = dot8(w, xa, xb, acc);
+        }
+        acc = warp_sum(acc);
+        routed = fmaf(round_bf16(acc), s_w[s], routed);
+    }
+    float out = routed;
+    if (shrow) {
+        const float* x = xin + K * I;
+        float acc = 0.f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int c = lane + 32 * u;
+            if (c < sh_pieces) {
+                const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
+                acc = dot8(shw[u], xa, xb, acc);
+            }
+        }
+        for (int c = lane + 128; c < sh_pieces; c += 32) {
+            const uint4 w = ld_stream16(shrow + c);
+            const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
+            acc = dot8(w, xa, xb, acc);
+        }
+        float sh = round_bf16(warp_sum(acc));
+        if (p.shared_gate_logit) sh *= 1.f / (1.f + expf(-*p.shared_gate_logit));
+        out += sh;
+    }
+    if (lane == 0) p.out[j] = res + out;
+}
+
+cudaError_t moe_down_f32_launch(const MoeDownF32Params& p, cudaStream_t stream, bool pdl) {
+    const size_t smem = (size_t(p.top_k) * p.inter + p.shared_inter) * sizeof(float);
+    if (smem > 48 * 1024) {
+        static bool once = false;
+        if (!once) {
+            cudaError_t e = cudaFuncSetAttribute(moe_down_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+            if (e != cudaSuccess) return e;
+            once = true;
+        }
+    }
+    const dim3 grid((p.hidden + kDownWarps - 1) / kDownWarps), block(kDownWarps * 32);
+    return launch_kernel(moe_down_f32_kernel, grid, block, smem, stream, pdl, p);
+}
+
 }  // namespace tfb

@@ -16,6 +16,7 @@ import os
 LIB_PATH = Path(os.environ.get("TFB200_LIB") or Path(__file__).resolve().parent / "csrc" / "libtfb200.so")
 
 NORM_NONE, NORM_F32GAIN, NORM_CAST_THEN_GAIN, NORM_GATED = 0, 1, 2, 3
+NORM_SEGMENT_GATED, NORM_F32_INPUT = 4, 5
 EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU, EPI_STORE_F32 = 0, 1, 2, 3
 
 _vp, _i32, _i64, _u64, _f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_uint64, C.c_float
@@ -121,6 +122,56 @@ class GraniteStepArgs(C.Structure):
 
 
 #: every symbol ``include/tfb200.h`` declares: name -> (restype, argtypes)
+class GemvF32Args(C.Structure):
+    _fields_ = [("w", _vp), ("w2", _vp), ("w_extra", _vp), ("w2_extra", _vp), ("x", _vp), ("gamma", _vp), ("gate", _vp),
+                ("residual", _vp), ("y", _vp), ("n", _i32), ("k", _i32), ("seg", _i32), ("prologue", _i32),
+                ("epilogue", _i32), ("eps", _f32), ("expert_idx", _vp), ("rows_per_expert", _i32),
+                ("routed_slots", _i32), ("pdl", _i32), ("reserved", _i32)]
+
+
+class GdnArgs(C.Structure):
+    _fields_ = [("proj", _vp), ("conv_state", _vp), ("conv_state_stride", _u64), ("pos", _vp), ("conv_w", _vp),
+                ("a_log", _vp), ("dt_bias", _vp), ("state", _vp), ("read", _vp), ("hk", _i32), ("hv", _i32), ("dk", _i32),
+                ("dv", _i32), ("kernel_width", _i32), ("q_scale", _f32), ("pdl", _i32), ("reserved", _i32),
+                ("direct_q", _vp), ("direct_k", _vp), ("direct_v", _vp), ("direct_g", _vp), ("direct_beta", _vp)]
+
+
+class AttnGatedArgs(C.Structure):
+    _fields_ = [("proj", _vp), ("gamma_q", _vp), ("gamma_k", _vp), ("cos_table", _vp), ("sin_table", _vp), ("pos", _vp),
+                ("rope_pos", _vp), ("k_pool", _vp), ("v_pool", _vp), ("block_table", _vp), ("out", _vp),
+                ("k_new_out", _vp), ("v_new_out", _vp), ("part_o", _vp), ("part_ml", _vp), ("counters", _vp),
+                ("hq", _i32), ("hkv", _i32), ("d", _i32), ("rotary_dim", _i32), ("page_size", _i32), ("table_len", _i32),
+                ("max_ctx", _i32), ("max_pos", _i32), ("eps", _f32), ("scale", _f32), ("pdl", _i32), ("reserved", _i32)]
+
+
+class MoeDownF32Args(C.Structure):
+    _fields_ = [("w_down", _vp), ("w_shared", _vp), ("inner", _vp), ("indices", _vp), ("weights", _vp),
+                ("shared_gate_logit", _vp), ("residual", _vp), ("out", _vp), ("hidden", _i32), ("inter", _i32),
+                ("shared_inter", _i32), ("top_k", _i32), ("pdl", _i32), ("reserved", _i32)]
+
+
+class Qwen35Layer(C.Structure):
+    _fields_ = [("kind", _i32), ("reserved", _i32), ("gamma_in", _vp), ("w_in", _vp), ("w_out", _vp), ("conv_w", _vp),
+                ("a_log", _vp), ("dt_bias", _vp), ("gamma_gdn", _vp), ("conv_state", _vp), ("state", _vp),
+                ("gamma_q", _vp), ("gamma_k", _vp), ("k_pool", _vp), ("v_pool", _vp), ("gamma_post", _vp),
+                ("w_router", _vp), ("w_gate", _vp), ("w_up", _vp), ("w_down", _vp), ("w_shared_gate", _vp),
+                ("w_shared_up", _vp), ("w_shared_down", _vp)]
+
+
+class Qwen35StepArgs(C.Structure):
+    _fields_ = [("layers", C.POINTER(Qwen35Layer)), ("n_layers", _i32), ("pdl", _i32), ("table", _vp),
+                ("gamma_final", _vp), ("w_head", _vp), ("cos_table", _vp), ("sin_table", _vp), ("tokens", _vp),
+                ("pos", _vp), ("n_prompt", _i32), ("max_tokens", _i32), ("block_table", _vp), ("page_size", _i32),
+                ("table_len", _i32), ("max_ctx", _i32), ("hidden", _i32), ("vocab", _i64), ("hk", _i32), ("hv", _i32),
+                ("dk", _i32), ("dv", _i32), ("conv_width", _i32), ("hq", _i32), ("hkv", _i32), ("d", _i32),
+                ("rotary_dim", _i32), ("experts", _i32), ("top_k", _i32), ("inter", _i32), ("shared_inter", _i32),
+                ("conv_state_stride", _u64), ("eps", _f32), ("attn_scale", _f32), ("q_scale", _f32),
+                ("hidden_buf", _vp), ("attended_buf", _vp), ("proj_buf", _vp), ("mixed_buf", _vp),
+                ("router_logits", _vp), ("router_idx", _vp), ("router_w", _vp), ("inner_buf", _vp), ("part_o", _vp),
+                ("part_ml", _vp), ("counters", _vp), ("head_val", _vp), ("head_idx", _vp), ("logits", _vp),
+                ("picked", _vp), ("hidden_trace", _vp), ("idx_trace", _vp)]
+
+
 SYMBOLS = {
     "tfb_version": (_i32, []),
     "tfb_status_string": (C.c_char_p, [_i32]),
@@ -145,6 +196,18 @@ SYMBOLS = {
     "tfb_granite_decode_step": (_i32, [C.POINTER(GraniteStepArgs), _vp]),
     "tfb_granite_step_part": (_i32, [C.POINTER(GraniteStepArgs), _i32, _i32, _vp]),
     "tfb_moe_finalize": (_i32, [_vp, _vp, _vp, _i32, _f32, _i32, _i32, _vp]),
+    "tfb_gemv_f32": (_i32, [C.POINTER(GemvF32Args), _vp]),
+    "tfb_gdn_step": (_i32, [C.POINTER(GdnArgs), _vp]),
+    "tfb_conv_silu_f32": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
+    "tfb_l2norm_f32": (_i32, [_vp, _vp, _i32, _i32, _f32, _i32, _vp]),
+    "tfb_partial_rope_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
+    "tfb_attn_gated_splits": (_i32, [_i32]),
+    "tfb_attn_gated_decode": (_i32, [C.POINTER(AttnGatedArgs), _vp]),
+    "tfb_moe_down_f32": (_i32, [C.POINTER(MoeDownF32Args), _vp]),
+    "tfb_embed_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _i64, _i32, _vp]),
+    "tfb_rmsnorm_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _f32, _i32, _vp]),
+    "tfb_residual_add_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp]),
+    "tfb_qwen35_decode_step": (_i32, [C.POINTER(Qwen35StepArgs), _vp]),
     "tfb_pick_finalize": (_i32, [_vp, _i32, _vp, _vp, _i32, _i32, _vp, _i32, _vp]),
 }
 
