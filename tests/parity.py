@@ -69,3 +69,31 @@ def compare_caches(want, sess, total):
         v_got = paged_kv.logical_view(sess.layers[li]["v_pool"], sess.table[0], total)
         assert_close_at_scale(k_got, k_ref[:, :total], f"layer {li} K cache")
         assert_close_at_scale(v_got, v_ref[:, :total], f"layer {li} V cache")
+
+
+def nested_walk(ref, cfg_kinds, forced, steps):
+    """Teacher-forced oracle walk of a root -> layer -> (mixer | moe -> router) model, one step at a time.
+    Yields ``(step, caches_before, logits, hidden per layer, routing indices per layer, routing margin per
+    layer, caches_after)``; the margin is the relative gap between the last selected expert's probability and
+    the best one left out -- a routing pick inside the arithmetic noise shows as a margin near zero."""
+    from tilefoundry_b200.authored.granite_4_0_h_small import _with_cache
+    caches = ref.init_caches()
+    for step in range(steps):
+        token_ids, layer_args, caches_in = ref.prepare_inputs_for_generation(forced[: step + 1], step, caches)
+        hidden = ref.embed(token_ids)
+        fresh, hiddens, picks, margins = [], [], [], []
+        for layer, margs, cache in zip(ref.modules, layer_args, caches_in):
+            mixed, *state = layer.mixer(hidden, *_with_cache(layer.mixer, margs, cache))
+            attended = layer.residual_add(hidden, mixed)
+            tokens = layer.moe.post_norm(attended)
+            rw, idx = layer.moe.router.routing(tokens)
+            hidden = layer.residual_add(attended, layer.moe.experts(tokens, rw, idx))
+            fresh.append(tuple(state))
+            hiddens.append(hidden.reshape(-1))
+            picks.append(idx.reshape(-1))
+            logits = torch.matmul(tokens.to(torch.bfloat16), layer.moe.router.constants["w_router"]).float().reshape(-1)
+            top = torch.topk(logits, idx.numel() + 1).values
+            margins.append(float(top[-2] - top[-1]))
+        after = ref.append_cache(caches, tuple(fresh))
+        yield step, caches, ref.lm_head(ref.final_rms_norm(hidden)), hiddens, picks, margins, after
+        caches = after

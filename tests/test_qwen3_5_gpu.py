@@ -111,53 +111,108 @@ def test_root_functions(dev, sides):
     assert int(twin.last_token) == int(torch.argmax(twin.lm_head(normed.to(dev))))
 
 
-@pytest.mark.parametrize("use_graph", [False, True])
-def test_session_matches_evaluator_tiny(dev, use_graph):
-    """Teacher-forced run of the whole hybrid stack: logits within the end-to-end bound at every step, greedy
-    picks equal except inside the measured noise, recurrent state, convolution windows and KV cache as the
-    evaluator left them."""
+def _setup(dev, max_new, seed=11):
     from tilefoundry_b200.engine.qwen3_5 import Qwen35Session
-    from tilefoundry_b200.engine import paged_kv
     cfg = qa.QWEN3_5_TINY
     mod = qa.build(cfg)
-    weights = random_weights(mod, seed=11, std=0.05, overrides=qa.weight_overrides)
+    weights = random_weights(mod, seed=seed, std=0.05, overrides=qa.weight_overrides)
     ref = evaluator.load(mod, DictResource(weights), oq.make(cfg))
-    n_prompt, n_new = 16, 80
+    n_prompt = 16
     prompt = torch.randint(0, cfg.vocab, (n_prompt,), generator=torch.Generator().manual_seed(111))
-    want = generation.decode_ids(ref, prompt, n_new, keep_logits=True)
+    want = generation.decode_ids(ref, prompt, max_new)
     forced = torch.cat([prompt, torch.tensor(want["tokens"], dtype=torch.int64)])
-    sess = Qwen35Session(cfg, DictResource(parity.cuda_weights(weights, dev)), max_ctx=n_prompt + n_new + 5, device=dev,
+    sess = Qwen35Session(cfg, DictResource(parity.cuda_weights(weights, dev)), max_ctx=n_prompt + max_new + 5, device=dev,
                          keep_logits=True, trace_hidden=True)
     sess.reset(forced)
+    return cfg, ref, sess, forced, n_prompt + max_new - 1
+
+
+def _load_state(sess, cfg, caches, step):
+    """Put the evaluator's caches into the session (the state the step at position *step* reads)."""
+    from tilefoundry_b200.engine import paged_kv
+    sess.pos.fill_(step)
+    for layer, kind, state in zip(sess.layers, cfg.layer_types, caches):
+        if kind == "linear_attention":
+            layer["conv_state"][step & 1].copy_(state[0][0])
+            layer["state"].copy_(state[1][0])
+        else:
+            paged_kv.fill_from_logical(layer["k_pool"], sess.table[0], state[0])
+            paged_kv.fill_from_logical(layer["v_pool"], sess.table[0], state[1])
+
+
+def _same_experts(sess, picks):
+    got = sess.idx_trace.cpu()
+    return [sorted(got[li].tolist()) == sorted(p.tolist()) for li, p in enumerate(picks)]
+
+
+# A routing pick is decided by bf16 router logits computed from inputs that already differ by the arithmetic
+# noise of the layers below: two logits closer than this may legitimately come out in the other order.
+TIE_MARGIN = 3e-2
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_step_matches_evaluator_from_its_own_state(dev, use_graph):
+    """Every step starts from the evaluator's caches, so one step of the whole hybrid stack is judged at a
+    time: per-layer hidden states, logits, routed experts, and the state the step leaves behind.  A step in
+    which a router pick differs is accepted only if the evaluator's own margin for that pick is a near-tie."""
+    from tilefoundry_b200.engine import paged_kv
+    cfg, ref, sess, forced, total = _setup(dev, 60)
     if use_graph:
         sess.capture()
-    total = n_prompt + n_new - 1
-    mismatched = 0
-    for step in range(total):
+    excused = 0
+    for step, before, logits, hiddens, picks, margins, after in parity.nested_walk(ref, cfg.layer_types, forced, total):
+        _load_state(sess, cfg, before, step)
         sess.run(1, use_graph)
-        ref_logits = want["logits"][step][0]
-        assert_close_at_scale(sess.logits, ref_logits, f"logits step {step}")
+        same = _same_experts(sess, picks)
+        if not all(same):
+            first = same.index(False)                # layers above it see a different input: only the first is judged
+            assert margins[first] <= TIE_MARGIN, f"step {step}: experts differ at layer {first}, margins {margins}"
+            for li in range(first):
+                assert_close_at_scale(sess.trace[li], hiddens[li], f"step {step} layer {li} hidden")
+            excused += 1
+            continue
+        for li, h in enumerate(hiddens):
+            assert_close_at_scale(sess.trace[li], h, f"step {step} layer {li} hidden")
+        assert_close_at_scale(sess.logits, logits[0], f"logits step {step}")
         assert int(sess.picked) == int(torch.argmax(sess.logits.float())), f"step {step}: pick is not argmax"
-        if int(sess.picked) != int(torch.argmax(ref_logits)):
-            top = torch.topk(ref_logits.float(), 2).values
-            noise = (sess.logits.float().cpu() - ref_logits.float()).abs().max()
-            assert float(top[0] - top[1]) <= 2 * float(noise), f"pick differs at step {step}"
-            mismatched += 1
-    assert mismatched <= 6
+        assert int(sess.pos) == step + 1
+        for li, (kind, state) in enumerate(zip(cfg.layer_types, after)):
+            layer = sess.layers[li]
+            if kind == "linear_attention":
+                assert_close_at_scale(sess.conv_window(layer), state[0][0], f"step {step} layer {li} conv window")
+                assert_close_at_scale(layer["state"], state[1][0], f"step {step} layer {li} recurrent state")
+            else:
+                n = step + 1
+                for name, want_cache in (("k_pool", state[0]), ("v_pool", state[1])):
+                    got = paged_kv.logical_view(layer[name], sess.table[0], n)
+                    assert_close_at_scale(got[:, -1], want_cache[:, n - 1], f"step {step} layer {li} new {name} row")
+    assert excused <= total // 5, f"{excused} of {total} steps had a routing near-tie"
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_free_running_session_tracks_evaluator(dev, use_graph):
+    """The session keeps its own state over the whole walk.  Until the first routing near-tie resolves the
+    other way the comparison is the strict one; after it the two trajectories are different (equally valid)
+    roundings of one sequence and must stay close in direction."""
+    from tilefoundry_b200.engine import paged_kv
+    cfg, ref, sess, forced, total = _setup(dev, 60)
+    if use_graph:
+        sess.capture()
+    diverged_at = None
+    for step, _, logits, hiddens, picks, margins, _ in parity.nested_walk(ref, cfg.layer_types, forced, total):
+        sess.run(1, use_graph)
+        if diverged_at is None and not all(_same_experts(sess, picks)):
+            diverged_at = step
+        if diverged_at is None:
+            assert_close_at_scale(sess.logits, logits[0], f"logits step {step}")
+            for li, h in enumerate(hiddens):
+                assert_close_at_scale(sess.trace[li], h, f"step {step} layer {li} hidden")
+        else:
+            cos = torch.nn.functional.cosine_similarity(sess.logits.float().cpu().flatten(), logits[0].flatten(), dim=0)
+            assert float(cos) >= 0.97, f"step {step} (routing diverged at {diverged_at}): logits cosine {float(cos):.4f}"
+    assert diverged_at is None or diverged_at >= 5, f"routing diverged at step {diverged_at}"
     assert int(sess.pos) == total
     assert torch.equal(sess.table.cpu(), paged_kv.block_table(1, sess.max_ctx))
-    for li, (kind, state) in enumerate(zip(cfg.layer_types, want["caches"])):
-        layer = sess.layers[li]
-        if kind == "linear_attention":
-            window, matrix = state
-            assert_close_at_scale(sess.conv_window(layer), window[0], f"layer {li} conv window")
-            assert_close_at_scale(layer["state"], matrix[0], f"layer {li} recurrent state after {total} steps")
-        else:
-            k_ref, v_ref = state
-            assert_close_at_scale(paged_kv.logical_view(layer["k_pool"], sess.table[0], total), k_ref[:, :total],
-                                  f"layer {li} K cache")
-            assert_close_at_scale(paged_kv.logical_view(layer["v_pool"], sess.table[0], total), v_ref[:, :total],
-                                  f"layer {li} V cache")
 
 
 def test_generate_equals_stepwise_and_replays(dev):

@@ -207,7 +207,3 @@ def weight_overrides(name, ty, gen):
         return torch.randn(tuple(ty.shape), generator=gen) * 0.3
     return None
 
-
-def tie_head(weights: dict) -> dict:
-    """This model's head is its own matrix; nothing is tied (kept so the workloads share one call shape)."""
-    return weights

@@ -256,9 +256,11 @@ int tfb_qwen3_decode_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
     uint16_t* hid = static_cast<uint16_t*>(a->hidden_buf);
     uint16_t* trace = static_cast<uint16_t*>(a->hidden_trace);
 
+    // The step's first launch carries no programmatic dependency: it starts only when the previous step has
+    // fully finished, so kernels of this step may read last step's state and position before their own wait.
     cudaError_t e = tfb::embed_launch(static_cast<const uint16_t*>(a->w_embed), nullptr,
                                       reinterpret_cast<const long long*>(a->tokens), a->pos, hid, 1, H,
-                                      a->vocab, 1.f, st, pdl);
+                                      a->vocab, 1.f, st, false);
     if (e != cudaSuccess) return fail_launch(e);
 
     for (int l = 0; l < a->n_layers; ++l) {

@@ -128,8 +128,10 @@ static int granite_part(const tfb_granite_step_args* a, int part, int layer, tfb
 
     cudaError_t e = cudaSuccess;
     if (part == 0) {
+        // The step's first launch carries no programmatic dependency: it starts only when the previous step has
+        // fully finished, so kernels of this step may read last step's state and position before their own wait.
         e = tfb::embed_launch(cu16(a->table), nullptr, reinterpret_cast<const long long*>(a->tokens), a->pos, hid, 1, H,
-                              a->vocab, a->embed_scale, st, pdl);
+                              a->vocab, a->embed_scale, st, false);
         return done(e);
     }
     if (part == 2) {

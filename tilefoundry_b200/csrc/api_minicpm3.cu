@@ -57,9 +57,11 @@ int tfb_minicpm3_decode_step(const tfb_minicpm3_step_args* a, tfb_stream_t strea
     uint16_t* qkv_a = static_cast<uint16_t*>(a->qkv_a_buf);
     uint16_t* trace = static_cast<uint16_t*>(a->hidden_trace);
 
+    // The step's first launch carries no programmatic dependency: it starts only when the previous step has
+    // fully finished, so kernels of this step may read last step's state and position before their own wait.
     cudaError_t e = tfb::embed_launch(static_cast<const uint16_t*>(a->w_embed), nullptr,
                                       reinterpret_cast<const long long*>(a->tokens), a->pos, hid, 1, H,
-                                      a->vocab, a->embed_scale, st, pdl);
+                                      a->vocab, a->embed_scale, st, false);
     if (e != cudaSuccess) return fail_launch(e);
 
     auto gemv = [&](const void* w, const void* w2, const void* x, const void* gamma, const void* res, void* y,

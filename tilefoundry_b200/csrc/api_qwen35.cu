@@ -150,9 +150,11 @@ int tfb_qwen35_decode_step(const tfb_qwen35_step_args* a, tfb_stream_t stream) {
     cudaStream_t st = S(stream);
     float* hid = a->hidden_buf;
     float* att = a->attended_buf;
+    // The step's first launch carries no programmatic dependency: it starts only when the previous step has
+    // fully finished, so kernels of this step may read last step's state and position before their own wait.
     cudaError_t e = tfb::embed_f32_launch(static_cast<const uint16_t*>(a->table), nullptr,
                                           reinterpret_cast<const long long*>(a->tokens), a->pos, hid, 1, H, a->vocab, st,
-                                          pdl != 0);
+                                          false);
     if (e != cudaSuccess) return fail_launch(e);
     int rc;
     tfb_gemv_f32_args g;
