@@ -307,6 +307,11 @@ def run_ours(args):
     sess = work.session_cls(cfg, DictResource(work.device_weights(dev, seed=0)), max_ctx=max_ctx, device=dev, **extra)
     units = 1 if sharded else world                           # sequences decoded per step over all ranks
     sess.reset(prompt)
+    if args.dominant_only:
+        name, ms_launch, nbytes = dominant_kernel(work, sess)
+        print(json.dumps({"kernel": name, "us_per_launch": ms_launch * 1e3, "algorithmic_bytes_per_launch": nbytes,
+                          "achieved_gbs": nbytes / (ms_launch * 1e-3) / 1e9}))
+        return
     sess.capture()
 
     def barrier():
@@ -420,6 +425,9 @@ def main():
                     choices=["qwen3_1_7b", "minicpm3_4b", "granite_4_0_h_small", "qwen3_5_35b_a3b"],
                     help="which BASELINE.json configuration to run (default: the one the metric is quoted on)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--dominant-only", action="store_true",
+                    help="build the session, time only the dominant kernel over every layer's weights, print it and exit "
+                         "(the small case a profiler capture of that kernel runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

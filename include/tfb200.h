@@ -100,7 +100,10 @@ enum { TFB_EPI_STORE = 0, TFB_EPI_RESIDUAL = 1, TFB_EPI_SWIGLU = 2, TFB_EPI_STOR
  * streaming loads (what AUTO picks: it measured faster at every decode shape on B200), and a
  * persistent one-CTA-per-SM kernel that streams weights through a shared-memory ring filled by
  * bulk async copies (cp.async.bulk + mbarrier), kept selectable for A/B measurement. */
-enum { TFB_KERNEL_AUTO = 0, TFB_KERNEL_ROWS = 1, TFB_KERNEL_RING = 2 };
+enum { TFB_KERNEL_AUTO = 0, TFB_KERNEL_ROWS = 1, TFB_KERNEL_RING = 2,
+       TFB_KERNEL_PERSIST = 3, /* grid sized to residency, grid-stride tiles, two weight batches in flight */
+       TFB_KERNEL_ASYNC = 4,   /* one CTA per SM, weights land in a shared-memory ring through cp.async */
+       TFB_KERNEL_CHAIN = 5    /* decode steps only: o / gate+up / down (/ next q|k|v) of a layer as ONE persistent launch */ };
 typedef struct {
     const void* w;
     const void* w2;
@@ -277,6 +280,7 @@ typedef struct {
     int32_t l2_prefetch;    /* bit 0: each projection prefetches its own remaining rows; bit 1: the next projection's */
     int32_t kernel;         /* TFB_KERNEL_* for every projection of the step */
     int64_t* picked;        /* optional [1]: the token this step picked, whatever the prompt says */
+    uint32_t* chain_sync;   /* TFB_KERNEL_CHAIN: u32[4] zeroed once ([0..1] grid barrier, [2] status: non-zero if a wait gave up) */
 } tfb_qwen3_step_args;
 TFB_API int tfb_qwen3_decode_step(const tfb_qwen3_step_args* args, tfb_stream_t stream);
 
@@ -504,6 +508,20 @@ TFB_API int tfb_granite_decode_step(const tfb_granite_step_args* args, tfb_strea
  * gathered pairs.  With ep_world <= 1 parts 0, 1.., 3 are the whole step (what tfb_granite_decode_step runs). */
 TFB_API int tfb_granite_step_part(const tfb_granite_step_args* args, int32_t part, int32_t layer, tfb_stream_t stream);
 
+/* Up to 4 dependent projections (each reads the outputs of the one before) in one persistent cooperative launch of
+ * one CTA per SM; same arithmetic as tfb_gemv with prologue NONE / F32GAIN / CAST_THEN_GAIN and epilogue STORE /
+ * RESIDUAL / SWIGLU.  The weight stream runs ahead across the phase boundaries through a shared-memory ring.
+ * sync: u32[4] zeroed once by the caller; sync[2] is set non-zero if a bounded grid-barrier wait gave up (the
+ * outputs are then invalid; nothing hangs).  Every k a multiple of 256 and <= 8192; every n >= the SM count.
+ * No reference counterpart: the reference launches these projections one by one
+ * (examples/qwen3_1_7b-tilelang/fast/engine.py:189-271). */
+typedef struct {
+    tfb_gemv_args phase[4];
+    int32_t n_phases, pdl;
+    uint32_t* sync;
+} tfb_gemv_chain_args;
+TFB_API int tfb_gemv_chain(const tfb_gemv_chain_args* args, tfb_stream_t stream);
+
 /* ================= f32-activation family (Qwen3.5-35B-A3B) =================
  * The reference's Qwen3.5 example keeps activations, recurrent state and KV cache in f32 and its contracted
  * weights in bf16: a product casts its activation to bf16, runs at bf16 and casts the result back
@@ -528,6 +546,12 @@ typedef struct {
     const int64_t* expert_idx;
     int32_t rows_per_expert, routed_slots;
     int32_t pdl, reserved;
+    /* Router launch (TFB_EPI_STORE, no expert mode), optional: when route_counter is set the last CTA to finish
+     * selects route_top_k of the first route_experts outputs -- softmax over all, top-k, renormalise by the k (the
+     * routing function, model.py:488-499) -- into idx_out [route_top_k] and w_out [route_top_k], so the selection
+     * needs no launch of its own.  route_counter: u32 zeroed once by the caller; the kernel leaves it zero. */
+    uint32_t* route_counter; int32_t route_experts, route_top_k;
+    int64_t* idx_out; float* w_out;
 } tfb_gemv_f32_args;
 TFB_API int tfb_gemv_f32(const tfb_gemv_f32_args* args, tfb_stream_t stream);
 
@@ -564,7 +588,8 @@ TFB_API int tfb_partial_rope_f32(const float* x, const float* cos_table, const f
 /* Gated GQA decode attention over a paged f32 cache: per-head RMSNorm of q and k with f32 gains, rotate-half
  * RoPE on the leading rotary_dim (a multiple of 64) of each head, append at *pos, softmax over positions
  * 0..*pos, output times sigmoid(gate) (examples/qwen3_5_35b_a3b-tilelang/model.py:293-417).
- * proj = [hq][2*d] (q then gate per head) | [hkv][d] k | [hkv][d] v.  Pools are [page][page_size][hkv][d] f32.
+ * proj = [hq][2*d] (q then gate per head) | [hkv][d] k | [hkv][d] v.  Pools are [page][page_size][hkv][d] f32,
+ * page_size a multiple of 64.
  * Scratch: part_o f32 [hq * nsplit * d], part_ml f32 [hq * nsplit * 2], counters u32 [hkv] zeroed once, with
  * nsplit = tfb_attn_gated_splits(max_ctx). */
 typedef struct {
@@ -619,7 +644,8 @@ typedef struct {
 
 /* The whole captured step of the reference's engine for this model (embed -> layers -> final norm -> head ->
  * greedy pick -> bookkeeping; examples/qwen3_5_35b_a3b-tilelang/model.py:800-892 and runtime_model.py).
- * 7 launches per layer; token history and position live on the device as in tfb_qwen3_decode_step. */
+ * 7 launches per layer; token history
+ * and position live on the device as in tfb_qwen3_decode_step. */
 typedef struct {
     const tfb_qwen35_layer* layers; int32_t n_layers; int32_t pdl;
     const void* table; const float* gamma_final; const void* w_head;
@@ -634,7 +660,7 @@ typedef struct {
     float eps, attn_scale, q_scale;
     float* hidden_buf; float* attended_buf; float* proj_buf; float* mixed_buf;
     float* router_logits; int64_t* router_idx; float* router_w; float* inner_buf;
-    float* part_o; float* part_ml; uint32_t* counters; float* head_val; int32_t* head_idx;
+    float* part_o; float* part_ml; uint32_t* counters /* [hkv + 2], zeroed once */; float* head_val; int32_t* head_idx;
     void* logits; int64_t* picked;
     float* hidden_trace;      /* optional f32 [(n_layers + 1)][hidden]: every layer's output, then the final norm */
     int64_t* idx_trace;       /* optional [n_layers][top_k] */

@@ -227,3 +227,32 @@ def test_generate_equals_stepwise_and_replays(dev):
     b = sess.generate(prompt, 40, use_graph=False).tokens
     c = sess.generate(prompt, 40, use_graph=True).tokens
     assert a == b == c
+
+
+def test_router_projection_selects_experts_in_its_last_cta(dev):
+    """The router projection can select the top-k itself (last CTA to finish); that must give the very experts
+    and weights the stand-alone selection gives from the same logits, and leave its ticket at zero."""
+    import ctypes as C
+    from tilefoundry_b200 import lib
+    E, K, H = 256, 8, 2048
+    g = torch.Generator().manual_seed(21)
+    w_r = (torch.randn(E + 1, H, generator=g) * H ** -0.5).to(torch.bfloat16).to(dev)
+    w_r[200] = w_r[17]                                             # an exact tie resolves to the lower index
+    x, gamma = torch.randn(H, generator=g).to(dev), (1 + 0.1 * torch.randn(H, generator=g)).to(dev)
+    logits = torch.empty(E + 1, device=dev)
+    idx, w = torch.zeros(K, dtype=torch.int64, device=dev), torch.zeros(K, device=dev)
+    counter = torch.zeros(1, dtype=torch.int32, device=dev)
+    a = lib.GemvF32Args(w=lib.ptr(w_r), x=lib.ptr(x), gamma=lib.ptr(gamma), y=lib.ptr(logits), n=E + 1, k=H,
+                        prologue=lib.NORM_F32GAIN, epilogue=lib.EPI_STORE, eps=1e-6, pdl=0, route_counter=lib.ptr(counter),
+                        route_experts=E, route_top_k=K, idx_out=lib.ptr(idx), w_out=lib.ptr(w))
+    for _ in range(2):
+        lib.check(lib.load().tfb_gemv_f32(C.byref(a), lib.stream()), "tfb_gemv_f32")
+    idx2, w2 = torch.zeros(K, dtype=torch.int64, device=dev), torch.zeros(K, device=dev)
+    lib.check(lib.load().tfb_router_select(None, lib.ptr(logits), lib.ptr(idx2), None, lib.ptr(w2), E, K, 1, 0, lib.stream()), "select")
+    assert torch.equal(idx.cpu(), idx2.cpu()) and torch.equal(w.cpu(), w2.cpu())
+    assert int(counter) == 0
+    probs = torch.softmax(logits[:E].cpu(), -1)
+    pv, _ = torch.topk(probs, K)
+    assert torch.equal(probs[idx.cpu()], pv)                       # same values in the same order (equal values: any order in torch)
+    got = idx.cpu().tolist()
+    assert (17 not in got and 200 not in got) or (17 in got and (200 not in got or got.index(17) < got.index(200)))

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from oracle import evaluator, generation, ops as tf, qwen3_1_7b as oq
-from tests.helpers import ATOL, RTOL, assert_close_at_scale, assert_close_bf16, assert_rel_l2
+from tests.helpers import ATOL, RTOL, assert_close_at_scale, assert_close_bf16, assert_rel_l2, assert_ulps
 from tilefoundry_b200.authored import qwen3_1_7b as q
 from tilefoundry_b200.authored.weights import random_weights
 from tilefoundry_b200.runtime import AllClose, DictResource, Equal, NanInf, check
@@ -47,6 +47,65 @@ def test_gemv_store_and_residual(dev, n, k):
     got32 = lib.gemv(w.to(dev), x.to(dev), torch.empty(n, device=dev, dtype=torch.float32),
                      epilogue=lib.EPI_STORE_F32)
     torch.testing.assert_close(got32.cpu(), x.float() @ w.float().t(), rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("kernel", [3, 4])
+@pytest.mark.parametrize("n,k", [(6144, 2048), (2048, 6144), (1000, 768), (4096, 2560)])
+def test_gemv_persistent_variants_match_default_kernel(dev, kernel, n, k):
+    """TFB_KERNEL_PERSIST / TFB_KERNEL_ASYNC hand rows out differently and may split K differently, so a sum can
+    differ in its last f32 bit: at most one bf16 rounding apart from the default kernel."""
+    from tilefoundry_b200 import lib
+    g = torch.Generator().manual_seed(n + k + kernel)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(BF).to(dev)
+    w2 = (torch.randn(n, k, generator=g) / k ** 0.5).to(BF).to(dev)
+    x, gamma = torch.randn(k, generator=g).to(BF).to(dev), (1 + 0.1 * torch.randn(k, generator=g)).to(BF).to(dev)
+    res = torch.randn(n, generator=g).to(BF).to(dev)
+    new = lambda: torch.empty(n, device=dev, dtype=BF)
+    for kw in (dict(), dict(residual=res, epilogue=lib.EPI_RESIDUAL, res_scale=0.25),
+               dict(w2=w2, gamma=gamma, prologue=lib.NORM_CAST_THEN_GAIN, epilogue=lib.EPI_SWIGLU, eps=1e-6),
+               dict(gamma=gamma, prologue=lib.NORM_F32GAIN, eps=1e-6, x_scale=-3.0)):
+        want = lib.gemv(w, x, new(), **kw)
+        got = lib.gemv(w, x, new(), kernel=kernel, **kw)
+        assert_ulps(got, want, 1, f"kernel {kernel} {n}x{k} {sorted(kw)}")
+
+
+@pytest.mark.parametrize("h,inter,qkv", [(2048, 6144, 4096), (256, 512, 512), (2560, 6400, 0)])
+def test_gemv_chain_matches_separate_launches(dev, h, inter, qkv):
+    """o-projection + residual -> norm + gate/up + SwiGLU -> down + residual (-> next q|k|v) as one persistent
+    launch: every phase equals the default kernel run on the chain's own inputs of that phase (one bf16
+    rounding for the different K-split), and the status word stays zero."""
+    import ctypes as C
+    from tilefoundry_b200 import lib
+    g = torch.Generator().manual_seed(h + inter)
+    rnd = lambda *s, scale=1.0: (torch.randn(*s, generator=g) * scale).to(BF).to(dev)
+    w_o, w_g, w_u, w_d = rnd(h, h, scale=h ** -0.5), rnd(inter, h, scale=h ** -0.5), rnd(inter, h, scale=h ** -0.5), rnd(h, inter, scale=inter ** -0.5)
+    w_q = rnd(max(qkv, 1), h, scale=h ** -0.5)
+    gamma, gamma2 = (1 + 0.1 * torch.randn(h, generator=g)).to(BF).to(dev), (1 + 0.1 * torch.randn(h, generator=g)).to(BF).to(dev)
+    attn, h0 = rnd(h), rnd(h)
+    new = lambda n: torch.empty(n, device=dev, dtype=BF)
+    h1, act, h2, q_out = new(h), new(inter), new(h), new(max(qkv, 1))
+    sync = torch.zeros(4, device=dev, dtype=torch.int32)
+    def args(**kw):
+        base = dict(n=0, k=0, prologue=0, epilogue=0, eps=1e-6, x_scale=1.0, res_scale=1.0, out_scale=1.0)
+        base.update(kw)
+        return lib.GemvArgs(**{k: (lib.ptr(v) if isinstance(v, torch.Tensor) else v) for k, v in base.items()})
+    phases = [args(w=w_o, x=attn, residual=h0, y=h1, n=h, k=h, epilogue=lib.EPI_RESIDUAL, res_scale=0.5),
+              args(w=w_g, w2=w_u, x=h1, gamma=gamma, y=act, n=inter, k=h, prologue=lib.NORM_CAST_THEN_GAIN, epilogue=lib.EPI_SWIGLU),
+              args(w=w_d, x=act, residual=h1, y=h2, n=h, k=inter, epilogue=lib.EPI_RESIDUAL, res_scale=0.5)]
+    if qkv:
+        phases.append(args(w=w_q, x=h2, gamma=gamma2, y=q_out, n=qkv, k=h, prologue=lib.NORM_F32GAIN))
+    a = lib.GemvChainArgs(n_phases=len(phases), pdl=0, sync=lib.ptr(sync))
+    for i, ph in enumerate(phases):
+        a.phase[i] = ph
+    for _ in range(3):                                   # the barrier counters return to zero after every launch
+        lib.check(lib.load().tfb_gemv_chain(C.byref(a), lib.stream()), "tfb_gemv_chain")
+    torch.cuda.synchronize()
+    assert sync.cpu().tolist() == [0, 0, 0, 0]
+    assert_ulps(h1, lib.gemv(w_o, attn, new(h), residual=h0, epilogue=lib.EPI_RESIDUAL, res_scale=0.5), 1, "o + residual")
+    assert_ulps(act, lib.gemv(w_g, h1, new(inter), w2=w_u, gamma=gamma, prologue=lib.NORM_CAST_THEN_GAIN, epilogue=lib.EPI_SWIGLU, eps=1e-6), 1, "gate/up")
+    assert_ulps(h2, lib.gemv(w_d, act, new(h), residual=h1, epilogue=lib.EPI_RESIDUAL, res_scale=0.5), 1, "down + residual")
+    if qkv:
+        assert_ulps(q_out, lib.gemv(w_q, h2, new(qkv), gamma=gamma2, prologue=lib.NORM_F32GAIN, eps=1e-6), 1, "next q|k|v")
 
 
 @pytest.mark.parametrize("mode", [1, 2])
@@ -211,7 +270,7 @@ def _compare_run(cfg, want, sess, got, n_prompt, n_new):
     return excused
 
 
-@pytest.mark.parametrize("use_graph,kernel", [(False, 0), (True, 0), (True, 2)])
+@pytest.mark.parametrize("use_graph,kernel", [(False, 0), (True, 0), (True, 2), (False, 5), (True, 5)])
 def test_session_matches_evaluator_tiny(dev, use_graph, kernel):
     cfg = q.QWEN3_TINY
     n_prompt, n_new = 24, 140          # crosses the 128-position split and the 64-slot page boundaries
@@ -315,17 +374,19 @@ def test_config0_full_model_first_32_tokens(dev):
             hidden = ref_out
 
 
-def test_generate_equals_stepwise_and_is_idempotent(dev):
+@pytest.mark.parametrize("kernel", [0, 5])
+def test_generate_equals_stepwise_and_is_idempotent(dev, kernel):
     from tilefoundry_b200.engine.qwen3 import Qwen3Session
     cfg = q.QWEN3_TINY
     mod = q.build(cfg)
     weights = q.tie_head(random_weights(mod, seed=2, std=0.05))
-    sess = Qwen3Session(cfg, DictResource(_cuda(weights, dev)), max_ctx=200, device=dev)
+    sess = Qwen3Session(cfg, DictResource(_cuda(weights, dev)), max_ctx=200, device=dev, kernel=kernel)
     prompt = torch.arange(5, 25)
     a = sess.generate(prompt, 100).tokens
     b = sess.generate(prompt, 100, use_graph=False).tokens
     c = sess.generate(prompt, 100).tokens
     assert a == b == c
+    assert sess.chain_sync.cpu().tolist() == [0, 0, 0, 0]          # no grid-barrier wait ever gave up
     with pytest.raises(ValueError, match="exceed capacity"):
         sess.generate(prompt, 500)
     with pytest.raises(ValueError, match="at least one token"):

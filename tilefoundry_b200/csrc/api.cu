@@ -2,6 +2,7 @@
 #include "../../include/tfb200.h"
 #include "kernels.h"
 #include "api_internal.h"
+#include <cstdlib>
 
 #include <cstdio>
 #include <cstring>
@@ -114,11 +115,45 @@ int tfb::host::gemv_checked(const tfb_gemv_args* a, tfb_stream_t stream) {
     p.expert_world = a->expert_world;
     if (a->kernel == TFB_KERNEL_RING && tfb::gemv_stream_supported(a->n, a->k))
         return done(tfb::gemv_stream_dispatch(p, a->prologue, a->epilogue, S(stream), a->pdl != 0));
+    if (a->kernel == TFB_KERNEL_ASYNC && tfb::gemv_async_supported(p, a->prologue, a->epilogue))
+        return done(tfb::gemv_async_dispatch(p, a->prologue, a->epilogue, S(stream), a->pdl != 0));
+    // Measured on B200 (28 back-to-back launches over distinct 50 MB gate/up pairs): the persistent form with one
+    // row pair per warp and both halves of the row in flight takes 11.7 us against 13.8 us for the one-shot
+    // grid; for the single-matrix projections the one-shot grid is as fast or faster, so only SwiGLU defaults to it.
+    const bool auto_persist = a->kernel == TFB_KERNEL_AUTO && a->epilogue == TFB_EPI_SWIGLU;
+    if ((a->kernel == TFB_KERNEL_PERSIST || auto_persist) && a->epilogue <= TFB_EPI_SWIGLU &&
+        tfb::gemv_persist_supported(p, a->prologue))
+        return done(tfb::gemv_persist_dispatch(p, a->prologue, a->epilogue, S(stream), a->pdl != 0));
     return done(tfb::gemv_dispatch(p, a->prologue, a->epilogue, S(stream), a->pdl != 0));
 }
 
 extern "C" {
 int tfb_gemv(const tfb_gemv_args* args, tfb_stream_t stream) { return gemv_checked(args, stream); }
+
+int tfb_gemv_chain(const tfb_gemv_chain_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->n_phases >= 1 && a->n_phases <= 4 && a->sync, TFB_EINVAL);
+    tfb::ChainParams p = {};
+    p.n_phases = a->n_phases;
+    p.barrier = a->sync;
+    p.status = a->sync + 2;
+    for (int q = 0; q < a->n_phases; ++q) {
+        const tfb_gemv_args& g = a->phase[q];
+        TFB_REQUIRE(g.w && g.x && g.y && g.n >= 256 && g.k > 0 && g.k % 256 == 0 && g.k <= 8192, TFB_EINVAL);
+        TFB_REQUIRE(g.prologue >= TFB_NORM_NONE && g.prologue <= TFB_NORM_CAST_THEN_GAIN, TFB_EINVAL);
+        TFB_REQUIRE(g.epilogue >= TFB_EPI_STORE && g.epilogue <= TFB_EPI_SWIGLU && !g.expert_idx, TFB_EINVAL);
+        TFB_REQUIRE(g.prologue == TFB_NORM_NONE || g.gamma, TFB_EINVAL);
+        TFB_REQUIRE(g.epilogue != TFB_EPI_RESIDUAL || g.residual, TFB_EINVAL);
+        TFB_REQUIRE(g.epilogue != TFB_EPI_SWIGLU || g.w2, TFB_EINVAL);
+        TFB_REQUIRE(aligned16(g.w) && aligned16(g.x) && (!g.w2 || aligned16(g.w2)) && (!g.gamma || aligned16(g.gamma)), TFB_EALIGN);
+        tfb::ChainPhase& ph = p.ph[q];
+        ph.w = static_cast<const uint4*>(g.w); ph.w2 = static_cast<const uint4*>(g.w2);
+        ph.x = static_cast<const uint16_t*>(g.x); ph.gamma = static_cast<const uint16_t*>(g.gamma);
+        ph.residual = static_cast<const uint16_t*>(g.residual); ph.y = static_cast<uint16_t*>(g.y);
+        ph.n = g.n; ph.k = g.k; ph.norm = g.prologue; ph.epi = g.epilogue;
+        ph.eps = g.eps; ph.x_scale = g.x_scale; ph.res_scale = g.res_scale;
+    }
+    return done(tfb::gemv_chain_launch(p, S(stream), a->pdl != 0, nullptr));
+}
 
 int32_t tfb_lm_head_scratch_entries(int32_t n) {
     if (n <= 0) return 0;
@@ -273,7 +308,9 @@ int tfb_qwen3_decode_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
         g.n = NQKV; g.k = H; g.prologue = TFB_NORM_CAST_THEN_GAIN; g.epilogue = TFB_EPI_STORE;
         g.eps = a->eps; g.x_scale = 1.f; g.res_scale = 1.f; g.out_scale = 1.f; g.pdl = pdl; g.kernel = a->kernel; g.self_prefetch = spf;
         if (pf) { g.prefetch = L.w_o; g.prefetch_bytes = 2ull * H * QP; }
-        int rc = gemv_checked(&g, stream);
+        const bool qkv_done = l > 0 && a->kernel == TFB_KERNEL_CHAIN && a->chain_sync != nullptr && !trace;
+        if (a->kernel == TFB_KERNEL_CHAIN) g.kernel = TFB_KERNEL_AUTO;
+        int rc = qkv_done ? TFB_OK : gemv_checked(&g, stream);
         if (rc) return rc;
         // 2. q/k norm, RoPE, KV append, attention
         tfb_attn_gqa_args t;
@@ -288,13 +325,22 @@ int tfb_qwen3_decode_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
         if (pf) { t.prefetch = L.w_gate; t.prefetch_bytes = 2ull * I * H; }
         rc = tfb_attn_gqa_decode(&t, stream);
         if (rc) return rc;
+        const bool chain = a->kernel == TFB_KERNEL_CHAIN && a->chain_sync != nullptr;
+        tfb_gemv_chain_args ch;
+        if (chain) std::memset(&ch, 0, sizeof ch);
+        auto emit = [&](const tfb_gemv_args& x) -> int {        // one launch, or the next phase of the chain
+            if (!chain) return gemv_checked(&x, stream);
+            ch.phase[ch.n_phases] = x;
+            ch.phase[ch.n_phases++].kernel = TFB_KERNEL_AUTO;
+            return TFB_OK;
+        };
         // 3. output projection + residual
         std::memset(&g, 0, sizeof g);
         g.w = L.w_o; g.x = a->attn_buf; g.residual = hid; g.y = hid;
         g.n = H; g.k = QP; g.prologue = TFB_NORM_NONE; g.epilogue = TFB_EPI_RESIDUAL;
         g.eps = a->eps; g.x_scale = 1.f; g.res_scale = 1.f; g.out_scale = 1.f; g.pdl = pdl; g.kernel = a->kernel; g.self_prefetch = spf;
         if (pf) { g.prefetch = L.w_up; g.prefetch_bytes = 2ull * I * H; }
-        rc = gemv_checked(&g, stream);
+        rc = emit(g);
         if (rc) return rc;
         // 4. post-attention norm + gate/up + SwiGLU
         std::memset(&g, 0, sizeof g);
@@ -302,7 +348,7 @@ int tfb_qwen3_decode_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
         g.n = I; g.k = H; g.prologue = TFB_NORM_CAST_THEN_GAIN; g.epilogue = TFB_EPI_SWIGLU;
         g.eps = a->eps; g.x_scale = 1.f; g.res_scale = 1.f; g.out_scale = 1.f; g.pdl = pdl; g.kernel = a->kernel; g.self_prefetch = spf;
         if (pf) { g.prefetch = L.w_down; g.prefetch_bytes = 2ull * I * H; }
-        rc = gemv_checked(&g, stream);
+        rc = emit(g);
         if (rc) return rc;
         // 5. down projection + residual
         std::memset(&g, 0, sizeof g);
@@ -310,8 +356,20 @@ int tfb_qwen3_decode_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
         g.n = H; g.k = I; g.prologue = TFB_NORM_NONE; g.epilogue = TFB_EPI_RESIDUAL;
         g.eps = a->eps; g.x_scale = 1.f; g.res_scale = 1.f; g.out_scale = 1.f; g.pdl = pdl; g.kernel = a->kernel; g.self_prefetch = spf;
         if (pf && next) { g.prefetch = next->w_qkv; g.prefetch_bytes = 2ull * NQKV * H; }
-        rc = gemv_checked(&g, stream);
+        rc = emit(g);
         if (rc) return rc;
+        if (chain) {
+            if (next && !trace) {                              // the next layer's q|k|v reads what `down` just wrote
+                std::memset(&g, 0, sizeof g);
+                g.w = next->w_qkv; g.x = hid; g.gamma = next->gamma_in; g.y = a->qkv_buf;
+                g.n = NQKV; g.k = H; g.prologue = TFB_NORM_CAST_THEN_GAIN; g.epilogue = TFB_EPI_STORE;
+                g.eps = a->eps; g.x_scale = 1.f; g.res_scale = 1.f; g.out_scale = 1.f;
+                ch.phase[ch.n_phases++] = g;
+            }
+            ch.pdl = pdl; ch.sync = a->chain_sync;
+            rc = tfb_gemv_chain(&ch, stream);
+            if (rc) return rc;
+        }
         if (trace) {
             e = tfb::copy_launch(hid, trace + size_t(l) * H, H * 2, st, pdl);
             if (e != cudaSuccess) return fail_launch(e);

@@ -27,6 +27,11 @@ int tfb_gemv_f32(const tfb_gemv_f32_args* a, tfb_stream_t stream) {
         const bool extra = a->routed_slots * a->rows_per_expert < a->n;
         TFB_REQUIRE(!extra || (a->w_extra && (ep != TFB_EPI_SWIGLU || a->w2_extra)), TFB_EINVAL);
     }
+    if (a->route_counter) {
+        TFB_REQUIRE(ep == TFB_EPI_STORE && a->rows_per_expert == 0 && a->k <= 2048 && a->idx_out && a->w_out, TFB_EINVAL);
+        TFB_REQUIRE(a->route_experts > 0 && a->route_experts <= 256 && a->route_experts <= a->n && a->route_top_k > 0 &&
+                        a->route_top_k <= 32 && a->route_top_k <= a->route_experts, TFB_EINVAL);
+    }
     TFB_REQUIRE(aligned16(a->w) && aligned16(a->x) && aligned16(a->y) && (!a->w2 || aligned16(a->w2)) &&
                     (!a->gamma || aligned16(a->gamma)) && (!a->gate || aligned16(a->gate)) &&
                     (!a->w_extra || aligned16(a->w_extra)) && (!a->w2_extra || aligned16(a->w2_extra)), TFB_EALIGN);
@@ -37,6 +42,8 @@ int tfb_gemv_f32(const tfb_gemv_f32_args* a, tfb_stream_t stream) {
     p.n = a->n; p.k = a->k; p.seg = a->seg; p.eps = a->eps;
     p.expert_idx = reinterpret_cast<const long long*>(a->expert_idx);
     p.rows_per_expert = a->rows_per_expert; p.routed_slots = a->routed_slots;
+    p.route_counter = a->route_counter; p.route_experts = a->route_experts; p.route_top_k = a->route_top_k;
+    p.idx_out = reinterpret_cast<long long*>(a->idx_out); p.w_out = a->w_out;
     p.trace = next_trace();
     return done(tfb::gemv_f32_dispatch(p, nm, ep, S(stream), a->pdl != 0));
 }
@@ -64,7 +71,8 @@ int32_t tfb_attn_gated_splits(int32_t max_ctx) { return tfb::attn_gated_splits(m
 int tfb_attn_gated_decode(const tfb_attn_gated_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->proj && a->gamma_q && a->gamma_k && a->cos_table && a->sin_table && a->pos && a->k_pool &&
                     a->v_pool && a->block_table && a->out && a->part_o && a->part_ml && a->counters, TFB_EINVAL);
-    TFB_REQUIRE(a->hq > 0 && a->hkv > 0 && a->hq % a->hkv == 0 && a->page_size > 0 && a->max_ctx > 0, TFB_EINVAL);
+    TFB_REQUIRE(a->hq > 0 && a->hkv > 0 && a->hq % a->hkv == 0 && a->page_size > 0 && a->page_size % 64 == 0 &&
+                    a->max_ctx > 0, TFB_EINVAL);
     TFB_REQUIRE(a->rotary_dim > 0 && a->rotary_dim % 64 == 0 && a->rotary_dim <= a->d, TFB_EINVAL);
     TFB_REQUIRE(int64_t(a->table_len) * a->page_size >= a->max_ctx && a->max_pos >= a->max_ctx, TFB_ECAPACITY);
     const int g = a->hq / a->hkv;
@@ -193,6 +201,7 @@ int tfb_qwen35_decode_step(const tfb_qwen35_step_args* a, tfb_stream_t stream) {
         base(g); g.w = L.w_router; g.x = att; g.gamma = L.gamma_post; g.y = a->router_logits; g.n = E + 1; g.k = H;
         g.prologue = TFB_NORM_F32GAIN; g.epilogue = TFB_EPI_STORE;
         if ((rc = tfb_gemv_f32(&g, stream))) return rc;
+        // the selection as a launch of its own measured 0.5 % faster per step than the last-CTA form of tfb_gemv_f32
         if ((rc = tfb_router_select(nullptr, a->router_logits, a->router_idx, nullptr, a->router_w, E, K, 1, pdl, stream)))
             return rc;
         if (a->idx_trace) {

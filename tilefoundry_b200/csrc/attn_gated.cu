@@ -23,7 +23,7 @@ __global__ void __launch_bounds__(kGatedThreads) attn_gated_kernel(const GatedAt
     constexpr int NWARP = kGatedThreads / 32;
     constexpr int EPL = D / 32;                       // elements of one vector per lane
     constexpr int HG = (G * D) / kGatedThreads;       // heads per thread in the PV stage (thread owns one dim)
-    static_assert((G * D) % kGatedThreads == 0 && HG >= 1 && kGatedThreads % D == 0, "shape");
+    static_assert((G * D) % kGatedThreads == 0 && HG >= 1 && kGatedThreads % D == 0 && EPL % 4 == 0, "shape");
     constexpr int NGRP = kGatedThreads / D;           // head groups in the PV stage
     static_assert(NGRP * HG == G, "shape");
 
@@ -101,32 +101,46 @@ __global__ void __launch_bounds__(kGatedThreads) attn_gated_kernel(const GatedAt
         }
     }
 
-    // ---- scores: a warp takes every NWARP-th position, lanes split the head dimension ----
+    __syncthreads();                                   // the appended row is visible to the whole CTA
+    // A split never straddles a page (the page size is a multiple of kGatedSplit): its rows are contiguous in the
+    // pool, hkv*D floats apart.
+    const int page = p.block_table[p0 / p.page_size];
+    const size_t row_stride = size_t(p.hkv) * D;
+    const size_t first = (size_t(page) * p.page_size + (p0 % p.page_size)) * p.hkv + g;
+    const float* kbase = p.k_pool + first * D;
+    const float* vbase = p.v_pool + first * D;
+
+    // ---- scores: a warp takes 4 consecutive positions at a time (all their loads in flight together) ----
     {
+        constexpr int V4 = EPL / 4;                    // float4 per lane per row
         float q[G][EPL];
 #pragma unroll
         for (int j = 0; j < G; ++j)
 #pragma unroll
-            for (int i = 0; i < EPL; ++i) q[j][i] = vec[j][lane + 32 * i];
-        for (int r = warp; r < n; r += NWARP) {
-            const int pp = p0 + r;
-            float kf[EPL];
-            if (pp == pos) {
+            for (int i = 0; i < EPL; ++i) q[j][i] = vec[j][(i / 4) * 128 + lane * 4 + (i % 4)];
+        for (int r0 = warp * 4; r0 < n; r0 += NWARP * 4) {
+            float4 kf[4][V4];
 #pragma unroll
-                for (int i = 0; i < EPL; ++i) kf[i] = vec[G][lane + 32 * i];
-            } else {
-                const int page = p.block_table[pp / p.page_size];
-                const float* row = p.k_pool + ((size_t(page) * p.page_size + (pp % p.page_size)) * p.hkv + g) * D;
+            for (int t = 0; t < 4; ++t)
 #pragma unroll
-                for (int i = 0; i < EPL; ++i) kf[i] = row[lane + 32 * i];
-            }
+                for (int h = 0; h < V4; ++h)
+                    kf[t][h] = (r0 + t < n) ? *reinterpret_cast<const float4*>(kbase + (r0 + t) * row_stride + h * 128 + lane * 4)
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-            for (int j = 0; j < G; ++j) {
-                float s = 0.f;
+            for (int t = 0; t < 4; ++t) {
 #pragma unroll
-                for (int i = 0; i < EPL; ++i) s = fmaf(q[j][i], kf[i], s);
-                s = warp_sum(s);
-                if (lane == 0) sc[j][r] = s;
+                for (int j = 0; j < G; ++j) {
+                    float s = 0.f;
+#pragma unroll
+                    for (int h = 0; h < V4; ++h) {
+                        s = fmaf(q[j][h * 4 + 0], kf[t][h].x, s);
+                        s = fmaf(q[j][h * 4 + 1], kf[t][h].y, s);
+                        s = fmaf(q[j][h * 4 + 2], kf[t][h].z, s);
+                        s = fmaf(q[j][h * 4 + 3], kf[t][h].w, s);
+                    }
+                    s = warp_sum(s);
+                    if (lane == 0 && r0 + t < n) sc[j][r0 + t] = s;
+                }
             }
         }
     }
@@ -152,16 +166,16 @@ __global__ void __launch_bounds__(kGatedThreads) attn_gated_kernel(const GatedAt
     float o[HG];
 #pragma unroll
     for (int t = 0; t < HG; ++t) o[t] = 0.f;
-    for (int r = 0; r < n; ++r) {
-        const int pp = p0 + r;
-        float v;
-        if (pp == pos) v = vec[G + 1][d];
-        else {
-            const int page = p.block_table[pp / p.page_size];
-            v = p.v_pool[((size_t(page) * p.page_size + (pp % p.page_size)) * p.hkv + g) * D + d];
-        }
+    for (int r0 = 0; r0 < n; r0 += 8) {                // 8 independent loads in flight per thread
+        float v[8];
 #pragma unroll
-        for (int t = 0; t < HG; ++t) o[t] = fmaf(sc[j0 + t][r], v, o[t]);
+        for (int t = 0; t < 8; ++t) v[t] = (r0 + t < n) ? vbase[(r0 + t) * row_stride + d] : 0.f;
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+            if (r0 + t < n) {
+#pragma unroll
+                for (int h = 0; h < HG; ++h) o[h] = fmaf(sc[j0 + h][r0 + t], v[t], o[h]);
+            }
     }
     const int nsplit = p.nsplit;
     if (n_active == 1) {

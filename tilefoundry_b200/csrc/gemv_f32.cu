@@ -12,6 +12,7 @@
 // Expert mode: output rows are grouped in slots of rows_per_expert; the first routed_slots slots read the
 // rows of expert expert_idx[slot], later slots read consecutive rows of w_extra (the shared expert).
 #include "gemv.cuh"
+#include "route.cuh"
 #include "kernels.h"
 #include "launch.h"
 
@@ -177,6 +178,24 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_f32_kernel(const GemvF32Param
         if (EPI == 0) p.y[row] = round_bf16(v);
         else if (EPI == 1) p.y[row] = res_early + round_bf16(v);
         else p.y[row] = round_bf16(silu_f32(round_bf16(v)) * round_bf16(v2));
+    }
+    if (EPI == 0 && KSPLIT == 1 && p.route_counter != nullptr) {
+        // Router launch: the last CTA to finish (an atomic ticket, no spinning) selects the top-k from the logits
+        // the grid has just written -- softmax over all experts, top-k, renormalise -- so the selection needs no
+        // launch of its own.
+        __shared__ int s_last;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) s_last = atomicAdd(p.route_counter, 1u) == gridDim.x - 1;
+        __syncthreads();
+        if (s_last && warp == 0) {
+            __threadfence();
+            float rw;
+            int re;
+            route_select<256>(p.y, nullptr, p.route_experts, p.route_top_k, 1, lane, rw, re);
+            if (lane < p.route_top_k) { p.idx_out[lane] = re; p.w_out[lane] = rw; }
+            if (lane == 0) *p.route_counter = 0;
+        }
     }
     trace_end(p.trace);
 }

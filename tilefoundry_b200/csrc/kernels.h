@@ -37,6 +37,10 @@ bool gemv_stream_supported(int n, int k);
 cudaError_t gemv_stream_dispatch(const GemvParams& p, int norm_mode, int epi, cudaStream_t stream, bool pdl);
 int lm_head_stream_ctas();
 cudaError_t gemv_dispatch(const GemvParams& p, int norm_mode, int epi, cudaStream_t stream, bool pdl);
+bool gemv_async_supported(const GemvParams& p, int norm_mode, int epi);
+cudaError_t gemv_async_dispatch(const GemvParams& p, int norm_mode, int epi, cudaStream_t stream, bool pdl);
+bool gemv_persist_supported(const GemvParams& p, int norm_mode);
+cudaError_t gemv_persist_dispatch(const GemvParams& p, int norm_mode, int epi, cudaStream_t stream, bool pdl);
 
 struct AttnParams {
     const uint16_t* qkv;
@@ -198,6 +202,12 @@ struct GemvF32Params {
     const long long* expert_idx;
     int rows_per_expert, routed_slots;
     unsigned long long* trace;
+    // router launch (epilogue store, no expert mode), optional: the last CTA selects route_top_k of the first
+    // route_experts outputs (softmax over all, top-k, renormalise) into idx_out / w_out
+    unsigned* route_counter;         // u32, zero before the first launch; the kernel leaves it zero
+    int route_experts, route_top_k;
+    long long* idx_out;
+    float* w_out;
 };
 cudaError_t gemv_f32_dispatch(const GemvF32Params& p, int norm_mode, int epi, cudaStream_t stream, bool pdl);
 
@@ -264,5 +274,26 @@ cudaError_t embed_f32_launch(const uint16_t* table, const long long* ids, const 
 cudaError_t rmsnorm_f32_launch(const float* x, const float* gamma, float* y, int rows, int width, float eps,
                                cudaStream_t stream, bool pdl);
 cudaError_t residual_add_f32_launch(const float* a, const float* b, float* out, int n, cudaStream_t stream, bool pdl);
+
+// ---- a chain of dependent projections in one persistent launch (chain.cu) ----
+struct ChainPhase {
+    const uint4* w;
+    const uint4* w2;
+    const uint16_t* x;
+    const uint16_t* gamma;
+    const uint16_t* residual;
+    uint16_t* y;
+    int n, k, norm, epi;
+    int ksplit, si;                  // filled by the launcher: K-slices per row, 256-element iterations per stage
+    float eps, x_scale, res_scale;
+};
+struct ChainParams {
+    ChainPhase ph[4];
+    int n_phases;
+    int kmax, part_floats;           // filled by the launcher
+    unsigned* barrier;               // u32[2], zero before the first launch; the kernel leaves it zero
+    unsigned* status;                // u32, set non-zero if a bounded wait gave up
+};
+cudaError_t gemv_chain_launch(ChainParams& p, cudaStream_t stream, bool pdl, size_t* smem_out);
 
 }  // namespace tfb

@@ -5,6 +5,7 @@
 // launch = hidden * (top_k * inter + shared_inter) * 2 (each output row reads its top_k expert rows
 // and its shared-expert row once); granite: 4096 * (10*768 + 1536) * 2 = 75.5 MB.
 #include "common.cuh"
+#include "route.cuh"
 #include "kernels.h"
 #include "launch.h"
 
@@ -17,62 +18,15 @@ namespace tfb {
 // Selection order is by value descending; equal values resolve to the lower index.
 template <int MAXE>
 __global__ void __launch_bounds__(32) router_select_kernel(const RouterParams p) {
-    constexpr int PER = MAXE / 32;
-    const int lane = threadIdx.x;
     pdl_trigger();
     pdl_wait();
-    float v[PER];
-#pragma unroll
-    for (int i = 0; i < PER; ++i) {
-        const int e = lane + 32 * i;
-        v[i] = -INFINITY;
-        if (e < p.experts) v[i] = p.logits_f32 ? p.logits_f32[e] : bf16_bits_to_f32(p.logits_bf16[e]);
-    }
-    if (p.mode == 1) {                         // probabilities over all experts
-        float m = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < PER; ++i) m = fmaxf(m, v[i]);
-        m = warp_max(m);
-        float s = 0.f;
-#pragma unroll
-        for (int i = 0; i < PER; ++i) { v[i] = (lane + 32 * i < p.experts) ? expf(v[i] - m) : -INFINITY; s += fmaxf(v[i], 0.f); }
-        s = warp_sum(s);
-#pragma unroll
-        for (int i = 0; i < PER; ++i) if (lane + 32 * i < p.experts) v[i] = v[i] / s;
-    }
-    float top_v = 0.f;                          // lane j keeps the j-th selection
-    int top_i = 0;
-    for (int j = 0; j < p.top_k; ++j) {
-        float best = -INFINITY;
-        int best_e = 0x7fffffff;
-#pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            const int e = lane + 32 * i;
-            if (e < p.experts && (v[i] > best || (v[i] == best && e < best_e))) { best = v[i]; best_e = e; }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-            if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
-        }
-        if (lane == j) { top_v = best; top_i = best_e; }
-#pragma unroll
-        for (int i = 0; i < PER; ++i) if (lane + 32 * i == best_e) v[i] = -INFINITY;
-    }
-    const bool mine = lane < p.top_k;
     float w;
-    if (p.mode == 0) {
-        const float m = warp_max(mine ? top_v : -INFINITY);
-        const float e = mine ? expf(top_v - m) : 0.f;
-        w = e / warp_sum(e);
-    } else {
-        w = top_v / warp_sum(mine ? top_v : 0.f);
-    }
-    if (mine) {
-        p.indices[lane] = top_i;
-        if (p.weights_bf16) p.weights_bf16[lane] = f32_to_bf16_bits(w);
-        if (p.weights_f32) p.weights_f32[lane] = w;
+    int e;
+    route_select<MAXE>(p.logits_f32, p.logits_bf16, p.experts, p.top_k, p.mode, threadIdx.x, w, e);
+    if (int(threadIdx.x) < p.top_k) {
+        p.indices[threadIdx.x] = e;
+        if (p.weights_bf16) p.weights_bf16[threadIdx.x] = f32_to_bf16_bits(w);
+        if (p.weights_f32) p.weights_f32[threadIdx.x] = w;
     }
 }
 
@@ -257,19 +211,47 @@ __global__ void __launch_bounds__(kDownWarps * 32) moe_down_f32_kernel(const Moe
     __syncthreads();
     if (j >= p.hidden) return;
 
+    // every selected expert's row is requested before the first one is used: one memory round trip, not top_k
     float routed = 0.f;
     const int pieces = I >> 3;
-    for (int s = 0; s < K; ++s) {
-        const uint4* row = p.w_down + (size_t(s_idx[s]) * p.hidden + j) * pieces;
-        const float* x = xin + s * I;
-        float acc = 0.f;
-        for (int c = lane; c < pieces; c += 32) {
-            const uint4 w = ld_stream16(row + c);
-            const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
-            acc = dot8(w, xa, xb, acc);
+    for (int s0 = 0; s0 < K; s0 += 8) {
+        uint4 wb[8][2];
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            const bool live = s0 + s < K;
+            const uint4* row = p.w_down + (size_t(live ? s_idx[s0 + s] : 0) * p.hidden + j) * pieces;
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+                wb[s][u] = (live && lane + 32 * u < pieces) ? ld_stream16(row + lane + 32 * u) : make_uint4(0, 0, 0, 0);
         }
-        acc = warp_sum(acc);
-        routed = fmaf(round_bf16(acc), s_w[s], routed);
+        float acc[8];
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            acc[s] = 0.f;
+            if (s0 + s >= K) continue;
+            const float* x = xin + (s0 + s) * I;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int c = lane + 32 * u;
+                if (c < pieces) {
+                    const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
+                    acc[s] = dot8(wb[s][u], xa, xb, acc[s]);
+                }
+            }
+            const uint4* row = p.w_down + (size_t(s_idx[s0 + s]) * p.hidden + j) * pieces;
+            for (int c = lane + 64; c < pieces; c += 32) {        // rows wider than 512 elements
+                const uint4 w = ld_stream16(row + c);
+                const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
+                acc[s] = dot8(w, xa, xb, acc[s]);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int s = 0; s < 8; ++s) acc[s] += __shfl_xor_sync(0xffffffffu, acc[s], o);
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+            if (s0 + s < K) routed = fmaf(round_bf16(acc[s]), s_w[s0 + s], routed);
     }
     float out = routed;
     if (shrow) {

@@ -90,6 +90,7 @@ class Qwen3Session(DecodeSession):
             for name, _ in lib.Qwen3Layer._fields_:
                 setattr(s, name, lib.ptr(layer[name]))
         scale = float(torch.tensor(D ** -0.5, dtype=bf))   # the authored step holds it as a bf16 tensor
+        self.chain_sync = torch.zeros(4, device=self.device, dtype=torch.int32)   # grid barrier + status of the chained launch
         self.args = lib.Qwen3StepArgs(
             layers=self._layer_structs, n_layers=len(self.layers), hidden=H, hq=HQ, hkv=HKV, d=D, inter=I,
             vocab=V, eps=cfg.rms_norm_eps, scale=scale,
@@ -102,7 +103,8 @@ class Qwen3Session(DecodeSession):
             act_buf=lib.ptr(self.act), logits=lib.ptr(self.logits), part_o=lib.ptr(self.part_o),
             part_ml=lib.ptr(self.part_ml), counters=lib.ptr(self.counters), head_val=lib.ptr(self.head_val),
             head_idx=lib.ptr(self.head_idx), hidden_trace=lib.ptr(self.trace),
-            pdl=int(pdl), l2_prefetch=int(l2_prefetch), kernel=int(kernel), picked=lib.ptr(self.picked))
+            pdl=int(pdl), l2_prefetch=int(l2_prefetch), kernel=int(kernel), picked=lib.ptr(self.picked),
+            chain_sync=lib.ptr(self.chain_sync))
         self.graph = None
         self._graph_prompt = None
         #: kernels one step enqueues (embed + 5 per layer + lm_head [+ trace copies and final norm])

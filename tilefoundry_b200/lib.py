@@ -61,7 +61,12 @@ class Qwen3StepArgs(C.Structure):
                 ("block_table", _vp), ("tokens", _vp), ("pos", _vp), ("n_prompt", _i32), ("max_tokens", _i32),
                 ("hidden_buf", _vp), ("qkv_buf", _vp), ("attn_buf", _vp), ("act_buf", _vp), ("logits", _vp),
                 ("part_o", _vp), ("part_ml", _vp), ("counters", _vp), ("head_val", _vp), ("head_idx", _vp),
-                ("hidden_trace", _vp), ("pdl", _i32), ("l2_prefetch", _i32), ("kernel", _i32), ("picked", _vp)]
+                ("hidden_trace", _vp), ("pdl", _i32), ("l2_prefetch", _i32), ("kernel", _i32), ("picked", _vp),
+                ("chain_sync", _vp)]
+
+
+class GemvChainArgs(C.Structure):
+    _fields_ = [("phase", GemvArgs * 4), ("n_phases", _i32), ("pdl", _i32), ("sync", _vp)]
 
 
 class AttnMlaArgs(C.Structure):
@@ -126,7 +131,8 @@ class GemvF32Args(C.Structure):
     _fields_ = [("w", _vp), ("w2", _vp), ("w_extra", _vp), ("w2_extra", _vp), ("x", _vp), ("gamma", _vp), ("gate", _vp),
                 ("residual", _vp), ("y", _vp), ("n", _i32), ("k", _i32), ("seg", _i32), ("prologue", _i32),
                 ("epilogue", _i32), ("eps", _f32), ("expert_idx", _vp), ("rows_per_expert", _i32),
-                ("routed_slots", _i32), ("pdl", _i32), ("reserved", _i32)]
+                ("routed_slots", _i32), ("pdl", _i32), ("reserved", _i32), ("route_counter", _vp), ("route_experts", _i32),
+                ("route_top_k", _i32), ("idx_out", _vp), ("w_out", _vp)]
 
 
 class GdnArgs(C.Structure):
@@ -180,6 +186,7 @@ SYMBOLS = {
     "tfb_embed": (_i32, [_vp, _vp, _vp, _i32, _i32, _i64, _f32, _vp]),
     "tfb_rmsnorm": (_i32, [_vp, _vp, _vp, _i32, _i32, _f32, _i32, _vp]),
     "tfb_gemv": (_i32, [C.POINTER(GemvArgs), _vp]),
+    "tfb_gemv_chain": (_i32, [C.POINTER(GemvChainArgs), _vp]),
     "tfb_lm_head_scratch_entries": (_i32, [_i32]),
     "tfb_lm_head_argmax": (_i32, [C.POINTER(LmHeadArgs), _vp]),
     "tfb_attn_splits": (_i32, [_i32]),
