@@ -522,6 +522,21 @@ typedef struct {
 } tfb_gemv_chain_args;
 TFB_API int tfb_gemv_chain(const tfb_gemv_chain_args* args, tfb_stream_t stream);
 
+/* ---- small-batch projection on the tensor cores (tcgen05 + TMEM + TMA) -----------------------------------
+ * y[M, N] = x[M, K] . w[N, K]^T (+ residual), 1 <= M <= 32 tokens, bf16 in / f32 accumulate / bf16 out; w in the
+ * same [out, in] layout tfb_gemv reads.  With residual: y = bf16(residual + bf16(acc)) (TFB_EPI_RESIDUAL's
+ * rounding).  K a multiple of 64; w, x 16-byte aligned.  K is split over tfb_gemm_small_m_splits(N, K) CTAs per
+ * 128-row tile; partial: f32 [splits * M * N] scratch, tickets: u32 [ceil(N/128)] zeroed once, status: u32 set
+ * non-zero if a bounded wait gave up (outputs then invalid; nothing hangs).  The batch-32 form of the projections of
+ * examples/qwen3_1_7b-tilelang/fast/kernels.py:124-260 (the reference runs batch 1 only). */
+typedef struct {
+    const void* w; const void* x; const void* residual; void* y;
+    float* partial; uint32_t* tickets; uint32_t* status;
+    int32_t m, n, k, pdl;
+} tfb_gemm_small_m_args;
+TFB_API int32_t tfb_gemm_small_m_splits(int32_t n, int32_t k);
+TFB_API int tfb_gemm_small_m(const tfb_gemm_small_m_args* args, tfb_stream_t stream);
+
 /* ================= f32-activation family (Qwen3.5-35B-A3B) =================
  * The reference's Qwen3.5 example keeps activations, recurrent state and KV cache in f32 and its contracted
  * weights in bf16: a product casts its activation to bf16, runs at bf16 and casts the result back

@@ -119,8 +119,10 @@ int tfb::host::gemv_checked(const tfb_gemv_args* a, tfb_stream_t stream) {
         return done(tfb::gemv_async_dispatch(p, a->prologue, a->epilogue, S(stream), a->pdl != 0));
     // Measured on B200 (28 back-to-back launches over distinct 50 MB gate/up pairs): the persistent form with one
     // row pair per warp and both halves of the row in flight takes 11.7 us against 13.8 us for the one-shot
-    // grid; for the single-matrix projections the one-shot grid is as fast or faster, so only SwiGLU defaults to it.
-    const bool auto_persist = a->kernel == TFB_KERNEL_AUTO && a->epilogue == TFB_EPI_SWIGLU;
+    // grid (66 MB at K = 2560: 15.5 against 17.6 us).  For the single-matrix projections the one-shot grid is as fast
+    // or faster, and so it is for SwiGLU with fewer row pairs than resident warps (1536 x 4096: 6.9 against 8.1 us),
+    // so only wide SwiGLU projections default to the persistent form.
+    const bool auto_persist = a->kernel == TFB_KERNEL_AUTO && a->epilogue == TFB_EPI_SWIGLU && a->n >= 4096;
     if ((a->kernel == TFB_KERNEL_PERSIST || auto_persist) && a->epilogue <= TFB_EPI_SWIGLU &&
         tfb::gemv_persist_supported(p, a->prologue))
         return done(tfb::gemv_persist_dispatch(p, a->prologue, a->epilogue, S(stream), a->pdl != 0));
@@ -153,6 +155,24 @@ int tfb_gemv_chain(const tfb_gemv_chain_args* a, tfb_stream_t stream) {
         ph.eps = g.eps; ph.x_scale = g.x_scale; ph.res_scale = g.res_scale;
     }
     return done(tfb::gemv_chain_launch(p, S(stream), a->pdl != 0, nullptr));
+}
+
+int32_t tfb_gemm_small_m_splits(int32_t n, int32_t k) {
+    if (n <= 0 || k < 64) return 0;
+    return tfb::gemm_tc_splits(n, k);
+}
+
+int tfb_gemm_small_m(const tfb_gemm_small_m_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->w && a->x && a->y && a->status, TFB_EINVAL);
+    TFB_REQUIRE(a->m >= 1 && a->m <= 32 && a->n > 0 && a->k >= 64 && a->k % 64 == 0, TFB_EINVAL);
+    TFB_REQUIRE(aligned16(a->w) && aligned16(a->x), TFB_EALIGN);
+    tfb::TcParams p = {};
+    p.M = a->m; p.N = a->n; p.K = a->k;
+    p.splits = tfb::gemm_tc_splits(a->n, a->k);
+    TFB_REQUIRE(p.splits == 1 || (a->partial && a->tickets), TFB_EINVAL);
+    p.partial = a->partial; p.tickets = a->tickets; p.status = a->status;
+    p.y = static_cast<uint16_t*>(a->y); p.residual = static_cast<const uint16_t*>(a->residual);
+    return done(tfb::gemm_tc_launch(a->w, a->x, p, S(stream), a->pdl != 0));
 }
 
 int32_t tfb_lm_head_scratch_entries(int32_t n) {

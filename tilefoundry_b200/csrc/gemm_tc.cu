@@ -1,0 +1,259 @@
+// Small-batch projection on the 5th-generation tensor cores: Y[M, N] = X[M, K] . W[N, K]^T (+ residual) for
+// M <= 32 tokens, bf16 in, f32 accumulate, bf16 out.
+//
+// At batch 32 a projection is still HBM-bound (64 flop per weight byte against a ridge near 290), but the
+// CUDA cores can no longer keep up with the weight stream (it would need ~200 TFLOP/s of FMA), so the
+// products move to tcgen05.mma with the operands swapped: the WEIGHT tile is the MMA's 128-row A operand
+// and the token block its N = 32 B operand, both K-major in shared memory, the 128 x 32 f32 accumulator in
+// tensor memory.  The weight stream is what matters: a producer thread keeps TC_STAGES TMA tiles of
+// 128 rows x 64 columns (16 KB, 128-byte swizzle) in flight per SM, completion counted by mbarriers.
+//
+// Roles in a CTA of 6 warps: warp 0 (one lane) issues TMA loads; warp 1 allocates tensor memory and (one lane)
+// issues the MMAs, four per stage (K = 16 each), releasing a stage with tcgen05.commit; warps 2-5 read the
+// accumulator back (tcgen05.ld, one TMEM lane quadrant each) and write it out.  K is split over blockIdx.y so
+// that a 6144 x 2048 projection (48 row tiles) still fills 144 SMs; the splits' f32 partials are added in
+// fixed order by the last CTA of a row tile (atomic ticket, no spinning): deterministic.
+//
+// Every mbarrier wait is bounded; a timeout sets *status, and the CTA still frees its tensor memory.
+//
+// HBM-bound: algorithmic bytes per launch = N*K*2 (weights) + M*K*2 per row tile from L2.
+#include "common.cuh"
+#include "kernels.h"
+#include "launch.h"
+
+#include <cuda.h>
+
+namespace tfb {
+
+constexpr int TC_BM = 128, TC_BN = 32, TC_BK = 64, TC_STAGES = 8, TC_THREADS = 192;
+constexpr int TC_A_BYTES = TC_BM * TC_BK * 2, TC_B_BYTES = TC_BN * TC_BK * 2;
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 20;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase of the given parity; false if it gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t spin = 0; spin < TC_WAIT_LIMIT; ++spin) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 :: "r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+// K-major operand tile with 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(const void* tile) {
+    uint64_t d = 0;
+    d |= uint64_t((smem_u32(tile) & 0x3FFFF) >> 4);          // start address, 16-byte units
+    d |= uint64_t(1) << 16;                                   // leading-dimension byte offset: unused with swizzle
+    d |= uint64_t(1024 >> 4) << 32;                           // stride-dimension byte offset: one 8-row group
+    d |= uint64_t(1) << 46;                                   // descriptor version of this architecture
+    d |= uint64_t(2) << 61;                                   // 128-byte swizzle
+    return d;
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(smem_u32(bar)) : "memory");
+}
+
+struct TcSmemTail {
+    uint64_t full[TC_STAGES], empty[TC_STAGES], accum;
+    uint32_t tmem_base;
+    int aborted, last;
+};
+
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                const __grid_constant__ CUtensorMap map_x, const TcParams p) {
+    extern __shared__ unsigned char tc_smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* a_tiles = base;                                      // TC_STAGES x 16 KB, 1024-byte aligned
+    unsigned char* b_tiles = base + TC_STAGES * TC_A_BYTES;             // TC_STAGES x 4 KB
+    TcSmemTail* t = reinterpret_cast<TcSmemTail*>(b_tiles + TC_STAGES * TC_B_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x, split = blockIdx.y;
+    const int per = (p.ksteps + p.splits - 1) / p.splits;
+    const int k_begin = split * per, k_end = min(p.ksteps, k_begin + per);
+    const int nsteps = max(k_end - k_begin, 0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&t->full[s], 1); mbar_init(&t->empty[s], 1); }
+        mbar_init(&t->accum, 1);
+        t->aborted = 0;
+        t->last = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {                                                    // 32 columns of tensor memory: the 128 x 32 f32 tile
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&t->tmem_base)), "r"(32u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = t->tmem_base;
+    pdl_trigger();
+    pdl_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {                                                // ---- TMA producer ----
+            for (int i = 0; i < nsteps; ++i) {
+                const int s = i % TC_STAGES;
+                if (!mbar_wait(&t->empty[s], ((i / TC_STAGES) & 1) ^ 1)) { t->aborted = 1; atomicExch(p.status, 1u); break; }
+                mbar_expect_tx(&t->full[s], TC_A_BYTES + TC_B_BYTES);
+                tma_load_2d(a_tiles + s * TC_A_BYTES, &map_w, &t->full[s], (k_begin + i) * TC_BK, tile * TC_BM);
+                tma_load_2d(b_tiles + s * TC_B_BYTES, &map_x, &t->full[s], (k_begin + i) * TC_BK, 0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {                                                // ---- MMA issuer ----
+            // instruction descriptor: D f32, A and B bf16, both K-major, N = 32, M = 128
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(TC_BN >> 3) << 17) | (uint32_t(TC_BM >> 4) << 24);
+            bool ok = true;
+            for (int i = 0; i < nsteps && ok; ++i) {
+                const int s = i % TC_STAGES;
+                ok = mbar_wait(&t->full[s], (i / TC_STAGES) & 1);
+                if (!ok) { t->aborted = 1; atomicExch(p.status, 2u); break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t da = umma_desc_sw128(a_tiles + s * TC_A_BYTES), db = umma_desc_sw128(b_tiles + s * TC_B_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < TC_BK / 16; ++kk)                 // 16 bf16 = 32 bytes = 2 descriptor units per step
+                    umma_bf16(tmem, da + 2 * kk, db + 2 * kk, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&t->empty[s]);                              // arrives when these MMAs have read the stage
+            }
+            if (ok) umma_commit(&t->accum);                             // arrives when the accumulator is complete
+        }
+    } else {                                                            // ---- epilogue: warps 2..5 ----
+        const int quad = warp & 3;                                      // the TMEM lane quadrant this warp may read
+        const int n = tile * TC_BM + quad * 32 + lane;
+        bool ok = nsteps > 0 ? mbar_wait(&t->accum, 0) : true;
+        if (!ok) { t->aborted = 1; atomicExch(p.status, 3u); }
+        uint32_t v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0u;
+        if (ok && nsteps > 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t taddr = tmem + (uint32_t(quad * 32) << 16);
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                         "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                           "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                           "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                           "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                         : "r"(taddr) : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        }
+        if (n < p.N) {
+            if (p.splits == 1) {
+#pragma unroll
+                for (int m = 0; m < 32; ++m)
+                    if (m < p.M) {
+                        float o = __uint_as_float(v[m]);
+                        if (p.residual) o = bf16_bits_to_f32(p.residual[size_t(m) * p.N + n]) + round_bf16(o);
+                        p.y[size_t(m) * p.N + n] = f32_to_bf16_bits(o);
+                    }
+            } else {
+#pragma unroll
+                for (int m = 0; m < 32; ++m)
+                    if (m < p.M) p.partial[(size_t(split) * p.M + m) * p.N + n] = __uint_as_float(v[m]);
+            }
+        }
+    }
+
+    // ---- teardown, and the split-K reduction by the last CTA of this row tile ----
+    __threadfence();
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(32u) : "memory");
+    }
+    if (p.splits > 1) {
+        if (threadIdx.x == 0) t->last = atomicAdd(&p.tickets[tile], 1u) == unsigned(p.splits - 1);
+        __syncthreads();
+        if (t->last && warp >= 2) {
+            __threadfence();
+            const int n = tile * TC_BM + (warp & 3) * 32 + lane;
+            if (n < p.N) {
+                for (int m = 0; m < p.M; ++m) {
+                    float acc = 0.f;
+                    for (int s = 0; s < p.splits; ++s) acc += __ldcg(p.partial + (size_t(s) * p.M + m) * p.N + n);   // fixed order
+                    float o = acc;
+                    if (p.residual) o = bf16_bits_to_f32(p.residual[size_t(m) * p.N + n]) + round_bf16(acc);
+                    p.y[size_t(m) * p.N + n] = f32_to_bf16_bits(o);
+                }
+            }
+            if (threadIdx.x == 64) p.tickets[tile] = 0;
+        }
+    }
+}
+
+// ---- host side: tensor maps and launch ----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+static bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
+    const cuuint64_t strides[1] = {cuuint64_t(cols) * 2};
+    const cuuint32_t box[2] = {cuuint32_t(TC_BK), cuuint32_t(box_rows)};
+    const cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int gemm_tc_splits(int n, int k) {
+    int sms = 148, dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int tiles = (n + TC_BM - 1) / TC_BM, ksteps = k / TC_BK;
+    int splits = sms / tiles;
+    if (splits < 1) splits = 1;
+    if (splits > ksteps) splits = ksteps;
+    if (splits > 16) splits = 16;
+    return splits;
+}
+
+cudaError_t gemm_tc_launch(const void* w, const void* x, TcParams p, cudaStream_t stream, bool pdl) {
+    CUtensorMap map_w, map_x;
+    if (!make_map(&map_w, w, p.N, p.K, TC_BM) || !make_map(&map_x, x, p.M, p.K, TC_BN)) return cudaErrorInvalidValue;
+    p.ksteps = p.K / TC_BK;
+    const size_t smem = 1024 + size_t(TC_STAGES) * (TC_A_BYTES + TC_B_BYTES) + sizeof(TcSmemTail);
+    static bool once = false;
+    if (!once) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return e;
+        once = true;
+    }
+    const dim3 grid((p.N + TC_BM - 1) / TC_BM, p.splits), block(TC_THREADS);
+    return launch_kernel(gemm_tc_kernel, grid, block, smem, stream, pdl, map_w, map_x, p);
+}
+
+}  // namespace tfb

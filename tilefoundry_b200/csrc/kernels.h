@@ -296,4 +296,16 @@ struct ChainParams {
 };
 cudaError_t gemv_chain_launch(ChainParams& p, cudaStream_t stream, bool pdl, size_t* smem_out);
 
+// ---- small-batch projection on tcgen05 tensor cores (gemm_tc.cu) ----
+struct TcParams {
+    float* partial;              // f32 [splits][M][N] (splits > 1)
+    uint16_t* y;                 // bf16 [M][N]
+    const uint16_t* residual;    // optional bf16 [M][N]
+    unsigned* tickets;           // u32 [ceil(N/128)], zero before the first launch (splits > 1)
+    unsigned* status;            // u32, set non-zero if a bounded wait gave up
+    int M, N, K, ksteps, splits;
+};
+int gemm_tc_splits(int n, int k);
+cudaError_t gemm_tc_launch(const void* w, const void* x, TcParams p, cudaStream_t stream, bool pdl);
+
 }  // namespace tfb

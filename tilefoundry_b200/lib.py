@@ -69,6 +69,11 @@ class GemvChainArgs(C.Structure):
     _fields_ = [("phase", GemvArgs * 4), ("n_phases", _i32), ("pdl", _i32), ("sync", _vp)]
 
 
+class GemmSmallMArgs(C.Structure):
+    _fields_ = [("w", _vp), ("x", _vp), ("residual", _vp), ("y", _vp), ("partial", _vp), ("tickets", _vp), ("status", _vp),
+                ("m", _i32), ("n", _i32), ("k", _i32), ("pdl", _i32)]
+
+
 class AttnMlaArgs(C.Structure):
     _fields_ = [("q_up", _vp), ("kv_up", _vp), ("k_rope", _vp), ("cos_table", _vp), ("sin_table", _vp),
                 ("pos", _vp), ("rope_pos", _vp), ("k_pool", _vp), ("v_pool", _vp), ("block_table", _vp),
@@ -187,6 +192,8 @@ SYMBOLS = {
     "tfb_rmsnorm": (_i32, [_vp, _vp, _vp, _i32, _i32, _f32, _i32, _vp]),
     "tfb_gemv": (_i32, [C.POINTER(GemvArgs), _vp]),
     "tfb_gemv_chain": (_i32, [C.POINTER(GemvChainArgs), _vp]),
+    "tfb_gemm_small_m_splits": (_i32, [_i32, _i32]),
+    "tfb_gemm_small_m": (_i32, [C.POINTER(GemmSmallMArgs), _vp]),
     "tfb_lm_head_scratch_entries": (_i32, [_i32]),
     "tfb_lm_head_argmax": (_i32, [C.POINTER(LmHeadArgs), _vp]),
     "tfb_attn_splits": (_i32, [_i32]),
