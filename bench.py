@@ -48,6 +48,7 @@ class Workload:
 
     def __init__(self, key):
         self.key = key
+        self.dtype = "bf16"                      # the arithmetic type of the path: bf16 storage, f32 accumulation
         if key == "qwen3_1_7b":
             from tilefoundry_b200.authored import qwen3_1_7b as a
             from tilefoundry_b200.engine.qwen3 import Qwen3Session as S
@@ -81,6 +82,7 @@ class Workload:
                              "bf16 contracted weights, batch 1, 64-token random prompt, greedy decode, paged f32 KV "
                              "for the attention layers")
             self.oracle_name, self.cpu_layers = "qwen3_5_35b_a3b", 4
+            self.dtype = "f32 activations/state, bf16 weights and products"
         else:
             raise SystemExit(f"unknown --config {key!r}")
 
@@ -197,8 +199,8 @@ def _graph_time(launches, n_launches, reps=10):
 
 
 #: dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from one ncu capture
-#: (profiles/gemv_kernel_gate_up_qwen3_1_7b.md); None where no capture was taken for that configuration.
-NCU_TRAFFIC = {"qwen3_1_7b": 50388736 + 7936}
+#: (profiles/gemv_persist_kernel_gate_up_qwen3_1_7b.md); None where no capture was taken for that configuration.
+NCU_TRAFFIC = {"qwen3_1_7b": 50387200 + 768}
 
 
 def dominant_kernel(work, sess):
@@ -213,7 +215,7 @@ def dominant_kernel(work, sess):
                 lib.gemv(layer["w_gate"], sess.hidden, sess.act, w2=layer["w_up"], gamma=layer["gamma_post"],
                          prologue=lib.NORM_CAST_THEN_GAIN, epilogue=lib.EPI_SWIGLU, eps=cfg.rms_norm_eps, pdl=True)
         nbytes = 2 * cfg.intermediate_size * cfg.hidden_size * 2
-        return ("gemv_kernel<SwiGLU> (post-attention norm + gate/up projection)",
+        return ("gemv_persist_kernel<SwiGLU> (post-attention norm + gate/up projection)",
                 _graph_time(launches, len(sess.layers)), nbytes)
     if work.key == "qwen3_5_35b_a3b":
         import ctypes as C
@@ -272,7 +274,7 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tok/s", "n_gpus": args.gpus,
         "steps": steps, "warmup": warm, "ms_per_step": 1e3 / base["value"], "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": work.dtype, "data": "synthetic",
         "config": {"workload": work.describe + " -- on host cores",
                    "note": f"bounded sample: {steps} of the requested {args.steps} steps"},
         "cpu_baseline": base,
@@ -280,6 +282,47 @@ def run_reference(args):
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def run_batch32_projection(args):
+    """The batch-32 form of the projections (config 1 of the north star): y[32, n] = x[32, k] . w[n, k]^T on the
+    tensor cores, timed over distinct weight matrices (far more than L2) in one CUDA graph, as HBM GB/s of weight
+    bytes and as TFLOP/s.  Qwen3-1.7B shapes: head, fused gate|up, down, q|k|v, o."""
+    import ctypes as C
+
+    from tilefoundry_b200 import lib
+
+    lib.load()
+    dev = torch.device("cuda:0")
+    cfg = Workload("qwen3_1_7b").cfg
+    H, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    QKV = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
+    M, out = 32, []
+    peak, kind = peaks()
+    for name, n, k in (("lm_head", V, H), ("gate|up", 2 * I, H), ("down", H, I), ("q|k|v", QKV, H), ("o", H, H)):
+        L = max(2, min(24, int(2e9 // (n * k * 2))))
+        W = [torch.randn(n, k, device=dev).to(torch.bfloat16) for _ in range(L)]
+        x = torch.randn(M, k, device=dev).to(torch.bfloat16)
+        y = torch.empty(M, n, device=dev, dtype=torch.bfloat16)
+        splits = lib.load().tfb_gemm_small_m_splits(n, k)
+        partial = torch.empty(splits * M * n, device=dev, dtype=torch.float32)
+        tickets = torch.zeros((n + 127) // 128, device=dev, dtype=torch.int32)
+        status = torch.zeros(1, device=dev, dtype=torch.int32)
+        calls = [lib.GemmSmallMArgs(w=lib.ptr(w), x=lib.ptr(x), y=lib.ptr(y), partial=lib.ptr(partial), tickets=lib.ptr(tickets),
+                                    status=lib.ptr(status), m=M, n=n, k=k, pdl=1) for w in W]
+
+        def launches():
+            for a in calls:
+                lib.check(lib.load().tfb_gemm_small_m(C.byref(a), lib.stream()), "tfb_gemm_small_m")
+        ms = _graph_time(launches, L)
+        if int(status):
+            raise RuntimeError(f"tfb_gemm_small_m: a bounded wait gave up (role {int(status)})")
+        gbs = n * k * 2 / (ms * 1e-3) / 1e9
+        out.append({"projection": name, "n": n, "k": k, "k_splits": splits, "us_per_launch": ms * 1e3, "weight_GBs": gbs,
+                    "frac_of_hbm_peak": gbs / peak, "TFLOPs": 2 * M * n * k / (ms * 1e-3) / 1e12})
+        del W
+    print(json.dumps({"mode": "batch32_projection", "kernel": "gemm_tc_kernel (tcgen05.mma, TMEM accumulator, TMA ring)",
+                      "batch": M, "dtype": "bf16", "peak_GBs": peak, "peak_kind": kind, "shapes": out}))
 
 
 def run_ours(args):
@@ -397,7 +440,7 @@ def run_ours(args):
         "metric": METRIC, "value": units * K / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong" if sharded else "weak",
         "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic",
+        "dtype": work.dtype, "data": "synthetic",
         "config": {"workload": work.describe, "name": work.key, "timed_positions": [W, W + K],
                    "parallelism": (f"ep{world} routed experts + tp{world} shared expert + vocabulary-parallel head, mixers "
                                    "replicated, one all-reduce per MoE block" if sharded else
@@ -425,12 +468,17 @@ def main():
                     choices=["qwen3_1_7b", "minicpm3_4b", "granite_4_0_h_small", "qwen3_5_35b_a3b"],
                     help="which BASELINE.json configuration to run (default: the one the metric is quoted on)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--batch32-projection", action="store_true",
+                    help="time the batch-32 tensor-core projection (tcgen05) on this configuration's projection shapes, "
+                         "print one JSON line and exit")
     ap.add_argument("--dominant-only", action="store_true",
                     help="build the session, time only the dominant kernel over every layer's weights, print it and exit "
                          "(the small case a profiler capture of that kernel runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.batch32_projection:
+        run_batch32_projection(args)
     else:
         run_ours(args)
 

@@ -6,12 +6,13 @@
 // products move to tcgen05.mma with the operands swapped: the WEIGHT tile is the MMA's 128-row A operand
 // and the token block its N = 32 B operand, both K-major in shared memory, the 128 x 32 f32 accumulator in
 // tensor memory.  The weight stream is what matters: a producer thread keeps TC_STAGES TMA tiles of
-// 128 rows x 64 columns (16 KB, 128-byte swizzle) in flight per SM, completion counted by mbarriers.
+// 128 rows x 64 columns (16 KB, 128-byte swizzle) in flight per CTA, two CTAs per SM (one fills its ring while the
+// other streams), completion counted by mbarriers.
 //
 // Roles in a CTA of 6 warps: warp 0 (one lane) issues TMA loads; warp 1 allocates tensor memory and (one lane)
 // issues the MMAs, four per stage (K = 16 each), releasing a stage with tcgen05.commit; warps 2-5 read the
 // accumulator back (tcgen05.ld, one TMEM lane quadrant each) and write it out.  K is split over blockIdx.y so
-// that a 6144 x 2048 projection (48 row tiles) still fills 144 SMs; the splits' f32 partials are added in
+// that a 6144 x 2048 projection (48 row tiles) still fills every SM; the splits' f32 partials are added in
 // fixed order by the last CTA of a row tile (atomic ticket, no spinning): deterministic.
 //
 // Every mbarrier wait is bounded; a timeout sets *status, and the CTA still frees its tensor memory.
@@ -25,7 +26,7 @@
 
 namespace tfb {
 
-constexpr int TC_BM = 128, TC_BN = 32, TC_BK = 64, TC_STAGES = 8, TC_THREADS = 192;
+constexpr int TC_BM = 128, TC_BN = 32, TC_BK = 64, TC_STAGES = 4, TC_THREADS = 192;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2, TC_B_BYTES = TC_BN * TC_BK * 2;
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 20;
 
@@ -75,7 +76,7 @@ struct TcSmemTail {
     int aborted, last;
 };
 
-__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
+__global__ void __launch_bounds__(TC_THREADS, 2) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     extern __shared__ unsigned char tc_smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~uintptr_t(1023));
@@ -188,13 +189,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
             __threadfence();
             const int n = tile * TC_BM + (warp & 3) * 32 + lane;
             if (n < p.N) {
-                for (int m = 0; m < p.M; ++m) {
-                    float acc = 0.f;
-                    for (int s = 0; s < p.splits; ++s) acc += __ldcg(p.partial + (size_t(s) * p.M + m) * p.N + n);   // fixed order
-                    float o = acc;
-                    if (p.residual) o = bf16_bits_to_f32(p.residual[size_t(m) * p.N + n]) + round_bf16(acc);
-                    p.y[size_t(m) * p.N + n] = f32_to_bf16_bits(o);
+                float acc[32];
+#pragma unroll
+                for (int m = 0; m < 32; ++m) acc[m] = 0.f;
+                for (int s = 0; s < p.splits; ++s) {                    // fixed order; 32 independent loads in flight
+                    const float* src = p.partial + size_t(s) * p.M * p.N + n;
+                    float v[32];
+#pragma unroll
+                    for (int m = 0; m < 32; ++m) v[m] = (m < p.M) ? __ldcg(src + size_t(m) * p.N) : 0.f;
+#pragma unroll
+                    for (int m = 0; m < 32; ++m) acc[m] += v[m];
                 }
+#pragma unroll
+                for (int m = 0; m < 32; ++m)
+                    if (m < p.M) {
+                        float o = acc[m];
+                        if (p.residual) o = bf16_bits_to_f32(p.residual[size_t(m) * p.N + n]) + round_bf16(acc[m]);
+                        p.y[size_t(m) * p.N + n] = f32_to_bf16_bits(o);
+                    }
             }
             if (threadIdx.x == 64) p.tickets[tile] = 0;
         }
@@ -234,7 +246,7 @@ int gemm_tc_splits(int n, int k) {
     int sms = 148, dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int tiles = (n + TC_BM - 1) / TC_BM, ksteps = k / TC_BK;
-    int splits = sms / tiles;
+    int splits = 2 * sms / tiles;                      // two CTAs (each a 4-stage, 80 KB ring) share an SM
     if (splits < 1) splits = 1;
     if (splits > ksteps) splits = ksteps;
     if (splits > 16) splits = 16;
