@@ -443,7 +443,7 @@ def run_ours(args):
         "dtype": work.dtype, "data": "synthetic",
         "config": {"workload": work.describe, "name": work.key, "timed_positions": [W, W + K],
                    "parallelism": (f"ep{world} routed experts + tp{world} shared expert + vocabulary-parallel head, mixers "
-                                   "replicated, one all-reduce per MoE block" if sharded else
+                                   f"replicated, one exchange per MoE block ({getattr(sess, 'collectives', 'nccl')} collectives)" if sharded else
                                    "replicas only" if world > 1 else "1 gpu"),
                    "l2": f"inputs larger than L2: {w_bytes / 1e9:.2f} GB of weights are streamed every step",
                    "first_tokens": tokens_out[:8]},

@@ -682,6 +682,28 @@ typedef struct {
 } tfb_qwen35_step_args;
 TFB_API int tfb_qwen35_decode_step(const tfb_qwen35_step_args* args, tfb_stream_t stream);
 
+/* ---- exchange steps of the sharded MoE step as single kernels over NVLink peer memory ---------------------
+ * tfb_moe_allreduce_finalize = all-reduce of the ranks' partial sums + tfb_moe_finalize in one launch;
+ * tfb_pick_allgather = all-gather of the ranks' (logit, index) pairs + tfb_pick_finalize in one launch.
+ * inbox[r] / flags[r] are pointers to rank r's buffers as mapped in THIS process (peer pointers for r != rank;
+ * e.g. from torch.distributed._symmetric_memory).  Sizes, per rank: reduce inbox f32 [2][world][2][hidden], reduce
+ * flags u32 [world][ceil(hidden/256)], pick inbox f32 [2][world][2], pick flags u32 [world]; all zeroed once before
+ * the first call.  epoch: local u32 [ceil(hidden/256)] (reduce) / [1] (pick), zeroed once.  Every rank must make the
+ * same sequence of calls.  Waits are bounded: on a timeout *status becomes non-zero and the outputs are invalid.
+ * No reference counterpart (the reference's sharded examples call NCCL). */
+typedef struct {
+    const float* partial; float* inbox[8]; uint32_t* flags[8]; uint32_t* epoch; uint32_t* status;
+    const void* residual; void* out;
+    int32_t hidden, rank, world, has_shared; float res_scale; int32_t pdl;
+} tfb_moe_allreduce_args;
+TFB_API int tfb_moe_allreduce_finalize(const tfb_moe_allreduce_args* args, tfb_stream_t stream);
+typedef struct {
+    const float* pair; float* inbox[8]; uint32_t* flags[8]; uint32_t* epoch; uint32_t* status;
+    int64_t* tokens; int32_t* pos; int64_t* picked;
+    int32_t n_prompt, max_tokens, rank, world, pdl, reserved;
+} tfb_pick_allgather_args;
+TFB_API int tfb_pick_allgather(const tfb_pick_allgather_args* args, tfb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

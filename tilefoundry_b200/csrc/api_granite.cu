@@ -87,6 +87,34 @@ int tfb_pick_finalize(const float* pairs, int32_t world, int64_t* tokens, int32_
                                           reinterpret_cast<long long*>(picked), S(stream), pdl != 0));
 }
 
+int tfb_moe_allreduce_finalize(const tfb_moe_allreduce_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->partial && a->epoch && a->status && a->out && a->hidden > 0, TFB_EINVAL);
+    TFB_REQUIRE(a->world >= 2 && a->world <= tfb::kMaxPeers && a->rank >= 0 && a->rank < a->world, TFB_EINVAL);
+    tfb::PeerReduceParams p = {};
+    for (int r = 0; r < a->world; ++r) {
+        TFB_REQUIRE(a->inbox[r] && a->flags[r], TFB_EINVAL);
+        p.inbox[r] = a->inbox[r]; p.flags[r] = a->flags[r];
+    }
+    p.partial = a->partial; p.epoch = a->epoch; p.status = a->status; p.residual = cu16(a->residual);
+    p.out = static_cast<uint16_t*>(a->out); p.hidden = a->hidden; p.rank = a->rank; p.world = a->world;
+    p.has_shared = a->has_shared; p.res_scale = a->res_scale;
+    return done(tfb::moe_allreduce_finalize_launch(p, S(stream), a->pdl != 0));
+}
+
+int tfb_pick_allgather(const tfb_pick_allgather_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->pair && a->epoch && a->status && (a->picked || (a->tokens && a->pos)), TFB_EINVAL);
+    TFB_REQUIRE(a->world >= 2 && a->world <= tfb::kMaxPeers && a->rank >= 0 && a->rank < a->world, TFB_EINVAL);
+    tfb::PeerPickParams p = {};
+    for (int r = 0; r < a->world; ++r) {
+        TFB_REQUIRE(a->inbox[r] && a->flags[r], TFB_EINVAL);
+        p.inbox[r] = a->inbox[r]; p.flags[r] = a->flags[r];
+    }
+    p.pair = a->pair; p.epoch = a->epoch; p.status = a->status; p.tokens = reinterpret_cast<long long*>(a->tokens);
+    p.pos = a->pos; p.picked = reinterpret_cast<long long*>(a->picked); p.n_prompt = a->n_prompt;
+    p.max_tokens = a->max_tokens; p.rank = a->rank; p.world = a->world;
+    return done(tfb::pick_allgather_launch(p, S(stream), a->pdl != 0));
+}
+
 static int granite_part(const tfb_granite_step_args* a, int part, int layer, tfb_stream_t stream);
 
 int tfb_granite_step_part(const tfb_granite_step_args* a, int32_t part, int32_t layer, tfb_stream_t stream) {

@@ -308,4 +308,31 @@ struct TcParams {
 int gemm_tc_splits(int n, int k);
 cudaError_t gemm_tc_launch(const void* w, const void* x, TcParams p, cudaStream_t stream, bool pdl);
 
+// ---- exchange steps over NVLink peer memory (collective.cu) ----
+constexpr int kMaxPeers = 8;
+struct PeerReduceParams {
+    const float* partial;            // local f32 [2][hidden]: this rank's routed sum and shared dot
+    float* inbox[kMaxPeers];         // rank r's inbox (peer pointer): f32 [2 parities][world][2][hidden]
+    unsigned* flags[kMaxPeers];      // rank r's flags (peer pointer): u32 [world][ceil(hidden/256)]
+    unsigned* epoch;                 // local u32 [ceil(hidden/256)], zero at start
+    unsigned* status;                // local u32
+    const uint16_t* residual;
+    uint16_t* out;
+    int hidden, rank, world, has_shared;
+    float res_scale;
+};
+cudaError_t moe_allreduce_finalize_launch(const PeerReduceParams& p, cudaStream_t stream, bool pdl);
+struct PeerPickParams {
+    const float* pair;               // local f32 [2]: (best logit, global index) of this rank's vocabulary slice
+    float* inbox[kMaxPeers];         // rank r's inbox: f32 [2 parities][world][2]
+    unsigned* flags[kMaxPeers];      // rank r's flags: u32 [world]
+    unsigned* epoch;                 // local u32 [1]
+    unsigned* status;
+    long long* tokens;
+    int* pos;
+    long long* picked;
+    int n_prompt, max_tokens, rank, world;
+};
+cudaError_t pick_allgather_launch(const PeerPickParams& p, cudaStream_t stream, bool pdl);
+
 }  // namespace tfb

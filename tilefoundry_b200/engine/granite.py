@@ -26,9 +26,12 @@ def pack_mixer(kind: str, w: dict) -> dict:
 
 class GraniteSession(DecodeSession):
     def __init__(self, cfg: GraniteConfig, resource, *, max_ctx: int = 2176, device="cuda:0",
-                 keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True, group=None):
+                 keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True, group=None,
+                 collectives: str | None = None):
         """*group*: a ``torch.distributed`` process group (NCCL) to shard the MoE blocks and the head over;
-        ``None`` runs everything on this GPU."""
+        ``None`` runs everything on this GPU.  *collectives*: ``"peer"`` = the two exchange steps as single kernels
+        over NVLink peer memory (symmetric memory), ``"nccl"`` = NCCL all-reduce / all-gather followed by the
+        finishing kernels; ``None`` picks ``"peer"`` when symmetric memory can be set up, else ``"nccl"``."""
         if not torch.cuda.is_available():
             raise RuntimeError("GraniteSession needs a CUDA device; there is no CPU path")
         self.group = group
@@ -117,12 +120,66 @@ class GraniteSession(DecodeSession):
             hidden_trace=lib.ptr(self.trace), idx_trace=lib.ptr(self.idx_trace), picked=lib.ptr(self.picked),
             pdl=int(pdl), ep_rank=self.rank, ep_world=self.world, partial=lib.ptr(self.partial),
             pair=lib.ptr(self.pair), gathered=lib.ptr(self.gathered))
+        self.collectives = "none"
+        if self.world > 1:
+            self.collectives = self._setup_peer_exchange(H, collectives)
         n_m = sum(1 for l in self.layers if l["kind"] == "linear_attention")
         self.launches_per_step = 2 + 9 * n_m + 8 * (L - n_m) + (2 * L + 1 if trace_hidden else 0) + (
             L + 1 if self.world > 1 else 0)              # sharded: one finalize per layer and the final pick
 
+    def _setup_peer_exchange(self, H: int, want: str | None) -> str:
+        """Symmetric buffers for the peer-memory exchange kernels: every rank's inboxes and flags, mapped into every
+        process.  Returns the mode in use."""
+        import torch.distributed as dist
+        if want == "nccl":
+            return "nccl"
+        W, n_cta = self.world, (H + 255) // 256
+        words = [2 * W * 2 * H, W * n_cta, 2 * W * 2, W]              # reduce inbox, reduce flags, pick inbox, pick flags
+        words = [(w + 63) // 64 * 64 for w in words]                   # keep every region 256-byte aligned
+        ok = torch.ones(1, device=self.device)
+        try:
+            import torch.distributed._symmetric_memory as symm
+            self._sym = symm.empty(sum(words), dtype=torch.float32, device=self.device)
+            self._sym.zero_()
+            self._sym_handle = symm.rendezvous(self._sym, self.group)
+            ptrs = [int(p) for p in self._sym_handle.buffer_ptrs]
+        except Exception as exc:                                       # noqa: BLE001 -- any failure means "not available here"
+            why = repr(exc)
+            ok.zero_()
+            ptrs = None
+        else:
+            why = "another rank could not map symmetric memory"
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)    # all ranks agree on the mode
+        if float(ok) == 0.0:
+            if want == "peer":
+                raise RuntimeError(f"peer-memory collectives were requested but are unavailable: {why}")
+            return "nccl"
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)                                 # every inbox and flag is zero before any push
+        off = [0, words[0] * 4, (words[0] + words[1]) * 4, (words[0] + words[1] + words[2]) * 4]
+        z = lambda n: torch.zeros(n, device=self.device, dtype=torch.int32)
+        self.peer_epoch, self.pick_epoch, self.peer_status = z(n_cta), z(1), z(1)
+        a = self.args
+        self._reduce_args = lib.MoeAllreduceArgs(
+            partial=lib.ptr(self.partial), epoch=lib.ptr(self.peer_epoch), status=lib.ptr(self.peer_status),
+            residual=lib.ptr(self.hidden), out=lib.ptr(self.hidden), hidden=H, rank=self.rank, world=W, has_shared=1,
+            res_scale=a.res_scale, pdl=a.pdl)
+        self._pick_args = lib.PickAllgatherArgs(
+            pair=lib.ptr(self.pair), epoch=lib.ptr(self.pick_epoch), status=lib.ptr(self.peer_status),
+            tokens=lib.ptr(self.tokens), pos=lib.ptr(self.pos), picked=lib.ptr(self.picked), n_prompt=0,
+            max_tokens=self.max_ctx + 1, rank=self.rank, world=W, pdl=a.pdl)
+        for r in range(W):
+            self._reduce_args.inbox[r], self._reduce_args.flags[r] = ptrs[r] + off[0], ptrs[r] + off[1]
+            self._pick_args.inbox[r], self._pick_args.flags[r] = ptrs[r] + off[2], ptrs[r] + off[3]
+        return "peer"
+
     def reset(self, prompt_ids) -> None:
         super().reset(prompt_ids)
+        if self.collectives == "peer":
+            import torch.distributed as dist
+            self._pick_args.n_prompt = self.args.n_prompt
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)           # the ranks' kernels wait on one another: start them together
         for layer in self.layers:                    # recurrent state starts at zero for a new sequence
             if layer["kind"] == "linear_attention":
                 layer["conv_state"].zero_()
@@ -165,11 +222,19 @@ class GraniteSession(DecodeSession):
         import torch.distributed as dist
         part = lambda p, l=0: lib.check(lib.load().tfb_granite_step_part(C.byref(self.args), p, l, lib.stream()),
                                         "tfb_granite_step_part")
+        peer = self.collectives == "peer"
         part(0)
         for l in range(len(self.layers)):
             part(1, l)
-            dist.all_reduce(self.partial, group=self.group)          # one reduction per MoE block
-            part(2, l)
+            if peer:                                                 # exchange + finish in one kernel over NVLink
+                lib.check(lib.load().tfb_moe_allreduce_finalize(C.byref(self._reduce_args), lib.stream()),
+                          "tfb_moe_allreduce_finalize")
+            else:
+                dist.all_reduce(self.partial, group=self.group)      # one reduction per MoE block
+                part(2, l)
         part(3)
-        dist.all_gather_into_tensor(self.gathered, self.pair, group=self.group)
-        part(4)
+        if peer:
+            lib.check(lib.load().tfb_pick_allgather(C.byref(self._pick_args), lib.stream()), "tfb_pick_allgather")
+        else:
+            dist.all_gather_into_tensor(self.gathered, self.pair, group=self.group)
+            part(4)

@@ -74,6 +74,18 @@ class GemmSmallMArgs(C.Structure):
                 ("m", _i32), ("n", _i32), ("k", _i32), ("pdl", _i32)]
 
 
+class MoeAllreduceArgs(C.Structure):
+    _fields_ = [("partial", _vp), ("inbox", _vp * 8), ("flags", _vp * 8), ("epoch", _vp), ("status", _vp),
+                ("residual", _vp), ("out", _vp), ("hidden", _i32), ("rank", _i32), ("world", _i32), ("has_shared", _i32),
+                ("res_scale", _f32), ("pdl", _i32)]
+
+
+class PickAllgatherArgs(C.Structure):
+    _fields_ = [("pair", _vp), ("inbox", _vp * 8), ("flags", _vp * 8), ("epoch", _vp), ("status", _vp), ("tokens", _vp),
+                ("pos", _vp), ("picked", _vp), ("n_prompt", _i32), ("max_tokens", _i32), ("rank", _i32), ("world", _i32),
+                ("pdl", _i32), ("reserved", _i32)]
+
+
 class AttnMlaArgs(C.Structure):
     _fields_ = [("q_up", _vp), ("kv_up", _vp), ("k_rope", _vp), ("cos_table", _vp), ("sin_table", _vp),
                 ("pos", _vp), ("rope_pos", _vp), ("k_pool", _vp), ("v_pool", _vp), ("block_table", _vp),
@@ -222,6 +234,8 @@ SYMBOLS = {
     "tfb_rmsnorm_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _f32, _i32, _vp]),
     "tfb_residual_add_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp]),
     "tfb_qwen35_decode_step": (_i32, [C.POINTER(Qwen35StepArgs), _vp]),
+    "tfb_moe_allreduce_finalize": (_i32, [C.POINTER(MoeAllreduceArgs), _vp]),
+    "tfb_pick_allgather": (_i32, [C.POINTER(PickAllgatherArgs), _vp]),
     "tfb_pick_finalize": (_i32, [_vp, _i32, _vp, _vp, _i32, _i32, _vp, _i32, _vp]),
 }
 
