@@ -97,6 +97,22 @@ __global__ void __launch_bounds__(kAttnThreads) attn_gqa_kernel(const AttnParams
     pdl_wait();
     trace_waited(p.trace);
 
+    // this token's q/k/v do not depend on the position word: request them before reading it
+    uint16_t xraw[2][D / 32];                    // up to two vectors per warp (NV + 1 <= 2 * NWARP)
+    int vis[2] = {warp, warp + NWARP};
+#pragma unroll
+    for (int s2 = 0; s2 < 2; ++s2) {
+        const int vi = vis[s2];
+        if (vi < NV + 1) {
+            const uint16_t* src;
+            if (vi < G) src = p.qkv + size_t(g * G + vi) * D;
+            else if (vi == G) src = p.qkv + size_t(p.hq) * D + size_t(g) * D;
+            else src = p.qkv + size_t(p.hq + p.hkv) * D + size_t(g) * D;
+#pragma unroll
+            for (int i = 0; i < D / 32; ++i) xraw[s2][i] = src[lane + 32 * i];
+        }
+    }
+
     const int pos = *p.pos;
     const int total = pos + 1;
     const int n_active = (total + kSplitLen - 1) / kSplitLen;
@@ -126,20 +142,11 @@ __global__ void __launch_bounds__(kAttnThreads) attn_gqa_kernel(const AttnParams
         rot[0][tid] = bf16_bits_to_f32(p.cos_table[size_t(rpos) * rd + tid]);
         rot[1][tid] = bf16_bits_to_f32(p.sin_table[size_t(rpos) * rd + tid]);
     }
-    float xv[2][D / 32];                         // up to two vectors per warp (NV + 1 <= 2 * NWARP)
-    int vis[2] = {warp, warp + NWARP};
+    float xv[2][D / 32];
 #pragma unroll
-    for (int s2 = 0; s2 < 2; ++s2) {
-        const int vi = vis[s2];
-        if (vi < NV + 1) {
-            const uint16_t* src;
-            if (vi < G) src = p.qkv + size_t(g * G + vi) * D;
-            else if (vi == G) src = p.qkv + size_t(p.hq) * D + size_t(g) * D;
-            else src = p.qkv + size_t(p.hq + p.hkv) * D + size_t(g) * D;
+    for (int s2 = 0; s2 < 2; ++s2)
 #pragma unroll
-            for (int i = 0; i < D / 32; ++i) xv[s2][i] = bf16_bits_to_f32(src[lane + 32 * i]);
-        }
-    }
+        for (int i = 0; i < D / 32; ++i) xv[s2][i] = (vis[s2] < NV + 1) ? bf16_bits_to_f32(xraw[s2][i]) : 0.f;
     __syncthreads();                             // rot[] / gain[] visible
 #pragma unroll
     for (int s2 = 0; s2 < 2; ++s2) {
