@@ -91,7 +91,9 @@ def nested_walk(ref, cfg_kinds, forced, steps):
             fresh.append(tuple(state))
             hiddens.append(hidden.reshape(-1))
             picks.append(idx.reshape(-1))
-            logits = torch.matmul(tokens.to(torch.bfloat16), layer.moe.router.constants["w_router"]).float().reshape(-1)
+            w_r = layer.moe.router.constants["w_router"]
+            w_r = w_r if w_r.shape[0] == tokens.shape[-1] else w_r.t()          # authored as (in, out) or (out, in)
+            logits = torch.matmul(tokens.to(w_r.dtype), w_r).float().reshape(-1)
             top = torch.topk(logits, idx.numel() + 1).values
             margins.append(float(top[-2] - top[-1]))
         after = ref.append_cache(caches, tuple(fresh))

@@ -152,3 +152,41 @@ def test_qwen3_5_layers_match_reference_torch_ref_vectors(golden_dir):
     normed = loaded.final_rms_norm(fx["attn_cases"][-1]["out"])
     _close_f32(normed, fx["final_norm"], "final norm", tol=1e-5)
     _close_f32(loaded.lm_head(fx["final_norm"]), fx["logits"], "logits", tol=0)
+
+
+# ---- granite-4.0-h: pinned by Hugging Face GraniteMoeHybridForCausalLM on seeded weights ---------------------
+
+def test_granite_matches_hf_granitemoehybrid(golden_dir):
+    """`tests/golden/granite_tiny_hf.pt` holds Hugging Face ``GraniteMoeHybridForCausalLM`` (plain-torch Mamba-2 path)
+    on the seeded weights, mapped as the reference's ``examples/granite_4_0_h_small-cuda/hf_alias.py`` maps a
+    checkpoint, run over 20 tokens at f32 and at bf16.  The evaluator walks the same tokens step by step (recurrent
+    state and KV cache carried), rounding to bf16 after every op; against the f32 run it must stay inside bf16
+    noise at every position: logits within 1 % of their scale, every layer's output within 2.5 %, and the same
+    greedy token unless the f32 run's own top-2 margin is inside that noise."""
+    from oracle import granite_4_0_h_small as og
+    from tests import parity
+    from tilefoundry_b200.authored import granite_4_0_h_small as gr
+
+    fx = torch.load(golden_dir / "granite_tiny_hf.pt")
+    cfg = gr.GraniteConfig(**{**fx["config"], "attention_layers": tuple(fx["config"]["attention_layers"])})
+    mod = gr.build(cfg)
+    weights = random_weights(mod, seed=fx["seed_w"], std=fx["std"], overrides=gr.weight_overrides)
+    ref = evaluator.load(mod, DictResource(weights), og.make(cfg))
+    ids, want = fx["ids"], fx["f32"]
+    L = cfg.num_hidden_layers
+    for step, _, logits, hiddens, _, _, _ in parity.nested_walk(ref, cfg.layer_types, ids, ids.numel()):
+        hl = want["logits"][step].float()
+        err = (logits[0].float() - hl).abs().max().item()
+        assert err <= 1e-2 * hl.abs().max().item(), f"position {step}: logits differ by {err:.4g}"
+        for li in range(L - 1):                          # HF's last entry is after the final norm
+            hh = want["hidden"][li + 1, step].float()
+            eh = (hiddens[li].float() - hh).abs().max().item()
+            assert eh <= 2.5e-2 * hh.abs().max().item(), f"position {step} layer {li}: hidden differs by {eh:.4g}"
+        if int(logits.argmax()) != int(hl.argmax()):
+            top = torch.topk(hl, 2).values
+            assert float(top[0] - top[1]) <= 2 * err, f"position {step}: greedy token differs outside the noise"
+    # the two Hugging Face runs bracket the evaluator: it is no farther from f32 than HF's own bf16 run is
+    hf_gap = (fx["bf16"]["logits"].float() - want["logits"].float()).abs().max().item()
+    ours = max((logits[0].float() - want["logits"][step].float()).abs().max().item()
+               for step, _, logits, _, _, _, _ in parity.nested_walk(ref, cfg.layer_types, ids, ids.numel()))
+    assert ours <= 1.25 * hf_gap + 1e-3, f"evaluator {ours:.4g} vs HF bf16 {hf_gap:.4g} from the f32 run"
