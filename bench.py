@@ -44,7 +44,7 @@ def peaks():
 
 
 class Workload:
-    """One BASELINE.json configuration: how to build the authored Module, the session, the oracle."""
+    """One benchmark configuration: how to build the authored Module, the session, the oracle."""
 
     def __init__(self, key):
         self.key = key
@@ -466,7 +466,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="qwen3_1_7b",
                     choices=["qwen3_1_7b", "minicpm3_4b", "granite_4_0_h_small", "qwen3_5_35b_a3b"],
-                    help="which BASELINE.json configuration to run (default: the one the metric is quoted on)")
+                    help="which configuration to run (default: the one the metric is quoted on)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--batch32-projection", action="store_true",
                     help="time the batch-32 tensor-core projection (tcgen05) on this configuration's projection shapes, "

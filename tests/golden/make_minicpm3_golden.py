@@ -6,7 +6,7 @@ composes it (``examples/minicpm3_4b-cutedsl/runtime_model.py:148-196``).
 transformers 5.5.0 has no MiniCPM3 class, so a Hugging Face pin is not available for this model; this
 is the reference-produced pin that is.  Run where the reference checkout is mounted:
 
-    python tests/golden/make_minicpm3_golden.py [/root/reference]
+    python tests/golden/make_minicpm3_golden.py <path to the reference checkout>
 """
 from __future__ import annotations
 
@@ -52,7 +52,9 @@ def layer(K, cfg, w, hidden, cos, sin, pos, k_cache, v_cache, scale, alpha):
 
 
 def main():
-    ref_root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_minicpm3_golden.py <path to the reference checkout>")
+    ref_root = Path(sys.argv[1])
     K = load_reference_ops(ref_root)
     cfg = m.MINICPM3_TINY
     weights = random_weights(m.build(cfg), seed=SEED_W, std=STD)

@@ -6,7 +6,7 @@ on torch and its sibling ``config.py`` only), composed as the authored layer for
 
 Run where the reference checkout is mounted:
 
-    python tests/golden/make_qwen3_5_golden.py [/root/reference]
+    python tests/golden/make_qwen3_5_golden.py <path to the reference checkout>
 """
 from __future__ import annotations
 
@@ -50,7 +50,9 @@ def moe(R, w, hidden):
 
 
 def main():
-    ref_root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_qwen3_5_golden.py <path to the reference checkout>")
+    ref_root = Path(sys.argv[1])
     R = load_torch_ref(ref_root)
     cfg = m.QWEN3_5_TINY
     R.TOP_K = cfg.top_k

@@ -18,7 +18,7 @@ def assert_ulps(got, want, ulps, msg=""):
     assert err <= bound, f"{msg}: max err {err:.4g} > {ulps} ulp-at-scale = {bound:.4g}"
 
 
-# BASELINE tolerance for bf16 hidden states and logits
+# the stated tolerance for bf16 hidden states and logits
 RTOL = 2e-2
 ATOL = 2e-2
 
