@@ -605,8 +605,8 @@ TFB_API int tfb_partial_rope_f32(const float* x, const float* cos_table, const f
  * 0..*pos, output times sigmoid(gate) (examples/qwen3_5_35b_a3b-tilelang/model.py:293-417).
  * proj = [hq][2*d] (q then gate per head) | [hkv][d] k | [hkv][d] v.  Pools are [page][page_size][hkv][d] f32,
  * page_size a multiple of 64.
- * Scratch: part_o f32 [hq * nsplit * d], part_ml f32 [hq * nsplit * 2], counters u32 [hkv] zeroed once, with
- * nsplit = tfb_attn_gated_splits(max_ctx). */
+ * Scratch: part_o f32 [hq * nsplit * d], part_ml f32 [hq * nsplit * 2], counters u32 [tfb_attn_gated_groups(hq, hkv, d)]
+ * zeroed once, with nsplit = tfb_attn_gated_splits(max_ctx). */
 typedef struct {
     const float* proj; const float* gamma_q; const float* gamma_k;
     const float* cos_table; const float* sin_table;
@@ -619,6 +619,7 @@ typedef struct {
     int32_t pdl, reserved;
 } tfb_attn_gated_args;
 TFB_API int32_t tfb_attn_gated_splits(int32_t max_ctx);
+TFB_API int32_t tfb_attn_gated_groups(int32_t hq, int32_t hkv, int32_t d);
 TFB_API int tfb_attn_gated_decode(const tfb_attn_gated_args* args, tfb_stream_t stream);
 
 /* out[j] = residual[j] + sum_s weights[s] * bf16(w_down[indices[s]][j,:] . inner[s,:])
@@ -675,7 +676,7 @@ typedef struct {
     float eps, attn_scale, q_scale;
     float* hidden_buf; float* attended_buf; float* proj_buf; float* mixed_buf;
     float* router_logits; int64_t* router_idx; float* router_w; float* inner_buf;
-    float* part_o; float* part_ml; uint32_t* counters /* [hkv + 2], zeroed once */; float* head_val; int32_t* head_idx;
+    float* part_o; float* part_ml; uint32_t* counters /* [tfb_attn_gated_groups(hq, hkv, d) + 1], zeroed once */; float* head_val; int32_t* head_idx;
     void* logits; int64_t* picked;
     float* hidden_trace;      /* optional f32 [(n_layers + 1)][hidden]: every layer's output, then the final norm */
     int64_t* idx_trace;       /* optional [n_layers][top_k] */

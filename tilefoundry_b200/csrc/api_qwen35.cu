@@ -67,6 +67,9 @@ int tfb_gdn_step(const tfb_gdn_args* a, tfb_stream_t stream) {
 }
 
 int32_t tfb_attn_gated_splits(int32_t max_ctx) { return tfb::attn_gated_splits(max_ctx); }
+int32_t tfb_attn_gated_groups(int32_t hq, int32_t hkv, int32_t d) {
+    return (hq > 0 && hkv > 0 && hq % hkv == 0) ? tfb::attn_gated_groups(hq, hkv, d) : 0;
+}
 
 int tfb_attn_gated_decode(const tfb_attn_gated_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->proj && a->gamma_q && a->gamma_k && a->cos_table && a->sin_table && a->pos && a->k_pool &&
@@ -84,6 +87,7 @@ int tfb_attn_gated_decode(const tfb_attn_gated_args* a, tfb_stream_t stream) {
     p.part_o = a->part_o; p.part_ml = a->part_ml; p.counters = a->counters;
     p.hq = a->hq; p.hkv = a->hkv; p.d = a->d; p.rotary_dim = a->rotary_dim; p.page_size = a->page_size;
     p.max_ctx = a->max_ctx; p.nsplit = tfb::attn_gated_splits(a->max_ctx); p.eps = a->eps; p.scale = a->scale;
+    p.trace = next_trace();
     return done(tfb::attn_gated_dispatch(p, S(stream), a->pdl != 0));
 }
 
@@ -230,7 +234,7 @@ int tfb_qwen35_decode_step(const tfb_qwen35_step_args* a, tfb_stream_t stream) {
     tfb_lm_head_args h;
     std::memset(&h, 0, sizeof h);
     h.w = a->w_head; h.x = hid; h.gamma = a->gamma_final; h.logits = a->logits;
-    h.scratch_val = a->head_val; h.scratch_idx = a->head_idx; h.counter = a->counters + a->hkv;
+    h.scratch_val = a->head_val; h.scratch_idx = a->head_idx; h.counter = a->counters + tfb::attn_gated_groups(a->hq, a->hkv, a->d);
     h.n = int(a->vocab); h.k = H; h.prologue = TFB_NORM_F32_INPUT; h.eps = a->eps;
     h.x_scale = 1.f; h.out_scale = 1.f; h.pdl = pdl; h.token_out = a->picked;
     h.tokens = a->tokens; h.pos = a->pos; h.n_prompt = a->n_prompt; h.max_tokens = a->max_tokens;

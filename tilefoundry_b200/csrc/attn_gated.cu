@@ -18,27 +18,65 @@ constexpr int kGatedThreads = 256;
 
 int attn_gated_splits(int max_ctx) { return (max_ctx + kGatedSplit - 1) / kGatedSplit; }
 
-template <int D, int G>
+// GH query heads per CTA: the G heads of a KV head are spread over G/GH CTAs so that a short context still
+// occupies tens of SMs and no CTA carries more than GH heads x 64 positions of serial work.
+template <int D, int G, int GH>
 __global__ void __launch_bounds__(kGatedThreads) attn_gated_kernel(const GatedAttnParams p) {
     constexpr int NWARP = kGatedThreads / 32;
     constexpr int EPL = D / 32;                       // elements of one vector per lane
-    constexpr int HG = (G * D) / kGatedThreads;       // heads per thread in the PV stage (thread owns one dim)
-    static_assert((G * D) % kGatedThreads == 0 && HG >= 1 && kGatedThreads % D == 0 && EPL % 4 == 0, "shape");
+    constexpr int V4 = EPL / 4;                       // float4 per lane per row
+    constexpr int HG = (GH * D) / kGatedThreads;      // heads per thread in the PV stage (thread owns one dim)
     constexpr int NGRP = kGatedThreads / D;           // head groups in the PV stage
-    static_assert(NGRP * HG == G, "shape");
+    constexpr int NV = GH + 2;                        // vectors prepared: GH queries, the key, the value
+    static_assert(G % GH == 0 && (GH * D) % kGatedThreads == 0 && HG >= 1 && kGatedThreads % D == 0 && EPL % 4 == 0 &&
+                      NGRP * HG == GH && NV <= NWARP, "shape");
 
-    __shared__ __align__(16) float vec[G + 2][D];     // q_0..q_{G-1} (scaled), k_new, v_new
-    __shared__ float sc[G][kGatedSplit];
-    __shared__ float stat_m[G], stat_l[G];
-    __shared__ float mrg_w[G][64];
+    __shared__ __align__(16) float vec[NV][D];        // q_0..q_{GH-1} (scaled), k_new, v_new
+    __shared__ float sc[GH][kGatedSplit];
+    __shared__ float stat_m[GH], stat_l[GH];
+    __shared__ float mrg_w[GH][64];
     __shared__ int s_last;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = blockIdx.x, split = blockIdx.y;
+    const int g = blockIdx.x / (G / GH), hg = blockIdx.x % (G / GH), split = blockIdx.y;
+    const int head0 = g * G + hg * GH;                // first query head of this CTA
     const int p0 = split * kGatedSplit;
 
+    // ---- before the dependency wait: ask L2 for this split's cached rows.  Between two uses of a row a whole
+    // step's weights (GBs) stream through L2, so the rows come from HBM; the position word may be a step behind
+    // here, which only leaves one row un-prefetched. ----
+    if (hg == 0) {
+        const int pos_early = *reinterpret_cast<const volatile int*>(p.pos);
+        if (pos_early >= 0 && pos_early < p.max_ctx && p0 < pos_early) {
+            const int rows = min(kGatedSplit, pos_early - p0);
+            const int page_e = p.block_table[p0 / p.page_size];
+            const size_t first_e = (size_t(page_e) * p.page_size + (p0 % p.page_size)) * p.hkv + g;
+            constexpr int LINES = D * 4 / 128;             // 128-byte lines per row
+            for (int i = tid; i < rows * LINES * 2; i += kGatedThreads) {
+                const int which = i / (rows * LINES), rest = i % (rows * LINES);
+                const float* base = (which ? p.v_pool : p.k_pool) + (first_e + size_t(rest / LINES) * p.hkv) * D + (rest % LINES) * 32;
+                asm volatile("prefetch.global.L2 [%0];" :: "l"(base));
+            }
+        }
+    }
+    trace_start(p.trace);
     pdl_trigger();
     pdl_wait();
+    trace_waited(p.trace);
+    // ---- this token's q (GH heads), k, v: one warp per vector; the loads go out before the position is read ----
+    float x[EPL], gm[EPL], cs[EPL], sn[EPL];
+    const int vi = warp;
+    const int rd = p.rotary_dim, half = rd >> 1;
+    const int rpos_early = p.rope_pos ? *p.rope_pos : *p.pos;          // issued together with the vector loads
+    if (vi < NV) {
+        const float* src;
+        if (vi < GH) src = p.proj + size_t(head0 + vi) * 2 * D;                      // q half of the q|gate pair
+        else if (vi == GH) src = p.proj + size_t(p.hq) * 2 * D + size_t(g) * D;
+        else src = p.proj + size_t(p.hq) * 2 * D + size_t(p.hkv) * D + size_t(g) * D;
+        const float* gsrc = vi < GH ? p.gamma_q : p.gamma_k;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) { x[i] = src[lane + 32 * i]; gm[i] = gsrc[lane + 32 * i]; }
+    }
     const int pos = *p.pos;
     const int total = pos + 1;
     const int n_active = (total + kGatedSplit - 1) / kGatedSplit;
@@ -46,107 +84,131 @@ __global__ void __launch_bounds__(kGatedThreads) attn_gated_kernel(const GatedAt
     const bool owner = (split == n_active - 1);
     const int p1 = min(p0 + kGatedSplit, total);
     const int n = p1 - p0;                             // positions of this split, the new one included
-    const int rd = p.rotary_dim, half = rd >> 1;
-    const int rpos = p.rope_pos ? *p.rope_pos : pos;
+    const int rpos = rpos_early;
 
-    // ---- this token's q (G heads), k, v for KV head g: one warp per vector, all in registers ----
-    for (int vi = warp; vi < G + 2; vi += NWARP) {
-        const float* src;
-        if (vi < G) src = p.proj + size_t(g * G + vi) * 2 * D;                       // q half of the q|gate pair
-        else if (vi == G) src = p.proj + size_t(p.hq) * 2 * D + size_t(g) * D;
-        else src = p.proj + size_t(p.hq) * 2 * D + size_t(p.hkv) * D + size_t(g) * D;
-        float x[EPL];
-#pragma unroll
-        for (int i = 0; i < EPL; ++i) x[i] = src[lane + 32 * i];
-        if (vi == G + 1) {
+    if (vi < NV) {
+        if (vi == GH + 1) {
 #pragma unroll
             for (int i = 0; i < EPL; ++i) vec[vi][lane + 32 * i] = x[i];
-            continue;
-        }
-        float ss = 0.f;
+        } else {
 #pragma unroll
-        for (int i = 0; i < EPL; ++i) ss = fmaf(x[i], x[i], ss);
-        ss = warp_sum(ss);
-        const float rstd = rsqrtf(ss / float(D) + p.eps);
-        const float* gm = vi < G ? p.gamma_q : p.gamma_k;
-#pragma unroll
-        for (int i = 0; i < EPL; ++i) x[i] = x[i] * rstd * gm[lane + 32 * i];
-#pragma unroll
-        for (int i = 0; i < EPL; ++i) {
-            const int e = lane + 32 * i;
-            float r = x[i];
-            if (e < rd) {                              // partner e +- half sits in the same lane (half % 32 == 0)
-                const int pi = (e < half) ? i + half / 32 : i - half / 32;
-                float partner = 0.f;
-#pragma unroll
-                for (int k2 = 0; k2 < EPL; ++k2) if (k2 == pi) partner = x[k2];
-                if (e < half) partner = -partner;
-                r = __fadd_rn(__fmul_rn(x[i], p.cos_table[size_t(rpos) * rd + e]),
-                              __fmul_rn(partner, p.sin_table[size_t(rpos) * rd + e]));
+            for (int i = 0; i < EPL; ++i) {
+                const int e = lane + 32 * i;
+                cs[i] = e < rd ? p.cos_table[size_t(rpos) * rd + e] : 1.f;
+                sn[i] = e < rd ? p.sin_table[size_t(rpos) * rd + e] : 0.f;
             }
-            if (vi < G) r *= p.scale;
-            vec[vi][e] = r;
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) ss = fmaf(x[i], x[i], ss);
+            ss = warp_sum(ss);
+            const float rstd = rsqrtf(ss / float(D) + p.eps);
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) x[i] = x[i] * rstd * gm[i];
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) {
+                const int e = lane + 32 * i;
+                float r = x[i];
+                if (e < rd) {                          // partner e +- half sits in the same lane (half % 32 == 0)
+                    const int pi = (e < half) ? i + half / 32 : i - half / 32;
+                    float partner = 0.f;
+#pragma unroll
+                    for (int k2 = 0; k2 < EPL; ++k2) if (k2 == pi) partner = x[k2];
+                    if (e < half) partner = -partner;
+                    r = __fadd_rn(__fmul_rn(x[i], cs[i]), __fmul_rn(partner, sn[i]));
+                }
+                if (vi < GH) r *= p.scale;
+                vec[vi][e] = r;
+            }
         }
     }
     __syncthreads();
+    trace_mark(p.trace, 0);
 
-    if (owner) {                                       // append this token's entry
+    if (owner && hg == 0) {                            // append this token's entry (one CTA per KV head)
         const int page = p.block_table[pos / p.page_size];
         const size_t base = ((size_t(page) * p.page_size + (pos % p.page_size)) * p.hkv + g) * D;
         for (int i = tid; i < D; i += kGatedThreads) {
-            p.k_pool[base + i] = vec[G][i];
-            p.v_pool[base + i] = vec[G + 1][i];
-            if (p.k_new_out) p.k_new_out[size_t(g) * D + i] = vec[G][i];
-            if (p.v_new_out) p.v_new_out[size_t(g) * D + i] = vec[G + 1][i];
+            p.k_pool[base + i] = vec[GH][i];
+            p.v_pool[base + i] = vec[GH + 1][i];
+            if (p.k_new_out) p.k_new_out[size_t(g) * D + i] = vec[GH][i];
+            if (p.v_new_out) p.v_new_out[size_t(g) * D + i] = vec[GH + 1][i];
         }
     }
-
-    __syncthreads();                                   // the appended row is visible to the whole CTA
     // A split never straddles a page (the page size is a multiple of kGatedSplit): its rows are contiguous in the
-    // pool, hkv*D floats apart.
+    // pool, hkv*D floats apart.  The new row is taken from shared memory: the CTA that appends it may be another.
     const int page = p.block_table[p0 / p.page_size];
     const size_t row_stride = size_t(p.hkv) * D;
     const size_t first = (size_t(page) * p.page_size + (p0 % p.page_size)) * p.hkv + g;
     const float* kbase = p.k_pool + first * D;
     const float* vbase = p.v_pool + first * D;
+    const int n_cached = owner ? n - 1 : n;            // rows of this split that are in the pool already
+    const int r_new = owner ? n - 1 : -1;
 
-    // ---- scores: a warp takes 4 consecutive positions at a time (all their loads in flight together) ----
+    // ---- scores: a warp takes 4-8 consecutive positions at a time (all their loads in flight together) ----
     {
-        constexpr int V4 = EPL / 4;                    // float4 per lane per row
-        float q[G][EPL];
+        float q[GH][EPL];
 #pragma unroll
-        for (int j = 0; j < G; ++j)
+        for (int j = 0; j < GH; ++j)
 #pragma unroll
             for (int i = 0; i < EPL; ++i) q[j][i] = vec[j][(i / 4) * 128 + lane * 4 + (i % 4)];
-        for (int r0 = warp * 4; r0 < n; r0 += NWARP * 4) {
-            float4 kf[4][V4];
+        constexpr int PB = 8 / V4;                     // positions a warp loads together (8 float4 per lane)
+        for (int r0 = warp * PB; r0 < n; r0 += NWARP * PB) {
+            float4 kf[PB][V4];
 #pragma unroll
-            for (int t = 0; t < 4; ++t)
+            for (int t = 0; t < PB; ++t)
 #pragma unroll
-                for (int h = 0; h < V4; ++h)
-                    kf[t][h] = (r0 + t < n) ? *reinterpret_cast<const float4*>(kbase + (r0 + t) * row_stride + h * 128 + lane * 4)
-                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int h = 0; h < V4; ++h) {
+                    const int r = r0 + t;
+                    if (r < n_cached) kf[t][h] = *reinterpret_cast<const float4*>(kbase + r * row_stride + h * 128 + lane * 4);
+                    else if (r == r_new) kf[t][h] = *reinterpret_cast<const float4*>(&vec[GH][h * 128 + lane * 4]);
+                    else kf[t][h] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            float s[PB][GH];
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
+            for (int t = 0; t < PB; ++t)
 #pragma unroll
-                for (int j = 0; j < G; ++j) {
-                    float s = 0.f;
+                for (int j = 0; j < GH; ++j) {
+                    float a = 0.f;
 #pragma unroll
                     for (int h = 0; h < V4; ++h) {
-                        s = fmaf(q[j][h * 4 + 0], kf[t][h].x, s);
-                        s = fmaf(q[j][h * 4 + 1], kf[t][h].y, s);
-                        s = fmaf(q[j][h * 4 + 2], kf[t][h].z, s);
-                        s = fmaf(q[j][h * 4 + 3], kf[t][h].w, s);
+                        a = fmaf(q[j][h * 4 + 0], kf[t][h].x, a);
+                        a = fmaf(q[j][h * 4 + 1], kf[t][h].y, a);
+                        a = fmaf(q[j][h * 4 + 2], kf[t][h].z, a);
+                        a = fmaf(q[j][h * 4 + 3], kf[t][h].w, a);
                     }
-                    s = warp_sum(s);
-                    if (lane == 0 && r0 + t < n) sc[j][r0 + t] = s;
+                    s[t][j] = a;
                 }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)           // the PB x GH reductions interleaved
+#pragma unroll
+                for (int t = 0; t < PB; ++t)
+#pragma unroll
+                    for (int j = 0; j < GH; ++j) s[t][j] += __shfl_xor_sync(0xffffffffu, s[t][j], o);
+            if (lane == 0) {
+#pragma unroll
+                for (int t = 0; t < PB; ++t)
+#pragma unroll
+                    for (int j = 0; j < GH; ++j)
+                        if (r0 + t < n) sc[j][r0 + t] = s[t][j];
             }
         }
     }
     __syncthreads();
+    trace_mark(p.trace, 1);
 
-    for (int j = warp; j < G; j += NWARP) {            // softmax statistics of this split
+    // the value rows do not depend on the scores: all of the split's loads go out before the softmax
+    const int d = tid % D, j0 = (tid / D) * HG;
+    float va[32], vb[32];
+#pragma unroll
+    for (int t = 0; t < 32; ++t) {
+        va[t] = t < n_cached ? vbase[t * row_stride + d] : (t == r_new ? vec[GH + 1][d] : 0.f);
+        vb[t] = 32 + t < n_cached ? vbase[(32 + t) * row_stride + d] : (32 + t == r_new ? vec[GH + 1][d] : 0.f);
+    }
+    float gate[HG];                                    // needed last, requested first
+#pragma unroll
+    for (int t = 0; t < HG; ++t) gate[t] = p.proj[size_t(head0 + j0 + t) * 2 * D + D + d];
+
+    for (int j = warp; j < GH; j += NWARP) {           // softmax statistics of this split
         float m = -INFINITY;
         for (int i = lane; i < n; i += 32) m = fmaxf(m, sc[j][i]);
         m = warp_max(m);
@@ -161,57 +223,57 @@ __global__ void __launch_bounds__(kGatedThreads) attn_gated_kernel(const GatedAt
     }
     __syncthreads();
 
-    // ---- probability-weighted V: a thread owns dimension d of HG heads; each V element is loaded once ----
-    const int d = tid % D, j0 = (tid / D) * HG;
+    // ---- probability-weighted V: a thread owns dimension d of HG heads ----
     float o[HG];
 #pragma unroll
     for (int t = 0; t < HG; ++t) o[t] = 0.f;
-    for (int r0 = 0; r0 < n; r0 += 8) {                // 8 independent loads in flight per thread
-        float v[8];
 #pragma unroll
-        for (int t = 0; t < 8; ++t) v[t] = (r0 + t < n) ? vbase[(r0 + t) * row_stride + d] : 0.f;
+    for (int t = 0; t < 32; ++t) {
+        if (t < n) {
 #pragma unroll
-        for (int t = 0; t < 8; ++t)
-            if (r0 + t < n) {
+            for (int h = 0; h < HG; ++h) o[h] = fmaf(sc[j0 + h][t], va[t], o[h]);
+        }
+        if (32 + t < n) {
 #pragma unroll
-                for (int h = 0; h < HG; ++h) o[h] = fmaf(sc[j0 + h][r0 + t], v[t], o[h]);
-            }
+            for (int h = 0; h < HG; ++h) o[h] = fmaf(sc[j0 + h][32 + t], vb[t], o[h]);
+        }
     }
     const int nsplit = p.nsplit;
     if (n_active == 1) {
 #pragma unroll
         for (int t = 0; t < HG; ++t) {
-            const int head = g * G + j0 + t;
-            const float gate = p.proj[size_t(head) * 2 * D + D + d];
-            p.out[size_t(head) * D + d] = (o[t] / stat_l[j0 + t]) * (1.f / (1.f + expf(-gate)));
+            const int head = head0 + j0 + t;
+            p.out[size_t(head) * D + d] = (o[t] / stat_l[j0 + t]) * (1.f / (1.f + expf(-gate[t])));
         }
         return;
     }
 #pragma unroll
-    for (int t = 0; t < HG; ++t) p.part_o[(size_t(g * G + j0 + t) * nsplit + split) * D + d] = o[t];
-    if (tid < G) {
-        p.part_ml[(size_t(g * G + tid) * nsplit + split) * 2] = stat_m[tid];
-        p.part_ml[(size_t(g * G + tid) * nsplit + split) * 2 + 1] = stat_l[tid];
+    for (int t = 0; t < HG; ++t) p.part_o[(size_t(head0 + j0 + t) * nsplit + split) * D + d] = o[t];
+    if (tid < GH) {
+        p.part_ml[(size_t(head0 + tid) * nsplit + split) * 2] = stat_m[tid];
+        p.part_ml[(size_t(head0 + tid) * nsplit + split) * 2 + 1] = stat_l[tid];
     }
+    trace_mark(p.trace, 2);
     __threadfence();
     __syncthreads();
     if (tid == 0) {
-        const unsigned ticket = atomicAdd(&p.counters[g], 1u);
+        const unsigned ticket = atomicAdd(&p.counters[blockIdx.x], 1u);
         s_last = (ticket == unsigned(n_active - 1));
     }
     __syncthreads();
+    trace_mark(p.trace, 3);
     if (!s_last) return;
     __threadfence();
 
-    // ---- merge by the last CTA of this KV head ----
+    // ---- merge by the last CTA of this head group ----
     float num[HG], den[HG], run_m[HG];
 #pragma unroll
     for (int t = 0; t < HG; ++t) { num[t] = 0.f; den[t] = 0.f; run_m[t] = -INFINITY; }
     for (int s0 = 0; s0 < n_active; s0 += 64) {
         const int ns = min(64, n_active - s0);
         __syncthreads();
-        for (int j = warp; j < G; j += NWARP) {
-            const float* ml = p.part_ml + (size_t(g * G + j) * nsplit + s0) * 2;
+        for (int j = warp; j < GH; j += NWARP) {
+            const float* ml = p.part_ml + (size_t(head0 + j) * nsplit + s0) * 2;
             const float m0 = lane < ns ? __ldcg(ml + 2 * lane) : -INFINITY;
             const float m1 = lane + 32 < ns ? __ldcg(ml + 2 * (lane + 32)) : -INFINITY;
             const float M = warp_max(fmaxf(m0, m1));
@@ -222,11 +284,22 @@ __global__ void __launch_bounds__(kGatedThreads) attn_gated_kernel(const GatedAt
         __syncthreads();
 #pragma unroll
         for (int t = 0; t < HG; ++t) {
-            const int j = j0 + t, head = g * G + j;
+            const int j = j0 + t, head = head0 + j;
             const float* po = p.part_o + (size_t(head) * nsplit + s0) * D + d;
             const float* ml = p.part_ml + (size_t(head) * nsplit + s0) * 2;
             float a = 0.f, b = 0.f;
-            for (int s = 0; s < ns; ++s) {
+            int s = 0;
+            for (; s + 4 <= ns; s += 4) {              // independent loads, four in flight
+                const float v0 = __ldcg(po + size_t(s) * D), v1 = __ldcg(po + size_t(s + 1) * D);
+                const float v2 = __ldcg(po + size_t(s + 2) * D), v3 = __ldcg(po + size_t(s + 3) * D);
+                const float l0 = __ldcg(ml + 2 * s + 1), l1 = __ldcg(ml + 2 * s + 3);
+                const float l2 = __ldcg(ml + 2 * s + 5), l3 = __ldcg(ml + 2 * s + 7);
+                a = fmaf(mrg_w[j][s], v0, a); a = fmaf(mrg_w[j][s + 1], v1, a);
+                a = fmaf(mrg_w[j][s + 2], v2, a); a = fmaf(mrg_w[j][s + 3], v3, a);
+                b = fmaf(mrg_w[j][s], l0, b); b = fmaf(mrg_w[j][s + 1], l1, b);
+                b = fmaf(mrg_w[j][s + 2], l2, b); b = fmaf(mrg_w[j][s + 3], l3, b);
+            }
+            for (; s < ns; ++s) {
                 a = fmaf(mrg_w[j][s], __ldcg(po + size_t(s) * D), a);
                 b = fmaf(mrg_w[j][s], __ldcg(ml + 2 * s + 1), b);
             }
@@ -241,11 +314,18 @@ __global__ void __launch_bounds__(kGatedThreads) attn_gated_kernel(const GatedAt
     }
 #pragma unroll
     for (int t = 0; t < HG; ++t) {
-        const int head = g * G + j0 + t;
-        const float gate = p.proj[size_t(head) * 2 * D + D + d];
-        p.out[size_t(head) * D + d] = (num[t] / den[t]) * (1.f / (1.f + expf(-gate)));
+        const int head = head0 + j0 + t;
+        p.out[size_t(head) * D + d] = (num[t] / den[t]) * (1.f / (1.f + expf(-gate[t])));
     }
-    if (tid == 0) p.counters[g] = 0;
+    if (tid == 0) p.counters[blockIdx.x] = 0;
+    trace_end(p.trace);
+}
+
+// CTAs along x for a shape: one per (KV head, group of GH query heads)
+int attn_gated_groups(int hq, int hkv, int d) {
+    const int G = hq / hkv;
+    const int gh = (d == 256) ? 2 : (G >= 2 ? 2 : 1);
+    return hkv * (G / gh);
 }
 
 // rotate-half RoPE on the leading `rd` elements of each head, the tail copied (partial_rope / partial_rope_kv)
@@ -273,10 +353,10 @@ cudaError_t partial_rope_f32_launch(const float* x, const float* cos_table, cons
 cudaError_t attn_gated_dispatch(const GatedAttnParams& p, cudaStream_t stream, bool pdl) {
     const int G = p.hq / p.hkv;
     if (p.rotary_dim % 64 != 0 || p.rotary_dim > p.d) return cudaErrorInvalidValue;
-    const dim3 grid(p.hkv, p.nsplit), block(kGatedThreads);
-#define TFB_ATTN(DD, GG) \
-    if (p.d == DD && G == GG) return launch_kernel(attn_gated_kernel<DD, GG>, grid, block, 0, stream, pdl, p);
-    TFB_ATTN(256, 8) TFB_ATTN(128, 2) TFB_ATTN(128, 4) TFB_ATTN(256, 4)
+    const dim3 grid(attn_gated_groups(p.hq, p.hkv, p.d), p.nsplit), block(kGatedThreads);
+#define TFB_ATTN(DD, GG, HH) \
+    if (p.d == DD && G == GG) return launch_kernel(attn_gated_kernel<DD, GG, HH>, grid, block, 0, stream, pdl, p);
+    TFB_ATTN(256, 8, 2) TFB_ATTN(256, 4, 2) TFB_ATTN(128, 2, 2) TFB_ATTN(128, 4, 2)
 #undef TFB_ATTN
     return cudaErrorInvalidValue;
 }

@@ -252,8 +252,10 @@ struct GatedAttnParams {
     unsigned* counters;
     int hq, hkv, d, rotary_dim, page_size, max_ctx, nsplit;
     float eps, scale;
+    unsigned long long* trace;
 };
 int attn_gated_splits(int max_ctx);
+int attn_gated_groups(int hq, int hkv, int d);      // merge tickets the kernel needs
 cudaError_t attn_gated_dispatch(const GatedAttnParams& p, cudaStream_t stream, bool pdl);
 
 struct MoeDownF32Params {

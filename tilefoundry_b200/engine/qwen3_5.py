@@ -93,7 +93,7 @@ class Qwen35Session(DecodeSession):
         self.inner = z(K * I + IS)
         self.logits = z(V, dtype=bf) if keep_logits else None
         self.part_o, self.part_ml = z(HQ * nsplit * D), z(HQ * nsplit * 2)
-        self.counters = z(HKV + 2, dtype=torch.int32)            # attention tickets, head ticket, router ticket
+        self.counters = z(lib.load().tfb_attn_gated_groups(HQ, HKV, D) + 1, dtype=torch.int32)   # attention tickets, head ticket
         n_head = lib.lm_head_scratch_entries(V)
         self.head_val, self.head_idx = z(n_head), z(n_head, dtype=torch.int32)
         self.trace = z(L + 1, H) if trace_hidden else None

@@ -228,6 +228,7 @@ SYMBOLS = {
     "tfb_l2norm_f32": (_i32, [_vp, _vp, _i32, _i32, _f32, _i32, _vp]),
     "tfb_partial_rope_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "tfb_attn_gated_splits": (_i32, [_i32]),
+    "tfb_attn_gated_groups": (_i32, [_i32, _i32, _i32]),
     "tfb_attn_gated_decode": (_i32, [C.POINTER(AttnGatedArgs), _vp]),
     "tfb_moe_down_f32": (_i32, [C.POINTER(MoeDownF32Args), _vp]),
     "tfb_embed_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _i64, _i32, _vp]),

@@ -127,7 +127,7 @@ def make_twin(cfg: authored.Qwen35Config = authored.QWEN3_5_35B_A3B):
             nsplit = L().tfb_attn_gated_splits(CAP)
             out, k_new, v_new = _new(HQ * D, hidden), _new((1, 1, HKV, D), hidden), _new((1, 1, HKV, D), hidden)
             part_o, part_ml = _new(HQ * nsplit * D, hidden), _new(HQ * nsplit * 2, hidden)
-            counters = torch.zeros(HKV, device=dev, dtype=torch.int32)
+            counters = torch.zeros(L().tfb_attn_gated_groups(HQ, HKV, D), device=dev, dtype=torch.int32)
             at = torch.tensor([ctx], device=dev, dtype=torch.int32)       # the cache holds ctx rows: append at ctx
             a = lib.AttnGatedArgs(proj=lib.ptr(proj), gamma_q=lib.ptr(gamma_q), gamma_k=lib.ptr(gamma_k),
                                   cos_table=lib.ptr(cos_cache), sin_table=lib.ptr(sin_cache), pos=lib.ptr(at),
