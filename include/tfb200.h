@@ -128,6 +128,10 @@ typedef struct {
     int32_t expert_world;  /* e % expert_world == expert_rank, as local expert e / expert_world; other slots give 0 */
 } tfb_gemv_args;
 TFB_API int tfb_gemv(const tfb_gemv_args* args, tfb_stream_t stream);
+/* Two independent TFB_EPI_STORE projections (same prologue kind, k <= 2048 each) in one launch: MiniCPM3's q and kv
+ * up-projections, which the reference also runs as one "pair" kernel (examples/minicpm3_4b-cutedsl/kernels/
+ * reference_ops.py rmsnorm_gemv_pair).  Same results as two tfb_gemv calls. */
+TFB_API int tfb_gemv_pair(const tfb_gemv_args* a, const tfb_gemv_args* b, tfb_stream_t stream);
 
 /* ---- lm_head + greedy pick -------------------------------------------------
  * logits[i] = bf16( W[i,:] . prologue(x) * out_scale ), token = argmax over the bf16

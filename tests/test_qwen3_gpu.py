@@ -69,6 +69,30 @@ def test_gemv_persistent_variants_match_default_kernel(dev, kernel, n, k):
         assert_ulps(got, want, 1, f"kernel {kernel} {n}x{k} {sorted(kw)}")
 
 
+def test_gemv_pair_equals_two_launches(dev):
+    """Two independent projections in one launch (different K, different inputs and gains) give bit for bit what
+    two launches give."""
+    import ctypes as C
+    from tilefoundry_b200 import lib
+    g = torch.Generator().manual_seed(77)
+    rnd = lambda *s, scale=1.0: (torch.randn(*s, generator=g) * scale).to(BF).to(dev)
+    x = rnd(768 + 256 + 32)
+    wa, wb = rnd(3840, 768, scale=768 ** -0.5), rnd(5120, 256, scale=256 ** -0.5)
+    ga, gb = (1 + 0.1 * torch.randn(768, generator=g)).to(BF).to(dev), (1 + 0.1 * torch.randn(256, generator=g)).to(BF).to(dev)
+    xa, xb = x[:768], x[768:1024]
+    ya, yb = torch.empty(3840, device=dev, dtype=BF), torch.empty(5120, device=dev, dtype=BF)
+    mk = lambda w, xx, gg, y: lib.GemvArgs(w=lib.ptr(w), x=lib.ptr(xx), gamma=lib.ptr(gg), y=lib.ptr(y), n=w.shape[0], k=w.shape[1],
+                                           prologue=lib.NORM_CAST_THEN_GAIN, epilogue=lib.EPI_STORE, eps=1e-5, x_scale=1.0,
+                                           res_scale=1.0, out_scale=1.0)
+    a, b = mk(wa, xa, ga, ya), mk(wb, xb, gb, yb)
+    lib.check(lib.load().tfb_gemv_pair(C.byref(a), C.byref(b), lib.stream()), "tfb_gemv_pair")
+    want_a = lib.gemv(wa, xa, torch.empty_like(ya), gamma=ga, prologue=lib.NORM_CAST_THEN_GAIN, eps=1e-5)
+    want_b = lib.gemv(wb, xb, torch.empty_like(yb), gamma=gb, prologue=lib.NORM_CAST_THEN_GAIN, eps=1e-5)
+    assert torch.equal(ya, want_a) and torch.equal(yb, want_b)
+    b.epilogue = lib.EPI_RESIDUAL
+    assert lib.load().tfb_gemv_pair(C.byref(a), C.byref(b), lib.stream()) == 1      # only plain stores pair up
+
+
 @pytest.mark.parametrize("h,inter,qkv", [(2048, 6144, 4096), (256, 512, 512), (2560, 6400, 0)])
 def test_gemv_chain_matches_separate_launches(dev, h, inter, qkv):
     """o-projection + residual -> norm + gate/up + SwiGLU -> down + residual (-> next q|k|v) as one persistent

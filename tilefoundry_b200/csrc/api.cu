@@ -76,7 +76,8 @@ int tfb_rmsnorm(const void* x, const void* gamma, void* y, int32_t rows, int32_t
 }
 
 }  // extern "C"
-int tfb::host::gemv_checked(const tfb_gemv_args* a, tfb_stream_t stream) {
+// argument checks of one projection and its kernel parameters
+static int gemv_params(const tfb_gemv_args* a, tfb::GemvParams& p) {
     TFB_REQUIRE(a && a->w && a->x && a->y, TFB_EINVAL);
     TFB_REQUIRE(a->n > 0 && a->k > 0 && a->k % 256 == 0 && a->k <= 16384, TFB_EINVAL);
     TFB_REQUIRE(a->prologue >= TFB_NORM_NONE && a->prologue <= TFB_NORM_GATED, TFB_EINVAL);
@@ -91,7 +92,7 @@ int tfb::host::gemv_checked(const tfb_gemv_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(aligned16(a->w) && aligned16(a->x) && (!a->w2 || aligned16(a->w2)) &&
                     (!a->gamma || aligned16(a->gamma)), TFB_EALIGN);
     TFB_REQUIRE(!a->prefetch || (aligned16(a->prefetch) && a->prefetch_bytes % 16 == 0), TFB_EALIGN);
-    tfb::GemvParams p = {};
+    p = {};
     p.w = static_cast<const uint4*>(a->w);
     p.w2 = static_cast<const uint4*>(a->w2);
     p.x = static_cast<const uint16_t*>(a->x);
@@ -113,6 +114,12 @@ int tfb::host::gemv_checked(const tfb_gemv_args* a, tfb_stream_t stream) {
     p.rows_per_expert = a->rows_per_expert;
     p.expert_rank = a->expert_rank;
     p.expert_world = a->expert_world;
+    return TFB_OK;
+}
+
+int tfb::host::gemv_checked(const tfb_gemv_args* a, tfb_stream_t stream) {
+    tfb::GemvParams p;
+    if (const int rc = gemv_params(a, p)) return rc;
     if (a->kernel == TFB_KERNEL_RING && tfb::gemv_stream_supported(a->n, a->k))
         return done(tfb::gemv_stream_dispatch(p, a->prologue, a->epilogue, S(stream), a->pdl != 0));
     if (a->kernel == TFB_KERNEL_ASYNC && tfb::gemv_async_supported(p, a->prologue, a->epilogue))
@@ -131,6 +138,15 @@ int tfb::host::gemv_checked(const tfb_gemv_args* a, tfb_stream_t stream) {
 
 extern "C" {
 int tfb_gemv(const tfb_gemv_args* args, tfb_stream_t stream) { return gemv_checked(args, stream); }
+
+int tfb_gemv_pair(const tfb_gemv_args* a, const tfb_gemv_args* b, tfb_stream_t stream) {
+    tfb::GemvParams pa, pb;
+    if (const int rc = gemv_params(a, pa)) return rc;
+    if (const int rc = gemv_params(b, pb)) return rc;
+    TFB_REQUIRE(a->prologue == b->prologue && a->epilogue == TFB_EPI_STORE && b->epilogue == TFB_EPI_STORE, TFB_EINVAL);
+    TFB_REQUIRE(a->prologue != TFB_NORM_GATED && a->k <= 2048 && b->k <= 2048 && !a->expert_idx && !b->expert_idx, TFB_EINVAL);
+    return done(tfb::gemv_pair_dispatch(pa, pb, a->prologue, a->epilogue, S(stream), a->pdl != 0));
+}
 
 int tfb_gemv_chain(const tfb_gemv_chain_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->n_phases >= 1 && a->n_phases <= 4 && a->sync, TFB_EINVAL);

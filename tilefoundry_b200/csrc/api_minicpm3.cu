@@ -80,12 +80,19 @@ int tfb_minicpm3_decode_step(const tfb_minicpm3_step_args* a, tfb_stream_t strea
         // 1. input norm + q down-projection | kv compression (one fused projection)
         if ((rc = gemv(L.w_qkv_a, nullptr, hid, L.gamma_in, nullptr, qkv_a, NA, H, TFB_NORM_CAST_THEN_GAIN,
                        TFB_EPI_STORE, a->eps, 1.f))) return rc;
-        // 2. low-rank norm + q up-projection
-        if ((rc = gemv(L.w_q_b, nullptr, qkv_a, L.gamma_q_a, nullptr, a->q_up_buf, NQ, a->q_lora,
-                       TFB_NORM_CAST_THEN_GAIN, TFB_EPI_STORE, a->lora_eps, 1.f))) return rc;
-        // 3. low-rank norm + kv up-projection (k_nope | v per head)
-        if ((rc = gemv(L.w_kv_b, nullptr, qkv_a + a->q_lora, L.gamma_kv_a, nullptr, a->kv_up_buf, NKV, a->kv_lora,
-                       TFB_NORM_CAST_THEN_GAIN, TFB_EPI_STORE, a->lora_eps, 1.f))) return rc;
+        // 2 + 3. low-rank norms + q up-projection and kv up-projection (k_nope | v per head): independent of each
+        // other, one launch
+        {
+            tfb_gemv_args gq, gkv;
+            std::memset(&gq, 0, sizeof gq);
+            gq.w = L.w_q_b; gq.x = qkv_a; gq.gamma = L.gamma_q_a; gq.y = a->q_up_buf; gq.n = NQ; gq.k = a->q_lora;
+            gq.prologue = TFB_NORM_CAST_THEN_GAIN; gq.epilogue = TFB_EPI_STORE; gq.eps = a->lora_eps;
+            gq.x_scale = 1.f; gq.res_scale = 1.f; gq.out_scale = 1.f; gq.pdl = pdl;
+            gkv = gq;
+            gkv.w = L.w_kv_b; gkv.x = qkv_a + a->q_lora; gkv.gamma = L.gamma_kv_a; gkv.y = a->kv_up_buf; gkv.n = NKV;
+            gkv.k = a->kv_lora;
+            if ((rc = tfb_gemv_pair(&gq, &gkv, stream))) return rc;
+        }
         // 4. RoPE, assembly, cache append, attention
         tfb_attn_mla_args t;
         std::memset(&t, 0, sizeof t);

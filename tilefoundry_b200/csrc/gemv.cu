@@ -16,7 +16,7 @@ namespace tfb {
 // WARPS warps per CTA; KSPLIT of them share one group of ROWS rows, each taking a
 // contiguous slice of K.  EPI: 0 store bf16, 1 residual, 2 SwiGLU, 3 store f32.
 template <int ROWS, int KSPLIT, int WARPS, int UNROLL, int NORM_MODE, int EPI>
-__global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
+__device__ __forceinline__ void gemv_body(const GemvParams& p, const int bid, const int nblocks) {
     extern __shared__ __align__(16) float smem[];
     float* xs = smem;                         // k floats
     float* red = smem + p.k;                  // 32 floats
@@ -26,7 +26,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
     constexpr int NMAT = (EPI == 2) ? 2 : 1;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int group = warp / KSPLIT, ks = warp % KSPLIT;
-    const int row0 = (blockIdx.x * GROUPS + group) * ROWS;
+    const int row0 = (bid * GROUPS + group) * ROWS;
     const int rows_valid = min(ROWS, p.n - row0);
     const int row_stride = p.k >> 3;                       // uint4 per row
     const int its = p.k >> 8;                              // 256 elements per warp iteration
@@ -45,7 +45,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
         a.load(wrow, row_stride, rows_valid, it_begin, it_end, lane);
         if (EPI == 2) b.load(w2row, row_stride, rows_valid, it_begin, it_end, lane);
     }
-    if (threadIdx.x == 0) l2_prefetch_slice(p.prefetch, p.prefetch_bytes, blockIdx.x, gridDim.x);
+    if (threadIdx.x == 0) l2_prefetch_slice(p.prefetch, p.prefetch_bytes, bid, nblocks);
     constexpr int MAXC = 4;
     const bool fast_stage = (p.k >> 3) <= MAXC * WARPS * 32;
     uint4* gs = reinterpret_cast<uint4*>(part + WARPS * ROWS * 2);     // parked norm gains
@@ -141,6 +141,42 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
         }
     }
     trace_end(p.trace);
+}
+
+template <int ROWS, int KSPLIT, int WARPS, int UNROLL, int NORM_MODE, int EPI>
+__global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
+    gemv_body<ROWS, KSPLIT, WARPS, UNROLL, NORM_MODE, EPI>(p, blockIdx.x, gridDim.x);
+}
+
+// Two independent projections in ONE launch: the first ctas_a CTAs work on `a`, the rest on `b` (MiniCPM3's q and kv
+// up-projections both read the low-rank vector the launch before them wrote; examples/minicpm3_4b-cutedsl runs them
+// as one "pair" kernel too, kernels/cute_gemv.py).  Same arithmetic as two launches, one launch latency.
+template <int ROWS, int KSPLIT, int WARPS, int UNROLL, int NORM_MODE, int EPI>
+__global__ void __launch_bounds__(WARPS * 32) gemv_pair_kernel(const GemvParams a, const GemvParams b, const int ctas_a) {
+    if (int(blockIdx.x) < ctas_a) gemv_body<ROWS, KSPLIT, WARPS, UNROLL, NORM_MODE, EPI>(a, blockIdx.x, ctas_a);
+    else gemv_body<ROWS, KSPLIT, WARPS, UNROLL, NORM_MODE, EPI>(b, blockIdx.x - ctas_a, gridDim.x - ctas_a);
+}
+
+template <int NORM_MODE, int EPI>
+static cudaError_t launch_pair(const GemvParams& a, const GemvParams& b, cudaStream_t stream, bool pdl) {
+    constexpr int ROWS = 1, KSPLIT = 1, WARPS = 8, UNROLL = 8;          // the k <= 2048 shape of pick_shape
+    const unsigned ca = (a.n + WARPS - 1) / WARPS, cb = (b.n + WARPS - 1) / WARPS;
+    const int kmax = a.k > b.k ? a.k : b.k;
+    const size_t smem = (size_t(kmax) + 32 + WARPS * ROWS * 2) * sizeof(float) + (NORM_MODE ? size_t(kmax) * 2 : 0);
+    auto kern = gemv_pair_kernel<ROWS, KSPLIT, WARPS, UNROLL, NORM_MODE, EPI>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return e;
+    }
+    return launch_kernel(kern, dim3(ca + cb), dim3(WARPS * 32), smem, stream, pdl, a, b, int(ca));
+}
+
+cudaError_t gemv_pair_dispatch(const GemvParams& a, const GemvParams& b, int norm_mode, int epi, cudaStream_t stream, bool pdl) {
+    if (a.k > 2048 || b.k > 2048 || a.expert_idx || b.expert_idx) return cudaErrorInvalidValue;
+    if (norm_mode == 0 && epi == 0) return launch_pair<0, 0>(a, b, stream, pdl);
+    if (norm_mode == 1 && epi == 0) return launch_pair<1, 0>(a, b, stream, pdl);
+    if (norm_mode == 2 && epi == 0) return launch_pair<2, 0>(a, b, stream, pdl);
+    return cudaErrorInvalidValue;
 }
 
 template <int ROWS, int KSPLIT, int WARPS, int UNROLL, int NORM_MODE, int EPI>

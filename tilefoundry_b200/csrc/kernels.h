@@ -37,6 +37,7 @@ bool gemv_stream_supported(int n, int k);
 cudaError_t gemv_stream_dispatch(const GemvParams& p, int norm_mode, int epi, cudaStream_t stream, bool pdl);
 int lm_head_stream_ctas();
 cudaError_t gemv_dispatch(const GemvParams& p, int norm_mode, int epi, cudaStream_t stream, bool pdl);
+cudaError_t gemv_pair_dispatch(const GemvParams& a, const GemvParams& b, int norm_mode, int epi, cudaStream_t stream, bool pdl);
 bool gemv_async_supported(const GemvParams& p, int norm_mode, int epi);
 cudaError_t gemv_async_dispatch(const GemvParams& p, int norm_mode, int epi, cudaStream_t stream, bool pdl);
 bool gemv_persist_supported(const GemvParams& p, int norm_mode);

@@ -66,54 +66,24 @@ __global__ void __launch_bounds__(kDownWarps * 32) moe_down_kernel(const MoeDown
     __syncthreads();
     if (j >= p.hidden) return;
 
-    // The selected experts' rows are requested five slots at a time before any is used: two or three memory round
-    // trips for the routed part instead of one per slot.
     float routed = 0.f;
     const int pieces = I >> 3;
-    for (int s0 = 0; s0 < K; s0 += 5) {
-        uint4 wb[5][3];
-        bool live[5];
-        const uint4* rows[5];
-#pragma unroll
-        for (int s = 0; s < 5; ++s) {
-            live[s] = s0 + s < K;
-            long long e = live[s] ? s_idx[s0 + s] : 0;
-            if (live[s] && p.expert_world > 1) {               // expert parallel: only this rank's experts are here
-                if (e % p.expert_world != p.expert_rank) live[s] = false;
-                e /= p.expert_world;
-            }
-            rows[s] = p.w_down + (size_t(live[s] ? e : 0) * p.hidden + j) * pieces;
-#pragma unroll
-            for (int u = 0; u < 3; ++u)
-                wb[s][u] = (live[s] && lane + 32 * u < pieces) ? ld_stream16(rows[s] + lane + 32 * u) : make_uint4(0, 0, 0, 0);
+    for (int s = 0; s < K; ++s) {
+        long long e = s_idx[s];
+        if (p.expert_world > 1) {                              // expert parallel: only this rank's experts are here
+            if (e % p.expert_world != p.expert_rank) continue;
+            e /= p.expert_world;
         }
-        float acc[5];
-#pragma unroll
-        for (int s = 0; s < 5; ++s) {
-            acc[s] = 0.f;
-            if (!live[s]) continue;
-            const float* x = xin + (s0 + s) * I;
-#pragma unroll
-            for (int u = 0; u < 3; ++u) {
-                const int c = lane + 32 * u;
-                if (c < pieces) {
-                    const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
-                    acc[s] = dot8(wb[s][u], xa, xb, acc[s]);
-                }
-            }
-            for (int c = lane + 96; c < pieces; c += 32) {       // rows wider than 768 elements
-                const uint4 w = ld_stream16(rows[s] + c);
-                const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
-                acc[s] = dot8(w, xa, xb, acc[s]);
-            }
+        const uint4* row = p.w_down + (size_t(e) * p.hidden + j) * pieces;
+        const float* x = xin + s * I;
+        float acc = 0.f;
+        for (int c = lane; c < pieces; c += 32) {
+            const uint4 w = ld_stream16(row + c);
+            const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
+            acc = dot8(w, xa, xb, acc);
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-            for (int s = 0; s < 5; ++s) acc[s] += __shfl_xor_sync(0xffffffffu, acc[s], o);
-#pragma unroll
-        for (int s = 0; s < 5; ++s)
-            if (live[s]) routed += round_bf16(round_bf16(acc[s]) * s_w[s0 + s]);   // bf16 products, f32 running sum
+        acc = warp_sum(acc);
+        routed += round_bf16(round_bf16(acc) * s_w[s]);        // bf16 products, f32 running sum
     }
     float out = round_bf16(routed);                            // the reduce over slots returns bf16
     float sh_raw = 0.f;

@@ -89,7 +89,7 @@ class MiniCPM3Session(DecodeSession):
             part_ml=lib.ptr(self.part_ml), counters=lib.ptr(self.counters), head_val=lib.ptr(self.head_val),
             head_idx=lib.ptr(self.head_idx), hidden_trace=lib.ptr(self.trace), picked=lib.ptr(self.picked),
             pdl=int(pdl))
-        self.launches_per_step = 2 + 7 * len(self.layers) + (len(self.layers) + 1 if trace_hidden else 0)
+        self.launches_per_step = 2 + 6 * len(self.layers) + (len(self.layers) + 1 if trace_hidden else 0)
 
     def weight_bytes(self) -> int:
         names = ("w_qkv_a", "w_q_b", "w_kv_b", "w_o", "w_gate", "w_up", "w_down")

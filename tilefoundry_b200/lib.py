@@ -203,6 +203,7 @@ SYMBOLS = {
     "tfb_embed": (_i32, [_vp, _vp, _vp, _i32, _i32, _i64, _f32, _vp]),
     "tfb_rmsnorm": (_i32, [_vp, _vp, _vp, _i32, _i32, _f32, _i32, _vp]),
     "tfb_gemv": (_i32, [C.POINTER(GemvArgs), _vp]),
+    "tfb_gemv_pair": (_i32, [C.POINTER(GemvArgs), C.POINTER(GemvArgs), _vp]),
     "tfb_gemv_chain": (_i32, [C.POINTER(GemvChainArgs), _vp]),
     "tfb_gemm_small_m_splits": (_i32, [_i32, _i32]),
     "tfb_gemm_small_m": (_i32, [C.POINTER(GemmSmallMArgs), _vp]),
