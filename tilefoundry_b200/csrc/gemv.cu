@@ -157,10 +157,10 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_pair_kernel(const GemvParams 
     else gemv_body<ROWS, KSPLIT, WARPS, UNROLL, NORM_MODE, EPI>(b, blockIdx.x - ctas_a, gridDim.x - ctas_a);
 }
 
-template <int NORM_MODE, int EPI>
-static cudaError_t launch_pair(const GemvParams& a, const GemvParams& b, cudaStream_t stream, bool pdl) {
-    constexpr int ROWS = 1, KSPLIT = 1, WARPS = 8, UNROLL = 8;          // the k <= 2048 shape of pick_shape
-    const unsigned ca = (a.n + WARPS - 1) / WARPS, cb = (b.n + WARPS - 1) / WARPS;
+template <int ROWS, int UNROLL, int NORM_MODE, int EPI>
+static cudaError_t launch_pair_cfg(const GemvParams& a, const GemvParams& b, cudaStream_t stream, bool pdl) {
+    constexpr int KSPLIT = 1, WARPS = 8;
+    const unsigned ca = (a.n + WARPS * ROWS - 1) / (WARPS * ROWS), cb = (b.n + WARPS * ROWS - 1) / (WARPS * ROWS);
     const int kmax = a.k > b.k ? a.k : b.k;
     const size_t smem = (size_t(kmax) + 32 + WARPS * ROWS * 2) * sizeof(float) + (NORM_MODE ? size_t(kmax) * 2 : 0);
     auto kern = gemv_pair_kernel<ROWS, KSPLIT, WARPS, UNROLL, NORM_MODE, EPI>;
@@ -169,6 +169,14 @@ static cudaError_t launch_pair(const GemvParams& a, const GemvParams& b, cudaStr
         if (e != cudaSuccess) return e;
     }
     return launch_kernel(kern, dim3(ca + cb), dim3(WARPS * 32), smem, stream, pdl, a, b, int(ca));
+}
+
+template <int NORM_MODE, int EPI>
+static cudaError_t launch_pair(const GemvParams& a, const GemvParams& b, cudaStream_t stream, bool pdl) {
+    // Short rows (low-rank up-projections, 0.5-1.5 KB each): four rows per warp, so a CTA streams 16-48 KB instead of
+    // 4-12 KB for the same staging and launch cost.  Otherwise the k <= 2048 shape of pick_shape.
+    if (a.k <= 1024 && b.k <= 1024) return launch_pair_cfg<4, 4, NORM_MODE, EPI>(a, b, stream, pdl);
+    return launch_pair_cfg<1, 8, NORM_MODE, EPI>(a, b, stream, pdl);
 }
 
 cudaError_t gemv_pair_dispatch(const GemvParams& a, const GemvParams& b, int norm_mode, int epi, cudaStream_t stream, bool pdl) {
