@@ -343,7 +343,7 @@ def run_ours(args):
     K, W = args.steps, max(args.warmup, 3)
     # The MoE configuration shards one sequence over the GPUs (expert / shared-expert / vocabulary parallel);
     # the dense ones do not shard: each rank decodes its own sequence ("replicas only").
-    sharded = world > 1 and work.key == "granite_4_0_h_small"
+    sharded = world > 1 and work.key in ("granite_4_0_h_small", "qwen3_5_35b_a3b")
     prompt = prompt_ids(cfg, seed=0 if sharded else rank)
     max_ctx = max(W + K + 8, PROMPT_TOKENS + 8)
     extra = {"group": dist.group.WORLD} if sharded else {}

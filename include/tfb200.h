@@ -552,7 +552,8 @@ TFB_API int tfb_gemm_small_m(const tfb_gemm_small_m_args* args, tfb_stream_t str
  * epilogue TFB_EPI_STORE, TFB_EPI_RESIDUAL (y = residual + bf16(acc)) or TFB_EPI_SWIGLU
  * (y = bf16(silu(bf16(acc_gate)) * bf16(acc_up)), w = gate rows, w2 = up rows).
  * Expert mode (rows_per_expert > 0): output rows come in slots of rows_per_expert; slot s < routed_slots reads
- * the rows of expert expert_idx[s] of w (and w2), later slots read consecutive rows of w_extra (w2_extra).
+ * the rows of expert expert_idx[s] of w (and w2), later rows (n need not end on a slot boundary) read consecutive
+ * rows of w_extra (w2_extra).
  * Replaces the projections inside linear_attention / full_attention / routing / routed_experts / shared_expert
  * (examples/qwen3_5_35b_a3b-tilelang/model.py:214-228,380-417,488-499,540-590). */
 typedef struct {
@@ -571,6 +572,9 @@ typedef struct {
      * needs no launch of its own.  route_counter: u32 zeroed once by the caller; the kernel leaves it zero. */
     uint32_t* route_counter; int32_t route_experts, route_top_k;
     int64_t* idx_out; float* w_out;
+    /* Expert mode on several GPUs: expert e lives on rank e % expert_world as local expert e / expert_world; slots
+     * whose expert is another rank's are skipped (their outputs are left untouched).  0 or 1: all experts local. */
+    int32_t expert_rank, expert_world;
 } tfb_gemv_f32_args;
 TFB_API int tfb_gemv_f32(const tfb_gemv_f32_args* args, tfb_stream_t stream);
 
@@ -636,6 +640,11 @@ typedef struct {
     const float* residual; float* out;
     int32_t hidden, inter, shared_inter, top_k;
     int32_t pdl, reserved;
+    /* Several GPUs: only this rank's experts (e % expert_world == expert_rank, stored as local expert
+     * e / expert_world) and this rank's slice of the shared expert are here; with `partial` (f32 [2][hidden]) the
+     * kernel writes its routed sum and its un-rounded shared dot there instead of `out`, for
+     * tfb_moe_allreduce_finalize to add across ranks. */
+    int32_t expert_rank, expert_world; float* partial;
 } tfb_moe_down_f32_args;
 TFB_API int tfb_moe_down_f32(const tfb_moe_down_f32_args* args, tfb_stream_t stream);
 
@@ -684,8 +693,18 @@ typedef struct {
     void* logits; int64_t* picked;
     float* hidden_trace;      /* optional f32 [(n_layers + 1)][hidden]: every layer's output, then the final norm */
     int64_t* idx_trace;       /* optional [n_layers][top_k] */
+    /* several GPUs (expert / shared-expert / vocabulary parallel as in tfb_granite_step_args): the layers hold this
+     * rank's experts, its slice of the shared expert (shared_inter is the FULL size) and w_head its vocabulary slice */
+    int32_t ep_rank, ep_world;
+    float* partial;           /* f32 [2][hidden] */
+    float* pair;              /* f32 [2] */
 } tfb_qwen35_step_args;
 TFB_API int tfb_qwen35_decode_step(const tfb_qwen35_step_args* args, tfb_stream_t stream);
+/* One piece of the step, so a sharded caller can put its exchange kernels between them: part 0 embed; part 1 layer
+ * `layer` up to the expert down stage (on several GPUs it leaves this rank's partial sums in args->partial and the
+ * attended hidden state in attended_buf for tfb_moe_allreduce_finalize); part 3 final norm + head (several GPUs: this
+ * rank's vocabulary slice, leaving (logit, index) in args->pair for tfb_pick_allgather). */
+TFB_API int tfb_qwen35_step_part(const tfb_qwen35_step_args* args, int32_t part, int32_t layer, tfb_stream_t stream);
 
 /* ---- exchange steps of the sharded MoE step as single kernels over NVLink peer memory ---------------------
  * tfb_moe_allreduce_finalize = all-reduce of the ranks' partial sums + tfb_moe_finalize in one launch;
@@ -700,6 +719,9 @@ typedef struct {
     const float* partial; float* inbox[8]; uint32_t* flags[8]; uint32_t* epoch; uint32_t* status;
     const void* residual; void* out;
     int32_t hidden, rank, world, has_shared; float res_scale; int32_t pdl;
+    /* f32-activation form (Qwen3.5), used when out_f32 is set:
+     * out_f32 = residual_f32 + sum_r routed_r + bf16(sum_r shared_r) * sigmoid(*gate_logit). */
+    const float* residual_f32; float* out_f32; const float* gate_logit;
 } tfb_moe_allreduce_args;
 TFB_API int tfb_moe_allreduce_finalize(const tfb_moe_allreduce_args* args, tfb_stream_t stream);
 typedef struct {

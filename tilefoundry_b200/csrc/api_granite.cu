@@ -88,7 +88,7 @@ int tfb_pick_finalize(const float* pairs, int32_t world, int64_t* tokens, int32_
 }
 
 int tfb_moe_allreduce_finalize(const tfb_moe_allreduce_args* a, tfb_stream_t stream) {
-    TFB_REQUIRE(a && a->partial && a->epoch && a->status && a->out && a->hidden > 0, TFB_EINVAL);
+    TFB_REQUIRE(a && a->partial && a->epoch && a->status && (a->out || a->out_f32) && a->hidden > 0, TFB_EINVAL);
     TFB_REQUIRE(a->world >= 2 && a->world <= tfb::kMaxPeers && a->rank >= 0 && a->rank < a->world, TFB_EINVAL);
     tfb::PeerReduceParams p = {};
     for (int r = 0; r < a->world; ++r) {
@@ -98,6 +98,7 @@ int tfb_moe_allreduce_finalize(const tfb_moe_allreduce_args* a, tfb_stream_t str
     p.partial = a->partial; p.epoch = a->epoch; p.status = a->status; p.residual = cu16(a->residual);
     p.out = static_cast<uint16_t*>(a->out); p.hidden = a->hidden; p.rank = a->rank; p.world = a->world;
     p.has_shared = a->has_shared; p.res_scale = a->res_scale;
+    p.residual_f32 = a->residual_f32; p.out_f32 = a->out_f32; p.gate_logit = a->gate_logit;
     return done(tfb::moe_allreduce_finalize_launch(p, S(stream), a->pdl != 0));
 }
 

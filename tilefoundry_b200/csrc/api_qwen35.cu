@@ -22,7 +22,8 @@ int tfb_gemv_f32(const tfb_gemv_f32_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(ep != TFB_EPI_RESIDUAL || a->residual, TFB_EINVAL);
     TFB_REQUIRE(ep != TFB_EPI_SWIGLU || a->w2, TFB_EINVAL);
     if (a->rows_per_expert > 0) {
-        TFB_REQUIRE(a->rows_per_expert % 8 == 0 && a->n % a->rows_per_expert == 0 && a->routed_slots >= 0, TFB_EINVAL);
+        TFB_REQUIRE(a->rows_per_expert % 8 == 0 && a->routed_slots >= 0 &&
+                        int64_t(a->routed_slots) * a->rows_per_expert <= a->n, TFB_EINVAL);   // the last extra slot may be partial
         TFB_REQUIRE(a->routed_slots == 0 || a->expert_idx, TFB_EINVAL);
         const bool extra = a->routed_slots * a->rows_per_expert < a->n;
         TFB_REQUIRE(!extra || (a->w_extra && (ep != TFB_EPI_SWIGLU || a->w2_extra)), TFB_EINVAL);
@@ -42,6 +43,8 @@ int tfb_gemv_f32(const tfb_gemv_f32_args* a, tfb_stream_t stream) {
     p.n = a->n; p.k = a->k; p.seg = a->seg; p.eps = a->eps;
     p.expert_idx = reinterpret_cast<const long long*>(a->expert_idx);
     p.rows_per_expert = a->rows_per_expert; p.routed_slots = a->routed_slots;
+    p.expert_rank = a->expert_rank; p.expert_world = a->expert_world;
+    TFB_REQUIRE(a->expert_world <= 1 || (a->expert_rank >= 0 && a->expert_rank < a->expert_world), TFB_EINVAL);
     p.route_counter = a->route_counter; p.route_experts = a->route_experts; p.route_top_k = a->route_top_k;
     p.idx_out = reinterpret_cast<long long*>(a->idx_out); p.w_out = a->w_out;
     p.trace = next_trace();
@@ -105,6 +108,8 @@ int tfb_moe_down_f32(const tfb_moe_down_f32_args* a, tfb_stream_t stream) {
     p.inner = a->inner; p.indices = reinterpret_cast<const long long*>(a->indices); p.weights = a->weights;
     p.shared_gate_logit = a->shared_gate_logit; p.residual = a->residual; p.out = a->out;
     p.hidden = a->hidden; p.inter = a->inter; p.shared_inter = is; p.top_k = a->top_k;
+    p.expert_rank = a->expert_rank; p.expert_world = a->expert_world; p.partial = a->partial;
+    TFB_REQUIRE(a->expert_world <= 1 || (a->expert_rank >= 0 && a->expert_rank < a->expert_world), TFB_EINVAL);
     return done(tfb::moe_down_f32_launch(p, S(stream), a->pdl != 0));
 }
 
@@ -148,30 +153,51 @@ int tfb_residual_add_f32(const float* a, const float* b, float* out, int32_t n, 
     return done(tfb::residual_add_f32_launch(a, b, out, n, S(stream), pdl != 0));
 }
 
+static int qwen35_part(const tfb_qwen35_step_args* a, int part, int layer, tfb_stream_t stream);
+
+int tfb_qwen35_step_part(const tfb_qwen35_step_args* a, int32_t part, int32_t layer, tfb_stream_t stream) {
+    TFB_REQUIRE(a && (part == 0 || part == 1 || part == 3), TFB_EINVAL);
+    TFB_REQUIRE(part != 1 || (layer >= 0 && layer < a->n_layers), TFB_EINVAL);
+    return qwen35_part(a, part, layer, stream);
+}
+
 int tfb_qwen35_decode_step(const tfb_qwen35_step_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->ep_world <= 1, TFB_EINVAL);          // sharded steps interleave exchange kernels: use the parts
+    int rc = qwen35_part(a, 0, 0, stream);
+    for (int l = 0; !rc && l < a->n_layers; ++l) rc = qwen35_part(a, 1, l, stream);
+    return rc ? rc : qwen35_part(a, 3, 0, stream);
+}
+
+static int qwen35_part(const tfb_qwen35_step_args* a, int part, int layer, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->layers && a->n_layers > 0 && a->table && a->gamma_final && a->w_head && a->tokens && a->pos, TFB_EINVAL);
     TFB_REQUIRE(a->hidden_buf && a->attended_buf && a->proj_buf && a->mixed_buf && a->router_logits && a->router_idx &&
                     a->router_w && a->inner_buf && a->part_o && a->part_ml && a->counters && a->head_val && a->head_idx,
                 TFB_EINVAL);
     TFB_REQUIRE(a->max_tokens <= a->max_ctx + 1, TFB_ECAPACITY);
     TFB_REQUIRE(a->inter > 0 && a->shared_inter % a->inter == 0, TFB_EINVAL);
+    const bool sharded = a->ep_world > 1;
+    TFB_REQUIRE(!sharded || (a->partial && a->pair && a->ep_rank >= 0 && a->ep_rank < a->ep_world &&
+                             a->shared_inter % a->ep_world == 0 && a->vocab % a->ep_world == 0), TFB_EINVAL);
     const int pdl = a->pdl;
     const int H = a->hidden, KEY = a->hk * a->dk, VAL = a->hv * a->dv, CONV = 2 * KEY + VAL;
     const int N_GDN = CONV + VAL + 2 * a->hv, QD = a->hq * a->d, N_ATT = 2 * QD + 2 * a->hkv * a->d;
-    const int E = a->experts, K = a->top_k, I = a->inter, IS = a->shared_inter;
+    const int E = a->experts, K = a->top_k, I = a->inter;
+    const int IS = sharded ? a->shared_inter / a->ep_world : a->shared_inter;   // this rank's slice of the shared expert
     cudaStream_t st = S(stream);
     float* hid = a->hidden_buf;
     float* att = a->attended_buf;
     // The step's first launch carries no programmatic dependency: it starts only when the previous step has
     // fully finished, so kernels of this step may read last step's state and position before their own wait.
-    cudaError_t e = tfb::embed_f32_launch(static_cast<const uint16_t*>(a->table), nullptr,
-                                          reinterpret_cast<const long long*>(a->tokens), a->pos, hid, 1, H, a->vocab, st,
-                                          false);
-    if (e != cudaSuccess) return fail_launch(e);
+    cudaError_t e = cudaSuccess;
+    if (part == 0) {
+        e = tfb::embed_f32_launch(static_cast<const uint16_t*>(a->table), nullptr,
+                                  reinterpret_cast<const long long*>(a->tokens), a->pos, hid, 1, H, a->vocab, st, false);
+        return done(e);
+    }
     int rc;
     tfb_gemv_f32_args g;
     auto base = [&](tfb_gemv_f32_args& x) { std::memset(&x, 0, sizeof x); x.eps = a->eps; x.pdl = pdl; };
-    for (int l = 0; l < a->n_layers; ++l) {
+    for (int l = layer; part == 1 && l <= layer; ++l) {
         const tfb_qwen35_layer& L = a->layers[l];
         base(g); g.w = L.w_in; g.x = hid; g.gamma = L.gamma_in; g.y = a->proj_buf; g.k = H;
         g.n = L.kind == 0 ? N_GDN : N_ATT; g.prologue = TFB_NORM_F32GAIN; g.epilogue = TFB_EPI_STORE;
@@ -215,18 +241,21 @@ int tfb_qwen35_decode_step(const tfb_qwen35_step_args* a, tfb_stream_t stream) {
         base(g); g.w = L.w_gate; g.w2 = L.w_up; g.w_extra = L.w_shared_gate; g.w2_extra = L.w_shared_up; g.x = att;
         g.gamma = L.gamma_post; g.y = a->inner_buf; g.n = K * I + IS; g.k = H; g.prologue = TFB_NORM_F32GAIN;
         g.epilogue = TFB_EPI_SWIGLU; g.expert_idx = a->router_idx; g.rows_per_expert = I; g.routed_slots = K;
+        g.expert_rank = a->ep_rank; g.expert_world = a->ep_world;
         if ((rc = tfb_gemv_f32(&g, stream))) return rc;
         tfb_moe_down_f32_args d;
         std::memset(&d, 0, sizeof d);
         d.w_down = L.w_down; d.w_shared = L.w_shared_down; d.inner = a->inner_buf; d.indices = a->router_idx;
         d.weights = a->router_w; d.shared_gate_logit = a->router_logits + E; d.residual = att; d.out = hid;
         d.hidden = H; d.inter = I; d.shared_inter = IS; d.top_k = K; d.pdl = pdl;
+        d.expert_rank = a->ep_rank; d.expert_world = a->ep_world; d.partial = sharded ? a->partial : nullptr;
         if ((rc = tfb_moe_down_f32(&d, stream))) return rc;
-        if (a->hidden_trace) {
+        if (a->hidden_trace && !sharded) {
             e = tfb::copy_launch(hid, a->hidden_trace + size_t(l) * H, H * 4, st, pdl != 0);
             if (e != cudaSuccess) return fail_launch(e);
         }
     }
+    if (part == 1) return TFB_OK;
     if (a->hidden_trace) {
         e = tfb::rmsnorm_f32_launch(hid, a->gamma_final, a->hidden_trace + size_t(a->n_layers) * H, 1, H, a->eps, st, pdl != 0);
         if (e != cudaSuccess) return fail_launch(e);
@@ -235,7 +264,12 @@ int tfb_qwen35_decode_step(const tfb_qwen35_step_args* a, tfb_stream_t stream) {
     std::memset(&h, 0, sizeof h);
     h.w = a->w_head; h.x = hid; h.gamma = a->gamma_final; h.logits = a->logits;
     h.scratch_val = a->head_val; h.scratch_idx = a->head_idx; h.counter = a->counters + tfb::attn_gated_groups(a->hq, a->hkv, a->d);
-    h.n = int(a->vocab); h.k = H; h.prologue = TFB_NORM_F32_INPUT; h.eps = a->eps;
+    const int vslice = sharded ? int(a->vocab / a->ep_world) : int(a->vocab);
+    if (sharded) {                                             // w_head already is this rank's slice
+        if (a->logits) h.logits = static_cast<uint16_t*>(a->logits) + size_t(a->ep_rank) * vslice;
+        h.pair_out = a->pair; h.index_offset = a->ep_rank * vslice;
+    }
+    h.n = vslice; h.k = H; h.prologue = TFB_NORM_F32_INPUT; h.eps = a->eps;
     h.x_scale = 1.f; h.out_scale = 1.f; h.pdl = pdl; h.token_out = a->picked;
     h.tokens = a->tokens; h.pos = a->pos; h.n_prompt = a->n_prompt; h.max_tokens = a->max_tokens;
     return tfb_lm_head_argmax(&h, stream);

@@ -66,10 +66,16 @@ __global__ void __launch_bounds__(256) moe_allreduce_finalize_kernel(const PeerR
             routed += (r == p.rank) ? mine_r : __ldcg(boxes + size_t(r) * 2 * H + j);
             shared += (r == p.rank) ? mine_s : __ldcg(boxes + size_t(r) * 2 * H + H + j);
         }
-        float v = round_bf16(routed);
-        if (p.has_shared) v = round_bf16(v + round_bf16(shared));
-        if (p.residual) v = bf16_bits_to_f32(p.residual[j]) + round_bf16(v * p.res_scale);
-        p.out[j] = f32_to_bf16_bits(v);
+        if (p.out_f32) {                                                         // f32 activations (Qwen3.5)
+            float sh = round_bf16(shared);
+            if (p.gate_logit) sh *= 1.f / (1.f + expf(-*p.gate_logit));
+            p.out_f32[j] = (p.residual_f32 ? p.residual_f32[j] : 0.f) + (routed + sh);
+        } else {
+            float v = round_bf16(routed);
+            if (p.has_shared) v = round_bf16(v + round_bf16(shared));
+            if (p.residual) v = bf16_bits_to_f32(p.residual[j]) + round_bf16(v * p.res_scale);
+            p.out[j] = f32_to_bf16_bits(v);
+        }
     }
     if (tid == 0) p.epoch[b] = e;
 }

@@ -115,13 +115,18 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_f32_kernel(const GemvF32Param
     pdl_wait();
     trace_waited(p.trace);
 
+    int rows_live = rows_valid;
     if (routed) {
-        const long long e = p.expert_idx[slot];
-        const size_t erow = size_t(e) * p.rows_per_expert + within;
+        long long e = p.expert_idx[slot];
+        if (p.expert_world > 1) {                              // another rank owns this expert: nothing to read or write
+            if (e % p.expert_world != p.expert_rank) rows_live = 0;
+            e /= p.expert_world;
+        }
+        const size_t erow = size_t(rows_live ? e : 0) * p.rows_per_expert + within;
         wrow = p.w + erow * row_stride;
         if (EPI == 2) w2row = p.w2 + erow * row_stride;
-        a.load(wrow, row_stride, rows_valid, it_begin, it_end, lane);
-        if (EPI == 2) b.load(w2row, row_stride, rows_valid, it_begin, it_end, lane);
+        a.load(wrow, row_stride, rows_live, it_begin, it_end, lane);
+        if (EPI == 2) b.load(w2row, row_stride, rows_live, it_begin, it_end, lane);
     }
     float res_early = 0.f;
     if (EPI == 1 && ks == 0 && lane < rows_valid) res_early = p.residual[row0 + lane];
@@ -138,8 +143,8 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_f32_kernel(const GemvF32Param
         a.fma(xs, it0, it_end, lane, acc);
         if (EPI == 2) b.fma(xs, it0, it_end, lane, acc2);
         if (it0 + UNROLL < it_end) {
-            a.load(wrow, row_stride, rows_valid, it0 + UNROLL, it_end, lane);
-            if (EPI == 2) b.load(w2row, row_stride, rows_valid, it0 + UNROLL, it_end, lane);
+            a.load(wrow, row_stride, rows_live, it0 + UNROLL, it_end, lane);
+            if (EPI == 2) b.load(w2row, row_stride, rows_live, it0 + UNROLL, it_end, lane);
         }
     }
 #pragma unroll
@@ -169,7 +174,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_f32_kernel(const GemvF32Param
             acc2[r] = s2;
         }
     }
-    if (lane < rows_valid) {
+    if (lane < rows_live) {
         float v = 0.f, v2 = 0.f;
 #pragma unroll
         for (int r = 0; r < ROWS; ++r)

@@ -203,6 +203,7 @@ struct GemvF32Params {
     const long long* expert_idx;
     int rows_per_expert, routed_slots;
     unsigned long long* trace;
+    int expert_rank, expert_world;   // expert mode: expert e lives on rank e % world as local expert e / world
     // router launch (epilogue store, no expert mode), optional: the last CTA selects route_top_k of the first
     // route_experts outputs (softmax over all, top-k, renormalise) into idx_out / w_out
     unsigned* route_counter;         // u32, zero before the first launch; the kernel leaves it zero
@@ -269,6 +270,8 @@ struct MoeDownF32Params {
     const float* residual;
     float* out;
     int hidden, inter, shared_inter, top_k;
+    int expert_rank, expert_world;   // expert e lives on rank e % world as local expert e / world (world <= 1: all local)
+    float* partial;                  // optional f32 [2][hidden]: this rank's routed sum and un-rounded shared dot
 };
 cudaError_t moe_down_f32_launch(const MoeDownF32Params& p, cudaStream_t stream, bool pdl);
 
@@ -323,6 +326,10 @@ struct PeerReduceParams {
     uint16_t* out;
     int hidden, rank, world, has_shared;
     float res_scale;
+    // f32 form (Qwen3.5): out_f32 = residual_f32 + sum(routed) + bf16(sum(shared)) * sigmoid(*gate_logit)
+    const float* residual_f32;
+    float* out_f32;
+    const float* gate_logit;
 };
 cudaError_t moe_allreduce_finalize_launch(const PeerReduceParams& p, cudaStream_t stream, bool pdl);
 struct PeerPickParams {

@@ -216,10 +216,19 @@ __global__ void __launch_bounds__(kDownWarps * 32) moe_down_f32_kernel(const Moe
     const int pieces = I >> 3;
     for (int s0 = 0; s0 < K; s0 += 8) {
         uint4 wb[8][2];
+        bool alive[8];
+        const uint4* rows[8];
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
-            const bool live = s0 + s < K;
-            const uint4* row = p.w_down + (size_t(live ? s_idx[s0 + s] : 0) * p.hidden + j) * pieces;
+            bool live = s0 + s < K;
+            long long e = live ? s_idx[s0 + s] : 0;
+            if (live && p.expert_world > 1) {                  // expert parallel: only this rank's experts are here
+                if (e % p.expert_world != p.expert_rank) live = false;
+                e /= p.expert_world;
+            }
+            alive[s] = live;
+            const uint4* row = p.w_down + (size_t(live ? e : 0) * p.hidden + j) * pieces;
+            rows[s] = row;
 #pragma unroll
             for (int u = 0; u < 2; ++u)
                 wb[s][u] = (live && lane + 32 * u < pieces) ? ld_stream16(row + lane + 32 * u) : make_uint4(0, 0, 0, 0);
@@ -228,7 +237,7 @@ __global__ void __launch_bounds__(kDownWarps * 32) moe_down_f32_kernel(const Moe
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
             acc[s] = 0.f;
-            if (s0 + s >= K) continue;
+            if (!alive[s]) continue;
             const float* x = xin + (s0 + s) * I;
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
@@ -238,9 +247,8 @@ __global__ void __launch_bounds__(kDownWarps * 32) moe_down_f32_kernel(const Moe
                     acc[s] = dot8(wb[s][u], xa, xb, acc[s]);
                 }
             }
-            const uint4* row = p.w_down + (size_t(s_idx[s0 + s]) * p.hidden + j) * pieces;
             for (int c = lane + 64; c < pieces; c += 32) {        // rows wider than 512 elements
-                const uint4 w = ld_stream16(row + c);
+                const uint4 w = ld_stream16(rows[s] + c);
                 const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
                 acc[s] = dot8(w, xa, xb, acc[s]);
             }
@@ -251,7 +259,7 @@ __global__ void __launch_bounds__(kDownWarps * 32) moe_down_f32_kernel(const Moe
             for (int s = 0; s < 8; ++s) acc[s] += __shfl_xor_sync(0xffffffffu, acc[s], o);
 #pragma unroll
         for (int s = 0; s < 8; ++s)
-            if (s0 + s < K) routed = fmaf(round_bf16(acc[s]), s_w[s0 + s], routed);
+            if (alive[s]) routed = fmaf(round_bf16(acc[s]), s_w[s0 + s], routed);
     }
     float out = routed;
     if (shrow) {
@@ -270,11 +278,19 @@ __global__ void __launch_bounds__(kDownWarps * 32) moe_down_f32_kernel(const Moe
             const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
             acc = dot8(w, xa, xb, acc);
         }
-        float sh = round_bf16(warp_sum(acc));
-        if (p.shared_gate_logit) sh *= 1.f / (1.f + expf(-*p.shared_gate_logit));
-        out += sh;
+        const float sh_raw = warp_sum(acc);
+        if (p.partial) {                                         // sharded: the ranks' dots are added before the rounding
+            if (lane == 0) p.partial[p.hidden + j] = sh_raw;
+        } else {
+            float sh = round_bf16(sh_raw);
+            if (p.shared_gate_logit) sh *= 1.f / (1.f + expf(-*p.shared_gate_logit));
+            out += sh;
+        }
     }
-    if (lane == 0) p.out[j] = res + out;
+    if (lane == 0) {
+        if (p.partial) p.partial[j] = routed;
+        else p.out[j] = res + out;
+    }
 }
 
 cudaError_t moe_down_f32_launch(const MoeDownF32Params& p, cudaStream_t stream, bool pdl) {

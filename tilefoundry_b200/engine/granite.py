@@ -128,49 +128,24 @@ class GraniteSession(DecodeSession):
             L + 1 if self.world > 1 else 0)              # sharded: one finalize per layer and the final pick
 
     def _setup_peer_exchange(self, H: int, want: str | None) -> str:
-        """Symmetric buffers for the peer-memory exchange kernels: every rank's inboxes and flags, mapped into every
-        process.  Returns the mode in use."""
-        import torch.distributed as dist
-        if want == "nccl":
-            return "nccl"
-        W, n_cta = self.world, (H + 255) // 256
-        words = [2 * W * 2 * H, W * n_cta, 2 * W * 2, W]              # reduce inbox, reduce flags, pick inbox, pick flags
-        words = [(w + 63) // 64 * 64 for w in words]                   # keep every region 256-byte aligned
-        ok = torch.ones(1, device=self.device)
-        try:
-            import torch.distributed._symmetric_memory as symm
-            self._sym = symm.empty(sum(words), dtype=torch.float32, device=self.device)
-            self._sym.zero_()
-            self._sym_handle = symm.rendezvous(self._sym, self.group)
-            ptrs = [int(p) for p in self._sym_handle.buffer_ptrs]
-        except Exception as exc:                                       # noqa: BLE001 -- any failure means "not available here"
-            why = repr(exc)
-            ok.zero_()
-            ptrs = None
-        else:
-            why = "another rank could not map symmetric memory"
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)    # all ranks agree on the mode
-        if float(ok) == 0.0:
-            if want == "peer":
-                raise RuntimeError(f"peer-memory collectives were requested but are unavailable: {why}")
-            return "nccl"
-        torch.cuda.synchronize()
-        dist.barrier(group=self.group)                                 # every inbox and flag is zero before any push
-        off = [0, words[0] * 4, (words[0] + words[1]) * 4, (words[0] + words[1] + words[2]) * 4]
-        z = lambda n: torch.zeros(n, device=self.device, dtype=torch.int32)
-        self.peer_epoch, self.pick_epoch, self.peer_status = z(n_cta), z(1), z(1)
-        a = self.args
+        """Argument blocks of the two exchange kernels over the ranks' symmetric buffers.  Returns the mode in use."""
+        from .peer import PeerBuffers
+        self._peer = PeerBuffers(self.group, self.rank, self.world, H, self.device, want)
+        if self._peer.mode != "peer":
+            return self._peer.mode
+        pb, W, a = self._peer, self.world, self.args
+        self.peer_epoch, self.pick_epoch, self.peer_status = pb.reduce_epoch, pb.pick_epoch, pb.status
         self._reduce_args = lib.MoeAllreduceArgs(
-            partial=lib.ptr(self.partial), epoch=lib.ptr(self.peer_epoch), status=lib.ptr(self.peer_status),
+            partial=lib.ptr(self.partial), epoch=lib.ptr(pb.reduce_epoch), status=lib.ptr(pb.status),
             residual=lib.ptr(self.hidden), out=lib.ptr(self.hidden), hidden=H, rank=self.rank, world=W, has_shared=1,
             res_scale=a.res_scale, pdl=a.pdl)
         self._pick_args = lib.PickAllgatherArgs(
-            pair=lib.ptr(self.pair), epoch=lib.ptr(self.pick_epoch), status=lib.ptr(self.peer_status),
+            pair=lib.ptr(self.pair), epoch=lib.ptr(pb.pick_epoch), status=lib.ptr(pb.status),
             tokens=lib.ptr(self.tokens), pos=lib.ptr(self.pos), picked=lib.ptr(self.picked), n_prompt=0,
             max_tokens=self.max_ctx + 1, rank=self.rank, world=W, pdl=a.pdl)
         for r in range(W):
-            self._reduce_args.inbox[r], self._reduce_args.flags[r] = ptrs[r] + off[0], ptrs[r] + off[1]
-            self._pick_args.inbox[r], self._pick_args.flags[r] = ptrs[r] + off[2], ptrs[r] + off[3]
+            self._reduce_args.inbox[r], self._reduce_args.flags[r] = pb.reduce_inbox[r], pb.reduce_flags[r]
+            self._pick_args.inbox[r], self._pick_args.flags[r] = pb.pick_inbox[r], pb.pick_flags[r]
         return "peer"
 
     def reset(self, prompt_ids) -> None:

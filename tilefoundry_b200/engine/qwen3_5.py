@@ -9,7 +9,7 @@ import torch
 
 from .. import lib
 from ..authored.qwen3_5_35b_a3b import Qwen35Config, rope_tables
-from . import paged_kv
+from . import paged_kv, sharding
 from .session import DecodeSession
 
 
@@ -45,9 +45,19 @@ MOE_W = ("gamma_post", "w_gate", "w_up", "w_down", "w_shared_gate", "w_shared_up
 
 class Qwen35Session(DecodeSession):
     def __init__(self, cfg: Qwen35Config, resource, *, max_ctx: int | None = None, device="cuda:0",
-                 keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True):
+                 keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True, group=None,
+                 collectives: str | None = None):
+        """*group*: a ``torch.distributed`` process group to shard the MoE blocks (expert e on rank ``e % n``, the
+        shared expert sliced) and the head (vocabulary slices) over; ``None`` runs everything on this GPU.  The
+        exchange steps run as single kernels over NVLink peer memory (*collectives* ``"peer"``, required)."""
         if not torch.cuda.is_available():
             raise RuntimeError("Qwen35Session needs a CUDA device; there is no CPU path")
+        self.group = group
+        if group is not None:
+            import torch.distributed as dist
+            self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        else:
+            self.rank, self.world = 0, 1
         lib.load()
         self.cfg, self.device = cfg, torch.device(device)
         self.max_ctx = int(max_ctx or cfg.max_ctx)
@@ -62,7 +72,11 @@ class Qwen35Session(DecodeSession):
         E, K, I, IS = cfg.n_experts, cfg.top_k, cfg.moe_intermediate, cfg.shared_intermediate
         self.table_w = to(resource.load("table")).contiguous()
         self.gamma_final = to(resource.load("gamma_final")).contiguous()
-        self.w_head = _rows(to(resource.load("w_head")))
+        head = resource.load("w_head")                                   # authored (hidden, vocab)
+        if self.world > 1:
+            lo, hi = sharding.vocab_slice(V, self.rank, self.world)
+            head = head[:, lo:hi]
+        self.w_head = _rows(to(head))
         cos, sin = rope_tables(cfg, "cpu")
         self.cos, self.sin = to(cos).contiguous(), to(sin).contiguous()
         self.table = paged_kv.block_table(1, self.max_ctx, device=dev)
@@ -73,7 +87,15 @@ class Qwen35Session(DecodeSession):
             mix, moe = sub.subtree("mixer"), sub.subtree("moe")
             names = GDN_W if kind == "linear_attention" else ATTN_W
             layer = pack_mixer(kind, {n: to(mix.load(n)) for n in names})
-            layer.update(pack_moe({n: to(moe.load(n)) for n in MOE_W}, to(moe.subtree("router").load("w_router"))))
+            moe_w = {n: moe.load(n) for n in MOE_W}
+            if self.world > 1:                                           # keep only this rank's shard on the device
+                for n in ("w_gate", "w_up", "w_down"):
+                    moe_w[n] = sharding.local_experts(moe_w[n], self.rank, self.world)
+                per = IS // self.world
+                lo, hi = self.rank * per, (self.rank + 1) * per
+                moe_w["w_shared_gate"], moe_w["w_shared_up"] = moe_w["w_shared_gate"][:, lo:hi], moe_w["w_shared_up"][:, lo:hi]
+                moe_w["w_shared_down"] = moe_w["w_shared_down"][lo:hi, :]
+            layer.update(pack_moe({n: to(t) for n, t in moe_w.items()}, to(moe.subtree("router").load("w_router"))))
             layer["kind"] = kind
             if kind == "linear_attention":
                 layer["conv_state"] = z(2, cfg.conv_dim, cfg.gdn_conv_kernel - 1)
@@ -99,6 +121,9 @@ class Qwen35Session(DecodeSession):
         self.trace = z(L + 1, H) if trace_hidden else None
         self.idx_trace = z(L, K, dtype=torch.int64) if trace_hidden else None
         self.picked = z(1, dtype=torch.int64)
+        self.partial, self.pair = z(2, H), z(2)
+        if self.world > 1 and (IS % self.world or (IS // self.world) % 8):
+            raise ValueError(f"shared intermediate size {IS} does not slice over {self.world} ranks in multiples of 8")
 
         self._layer_structs = (lib.Qwen35Layer * L)()
         for s, layer in zip(self._layer_structs, self.layers):
@@ -119,14 +144,39 @@ class Qwen35Session(DecodeSession):
             router_w=lib.ptr(self.router_w), inner_buf=lib.ptr(self.inner), part_o=lib.ptr(self.part_o),
             part_ml=lib.ptr(self.part_ml), counters=lib.ptr(self.counters), head_val=lib.ptr(self.head_val),
             head_idx=lib.ptr(self.head_idx), logits=lib.ptr(self.logits), picked=lib.ptr(self.picked),
-            hidden_trace=lib.ptr(self.trace), idx_trace=lib.ptr(self.idx_trace))
-        self.launches_per_step = 2 + 7 * L + (2 * L + 1 if trace_hidden else 0)
+            hidden_trace=lib.ptr(self.trace), idx_trace=lib.ptr(self.idx_trace), ep_rank=self.rank, ep_world=self.world,
+            partial=lib.ptr(self.partial), pair=lib.ptr(self.pair))
+        self.collectives = "none"
+        if self.world > 1:
+            from .peer import PeerBuffers
+            self._peer = pb = PeerBuffers(self.group, self.rank, self.world, H, dev, "peer" if collectives is None else collectives)
+            if pb.mode != "peer":
+                raise RuntimeError("the sharded Qwen3.5 step needs peer-memory collectives (symmetric memory)")
+            self.collectives, self.peer_status = "peer", pb.status
+            self._reduce_args = lib.MoeAllreduceArgs(
+                partial=lib.ptr(self.partial), epoch=lib.ptr(pb.reduce_epoch), status=lib.ptr(pb.status), hidden=H,
+                rank=self.rank, world=self.world, has_shared=1, res_scale=1.0, pdl=int(pdl),
+                residual_f32=lib.ptr(self.attended), out_f32=lib.ptr(self.hidden),
+                gate_logit=self.router_logits.data_ptr() + 4 * E)
+            self._pick_args = lib.PickAllgatherArgs(
+                pair=lib.ptr(self.pair), epoch=lib.ptr(pb.pick_epoch), status=lib.ptr(pb.status), tokens=lib.ptr(self.tokens),
+                pos=lib.ptr(self.pos), picked=lib.ptr(self.picked), n_prompt=0, max_tokens=self.max_ctx + 1,
+                rank=self.rank, world=self.world, pdl=int(pdl))
+            for r in range(self.world):
+                self._reduce_args.inbox[r], self._reduce_args.flags[r] = pb.reduce_inbox[r], pb.reduce_flags[r]
+                self._pick_args.inbox[r], self._pick_args.flags[r] = pb.pick_inbox[r], pb.pick_flags[r]
+        self.launches_per_step = 2 + 7 * L + (2 * L + 1 if trace_hidden else 0) + (L + 1 if self.world > 1 else 0)
 
     def _recurrent(self):
         return [l for l in self.layers if l["kind"] == "linear_attention"]
 
     def reset(self, prompt_ids) -> None:
         super().reset(prompt_ids)
+        if self.world > 1:
+            import torch.distributed as dist
+            self._pick_args.n_prompt = self.args.n_prompt
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)           # the ranks' kernels wait on one another: start them together
         for layer in self._recurrent():               # recurrent state starts at zero for a new sequence
             layer["conv_state"].zero_()
             layer["state"].zero_()
@@ -148,7 +198,7 @@ class Qwen35Session(DecodeSession):
         for l in self.layers:
             total += (l["w_in"].numel() + l["w_out"].numel() + l["w_router"].numel() + l["w_shared_gate"].numel()
                       + l["w_shared_up"].numel() + l["w_shared_down"].numel()) * 2
-            total += cfg.top_k * 3 * cfg.moe_intermediate * cfg.hidden * 2
+            total += cfg.top_k * 3 * cfg.moe_intermediate * cfg.hidden * 2 // self.world
         return total
 
     def state_bytes(self) -> int:
@@ -161,4 +211,14 @@ class Qwen35Session(DecodeSession):
         return 2 * c.n_kv_heads * c.head_dim * 4 * (len(self.layers) - len(self._recurrent()))
 
     def step(self) -> None:
-        lib.check(lib.load().tfb_qwen35_decode_step(C.byref(self.args), lib.stream()), "tfb_qwen35_decode_step")
+        so = lib.load()
+        if self.world == 1:
+            lib.check(so.tfb_qwen35_decode_step(C.byref(self.args), lib.stream()), "tfb_qwen35_decode_step")
+            return
+        part = lambda p, l=0: lib.check(so.tfb_qwen35_step_part(C.byref(self.args), p, l, lib.stream()), "tfb_qwen35_step_part")
+        part(0)
+        for l in range(len(self.layers)):
+            part(1, l)                               # ... this rank's partial sums of the MoE block
+            lib.check(so.tfb_moe_allreduce_finalize(C.byref(self._reduce_args), lib.stream()), "tfb_moe_allreduce_finalize")
+        part(3)                                      # this rank's vocabulary slice -> (best logit, index)
+        lib.check(so.tfb_pick_allgather(C.byref(self._pick_args), lib.stream()), "tfb_pick_allgather")

@@ -77,7 +77,7 @@ class GemmSmallMArgs(C.Structure):
 class MoeAllreduceArgs(C.Structure):
     _fields_ = [("partial", _vp), ("inbox", _vp * 8), ("flags", _vp * 8), ("epoch", _vp), ("status", _vp),
                 ("residual", _vp), ("out", _vp), ("hidden", _i32), ("rank", _i32), ("world", _i32), ("has_shared", _i32),
-                ("res_scale", _f32), ("pdl", _i32)]
+                ("res_scale", _f32), ("pdl", _i32), ("residual_f32", _vp), ("out_f32", _vp), ("gate_logit", _vp)]
 
 
 class PickAllgatherArgs(C.Structure):
@@ -149,7 +149,7 @@ class GemvF32Args(C.Structure):
                 ("residual", _vp), ("y", _vp), ("n", _i32), ("k", _i32), ("seg", _i32), ("prologue", _i32),
                 ("epilogue", _i32), ("eps", _f32), ("expert_idx", _vp), ("rows_per_expert", _i32),
                 ("routed_slots", _i32), ("pdl", _i32), ("reserved", _i32), ("route_counter", _vp), ("route_experts", _i32),
-                ("route_top_k", _i32), ("idx_out", _vp), ("w_out", _vp)]
+                ("route_top_k", _i32), ("idx_out", _vp), ("w_out", _vp), ("expert_rank", _i32), ("expert_world", _i32)]
 
 
 class GdnArgs(C.Structure):
@@ -170,7 +170,8 @@ class AttnGatedArgs(C.Structure):
 class MoeDownF32Args(C.Structure):
     _fields_ = [("w_down", _vp), ("w_shared", _vp), ("inner", _vp), ("indices", _vp), ("weights", _vp),
                 ("shared_gate_logit", _vp), ("residual", _vp), ("out", _vp), ("hidden", _i32), ("inter", _i32),
-                ("shared_inter", _i32), ("top_k", _i32), ("pdl", _i32), ("reserved", _i32)]
+                ("shared_inter", _i32), ("top_k", _i32), ("pdl", _i32), ("reserved", _i32), ("expert_rank", _i32),
+                ("expert_world", _i32), ("partial", _vp)]
 
 
 class Qwen35Layer(C.Structure):
@@ -192,7 +193,8 @@ class Qwen35StepArgs(C.Structure):
                 ("hidden_buf", _vp), ("attended_buf", _vp), ("proj_buf", _vp), ("mixed_buf", _vp),
                 ("router_logits", _vp), ("router_idx", _vp), ("router_w", _vp), ("inner_buf", _vp), ("part_o", _vp),
                 ("part_ml", _vp), ("counters", _vp), ("head_val", _vp), ("head_idx", _vp), ("logits", _vp),
-                ("picked", _vp), ("hidden_trace", _vp), ("idx_trace", _vp)]
+                ("picked", _vp), ("hidden_trace", _vp), ("idx_trace", _vp), ("ep_rank", _i32), ("ep_world", _i32),
+                ("partial", _vp), ("pair", _vp)]
 
 
 SYMBOLS = {
@@ -236,6 +238,7 @@ SYMBOLS = {
     "tfb_rmsnorm_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _f32, _i32, _vp]),
     "tfb_residual_add_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp]),
     "tfb_qwen35_decode_step": (_i32, [C.POINTER(Qwen35StepArgs), _vp]),
+    "tfb_qwen35_step_part": (_i32, [C.POINTER(Qwen35StepArgs), _i32, _i32, _vp]),
     "tfb_moe_allreduce_finalize": (_i32, [C.POINTER(MoeAllreduceArgs), _vp]),
     "tfb_pick_allgather": (_i32, [C.POINTER(PickAllgatherArgs), _vp]),
     "tfb_pick_finalize": (_i32, [_vp, _i32, _vp, _vp, _i32, _i32, _vp, _i32, _vp]),
