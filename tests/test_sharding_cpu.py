@@ -97,3 +97,65 @@ def test_sharding_helpers_reject_uneven_splits():
     with pytest.raises(ValueError, match="multiples of 8"):
         sharding.shared_slices(torch.zeros(24, 8), torch.zeros(8, 12), 0, 2)
     assert sharding.pick_from_pairs(torch.tensor([[1.0, 700.0], [1.0, 20.0], [0.5, 3.0]])) == 20
+
+
+def _worker_qwen35(rank, world, port, out):
+    """The f32-activation MoE block (Qwen3.5) split the way `Qwen35Session` splits it: every rank computes, with the
+    kernels' rounding points, the routed sum of the experts it owns and its slice's un-rounded shared dot; the sums
+    are added across ranks before the shared expert's single rounding and its sigmoid gate are applied."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import evaluator, qwen3_5_35b_a3b as oq
+        from tilefoundry_b200.authored import qwen3_5_35b_a3b as qa
+        from tilefoundry_b200.authored.weights import random_weights
+        from tilefoundry_b200.runtime import DictResource
+
+        cfg = qa.QWEN3_5_TINY
+        mod = qa.build(cfg)
+        weights = random_weights(mod, seed=5, std=0.05, overrides=qa.weight_overrides)
+        ref = evaluator.load(mod, DictResource(weights), oq.make(cfg))
+        moe = ref.layer0.moe
+        attended = torch.randn(1, 1, cfg.hidden, generator=torch.Generator().manual_seed(1))
+        tokens = moe.post_norm(attended)
+        w, idx = moe.router.routing(tokens)                       # replicated router: same on every rank
+        gathered_idx = [torch.zeros_like(idx) for _ in range(world)]
+        dist.all_gather(gathered_idx, idx)
+        assert all(torch.equal(g, idx) for g in gathered_idx)
+
+        c = moe.constants
+        K, IS, H = cfg.top_k, cfg.shared_intermediate, cfg.hidden
+        mm = lambda a, b: torch.matmul(a.to(BF), b.to(BF)).float()  # a product: bf16 in, bf16 out, carried as f32
+        gate_l, up_l, down_l = (sharding.local_experts(c[n], rank, world) for n in ("w_gate", "w_up", "w_down"))
+        x = tokens.reshape(H)
+        routed = torch.zeros(H)
+        for s in range(K):
+            e = int(idx[0, s])
+            if sharding.expert_owner(e, world) != rank:
+                continue
+            le = e // world
+            inner = torch.nn.functional.silu(mm(gate_l[le], x)) * mm(up_l[le], x)
+            routed += mm(down_l[le], inner) * w[0, s]
+        per = IS // world
+        lo, hi = rank * per, (rank + 1) * per
+        act = (torch.nn.functional.silu(mm(x, c["w_shared_gate"][:, lo:hi])) * mm(x, c["w_shared_up"][:, lo:hi])).to(BF)
+        shared = act.float() @ c["w_shared_down"][lo:hi, :].float()                     # un-rounded partial dot
+        partial = torch.stack([routed, shared])
+        dist.all_reduce(partial)
+        gate = torch.sigmoid(mm(x, c["w_shared_scale"]))
+        got = attended.reshape(H) + partial[0] + partial[1].to(BF).float() * gate
+        want = ref.layer0.residual_add(attended, moe.experts(tokens, w, idx)).reshape(H)
+        err = (got - want).abs().max().item()
+        out[rank] = (err, 2e-2 + 2e-2 * want.abs().max().item())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_qwen3_5_moe_block():
+    world = 2
+    out = mp.Manager().dict()
+    mp.spawn(_worker_qwen35, args=(world, 29331 + os.getpid() % 200, out), nprocs=world, join=True)
+    assert len(out) == world
+    for rank in range(world):
+        err, bound = out[rank]
+        assert err <= bound, f"rank {rank}: sharded Qwen3.5 MoE block differs by {err:.4g} > {bound:.4g}"
