@@ -402,6 +402,17 @@ TFB_API int tfb_ssm_step(const float* state_in, float* state_out, const void* x,
  * tfb_moe_down: out = residual + bf16(res_scale * (sum_s weight[s] * (W_down[idx[s]] . inner[s])
  * + W_shared . shared_act)) with the authored rounding points (routed_experts / experts /
  * residual_add, granite model.py:406-470,502); reference kernels granite.cu:537-700. */
+/* tfb_router_select_prefetch: the same selection; in addition lane j asks L2 (cp.async.bulk.prefetch.L2) for its
+ * expert's block of each of up to 4 weight slabs [experts][slab_bytes[i]] (16-byte multiples), e.g. the gate, up and
+ * down matrices: the kernels that read them cannot know the indices before their own dependency wait, and HBM is idle
+ * while this one-warp kernel runs.  expert_world > 1: only experts with e % world == rank, at local index e / world. */
+typedef struct {
+    const void* logits_bf16; const float* logits_f32; int64_t* indices; void* weights_bf16; float* weights_f32;
+    int32_t experts, top_k, mode, pdl;
+    const void* slab[4]; uint64_t slab_bytes[4];
+    int32_t n_slabs, expert_rank, expert_world, reserved;
+} tfb_router_select_args;
+TFB_API int tfb_router_select_prefetch(const tfb_router_select_args* args, tfb_stream_t stream);
 TFB_API int tfb_router_select(const void* logits_bf16, const float* logits_f32, int64_t* indices,
                               void* weights_bf16, float* weights_f32, int32_t experts, int32_t top_k,
                               int32_t mode, int32_t pdl, tfb_stream_t stream);
@@ -698,6 +709,8 @@ typedef struct {
     int32_t ep_rank, ep_world;
     float* partial;           /* f32 [2][hidden] */
     float* pair;              /* f32 [2] */
+    int32_t expert_prefetch;  /* non-zero: the selection kernel asks L2 for the selected experts' weights */
+    int32_t reserved;
 } tfb_qwen35_step_args;
 TFB_API int tfb_qwen35_decode_step(const tfb_qwen35_step_args* args, tfb_stream_t stream);
 /* One piece of the step, so a sharded caller can put its exchange kernels between them: part 0 embed; part 1 layer

@@ -257,3 +257,26 @@ def test_router_projection_selects_experts_in_its_last_cta(dev):
     assert torch.equal(probs[idx.cpu()], pv)                       # same values in the same order (equal values: any order in torch)
     got = idx.cpu().tolist()
     assert (17 not in got and 200 not in got) or (17 in got and (200 not in got or got.index(17) < got.index(200)))
+
+
+def test_select_with_expert_prefetch_selects_the_same(dev):
+    """The selection that also asks L2 for the chosen experts' weights returns what the plain selection returns
+    (the prefetch has no architectural effect), with and without an expert-parallel split."""
+    import ctypes as C
+    from tilefoundry_b200 import lib
+    E, K, I, H = 64, 8, 128, 256
+    g = torch.Generator().manual_seed(31)
+    logits = torch.randn(E, generator=g).to(dev)
+    slabs = [torch.zeros(E, I, H, dtype=torch.bfloat16, device=dev) for _ in range(3)]
+    idx, w = torch.zeros(K, dtype=torch.int64, device=dev), torch.zeros(K, device=dev)
+    lib.check(lib.load().tfb_router_select(None, lib.ptr(logits), lib.ptr(idx), None, lib.ptr(w), E, K, 1, 0, lib.stream()), "select")
+    for world, rank in ((1, 0), (2, 1)):
+        idx2, w2 = torch.zeros(K, dtype=torch.int64, device=dev), torch.zeros(K, device=dev)
+        local = [s[rank::world].contiguous() for s in slabs]
+        a = lib.RouterSelectArgs(logits_f32=lib.ptr(logits), indices=lib.ptr(idx2), weights_f32=lib.ptr(w2), experts=E, top_k=K,
+                                 mode=1, pdl=0, n_slabs=3, expert_rank=rank, expert_world=world)
+        for i, s in enumerate(local):
+            a.slab[i], a.slab_bytes[i] = s.data_ptr(), I * H * 2
+        lib.check(lib.load().tfb_router_select_prefetch(C.byref(a), lib.stream()), "tfb_router_select_prefetch")
+        torch.cuda.synchronize()
+        assert torch.equal(idx2.cpu(), idx.cpu()) and torch.equal(w2.cpu(), w.cpu())

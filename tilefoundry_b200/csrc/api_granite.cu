@@ -55,6 +55,24 @@ int tfb_router_select(const void* logits_bf16, const float* logits_f32, int64_t*
     return done(tfb::router_select_launch(p, S(stream), pdl != 0));
 }
 
+int tfb_router_select_prefetch(const tfb_router_select_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && (a->logits_bf16 || a->logits_f32) && a->indices && (a->weights_bf16 || a->weights_f32), TFB_EINVAL);
+    TFB_REQUIRE(a->experts > 0 && a->experts <= 256 && a->top_k > 0 && a->top_k <= 32 && a->top_k <= a->experts, TFB_EINVAL);
+    TFB_REQUIRE((a->mode == 0 || a->mode == 1) && a->n_slabs >= 0 && a->n_slabs <= 4, TFB_EINVAL);
+    TFB_REQUIRE(a->expert_world <= 1 || (a->expert_rank >= 0 && a->expert_rank < a->expert_world), TFB_EINVAL);
+    tfb::RouterParams p = {};
+    p.logits_bf16 = cu16(a->logits_bf16); p.logits_f32 = a->logits_f32;
+    p.indices = reinterpret_cast<long long*>(a->indices);
+    p.weights_bf16 = static_cast<uint16_t*>(a->weights_bf16); p.weights_f32 = a->weights_f32;
+    p.experts = a->experts; p.top_k = a->top_k; p.mode = a->mode;
+    for (int i = 0; i < a->n_slabs; ++i) {
+        TFB_REQUIRE(a->slab[i] && aligned16(a->slab[i]) && a->slab_bytes[i] > 0 && a->slab_bytes[i] % 16 == 0, TFB_EALIGN);
+        p.slab[i] = a->slab[i]; p.slab_bytes[i] = a->slab_bytes[i];
+    }
+    p.n_slabs = a->n_slabs; p.expert_rank = a->expert_rank; p.expert_world = a->expert_world;
+    return done(tfb::router_select_launch(p, S(stream), a->pdl != 0));
+}
+
 int tfb_moe_down(const tfb_moe_down_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->w_down && a->inner && a->indices && a->weights && a->out, TFB_EINVAL);
     TFB_REQUIRE(a->hidden > 0 && a->inter > 0 && a->inter % 8 == 0 && a->top_k > 0 && a->top_k <= 32, TFB_EINVAL);

@@ -167,6 +167,11 @@ struct RouterParams {
     uint16_t* weights_bf16;
     float* weights_f32;
     int experts, top_k, mode;
+    // optional: ask L2 for the selected experts' weights (the kernels that read them cannot know the indices before
+    // their own dependency wait, and HBM idles while this one-warp kernel runs)
+    const void* slab[4];             // [experts][slab_bytes[i]] each
+    unsigned long long slab_bytes[4];
+    int n_slabs, expert_rank, expert_world;
 };
 cudaError_t router_select_launch(const RouterParams& p, cudaStream_t stream, bool pdl);
 

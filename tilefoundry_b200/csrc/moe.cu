@@ -27,6 +27,16 @@ __global__ void __launch_bounds__(32) router_select_kernel(const RouterParams p)
         p.indices[threadIdx.x] = e;
         if (p.weights_bf16) p.weights_bf16[threadIdx.x] = f32_to_bf16_bits(w);
         if (p.weights_f32) p.weights_f32[threadIdx.x] = w;
+        long long le = e;
+        bool local = true;
+        if (p.expert_world > 1) { local = (e % p.expert_world) == p.expert_rank; le = e / p.expert_world; }
+        for (int i = 0; local && i < p.n_slabs; ++i) {
+            const char* base = static_cast<const char*>(p.slab[i]) + size_t(le) * p.slab_bytes[i];
+            for (unsigned long long off = 0; off < p.slab_bytes[i]; off += (1u << 20)) {
+                const unsigned long long left = p.slab_bytes[i] - off;
+                l2_prefetch_bulk(base + off, uint32_t(left < (1u << 20) ? left : (1u << 20)));
+            }
+        }
     }
 }
 

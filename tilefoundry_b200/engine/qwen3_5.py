@@ -46,10 +46,12 @@ MOE_W = ("gamma_post", "w_gate", "w_up", "w_down", "w_shared_gate", "w_shared_up
 class Qwen35Session(DecodeSession):
     def __init__(self, cfg: Qwen35Config, resource, *, max_ctx: int | None = None, device="cuda:0",
                  keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True, group=None,
-                 collectives: str | None = None):
+                 collectives: str | None = None, expert_prefetch: bool = False):
         """*group*: a ``torch.distributed`` process group to shard the MoE blocks (expert e on rank ``e % n``, the
         shared expert sliced) and the head (vocabulary slices) over; ``None`` runs everything on this GPU.  The
-        exchange steps run as single kernels over NVLink peer memory (*collectives* ``"peer"``, required)."""
+        exchange steps run as single kernels over NVLink peer memory (*collectives* ``"peer"``, required).
+        *expert_prefetch*: the selection kernel asks L2 for the selected experts' weights (measured 2.5 % slower per
+        step on B200, so off by default)."""
         if not torch.cuda.is_available():
             raise RuntimeError("Qwen35Session needs a CUDA device; there is no CPU path")
         self.group = group
@@ -145,7 +147,7 @@ class Qwen35Session(DecodeSession):
             part_ml=lib.ptr(self.part_ml), counters=lib.ptr(self.counters), head_val=lib.ptr(self.head_val),
             head_idx=lib.ptr(self.head_idx), logits=lib.ptr(self.logits), picked=lib.ptr(self.picked),
             hidden_trace=lib.ptr(self.trace), idx_trace=lib.ptr(self.idx_trace), ep_rank=self.rank, ep_world=self.world,
-            partial=lib.ptr(self.partial), pair=lib.ptr(self.pair))
+            partial=lib.ptr(self.partial), pair=lib.ptr(self.pair), expert_prefetch=int(expert_prefetch))
         self.collectives = "none"
         if self.world > 1:
             from .peer import PeerBuffers

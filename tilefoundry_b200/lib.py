@@ -194,7 +194,13 @@ class Qwen35StepArgs(C.Structure):
                 ("router_logits", _vp), ("router_idx", _vp), ("router_w", _vp), ("inner_buf", _vp), ("part_o", _vp),
                 ("part_ml", _vp), ("counters", _vp), ("head_val", _vp), ("head_idx", _vp), ("logits", _vp),
                 ("picked", _vp), ("hidden_trace", _vp), ("idx_trace", _vp), ("ep_rank", _i32), ("ep_world", _i32),
-                ("partial", _vp), ("pair", _vp)]
+                ("partial", _vp), ("pair", _vp), ("expert_prefetch", _i32), ("reserved", _i32)]
+
+
+class RouterSelectArgs(C.Structure):
+    _fields_ = [("logits_bf16", _vp), ("logits_f32", _vp), ("indices", _vp), ("weights_bf16", _vp), ("weights_f32", _vp),
+                ("experts", _i32), ("top_k", _i32), ("mode", _i32), ("pdl", _i32), ("slab", _vp * 4), ("slab_bytes", _u64 * 4),
+                ("n_slabs", _i32), ("expert_rank", _i32), ("expert_world", _i32), ("reserved", _i32)]
 
 
 SYMBOLS = {
@@ -220,6 +226,7 @@ SYMBOLS = {
     "tfb_residual_add": (_i32, [_vp, _vp, _vp, _i32, _f32, _vp]),
     "tfb_conv_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "tfb_ssm_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "tfb_router_select_prefetch": (_i32, [C.POINTER(RouterSelectArgs), _vp]),
     "tfb_router_select": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "tfb_moe_down": (_i32, [C.POINTER(MoeDownArgs), _vp]),
     "tfb_granite_decode_step": (_i32, [C.POINTER(GraniteStepArgs), _vp]),
