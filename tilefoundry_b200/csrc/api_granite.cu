@@ -77,7 +77,8 @@ int tfb_moe_down(const tfb_moe_down_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->w_down && a->inner && a->indices && a->weights && a->out, TFB_EINVAL);
     TFB_REQUIRE(a->hidden > 0 && a->inter > 0 && a->inter % 8 == 0 && a->top_k > 0 && a->top_k <= 32, TFB_EINVAL);
     TFB_REQUIRE(!a->w_shared || (a->shared_act && a->shared_inter > 0 && a->shared_inter % 8 == 0), TFB_EINVAL);
-    TFB_REQUIRE(aligned16(a->w_down) && (!a->w_shared || aligned16(a->w_shared)), TFB_EALIGN);
+    TFB_REQUIRE(aligned16(a->w_down) && (!a->w_shared || aligned16(a->w_shared)) && aligned16(a->inner) &&
+                    (!a->shared_act || aligned16(a->shared_act)), TFB_EALIGN);
     TFB_REQUIRE((size_t(a->top_k) * a->inter + a->shared_inter) * 4 <= 96 * 1024, TFB_ECAPACITY);
     tfb::MoeDownParams p = {};
     p.w_down = static_cast<const uint4*>(a->w_down); p.w_shared = static_cast<const uint4*>(a->w_shared);

@@ -46,86 +46,147 @@ cudaError_t router_select_launch(const RouterParams& p, cudaStream_t stream, boo
     return cudaErrorInvalidValue;
 }
 
-// One warp per output row j: for each selected slot s, dot(w_down[idx[s]][j, :], inner[s, :]) rounded to
-// bf16, times the routing weight (bf16), summed over slots with one rounding; plus the shared
-// expert's row; then the layer's scaled residual.  All rounding points of routed_experts / experts /
-// residual_add (examples/granite_4_0_h_small-cuda/model.py:406-470,502) are kept.
+// A warp owns kDownRows output rows: for each selected slot s, dot(w_down[idx[s]][j, :], inner[s, :]) rounded to
+// bf16, times the routing weight (bf16), summed over slots with one rounding; plus the shared expert's row; then
+// the layer's scaled residual.  All rounding points of routed_experts / experts / residual_add
+// (examples/granite_4_0_h_small-cuda/model.py:406-470,502) are kept.
+// Latency plan: the gathered activations are staged once per CTA with 16-byte loads and serve 16 rows; a warp has
+// the rows of TWO slots for both of its output rows in flight at a time (12 x 16 bytes per lane), so the routed
+// part takes top_k/2 memory round trips instead of top_k, each carrying four times the bytes.
 constexpr int kDownWarps = 8;
+constexpr int kDownRows = 2;
 __global__ void __launch_bounds__(kDownWarps * 32) moe_down_kernel(const MoeDownParams p) {
     extern __shared__ __align__(16) float smem[];
     float* xin = smem;                                        // [top_k][inter] then [shared_inter]
     __shared__ long long s_idx[32];
     __shared__ float s_w[32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int j = blockIdx.x * kDownWarps + warp;
+    const int j0 = (blockIdx.x * kDownWarps + warp) * kDownRows;
     const int I = p.inter, IS = p.shared_inter, K = p.top_k;
 
-    // the shared expert's row does not depend on the routing: fetch it before the wait
+    // the shared expert's rows do not depend on the routing: fetch them before the wait
     const int sh_pieces = IS >> 3;                            // 16-byte pieces in a shared-expert row
-    uint4 shw[4];
-    const uint4* shrow = (p.w_shared && j < p.hidden) ? p.w_shared + size_t(j) * sh_pieces : nullptr;
+    uint4 shw[kDownRows][4];
+    const uint4* shrow[kDownRows];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) shw[u] = (shrow && lane + 32 * u < sh_pieces) ? ld_stream16(shrow + lane + 32 * u) : make_uint4(0, 0, 0, 0);
+    for (int r = 0; r < kDownRows; ++r) {
+        shrow[r] = (p.w_shared && j0 + r < p.hidden) ? p.w_shared + size_t(j0 + r) * sh_pieces : nullptr;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            shw[r][u] = (shrow[r] && lane + 32 * u < sh_pieces) ? ld_stream16(shrow[r] + lane + 32 * u) : make_uint4(0, 0, 0, 0);
+    }
     pdl_trigger();
     pdl_wait();
 
-    const float res = (p.residual && j < p.hidden) ? bf16_bits_to_f32(p.residual[j]) : 0.f;
-    if (threadIdx.x < K) { s_idx[threadIdx.x] = p.indices[threadIdx.x]; s_w[threadIdx.x] = bf16_bits_to_f32(p.weights[threadIdx.x]); }
-    for (int i = threadIdx.x; i < K * I + IS; i += blockDim.x)
-        xin[i] = bf16_bits_to_f32(i < K * I ? p.inner[i] : p.shared_act[i - K * I]);
-    __syncthreads();
-    if (j >= p.hidden) return;
-
-    float routed = 0.f;
-    const int pieces = I >> 3;
-    for (int s = 0; s < K; ++s) {
-        long long e = s_idx[s];
-        if (p.expert_world > 1) {                              // expert parallel: only this rank's experts are here
-            if (e % p.expert_world != p.expert_rank) continue;
-            e /= p.expert_world;
-        }
-        const uint4* row = p.w_down + (size_t(e) * p.hidden + j) * pieces;
-        const float* x = xin + s * I;
-        float acc = 0.f;
-        for (int c = lane; c < pieces; c += 32) {
-            const uint4 w = ld_stream16(row + c);
-            const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
-            acc = dot8(w, xa, xb, acc);
-        }
-        acc = warp_sum(acc);
-        routed += round_bf16(round_bf16(acc) * s_w[s]);        // bf16 products, f32 running sum
-    }
-    float out = round_bf16(routed);                            // the reduce over slots returns bf16
-    float sh_raw = 0.f;
-    if (shrow) {
-        const float* x = xin + K * I;
-        float acc = 0.f;
+    float res[kDownRows];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int c = lane + 32 * u;
-            if (c < sh_pieces) {
-                const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
-                acc = dot8(shw[u], xa, xb, acc);
+    for (int r = 0; r < kDownRows; ++r) res[r] = (p.residual && j0 + r < p.hidden) ? bf16_bits_to_f32(p.residual[j0 + r]) : 0.f;
+    if (threadIdx.x < K) { s_idx[threadIdx.x] = p.indices[threadIdx.x]; s_w[threadIdx.x] = bf16_bits_to_f32(p.weights[threadIdx.x]); }
+    for (int c = threadIdx.x; c < (K * I + IS) >> 3; c += blockDim.x) {          // 8 activations per 16-byte load
+        const int i = c << 3;
+        const uint4 v = i < K * I ? *reinterpret_cast<const uint4*>(p.inner + i) : *reinterpret_cast<const uint4*>(p.shared_act + (i - K * I));
+        *reinterpret_cast<float4*>(xin + i) = make_float4(bf16_lo(v.x), bf16_hi(v.x), bf16_lo(v.y), bf16_hi(v.y));
+        *reinterpret_cast<float4*>(xin + i + 4) = make_float4(bf16_lo(v.z), bf16_hi(v.z), bf16_lo(v.w), bf16_hi(v.w));
+    }
+    __syncthreads();
+    if (j0 >= p.hidden) return;
+
+    float routed[kDownRows];
+#pragma unroll
+    for (int r = 0; r < kDownRows; ++r) routed[r] = 0.f;
+    const int pieces = I >> 3;
+    for (int s0 = 0; s0 < K; s0 += 2) {
+        uint4 wb[2][kDownRows][3];
+        bool live[2];
+        const uint4* rows[2];
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            live[t] = s0 + t < K;
+            long long e = live[t] ? s_idx[s0 + t] : 0;
+            if (live[t] && p.expert_world > 1) {               // expert parallel: only this rank's experts are here
+                if (e % p.expert_world != p.expert_rank) live[t] = false;
+                e /= p.expert_world;
+            }
+            rows[t] = p.w_down + (size_t(live[t] ? e : 0) * p.hidden + j0) * pieces;
+#pragma unroll
+            for (int r = 0; r < kDownRows; ++r)
+#pragma unroll
+                for (int u = 0; u < 3; ++u)
+                    wb[t][r][u] = (live[t] && j0 + r < p.hidden && lane + 32 * u < pieces)
+                                      ? ld_stream16(rows[t] + size_t(r) * pieces + lane + 32 * u) : make_uint4(0, 0, 0, 0);
+        }
+        float acc[2][kDownRows];
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            const float* x = xin + (s0 + t) * I;
+#pragma unroll
+            for (int r = 0; r < kDownRows; ++r) {
+                acc[t][r] = 0.f;
+                if (!live[t]) continue;
+#pragma unroll
+                for (int u = 0; u < 3; ++u) {
+                    const int c = lane + 32 * u;
+                    if (c < pieces) {
+                        const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
+                        acc[t][r] = dot8(wb[t][r][u], xa, xb, acc[t][r]);
+                    }
+                }
+                for (int c = lane + 96; c < pieces; c += 32) {   // rows wider than 768 elements
+                    const uint4 w = ld_stream16(rows[t] + size_t(r) * pieces + c);
+                    const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
+                    acc[t][r] = dot8(w, xa, xb, acc[t][r]);
+                }
             }
         }
-        for (int c = lane + 128; c < sh_pieces; c += 32) {       // rows wider than 1024 elements
-            const uint4 w = ld_stream16(shrow + c);
-            const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
-            acc = dot8(w, xa, xb, acc);
-        }
-        sh_raw = warp_sum(acc);
-        float sh = round_bf16(sh_raw);
-        if (p.shared_gate) sh = round_bf16(sh * *p.shared_gate);  // Qwen3.5: sigmoid gate on the shared expert
-        out = round_bf16(out + sh);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int t = 0; t < 2; ++t)
+#pragma unroll
+                for (int r = 0; r < kDownRows; ++r) acc[t][r] += __shfl_xor_sync(0xffffffffu, acc[t][r], o);
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+            if (live[t]) {
+#pragma unroll
+                for (int r = 0; r < kDownRows; ++r) routed[r] += round_bf16(round_bf16(acc[t][r]) * s_w[s0 + t]);   // bf16 products, f32 running sum
+            }
     }
-    if (lane == 0) {
-        if (p.partial) {                                         // sharded: the ranks' sums are added before any rounding
-            p.partial[j] = routed;
-            p.partial[p.hidden + j] = sh_raw;
-            return;
+#pragma unroll
+    for (int r = 0; r < kDownRows; ++r) {
+        const int j = j0 + r;
+        if (j >= p.hidden) continue;
+        float out = round_bf16(routed[r]);                     // the reduce over slots returns bf16
+        float sh_raw = 0.f;
+        if (shrow[r]) {
+            const float* x = xin + K * I;
+            float acc = 0.f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int c = lane + 32 * u;
+                if (c < sh_pieces) {
+                    const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
+                    acc = dot8(shw[r][u], xa, xb, acc);
+                }
+            }
+            for (int c = lane + 128; c < sh_pieces; c += 32) {   // rows wider than 1024 elements
+                const uint4 w = ld_stream16(shrow[r] + c);
+                const float4 xa = *reinterpret_cast<const float4*>(x + c * 8), xb = *reinterpret_cast<const float4*>(x + c * 8 + 4);
+                acc = dot8(w, xa, xb, acc);
+            }
+            sh_raw = warp_sum(acc);
+            float sh = round_bf16(sh_raw);
+            if (p.shared_gate) sh = round_bf16(sh * *p.shared_gate);  // a gate on the shared expert
+            out = round_bf16(out + sh);
         }
-        if (p.residual) out = res + round_bf16(out * p.res_scale);
-        p.out[j] = f32_to_bf16_bits(out);
+        if (lane == 0) {
+            if (p.partial) {                                     // sharded: the ranks' sums are added before any rounding
+                p.partial[j] = routed[r];
+                p.partial[p.hidden + j] = sh_raw;
+            } else {
+                if (p.residual) out = res[r] + round_bf16(out * p.res_scale);
+                p.out[j] = f32_to_bf16_bits(out);
+            }
+        }
     }
 }
 
@@ -187,7 +248,7 @@ cudaError_t moe_down_launch(const MoeDownParams& p, cudaStream_t stream, bool pd
             once = true;
         }
     }
-    const dim3 grid((p.hidden + kDownWarps - 1) / kDownWarps), block(kDownWarps * 32);
+    const dim3 grid((p.hidden + kDownWarps * kDownRows - 1) / (kDownWarps * kDownRows)), block(kDownWarps * 32);
     return launch_kernel(moe_down_kernel, grid, block, smem, stream, pdl, p);
 }
 
