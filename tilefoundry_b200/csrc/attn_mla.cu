@@ -3,7 +3,7 @@
 // values [heads][v], one launch per layer.
 //
 // HBM/L2-bound on the cache: algorithmic bytes per launch = (ctx+1) * heads * (nope+rope+v) * 2.
-// Grid = (heads, splits): one CTA owns one head and one 64-row page.  Same latency plan as the GQA
+// Grid = (heads, splits): one CTA owns one head and 128 positions (two pages).  Same latency plan as the GQA
 // kernel: cached rows stream into shared memory with cp.async before griddepcontrol.wait; after the
 // wait this token's query is rotated and scaled, its key/value row joins the shared tile, and the
 // last CTA of a head to finish (atomic ticket, no spinning) merges the split partials.
@@ -13,8 +13,9 @@
 
 namespace tfb {
 
-constexpr int kMlaSplit = 64;
-constexpr int kMlaThreads = 128;
+constexpr int kMlaSplit = 128;                     // positions per CTA: two 64-row pages (fewer, fatter CTAs launch faster
+                                                   // and leave half as many partials to merge)
+constexpr int kMlaThreads = 256;
 
 __device__ __forceinline__ void mla_cp16(void* smem_dst, const void* gsrc) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
@@ -27,12 +28,13 @@ __global__ void __launch_bounds__(kMlaThreads) attn_mla_kernel(const MlaParams p
     constexpr int DK = NOPE + R;
     constexpr int KP = DK / 8, VP = VD / 8;            // 16-byte pieces per row
     constexpr int NWARP = kMlaThreads / 32;
-    static_assert(DK % 32 == 0 && VD <= kMlaThreads && DK <= kMlaThreads, "layout");
+    static_assert(DK % 32 == 0 && kMlaThreads % VD == 0 && DK <= kMlaThreads, "layout");
 
     __shared__ __align__(16) uint16_t kbuf[kMlaSplit][DK];
     __shared__ __align__(16) uint16_t vbuf[kMlaSplit][VD];
     __shared__ float qraw[DK], qs[DK], kraw[R];
     __shared__ float sc[kMlaSplit];
+    __shared__ float pv_part[kMlaThreads / VD][VD];
     __shared__ float stat[2];
     __shared__ float mrg_w[64];
     __shared__ int s_last;
@@ -111,15 +113,30 @@ __global__ void __launch_bounds__(kMlaThreads) attn_mla_kernel(const MlaParams p
     }
     mla_cp_wait();
     __syncthreads();
+    trace_mark(p.trace, 0);
 
-    // ---- scores: one warp per row, DK/32 elements per lane ------------------------------------------
+    // ---- scores: a warp takes four rows at a time (their reductions interleave), DK/32 elements per lane -------
     const int n = p1 - p0;
-    for (int r = warp; r < n; r += NWARP) {
-        float s = 0.f;
+    {
+        float q[DK / 32];
 #pragma unroll
-        for (int i = 0; i < DK / 32; ++i) s = fmaf(qs[lane + 32 * i], bf16_bits_to_f32(kbuf[r][lane + 32 * i]), s);
-        s = warp_sum(s);
-        if (lane == 0) sc[r] = s;
+        for (int i = 0; i < DK / 32; ++i) q[i] = qs[lane + 32 * i];
+        for (int r0 = warp * 4; r0 < n; r0 += NWARP * 4) {
+            float sv[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                sv[t] = 0.f;
+                if (r0 + t < n) {
+#pragma unroll
+                    for (int i = 0; i < DK / 32; ++i) sv[t] = fmaf(q[i], bf16_bits_to_f32(kbuf[r0 + t][lane + 32 * i]), sv[t]);
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int t = 0; t < 4; ++t) sv[t] += __shfl_xor_sync(0xffffffffu, sv[t], o);
+            if (lane < 4 && r0 + lane < n) sc[r0 + lane] = lane == 0 ? sv[0] : lane == 1 ? sv[1] : lane == 2 ? sv[2] : sv[3];
+        }
     }
     __syncthreads();
     if (warp == 0) {
@@ -137,16 +154,21 @@ __global__ void __launch_bounds__(kMlaThreads) attn_mla_kernel(const MlaParams p
     }
     __syncthreads();
 
+    trace_mark(p.trace, 1);
     const int nsplit = p.nsplit;
+    {
+        // kMlaThreads / VD groups of threads share the rows: thread (d, grp) sums rows grp, grp + NG, ...
+        constexpr int NG = kMlaThreads / VD;
+        const int d = tid % VD, grp = tid / VD;
+        float o = 0.f;
+        for (int r = grp; r < n; r += NG) o = fmaf(sc[r], bf16_bits_to_f32(vbuf[r][d]), o);
+        pv_part[grp][d] = o;
+    }
+    __syncthreads();
     if (tid < VD) {
-        float o0 = 0.f, o1 = 0.f;
-        int r = 0;
-        for (; r + 1 < n; r += 2) {
-            o0 = fmaf(sc[r], bf16_bits_to_f32(vbuf[r][tid]), o0);
-            o1 = fmaf(sc[r + 1], bf16_bits_to_f32(vbuf[r + 1][tid]), o1);
-        }
-        if (r < n) o0 = fmaf(sc[r], bf16_bits_to_f32(vbuf[r][tid]), o0);
-        const float o = o0 + o1;
+        float o = 0.f;
+#pragma unroll
+        for (int g2 = 0; g2 < kMlaThreads / VD; ++g2) o += pv_part[g2][tid];          // fixed order
         if (n_active == 1) p.out[size_t(h) * VD + tid] = f32_to_bf16_bits(o / stat[1]);
         else p.part_o[(size_t(h) * nsplit + split) * VD + tid] = o;
     }
@@ -155,10 +177,12 @@ __global__ void __launch_bounds__(kMlaThreads) attn_mla_kernel(const MlaParams p
         p.part_ml[(size_t(h) * nsplit + split) * 2] = stat[0];
         p.part_ml[(size_t(h) * nsplit + split) * 2 + 1] = stat[1];
     }
+    trace_mark(p.trace, 2);
     __threadfence();
     __syncthreads();
     if (tid == 0) s_last = (atomicAdd(&p.counters[h], 1u) == unsigned(n_active - 1));
     __syncthreads();
+    trace_mark(p.trace, 3);
     if (!s_last) { trace_end(p.trace); return; }
     __threadfence();
 
@@ -179,7 +203,16 @@ __global__ void __launch_bounds__(kMlaThreads) attn_mla_kernel(const MlaParams p
         if (tid < VD) {
             const float* po = p.part_o + (size_t(h) * nsplit + s0) * VD + tid;
             float a = 0.f, b = 0.f;
-            for (int s = 0; s < ns; ++s) {
+            int s = 0;
+            for (; s + 4 <= ns; s += 4) {                      // independent loads, four in flight
+                const float v0 = __ldcg(po + size_t(s) * VD), v1 = __ldcg(po + size_t(s + 1) * VD);
+                const float v2 = __ldcg(po + size_t(s + 2) * VD), v3 = __ldcg(po + size_t(s + 3) * VD);
+                const float l0 = __ldcg(ml + 2 * s + 1), l1 = __ldcg(ml + 2 * s + 3);
+                const float l2 = __ldcg(ml + 2 * s + 5), l3 = __ldcg(ml + 2 * s + 7);
+                a = fmaf(mrg_w[s], v0, a); a = fmaf(mrg_w[s + 1], v1, a); a = fmaf(mrg_w[s + 2], v2, a); a = fmaf(mrg_w[s + 3], v3, a);
+                b = fmaf(mrg_w[s], l0, b); b = fmaf(mrg_w[s + 1], l1, b); b = fmaf(mrg_w[s + 2], l2, b); b = fmaf(mrg_w[s + 3], l3, b);
+            }
+            for (; s < ns; ++s) {
                 a = fmaf(mrg_w[s], __ldcg(po + size_t(s) * VD), a);
                 b = fmaf(mrg_w[s], __ldcg(ml + 2 * s + 1), b);
             }
