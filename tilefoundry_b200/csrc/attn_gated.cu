@@ -15,6 +15,7 @@ namespace tfb {
 
 constexpr int kGatedSplit = 64;
 constexpr int kGatedThreads = 256;
+constexpr int kGatedMergeBatch = 16;        // split partials one merging thread requests at once
 
 int attn_gated_splits(int max_ctx) { return (max_ctx + kGatedSplit - 1) / kGatedSplit; }
 
@@ -273,35 +274,30 @@ __global__ void __launch_bounds__(kGatedThreads) attn_gated_kernel(const GatedAt
         const int ns = min(64, n_active - s0);
         __syncthreads();
         for (int j = warp; j < GH; j += NWARP) {
-            const float* ml = p.part_ml + (size_t(head0 + j) * nsplit + s0) * 2;
-            const float m0 = lane < ns ? __ldcg(ml + 2 * lane) : -INFINITY;
-            const float m1 = lane + 32 < ns ? __ldcg(ml + 2 * (lane + 32)) : -INFINITY;
-            const float M = warp_max(fmaxf(m0, m1));
-            if (lane < ns) mrg_w[j][lane] = expf(m0 - M);
-            if (lane + 32 < ns) mrg_w[j][lane + 32] = expf(m1 - M);
-            if (lane == 0) stat_m[j] = M;
+            const float2* ml = reinterpret_cast<const float2*>(p.part_ml + (size_t(head0 + j) * nsplit + s0) * 2);
+            const float2 a0 = lane < ns ? __ldcg(ml + lane) : make_float2(-INFINITY, 0.f);
+            const float2 a1 = lane + 32 < ns ? __ldcg(ml + lane + 32) : make_float2(-INFINITY, 0.f);
+            const float M = warp_max(fmaxf(a0.x, a1.x));
+            const float w0 = lane < ns ? expf(a0.x - M) : 0.f;
+            const float w1 = lane + 32 < ns ? expf(a1.x - M) : 0.f;
+            mrg_w[j][lane] = w0;
+            mrg_w[j][lane + 32] = w1;
+            const float den_pass = warp_sum(fmaf(w0, a0.y, w1 * a1.y));
+            if (lane == 0) { stat_m[j] = M; stat_l[j] = den_pass; }
         }
         __syncthreads();
 #pragma unroll
         for (int t = 0; t < HG; ++t) {
             const int j = j0 + t, head = head0 + j;
             const float* po = p.part_o + (size_t(head) * nsplit + s0) * D + d;
-            const float* ml = p.part_ml + (size_t(head) * nsplit + s0) * 2;
-            float a = 0.f, b = 0.f;
-            int s = 0;
-            for (; s + 4 <= ns; s += 4) {              // independent loads, four in flight
-                const float v0 = __ldcg(po + size_t(s) * D), v1 = __ldcg(po + size_t(s + 1) * D);
-                const float v2 = __ldcg(po + size_t(s + 2) * D), v3 = __ldcg(po + size_t(s + 3) * D);
-                const float l0 = __ldcg(ml + 2 * s + 1), l1 = __ldcg(ml + 2 * s + 3);
-                const float l2 = __ldcg(ml + 2 * s + 5), l3 = __ldcg(ml + 2 * s + 7);
-                a = fmaf(mrg_w[j][s], v0, a); a = fmaf(mrg_w[j][s + 1], v1, a);
-                a = fmaf(mrg_w[j][s + 2], v2, a); a = fmaf(mrg_w[j][s + 3], v3, a);
-                b = fmaf(mrg_w[j][s], l0, b); b = fmaf(mrg_w[j][s + 1], l1, b);
-                b = fmaf(mrg_w[j][s + 2], l2, b); b = fmaf(mrg_w[j][s + 3], l3, b);
-            }
-            for (; s < ns; ++s) {
-                a = fmaf(mrg_w[j][s], __ldcg(po + size_t(s) * D), a);
-                b = fmaf(mrg_w[j][s], __ldcg(ml + 2 * s + 1), b);
+            float a = 0.f;
+            const float b = stat_l[j];
+            for (int s = 0; s < ns; s += kGatedMergeBatch) {   // kGatedMergeBatch independent loads in flight
+                float v[kGatedMergeBatch];
+#pragma unroll
+                for (int i = 0; i < kGatedMergeBatch; ++i) v[i] = (s + i < ns) ? __ldcg(po + size_t(s + i) * D) : 0.f;
+#pragma unroll
+                for (int i = 0; i < kGatedMergeBatch; ++i) a = fmaf(mrg_w[j][(s + i) & 63], v[i], a);
             }
             const float M = stat_m[j];
             const float newm = fmaxf(run_m[t], M);

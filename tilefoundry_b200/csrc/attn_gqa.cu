@@ -26,6 +26,7 @@ namespace tfb {
 
 constexpr int kSplitLen = 64;
 constexpr int kAttnThreads = 256;
+constexpr int kMergeBatch = 16;             // split partials one merging thread requests at once
 
 int attn_splits(int max_ctx) { return (max_ctx + kSplitLen - 1) / kSplitLen; }
 
@@ -262,14 +263,16 @@ __global__ void __launch_bounds__(kAttnThreads) attn_gqa_kernel(const AttnParams
         const int e = tid + t * kAttnThreads;
         if (e < G * D) {
             const int j = e / D, d = e % D;
-            float o0 = 0.f, o1 = 0.f;
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
             int r = 0;
-            for (; r + 1 < n; r += 2) {
+            for (; r + 3 < n; r += 4) {
                 o0 = fmaf(sc[j][r], bf16_bits_to_f32(vbuf[r][d]), o0);
                 o1 = fmaf(sc[j][r + 1], bf16_bits_to_f32(vbuf[r + 1][d]), o1);
+                o2 = fmaf(sc[j][r + 2], bf16_bits_to_f32(vbuf[r + 2][d]), o2);
+                o3 = fmaf(sc[j][r + 3], bf16_bits_to_f32(vbuf[r + 3][d]), o3);
             }
-            if (r < n) o0 = fmaf(sc[j][r], bf16_bits_to_f32(vbuf[r][d]), o0);
-            const float o = o0 + o1;
+            for (; r < n; ++r) o0 = fmaf(sc[j][r], bf16_bits_to_f32(vbuf[r][d]), o0);
+            const float o = (o0 + o1) + (o2 + o3);
             const int head = g * G + j;
             if (n_active == 1) p.out[size_t(head) * D + d] = f32_to_bf16_bits(o / stat_l[j]);
             else p.part_o[(size_t(head) * nsplit + split) * D + d] = o;
@@ -301,15 +304,19 @@ __global__ void __launch_bounds__(kAttnThreads) attn_gqa_kernel(const AttnParams
     for (int s0 = 0; s0 < n_active; s0 += 64) {              // 64 splits per pass (4096 positions)
         const int ns = min(64, n_active - s0);
         __syncthreads();
-        // per head: max over this pass, weights exp(m_s - M) into shared
+        // per head: max over this pass, weights exp(m_s - M) into shared, and the pass's denominator
         for (int j = warp; j < G; j += NWARP) {
             const float* ml = p.part_ml + (size_t(g * G + j) * nsplit + s0) * 2;
-            const float m0 = lane < ns ? __ldcg(ml + 2 * lane) : -INFINITY;
-            const float m1 = lane + 32 < ns ? __ldcg(ml + 2 * (lane + 32)) : -INFINITY;
-            const float M = warp_max(fmaxf(m0, m1));
-            if (lane < ns) mrg_w[j][lane] = __expf(m0 - M);
-            if (lane + 32 < ns) mrg_w[j][lane + 32] = __expf(m1 - M);
-            if (lane == 0) stat_m[j] = M;
+            const float2 a0 = lane < ns ? __ldcg(reinterpret_cast<const float2*>(ml) + lane) : make_float2(-INFINITY, 0.f);
+            const float2 a1 = lane + 32 < ns ? __ldcg(reinterpret_cast<const float2*>(ml) + lane + 32)
+                                             : make_float2(-INFINITY, 0.f);
+            const float M = warp_max(fmaxf(a0.x, a1.x));
+            const float w0 = lane < ns ? __expf(a0.x - M) : 0.f;
+            const float w1 = lane + 32 < ns ? __expf(a1.x - M) : 0.f;
+            mrg_w[j][lane] = w0;
+            mrg_w[j][lane + 32] = w1;
+            const float den_pass = warp_sum(fmaf(w0, a0.y, w1 * a1.y));
+            if (lane == 0) { stat_m[j] = M; stat_l[j] = den_pass; }
         }
         __syncthreads();
 #pragma unroll
@@ -319,22 +326,14 @@ __global__ void __launch_bounds__(kAttnThreads) attn_gqa_kernel(const AttnParams
                 const int j = e / D, d = e % D;
                 const int head = g * G + j;
                 const float* po = p.part_o + (size_t(head) * nsplit + s0) * D + d;
-                const float* ml = p.part_ml + (size_t(head) * nsplit + s0) * 2;
-                float a = 0.f, b = 0.f;
-                int s = 0;
-                for (; s + 4 <= ns; s += 4) {                  // independent loads, four in flight
-                    const float v0 = __ldcg(po + size_t(s) * D), v1 = __ldcg(po + size_t(s + 1) * D);
-                    const float v2 = __ldcg(po + size_t(s + 2) * D), v3 = __ldcg(po + size_t(s + 3) * D);
-                    const float l0 = __ldcg(ml + 2 * s + 1), l1 = __ldcg(ml + 2 * s + 3);
-                    const float l2 = __ldcg(ml + 2 * s + 5), l3 = __ldcg(ml + 2 * s + 7);
-                    a = fmaf(mrg_w[j][s], v0, a); a = fmaf(mrg_w[j][s + 1], v1, a);
-                    a = fmaf(mrg_w[j][s + 2], v2, a); a = fmaf(mrg_w[j][s + 3], v3, a);
-                    b = fmaf(mrg_w[j][s], l0, b); b = fmaf(mrg_w[j][s + 1], l1, b);
-                    b = fmaf(mrg_w[j][s + 2], l2, b); b = fmaf(mrg_w[j][s + 3], l3, b);
-                }
-                for (; s < ns; ++s) {
-                    a = fmaf(mrg_w[j][s], __ldcg(po + size_t(s) * D), a);
-                    b = fmaf(mrg_w[j][s], __ldcg(ml + 2 * s + 1), b);
+                float a = 0.f;
+                const float b = stat_l[j];
+                for (int s = 0; s < ns; s += kMergeBatch) {    // kMergeBatch independent loads in flight
+                    float v[kMergeBatch];
+#pragma unroll
+                    for (int i = 0; i < kMergeBatch; ++i) v[i] = (s + i < ns) ? __ldcg(po + size_t(s + i) * D) : 0.f;
+#pragma unroll
+                    for (int i = 0; i < kMergeBatch; ++i) a = fmaf(mrg_w[j][(s + i) & 63], v[i], a);
                 }
                 // fold this pass into the running (max, num, den)
                 const float M = stat_m[j];
