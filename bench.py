@@ -325,6 +325,42 @@ def run_batch32_projection(args):
                       "batch": M, "dtype": "bf16", "peak_GBs": peak, "peak_kind": kind, "shapes": out}))
 
 
+def run_batch_decode(args):
+    """Several sequences at once (config 1's batch-32 clause): `--batch B` independent sequences of the Qwen3-1.7B
+    architecture, each a 64-token random prompt walked token by token and then `--steps` greedy tokens; every
+    projection on the tensor cores, the KV cache of every sequence read once per step.  One JSON line: total
+    tokens/s over all sequences and the fraction of the measured HBM peak the step's algorithmic bytes reach."""
+    from tilefoundry_b200.engine.qwen3_batch import Qwen3BatchSession
+    from tilefoundry_b200.runtime import DictResource
+
+    work = Workload("qwen3_1_7b")
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    B, steps = args.batch, args.steps
+    max_ctx = PROMPT_TOKENS + steps + 8
+    sess = Qwen3BatchSession(work.cfg, DictResource(work.device_weights(dev)), batch=B, max_ctx=max_ctx, device=dev)
+    prompts = torch.randint(0, work.cfg.vocab_size, (B, PROMPT_TOKENS), generator=torch.Generator().manual_seed(1))
+    sess.generate(prompts, 8)                                   # capture + warm-up
+    sampler = ClockSampler(0)
+    gen = sess.generate(prompts, steps)
+    clocks = sampler.stop()
+    W, kv = sess.weight_bytes(), sess.kv_bytes_per_position()
+    # bytes(t) = weights + batch * kv_per_position * (context read + the entry written)
+    total_bytes = sum(W + B * kv * (PROMPT_TOKENS + t + 1) for t in range(steps))
+    peak, kind = peaks()
+    achieved = total_bytes / gen.seconds / 1e9
+    print(json.dumps({
+        "mode": "batch_decode", "metric": "decode tok/s, all sequences", "value": B * steps / gen.seconds,
+        "unit": "tok/s", "batch": B, "steps": steps, "ms_per_step": gen.seconds * 1e3 / steps,
+        "prompt_ms_per_step": gen.prompt_seconds * 1e3 / max(gen.prompt_steps - 1, 1),
+        "dtype": "bf16", "data": "synthetic", "gpu_launches": sess.launches_per_step * steps,
+        "config": {"workload": work.describe.replace("batch 1", f"batch {B}"), "l2": "inputs larger than L2"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": kind, "weights_bytes_per_step": W, "kv_bytes_per_step_at_end":
+                     B * kv * (PROMPT_TOKENS + steps)},
+        "clocks": clocks}))
+
+
 def run_ours(args):
     import torch.distributed as dist
 
@@ -471,6 +507,9 @@ def main():
     ap.add_argument("--batch32-projection", action="store_true",
                     help="time the batch-32 tensor-core projection (tcgen05) on this configuration's projection shapes, "
                          "print one JSON line and exit")
+    ap.add_argument("--batch", type=int, default=1,
+                    help="decode this many independent Qwen3-1.7B sequences per step (2..32) on the tensor-core "
+                         "projections, print one JSON line and exit")
     ap.add_argument("--dominant-only", action="store_true",
                     help="build the session, time only the dominant kernel over every layer's weights, print it and exit "
                          "(the small case a profiler capture of that kernel runs)")
@@ -479,6 +518,8 @@ def main():
         run_reference(args)
     elif args.batch32_projection:
         run_batch32_projection(args)
+    elif args.batch > 1:
+        run_batch_decode(args)
     else:
         run_ours(args)
 

@@ -209,6 +209,10 @@ typedef struct {
     int32_t pdl;
     const void* prefetch;
     uint64_t prefetch_bytes;
+    /* batch > 1: that many independent sequences in one launch.  qkv [batch][(hq+2hkv)*d], out [batch][hq*d],
+     * pos (and rope_pos) [batch], block_table [batch][table_len] into the shared pools, k_new_out/v_new_out
+     * [batch][hkv*d], part_o/part_ml/counters sized batch times the single-sequence scratch. */
+    int32_t batch;
 } tfb_attn_gqa_args;
 TFB_API int32_t tfb_attn_splits(int32_t max_ctx);
 TFB_API int tfb_attn_gqa_decode(const tfb_attn_gqa_args* args, tfb_stream_t stream);
@@ -548,9 +552,70 @@ typedef struct {
     const void* w; const void* x; const void* residual; void* y;
     float* partial; uint32_t* tickets; uint32_t* status;
     int32_t m, n, k, pdl;
+    /* swiglu != 0: w is [2n, k] = n gate rows then n up rows, y[M, n] = bf16(silu(bf16(x.gate^T)) * bf16(x.up^T))
+     * (TFB_EPI_SWIGLU's rounding); n a multiple of 64, no residual; partial: f32
+     * [tfb_gemm_small_m_swiglu_splits(n, k) * M * 2n], tickets: u32 [n/64]. */
+    int32_t swiglu;
 } tfb_gemm_small_m_args;
 TFB_API int32_t tfb_gemm_small_m_splits(int32_t n, int32_t k);
+TFB_API int32_t tfb_gemm_small_m_swiglu_splits(int32_t n, int32_t k);
 TFB_API int tfb_gemm_small_m(const tfb_gemm_small_m_args* args, tfb_stream_t stream);
+
+/* ---- Qwen3-architecture decode step for several sequences (batch <= 32) ------------------------------------
+ * One token for each of `batch` independent sequences: every projection runs once on the tensor cores for the
+ * whole batch (tfb_gemm_small_m), attention once per layer with one CTA set per sequence (tfb_attn_gqa_decode
+ * with batch), norms / embedding / pick row-wise.  Per sequence the arithmetic and its rounding points are those
+ * of tfb_qwen3_decode_step; only the order of the f32 sums inside a projection differs (tensor-core tiles).
+ * The batch form of examples/qwen3_1_7b-tilelang/fast/engine.py:189-271 (the reference decodes one sequence).
+ * Launches per step: 4 + 7 * n_layers. */
+typedef struct {
+    const void* gamma_in;
+    const void* w_qkv;      /* [(hq+2hkv)*d, hidden] */
+    const void* gamma_q;
+    const void* gamma_k;
+    const void* w_o;        /* [hidden, hq*d] */
+    const void* gamma_post;
+    const void* w_gate_up;  /* [2*inter, hidden]: gate rows, then up rows */
+    const void* w_down;     /* [hidden, inter] */
+    void* k_pool;           /* pages of every sequence */
+    void* v_pool;
+} tfb_qwen3_batch_layer;
+typedef struct {
+    const tfb_qwen3_batch_layer* layers; /* host array [n_layers] */
+    int32_t n_layers, batch, hidden, hq, hkv, d, inter, pdl;
+    int64_t vocab;
+    float eps, scale;
+    const void* w_embed;    /* [vocab, hidden] */
+    const void* gamma_final;
+    const void* w_head;     /* [vocab, hidden] */
+    const void* cos_table;
+    const void* sin_table;
+    int32_t max_pos, page_size, table_len, max_ctx;
+    const int32_t* block_table; /* [batch][table_len] */
+    int64_t* tokens;        /* [batch][max_tokens]: prompt, then the picked tokens */
+    int32_t* pos;           /* [batch]: advanced by the step */
+    int32_t n_prompt, max_tokens;
+    void* hidden_buf;       /* [batch][hidden] bf16 residual stream */
+    void* norm_buf;         /* [batch][hidden] */
+    void* qkv_buf;          /* [batch][(hq+2hkv)*d] */
+    void* attn_buf;         /* [batch][hq*d] */
+    void* act_buf;          /* [batch][inter] */
+    void* logits;           /* [batch][vocab] bf16 (required: the pick reads it) */
+    float* part_o;          /* attention split scratch, batch times the single-sequence size */
+    float* part_ml;
+    uint32_t* counters;     /* [batch*hkv + batch] zeroed once: attention tickets, then pick tickets */
+    float* gemm_partial;    /* f32 [tfb_qwen3_batch_partial_floats(...)] */
+    uint32_t* gemm_tickets; /* u32 [tfb_qwen3_batch_tickets(...)] zeroed once */
+    uint32_t* status;       /* u32 zeroed once; non-zero after a step: a bounded wait gave up, outputs invalid */
+    float* pick_val;        /* f32 [batch * 8] */
+    int32_t* pick_idx;      /* i32 [batch * 8] */
+    int64_t* picked;        /* optional [batch]: the token each sequence picked, whatever its prompt says */
+    void* hidden_trace;     /* optional [n_layers+1][batch][hidden] bf16 */
+} tfb_qwen3_batch_step_args;
+TFB_API int64_t tfb_qwen3_batch_partial_floats(int32_t batch, int32_t hidden, int32_t hq, int32_t hkv, int32_t d,
+                                               int32_t inter, int64_t vocab);
+TFB_API int32_t tfb_qwen3_batch_tickets(int32_t hidden, int32_t hq, int32_t hkv, int32_t d, int32_t inter, int64_t vocab);
+TFB_API int tfb_qwen3_batch_decode_step(const tfb_qwen3_batch_step_args* args, tfb_stream_t stream);
 
 /* ================= f32-activation family (Qwen3.5-35B-A3B) =================
  * The reference's Qwen3.5 example keeps activations, recurrent state and KV cache in f32 and its contracted

@@ -177,14 +177,19 @@ int32_t tfb_gemm_small_m_splits(int32_t n, int32_t k) {
     if (n <= 0 || k < 64) return 0;
     return tfb::gemm_tc_splits(n, k);
 }
+int32_t tfb_gemm_small_m_swiglu_splits(int32_t n, int32_t k) {
+    if (n <= 0 || k < 64) return 0;
+    return tfb::gemm_tc_splits_swiglu(n, k);
+}
 
 int tfb_gemm_small_m(const tfb_gemm_small_m_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->w && a->x && a->y && a->status, TFB_EINVAL);
     TFB_REQUIRE(a->m >= 1 && a->m <= 32 && a->n > 0 && a->k >= 64 && a->k % 64 == 0, TFB_EINVAL);
     TFB_REQUIRE(aligned16(a->w) && aligned16(a->x), TFB_EALIGN);
+    TFB_REQUIRE(a->swiglu == 0 || (a->n % 64 == 0 && !a->residual), TFB_EINVAL);
     tfb::TcParams p = {};
-    p.M = a->m; p.N = a->n; p.K = a->k;
-    p.splits = tfb::gemm_tc_splits(a->n, a->k);
+    p.M = a->m; p.N = a->n; p.K = a->k; p.swiglu = a->swiglu != 0;
+    p.splits = p.swiglu ? tfb::gemm_tc_splits_swiglu(a->n, a->k) : tfb::gemm_tc_splits(a->n, a->k);
     TFB_REQUIRE(p.splits == 1 || (a->partial && a->tickets), TFB_EINVAL);
     p.partial = a->partial; p.tickets = a->tickets; p.status = a->status;
     p.y = static_cast<uint16_t*>(a->y); p.residual = static_cast<const uint16_t*>(a->residual);
@@ -286,6 +291,11 @@ int tfb_attn_gqa_decode(const tfb_attn_gqa_args* a, tfb_stream_t stream) {
     p.prefetch = a->prefetch;
     p.prefetch_bytes = a->prefetch_bytes;
     p.trace = next_trace();
+    p.batch = a->batch > 1 ? a->batch : 1;
+    p.qkv_stride = (a->hq + 2 * a->hkv) * a->d;
+    p.out_stride = a->hq * a->d;
+    p.bt_stride = a->table_len;
+    TFB_REQUIRE(p.batch <= 65535, TFB_EINVAL);
     const int G = a->hq / a->hkv;
     TFB_REQUIRE(G == 1 || G == 2 || (G == 4 && a->d == 128), TFB_EINVAL);
     return done(tfb::attn_gqa_dispatch(p, S(stream), a->pdl != 0));
@@ -293,6 +303,7 @@ int tfb_attn_gqa_decode(const tfb_attn_gqa_args* a, tfb_stream_t stream) {
 
 int tfb_attn_gqa_decode_noalloc(const tfb_attn_gqa_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->max_ctx > 0 && a->hq > 0, TFB_EINVAL);
+    TFB_REQUIRE(a->batch <= 1, TFB_ECAPACITY);               // the built-in scratch holds one sequence
     tfb_attn_gqa_args b = *a;
     bool fits = false;
     const cudaError_t e = tfb::attn_static_scratch(a->hq, tfb::attn_splits(a->max_ctx), a->d, &b.part_o, &b.part_ml,

@@ -41,7 +41,7 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 template <int D, int G>
-__global__ void __launch_bounds__(kAttnThreads) attn_gqa_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kAttnThreads) attn_gqa_kernel(AttnParams p) {
     constexpr int LPP = D / 8;                 // lanes that share one position's row (16 B each)
     constexpr int NSG = kAttnThreads / LPP;    // position sub-groups in the CTA
     constexpr int NWARP = kAttnThreads / 32;
@@ -61,6 +61,19 @@ __global__ void __launch_bounds__(kAttnThreads) attn_gqa_kernel(const AttnParams
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = blockIdx.x, split = blockIdx.y;
     const int p0 = split * kSplitLen;
+    if (blockIdx.z != 0) {                       // sequence blockIdx.z of a batch: shift every per-sequence pointer
+        const size_t b = blockIdx.z;
+        p.qkv += b * p.qkv_stride;
+        p.out += b * p.out_stride;
+        p.block_table += b * p.bt_stride;
+        p.pos += b;
+        if (p.rope_pos) p.rope_pos += b;
+        p.part_o += b * p.hq * p.nsplit * D;
+        p.part_ml += b * p.hq * p.nsplit * 2;
+        p.counters += b * p.hkv;
+        if (p.k_new_out) p.k_new_out += b * p.hkv * D;
+        if (p.v_new_out) p.v_new_out += b * p.hkv * D;
+    }
 
     trace_start(p.trace);
     // ---- before the dependency wait: start fetching the cached rows ---------------------
@@ -360,7 +373,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_gqa_kernel(const AttnParams
 
 cudaError_t attn_gqa_dispatch(const AttnParams& p, cudaStream_t stream, bool pdl) {
     const int G = p.hq / p.hkv;
-    const dim3 grid(p.hkv, p.nsplit), block(kAttnThreads);
+    const dim3 grid(p.hkv, p.nsplit, p.batch > 1 ? p.batch : 1), block(kAttnThreads);
 #define TFB_ATTN(DD, GG)                                                                                  \
     if (p.d == DD && G == GG) {                                                                           \
         static bool once = false;                                                                         \

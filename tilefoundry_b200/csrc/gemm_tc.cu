@@ -15,6 +15,13 @@
 // that a 6144 x 2048 projection (48 row tiles) still fills every SM; the splits' f32 partials are added in
 // fixed order by the last CTA of a row tile (atomic ticket, no spinning): deterministic.
 //
+// SwiGLU form (p.swiglu): a row tile holds 64 gate rows and the 64 up rows of the same outputs (two 64-row TMA
+// boxes from a [gate; up] matrix), so one accumulator carries both halves; the up half crosses to the gate half's
+// threads through shared memory and y = bf16(silu(bf16 g)) * bf16 u is written, rounding as the batch-1 epilogue.
+//
+// The weight tiles of the first ring pass do not depend on the kernel before: the producer requests them before
+// griddepcontrol.wait and only the token tiles after it.
+//
 // Every mbarrier wait is bounded; a timeout sets *status, and the CTA still frees its tensor memory.
 //
 // HBM-bound: algorithmic bytes per launch = N*K*2 (weights) + M*K*2 per row tile from L2.
@@ -74,7 +81,38 @@ struct TcSmemTail {
     uint64_t full[TC_STAGES], empty[TC_STAGES], accum;
     uint32_t tmem_base;
     int aborted, last;
+    float exch[64][33];                                                 // SwiGLU: the up half of a finished tile
 };
+
+// The finished f32 sums of tile row r (0..127) for the M tokens -> y.  Called by all 128 epilogue threads.
+__device__ __forceinline__ void tc_finish_row(const TcParams& p, TcSmemTail* t, int tile, int r, const float (&acc)[32]) {
+    if (p.swiglu) {
+        if (r >= 64) {
+#pragma unroll
+            for (int m = 0; m < 32; ++m) t->exch[r - 64][m] = acc[m];
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");                  // the four epilogue warps only
+        const int j = tile * 64 + r;
+        if (r < 64 && j < p.N) {
+#pragma unroll
+            for (int m = 0; m < 32; ++m)
+                if (m < p.M) {
+                    const float g = round_bf16(acc[m]), u = round_bf16(t->exch[r][m]);
+                    p.y[size_t(m) * p.N + j] = f32_to_bf16_bits(round_bf16(silu_f32(g)) * u);
+                }
+        }
+        return;
+    }
+    const int n = tile * TC_BM + r;
+    if (n >= p.N) return;
+#pragma unroll
+    for (int m = 0; m < 32; ++m)
+        if (m < p.M) {
+            float o = acc[m];
+            if (p.residual) o = bf16_bits_to_f32(p.residual[size_t(m) * p.N + n]) + round_bf16(acc[m]);
+            p.y[size_t(m) * p.N + n] = f32_to_bf16_bits(o);
+        }
+}
 
 __global__ void __launch_bounds__(TC_THREADS, 2) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x, const TcParams p) {
@@ -106,15 +144,33 @@ __global__ void __launch_bounds__(TC_THREADS, 2) gemm_tc_kernel(const __grid_con
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = t->tmem_base;
     pdl_trigger();
-    pdl_wait();
+    const bool producer = (warp == 0 && lane == 0);
+    if (!producer) pdl_wait();
 
     if (warp == 0) {
         if (lane == 0) {                                                // ---- TMA producer ----
-            for (int i = 0; i < nsteps; ++i) {
+            auto load_w = [&](int i, int s) {
+                const int kx = (k_begin + i) * TC_BK;
+                if (p.swiglu) {                                         // 64 gate rows, then the 64 up rows of the same outputs
+                    tma_load_2d(a_tiles + s * TC_A_BYTES, &map_w, &t->full[s], kx, tile * 64);
+                    tma_load_2d(a_tiles + s * TC_A_BYTES + TC_A_BYTES / 2, &map_w, &t->full[s], kx, p.N + tile * 64);
+                } else {
+                    tma_load_2d(a_tiles + s * TC_A_BYTES, &map_w, &t->full[s], kx, tile * TC_BM);
+                }
+            };
+            const int pre = min(nsteps, TC_STAGES);
+            for (int i = 0; i < pre; ++i) {                             // weights never depend on the kernel before
+                mbar_expect_tx(&t->full[i], TC_A_BYTES + TC_B_BYTES);
+                load_w(i, i);
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i)
+                tma_load_2d(b_tiles + i * TC_B_BYTES, &map_x, &t->full[i], (k_begin + i) * TC_BK, 0);
+            for (int i = pre; i < nsteps; ++i) {
                 const int s = i % TC_STAGES;
                 if (!mbar_wait(&t->empty[s], ((i / TC_STAGES) & 1) ^ 1)) { t->aborted = 1; atomicExch(p.status, 1u); break; }
                 mbar_expect_tx(&t->full[s], TC_A_BYTES + TC_B_BYTES);
-                tma_load_2d(a_tiles + s * TC_A_BYTES, &map_w, &t->full[s], (k_begin + i) * TC_BK, tile * TC_BM);
+                load_w(i, s);
                 tma_load_2d(b_tiles + s * TC_B_BYTES, &map_x, &t->full[s], (k_begin + i) * TC_BK, 0);
             }
         }
@@ -157,20 +213,15 @@ __global__ void __launch_bounds__(TC_THREADS, 2) gemm_tc_kernel(const __grid_con
                          : "r"(taddr) : "memory");
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         }
-        if (n < p.N) {
-            if (p.splits == 1) {
+        if (p.splits == 1) {
+            float acc[32];
 #pragma unroll
-                for (int m = 0; m < 32; ++m)
-                    if (m < p.M) {
-                        float o = __uint_as_float(v[m]);
-                        if (p.residual) o = bf16_bits_to_f32(p.residual[size_t(m) * p.N + n]) + round_bf16(o);
-                        p.y[size_t(m) * p.N + n] = f32_to_bf16_bits(o);
-                    }
-            } else {
+            for (int m = 0; m < 32; ++m) acc[m] = __uint_as_float(v[m]);
+            tc_finish_row(p, t, tile, quad * 32 + lane, acc);
+        } else if (n < p.ntot) {
 #pragma unroll
-                for (int m = 0; m < 32; ++m)
-                    if (m < p.M) p.partial[(size_t(split) * p.M + m) * p.N + n] = __uint_as_float(v[m]);
-            }
+            for (int m = 0; m < 32; ++m)
+                if (m < p.M) p.partial[(size_t(split) * p.M + m) * p.ntot + n] = __uint_as_float(v[m]);
         }
     }
 
@@ -187,27 +238,21 @@ __global__ void __launch_bounds__(TC_THREADS, 2) gemm_tc_kernel(const __grid_con
         __syncthreads();
         if (t->last && warp >= 2) {
             __threadfence();
-            const int n = tile * TC_BM + (warp & 3) * 32 + lane;
-            if (n < p.N) {
-                float acc[32];
+            const int r = (warp & 3) * 32 + lane, n = tile * TC_BM + r;
+            float acc[32];
 #pragma unroll
-                for (int m = 0; m < 32; ++m) acc[m] = 0.f;
+            for (int m = 0; m < 32; ++m) acc[m] = 0.f;
+            if (n < p.ntot) {
                 for (int s = 0; s < p.splits; ++s) {                    // fixed order; 32 independent loads in flight
-                    const float* src = p.partial + size_t(s) * p.M * p.N + n;
+                    const float* src = p.partial + size_t(s) * p.M * p.ntot + n;
                     float v[32];
 #pragma unroll
-                    for (int m = 0; m < 32; ++m) v[m] = (m < p.M) ? __ldcg(src + size_t(m) * p.N) : 0.f;
+                    for (int m = 0; m < 32; ++m) v[m] = (m < p.M) ? __ldcg(src + size_t(m) * p.ntot) : 0.f;
 #pragma unroll
                     for (int m = 0; m < 32; ++m) acc[m] += v[m];
                 }
-#pragma unroll
-                for (int m = 0; m < 32; ++m)
-                    if (m < p.M) {
-                        float o = acc[m];
-                        if (p.residual) o = bf16_bits_to_f32(p.residual[size_t(m) * p.N + n]) + round_bf16(acc[m]);
-                        p.y[size_t(m) * p.N + n] = f32_to_bf16_bits(o);
-                    }
             }
+            tc_finish_row(p, t, tile, r, acc);
             if (threadIdx.x == 64) p.tickets[tile] = 0;
         }
     }
@@ -242,10 +287,13 @@ static bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int 
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int gemm_tc_splits(int n, int k) {
+static int splits_for_tiles(int tiles, int k);
+int gemm_tc_splits(int n, int k) { return splits_for_tiles((n + TC_BM - 1) / TC_BM, k); }
+int gemm_tc_splits_swiglu(int n, int k) { return splits_for_tiles((n + 63) / 64, k); }
+static int splits_for_tiles(int tiles, int k) {
     int sms = 148, dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int tiles = (n + TC_BM - 1) / TC_BM, ksteps = k / TC_BK;
+    const int ksteps = k / TC_BK;
     int splits = 2 * sms / tiles;                      // two CTAs (each a 4-stage, 80 KB ring) share an SM
     if (splits < 1) splits = 1;
     if (splits > ksteps) splits = ksteps;
@@ -255,8 +303,12 @@ int gemm_tc_splits(int n, int k) {
 
 cudaError_t gemm_tc_launch(const void* w, const void* x, TcParams p, cudaStream_t stream, bool pdl) {
     CUtensorMap map_w, map_x;
-    if (!make_map(&map_w, w, p.N, p.K, TC_BM) || !make_map(&map_x, x, p.M, p.K, TC_BN)) return cudaErrorInvalidValue;
+    const int w_rows = p.swiglu ? 2 * p.N : p.N;
+    if (!make_map(&map_w, w, w_rows, p.K, p.swiglu ? 64 : TC_BM) || !make_map(&map_x, x, p.M, p.K, TC_BN))
+        return cudaErrorInvalidValue;
     p.ksteps = p.K / TC_BK;
+    const int tiles = p.swiglu ? (p.N + 63) / 64 : (p.N + TC_BM - 1) / TC_BM;
+    p.ntot = p.swiglu ? tiles * TC_BM : p.N;
     const size_t smem = 1024 + size_t(TC_STAGES) * (TC_A_BYTES + TC_B_BYTES) + sizeof(TcSmemTail);
     static bool once = false;
     if (!once) {
@@ -264,7 +316,7 @@ cudaError_t gemm_tc_launch(const void* w, const void* x, TcParams p, cudaStream_
         if (e != cudaSuccess) return e;
         once = true;
     }
-    const dim3 grid((p.N + TC_BM - 1) / TC_BM, p.splits), block(TC_THREADS);
+    const dim3 grid(tiles, p.splits), block(TC_THREADS);
     return launch_kernel(gemm_tc_kernel, grid, block, smem, stream, pdl, map_w, map_x, p);
 }
 

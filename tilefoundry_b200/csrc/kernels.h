@@ -66,6 +66,9 @@ struct AttnParams {
     const void* prefetch;
     unsigned long long prefetch_bytes;
     unsigned long long* trace;
+    // several sequences in one launch (blockIdx.z = sequence): element strides of qkv / out, row stride of the
+    // block table; pos, rope_pos and the split scratch are indexed by sequence.  batch <= 1: one sequence.
+    int batch, qkv_stride, out_stride, bt_stride;
 };
 int attn_splits(int max_ctx);
 cudaError_t attn_gqa_dispatch(const AttnParams& p, cudaStream_t stream, bool pdl);
@@ -315,9 +318,20 @@ struct TcParams {
     unsigned* tickets;           // u32 [ceil(N/128)], zero before the first launch (splits > 1)
     unsigned* status;            // u32, set non-zero if a bounded wait gave up
     int M, N, K, ksteps, splits;
+    int ntot;                    // accumulator rows over all tiles: N, or tiles * 128 in the SwiGLU form
+    int swiglu;                  // 1: w holds [gate rows; up rows] (2N rows), y[M][N] = bf16(silu(bf16 g)) * bf16 u
 };
 int gemm_tc_splits(int n, int k);
+int gemm_tc_splits_swiglu(int n, int k);
 cudaError_t gemm_tc_launch(const void* w, const void* x, TcParams p, cudaStream_t stream, bool pdl);
+
+// ---- row-wise kernels of the several-sequence step (batch.cu) ----
+cudaError_t embed_rows_launch(const uint16_t* table, const long long* tokens, const int* pos, int max_tokens,
+                              uint16_t* out, int rows, int hidden, long long vocab, cudaStream_t stream, bool pdl);
+int pick_rows_parts();
+cudaError_t pick_rows_launch(const uint16_t* logits, int rows, int vocab, long long* tokens, int* pos, int n_prompt,
+                             int max_tokens, long long* picked, float* part_val, int* part_idx, unsigned* tickets,
+                             cudaStream_t stream, bool pdl);
 
 // ---- exchange steps over NVLink peer memory (collective.cu) ----
 constexpr int kMaxPeers = 8;

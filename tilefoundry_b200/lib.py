@@ -44,7 +44,7 @@ class AttnGqaArgs(C.Structure):
                 ("hq", _i32), ("hkv", _i32), ("d", _i32), ("rotary_dim", _i32),
                 ("page_size", _i32), ("table_len", _i32), ("max_ctx", _i32), ("max_pos", _i32),
                 ("eps", _f32), ("scale", _f32), ("norm_mode", _i32), ("pdl", _i32),
-                ("prefetch", _vp), ("prefetch_bytes", _u64)]
+                ("prefetch", _vp), ("prefetch_bytes", _u64), ("batch", _i32)]
 
 
 class Qwen3Layer(C.Structure):
@@ -71,7 +71,25 @@ class GemvChainArgs(C.Structure):
 
 class GemmSmallMArgs(C.Structure):
     _fields_ = [("w", _vp), ("x", _vp), ("residual", _vp), ("y", _vp), ("partial", _vp), ("tickets", _vp), ("status", _vp),
-                ("m", _i32), ("n", _i32), ("k", _i32), ("pdl", _i32)]
+                ("m", _i32), ("n", _i32), ("k", _i32), ("pdl", _i32), ("swiglu", _i32)]
+
+
+class Qwen3BatchLayer(C.Structure):
+    _fields_ = [(n, _vp) for n in ("gamma_in", "w_qkv", "gamma_q", "gamma_k", "w_o", "gamma_post", "w_gate_up",
+                                   "w_down", "k_pool", "v_pool")]
+
+
+class Qwen3BatchStepArgs(C.Structure):
+    _fields_ = [("layers", C.POINTER(Qwen3BatchLayer)),
+                ("n_layers", _i32), ("batch", _i32), ("hidden", _i32), ("hq", _i32), ("hkv", _i32), ("d", _i32),
+                ("inter", _i32), ("pdl", _i32), ("vocab", _i64), ("eps", _f32), ("scale", _f32),
+                ("w_embed", _vp), ("gamma_final", _vp), ("w_head", _vp), ("cos_table", _vp), ("sin_table", _vp),
+                ("max_pos", _i32), ("page_size", _i32), ("table_len", _i32), ("max_ctx", _i32),
+                ("block_table", _vp), ("tokens", _vp), ("pos", _vp), ("n_prompt", _i32), ("max_tokens", _i32),
+                ("hidden_buf", _vp), ("norm_buf", _vp), ("qkv_buf", _vp), ("attn_buf", _vp), ("act_buf", _vp),
+                ("logits", _vp), ("part_o", _vp), ("part_ml", _vp), ("counters", _vp), ("gemm_partial", _vp),
+                ("gemm_tickets", _vp), ("status", _vp), ("pick_val", _vp), ("pick_idx", _vp), ("picked", _vp),
+                ("hidden_trace", _vp)]
 
 
 class MoeAllreduceArgs(C.Structure):
@@ -214,7 +232,11 @@ SYMBOLS = {
     "tfb_gemv_pair": (_i32, [C.POINTER(GemvArgs), C.POINTER(GemvArgs), _vp]),
     "tfb_gemv_chain": (_i32, [C.POINTER(GemvChainArgs), _vp]),
     "tfb_gemm_small_m_splits": (_i32, [_i32, _i32]),
+    "tfb_gemm_small_m_swiglu_splits": (_i32, [_i32, _i32]),
     "tfb_gemm_small_m": (_i32, [C.POINTER(GemmSmallMArgs), _vp]),
+    "tfb_qwen3_batch_partial_floats": (_i64, [_i32, _i32, _i32, _i32, _i32, _i32, _i64]),
+    "tfb_qwen3_batch_tickets": (_i32, [_i32, _i32, _i32, _i32, _i32, _i64]),
+    "tfb_qwen3_batch_decode_step": (_i32, [C.POINTER(Qwen3BatchStepArgs), _vp]),
     "tfb_lm_head_scratch_entries": (_i32, [_i32]),
     "tfb_lm_head_argmax": (_i32, [C.POINTER(LmHeadArgs), _vp]),
     "tfb_attn_splits": (_i32, [_i32]),
