@@ -305,10 +305,8 @@ def run_batch32_projection(args):
         x = torch.randn(M, k, device=dev).to(torch.bfloat16)
         y = torch.empty(M, n, device=dev, dtype=torch.bfloat16)
         splits = lib.load().tfb_gemm_small_m_splits(n, k)
-        partial = torch.empty(splits * M * n, device=dev, dtype=torch.float32)
-        tickets = torch.zeros((n + 127) // 128, device=dev, dtype=torch.int32)
         status = torch.zeros(1, device=dev, dtype=torch.int32)
-        calls = [lib.GemmSmallMArgs(w=lib.ptr(w), x=lib.ptr(x), y=lib.ptr(y), partial=lib.ptr(partial), tickets=lib.ptr(tickets),
+        calls = [lib.GemmSmallMArgs(w=lib.ptr(w), x=lib.ptr(x), y=lib.ptr(y),
                                     status=lib.ptr(status), m=M, n=n, k=k, pdl=1) for w in W]
 
         def launches():

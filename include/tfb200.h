@@ -544,17 +544,18 @@ TFB_API int tfb_gemv_chain(const tfb_gemv_chain_args* args, tfb_stream_t stream)
 /* ---- small-batch projection on the tensor cores (tcgen05 + TMEM + TMA) -----------------------------------
  * y[M, N] = x[M, K] . w[N, K]^T (+ residual), 1 <= M <= 32 tokens, bf16 in / f32 accumulate / bf16 out; w in the
  * same [out, in] layout tfb_gemv reads.  With residual: y = bf16(residual + bf16(acc)) (TFB_EPI_RESIDUAL's
- * rounding).  K a multiple of 64; w, x 16-byte aligned.  K is split over tfb_gemm_small_m_splits(N, K) CTAs per
- * 128-row tile; partial: f32 [splits * M * N] scratch, tickets: u32 [ceil(N/128)] zeroed once, status: u32 set
- * non-zero if a bounded wait gave up (outputs then invalid; nothing hangs).  The batch-32 form of the projections of
- * examples/qwen3_1_7b-tilelang/fast/kernels.py:124-260 (the reference runs batch 1 only). */
+ * rounding).  K a multiple of 64; w, x 16-byte aligned.  K is split over the tfb_gemm_small_m_splits(N, K) CTAs
+ * (1, 2, 4 or 8) of a thread-block cluster and the partial tiles are added in fixed order through distributed
+ * shared memory: deterministic, nothing spins, no scratch in global memory (partial and tickets are not used and
+ * may be NULL).  status: u32 set non-zero if a bounded mbarrier wait gave up (outputs then invalid; nothing hangs).
+ * The batch-32 form of the projections of examples/qwen3_1_7b-tilelang/fast/kernels.py:124-260 (the reference
+ * runs batch 1 only). */
 typedef struct {
     const void* w; const void* x; const void* residual; void* y;
     float* partial; uint32_t* tickets; uint32_t* status;
     int32_t m, n, k, pdl;
     /* swiglu != 0: w is [2n, k] = n gate rows then n up rows, y[M, n] = bf16(silu(bf16(x.gate^T)) * bf16(x.up^T))
-     * (TFB_EPI_SWIGLU's rounding); n a multiple of 64, no residual; partial: f32
-     * [tfb_gemm_small_m_swiglu_splits(n, k) * M * 2n], tickets: u32 [n/64]. */
+     * (TFB_EPI_SWIGLU's rounding); n a multiple of 64, no residual. */
     int32_t swiglu;
 } tfb_gemm_small_m_args;
 TFB_API int32_t tfb_gemm_small_m_splits(int32_t n, int32_t k);
@@ -604,17 +605,12 @@ typedef struct {
     float* part_o;          /* attention split scratch, batch times the single-sequence size */
     float* part_ml;
     uint32_t* counters;     /* [batch*hkv + batch] zeroed once: attention tickets, then pick tickets */
-    float* gemm_partial;    /* f32 [tfb_qwen3_batch_partial_floats(...)] */
-    uint32_t* gemm_tickets; /* u32 [tfb_qwen3_batch_tickets(...)] zeroed once */
     uint32_t* status;       /* u32 zeroed once; non-zero after a step: a bounded wait gave up, outputs invalid */
     float* pick_val;        /* f32 [batch * 8] */
     int32_t* pick_idx;      /* i32 [batch * 8] */
     int64_t* picked;        /* optional [batch]: the token each sequence picked, whatever its prompt says */
     void* hidden_trace;     /* optional [n_layers+1][batch][hidden] bf16 */
 } tfb_qwen3_batch_step_args;
-TFB_API int64_t tfb_qwen3_batch_partial_floats(int32_t batch, int32_t hidden, int32_t hq, int32_t hkv, int32_t d,
-                                               int32_t inter, int64_t vocab);
-TFB_API int32_t tfb_qwen3_batch_tickets(int32_t hidden, int32_t hq, int32_t hkv, int32_t d, int32_t inter, int64_t vocab);
 TFB_API int tfb_qwen3_batch_decode_step(const tfb_qwen3_batch_step_args* args, tfb_stream_t stream);
 
 /* ================= f32-activation family (Qwen3.5-35B-A3B) =================

@@ -26,16 +26,14 @@ def _run(dev, w, x, residual=None, reps=1):
     n = w.shape[0]
     splits = lib.load().tfb_gemm_small_m_splits(n, k)
     y = torch.empty(m, n, device=dev, dtype=BF)
-    partial = torch.empty(max(splits, 1) * m * n, device=dev, dtype=torch.float32)
-    tickets = torch.zeros((n + 127) // 128, device=dev, dtype=torch.int32)
     status = torch.zeros(1, device=dev, dtype=torch.int32)
-    a = lib.GemmSmallMArgs(w=lib.ptr(w), x=lib.ptr(x), residual=lib.ptr(residual), y=lib.ptr(y), partial=lib.ptr(partial),
-                           tickets=lib.ptr(tickets), status=lib.ptr(status), m=m, n=n, k=k, pdl=0)
+    assert splits in (1, 2, 4, 8)
+    a = lib.GemmSmallMArgs(w=lib.ptr(w), x=lib.ptr(x), residual=lib.ptr(residual), y=lib.ptr(y), partial=None,
+                           tickets=None, status=lib.ptr(status), m=m, n=n, k=k, pdl=0)
     for _ in range(reps):
         lib.check(lib.load().tfb_gemm_small_m(C.byref(a), lib.stream()), "tfb_gemm_small_m")
     torch.cuda.synchronize()
     assert int(status) == 0, f"a bounded wait gave up (role {int(status)})"
-    assert int(tickets.abs().sum()) == 0
     return y
 
 
@@ -46,7 +44,7 @@ def test_small_batch_projection_matches_f32_reference(dev, m, n, k):
     w = (torch.randn(n, k, generator=g) * k ** -0.5).to(BF)
     x = torch.randn(m, k, generator=g).to(BF)
     want = (x.float() @ w.float().t())
-    got = _run(dev, w.to(dev), x.to(dev), reps=2)                 # twice: tickets and barriers return to their start state
+    got = _run(dev, w.to(dev), x.to(dev), reps=2)                 # twice: nothing carries over between launches
     assert_ulps(got.cpu(), want.to(BF), 1, f"y {m}x{n}x{k}")
     res = torch.randn(m, n, generator=g).to(BF)
     got = _run(dev, w.to(dev), x.to(dev), residual=res.to(dev))

@@ -45,15 +45,14 @@ def test_swiglu_projection_matches_f32_reference(dev, m, n, k):
     splits = native.tfb_gemm_small_m_swiglu_splits(n, k)
     wd, xd = w.to(dev), x.to(dev)
     y = torch.empty(m, n, device=dev, dtype=BF)
-    partial = torch.empty(max(splits, 1) * m * 2 * n, device=dev, dtype=torch.float32)
-    tickets = torch.zeros(n // 64, device=dev, dtype=torch.int32)
     status = torch.zeros(1, device=dev, dtype=torch.int32)
-    a = lib.GemmSmallMArgs(w=lib.ptr(wd), x=lib.ptr(xd), residual=None, y=lib.ptr(y), partial=lib.ptr(partial),
-                           tickets=lib.ptr(tickets), status=lib.ptr(status), m=m, n=n, k=k, pdl=0, swiglu=1)
-    for _ in range(2):                                  # twice: tickets and barriers return to their start state
+    assert splits in (1, 2, 4, 8)
+    a = lib.GemmSmallMArgs(w=lib.ptr(wd), x=lib.ptr(xd), residual=None, y=lib.ptr(y), partial=None,
+                           tickets=None, status=lib.ptr(status), m=m, n=n, k=k, pdl=0, swiglu=1)
+    for _ in range(2):                                  # twice: nothing carries over between launches
         lib.check(native.tfb_gemm_small_m(C.byref(a), lib.stream()), "tfb_gemm_small_m")
     torch.cuda.synchronize()
-    assert int(status) == 0 and int(tickets.abs().sum()) == 0
+    assert int(status) == 0
     assert_close_bf16(y.cpu(), want, f"swiglu {m}x{n}x{k}")
     # exact where the two halves land on the same bf16 values: most elements are bit-equal
     assert (y.cpu() == want).float().mean() > 0.9
@@ -62,8 +61,8 @@ def test_swiglu_projection_matches_f32_reference(dev, m, n, k):
 def test_swiglu_projection_rejects_bad_shapes(dev):
     from tilefoundry_b200 import lib
     z = torch.zeros(64, device=dev, dtype=BF)
-    a = lib.GemmSmallMArgs(w=lib.ptr(z), x=lib.ptr(z), residual=None, y=lib.ptr(z), partial=lib.ptr(z),
-                           tickets=lib.ptr(z), status=lib.ptr(z), m=4, n=100, k=64, pdl=0, swiglu=1)
+    a = lib.GemmSmallMArgs(w=lib.ptr(z), x=lib.ptr(z), residual=None, y=lib.ptr(z), partial=None,
+                           tickets=None, status=lib.ptr(z), m=4, n=100, k=64, pdl=0, swiglu=1)
     assert lib.load().tfb_gemm_small_m(C.byref(a), lib.stream()) != 0      # n not a multiple of 64
 
 

@@ -2,56 +2,17 @@
 #include "api_internal.h"
 #include "kernels.h"
 
-#include <algorithm>
 #include <cstring>
 
 using namespace tfb::host;
 
-namespace {
-
-struct Proj { int n, k; bool swiglu; };
-
-// the projections of one step, in launch order
-void batch_projections(int hidden, int hq, int hkv, int d, int inter, long long vocab, Proj (&out)[5]) {
-    out[0] = {(hq + 2 * hkv) * d, hidden, false};
-    out[1] = {hidden, hq * d, false};
-    out[2] = {inter, hidden, true};
-    out[3] = {hidden, inter, false};
-    out[4] = {int(vocab), hidden, false};
-}
-
-}  // namespace
-
 extern "C" {
-
-int64_t tfb_qwen3_batch_partial_floats(int32_t batch, int32_t hidden, int32_t hq, int32_t hkv, int32_t d, int32_t inter,
-                                       int64_t vocab) {
-    if (batch <= 0 || hidden <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || inter <= 0 || vocab <= 0) return 0;
-    Proj pr[5];
-    batch_projections(hidden, hq, hkv, d, inter, vocab, pr);
-    long long need = 1;
-    for (const Proj& p : pr) {
-        const int splits = p.swiglu ? tfb::gemm_tc_splits_swiglu(p.n, p.k) : tfb::gemm_tc_splits(p.n, p.k);
-        const long long rows = p.swiglu ? 2ll * p.n : p.n;
-        if (splits > 1) need = std::max(need, splits * (long long)batch * rows);
-    }
-    return need;
-}
-
-int32_t tfb_qwen3_batch_tickets(int32_t hidden, int32_t hq, int32_t hkv, int32_t d, int32_t inter, int64_t vocab) {
-    if (hidden <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || inter <= 0 || vocab <= 0) return 0;
-    Proj pr[5];
-    batch_projections(hidden, hq, hkv, d, inter, vocab, pr);
-    int need = 1;
-    for (const Proj& p : pr) need = std::max(need, p.swiglu ? (p.n + 63) / 64 : (p.n + 127) / 128);
-    return need;
-}
 
 int tfb_qwen3_batch_decode_step(const tfb_qwen3_batch_step_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->layers && a->n_layers > 0 && a->batch >= 1 && a->batch <= 32, TFB_EINVAL);
     TFB_REQUIRE(a->w_embed && a->gamma_final && a->w_head && a->tokens && a->pos && a->block_table, TFB_EINVAL);
     TFB_REQUIRE(a->hidden_buf && a->norm_buf && a->qkv_buf && a->attn_buf && a->act_buf && a->logits, TFB_EINVAL);
-    TFB_REQUIRE(a->part_o && a->part_ml && a->counters && a->gemm_partial && a->gemm_tickets && a->status, TFB_EINVAL);
+    TFB_REQUIRE(a->part_o && a->part_ml && a->counters && a->status, TFB_EINVAL);
     TFB_REQUIRE(a->pick_val && a->pick_idx, TFB_EINVAL);
     TFB_REQUIRE(a->hidden % 64 == 0 && a->inter % 64 == 0 && (a->hq * a->d) % 64 == 0 && a->hidden % 8 == 0, TFB_EINVAL);
     TFB_REQUIRE((long long)a->page_size * a->table_len >= a->max_ctx, TFB_ECAPACITY);
@@ -68,7 +29,7 @@ int tfb_qwen3_batch_decode_step(const tfb_qwen3_batch_step_args* a, tfb_stream_t
         tfb_gemm_small_m_args g;
         std::memset(&g, 0, sizeof g);
         g.w = w; g.x = x; g.residual = residual; g.y = y;
-        g.partial = a->gemm_partial; g.tickets = a->gemm_tickets; g.status = a->status;
+        g.status = a->status;
         g.m = B; g.n = n; g.k = k; g.pdl = pdl; g.swiglu = swiglu;
         return tfb_gemm_small_m(&g, stream);
     };

@@ -11,9 +11,11 @@
 //
 // Roles in a CTA of 6 warps: warp 0 (one lane) issues TMA loads; warp 1 allocates tensor memory and (one lane)
 // issues the MMAs, four per stage (K = 16 each), releasing a stage with tcgen05.commit; warps 2-5 read the
-// accumulator back (tcgen05.ld, one TMEM lane quadrant each) and write it out.  K is split over blockIdx.y so
-// that a 6144 x 2048 projection (48 row tiles) still fills every SM; the splits' f32 partials are added in
-// fixed order by the last CTA of a row tile (atomic ticket, no spinning): deterministic.
+// accumulator back (tcgen05.ld, one TMEM lane quadrant each) and write it out.  K is split over the 1, 2, 4 or 8
+// CTAs of a thread-block cluster so that a 2048 x 2048 projection (16 row tiles) still reaches most SMs.  The
+// splits' f32 partials never leave the chip: every CTA parks its 128 x 32 tile in its own shared memory, and
+// after a cluster barrier CTA c adds, in fixed split order (deterministic), the 32/S token rows it owns from all
+// S CTAs through distributed shared memory and writes them out.
 //
 // SwiGLU form (p.swiglu): a row tile holds 64 gate rows and the 64 up rows of the same outputs (two 64-row TMA
 // boxes from a [gate; up] matrix), so one accumulator carries both halves; the up half crosses to the gate half's
@@ -80,11 +82,29 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 struct TcSmemTail {
     uint64_t full[TC_STAGES], empty[TC_STAGES], accum;
     uint32_t tmem_base;
-    int aborted, last;
-    float exch[64][33];                                                 // SwiGLU: the up half of a finished tile
+    int aborted;
+    float exch[64][33];                                                 // SwiGLU, unsplit: the up half of a finished tile
 };
 
-// The finished f32 sums of tile row r (0..127) for the M tokens -> y.  Called by all 128 epilogue threads.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release;\nbarrier.cluster.wait.acquire;" ::: "memory");
+}
+// 16 bytes of CTA `rank`'s shared memory at the address `local` has in this CTA's window
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t local, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
+
+// The finished f32 sums of tile row r (0..127) for the M tokens -> y (unsplit launch).  Called by all 128
+// epilogue threads.
 __device__ __forceinline__ void tc_finish_row(const TcParams& p, TcSmemTail* t, int tile, int r, const float (&acc)[32]) {
     if (p.swiglu) {
         if (r >= 64) {
@@ -114,6 +134,37 @@ __device__ __forceinline__ void tc_finish_row(const TcParams& p, TcSmemTail* t, 
         }
 }
 
+// Split launch: token row m, tile rows 4q .. 4q+3 summed over the splits -> y.  Called by whole warps (the SwiGLU
+// form moves the up half to the gate half's lanes by shuffle: lane q holds gate rows 4q.., lane q + 16 the up rows
+// of the same outputs).
+__device__ __forceinline__ void tc_finish_quad(const TcParams& p, int tile, int m, int q, float4 acc) {
+    const float a[4] = {acc.x, acc.y, acc.z, acc.w};
+    if (p.swiglu) {
+        float u[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) u[i] = __shfl_down_sync(0xffffffffu, a[i], 16);
+        if (q < 16 && m < p.M) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int j = tile * 64 + 4 * q + i;
+                if (j < p.N)
+                    p.y[size_t(m) * p.N + j] = f32_to_bf16_bits(round_bf16(silu_f32(round_bf16(a[i]))) * round_bf16(u[i]));
+            }
+        }
+        return;
+    }
+    if (m >= p.M) return;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int n = tile * TC_BM + 4 * q + i;
+        if (n < p.N) {
+            float o = a[i];
+            if (p.residual) o = bf16_bits_to_f32(p.residual[size_t(m) * p.N + n]) + round_bf16(a[i]);
+            p.y[size_t(m) * p.N + n] = f32_to_bf16_bits(o);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(TC_THREADS, 2) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     extern __shared__ unsigned char tc_smem_raw[];
@@ -123,7 +174,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) gemm_tc_kernel(const __grid_con
     TcSmemTail* t = reinterpret_cast<TcSmemTail*>(b_tiles + TC_STAGES * TC_B_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.x, split = blockIdx.y;
+    const int tile = blockIdx.x, split = p.splits > 1 ? int(cluster_ctarank()) : 0;
     const int per = (p.ksteps + p.splits - 1) / p.splits;
     const int k_begin = split * per, k_end = min(p.ksteps, k_begin + per);
     const int nsteps = max(k_end - k_begin, 0);
@@ -132,7 +183,6 @@ __global__ void __launch_bounds__(TC_THREADS, 2) gemm_tc_kernel(const __grid_con
         for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&t->full[s], 1); mbar_init(&t->empty[s], 1); }
         mbar_init(&t->accum, 1);
         t->aborted = 0;
-        t->last = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {                                                    // 32 columns of tensor memory: the 128 x 32 f32 tile
@@ -218,15 +268,17 @@ __global__ void __launch_bounds__(TC_THREADS, 2) gemm_tc_kernel(const __grid_con
 #pragma unroll
             for (int m = 0; m < 32; ++m) acc[m] = __uint_as_float(v[m]);
             tc_finish_row(p, t, tile, quad * 32 + lane, acc);
-        } else if (n < p.ntot) {
+        } else {
+            // park this split's tile as red[m][r] in the first weight stage: every load into it has landed and
+            // every MMA that read it has completed once the accumulator barrier fires
+            float* red = reinterpret_cast<float*>(a_tiles);
+            (void)n;
 #pragma unroll
-            for (int m = 0; m < 32; ++m)
-                if (m < p.M) p.partial[(size_t(split) * p.M + m) * p.ntot + n] = __uint_as_float(v[m]);
+            for (int m = 0; m < 32; ++m) red[m * TC_BM + quad * 32 + lane] = __uint_as_float(v[m]);
         }
     }
 
-    // ---- teardown, and the split-K reduction by the last CTA of this row tile ----
-    __threadfence();
+    // ---- teardown, and the split-K reduction through distributed shared memory ----
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
@@ -234,27 +286,26 @@ __global__ void __launch_bounds__(TC_THREADS, 2) gemm_tc_kernel(const __grid_con
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(32u) : "memory");
     }
     if (p.splits > 1) {
-        if (threadIdx.x == 0) t->last = atomicAdd(&p.tickets[tile], 1u) == unsigned(p.splits - 1);
-        __syncthreads();
-        if (t->last && warp >= 2) {
-            __threadfence();
-            const int r = (warp & 3) * 32 + lane, n = tile * TC_BM + r;
-            float acc[32];
+        cluster_sync_all();                                             // every split's tile is parked
+        if (warp >= 2) {
+            const int tq = threadIdx.x - 64, q = tq & 31, mg = tq >> 5; // 4 token rows at a time, 32 row quads each
+            const int m_per = 32 / p.splits;                            // token rows this CTA finishes (>= 4)
+            const uint32_t red = smem_u32(a_tiles);
+            for (int j = 0; j < m_per; j += 4) {
+                const int m = split * m_per + j + mg;
+                const uint32_t local = red + uint32_t((m * TC_BM + 4 * q) * 4);
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 part[8];
 #pragma unroll
-            for (int m = 0; m < 32; ++m) acc[m] = 0.f;
-            if (n < p.ntot) {
-                for (int s = 0; s < p.splits; ++s) {                    // fixed order; 32 independent loads in flight
-                    const float* src = p.partial + size_t(s) * p.M * p.ntot + n;
-                    float v[32];
+                for (int s = 0; s < 8; ++s)
+                    if (s < p.splits) part[s] = ld_dsmem_f4(local, uint32_t(s));
 #pragma unroll
-                    for (int m = 0; m < 32; ++m) v[m] = (m < p.M) ? __ldcg(src + size_t(m) * p.ntot) : 0.f;
-#pragma unroll
-                    for (int m = 0; m < 32; ++m) acc[m] += v[m];
-                }
+                for (int s = 0; s < 8; ++s)                             // fixed order
+                    if (s < p.splits) { acc.x += part[s].x; acc.y += part[s].y; acc.z += part[s].z; acc.w += part[s].w; }
+                tc_finish_quad(p, tile, m, q, acc);
             }
-            tc_finish_row(p, t, tile, r, acc);
-            if (threadIdx.x == 64) p.tickets[tile] = 0;
         }
+        cluster_sync_all();                                             // nobody leaves while its tile is still being read
     }
 }
 
@@ -290,14 +341,14 @@ static bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int 
 static int splits_for_tiles(int tiles, int k);
 int gemm_tc_splits(int n, int k) { return splits_for_tiles((n + TC_BM - 1) / TC_BM, k); }
 int gemm_tc_splits_swiglu(int n, int k) { return splits_for_tiles((n + 63) / 64, k); }
+// K splits = CTAs of one cluster: the largest power of two (at most 8, the portable cluster size) that keeps the
+// grid within the two CTAs an SM holds.
 static int splits_for_tiles(int tiles, int k) {
     int sms = 148, dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int ksteps = k / TC_BK;
-    int splits = 2 * sms / tiles;                      // two CTAs (each a 4-stage, 80 KB ring) share an SM
-    if (splits < 1) splits = 1;
-    if (splits > ksteps) splits = ksteps;
-    if (splits > 16) splits = 16;
+    int splits = 1;
+    while (splits < 8 && tiles * splits * 2 <= 2 * sms && ksteps % (splits * 2) == 0) splits *= 2;
     return splits;
 }
 
@@ -317,7 +368,28 @@ cudaError_t gemm_tc_launch(const void* w, const void* x, TcParams p, cudaStream_
         once = true;
     }
     const dim3 grid(tiles, p.splits), block(TC_THREADS);
-    return launch_kernel(gemm_tc_kernel, grid, block, smem, stream, pdl, map_w, map_x, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (p.splits > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.y = unsigned(p.splits);
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel, map_w, map_x, p);
 }
 
 }  // namespace tfb

@@ -312,10 +312,10 @@ cudaError_t gemv_chain_launch(ChainParams& p, cudaStream_t stream, bool pdl, siz
 
 // ---- small-batch projection on tcgen05 tensor cores (gemm_tc.cu) ----
 struct TcParams {
-    float* partial;              // f32 [splits][M][N] (splits > 1)
+    float* partial;              // unused
     uint16_t* y;                 // bf16 [M][N]
     const uint16_t* residual;    // optional bf16 [M][N]
-    unsigned* tickets;           // u32 [ceil(N/128)], zero before the first launch (splits > 1)
+    unsigned* tickets;           // unused
     unsigned* status;            // u32, set non-zero if a bounded wait gave up
     int M, N, K, ksteps, splits;
     int ntot;                    // accumulator rows over all tiles: N, or tiles * 128 in the SwiGLU form

@@ -63,7 +63,6 @@ class Qwen3BatchSession:
         bf, f32, i32 = torch.bfloat16, torch.float32, torch.int32
         z = lambda *s, dtype=bf: torch.zeros(*s, device=dev, dtype=dtype)
         nsplit = lib.attn_splits(self.max_ctx)
-        native = lib.load()
         self.max_tokens = self.max_ctx + 1
         self.tokens = z(B, self.max_tokens, dtype=torch.int64)
         self.pos = z(B, dtype=i32)
@@ -76,8 +75,6 @@ class Qwen3BatchSession:
         self.part_o = z(B * HQ * nsplit * D, dtype=f32)
         self.part_ml = z(B * HQ * nsplit * 2, dtype=f32)
         self.counters = z(B * HKV + B, dtype=i32)
-        self.gemm_partial = z(int(native.tfb_qwen3_batch_partial_floats(B, H, HQ, HKV, D, I, V)), dtype=f32)
-        self.gemm_tickets = z(int(native.tfb_qwen3_batch_tickets(H, HQ, HKV, D, I, V)), dtype=i32)
         self.status = z(1, dtype=i32)
         self.pick_val = z(B * 8, dtype=f32)
         self.pick_idx = z(B * 8, dtype=i32)
@@ -100,7 +97,6 @@ class Qwen3BatchSession:
             hidden_buf=lib.ptr(self.hidden), norm_buf=lib.ptr(self.norm), qkv_buf=lib.ptr(self.qkv),
             attn_buf=lib.ptr(self.attn), act_buf=lib.ptr(self.act), logits=lib.ptr(self.logits),
             part_o=lib.ptr(self.part_o), part_ml=lib.ptr(self.part_ml), counters=lib.ptr(self.counters),
-            gemm_partial=lib.ptr(self.gemm_partial), gemm_tickets=lib.ptr(self.gemm_tickets),
             status=lib.ptr(self.status), pick_val=lib.ptr(self.pick_val), pick_idx=lib.ptr(self.pick_idx),
             picked=lib.ptr(self.picked), hidden_trace=lib.ptr(self.trace))
         self.graph = None
@@ -134,7 +130,6 @@ class Qwen3BatchSession:
         self.tokens[:, : prompts.shape[1]] = prompts.to(self.device)
         self.pos.zero_()
         self.counters.zero_()
-        self.gemm_tickets.zero_()
         self.status.zero_()
         if self.args.n_prompt != prompts.shape[1]:
             self.args.n_prompt = int(prompts.shape[1])

@@ -87,8 +87,8 @@ class Qwen3BatchStepArgs(C.Structure):
                 ("max_pos", _i32), ("page_size", _i32), ("table_len", _i32), ("max_ctx", _i32),
                 ("block_table", _vp), ("tokens", _vp), ("pos", _vp), ("n_prompt", _i32), ("max_tokens", _i32),
                 ("hidden_buf", _vp), ("norm_buf", _vp), ("qkv_buf", _vp), ("attn_buf", _vp), ("act_buf", _vp),
-                ("logits", _vp), ("part_o", _vp), ("part_ml", _vp), ("counters", _vp), ("gemm_partial", _vp),
-                ("gemm_tickets", _vp), ("status", _vp), ("pick_val", _vp), ("pick_idx", _vp), ("picked", _vp),
+                ("logits", _vp), ("part_o", _vp), ("part_ml", _vp), ("counters", _vp),
+                ("status", _vp), ("pick_val", _vp), ("pick_idx", _vp), ("picked", _vp),
                 ("hidden_trace", _vp)]
 
 
@@ -234,8 +234,6 @@ SYMBOLS = {
     "tfb_gemm_small_m_splits": (_i32, [_i32, _i32]),
     "tfb_gemm_small_m_swiglu_splits": (_i32, [_i32, _i32]),
     "tfb_gemm_small_m": (_i32, [C.POINTER(GemmSmallMArgs), _vp]),
-    "tfb_qwen3_batch_partial_floats": (_i64, [_i32, _i32, _i32, _i32, _i32, _i32, _i64]),
-    "tfb_qwen3_batch_tickets": (_i32, [_i32, _i32, _i32, _i32, _i32, _i64]),
     "tfb_qwen3_batch_decode_step": (_i32, [C.POINTER(Qwen3BatchStepArgs), _vp]),
     "tfb_lm_head_scratch_entries": (_i32, [_i32]),
     "tfb_lm_head_argmax": (_i32, [C.POINTER(LmHeadArgs), _vp]),
