@@ -6,7 +6,7 @@ import pytest
 import torch
 
 from oracle import evaluator, generation, qwen3_1_7b as oq
-from tests.helpers import assert_close_at_scale, assert_close_bf16
+from tests.helpers import assert_close_at_scale, assert_close_bf16, assert_ulps
 from tilefoundry_b200.authored import qwen3_1_7b as q
 from tilefoundry_b200.authored.weights import random_weights
 from tilefoundry_b200.runtime import DictResource
@@ -66,7 +66,7 @@ def test_swiglu_projection_rejects_bad_shapes(dev):
     assert lib.load().tfb_gemm_small_m(C.byref(a), lib.stream()) != 0      # n not a multiple of 64
 
 
-# ---- batched attention = one launch per sequence ------------------------------------------------------
+# ---- batched attention against one launch per sequence ------------------------------------------------------
 
 def test_batched_attention_equals_per_sequence_launches(dev):
     from tilefoundry_b200 import lib
@@ -109,7 +109,8 @@ def test_batched_attention_equals_per_sequence_launches(dev):
     ks, vs = k_pool.clone(), v_pool.clone()
     for b in range(B):
         launch(1, qkv[b], pos[b:b + 1], table[b:b + 1].contiguous(), out_s[b], ks, vs)
-    assert torch.equal(out_b, out_s)
+    # the batched kernel groups the softmax partials by 256 positions, the single one by 64: same sums, other order
+    assert_ulps(out_b.cpu(), out_s.cpu(), 2, "batched vs per-sequence attention")
     assert torch.equal(kb, ks) and torch.equal(vb, vs)       # every sequence appended to its own pages only
     assert not torch.equal(kb, k_pool)
 

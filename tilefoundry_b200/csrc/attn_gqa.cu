@@ -41,7 +41,7 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 template <int D, int G>
-__global__ void __launch_bounds__(kAttnThreads) attn_gqa_kernel(AttnParams p) {
+__global__ void __launch_bounds__(kAttnThreads) attn_gqa_kernel(const AttnParams p) {
     constexpr int LPP = D / 8;                 // lanes that share one position's row (16 B each)
     constexpr int NSG = kAttnThreads / LPP;    // position sub-groups in the CTA
     constexpr int NWARP = kAttnThreads / 32;
@@ -61,20 +61,6 @@ __global__ void __launch_bounds__(kAttnThreads) attn_gqa_kernel(AttnParams p) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = blockIdx.x, split = blockIdx.y;
     const int p0 = split * kSplitLen;
-    if (blockIdx.z != 0) {                       // sequence blockIdx.z of a batch: shift every per-sequence pointer
-        const size_t b = blockIdx.z;
-        p.qkv += b * p.qkv_stride;
-        p.out += b * p.out_stride;
-        p.block_table += b * p.bt_stride;
-        p.pos += b;
-        if (p.rope_pos) p.rope_pos += b;
-        p.part_o += b * p.hq * p.nsplit * D;
-        p.part_ml += b * p.hq * p.nsplit * 2;
-        p.counters += b * p.hkv;
-        if (p.k_new_out) p.k_new_out += b * p.hkv * D;
-        if (p.v_new_out) p.v_new_out += b * p.hkv * D;
-    }
-
     trace_start(p.trace);
     // ---- before the dependency wait: start fetching the cached rows ---------------------
     // Rows below the position word are final whatever step wrote that word last.
@@ -371,9 +357,361 @@ __global__ void __launch_bounds__(kAttnThreads) attn_gqa_kernel(AttnParams p) {
     trace_end(p.trace);
 }
 
+// ---- several sequences per launch ----------------------------------------------------------------------
+// At batch 32 the cache is the larger half of a step's bytes (32 sequences x context x 4 KB per KV head pair and
+// layer), so this form is built for bandwidth rather than for one round trip: grid (hkv, chunks, sequences),
+// a CTA walks up to kBatchTiles consecutive 64-position tiles of one KV head of one sequence through a
+// double-buffered cp.async ring (the next tile lands while this one is scored), carrying a running (max, sum)
+// and rescaled PV accumulators, so the q/k normalisation + rotation is paid once per 256 positions and a
+// context of 2048 leaves 8 partials per head to merge instead of 32.  Arithmetic and rounding points per
+// element are those of attn_gqa_kernel; only the grouping of the softmax partials differs.
+constexpr int kBatchTiles = 4;
+
+int attn_batch_chunks(int max_ctx) { return (attn_splits(max_ctx) + kBatchTiles - 1) / kBatchTiles; }
+
+template <int D, int G>
+__global__ void __launch_bounds__(kAttnThreads, 3) attn_gqa_batch_kernel(AttnParams p) {
+    constexpr int LPP = D / 8;
+    constexpr int NSG = kAttnThreads / LPP;
+    constexpr int NWARP = kAttnThreads / 32;
+    constexpr int NV = G + 1;
+    constexpr int OUT_PER_THREAD = (G * D + kAttnThreads - 1) / kAttnThreads;
+    constexpr int TILE = kSplitLen * D;                  // elements of one K (or V) tile
+
+    extern __shared__ __align__(16) unsigned char batch_smem[];
+    uint16_t* kbuf = reinterpret_cast<uint16_t*>(batch_smem);            // [2][kSplitLen][D]
+    uint16_t* vbuf = kbuf + 2 * TILE;                                     // [2][kSplitLen][D]
+    __shared__ __align__(16) float vec[NV + 1][D];
+    __shared__ float gain[2][D];
+    __shared__ float rot[2][D];
+    __shared__ float sc[G][kSplitLen];
+    __shared__ float stat_m[G], stat_l[G], rescale[G];
+    __shared__ float mrg_w[G][64];
+    __shared__ int s_last;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = blockIdx.x, chunk = blockIdx.y;
+    {
+        const size_t b = blockIdx.z;
+        p.qkv += b * p.qkv_stride;
+        p.out += b * p.out_stride;
+        p.block_table += b * p.bt_stride;
+        p.pos += b;
+        if (p.rope_pos) p.rope_pos += b;
+        p.part_o += b * p.hq * p.nsplit * D;
+        p.part_ml += b * p.hq * p.nsplit * 2;
+        p.counters += b * p.hkv;
+        if (p.k_new_out) p.k_new_out += b * p.hkv * D;
+        if (p.v_new_out) p.v_new_out += b * p.hkv * D;
+    }
+    if (tid < D) {                                       // weights: independent of the kernel before
+        gain[0][tid] = p.norm_mode ? bf16_bits_to_f32(p.gamma_q[tid]) : 1.f;
+        gain[1][tid] = p.norm_mode ? bf16_bits_to_f32(p.gamma_k[tid]) : 1.f;
+    }
+    pdl_trigger();
+    pdl_wait();
+
+    const int pos = *p.pos;
+    const int total = pos + 1;
+    const int n_tiles = (total + kSplitLen - 1) / kSplitLen;
+    const int t0 = chunk * kBatchTiles;
+    if (pos < 0 || pos >= p.max_ctx || t0 >= n_tiles) return;
+    const int t1 = min(t0 + kBatchTiles, n_tiles);
+    const int n_chunks = (n_tiles + kBatchTiles - 1) / kBatchTiles;
+    const bool owner = (t1 == n_tiles);                  // this CTA's last tile holds the new position
+
+    auto fetch = [&](int tile, int buf) {                // cached rows of a tile -> ring slot (the new row comes from vec[])
+        const int base = tile * kSplitLen;
+        const int rows = min(kSplitLen, pos - base);     // rows below pos are in the cache
+        for (int c = tid; c < rows * LPP; c += kAttnThreads) {
+            const int r = c / LPP, piece = c % LPP;
+            const int pp = base + r;
+            const int page = p.block_table[pp / p.page_size];
+            const size_t off = ((size_t(page) * p.page_size + (pp % p.page_size)) * p.hkv + g) * D + piece * 8;
+            cp_async16(&kbuf[buf * TILE + r * D + piece * 8], p.k_pool + off);
+            cp_async16(&vbuf[buf * TILE + r * D + piece * 8], p.v_pool + off);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch(t0, 0);
+
+    // ---- this token's q (G heads), k, v for KV head g: as in attn_gqa_kernel ----
+    const int rd = p.rotary_dim, half = rd >> 1;
+    const int rpos = p.rope_pos ? *p.rope_pos : pos;
+    if (tid < rd) {
+        rot[0][tid] = bf16_bits_to_f32(p.cos_table[size_t(rpos) * rd + tid]);
+        rot[1][tid] = bf16_bits_to_f32(p.sin_table[size_t(rpos) * rd + tid]);
+    }
+    int vis[2] = {warp, warp + NWARP};
+    float xv[2][D / 32];
+#pragma unroll
+    for (int s2 = 0; s2 < 2; ++s2) {
+        const int vi = vis[s2];
+#pragma unroll
+        for (int i = 0; i < D / 32; ++i) xv[s2][i] = 0.f;
+        if (vi < NV + 1) {
+            const uint16_t* src;
+            if (vi < G) src = p.qkv + size_t(g * G + vi) * D;
+            else if (vi == G) src = p.qkv + size_t(p.hq) * D + size_t(g) * D;
+            else src = p.qkv + size_t(p.hq + p.hkv) * D + size_t(g) * D;
+#pragma unroll
+            for (int i = 0; i < D / 32; ++i) xv[s2][i] = bf16_bits_to_f32(src[lane + 32 * i]);
+        }
+    }
+    __syncthreads();                                     // rot[] / gain[] visible
+#pragma unroll
+    for (int s2 = 0; s2 < 2; ++s2) {
+        const int vi = vis[s2];
+        if (vi >= NV + 1) continue;
+        float* x = xv[s2];
+        if (vi == G + 1) {
+#pragma unroll
+            for (int i = 0; i < D / 32; ++i) vec[vi][lane + 32 * i] = x[i];
+            continue;
+        }
+        if (p.norm_mode != 0) {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < D / 32; ++i) ss = fmaf(x[i], x[i], ss);
+            ss = warp_sum(ss);
+            const float rstd = rsqrtf(ss / float(D) + p.eps);
+            const float* gm = gain[vi < G ? 0 : 1];
+#pragma unroll
+            for (int i = 0; i < D / 32; ++i) x[i] = round_bf16(round_bf16(x[i] * rstd) * gm[lane + 32 * i]);
+        }
+#pragma unroll
+        for (int i = 0; i < D / 32; ++i) {
+            const int e = lane + 32 * i;
+            float r = x[i];
+            if (e < rd) {
+                const int pi = (e < half) ? i + half / 32 : i - half / 32;
+                float partner = 0.f;
+#pragma unroll
+                for (int k2 = 0; k2 < D / 32; ++k2) if (k2 == pi) partner = x[k2];
+                if (e < half) partner = -partner;
+                r = round_bf16(__fadd_rn(__fmul_rn(x[i], rot[0][e]), __fmul_rn(partner, rot[1][e])));
+            }
+            if (vi < G) r = round_bf16(r * p.scale);
+            vec[vi][e] = r;
+        }
+    }
+    if (tid < G) { stat_m[tid] = -INFINITY; stat_l[tid] = 0.f; }
+    __syncthreads();
+
+    if (owner) {                                         // append this token's entry to the cache
+        const int page = p.block_table[pos / p.page_size];
+        const size_t base = ((size_t(page) * p.page_size + (pos % p.page_size)) * p.hkv + g) * D;
+        for (int i = tid; i < D; i += kAttnThreads) {
+            const uint16_t kb = f32_to_bf16_bits(vec[G][i]), vb = f32_to_bf16_bits(vec[G + 1][i]);
+            p.k_pool[base + i] = kb;
+            p.v_pool[base + i] = vb;
+            if (p.k_new_out) p.k_new_out[size_t(g) * D + i] = kb;
+            if (p.v_new_out) p.v_new_out[size_t(g) * D + i] = vb;
+        }
+    }
+
+    // PV mapping: thread (dp, rg) owns the output pair d = 2dp, 2dp+1 of every query head for the rows of row
+    // group rg of each tile (one 4-byte V load feeds 2G products); the RG partial sums meet once, after the last
+    // tile, through shared memory in fixed order.
+    constexpr int PAIRS = D / 2, RG = kAttnThreads / PAIRS, ROWS_PER_RG = kSplitLen / RG;
+    const int dp = tid % PAIRS, rg = tid / PAIRS;
+    float o_acc[G][2];
+#pragma unroll
+    for (int j = 0; j < G; ++j) { o_acc[j][0] = 0.f; o_acc[j][1] = 0.f; }
+    const int sg = tid / LPP, sl = tid % LPP;
+    float q[G][8];
+#pragma unroll
+    for (int j = 0; j < G; ++j)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[j][i] = vec[j][sl * 8 + i];
+
+    for (int tile = t0; tile < t1; ++tile) {
+        const int buf = (tile - t0) & 1;
+        if (tile + 1 < t1) {
+            fetch(tile + 1, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        const int base = tile * kSplitLen;
+        const int n = min(kSplitLen, total - base);      // rows of this tile, the new one included
+        if (tile == n_tiles - 1)                         // the new entry goes straight into the ring slot
+            for (int i = tid; i < D; i += kAttnThreads) {
+                kbuf[buf * TILE + (pos - base) * D + i] = f32_to_bf16_bits(vec[G][i]);
+                vbuf[buf * TILE + (pos - base) * D + i] = f32_to_bf16_bits(vec[G + 1][i]);
+            }
+        __syncthreads();
+        const uint16_t* kt = kbuf + buf * TILE;
+        const uint16_t* vt = vbuf + buf * TILE;
+        // scores
+#pragma unroll
+        for (int r0 = 0; r0 < kSplitLen; r0 += NSG) {
+            const int r = r0 + sg;
+            float kf[8];
+            if (r < n) {
+                unpack8(*reinterpret_cast<const uint4*>(&kt[r * D + sl * 8]), kf);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) kf[i] = 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < G; ++j) {
+                float s = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) s = fmaf(q[j][i], kf[i], s);
+#pragma unroll
+                for (int o = LPP / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                if (sl == 0 && r < n) sc[j][r] = s;
+            }
+        }
+        __syncthreads();
+        // running softmax statistics; rows past n get probability 0 so the PV loop needs no bound
+        for (int j = warp; j < G; j += NWARP) {
+            float m = -INFINITY;
+            for (int i = lane; i < n; i += 32) m = fmaxf(m, sc[j][i]);
+            m = warp_max(m);
+            const float old_m = stat_m[j];
+            const float new_m = fmaxf(old_m, m);
+            float l = 0.f;
+            for (int i = lane; i < kSplitLen; i += 32) {
+                const float e = i < n ? __expf(sc[j][i] - new_m) : 0.f;
+                sc[j][i] = e;
+                l += e;
+            }
+            l = warp_sum(l);
+            if (lane == 0) {
+                const float c = old_m == -INFINITY ? 0.f : __expf(old_m - new_m);
+                rescale[j] = c;
+                stat_l[j] = stat_l[j] * c + l;
+                stat_m[j] = new_m;
+            }
+        }
+        __syncthreads();
+        // probability-weighted V
+        {
+            float a[G][2];
+#pragma unroll
+            for (int j = 0; j < G; ++j) { a[j][0] = 0.f; a[j][1] = 0.f; }
+            const int r_begin = rg * ROWS_PER_RG;
+            if (r_begin < n) {
+#pragma unroll 4
+                for (int i = 0; i < ROWS_PER_RG; ++i) {
+                    const int r = r_begin + i;
+                    // rows past n hold stale bytes: read them as zero bits, their probability is zero too
+                    const uint32_t v2 = r < n ? *reinterpret_cast<const uint32_t*>(&vt[r * D + 2 * dp]) : 0u;
+                    const float v_lo = bf16_lo(v2), v_hi = bf16_hi(v2);
+#pragma unroll
+                    for (int j = 0; j < G; ++j) {
+                        const float pr = sc[j][r];
+                        a[j][0] = fmaf(pr, v_lo, a[j][0]);
+                        a[j][1] = fmaf(pr, v_hi, a[j][1]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < G; ++j) {
+                const float c = rescale[j];
+                o_acc[j][0] = o_acc[j][0] * c + a[j][0];
+                o_acc[j][1] = o_acc[j][1] * c + a[j][1];
+            }
+        }
+        __syncthreads();                                 // the slot and sc[] are free for the tile after next
+    }
+
+    // the row groups' partial sums meet in the (now idle) ring: pv_red[rg][j][d]
+    float* pv_red = reinterpret_cast<float*>(batch_smem);
+#pragma unroll
+    for (int j = 0; j < G; ++j) {
+        pv_red[(rg * G + j) * D + 2 * dp] = o_acc[j][0];
+        pv_red[(rg * G + j) * D + 2 * dp + 1] = o_acc[j][1];
+    }
+    __syncthreads();
+    const int nsplit = p.nsplit;
+#pragma unroll
+    for (int t = 0; t < OUT_PER_THREAD; ++t) {
+        const int e = tid + t * kAttnThreads;
+        if (e < G * D) {
+            const int j = e / D, d = e % D;
+            const int head = g * G + j;
+            float o = 0.f;
+#pragma unroll
+            for (int r2 = 0; r2 < RG; ++r2) o += pv_red[(r2 * G + j) * D + d];
+            if (n_chunks == 1) p.out[size_t(head) * D + d] = f32_to_bf16_bits(o / stat_l[j]);
+            else p.part_o[(size_t(head) * nsplit + chunk) * D + d] = o;
+        }
+    }
+    if (n_chunks == 1) return;
+    if (tid < G) {
+        const int head = g * G + tid;
+        p.part_ml[(size_t(head) * nsplit + chunk) * 2] = stat_m[tid];
+        p.part_ml[(size_t(head) * nsplit + chunk) * 2 + 1] = stat_l[tid];
+    }
+    // ---- merge by the last CTA of this (sequence, KV head) ----
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = (atomicAdd(&p.counters[g], 1u) == unsigned(n_chunks - 1));
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // n_chunks <= 64 is checked on the host: one pass
+    for (int j = warp; j < G; j += NWARP) {
+        const float* ml = p.part_ml + size_t(g * G + j) * nsplit * 2;
+        const float2 a0 = lane < n_chunks ? __ldcg(reinterpret_cast<const float2*>(ml) + lane) : make_float2(-INFINITY, 0.f);
+        const float2 a1 = lane + 32 < n_chunks ? __ldcg(reinterpret_cast<const float2*>(ml) + lane + 32)
+                                               : make_float2(-INFINITY, 0.f);
+        const float M = warp_max(fmaxf(a0.x, a1.x));
+        const float w0 = lane < n_chunks ? __expf(a0.x - M) : 0.f;
+        const float w1 = lane + 32 < n_chunks ? __expf(a1.x - M) : 0.f;
+        mrg_w[j][lane] = w0;
+        mrg_w[j][lane + 32] = w1;
+        const float den = warp_sum(fmaf(w0, a0.y, w1 * a1.y));
+        if (lane == 0) stat_l[j] = den;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int t = 0; t < OUT_PER_THREAD; ++t) {
+        const int e = tid + t * kAttnThreads;
+        if (e < G * D) {
+            const int j = e / D, d = e % D;
+            const int head = g * G + j;
+            const float* po = p.part_o + size_t(head) * nsplit * D + d;
+            float a = 0.f;
+            for (int s = 0; s < n_chunks; s += kMergeBatch) {
+                float v[kMergeBatch];
+#pragma unroll
+                for (int i = 0; i < kMergeBatch; ++i) v[i] = (s + i < n_chunks) ? __ldcg(po + size_t(s + i) * D) : 0.f;
+#pragma unroll
+                for (int i = 0; i < kMergeBatch; ++i) a = fmaf(mrg_w[j][(s + i) & 63], v[i], a);
+            }
+            p.out[size_t(head) * D + d] = f32_to_bf16_bits(a / stat_l[j]);
+        }
+    }
+    if (tid == 0) p.counters[g] = 0;
+}
+
 cudaError_t attn_gqa_dispatch(const AttnParams& p, cudaStream_t stream, bool pdl) {
     const int G = p.hq / p.hkv;
-    const dim3 grid(p.hkv, p.nsplit, p.batch > 1 ? p.batch : 1), block(kAttnThreads);
+    if (p.batch > 1) {
+        const int chunks = attn_batch_chunks(p.max_ctx);
+        if (chunks > 64) return cudaErrorInvalidValue;
+        const dim3 bgrid(p.hkv, chunks, p.batch), bblock(kAttnThreads);
+#define TFB_ATTN_BATCH(DD, GG)                                                                                 \
+        if (p.d == DD && G == GG) {                                                                            \
+            const size_t smem = size_t(4) * kSplitLen * DD * sizeof(uint16_t);                                 \
+            static bool once = false;                                                                          \
+            if (!once) {                                                                                       \
+                cudaError_t e = cudaFuncSetAttribute(attn_gqa_batch_kernel<DD, GG>,                            \
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); \
+                if (e != cudaSuccess) return e;                                                                \
+                once = true;                                                                                   \
+            }                                                                                                  \
+            return launch_kernel(attn_gqa_batch_kernel<DD, GG>, bgrid, bblock, smem, stream, pdl, p);         \
+        }
+        TFB_ATTN_BATCH(128, 1) TFB_ATTN_BATCH(128, 2) TFB_ATTN_BATCH(128, 4) TFB_ATTN_BATCH(64, 2) TFB_ATTN_BATCH(64, 1)
+#undef TFB_ATTN_BATCH
+        return cudaErrorInvalidValue;
+    }
+    const dim3 grid(p.hkv, p.nsplit), block(kAttnThreads);
 #define TFB_ATTN(DD, GG)                                                                                  \
     if (p.d == DD && G == GG) {                                                                           \
         static bool once = false;                                                                         \

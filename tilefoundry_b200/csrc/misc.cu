@@ -43,14 +43,54 @@ cudaError_t embed_launch(const uint16_t* table, const long long* ids, const long
 }
 
 // ---- RMSNorm -------------------------------------------------------------------
+// One CTA per row.  Rows of up to 8 * blockDim elements (a multiple of 8) are read once with 16-byte loads and
+// kept in registers between the sum of squares and the scaling; other widths take the two-pass form.
 template <int MODE>
 __global__ void rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gamma,
                                uint16_t* __restrict__ y, int width, float eps) {
     __shared__ float red[32];
-    pdl_trigger();
-    pdl_wait();
     const uint16_t* xr = x + size_t(blockIdx.x) * width;
     uint16_t* yr = y + size_t(blockIdx.x) * width;
+    const bool one_pass = (width & 7) == 0 && width <= 8 * int(blockDim.x) &&
+                          ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) |
+                            reinterpret_cast<uintptr_t>(gamma)) & 15) == 0;
+    if (one_pass) {
+        const int c = threadIdx.x;
+        const bool mine = c * 8 < width;
+        uint4 gv = make_uint4(0, 0, 0, 0);
+        if (mine) gv = *(reinterpret_cast<const uint4*>(gamma) + c);     // the gain does not depend on the kernel before
+        pdl_trigger();
+        pdl_wait();
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = 0.f;
+        if (mine) {
+            const uint4 v = *(reinterpret_cast<const uint4*>(xr) + c);
+            const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { f[2 * i] = bf16_lo(u[i]); f[2 * i + 1] = bf16_hi(u[i]); }
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss = fmaf(f[i], f[i], ss);
+        ss = block_sum(ss, red);
+        const float rstd = rsqrtf(ss / float(width) + eps);
+        if (mine) {
+            const uint32_t gu[4] = {gv.x, gv.y, gv.z, gv.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float g0 = bf16_lo(gu[i]), g1 = bf16_hi(gu[i]);
+                const float a = (MODE == 2) ? round_bf16(f[2 * i] * rstd) * g0 : f[2 * i] * rstd * g0;
+                const float b = (MODE == 2) ? round_bf16(f[2 * i + 1] * rstd) * g1 : f[2 * i + 1] * rstd * g1;
+                o[i] = uint32_t(f32_to_bf16_bits(a)) | (uint32_t(f32_to_bf16_bits(b)) << 16);
+            }
+            *(reinterpret_cast<uint4*>(yr) + c) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        return;
+    }
+    pdl_trigger();
+    pdl_wait();
     float ss = 0.f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         const float v = bf16_bits_to_f32(xr[i]);
@@ -67,9 +107,10 @@ __global__ void rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* _
 
 cudaError_t rmsnorm_launch(const uint16_t* x, const uint16_t* gamma, uint16_t* y, int rows, int width,
                            float eps, int mode, cudaStream_t stream, bool pdl) {
+    const int threads = (width > 2048 && width <= 4096 && (width & 7) == 0) ? 512 : 256;
     if (mode == 2)
-        return launch_kernel(rmsnorm_kernel<2>, dim3(rows), dim3(256), 0, stream, pdl, x, gamma, y, width, eps);
-    return launch_kernel(rmsnorm_kernel<1>, dim3(rows), dim3(256), 0, stream, pdl, x, gamma, y, width, eps);
+        return launch_kernel(rmsnorm_kernel<2>, dim3(rows), dim3(threads), 0, stream, pdl, x, gamma, y, width, eps);
+    return launch_kernel(rmsnorm_kernel<1>, dim3(rows), dim3(threads), 0, stream, pdl, x, gamma, y, width, eps);
 }
 
 __global__ void copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int n16) {
