@@ -335,16 +335,38 @@ def run_batch_decode(args):
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
     B, steps = args.batch, args.steps
-    max_ctx = PROMPT_TOKENS + steps + 8
+    n_prompt = args.prompt_tokens or PROMPT_TOKENS
+    max_ctx = n_prompt + max(steps, 8) + 8
     sess = Qwen3BatchSession(work.cfg, DictResource(work.device_weights(dev)), batch=B, max_ctx=max_ctx, device=dev)
-    prompts = torch.randint(0, work.cfg.vocab_size, (B, PROMPT_TOKENS), generator=torch.Generator().manual_seed(1))
-    sess.generate(prompts, 8)                                   # capture + warm-up
-    sampler = ClockSampler(0)
-    gen = sess.generate(prompts, steps)
-    clocks = sampler.stop()
+    prompts = torch.randint(0, work.cfg.vocab_size, (B, n_prompt), generator=torch.Generator().manual_seed(1))
+    if args.skip_prompt_walk:
+        # the profiler-sized case: positions set straight to the end of the prompt (cache rows below stay zero, the
+        # bytes moved are the same), a few eager steps and no graph, so a capture meets few launches before its own
+        from tilefoundry_b200.engine.session import Generated
+        sess.reset(prompts)
+        sess.pos.fill_(n_prompt - 1)
+        for _ in range(3):
+            sess.step()
+        sess.pos.fill_(n_prompt - 1)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sampler = ClockSampler(0)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(steps):
+            sess.step()
+        end.record()
+        torch.cuda.synchronize()
+        sess.check_status()
+        clocks = sampler.stop()
+        gen = Generated([], start.elapsed_time(end) / 1e3, 0.0, 1)
+    else:
+        sess.generate(prompts, 8)                               # capture + warm-up
+        sampler = ClockSampler(0)
+        gen = sess.generate(prompts, steps)
+        clocks = sampler.stop()
     W, kv = sess.weight_bytes(), sess.kv_bytes_per_position()
     # bytes(t) = weights + batch * kv_per_position * (context read + the entry written)
-    total_bytes = sum(W + B * kv * (PROMPT_TOKENS + t + 1) for t in range(steps))
+    total_bytes = sum(W + B * kv * (n_prompt + t + 1) for t in range(steps))
     peak, kind = peaks()
     achieved = total_bytes / gen.seconds / 1e9
     print(json.dumps({
@@ -352,10 +374,12 @@ def run_batch_decode(args):
         "unit": "tok/s", "batch": B, "steps": steps, "ms_per_step": gen.seconds * 1e3 / steps,
         "prompt_ms_per_step": gen.prompt_seconds * 1e3 / max(gen.prompt_steps - 1, 1),
         "dtype": "bf16", "data": "synthetic", "gpu_launches": sess.launches_per_step * steps,
-        "config": {"workload": work.describe.replace("batch 1", f"batch {B}"), "l2": "inputs larger than L2"},
+        "launch": "eager, prompt walk skipped" if args.skip_prompt_walk else "one captured graph per step",
+        "config": {"workload": work.describe.replace("batch 1", f"batch {B}").replace("64-token", f"{n_prompt}-token"),
+                   "l2": "inputs larger than L2"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": kind, "weights_bytes_per_step": W, "kv_bytes_per_step_at_end":
-                     B * kv * (PROMPT_TOKENS + steps)},
+                     B * kv * (n_prompt + steps)},
         "clocks": clocks}))
 
 
@@ -508,6 +532,12 @@ def main():
     ap.add_argument("--batch", type=int, default=1,
                     help="decode this many independent Qwen3-1.7B sequences per step (2..32) on the tensor-core "
                          "projections, print one JSON line and exit")
+    ap.add_argument("--prompt-tokens", type=int, default=0,
+                    help="with --batch: prompt length per sequence (default 64); a long prompt puts the timed steps at a "
+                         "long context, e.g. for a profiler capture of the batched attention kernel")
+    ap.add_argument("--skip-prompt-walk", action="store_true",
+                    help="with --batch: start at the end of the prompt without walking it and launch eagerly (for profiler "
+                         "captures; the number includes host launch time)")
     ap.add_argument("--dominant-only", action="store_true",
                     help="build the session, time only the dominant kernel over every layer's weights, print it and exit "
                          "(the small case a profiler capture of that kernel runs)")
