@@ -384,7 +384,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attn_gqa_batch_kernel(AttnPar
     __shared__ __align__(16) float vec[NV + 1][D];
     __shared__ float gain[2][D];
     __shared__ float rot[2][D];
-    __shared__ float sc[G][kSplitLen];
+    __shared__ __align__(16) float sc[G][kSplitLen];
     __shared__ float stat_m[G], stat_l[G], rescale[G];
     __shared__ float mrg_w[G][64];
     __shared__ int s_last;
@@ -420,16 +420,33 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attn_gqa_batch_kernel(AttnPar
     const int n_chunks = (n_tiles + kBatchTiles - 1) / kBatchTiles;
     const bool owner = (t1 == n_tiles);                  // this CTA's last tile holds the new position
 
+    // A thread copies the same 16-byte piece of rows r_first, r_first + NSG, ...; when a page holds whole tiles
+    // (page_size a multiple of 64) the tile has one page and the source address is one multiply-add per row.
+    const int piece = tid % LPP, r_first = tid / LPP;
+    const size_t row_stride = size_t(p.hkv) * D;
+    const bool tile_in_page = (p.page_size % kSplitLen) == 0;
     auto fetch = [&](int tile, int buf) {                // cached rows of a tile -> ring slot (the new row comes from vec[])
         const int base = tile * kSplitLen;
         const int rows = min(kSplitLen, pos - base);     // rows below pos are in the cache
-        for (int c = tid; c < rows * LPP; c += kAttnThreads) {
-            const int r = c / LPP, piece = c % LPP;
-            const int pp = base + r;
-            const int page = p.block_table[pp / p.page_size];
-            const size_t off = ((size_t(page) * p.page_size + (pp % p.page_size)) * p.hkv + g) * D + piece * 8;
-            cp_async16(&kbuf[buf * TILE + r * D + piece * 8], p.k_pool + off);
-            cp_async16(&vbuf[buf * TILE + r * D + piece * 8], p.v_pool + off);
+        uint16_t* kd = kbuf + buf * TILE + piece * 8;
+        uint16_t* vd = vbuf + buf * TILE + piece * 8;
+        if (tile_in_page) {
+            const int page = p.block_table[base / p.page_size];
+            const size_t off0 = (size_t(page) * p.page_size + (base % p.page_size)) * row_stride + size_t(g) * D + piece * 8;
+#pragma unroll
+            for (int r = r_first; r < kSplitLen; r += NSG)
+                if (r < rows) {
+                    cp_async16(kd + r * D, p.k_pool + off0 + r * row_stride);
+                    cp_async16(vd + r * D, p.v_pool + off0 + r * row_stride);
+                }
+        } else {
+            for (int r = r_first; r < rows; r += NSG) {
+                const int pp = base + r;
+                const int page = p.block_table[pp / p.page_size];
+                const size_t off = (size_t(page) * p.page_size + (pp % p.page_size)) * row_stride + size_t(g) * D + piece * 8;
+                cp_async16(kd + r * D, p.k_pool + off);
+                cp_async16(vd + r * D, p.v_pool + off);
+            }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -594,17 +611,24 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attn_gqa_batch_kernel(AttnPar
             for (int j = 0; j < G; ++j) { a[j][0] = 0.f; a[j][1] = 0.f; }
             const int r_begin = rg * ROWS_PER_RG;
             if (r_begin < n) {
-#pragma unroll 4
-                for (int i = 0; i < ROWS_PER_RG; ++i) {
+#pragma unroll 2
+                for (int i = 0; i < ROWS_PER_RG; i += 4) {
                     const int r = r_begin + i;
                     // rows past n hold stale bytes: read them as zero bits, their probability is zero too
-                    const uint32_t v2 = r < n ? *reinterpret_cast<const uint32_t*>(&vt[r * D + 2 * dp]) : 0u;
-                    const float v_lo = bf16_lo(v2), v_hi = bf16_hi(v2);
+                    float v_lo[4], v_hi[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const uint32_t v2 = r + u < n ? *reinterpret_cast<const uint32_t*>(&vt[(r + u) * D + 2 * dp]) : 0u;
+                        v_lo[u] = bf16_lo(v2);
+                        v_hi[u] = bf16_hi(v2);
+                    }
 #pragma unroll
                     for (int j = 0; j < G; ++j) {
-                        const float pr = sc[j][r];
-                        a[j][0] = fmaf(pr, v_lo, a[j][0]);
-                        a[j][1] = fmaf(pr, v_hi, a[j][1]);
+                        const float4 pr = *reinterpret_cast<const float4*>(&sc[j][r]);   // four rows' probabilities
+                        a[j][0] = fmaf(pr.x, v_lo[0], a[j][0]); a[j][1] = fmaf(pr.x, v_hi[0], a[j][1]);
+                        a[j][0] = fmaf(pr.y, v_lo[1], a[j][0]); a[j][1] = fmaf(pr.y, v_hi[1], a[j][1]);
+                        a[j][0] = fmaf(pr.z, v_lo[2], a[j][0]); a[j][1] = fmaf(pr.z, v_hi[2], a[j][1]);
+                        a[j][0] = fmaf(pr.w, v_lo[3], a[j][0]); a[j][1] = fmaf(pr.w, v_hi[3], a[j][1]);
                     }
                 }
             }
