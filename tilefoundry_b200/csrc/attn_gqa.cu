@@ -428,7 +428,9 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attn_gqa_batch_kernel(AttnPar
     auto fetch = [&](int tile, int buf) {                // cached rows of a tile -> ring slot (the new row comes from vec[])
         const int base = tile * kSplitLen;
         const int rows = min(kSplitLen, pos - base);     // rows below pos are in the cache
-        uint16_t* kd = kbuf + buf * TILE + piece * 8;
+        // K rows are stored with their 16-byte pieces XOR-swizzled by the row's low three bits, so the score MMA's
+        // 4-byte operand loads (eight rows, one piece) fall on 32 different banks
+        uint16_t* kd = kbuf + buf * TILE;
         uint16_t* vd = vbuf + buf * TILE + piece * 8;
         if (tile_in_page) {
             const int page = p.block_table[base / p.page_size];
@@ -436,7 +438,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attn_gqa_batch_kernel(AttnPar
 #pragma unroll
             for (int r = r_first; r < kSplitLen; r += NSG)
                 if (r < rows) {
-                    cp_async16(kd + r * D, p.k_pool + off0 + r * row_stride);
+                    cp_async16(kd + r * D + ((piece ^ (r & 7)) * 8), p.k_pool + off0 + r * row_stride);
                     cp_async16(vd + r * D, p.v_pool + off0 + r * row_stride);
                 }
         } else {
@@ -444,7 +446,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attn_gqa_batch_kernel(AttnPar
                 const int pp = base + r;
                 const int page = p.block_table[pp / p.page_size];
                 const size_t off = (size_t(page) * p.page_size + (pp % p.page_size)) * row_stride + size_t(g) * D + piece * 8;
-                cp_async16(kd + r * D, p.k_pool + off);
+                cp_async16(kd + r * D + ((piece ^ (r & 7)) * 8), p.k_pool + off);
                 cp_async16(vd + r * D, p.v_pool + off);
             }
         }
@@ -535,12 +537,23 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attn_gqa_batch_kernel(AttnPar
     float o_acc[G][2];
 #pragma unroll
     for (int j = 0; j < G; ++j) { o_acc[j][0] = 0.f; o_acc[j][1] = 0.f; }
-    const int sg = tid / LPP, sl = tid % LPP;
-    float q[G][8];
+    // Scores on the tensor cores (mma.sync m16n8k16, bf16 in, f32 out): the G query heads are rows 0..G-1 of the
+    // 16-row A operand (the rest zero), a warp owns 8 positions of the tile as the B operand's columns.  A fragment
+    // of k-step ks, lane (gq, tq): a0 = q[gq][16ks + 2tq, +1], a2 = q[gq][16ks + 8 + 2tq, +1]; a1 = a3 = 0.
+    constexpr int KS = D / 16;
+    static_assert(kAttnThreads / 32 * 8 == kSplitLen, "one warp per 8 positions of a tile");
+    const int gq = lane >> 2, tq = lane & 3;
+    uint32_t qa[KS][2];
 #pragma unroll
-    for (int j = 0; j < G; ++j)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) q[j][i] = vec[j][sl * 8 + i];
+    for (int ks = 0; ks < KS; ++ks) {
+        qa[ks][0] = 0u; qa[ks][1] = 0u;
+        if (gq < G) {
+            const float* qv = vec[gq];
+            qa[ks][0] = uint32_t(f32_to_bf16_bits(qv[16 * ks + 2 * tq])) | (uint32_t(f32_to_bf16_bits(qv[16 * ks + 2 * tq + 1])) << 16);
+            qa[ks][1] = uint32_t(f32_to_bf16_bits(qv[16 * ks + 8 + 2 * tq])) |
+                        (uint32_t(f32_to_bf16_bits(qv[16 * ks + 8 + 2 * tq + 1])) << 16);
+        }
+    }
 
     for (int tile = t0; tile < t1; ++tile) {
         const int buf = (tile - t0) & 1;
@@ -554,31 +567,33 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attn_gqa_batch_kernel(AttnPar
         const int n = min(kSplitLen, total - base);      // rows of this tile, the new one included
         if (tile == n_tiles - 1)                         // the new entry goes straight into the ring slot
             for (int i = tid; i < D; i += kAttnThreads) {
-                kbuf[buf * TILE + (pos - base) * D + i] = f32_to_bf16_bits(vec[G][i]);
-                vbuf[buf * TILE + (pos - base) * D + i] = f32_to_bf16_bits(vec[G + 1][i]);
+                const int rn = pos - base;
+                kbuf[buf * TILE + rn * D + (((i >> 3) ^ (rn & 7)) << 3) + (i & 7)] = f32_to_bf16_bits(vec[G][i]);
+                vbuf[buf * TILE + rn * D + i] = f32_to_bf16_bits(vec[G + 1][i]);
             }
         __syncthreads();
         const uint16_t* kt = kbuf + buf * TILE;
         const uint16_t* vt = vbuf + buf * TILE;
-        // scores
+        // scores: warp w, positions 8w .. 8w+7.  B fragment of k-step ks, lane (gq, tq): b0 = K[8w + gq][16ks + 2tq, +1],
+        // b1 = K[8w + gq][16ks + 8 + 2tq, +1]; C fragment c0, c1 = score of head gq at positions 8w + 2tq, +1.
+        // Rows past n hold stale bytes; they only reach columns the statistics pass zeroes.
+        {
+            const int nrow = warp * 8 + gq;
+            const uint16_t* krow = kt + nrow * D + 2 * tq;
+            const int sw = nrow & 7;
+            float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
 #pragma unroll
-        for (int r0 = 0; r0 < kSplitLen; r0 += NSG) {
-            const int r = r0 + sg;
-            float kf[8];
-            if (r < n) {
-                unpack8(*reinterpret_cast<const uint4*>(&kt[r * D + sl * 8]), kf);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) kf[i] = 0.f;
+            for (int ks = 0; ks < KS; ++ks) {
+                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + (((2 * ks) ^ sw) << 3));
+                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + (((2 * ks + 1) ^ sw) << 3));
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+                             "{%0, %1, %2, %3};"
+                             : "+f"(c0), "+f"(c1), "+f"(c2), "+f"(c3)
+                             : "r"(qa[ks][0]), "r"(0u), "r"(qa[ks][1]), "r"(0u), "r"(b0), "r"(b1));
             }
-#pragma unroll
-            for (int j = 0; j < G; ++j) {
-                float s = 0.f;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) s = fmaf(q[j][i], kf[i], s);
-#pragma unroll
-                for (int o = LPP / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                if (sl == 0 && r < n) sc[j][r] = s;
+            if (gq < G) {
+                sc[gq][warp * 8 + 2 * tq] = c0;
+                sc[gq][warp * 8 + 2 * tq + 1] = c1;
             }
         }
         __syncthreads();
