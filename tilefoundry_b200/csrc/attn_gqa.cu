@@ -385,7 +385,8 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attn_gqa_batch_kernel(AttnPar
     __shared__ float gain[2][D];
     __shared__ float rot[2][D];
     __shared__ __align__(16) float sc[G][kSplitLen];
-    __shared__ float stat_m[G], stat_l[G], rescale[G];
+    __shared__ __align__(16) float prob[(kAttnThreads / 32) * G * kSplitLen];   // each warp's copy of a tile's probabilities
+    __shared__ float stat_m[G], stat_l[G];
     __shared__ float mrg_w[G][64];
     __shared__ int s_last;
 
@@ -514,7 +515,6 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attn_gqa_batch_kernel(AttnPar
             vec[vi][e] = r;
         }
     }
-    if (tid < G) { stat_m[tid] = -INFINITY; stat_l[tid] = 0.f; }
     __syncthreads();
 
     if (owner) {                                         // append this token's entry to the cache
@@ -555,14 +555,18 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attn_gqa_batch_kernel(AttnPar
         }
     }
 
+    // Two barriers per tile.  #1: this tile's copies have landed (and every warp has left the tile before, so the
+    // other ring slot, sc[] and each warp's prob[] may be rewritten) -- the next tile's copies are requested right
+    // after it.  #2: the scores of all 64 positions are in sc[].  The softmax statistics are then computed by every
+    // warp for itself (lane-uniform registers, its own copy of the probabilities), which saves the third barrier and
+    // the phase in which only G warps worked.
+    float m_run[G], l_run[G];
+#pragma unroll
+    for (int j = 0; j < G; ++j) { m_run[j] = -INFINITY; l_run[j] = 0.f; }
+    float* my_prob = prob + warp * (G * kSplitLen);
     for (int tile = t0; tile < t1; ++tile) {
         const int buf = (tile - t0) & 1;
-        if (tile + 1 < t1) {
-            fetch(tile + 1, buf ^ 1);
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         const int base = tile * kSplitLen;
         const int n = min(kSplitLen, total - base);      // rows of this tile, the new one included
         if (tile == n_tiles - 1)                         // the new entry goes straight into the ring slot
@@ -571,7 +575,8 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attn_gqa_batch_kernel(AttnPar
                 kbuf[buf * TILE + rn * D + (((i >> 3) ^ (rn & 7)) << 3) + (i & 7)] = f32_to_bf16_bits(vec[G][i]);
                 vbuf[buf * TILE + rn * D + i] = f32_to_bf16_bits(vec[G + 1][i]);
             }
-        __syncthreads();
+        __syncthreads();                                 // #1
+        if (tile + 1 < t1) fetch(tile + 1, buf ^ 1);
         const uint16_t* kt = kbuf + buf * TILE;
         const uint16_t* vt = vbuf + buf * TILE;
         // scores: warp w, positions 8w .. 8w+7.  B fragment of k-step ks, lane (gq, tq): b0 = K[8w + gq][16ks + 2tq, +1],
@@ -596,29 +601,24 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attn_gqa_batch_kernel(AttnPar
                 sc[gq][warp * 8 + 2 * tq + 1] = c1;
             }
         }
-        __syncthreads();
-        // running softmax statistics; rows past n get probability 0 so the PV loop needs no bound
-        for (int j = warp; j < G; j += NWARP) {
-            float m = -INFINITY;
-            for (int i = lane; i < n; i += 32) m = fmaxf(m, sc[j][i]);
-            m = warp_max(m);
-            const float old_m = stat_m[j];
-            const float new_m = fmaxf(old_m, m);
-            float l = 0.f;
-            for (int i = lane; i < kSplitLen; i += 32) {
-                const float e = i < n ? __expf(sc[j][i] - new_m) : 0.f;
-                sc[j][i] = e;
-                l += e;
-            }
-            l = warp_sum(l);
-            if (lane == 0) {
-                const float c = old_m == -INFINITY ? 0.f : __expf(old_m - new_m);
-                rescale[j] = c;
-                stat_l[j] = stat_l[j] * c + l;
-                stat_m[j] = new_m;
-            }
+        __syncthreads();                                 // #2
+        // running softmax statistics, per warp; rows past n get probability 0 so the PV loop needs no bound
+        float resc[G];
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+            const float s0 = lane < n ? sc[j][lane] : -INFINITY;
+            const float s1 = lane + 32 < n ? sc[j][lane + 32] : -INFINITY;
+            const float new_m = fmaxf(m_run[j], warp_max(fmaxf(s0, s1)));
+            const float e0 = lane < n ? __expf(s0 - new_m) : 0.f;
+            const float e1 = lane + 32 < n ? __expf(s1 - new_m) : 0.f;
+            my_prob[j * kSplitLen + lane] = e0;
+            my_prob[j * kSplitLen + lane + 32] = e1;
+            const float l = warp_sum(e0 + e1);
+            resc[j] = m_run[j] == -INFINITY ? 0.f : __expf(m_run[j] - new_m);
+            l_run[j] = l_run[j] * resc[j] + l;
+            m_run[j] = new_m;
         }
-        __syncthreads();
+        __syncwarp();
         // probability-weighted V
         {
             float a[G][2];
@@ -639,7 +639,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attn_gqa_batch_kernel(AttnPar
                     }
 #pragma unroll
                     for (int j = 0; j < G; ++j) {
-                        const float4 pr = *reinterpret_cast<const float4*>(&sc[j][r]);   // four rows' probabilities
+                        const float4 pr = *reinterpret_cast<const float4*>(&my_prob[j * kSplitLen + r]);   // four rows
                         a[j][0] = fmaf(pr.x, v_lo[0], a[j][0]); a[j][1] = fmaf(pr.x, v_hi[0], a[j][1]);
                         a[j][0] = fmaf(pr.y, v_lo[1], a[j][0]); a[j][1] = fmaf(pr.y, v_hi[1], a[j][1]);
                         a[j][0] = fmaf(pr.z, v_lo[2], a[j][0]); a[j][1] = fmaf(pr.z, v_hi[2], a[j][1]);
@@ -649,12 +649,15 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attn_gqa_batch_kernel(AttnPar
             }
 #pragma unroll
             for (int j = 0; j < G; ++j) {
-                const float c = rescale[j];
-                o_acc[j][0] = o_acc[j][0] * c + a[j][0];
-                o_acc[j][1] = o_acc[j][1] * c + a[j][1];
+                o_acc[j][0] = o_acc[j][0] * resc[j] + a[j][0];
+                o_acc[j][1] = o_acc[j][1] * resc[j] + a[j][1];
             }
         }
-        __syncthreads();                                 // the slot and sc[] are free for the tile after next
+    }
+    __syncthreads();                                     // every warp has left the ring: it becomes pv_red
+    if (warp == 0 && lane == 0) {
+#pragma unroll
+        for (int j = 0; j < G; ++j) { stat_m[j] = m_run[j]; stat_l[j] = l_run[j]; }
     }
 
     // the row groups' partial sums meet in the (now idle) ring: pv_red[rg][j][d]
