@@ -118,3 +118,34 @@ def test_recurrent_and_moe_entry_points_reject_bad_arguments(so):
     assert so.tfb_router_select(None, P, P, None, P, 300, 8, 1, 0, None) == EINVAL      # more experts than a warp holds
     assert so.tfb_router_select(None, P, P, None, P, 256, 8, 2, 0, None) == EINVAL      # unknown mode
     assert so.tfb_status_string(EINVAL) and so.tfb_status_string(ECAPACITY)
+
+
+def test_several_sequence_step_rejects_bad_arguments(so):
+    tc = dict(w=P, x=P, y=P, status=P, m=32, n=6144, k=2048, pdl=0, swiglu=1)
+    call = lambda **kw: so.tfb_gemm_small_m(C.byref(lib.GemmSmallMArgs(**{**tc, **kw})), None)
+    assert call(n=100) == EINVAL                            # the SwiGLU form pairs 64 gate rows with 64 up rows
+    assert call(residual=P) == EINVAL                       # and has no residual
+    assert so.tfb_gemm_small_m_swiglu_splits(6144, 2048) in (1, 2, 4, 8)
+    assert so.tfb_gemm_small_m_splits(2048, 2048) in (1, 2, 4, 8)
+    assert so.tfb_gemm_small_m_swiglu_splits(0, 2048) == 0
+
+    attn = dict(qkv=P, cos_table=P, sin_table=P, pos=P, k_pool=P, v_pool=P, block_table=P, out=P, part_o=P, part_ml=P,
+                counters=P, hq=16, hkv=8, d=128, rotary_dim=128, page_size=64, table_len=4, max_ctx=256, max_pos=256,
+                eps=1e-6, scale=0.1, norm_mode=0, pdl=0, batch=4)
+    assert so.tfb_attn_gqa_decode_noalloc(C.byref(lib.AttnGqaArgs(**attn)), None) == ECAPACITY   # built-in scratch: one sequence
+    assert so.tfb_attn_gqa_decode(C.byref(lib.AttnGqaArgs(**{**attn, "batch": 70000})), None) == EINVAL
+
+    layers = (lib.Qwen3BatchLayer * 1)()
+    step = dict(layers=layers, n_layers=1, batch=32, hidden=2048, hq=16, hkv=8, d=128, inter=6144, pdl=1, vocab=151936,
+                eps=1e-6, scale=0.088, w_embed=P, gamma_final=P, w_head=P, cos_table=P, sin_table=P, max_pos=2176,
+                page_size=64, table_len=34, max_ctx=2176, block_table=P, tokens=P, pos=P, n_prompt=64, max_tokens=2177,
+                hidden_buf=P, norm_buf=P, qkv_buf=P, attn_buf=P, act_buf=P, logits=P, part_o=P, part_ml=P, counters=P,
+                status=P, pick_val=P, pick_idx=P)
+    scall = lambda **kw: so.tfb_qwen3_batch_decode_step(C.byref(lib.Qwen3BatchStepArgs(**{**step, **kw})), None)
+    assert scall(batch=0) == EINVAL and scall(batch=33) == EINVAL        # 1..32 sequences
+    assert scall(logits=None) == EINVAL                                  # the pick reads the logits
+    assert scall(status=None) == EINVAL and scall(norm_buf=None) == EINVAL
+    assert scall(inter=6100) == EINVAL                                   # tile shapes
+    assert scall(table_len=8) == ECAPACITY                               # the block table does not cover max_ctx
+    assert scall(max_tokens=4000) == ECAPACITY
+    assert so.tfb_qwen3_batch_decode_step(None, None) == EINVAL
