@@ -166,6 +166,14 @@ typedef struct {
     int32_t index_offset;   /* vocabulary parallel: w is rows [index_offset, index_offset + n) of the head */
     float* pair_out;        /* optional f32[2]: (best logit, global index) for an all-gather; suppresses the
                                token / position update, which tfb_pick_finalize then does */
+    /* temperature > 0: the token is a draw from softmax(logits / temperature) by the Gumbel-max rule
+     * (argmax of logit / T - log(-log u)), u from a counter-based generator keyed by (seed, *pos or 0, global
+     * vocabulary index): reproducible, and the same token on any number of vocabulary shards.  With pair_out the
+     * pair's value is the perturbed score.  temperature <= 0: greedy.  Not with TFB_KERNEL_RING (falls back to the
+     * default kernel).  On-device sampling as in examples/granite_4_0_h_small-cuda/kernels/granite.cu:712-797
+     * (own generator: the draw is keyed by the vocabulary index, not by a launch geometry). */
+    float temperature;
+    uint64_t seed;
 } tfb_lm_head_args;
 TFB_API int32_t tfb_lm_head_scratch_entries(int32_t n);
 TFB_API int tfb_lm_head_argmax(const tfb_lm_head_args* args, tfb_stream_t stream);
@@ -289,6 +297,8 @@ typedef struct {
     int32_t kernel;         /* TFB_KERNEL_* for every projection of the step */
     int64_t* picked;        /* optional [1]: the token this step picked, whatever the prompt says */
     uint32_t* chain_sync;   /* TFB_KERNEL_CHAIN: u32[4] zeroed once ([0..1] grid barrier, [2] status: non-zero if a wait gave up) */
+    float temperature;      /* > 0: sample each token from softmax(logits / temperature) (see tfb_lm_head_args); else greedy */
+    uint64_t seed;
 } tfb_qwen3_step_args;
 TFB_API int tfb_qwen3_decode_step(const tfb_qwen3_step_args* args, tfb_stream_t stream);
 

@@ -208,7 +208,8 @@ int tfb_lm_head_argmax(const tfb_lm_head_args* a, tfb_stream_t stream) {
     TFB_REQUIRE((a->prologue >= TFB_NORM_NONE && a->prologue <= TFB_NORM_CAST_THEN_GAIN) || a->prologue == TFB_NORM_F32_INPUT, TFB_EINVAL);
     TFB_REQUIRE(a->prologue == TFB_NORM_NONE || a->prologue == TFB_NORM_F32_INPUT || a->gamma, TFB_EINVAL);
     TFB_REQUIRE(aligned16(a->w) && aligned16(a->x) && (!a->gamma || aligned16(a->gamma)), TFB_EALIGN);
-    if (a->kernel == TFB_KERNEL_RING && a->prologue != TFB_NORM_F32_INPUT && !a->pair_out && tfb::gemv_stream_supported(a->n, a->k)) {
+    if (a->kernel == TFB_KERNEL_RING && a->prologue != TFB_NORM_F32_INPUT && !a->pair_out && !(a->temperature > 0.f) &&
+        tfb::gemv_stream_supported(a->n, a->k)) {
         tfb::GemvParams g = {};
         g.w = static_cast<const uint4*>(a->w);
         g.x = static_cast<const uint16_t*>(a->x);
@@ -242,6 +243,8 @@ int tfb_lm_head_argmax(const tfb_lm_head_args* a, tfb_stream_t stream) {
     p.trace = next_trace();
     p.pair_out = a->pair_out;
     p.index_offset = a->index_offset;
+    p.temperature = a->temperature > 0.f ? a->temperature : 0.f;
+    p.seed = a->seed;
     return done(tfb::lm_head_dispatch(p, a->prologue, S(stream), a->pdl != 0));
 }
 
@@ -434,6 +437,7 @@ int tfb_qwen3_decode_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
     h.x_scale = 1.f; h.out_scale = 1.f; h.pdl = pdl; h.kernel = a->kernel; h.self_prefetch = spf;
     h.token_out = a->picked;
     h.tokens = a->tokens; h.pos = a->pos; h.n_prompt = a->n_prompt; h.max_tokens = a->max_tokens;
+    h.temperature = a->temperature; h.seed = a->seed;
     return tfb_lm_head_argmax(&h, stream);
 }
 

@@ -94,6 +94,8 @@ struct HeadParams {
     unsigned long long* trace;
     float* pair_out;            // optional f32[2]: (best logit, index + index_offset) instead of the token update
     int index_offset;
+    float temperature;          // > 0: Gumbel-max sample from softmax(logits / temperature); else greedy
+    unsigned long long seed;
 };
 int lm_head_ctas(int n);
 cudaError_t lm_head_dispatch(const HeadParams& p, int norm_mode, cudaStream_t stream, bool pdl);

@@ -136,16 +136,34 @@ cudaError_t residual_add_launch(const uint16_t* a, const uint16_t* b, uint16_t* 
     return launch_kernel(residual_add_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, pdl, a, b, out, n, scale);
 }
 
-// ---- lm_head + greedy pick -----------------------------------------------------
+// ---- lm_head + greedy pick (or Gumbel-max sample) ------------------------------
 // Algorithmic bytes per launch = n*k*2 (the head matrix, read once).  Each CTA
 // reduces its rows' bf16-rounded logits to one (max, lowest index) pair; the last
 // CTA to finish (atomic ticket) reduces the pairs, writes the token and advances
 // the generation state.  Ties resolve to the lowest index, as torch.argmax does.
+// With temperature > 0 the pairs are over logit / T + Gumbel noise instead: a draw
+// from softmax(logits / T) in the same single launch.
 constexpr int kHeadRows = 4, kHeadWarps = 8, kHeadUnroll = 2;
 int lm_head_ctas(int n) { return (n + kHeadRows * kHeadWarps - 1) / (kHeadRows * kHeadWarps); }
 
 __device__ __forceinline__ void argmax_merge(float& v, int& i, float ov, int oi) {
     if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+}
+
+// Gumbel-max sampling: argmax_i(logit_i / T + G_i) with G_i = -log(-log(u_i)) is a draw from softmax(logits / T),
+// so sampling is the greedy pick over perturbed scores -- no normalisation pass.  u_i comes from a counter-based
+// generator (the splitmix64 finaliser over seed, step and the GLOBAL vocabulary index), so a vocabulary-parallel
+// head draws the same token as one GPU.  u = (k + 0.5) / 2^23 with k the top 23 bits: never 0 or 1.  The two
+// logarithms run in double precision (one lane per row, so their cost does not matter): the fast single-precision
+// log loses the tail u -> 1 where the winning variates live.
+__device__ __forceinline__ float gumbel_variate(unsigned long long seed, int step, int index) {
+    unsigned long long z = seed + 0x9E3779B97F4A7C15ull * (unsigned long long)(unsigned(index) + 1u) +
+                           0xD1B54A32D192ED03ull * (unsigned long long)(unsigned(step) + 1u);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    const double u = (double(unsigned(z >> 41)) + 0.5) * (1.0 / 8388608.0);
+    return float(-log(-log(u)));
 }
 
 // f32 hidden state with an f32 gain, rounded to bf16 once on its way into the product (mode 5).
@@ -183,6 +201,8 @@ __global__ void __launch_bounds__(kHeadWarps * 32) lm_head_kernel(const HeadPara
     pdl_trigger();
     pdl_wait();
     trace_waited(p.trace);
+    // the draw of a step is keyed by its position word (read before any CTA can have advanced it)
+    const int sample_step = (p.temperature > 0.f && p.pos) ? *p.pos : 0;
     if (NORM_MODE == 5)
         stage_head_f32(reinterpret_cast<const float*>(p.x), reinterpret_cast<const float*>(p.gamma), xs, red, p.k, p.eps);
     else
@@ -198,12 +218,16 @@ __global__ void __launch_bounds__(kHeadWarps * 32) lm_head_kernel(const HeadPara
     }
     float best = -INFINITY;
     int best_i = 0x7fffffff;
+    float gumbel = 0.f;                                   // lane r: the variate of this warp's row r
+    if (p.temperature > 0.f && lane < rows_valid) gumbel = gumbel_variate(p.seed, sample_step, row0 + lane + p.index_offset);
 #pragma unroll
     for (int r = 0; r < kHeadRows; ++r) {
         const float s = round_bf16(warp_sum(acc[r]) * p.out_scale);
         if (r < rows_valid) {
             if (lane == 0 && p.logits) p.logits[row0 + r] = f32_to_bf16_bits(s);
-            argmax_merge(best, best_i, s, row0 + r);
+            float score = s;
+            if (p.temperature > 0.f) score = __fdiv_rn(s, p.temperature) + __shfl_sync(0xffffffffu, gumbel, r);
+            argmax_merge(best, best_i, score, row0 + r);
         }
     }
     if (lane == 0) { wv[warp] = best; wi[warp] = best_i; }

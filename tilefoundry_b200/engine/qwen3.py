@@ -33,7 +33,7 @@ def pack_layer(w: dict) -> dict:
 class Qwen3Session(DecodeSession):
     def __init__(self, cfg: Qwen3Config, resource, *, max_ctx: int = 2176, device="cuda:0",
                  keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True,
-                 l2_prefetch: int = 0, kernel: int = 0):
+                 l2_prefetch: int = 0, kernel: int = 0, temperature: float = 0.0, seed: int = 0):
         if not torch.cuda.is_available():
             raise RuntimeError("Qwen3Session needs a CUDA device; there is no CPU path")
         lib.load()
@@ -104,7 +104,7 @@ class Qwen3Session(DecodeSession):
             part_ml=lib.ptr(self.part_ml), counters=lib.ptr(self.counters), head_val=lib.ptr(self.head_val),
             head_idx=lib.ptr(self.head_idx), hidden_trace=lib.ptr(self.trace),
             pdl=int(pdl), l2_prefetch=int(l2_prefetch), kernel=int(kernel), picked=lib.ptr(self.picked),
-            chain_sync=lib.ptr(self.chain_sync))
+            chain_sync=lib.ptr(self.chain_sync), temperature=float(temperature), seed=int(seed) & (2 ** 64 - 1))
         self.graph = None
         self._graph_prompt = None
         #: kernels one step enqueues (embed + 5 per layer + lm_head [+ trace copies and final norm])

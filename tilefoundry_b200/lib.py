@@ -34,7 +34,8 @@ class LmHeadArgs(C.Structure):
                 ("scratch_val", _vp), ("scratch_idx", _vp), ("counter", _vp),
                 ("n", _i32), ("k", _i32), ("prologue", _i32),
                 ("eps", _f32), ("x_scale", _f32), ("out_scale", _f32), ("pdl", _i32),
-                ("tokens", _vp), ("pos", _vp), ("n_prompt", _i32), ("max_tokens", _i32), ("kernel", _i32), ("self_prefetch", _i32), ("index_offset", _i32), ("pair_out", _vp)]
+                ("tokens", _vp), ("pos", _vp), ("n_prompt", _i32), ("max_tokens", _i32), ("kernel", _i32), ("self_prefetch", _i32), ("index_offset", _i32), ("pair_out", _vp),
+                ("temperature", _f32), ("seed", _u64)]
 
 
 class AttnGqaArgs(C.Structure):
@@ -62,7 +63,7 @@ class Qwen3StepArgs(C.Structure):
                 ("hidden_buf", _vp), ("qkv_buf", _vp), ("attn_buf", _vp), ("act_buf", _vp), ("logits", _vp),
                 ("part_o", _vp), ("part_ml", _vp), ("counters", _vp), ("head_val", _vp), ("head_idx", _vp),
                 ("hidden_trace", _vp), ("pdl", _i32), ("l2_prefetch", _i32), ("kernel", _i32), ("picked", _vp),
-                ("chain_sync", _vp)]
+                ("chain_sync", _vp), ("temperature", _f32), ("seed", _u64)]
 
 
 class GemvChainArgs(C.Structure):
