@@ -221,6 +221,11 @@ typedef struct {
      * pos (and rope_pos) [batch], block_table [batch][table_len] into the shared pools, k_new_out/v_new_out
      * [batch][hkv*d], part_o/part_ml/counters sized batch times the single-sequence scratch. */
     int32_t batch;
+    /* chunk != 0 (with batch > 1): the `batch` entries are consecutive tokens of ONE sequence (prompt processing):
+     * pos[i] = pos[0] + i, block_table is that sequence's single row.  A token attends to the rows before it, some of
+     * which belong to the same chunk, so the chunk takes two launches: chunk = 1 writes every token's K/V row into the
+     * cache and nothing else, chunk = 2 (after it) computes the attention. */
+    int32_t chunk;
 } tfb_attn_gqa_args;
 TFB_API int32_t tfb_attn_splits(int32_t max_ctx);
 TFB_API int tfb_attn_gqa_decode(const tfb_attn_gqa_args* args, tfb_stream_t stream);
@@ -622,6 +627,38 @@ typedef struct {
     void* hidden_trace;     /* optional [n_layers+1][batch][hidden] bf16 */
 } tfb_qwen3_batch_step_args;
 TFB_API int tfb_qwen3_batch_decode_step(const tfb_qwen3_batch_step_args* args, tfb_stream_t stream);
+
+/* ---- Qwen3-architecture prompt processing, one chunk of <= 32 consecutive tokens of one sequence -----------
+ * Runs the layer stack for the chunk's tokens at once: projections on the tensor cores (tfb_gemm_small_m, M = m),
+ * attention in the chunk form of tfb_attn_gqa_decode (every token attends to the cached rows before it; two
+ * launches per layer, see `chunk` there).  Leaves the tokens' K/V rows in the cache and the residual stream of
+ * each token in hidden_buf; no head, no pick: a prompt's logits are not needed until its last token, which the
+ * decode step processes.  The reference walks a prompt token by token
+ * (tests/models/orchestrator/causal_lm/generation.py:56-61); per token the arithmetic and its rounding points are
+ * those of that walk, only the order of the f32 sums inside a projection differs.  Launches: 1 + 8 * n_layers. */
+typedef struct {
+    const tfb_qwen3_batch_layer* layers; /* host array [n_layers] */
+    int32_t n_layers, m, hidden, hq, hkv, d, inter, pdl;
+    float eps, scale;
+    int64_t vocab;
+    const void* w_embed;
+    const void* cos_table;
+    const void* sin_table;
+    int32_t max_pos, page_size, table_len, max_ctx;
+    const int32_t* block_table; /* [table_len]: the sequence's pages */
+    const int64_t* ids;         /* device [m]: the chunk's token ids */
+    const int32_t* pos_rows;    /* device [m]: first position + i (first + m <= max_ctx) */
+    void* hidden_buf;           /* [m][hidden] */
+    void* norm_buf;             /* [m][hidden] */
+    void* qkv_buf;              /* [m][(hq+2hkv)*d] */
+    void* attn_buf;             /* [m][hq*d] */
+    void* act_buf;              /* [m][inter] */
+    float* part_o;              /* attention split scratch, m times the single-sequence size */
+    float* part_ml;
+    uint32_t* counters;         /* [m*hkv] zeroed once */
+    uint32_t* status;           /* as in tfb_gemm_small_m */
+} tfb_qwen3_prefill_args;
+TFB_API int tfb_qwen3_prefill_chunk(const tfb_qwen3_prefill_args* args, tfb_stream_t stream);
 
 /* ================= f32-activation family (Qwen3.5-35B-A3B) =================
  * The reference's Qwen3.5 example keeps activations, recurrent state and KV cache in f32 and its contracted

@@ -296,7 +296,9 @@ int tfb_attn_gqa_decode(const tfb_attn_gqa_args* a, tfb_stream_t stream) {
     p.batch = a->batch > 1 ? a->batch : 1;
     p.qkv_stride = (a->hq + 2 * a->hkv) * a->d;
     p.out_stride = a->hq * a->d;
-    p.bt_stride = a->table_len;
+    p.bt_stride = a->chunk ? 0 : a->table_len;
+    p.append_only = a->chunk;
+    TFB_REQUIRE(a->chunk >= 0 && a->chunk <= 2 && (a->chunk == 0 || a->batch > 1), TFB_EINVAL);
     TFB_REQUIRE(p.batch <= 65535, TFB_EINVAL);
     const int G = a->hq / a->hkv;
     TFB_REQUIRE(G == 1 || G == 2 || (G == 4 && a->d == 128), TFB_EINVAL);

@@ -420,6 +420,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attn_gqa_batch_kernel(AttnPar
     const int t1 = min(t0 + kBatchTiles, n_tiles);
     const int n_chunks = (n_tiles + kBatchTiles - 1) / kBatchTiles;
     const bool owner = (t1 == n_tiles);                  // this CTA's last tile holds the new position
+    if (p.append_only == 1 && !owner) return;
 
     // A thread copies the same 16-byte piece of rows r_first, r_first + NSG, ...; when a page holds whole tiles
     // (page_size a multiple of 64) the tile has one page and the source address is one multiply-add per row.
@@ -453,7 +454,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attn_gqa_batch_kernel(AttnPar
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    fetch(t0, 0);
+    if (p.append_only != 1) fetch(t0, 0);
 
     // ---- this token's q (G heads), k, v for KV head g: as in attn_gqa_kernel ----
     const int rd = p.rotary_dim, half = rd >> 1;
@@ -517,7 +518,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attn_gqa_batch_kernel(AttnPar
     }
     __syncthreads();
 
-    if (owner) {                                         // append this token's entry to the cache
+    if (owner && p.append_only != 2) {                   // append this token's entry to the cache
         const int page = p.block_table[pos / p.page_size];
         const size_t base = ((size_t(page) * p.page_size + (pos % p.page_size)) * p.hkv + g) * D;
         for (int i = tid; i < D; i += kAttnThreads) {
@@ -528,6 +529,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attn_gqa_batch_kernel(AttnPar
             if (p.v_new_out) p.v_new_out[size_t(g) * D + i] = vb;
         }
     }
+    if (p.append_only == 1) return;
 
     // PV mapping: thread (dp, rg) owns the output pair d = 2dp, 2dp+1 of every query head for the rows of row
     // group rg of each tile (one 4-byte V load feeds 2G products); the RG partial sums meet once, after the last

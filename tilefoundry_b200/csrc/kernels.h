@@ -69,6 +69,7 @@ struct AttnParams {
     // several sequences in one launch (blockIdx.z = sequence): element strides of qkv / out, row stride of the
     // block table; pos, rope_pos and the split scratch are indexed by sequence.  batch <= 1: one sequence.
     int batch, qkv_stride, out_stride, bt_stride;
+    int append_only;             // batch form: 1 = only write each entry's new K/V row into the cache, 2 = attend without writing it
 };
 int attn_splits(int max_ctx);
 cudaError_t attn_gqa_dispatch(const AttnParams& p, cudaStream_t stream, bool pdl);

@@ -22,11 +22,14 @@ from .session import DecodeSession, Generated  # noqa: F401
 def pack_layer(w: dict) -> dict:
     """Authored ``(1, in, out)`` projections -> kernel layout ``[out, in]`` with q|k|v fused."""
     t = lambda name: w[name][0].t().contiguous()
+    gate_up = torch.cat([t("w_gate"), t("w_up")], dim=0).contiguous()     # gate rows, then up rows
+    inter = gate_up.shape[0] // 2
     return {
         "gamma_in": w["gamma_in"].contiguous(), "gamma_post": w["gamma_post"].contiguous(),
         "gamma_q": w["gamma_q"].contiguous(), "gamma_k": w["gamma_k"].contiguous(),
         "w_qkv": torch.cat([t("w_q"), t("w_k"), t("w_v")], dim=0).contiguous(),
-        "w_o": t("w_o"), "w_gate": t("w_gate"), "w_up": t("w_up"), "w_down": t("w_down"),
+        "w_o": t("w_o"), "w_gate_up": gate_up, "w_gate": gate_up[:inter], "w_up": gate_up[inter:],
+        "w_down": t("w_down"),
     }
 
 
@@ -123,3 +126,32 @@ class Qwen3Session(DecodeSession):
     def step(self) -> None:
         """Enqueue one decode step on the current stream."""
         lib.check(lib.load().tfb_qwen3_decode_step(C.byref(self.args), lib.stream()), "tfb_qwen3_decode_step")
+
+    def prefill(self, n_tokens: int) -> None:
+        """Process positions ``pos .. pos + n_tokens - 1`` of the token history in chunks of up to 32 tokens
+        (tensor-core projections, chunked attention) instead of one decode step each, and advance the position.
+        Nothing is picked: use it for prompt tokens whose successor is already known."""
+        from .qwen3_prefill import Qwen3Prefill
+        if getattr(self, "_prefill", None) is None:
+            self._prefill = Qwen3Prefill(self)
+        self._prefill.run(n_tokens)
+
+    def generate(self, prompt_ids, max_new: int, use_graph: bool = True, prefill: bool = False):
+        """As DecodeSession.generate; with ``prefill`` the prompt (all but its last token) is processed in chunks."""
+        if not prefill:
+            return super().generate(prompt_ids, max_new, use_graph)
+        self.reset(prompt_ids)
+        if self.n_prompt + max_new > self.max_ctx + 1:
+            raise ValueError(f"{self.n_prompt}+{max_new} tokens exceed capacity {self.max_ctx}")
+        if use_graph and self.graph is None:
+            self.capture()
+        start, mid, end = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        start.record()
+        self.prefill(self.n_prompt - 1)
+        mid.record()
+        self.run(max_new, use_graph)
+        end.record()
+        torch.cuda.synchronize()
+        self._prefill.check_status()
+        out = self.tokens[self.n_prompt: self.n_prompt + max_new].tolist()
+        return Generated(out, mid.elapsed_time(end) / 1e3, start.elapsed_time(mid) / 1e3, self.n_prompt)

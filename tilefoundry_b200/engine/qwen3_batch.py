@@ -45,7 +45,7 @@ class Qwen3BatchSession:
             names = ("gamma_in", "w_q", "w_k", "w_v", "gamma_q", "gamma_k", "w_o", "gamma_post",
                      "w_gate", "w_up", "w_down")
             packed = pack_layer({n: to(sub.load(n)) for n in names})
-            packed["w_gate_up"] = torch.cat([packed.pop("w_gate"), packed.pop("w_up")], dim=0).contiguous()
+            packed.pop("w_gate"); packed.pop("w_up")          # views of w_gate_up, which this step reads whole
             self.layers.append(packed)
 
         cos, sin = rope_tables(cfg, "cpu")

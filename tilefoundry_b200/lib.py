@@ -45,7 +45,7 @@ class AttnGqaArgs(C.Structure):
                 ("hq", _i32), ("hkv", _i32), ("d", _i32), ("rotary_dim", _i32),
                 ("page_size", _i32), ("table_len", _i32), ("max_ctx", _i32), ("max_pos", _i32),
                 ("eps", _f32), ("scale", _f32), ("norm_mode", _i32), ("pdl", _i32),
-                ("prefetch", _vp), ("prefetch_bytes", _u64), ("batch", _i32)]
+                ("prefetch", _vp), ("prefetch_bytes", _u64), ("batch", _i32), ("chunk", _i32)]
 
 
 class Qwen3Layer(C.Structure):
@@ -91,6 +91,17 @@ class Qwen3BatchStepArgs(C.Structure):
                 ("logits", _vp), ("part_o", _vp), ("part_ml", _vp), ("counters", _vp),
                 ("status", _vp), ("pick_val", _vp), ("pick_idx", _vp), ("picked", _vp),
                 ("hidden_trace", _vp)]
+
+
+class Qwen3PrefillArgs(C.Structure):
+    _fields_ = [("layers", C.POINTER(Qwen3BatchLayer)),
+                ("n_layers", _i32), ("m", _i32), ("hidden", _i32), ("hq", _i32), ("hkv", _i32), ("d", _i32),
+                ("inter", _i32), ("pdl", _i32), ("eps", _f32), ("scale", _f32), ("vocab", _i64),
+                ("w_embed", _vp), ("cos_table", _vp), ("sin_table", _vp),
+                ("max_pos", _i32), ("page_size", _i32), ("table_len", _i32), ("max_ctx", _i32),
+                ("block_table", _vp), ("ids", _vp), ("pos_rows", _vp),
+                ("hidden_buf", _vp), ("norm_buf", _vp), ("qkv_buf", _vp), ("attn_buf", _vp), ("act_buf", _vp),
+                ("part_o", _vp), ("part_ml", _vp), ("counters", _vp), ("status", _vp)]
 
 
 class MoeAllreduceArgs(C.Structure):
@@ -236,6 +247,7 @@ SYMBOLS = {
     "tfb_gemm_small_m_swiglu_splits": (_i32, [_i32, _i32]),
     "tfb_gemm_small_m": (_i32, [C.POINTER(GemmSmallMArgs), _vp]),
     "tfb_qwen3_batch_decode_step": (_i32, [C.POINTER(Qwen3BatchStepArgs), _vp]),
+    "tfb_qwen3_prefill_chunk": (_i32, [C.POINTER(Qwen3PrefillArgs), _vp]),
     "tfb_lm_head_scratch_entries": (_i32, [_i32]),
     "tfb_lm_head_argmax": (_i32, [C.POINTER(LmHeadArgs), _vp]),
     "tfb_attn_splits": (_i32, [_i32]),
