@@ -490,6 +490,17 @@ def run_ours(args):
                        "frac_of_8TBs_nominal": step_gbs / 8000.0},
     }
 
+    # prompt processing, outside the metric: the 64-token prompt walked one decode step per token against the same
+    # prompt in chunks of 32 tokens on the tensor-core projections (Qwen3 only)
+    prompt_info = None
+    if world == 1 and work.key == "qwen3_1_7b":
+        walk = sess.generate(prompt, 4)
+        sess.generate(prompt, 4, prefill=True)                                  # warm-up: buffers, tensor maps
+        chunked = sess.generate(prompt, 4, prefill=True)
+        prompt_info = {"tokens": PROMPT_TOKENS, "walk_ms": walk.prompt_seconds * 1e3,
+                       "chunked_prefill_ms": chunked.prompt_seconds * 1e3,
+                       "same_continuation": walk.tokens == chunked.tokens}
+
     base = None
     if world == 1 and not args.no_cpu:
         base = cpu_baseline(work, 32 if work.cpu_layers is None else 8, PROMPT_TOKENS if work.cpu_layers is None else 8)
@@ -508,7 +519,7 @@ def run_ours(args):
         "e2e": {"value": units * K / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 8,
                 "d2h_bytes_per_step": 8},
         "gpu_launches": sess.launches_per_step * K,
-        "clocks": clocks, "roofline": roofline, "cpu_baseline": base,
+        "clocks": clocks, "roofline": roofline, "cpu_baseline": base, "prompt": prompt_info,
     }
     print(json.dumps(line), flush=True)
     if world > 1:
