@@ -45,17 +45,14 @@ class Qwen3Session(DecodeSession):
         dev = self.device
         to = lambda t: t.to(dev)
 
-        root = {n: to(resource.load(n)) for n in ("w_embed", "gamma_final", "w_head")}
-        self.w_embed = root["w_embed"].contiguous()
-        head = root["w_head"].t().contiguous()
-        self.w_head = self.w_embed if torch.equal(head, self.w_embed) else head
-        self.gamma_final = root["gamma_final"].contiguous()
-        self.layers = []
-        for i in range(cfg.num_hidden_layers):
-            sub = resource.subtree(f"layer{i}")
-            names = ("gamma_in", "w_q", "w_k", "w_v", "gamma_q", "gamma_k", "w_o", "gamma_post",
-                     "w_gate", "w_up", "w_down")
-            self.layers.append(pack_layer({n: to(sub.load(n)) for n in names}))
+        from .packed import PackedQwen3, pack
+        # a resource speaks the authored names and is packed here; a PackedQwen3 (engine/packed.py) is already in
+        # the kernels' layout, e.g. read from a file written by save_packed
+        packed = (resource if isinstance(resource, PackedQwen3) else pack(cfg, resource)).to(dev)
+        self.w_embed = packed.root["w_embed"]
+        self.w_head = self.w_embed if packed.root["w_head"] is None else packed.root["w_head"]
+        self.gamma_final = packed.root["gamma_final"]
+        self.layers = packed.layers
 
         cos, sin = rope_tables(cfg, "cpu")
         self.max_pos = min(cfg.max_position_embeddings, max(self.max_ctx, 1))
