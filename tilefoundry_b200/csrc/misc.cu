@@ -156,7 +156,7 @@ __device__ __forceinline__ void argmax_merge(float& v, int& i, float ov, int oi)
 // head draws the same token as one GPU.  u = (k + 0.5) / 2^23 with k the top 23 bits: never 0 or 1.  The two
 // logarithms run in double precision (one lane per row, so their cost does not matter): the fast single-precision
 // log loses the tail u -> 1 where the winning variates live.
-__device__ __forceinline__ float gumbel_variate(unsigned long long seed, int step, int index) {
+__device__ __noinline__ float gumbel_variate(unsigned long long seed, int step, int index) {
     unsigned long long z = seed + 0x9E3779B97F4A7C15ull * (unsigned long long)(unsigned(index) + 1u) +
                            0xD1B54A32D192ED03ull * (unsigned long long)(unsigned(step) + 1u);
     z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
@@ -181,7 +181,7 @@ __device__ __forceinline__ void stage_head_f32(const float* __restrict__ x, cons
 }
 
 template <int NORM_MODE>
-__global__ void __launch_bounds__(kHeadWarps * 32) lm_head_kernel(const HeadParams p) {
+__global__ void __launch_bounds__(kHeadWarps * 32, 4) lm_head_kernel(const HeadParams p) {
     extern __shared__ __align__(16) float smem[];
     float* xs = smem;
     float* red = smem + p.k;
