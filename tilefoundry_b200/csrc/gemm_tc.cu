@@ -35,7 +35,7 @@
 
 namespace tfb {
 
-constexpr int TC_BM = 128, TC_BN = 32, TC_BK = 64, TC_STAGES = 4, TC_THREADS = 192;
+constexpr int TC_BM = 128, TC_BN = 32, TC_BK = 64, TC_STAGES = 5, TC_THREADS = 192;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2, TC_B_BYTES = TC_BN * TC_BK * 2;
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 20;
 
