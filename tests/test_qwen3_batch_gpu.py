@@ -71,10 +71,10 @@ def test_swiglu_projection_rejects_bad_shapes(dev):
 def test_batched_attention_equals_per_sequence_launches(dev):
     from tilefoundry_b200 import lib
     from tilefoundry_b200.engine import paged_kv
-    B, HQ, HKV, D, max_ctx = 5, 16, 8, 128, 320
+    B, HQ, HKV, D, max_ctx = 6, 16, 8, 128, 1600
     g = torch.Generator().manual_seed(9)
     cfg = q.Qwen3Config(hidden_size=256, num_attention_heads=HQ, num_key_value_heads=HKV, head_dim=D,
-                        intermediate_size=512, vocab_size=1024, num_hidden_layers=1, max_position_embeddings=512)
+                        intermediate_size=512, vocab_size=1024, num_hidden_layers=1, max_position_embeddings=2048)
     cos, sin = q.rope_tables(cfg)
     cos, sin = cos.to(dev), sin.to(dev)
     table = paged_kv.block_table(B, max_ctx, device=dev)
@@ -83,7 +83,8 @@ def test_batched_attention_equals_per_sequence_launches(dev):
     qkv = torch.randn(B, (HQ + 2 * HKV) * D, generator=g).to(BF).to(dev)
     gq = (1 + 0.1 * torch.randn(D, generator=g)).to(BF).to(dev)
     gk = (1 + 0.1 * torch.randn(D, generator=g)).to(BF).to(dev)
-    pos = torch.tensor([0, 63, 64, 200, 319], dtype=torch.int32, device=dev)     # ragged contexts
+    # ragged contexts: one tile, a page edge, one chunk of 8 tiles exactly, and two that need the merge of chunks
+    pos = torch.tensor([0, 63, 64, 511, 512, 1599], dtype=torch.int32, device=dev)
     nsplit = lib.attn_splits(max_ctx)
 
     def launch(batch, qkv_t, pos_t, table_t, out_t, kp, vp):
@@ -109,7 +110,7 @@ def test_batched_attention_equals_per_sequence_launches(dev):
     ks, vs = k_pool.clone(), v_pool.clone()
     for b in range(B):
         launch(1, qkv[b], pos[b:b + 1], table[b:b + 1].contiguous(), out_s[b], ks, vs)
-    # the batched kernel groups the softmax partials by 256 positions, the single one by 64: same sums, other order
+    # the batched kernel groups the softmax partials by 512 positions, the single one by 64: same sums, other order
     assert_ulps(out_b.cpu(), out_s.cpu(), 2, "batched vs per-sequence attention")
     assert torch.equal(kb, ks) and torch.equal(vb, vs)       # every sequence appended to its own pages only
     assert not torch.equal(kb, k_pool)

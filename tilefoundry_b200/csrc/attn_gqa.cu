@@ -362,10 +362,11 @@ __global__ void __launch_bounds__(kAttnThreads) attn_gqa_kernel(const AttnParams
 // layer), so this form is built for bandwidth rather than for one round trip: grid (hkv, chunks, sequences),
 // a CTA walks up to kBatchTiles consecutive 64-position tiles of one KV head of one sequence through a
 // double-buffered cp.async ring (the next tile lands while this one is scored), carrying a running (max, sum)
-// and rescaled PV accumulators, so the q/k normalisation + rotation is paid once per 256 positions and a
-// context of 2048 leaves 8 partials per head to merge instead of 32.  Arithmetic and rounding points per
+// and rescaled PV accumulators, so the q/k normalisation + rotation is paid once per 512 positions and a
+// context of 2048 leaves 4 partials per head to merge instead of 32 (measured: 2, 4, 6, 8, 16 tiles per CTA give
+// 2.90, 2.70, 2.67, 2.67, 2.75 ms per batch-32 step).  Arithmetic and rounding points per
 // element are those of attn_gqa_kernel; only the grouping of the softmax partials differs.
-constexpr int kBatchTiles = 4;
+constexpr int kBatchTiles = 8;
 
 int attn_batch_chunks(int max_ctx) { return (attn_splits(max_ctx) + kBatchTiles - 1) / kBatchTiles; }
 
