@@ -391,6 +391,8 @@ typedef struct {
     void* hidden_trace;     /* optional [n_layers+1][hidden] */
     int64_t* picked;
     int32_t pdl;
+    float temperature;        /* > 0: sample each token from softmax(logits / temperature) (see tfb_lm_head_args); else greedy */
+    uint64_t seed;
 } tfb_minicpm3_step_args;
 TFB_API int tfb_minicpm3_decode_step(const tfb_minicpm3_step_args* args, tfb_stream_t stream);
 
@@ -535,6 +537,8 @@ typedef struct {
     float* partial;           /* f32 [2][hidden] */
     float* pair;              /* f32 [2] */
     float* gathered;          /* f32 [ep_world][2] */
+    float temperature;        /* > 0: sample each token from softmax(logits / temperature) (see tfb_lm_head_args); else greedy */
+    uint64_t seed;
 } tfb_granite_step_args;
 TFB_API int tfb_granite_decode_step(const tfb_granite_step_args* args, tfb_stream_t stream);
 /* One piece of the step, so a sharded caller can interleave its collectives: part 0 embed; 1 layer `layer` up to
@@ -819,6 +823,8 @@ typedef struct {
     float* pair;              /* f32 [2] */
     int32_t expert_prefetch;  /* non-zero: the selection kernel asks L2 for the selected experts' weights */
     int32_t reserved;
+    float temperature;        /* > 0: sample each token from softmax(logits / temperature) (see tfb_lm_head_args); else greedy */
+    uint64_t seed;
 } tfb_qwen35_step_args;
 TFB_API int tfb_qwen35_decode_step(const tfb_qwen35_step_args* args, tfb_stream_t stream);
 /* One piece of the step, so a sharded caller can put its exchange kernels between them: part 0 embed; part 1 layer

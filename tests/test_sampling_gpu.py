@@ -131,3 +131,35 @@ def test_session_sampling_is_reproducible_and_seeded(dev):
     step = int(a.pos) - 1
     logits = a.logits.float().cpu().numpy()
     _expect(logits, 1.0, 42, step, one[-1])
+
+
+@pytest.mark.parametrize("model", ["minicpm3", "granite", "qwen3_5"])
+def test_other_sessions_sample_too(dev, model):
+    """The other three decode steps hand temperature and seed to the same head kernel."""
+    from tests import parity
+    if model == "minicpm3":
+        from tilefoundry_b200.authored import minicpm3_4b as a
+        from tilefoundry_b200.engine.minicpm3 import MiniCPM3Session as S
+        cfg = a.MINICPM3_TINY
+        weights = a.tie_head(random_weights(a.build(cfg), seed=9, std=0.05))
+    elif model == "granite":
+        from tilefoundry_b200.authored import granite_4_0_h_small as a
+        from tilefoundry_b200.engine.granite import GraniteSession as S
+        cfg = a.GRANITE_TINY
+        weights = random_weights(a.build(cfg), seed=9, std=0.05, overrides=a.weight_overrides)
+    else:
+        from tilefoundry_b200.authored import qwen3_5_35b_a3b as a
+        from tilefoundry_b200.engine.qwen3_5 import Qwen35Session as S
+        cfg = a.QWEN3_5_TINY
+        weights = random_weights(a.build(cfg), seed=9, std=0.05, overrides=a.weight_overrides)
+    res = DictResource(parity.cuda_weights(weights, dev))
+    prompt = torch.randint(0, cfg.vocab_size, (10,), generator=torch.Generator().manual_seed(3))
+    sess = S(cfg, res, max_ctx=96, device=dev, keep_logits=True, temperature=0.9, seed=77)
+    one = sess.generate(prompt, 40, use_graph=True).tokens
+    two = sess.generate(prompt, 40, use_graph=False).tokens
+    assert one == two
+    step = int(sess.pos) - 1
+    _expect(sess.logits.float().cpu().numpy().reshape(-1), 0.9, 77, step, one[-1])
+    greedy = S(cfg, res, max_ctx=96, device=dev).generate(prompt, 40).tokens
+    other = S(cfg, res, max_ctx=96, device=dev, temperature=0.9, seed=78).generate(prompt, 40).tokens
+    assert one != greedy and one != other

@@ -278,6 +278,7 @@ static int granite_part(const tfb_granite_step_args* a, int part, int layer, tfb
     h.n = vslice; h.k = H; h.prologue = TFB_NORM_F32GAIN; h.eps = a->eps;
     h.x_scale = 1.f; h.out_scale = a->logits_scale; h.pdl = pdl; h.token_out = a->picked;
     h.tokens = a->tokens; h.pos = a->pos; h.n_prompt = a->n_prompt; h.max_tokens = a->max_tokens;
+    h.temperature = a->temperature; h.seed = a->seed;
     return tfb_lm_head_argmax(&h, stream);
 }
 

@@ -131,6 +131,7 @@ int tfb_minicpm3_decode_step(const tfb_minicpm3_step_args* a, tfb_stream_t strea
     h.x_scale = -a->logits_div; h.out_scale = 1.f; h.pdl = pdl;
     h.token_out = a->picked;
     h.tokens = a->tokens; h.pos = a->pos; h.n_prompt = a->n_prompt; h.max_tokens = a->max_tokens;
+    h.temperature = a->temperature; h.seed = a->seed;
     return tfb_lm_head_argmax(&h, stream);
 }
 

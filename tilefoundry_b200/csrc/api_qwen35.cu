@@ -281,6 +281,7 @@ static int qwen35_part(const tfb_qwen35_step_args* a, int part, int layer, tfb_s
     h.n = vslice; h.k = H; h.prologue = TFB_NORM_F32_INPUT; h.eps = a->eps;
     h.x_scale = 1.f; h.out_scale = 1.f; h.pdl = pdl; h.token_out = a->picked;
     h.tokens = a->tokens; h.pos = a->pos; h.n_prompt = a->n_prompt; h.max_tokens = a->max_tokens;
+    h.temperature = a->temperature; h.seed = a->seed;
     return tfb_lm_head_argmax(&h, stream);
 }
 

@@ -27,7 +27,7 @@ def pack_mixer(kind: str, w: dict) -> dict:
 class GraniteSession(DecodeSession):
     def __init__(self, cfg: GraniteConfig, resource, *, max_ctx: int = 2176, device="cuda:0",
                  keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True, group=None,
-                 collectives: str | None = None):
+                 collectives: str | None = None, temperature: float = 0.0, seed: int = 0):
         """*group*: a ``torch.distributed`` process group (NCCL) to shard the MoE blocks and the head over;
         ``None`` runs everything on this GPU.  *collectives*: ``"peer"`` = the two exchange steps as single kernels
         over NVLink peer memory (symmetric memory), ``"nccl"`` = NCCL all-reduce / all-gather followed by the
@@ -104,6 +104,7 @@ class GraniteSession(DecodeSession):
                 setattr(s, name, lib.ptr(layer.get(name)))
         as_bf16 = lambda v: float(torch.tensor(v, dtype=bf))
         self.args = lib.GraniteStepArgs(
+            temperature=float(temperature), seed=int(seed) & (2 ** 64 - 1),
             layers=self._layer_structs, n_layers=L, hidden=H, nh=cfg.mamba_n_heads, pd=cfg.mamba_d_head,
             ns=cfg.mamba_d_state, ng=cfg.mamba_n_groups, conv_width=cfg.mamba_d_conv, hq=HQ, hkv=HKV, d=D,
             experts=E, top_k=K, inter=I, shared_inter=IS, vocab=V, eps=cfg.rms_norm_eps,

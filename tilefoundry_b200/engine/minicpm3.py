@@ -28,7 +28,8 @@ LAYER_WEIGHTS = ("gamma_in", "w_q_a", "gamma_q_a", "w_q_b", "w_kv_a", "gamma_kv_
 
 class MiniCPM3Session(DecodeSession):
     def __init__(self, cfg: MiniCPM3Config, resource, *, max_ctx: int = 2176, device="cuda:0",
-                 keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True):
+                 keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True,
+                 temperature: float = 0.0, seed: int = 0):
         if not torch.cuda.is_available():
             raise RuntimeError("MiniCPM3Session needs a CUDA device; there is no CPU path")
         lib.load()
@@ -75,6 +76,7 @@ class MiniCPM3Session(DecodeSession):
                 setattr(s, name, lib.ptr(layer[name]))
         as_bf16 = lambda v: float(torch.tensor(v, dtype=bf))    # the authored step holds these as bf16 tensors
         self.args = lib.MiniCPM3StepArgs(
+            temperature=float(temperature), seed=int(seed) & (2 ** 64 - 1),
             layers=self._layer_structs, n_layers=len(self.layers), hidden=H, heads=NH, q_lora=cfg.q_lora_rank,
             kv_lora=cfg.kv_lora_rank, nope=cfg.qk_nope_head_dim, rope=cfg.qk_rope_head_dim, v=VD, inter=I, vocab=V,
             eps=cfg.rms_norm_eps, lora_eps=cfg.lora_eps, scale=as_bf16(QK ** -0.5), embed_scale=cfg.scale_emb,

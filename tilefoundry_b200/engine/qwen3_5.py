@@ -46,7 +46,8 @@ MOE_W = ("gamma_post", "w_gate", "w_up", "w_down", "w_shared_gate", "w_shared_up
 class Qwen35Session(DecodeSession):
     def __init__(self, cfg: Qwen35Config, resource, *, max_ctx: int | None = None, device="cuda:0",
                  keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True, group=None,
-                 collectives: str | None = None, expert_prefetch: bool = False):
+                 collectives: str | None = None, expert_prefetch: bool = False,
+                 temperature: float = 0.0, seed: int = 0):
         """*group*: a ``torch.distributed`` process group to shard the MoE blocks (expert e on rank ``e % n``, the
         shared expert sliced) and the head (vocabulary slices) over; ``None`` runs everything on this GPU.  The
         exchange steps run as single kernels over NVLink peer memory (*collectives* ``"peer"``, required).
@@ -133,6 +134,7 @@ class Qwen35Session(DecodeSession):
             for name, _ in lib.Qwen35Layer._fields_[2:]:
                 setattr(s, name, lib.ptr(layer.get(name)))
         self.args = lib.Qwen35StepArgs(
+            temperature=float(temperature), seed=int(seed) & (2 ** 64 - 1),
             layers=self._layer_structs, n_layers=L, pdl=int(pdl), table=lib.ptr(self.table_w),
             gamma_final=lib.ptr(self.gamma_final), w_head=lib.ptr(self.w_head), cos_table=lib.ptr(self.cos),
             sin_table=lib.ptr(self.sin), tokens=lib.ptr(self.tokens), pos=lib.ptr(self.pos), n_prompt=0,

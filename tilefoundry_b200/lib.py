@@ -141,7 +141,8 @@ class MiniCPM3StepArgs(C.Structure):
                 ("block_table", _vp), ("tokens", _vp), ("pos", _vp), ("n_prompt", _i32), ("max_tokens", _i32),
                 ("hidden_buf", _vp), ("qkv_a_buf", _vp), ("q_up_buf", _vp), ("kv_up_buf", _vp), ("attn_buf", _vp),
                 ("act_buf", _vp), ("logits", _vp), ("part_o", _vp), ("part_ml", _vp), ("counters", _vp),
-                ("head_val", _vp), ("head_idx", _vp), ("hidden_trace", _vp), ("picked", _vp), ("pdl", _i32)]
+                ("head_val", _vp), ("head_idx", _vp), ("hidden_trace", _vp), ("picked", _vp), ("pdl", _i32),
+                ("temperature", _f32), ("seed", _u64)]
 
 
 class MoeDownArgs(C.Structure):
@@ -170,7 +171,8 @@ class GraniteStepArgs(C.Structure):
                 ("router_idx", _vp), ("router_w", _vp), ("inner_buf", _vp), ("shared_buf", _vp), ("logits", _vp),
                 ("part_o", _vp), ("part_ml", _vp), ("counters", _vp), ("head_val", _vp), ("head_idx", _vp),
                 ("hidden_trace", _vp), ("idx_trace", _vp), ("picked", _vp), ("pdl", _i32),
-                ("ep_rank", _i32), ("ep_world", _i32), ("partial", _vp), ("pair", _vp), ("gathered", _vp)]
+                ("ep_rank", _i32), ("ep_world", _i32), ("partial", _vp), ("pair", _vp), ("gathered", _vp),
+                ("temperature", _f32), ("seed", _u64)]
 
 
 #: every symbol ``include/tfb200.h`` declares: name -> (restype, argtypes)
@@ -224,7 +226,8 @@ class Qwen35StepArgs(C.Structure):
                 ("router_logits", _vp), ("router_idx", _vp), ("router_w", _vp), ("inner_buf", _vp), ("part_o", _vp),
                 ("part_ml", _vp), ("counters", _vp), ("head_val", _vp), ("head_idx", _vp), ("logits", _vp),
                 ("picked", _vp), ("hidden_trace", _vp), ("idx_trace", _vp), ("ep_rank", _i32), ("ep_world", _i32),
-                ("partial", _vp), ("pair", _vp), ("expert_prefetch", _i32), ("reserved", _i32)]
+                ("partial", _vp), ("pair", _vp), ("expert_prefetch", _i32), ("reserved", _i32),
+                ("temperature", _f32), ("seed", _u64)]
 
 
 class RouterSelectArgs(C.Structure):
