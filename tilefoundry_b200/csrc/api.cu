@@ -190,7 +190,7 @@ int tfb_gemm_small_m(const tfb_gemm_small_m_args* a, tfb_stream_t stream) {
     tfb::TcParams p = {};
     p.M = a->m; p.N = a->n; p.K = a->k; p.swiglu = a->swiglu != 0;
     p.splits = p.swiglu ? tfb::gemm_tc_splits_swiglu(a->n, a->k) : tfb::gemm_tc_splits(a->n, a->k);
-    p.partial = a->partial; p.tickets = a->tickets; p.status = a->status;
+    p.status = a->status;
     p.y = static_cast<uint16_t*>(a->y); p.residual = static_cast<const uint16_t*>(a->residual);
     return done(tfb::gemm_tc_launch(a->w, a->x, p, S(stream), a->pdl != 0));
 }

@@ -244,7 +244,6 @@ __global__ void __launch_bounds__(TC_THREADS, 2) gemm_tc_kernel(const __grid_con
         }
     } else {                                                            // ---- epilogue: warps 2..5 ----
         const int quad = warp & 3;                                      // the TMEM lane quadrant this warp may read
-        const int n = tile * TC_BM + quad * 32 + lane;
         bool ok = nsteps > 0 ? mbar_wait(&t->accum, 0) : true;
         if (!ok) { t->aborted = 1; atomicExch(p.status, 3u); }
         uint32_t v[32];
@@ -272,7 +271,6 @@ __global__ void __launch_bounds__(TC_THREADS, 2) gemm_tc_kernel(const __grid_con
             // park this split's tile as red[m][r] in the first weight stage: every load into it has landed and
             // every MMA that read it has completed once the accumulator barrier fires
             float* red = reinterpret_cast<float*>(a_tiles);
-            (void)n;
 #pragma unroll
             for (int m = 0; m < 32; ++m) red[m * TC_BM + quad * 32 + lane] = __uint_as_float(v[m]);
         }
@@ -359,7 +357,6 @@ cudaError_t gemm_tc_launch(const void* w, const void* x, TcParams p, cudaStream_
         return cudaErrorInvalidValue;
     p.ksteps = p.K / TC_BK;
     const int tiles = p.swiglu ? (p.N + 63) / 64 : (p.N + TC_BM - 1) / TC_BM;
-    p.ntot = p.swiglu ? tiles * TC_BM : p.N;
     const size_t smem = 1024 + size_t(TC_STAGES) * (TC_A_BYTES + TC_B_BYTES) + sizeof(TcSmemTail);
     static bool once = false;
     if (!once) {

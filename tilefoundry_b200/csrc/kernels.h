@@ -315,13 +315,10 @@ cudaError_t gemv_chain_launch(ChainParams& p, cudaStream_t stream, bool pdl, siz
 
 // ---- small-batch projection on tcgen05 tensor cores (gemm_tc.cu) ----
 struct TcParams {
-    float* partial;              // unused
     uint16_t* y;                 // bf16 [M][N]
     const uint16_t* residual;    // optional bf16 [M][N]
-    unsigned* tickets;           // unused
     unsigned* status;            // u32, set non-zero if a bounded wait gave up
     int M, N, K, ksteps, splits;
-    int ntot;                    // accumulator rows over all tiles: N, or tiles * 128 in the SwiGLU form
     int swiglu;                  // 1: w holds [gate rows; up rows] (2N rows), y[M][N] = bf16(silu(bf16 g)) * bf16 u
 };
 int gemm_tc_splits(int n, int k);
