@@ -71,17 +71,30 @@ def compare_caches(want, sess, total):
         assert_close_at_scale(v_got, v_ref[:, :total], f"layer {li} V cache")
 
 
+class WalkStep:
+    """One teacher-forced evaluator step of a root -> layer -> (mixer | moe -> router) model."""
+    __slots__ = ("step", "before", "logits", "hiddens", "picks", "margins", "after", "router_inputs")
+
+    def __init__(self, **kw):
+        for k, v in kw.items():
+            setattr(self, k, v)
+
+    def __iter__(self):                       # (step, caches before, logits, hiddens, picks, margins, caches after)
+        return iter((self.step, self.before, self.logits, self.hiddens, self.picks, self.margins, self.after))
+
+
 def nested_walk(ref, cfg_kinds, forced, steps):
     """Teacher-forced oracle walk of a root -> layer -> (mixer | moe -> router) model, one step at a time.
-    Yields ``(step, caches_before, logits, hidden per layer, routing indices per layer, routing margin per
-    layer, caches_after)``; the margin is the relative gap between the last selected expert's probability and
-    the best one left out -- a routing pick inside the arithmetic noise shows as a margin near zero."""
+    Yields a ``WalkStep``: the caches before and after, logits, hidden state after every layer, routing indices
+    per layer, the routing margin per layer and the router's own input per layer.  The margin is the gap
+    between the router logit of the last selected expert and the best one left out -- a routing pick inside
+    the arithmetic noise shows as a margin near zero, an exact tie as zero."""
     from tilefoundry_b200.authored.granite_4_0_h_small import _with_cache
     caches = ref.init_caches()
     for step in range(steps):
         token_ids, layer_args, caches_in = ref.prepare_inputs_for_generation(forced[: step + 1], step, caches)
         hidden = ref.embed(token_ids)
-        fresh, hiddens, picks, margins = [], [], [], []
+        fresh, hiddens, picks, margins, router_inputs = [], [], [], [], []
         for layer, margs, cache in zip(ref.modules, layer_args, caches_in):
             mixed, *state = layer.mixer(hidden, *_with_cache(layer.mixer, margs, cache))
             attended = layer.residual_add(hidden, mixed)
@@ -91,11 +104,25 @@ def nested_walk(ref, cfg_kinds, forced, steps):
             fresh.append(tuple(state))
             hiddens.append(hidden.reshape(-1))
             picks.append(idx.reshape(-1))
+            router_inputs.append(tokens)
             w_r = layer.moe.router.constants["w_router"]
             w_r = w_r if w_r.shape[0] == tokens.shape[-1] else w_r.t()          # authored as (in, out) or (out, in)
             logits = torch.matmul(tokens.to(w_r.dtype), w_r).float().reshape(-1)
             top = torch.topk(logits, idx.numel() + 1).values
             margins.append(float(top[-2] - top[-1]))
         after = ref.append_cache(caches, tuple(fresh))
-        yield step, caches, ref.lm_head(ref.final_rms_norm(hidden)), hiddens, picks, margins, after
+        yield WalkStep(step=step, before=caches, logits=ref.lm_head(ref.final_rms_norm(hidden)), hiddens=hiddens,
+                       picks=picks, margins=margins, after=after, router_inputs=router_inputs)
         caches = after
+
+
+def routing_on_evaluator_inputs(twin, walk_step, where):
+    """Every layer's router run through the twin on the very vector the evaluator's router saw: the selected
+    experts must be the evaluator's, bit for bit; a different set is admissible only on an exact tie between
+    the last expert taken and the first left out (margin 0), where the order is not determined."""
+    for li, (tokens, want, margin) in enumerate(zip(walk_step.router_inputs, walk_step.picks, walk_step.margins)):
+        router = getattr(twin, f"layer{li}").moe.router
+        _, got = router.routing(tokens.to(next(iter(router._bound.values())).device))
+        got = got.reshape(-1).cpu()
+        if sorted(got.tolist()) != sorted(want.tolist()):
+            assert margin == 0.0, f"{where} layer {li}: experts {got.tolist()} != {want.tolist()}, margin {margin:.4g}"

@@ -65,6 +65,13 @@ def test_attention_rejects_bad_geometry(so):
     assert call(hq=15) == EINVAL                            # heads must divide
     assert call(table_len=2) == ECAPACITY                   # the block table does not cover max_ctx
     assert call(out=None) == EINVAL
+    # the allocation-free form validates the same way before it touches its stream: more KV heads than query heads
+    # (a ticket clear of 128 words would run past its 64-word region) is refused with nothing queued
+    noalloc = lambda **kw: so.tfb_attn_gqa_decode_noalloc(
+        C.byref(lib.AttnGqaArgs(**{**base, "part_o": None, "part_ml": None, "counters": None, **kw})), None)
+    assert noalloc(hq=64, hkv=128) == EINVAL
+    assert noalloc(hq=15) == EINVAL and noalloc(out=None) == EINVAL and noalloc(table_len=2) == ECAPACITY
+    assert noalloc(batch=2) == ECAPACITY                    # the built-in scratch holds one sequence
     gated = dict(proj=P, gamma_q=P, gamma_k=P, cos_table=P, sin_table=P, pos=P, k_pool=P, v_pool=P, block_table=P, out=P,
                  part_o=P, part_ml=P, counters=P, hq=16, hkv=2, d=256, rotary_dim=64, page_size=64, table_len=64, max_ctx=4096,
                  max_pos=4096, eps=1e-6, scale=0.0625, pdl=0)

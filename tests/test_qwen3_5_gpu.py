@@ -24,16 +24,29 @@ def dev():
     return torch.device("cuda:0")
 
 
-@pytest.fixture(scope="module")
-def sides(dev):
+# The published widths on a stack cut to three Gated DeltaNet layers and one gated-attention layer and a
+# 4096-entry vocabulary: hidden 2048, 16 k / 32 v heads x 128, 16 q / 2 kv heads x 256 with 64 rotary dims, 256
+# experts top-8 of 512 + the shared expert.  Every kernel is instantiated by these widths, not by the depth, so
+# this is the configuration the benchmark runs.
+WIDE = qa.truncated(qa.QWEN3_5_35B_A3B, n_layers=4, vocab=4096, max_ctx=256)
+CONFIGS = {"tiny": (qa.QWEN3_5_TINY, 0.05), "wide": (WIDE, 0.02)}
+
+
+@pytest.fixture(scope="module", params=["tiny", "wide"])
+def sides(request, dev):
+    """(config, evaluator side, twin, device weights); pytest groups the tests by configuration, so each
+    configuration's weights are drawn once and dropped before the next is built."""
     from tilefoundry_b200.twins.qwen3_5_35b_a3b import make_twin
-    cfg = qa.QWEN3_5_TINY
+    cfg, std = CONFIGS[request.param]
     mod = qa.build(cfg)
-    weights = random_weights(mod, seed=3, std=0.05, overrides=qa.weight_overrides)
+    weights = random_weights(mod, seed=3, std=std, overrides=qa.weight_overrides)
+    on_dev = parity.cuda_weights(weights, dev)
     ref = evaluator.load(mod, DictResource(weights), oq.make(cfg))
     twin = make_twin(cfg)()
-    twin.load(DictResource(parity.cuda_weights(weights, dev)))
-    return cfg, ref, twin
+    twin.load(DictResource(on_dev))
+    yield cfg, ref, twin, on_dev
+    del ref, twin, weights, on_dev
+    torch.cuda.empty_cache()
 
 
 def _check(twin_fn, ref_fn, inputs, expect):
@@ -42,7 +55,7 @@ def _check(twin_fn, ref_fn, inputs, expect):
 
 
 def test_linear_attention_functions(dev, sides):
-    cfg, ref, twin = sides
+    cfg, ref, twin = sides[:3]
     g = torch.Generator().manual_seed(5)
     r = lambda *s, scale=1.0: (torch.randn(*s, generator=g) * scale).to(dev)
     HV, DK, DV, CONV = cfg.gdn_n_v_heads, cfg.gdn_head_k_dim, cfg.gdn_head_v_dim, cfg.conv_dim
@@ -63,7 +76,7 @@ def test_linear_attention_functions(dev, sides):
 
 @pytest.mark.parametrize("ctx", [0, 1, 63, 64, 130])
 def test_full_attention_functions(dev, sides, ctx):
-    cfg, ref, twin = sides
+    cfg, ref, twin = sides[:3]
     g = torch.Generator().manual_seed(ctx)
     HQ, HKV, D = cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim
     ai = cfg.full_attention_every - 1
@@ -82,13 +95,14 @@ def test_full_attention_functions(dev, sides, ctx):
 
 
 def test_moe_functions_and_routing_indices(dev, sides):
-    cfg, ref, twin = sides
+    cfg, ref, twin = sides[:3]
     g = torch.Generator().manual_seed(9)
-    hidden = torch.randn(1, 1, cfg.hidden, generator=g).to(dev)
     rm, tm = ref.layer0.moe, twin.layer0.moe
-    _check(tm.post_norm, rm.post_norm, (hidden,), {"output": F32})
-    tokens = rm.post_norm(hidden.cpu())
-    _check(tm.router.routing, rm.router.routing, (tokens.to(dev),), {"output[0]": CLOSE, "output[1]": [Equal()]})
+    for trial in range(4):                                       # routing is an integer output: several token vectors
+        hidden = torch.randn(1, 1, cfg.hidden, generator=g).to(dev)
+        _check(tm.post_norm, rm.post_norm, (hidden,), {"output": F32})
+        tokens = rm.post_norm(hidden.cpu())
+        _check(tm.router.routing, rm.router.routing, (tokens.to(dev),), {"output[0]": CLOSE, "output[1]": [Equal()]})
     weights, indices = rm.router.routing(tokens)
     args = tuple(t.to(dev) for t in (tokens, weights, indices))
     _check(tm.routed_experts, rm.routed_experts, args, {"output": CLOSE})
@@ -100,7 +114,7 @@ def test_moe_functions_and_routing_indices(dev, sides):
 
 
 def test_root_functions(dev, sides):
-    cfg, ref, twin = sides
+    cfg, ref, twin = sides[:3]
     g = torch.Generator().manual_seed(2)
     ids = torch.tensor([cfg.vocab - 1])
     assert torch.equal(twin.embed(ids.to(dev)).cpu(), ref.embed(ids))
@@ -111,17 +125,18 @@ def test_root_functions(dev, sides):
     assert int(twin.last_token) == int(torch.argmax(twin.lm_head(normed.to(dev))))
 
 
-def _setup(dev, max_new, seed=11):
+def cfg_is_tiny(cfg):
+    return cfg.hidden < 1024
+
+
+def _setup(dev, sides):
     from tilefoundry_b200.engine.qwen3_5 import Qwen35Session
-    cfg = qa.QWEN3_5_TINY
-    mod = qa.build(cfg)
-    weights = random_weights(mod, seed=seed, std=0.05, overrides=qa.weight_overrides)
-    ref = evaluator.load(mod, DictResource(weights), oq.make(cfg))
-    n_prompt = 16
+    cfg, ref, _, on_dev = sides
+    n_prompt, max_new = (16, 60) if cfg_is_tiny(cfg) else (64, 32)   # the wide stack: 64 prompt ids + 32 new tokens
     prompt = torch.randint(0, cfg.vocab, (n_prompt,), generator=torch.Generator().manual_seed(111))
     want = generation.decode_ids(ref, prompt, max_new)
     forced = torch.cat([prompt, torch.tensor(want["tokens"], dtype=torch.int64)])
-    sess = Qwen35Session(cfg, DictResource(parity.cuda_weights(weights, dev)), max_ctx=n_prompt + max_new + 5, device=dev,
+    sess = Qwen35Session(cfg, DictResource(on_dev), max_ctx=n_prompt + max_new + 5, device=dev,
                          keep_logits=True, trace_hidden=True)
     sess.reset(forced)
     return cfg, ref, sess, forced, n_prompt + max_new - 1
@@ -151,16 +166,20 @@ TIE_MARGIN = 3e-2
 
 
 @pytest.mark.parametrize("use_graph", [False, True])
-def test_step_matches_evaluator_from_its_own_state(dev, use_graph):
+def test_step_matches_evaluator_from_its_own_state(dev, sides, use_graph):
     """Every step starts from the evaluator's caches, so one step of the whole hybrid stack is judged at a
     time: per-layer hidden states, logits, routed experts, and the state the step leaves behind.  A step in
     which a router pick differs is accepted only if the evaluator's own margin for that pick is a near-tie."""
     from tilefoundry_b200.engine import paged_kv
-    cfg, ref, sess, forced, total = _setup(dev, 60)
+    cfg, ref, sess, forced, total = _setup(dev, sides)
+    twin = sides[2]
     if use_graph:
         sess.capture()
     excused = 0
-    for step, before, logits, hiddens, picks, margins, after in parity.nested_walk(ref, cfg.layer_types, forced, total):
+    for walk in parity.nested_walk(ref, cfg.layer_types, forced, total):
+        step, before, logits, hiddens, picks, margins, after = walk
+        if not use_graph:                            # routing on the evaluator's own router inputs: exact
+            parity.routing_on_evaluator_inputs(twin, walk, f"step {step}")
         _load_state(sess, cfg, before, step)
         sess.run(1, use_graph)
         same = _same_experts(sess, picks)
@@ -186,16 +205,19 @@ def test_step_matches_evaluator_from_its_own_state(dev, use_graph):
                 for name, want_cache in (("k_pool", state[0]), ("v_pool", state[1])):
                     got = paged_kv.logical_view(layer[name], sess.table[0], n)
                     assert_close_at_scale(got[:, -1], want_cache[:, n - 1], f"step {step} layer {li} new {name} row")
-    assert excused <= total // 5, f"{excused} of {total} steps had a routing near-tie"
+    # tiny: 4-8 well separated experts, near-ties are rare; wide: the gap between the last expert taken and the
+    # first left out is within two bf16 steps of the logits in about one layer-step in five
+    allowed = total // 5 if cfg_is_tiny(cfg) else total // 2
+    assert excused <= allowed, f"{excused} of {total} steps had a routing near-tie"
 
 
 @pytest.mark.parametrize("use_graph", [False, True])
-def test_free_running_session_tracks_evaluator(dev, use_graph):
+def test_free_running_session_tracks_evaluator(dev, sides, use_graph):
     """The session keeps its own state over the whole walk.  Until the first routing near-tie resolves the
     other way the comparison is the strict one; after it the two trajectories are different (equally valid)
     roundings of one sequence and must stay close in direction."""
     from tilefoundry_b200.engine import paged_kv
-    cfg, ref, sess, forced, total = _setup(dev, 60)
+    cfg, ref, sess, forced, total = _setup(dev, sides)
     if use_graph:
         sess.capture()
     diverged_at = None

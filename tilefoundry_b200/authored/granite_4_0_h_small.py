@@ -9,7 +9,7 @@ Modules (``residual_add`` + children ``mixer``/``moe`` + ``forward``, ``:481-530
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, replace
 from functools import lru_cache
 
 import torch
@@ -63,6 +63,13 @@ GRANITE_TINY = GraniteConfig(hidden_size=256, num_hidden_layers=4, attention_lay
                              num_local_experts=8, num_experts_per_tok=4, intermediate_size=256,
                              shared_intermediate_size=256, vocab_size=1000, max_ctx=256,
                              attention_multiplier=0.015625)
+
+
+def truncated(cfg: GraniteConfig, **changes) -> GraniteConfig:
+    """The same widths on a shorter stack / smaller vocabulary: what a host that cannot hold all 40 layers runs
+    the evaluator on (the reference cuts its own large example the same way, ``examples/qwen3_5_35b_a3b-tilelang/
+    config.py`` ``truncated``).  Kernel shapes depend on the widths only."""
+    return replace(cfg, **changes)
 
 
 def attention_mask(cfg, step, device="cpu"):

@@ -12,7 +12,7 @@ same tuples in its runtime (``runtime_model.py:372-385``).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, replace
 from functools import lru_cache
 
 import torch
@@ -66,6 +66,12 @@ QWEN3_5_35B_A3B = Qwen35Config()
 QWEN3_5_TINY = Qwen35Config(hidden=256, vocab=1024, n_layers=4, max_ctx=256, n_q_heads=4, n_kv_heads=2, head_dim=128,
                             rotary_dim=64, gdn_n_k_heads=2, gdn_n_v_heads=4, n_experts=16, top_k=4,
                             moe_intermediate=256, shared_intermediate=256)
+
+
+def truncated(cfg: Qwen35Config, **changes) -> Qwen35Config:
+    """The same widths on a shorter stack / smaller vocabulary (reference ``examples/qwen3_5_35b_a3b-tilelang/
+    config.py`` ``truncated``): what the CPU evaluator can hold.  Kernel shapes depend on the widths only."""
+    return replace(cfg, **changes)
 
 
 @lru_cache(maxsize=None)

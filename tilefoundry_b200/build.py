@@ -16,8 +16,14 @@ SOURCES = ("api.cu", "api_minicpm3.cu", "gemv.cu", "gemv_stream.cu", "attn_gqa.c
            "gemv_persist.cu", "gemv_async.cu", "chain.cu", "gemm_tc.cu", "collective.cu", "gemv_f32.cu", "gdn.cu", "attn_gated.cu", "api_qwen35.cu",
            "batch.cu", "api_batch.cu")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-         "--use_fast_math", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
-         "-Xcudafe", "--diag_suppress=177"]
+         "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-Xcudafe", "--diag_suppress=177"]
+# Approximate exp / division / rsqrt only where every output is a bf16-rounded activation.  The files that decide
+# integers (expert selection, its softmax) or carry f32 recurrent state across tokens keep IEEE arithmetic.
+PRECISE = frozenset({"moe.cu", "gemv_f32.cu", "mamba2.cu", "gdn.cu", "collective.cu"})
+
+
+def flags_for(src: str) -> list:
+    return list(FLAGS) if src in PRECISE else [*FLAGS, "--use_fast_math"]
 
 
 def _nvcc() -> str:
@@ -43,7 +49,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     procs = []
     for src in SOURCES:
         obj = CSRC / (src + ".o")
-        cmd = [nvcc, *FLAGS, "-c", str(CSRC / src), "-o", str(obj)]
+        cmd = [nvcc, *flags_for(src), "-c", str(CSRC / src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

@@ -250,10 +250,12 @@ int tfb_lm_head_argmax(const tfb_lm_head_args* a, tfb_stream_t stream) {
 
 int32_t tfb_attn_splits(int32_t max_ctx) { return max_ctx > 0 ? tfb::attn_splits(max_ctx) : 0; }
 
-int tfb_attn_gqa_decode(const tfb_attn_gqa_args* a, tfb_stream_t stream) {
+// Every argument check of the attention entry points; `own_scratch`: the caller passes part_o / part_ml / counters.
+// Runs before any stream work, so a refused call leaves nothing queued.
+static int attn_gqa_validate(const tfb_attn_gqa_args* a, bool own_scratch) {
     TFB_REQUIRE(a && a->qkv && a->pos && a->k_pool && a->v_pool && a->block_table && a->out, TFB_EINVAL);
-    TFB_REQUIRE(a->part_o && a->part_ml && a->counters, TFB_EINVAL);
-    TFB_REQUIRE(a->hq > 0 && a->hkv > 0 && a->hq % a->hkv == 0, TFB_EINVAL);
+    TFB_REQUIRE(!own_scratch || (a->part_o && a->part_ml && a->counters), TFB_EINVAL);
+    TFB_REQUIRE(a->hq > 0 && a->hkv > 0 && a->hkv <= a->hq && a->hq % a->hkv == 0, TFB_EINVAL);
     TFB_REQUIRE(a->d == 64 || a->d == 128, TFB_EINVAL);
     TFB_REQUIRE(a->rotary_dim >= 0 && a->rotary_dim <= a->d && a->rotary_dim % 64 == 0, TFB_EINVAL);
     TFB_REQUIRE(a->rotary_dim == 0 || (a->cos_table && a->sin_table), TFB_EINVAL);
@@ -263,6 +265,14 @@ int tfb_attn_gqa_decode(const tfb_attn_gqa_args* a, tfb_stream_t stream) {
     TFB_REQUIRE((long long)a->page_size * a->table_len >= a->max_ctx, TFB_ECAPACITY);
     TFB_REQUIRE(a->rotary_dim == 0 || a->max_pos >= a->max_ctx, TFB_ECAPACITY);
     TFB_REQUIRE(aligned16(a->k_pool) && aligned16(a->v_pool) && aligned16(a->qkv), TFB_EALIGN);
+    TFB_REQUIRE(a->chunk >= 0 && a->chunk <= 2 && (a->chunk == 0 || a->batch > 1), TFB_EINVAL);
+    TFB_REQUIRE(a->batch <= 65535, TFB_EINVAL);
+    const int G = a->hq / a->hkv;
+    TFB_REQUIRE(G == 1 || G == 2 || (G == 4 && a->d == 128), TFB_EINVAL);
+    return TFB_OK;
+}
+
+static int attn_gqa_run(const tfb_attn_gqa_args* a, tfb_stream_t stream) {
     tfb::AttnParams p;
     p.qkv = static_cast<const uint16_t*>(a->qkv);
     p.gamma_q = static_cast<const uint16_t*>(a->gamma_q);
@@ -298,15 +308,17 @@ int tfb_attn_gqa_decode(const tfb_attn_gqa_args* a, tfb_stream_t stream) {
     p.out_stride = a->hq * a->d;
     p.bt_stride = a->chunk ? 0 : a->table_len;
     p.append_only = a->chunk;
-    TFB_REQUIRE(a->chunk >= 0 && a->chunk <= 2 && (a->chunk == 0 || a->batch > 1), TFB_EINVAL);
-    TFB_REQUIRE(p.batch <= 65535, TFB_EINVAL);
-    const int G = a->hq / a->hkv;
-    TFB_REQUIRE(G == 1 || G == 2 || (G == 4 && a->d == 128), TFB_EINVAL);
     return done(tfb::attn_gqa_dispatch(p, S(stream), a->pdl != 0));
 }
 
+int tfb_attn_gqa_decode(const tfb_attn_gqa_args* a, tfb_stream_t stream) {
+    const int v = attn_gqa_validate(a, true);
+    return v != TFB_OK ? v : attn_gqa_run(a, stream);
+}
+
 int tfb_attn_gqa_decode_noalloc(const tfb_attn_gqa_args* a, tfb_stream_t stream) {
-    TFB_REQUIRE(a && a->max_ctx > 0 && a->hq > 0, TFB_EINVAL);
+    const int v = attn_gqa_validate(a, false);               // everything is checked before any stream work
+    if (v != TFB_OK) return v;
     TFB_REQUIRE(a->batch <= 1, TFB_ECAPACITY);               // the built-in scratch holds one sequence
     tfb_attn_gqa_args b = *a;
     bool fits = false;
@@ -320,9 +332,10 @@ int tfb_attn_gqa_decode_noalloc(const tfb_attn_gqa_args* a, tfb_stream_t stream)
         return TFB_ECAPACITY;
     }
     // the merge tickets must start at zero; everything else is written before it is read
-    const cudaError_t m = cudaMemsetAsync(b.counters, 0, size_t(a->hkv > 0 ? a->hkv : 1) * sizeof(uint32_t), S(stream));
+    // (hkv <= hq <= 64 was checked above: the ticket region of the array holds 64 words)
+    const cudaError_t m = cudaMemsetAsync(b.counters, 0, size_t(a->hkv) * sizeof(uint32_t), S(stream));
     if (m != cudaSuccess) return fail_launch(m);
-    return tfb_attn_gqa_decode(&b, stream);
+    return attn_gqa_run(&b, stream);
 }
 
 int tfb_qwen3_decode_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
