@@ -72,7 +72,7 @@ class Workload:
             self.describe = ("granite-4.0-h-small architecture (36 Mamba-2 + 4 attention layers, hidden 4096, MoE 72 "
                              "experts top-10 + shared expert, vocab 100352), batch 1, 64-token random prompt, greedy "
                              "decode, f32 recurrent state in place, paged bf16 KV for the attention layers")
-            self.oracle_name, self.cpu_layers = "granite_4_0_h_small", 6
+            self.oracle_name, self.cpu_layers = "granite_4_0_h_small", 3
         elif key == "qwen3_5_35b_a3b":
             from tilefoundry_b200.authored import qwen3_5_35b_a3b as a
             from tilefoundry_b200.engine.qwen3_5 import Qwen35Session as S
@@ -240,22 +240,33 @@ def dominant_kernel(work, sess):
             cfg.proj * cfg.hidden_size * 2)
 
 
-def cpu_baseline(work, steps, warm, seed=0):
+def cpu_baseline(work, steps, warm, seed=0, start_at=None):
     """The CPU oracle (a port of the reference evaluator's arithmetic) on all host cores.  Models too
-    large for a host run use a truncated layer stack and the time is scaled per layer (labelled)."""
+    large for a host run use a truncated layer stack and the time is scaled per layer (labelled).
+    *start_at*: walk the whole 64-token prompt and decode greedily, untimed, up to that position, then time
+    *steps* steps there (the reference arm: the positions the GPU arm times); default: *warm* prompt tokens then
+    *steps* timed steps straight after them (the short sample the GPU arm carries along)."""
     from oracle import generation
 
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
     cfg, scale = work.truncated()
     ref = work.oracle(cfg, work.host_weights(cfg, seed))
-    run = generation.decode_ids(ref, prompt_ids(cfg, 0)[:warm], steps)
-    per_token = run["seconds"] / steps
-    sample = (f"{warm} prompt steps (untimed) then {steps} greedy decode steps, same architecture and seed, "
-              f"torch CPU bf16, {threads} threads")
+    if start_at is None:
+        run = generation.decode_ids(ref, prompt_ids(cfg, 0)[:warm], steps)
+        per_token = run["seconds"] / steps
+        sample = f"{warm} prompt steps (untimed) then {steps} greedy decode steps"
+    else:
+        ahead = start_at - PROMPT_TOKENS                       # untimed greedy steps between the prompt and the window
+        lead = generation.decode_ids(ref, prompt_ids(cfg, 0), ahead)
+        history = torch.cat([prompt_ids(cfg, 0), torch.tensor(lead["tokens"], dtype=torch.int64)])
+        run = generation.decode_ids(ref, history, steps, caches=lead["caches"], logits=lead["last_logits"])
+        per_token = run["seconds"] / steps
+        sample = (f"{PROMPT_TOKENS} prompt steps and {ahead} greedy steps (untimed), then {steps} greedy decode steps "
+                  f"timed at positions {start_at}..{start_at + steps - 1}")
+    sample += f", same architecture and seed, torch CPU bf16, {threads} threads"
     if scale != 1.0:
-        # head and embedding are not per-layer: time them once via a zero-layer estimate is not possible,
-        # so the whole truncated step is scaled, which over-counts the head slightly
+        # head and embedding are not per-layer: the whole truncated step is scaled, which over-counts the head slightly
         sample += (f"; truncated to {cfg.num_hidden_layers} of {work.cfg.num_hidden_layers} layers and scaled "
                    f"x{scale:.2f} per layer (extrapolated)")
         per_token *= scale
@@ -264,19 +275,21 @@ def cpu_baseline(work, steps, warm, seed=0):
 
 def run_reference(args):
     """Reference arm: the reference's own CPU implementation of the path.  The reference package does not
-    import here (isl / ortools missing), so this is the oracle port of its evaluator."""
+    import here (isl / ortools missing), so this is the oracle port of its evaluator, on all host cores, over
+    the same prompt and the same timed positions as the GPU arm.  Rank 0 alone runs it."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
     work = Workload(args.config)
-    steps = max(1, min(args.steps, 32))
-    warm = max(1, min(args.warmup + 1, PROMPT_TOKENS))
-    base = cpu_baseline(work, steps, warm)
+    K, W = args.steps, max(args.warmup, 3)
+    first, mid = windows(K, W)
+    at = mid if mid is not None else first
+    base = cpu_baseline(work, K, None, start_at=at)
     line = {
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tok/s", "n_gpus": args.gpus,
-        "steps": steps, "warmup": warm, "ms_per_step": 1e3 / base["value"], "higher_is_better": True,
+        "steps": K, "warmup": W, "ms_per_step": 1e3 / base["value"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": work.dtype, "data": "synthetic",
-        "config": {"workload": work.describe + " -- on host cores",
-                   "note": f"bounded sample: {steps} of the requested {args.steps} steps"},
+        "config": {"workload": work.describe, "positions": describe_positions(K, W), "name": work.key,
+                   "timed_positions": [at, at + K]},
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -285,7 +298,7 @@ def run_reference(args):
 
 
 def run_batch32_projection(args):
-    """The batch-32 form of the projections (config 1 of the north star): y[32, n] = x[32, k] . w[n, k]^T on the
+    """The batch-32 form of the projections of the Qwen3-1.7B architecture: y[32, n] = x[32, k] . w[n, k]^T on the
     tensor cores, timed over distinct weight matrices (far more than L2) in one CUDA graph, as HBM GB/s of weight
     bytes and as TFLOP/s.  Qwen3-1.7B shapes: head, fused gate|up, down, q|k|v, o."""
     import ctypes as C
@@ -324,7 +337,7 @@ def run_batch32_projection(args):
 
 
 def run_batch_decode(args):
-    """Several sequences at once (config 1's batch-32 clause): `--batch B` independent sequences of the Qwen3-1.7B
+    """Several sequences at once: `--batch B` independent sequences of the Qwen3-1.7B
     architecture, each a 64-token random prompt walked token by token and then `--steps` greedy tokens; every
     projection on the tensor cores, the KV cache of every sequence read once per step.  One JSON line: total
     tokens/s over all sequences and the fraction of the measured HBM peak the step's algorithmic bytes reach."""
@@ -406,7 +419,179 @@ def batch32_summary(work, dev, packed_from, steps):
             "roofline_frac": achieved / peak, "achieved_GBs": achieved}
 
 
+NEW_TOKENS = 2048                      # the run the metric names: 2048 greedy tokens after the 64-token prompt
+
+
+def windows(K, W):
+    """Positions of the timed steps inside that run.  A step at position p reads p cached positions and writes
+    one; position 63 consumes the last prompt token and yields the first new one.  The prompt (positions 0..62)
+    is always walked untimed, then W untimed decode steps, then K timed steps ("after_prompt").  When K is
+    shorter than the whole run a second window of K steps is timed around the run's mean position (1087): time
+    per token grows linearly with the context, so that window estimates the mean over all 2048 tokens, and it
+    is the one `value` reports."""
+    first = PROMPT_TOKENS - 1 + W
+    if K + W >= NEW_TOKENS:
+        return first, None
+    mid = PROMPT_TOKENS - 1 + NEW_TOKENS // 2 - K // 2
+    return first, max(mid, first + K)
+
+
+def describe_positions(K, W):
+    first, mid = windows(K, W)
+    at = mid if mid is not None else first
+    return (f"{PROMPT_TOKENS}-token prompt walked untimed, {W} untimed decode steps, then {K} timed steps at positions "
+            f"{at}..{at + K - 1} of the 2048-token greedy run" + (" (centred on its mean context)" if mid is not None else ""))
+
+
+def measure(work, sess, prompt, K, W, dev, rank, world, units, sample_clocks):
+    """Device-resident and end-to-end timing of K decode steps of *sess*, in the window(s) `windows` gives."""
+    import torch.distributed as dist
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t)
+        return ms
+
+    stream = torch.cuda.current_stream()
+
+    def timed(K):
+        barrier()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        sess.run(K)
+        end.record(stream)
+        barrier()
+        return max_over_ranks(start.elapsed_time(end))
+
+    first, mid = windows(K, W)
+    sess.reset(prompt)
+    sess.run(first)                                  # prompt walk + W warm-up decode steps
+    sampler = ClockSampler(dev.index) if sample_clocks else None
+    snap = sess.snapshot() if mid is None else None
+    ms_first = timed(K)
+    at, ms = first, ms_first
+    if mid is not None:
+        sess.run(mid - (first + K))                  # the same greedy run, continued untimed up to the second window
+        torch.cuda.synchronize()
+        snap = sess.snapshot()
+        at, ms = mid, timed(K)
+    clocks = sampler.stop() if sampler else None
+    tokens_out = sess.tokens[at + 1: at + 1 + min(K, 8)].tolist()
+
+    # ---- end to end over the same positions: token in from pinned host memory, picked token back, every step ----
+    sess.restore(snap)
+    pin_in = torch.empty(1, dtype=torch.int64).pin_memory()
+    pin_out = torch.empty(1, dtype=torch.int64).pin_memory()
+    pin_in[0] = int(sess.tokens[at])
+    barrier()
+    t0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(K):
+        pos = at + i
+        sess.tokens[pos: pos + 1].copy_(pin_in, non_blocking=True)         # H2D: this step's input
+        sess.graph.replay()
+        pin_out.copy_(sess.tokens[pos + 1: pos + 2], non_blocking=True)    # D2H: this step's result
+        stream.synchronize()
+        pin_in[0] = pin_out[0]
+    e1.record(stream)
+    barrier()
+    e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3))
+
+    peak, peak_kind = peaks()
+    w_bytes, kv_pos = sess.weight_bytes(), sess.kv_bytes_per_position()
+    state = sess.state_bytes() if hasattr(sess, "state_bytes") else 0
+    # a step at position p reads its weights, the p cached positions and the recurrent state, writes one
+    # position and the state back
+    step_bytes = [w_bytes + state + kv_pos * (at + i + 1) for i in range(K)]
+    step_gbs = sum(step_bytes) / (ms * 1e-3) / 1e9
+    out = {
+        "value": units * K / (ms * 1e-3), "ms_per_step": ms / K, "timed_positions": [at, at + K],
+        "e2e": {"value": units * K / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
+        "gpu_launches": sess.launches_per_step * K, "clocks": clocks, "first_tokens": tokens_out,
+        "whole_step": {"achieved": step_gbs, "frac": step_gbs / peak, "bytes_per_token_mean": sum(step_bytes) / K,
+                       "weights_bytes": w_bytes, "state_bytes": state, "kv_bytes_per_position": kv_pos,
+                       "frac_of_8TBs_nominal": step_gbs / 8000.0},
+    }
+    if mid is not None:
+        first_bytes = sum(w_bytes + state + kv_pos * (first + i + 1) for i in range(K))
+        out["after_prompt"] = {"value": units * K / (ms_first * 1e-3), "ms_per_step": ms_first / K,
+                               "timed_positions": [first, first + K],
+                               "whole_step_frac": first_bytes / (ms_first * 1e-3) / 1e9 / peak}
+    return out
+
+
+def roofline_of(work, sess, whole_step):
+    peak, peak_kind = peaks()
+    k_name, k_ms, k_bytes = dominant_kernel(work, sess)
+    k_gbs = k_bytes / (k_ms * 1e-3) / 1e9
+    return {"kernel": k_name, "bound": "hbm", "achieved": k_gbs, "peak": peak,
+            "peak_kind": "measured (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback",
+            "unit": "GB/s", "frac": k_gbs / peak, "traffic": NCU_TRAFFIC.get(work.key),
+            "algorithmic_bytes_per_launch": k_bytes, "us_per_launch": k_ms * 1e3, "whole_step": whole_step}
+
+
+def side_config(key, dev, K, W, with_cpu):
+    """One of the other single-GPU configurations, measured the same way, as a bounded side entry of the line."""
+    from tilefoundry_b200.runtime import DictResource
+
+    work = Workload(key)
+    first, mid = windows(K, W)
+    max_ctx = (mid if mid is not None else first) + K + 8
+    sess = work.session_cls(work.cfg, DictResource(work.device_weights(dev, seed=0)), max_ctx=max_ctx, device=dev)
+    sess.reset(prompt_ids(work.cfg, 0))
+    sess.capture()
+    m = measure(work, sess, prompt_ids(work.cfg, 0), K, W, dev, 0, 1, 1, False)
+    whole = m.pop("whole_step")
+    out = {"workload": work.describe, "dtype": work.dtype, "unit": "tok/s", **m, "roofline": roofline_of(work, sess, whole)}
+    del sess
+    torch.cuda.empty_cache()
+    if with_cpu:
+        out["cpu_baseline"] = cpu_baseline(work, 8, 8)
+    return out
+
+
+def sharded_config(key, dev, K, W, rank, world):
+    """One sequence of a MoE configuration split over all ranks (routed experts by expert, shared expert and head
+    by slice; exchange kernels over NVLink peer memory): strong scaling, every rank the same tokens."""
+    import torch.distributed as dist
+
+    from tilefoundry_b200.runtime import DictResource
+
+    work = Workload(key)
+    first, mid = windows(K, W)
+    max_ctx = (mid if mid is not None else first) + K + 8
+    sess = work.session_cls(work.cfg, DictResource(work.device_weights(dev, seed=0)), max_ctx=max_ctx, device=dev,
+                            group=dist.group.WORLD)
+    prompt = prompt_ids(work.cfg, 0)
+    sess.reset(prompt)
+    sess.capture()
+    m = measure(work, sess, prompt, K, W, dev, rank, world, 1, False)
+    status = int(sess.peer_status) if getattr(sess, "collectives", "") == "peer" else 0
+    whole = m.pop("whole_step")
+    exchanges = len(sess.layers) + 1
+    out = {"workload": work.describe, "scaling": "strong", "gpus": world, "unit": "tok/s", **m,
+           "collectives": getattr(sess, "collectives", "nccl"), "exchanges_per_token": exchanges,
+           "bounded_wait_status": status, "per_gpu": whole,
+           "frac_of_n_gpu_roofline": whole["frac"],      # per-GPU bytes / time against ONE GPU's peak = total / (N x peak)
+           "parallelism": f"ep{world} routed experts + tp{world} shared expert + vocabulary-parallel head, mixers replicated"}
+    sess.graph = None
+    del sess
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_ours(args):
+    import datetime
+    import threading
+
     import torch.distributed as dist
 
     from tilefoundry_b200.runtime import DictResource
@@ -414,19 +599,24 @@ def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    # The exchange kernels use plain peer stores only: keep NCCL and symmetric memory from binding any buffer to an
+    # NVLink multicast object (a rank that ends while bound to one disturbs its peers).
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     torch.cuda.set_device(local)
     dev = torch.device(f"cuda:{local}")
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=600))
 
     work = Workload(args.config)
     cfg = work.cfg
     K, W = args.steps, max(args.warmup, 3)
-    # The MoE configuration shards one sequence over the GPUs (expert / shared-expert / vocabulary parallel);
-    # the dense ones do not shard: each rank decodes its own sequence ("replicas only").
+    # `--config <MoE model> --gpus N` shards one sequence over the GPUs; the dense ones do not shard: each rank
+    # decodes its own sequence ("replicas only").
     sharded = world > 1 and work.key in ("granite_4_0_h_small", "qwen3_5_35b_a3b")
     prompt = prompt_ids(cfg, seed=0 if sharded else rank)
-    max_ctx = max(W + K + 8, PROMPT_TOKENS + 8)
+    first, mid = windows(K, W)
+    max_ctx = (mid if mid is not None else first) + K + 8
     extra = {"group": dist.group.WORLD} if sharded else {}
     sess = work.session_cls(cfg, DictResource(work.device_weights(dev, seed=0)), max_ctx=max_ctx, device=dev, **extra)
     units = 1 if sharded else world                           # sequences decoded per step over all ranks
@@ -437,137 +627,96 @@ def run_ours(args):
                           "achieved_gbs": nbytes / (ms_launch * 1e-3) / 1e9}))
         return
     sess.capture()
+    m = measure(work, sess, prompt, K, W, dev, rank, world, units, rank == 0)
+    whole = m.pop("whole_step")
+    line = None
+    if rank == 0:
+        roofline = roofline_of(work, sess, whole)
+        # prompt processing, outside the metric: the 64-token prompt walked one decode step per token against the same
+        # prompt in chunks of 32 tokens on the tensor-core projections (Qwen3 only)
+        prompt_info = batch32 = None
+        if world == 1 and work.key == "qwen3_1_7b" and not args.no_sides:
+            walk = sess.generate(prompt, 4)
+            sess.generate(prompt, 4, prefill=True)                                  # warm-up: buffers, tensor maps
+            chunked = sess.generate(prompt, 4, prefill=True)
+            prompt_info = {"tokens": PROMPT_TOKENS, "walk_ms": walk.prompt_seconds * 1e3,
+                           "chunked_prefill_ms": chunked.prompt_seconds * 1e3,
+                           "same_continuation": walk.tokens == chunked.tokens}
+            try:
+                batch32 = batch32_summary(work, dev, sess, min(K, 2048))
+            except Exception as exc:                      # a side measurement: it must not cost the headline line
+                batch32 = {"error": f"{type(exc).__name__}: {exc}"}
+        base = None
+        if world == 1 and not args.no_cpu:
+            base = cpu_baseline(work, 32 if work.cpu_layers is None else 8, PROMPT_TOKENS if work.cpu_layers is None else 8)
+        line = {
+            "metric": METRIC, "value": m["value"], "unit": "tok/s", "n_gpus": world, "steps": K,
+            "warmup": W, "ms_per_step": m["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong" if sharded else "weak", "vs_baseline": None,
+            "dtype": work.dtype, "data": "synthetic",
+            "config": {"workload": work.describe, "positions": describe_positions(K, W), "name": work.key,
+                       "timed_positions": m["timed_positions"],
+                       "parallelism": (f"ep{world} routed experts + tp{world} shared expert + vocabulary-parallel head, mixers "
+                                       f"replicated, one exchange per MoE block ({getattr(sess, 'collectives', 'nccl')} collectives)"
+                                       if sharded else "replicas only" if world > 1 else "1 gpu"),
+                       "l2": f"inputs larger than L2: {whole['weights_bytes'] / 1e9:.2f} GB of weights are streamed every step",
+                       "first_tokens": m["first_tokens"]},
+            "e2e": m["e2e"], "gpu_launches": m["gpu_launches"], "clocks": m["clocks"], "roofline": roofline,
+            "cpu_baseline": base, "after_prompt": m.get("after_prompt"), "prompt": prompt_info, "batch32": batch32,
+        }
+    sess.graph = None
+    del sess
+    torch.cuda.empty_cache()
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # ---- device-resident timing ----------------------------------------------------------
-    sess.reset(prompt)
-    sess.run(W)
-    barrier()
-    sampler = ClockSampler(local) if rank == 0 else None
-    stream = torch.cuda.current_stream()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record(stream)
-    sess.run(K)
-    end.record(stream)
-    barrier()
-    clocks = sampler.stop() if sampler else None
-    ms = start.elapsed_time(end)
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t)
-    tokens_out = sess.tokens[W + 1: W + 1 + K].tolist()
-
-    # ---- end to end: token in from pinned host memory, picked token back, every step ---------
-    sess.reset(prompt)
-    sess.run(W)
-    pin_in = torch.empty(1, dtype=torch.int64).pin_memory()
-    pin_out = torch.empty(1, dtype=torch.int64).pin_memory()
-    pin_in[0] = int(sess.tokens[W])
-    barrier()
-    t0 = time.perf_counter()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for i in range(K):
-        pos = W + i
-        sess.tokens[pos: pos + 1].copy_(pin_in, non_blocking=True)         # H2D: this step's input
-        sess.graph.replay()
-        pin_out.copy_(sess.tokens[pos + 1: pos + 2], non_blocking=True)    # D2H: this step's result
-        stream.synchronize()
-        pin_in[0] = pin_out[0]
-    e1.record(stream)
-    barrier()
-    e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3)
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t)
-
-    if rank != 0:
-        # no process-group teardown: with collectives held in captured graphs it does not return
-        sys.stdout.flush()
-        os._exit(0)
-
-    # ---- roofline ---------------------------------------------------------------------------------
-    peak, peak_kind = peaks()
-    w_bytes = sess.weight_bytes()
-    kv_pos = sess.kv_bytes_per_position()
-    state = sess.state_bytes() if hasattr(sess, "state_bytes") else 0
-    # a step at position p reads its weights, the p cached positions and the recurrent state, writes one
-    # position and the state back
-    step_bytes = [w_bytes + state + kv_pos * (W + i + 1) for i in range(K)]
-    step_gbs = sum(step_bytes) / (ms * 1e-3) / 1e9
-    k_name, k_ms, k_bytes = dominant_kernel(work, sess)
-    k_gbs = k_bytes / (k_ms * 1e-3) / 1e9
-    roofline = {
-        "kernel": k_name, "bound": "hbm", "achieved": k_gbs, "peak": peak,
-        "peak_kind": "measured (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback",
-        "unit": "GB/s", "frac": k_gbs / peak, "traffic": NCU_TRAFFIC.get(work.key),
-        "algorithmic_bytes_per_launch": k_bytes, "us_per_launch": k_ms * 1e3,
-        "whole_step": {"achieved": step_gbs, "frac": step_gbs / peak, "bytes_per_token_mean": sum(step_bytes) / K,
-                       "weights_bytes": w_bytes, "state_bytes": state, "kv_bytes_per_position": kv_pos,
-                       "frac_of_8TBs_nominal": step_gbs / 8000.0},
-    }
-
-    # prompt processing, outside the metric: the 64-token prompt walked one decode step per token against the same
-    # prompt in chunks of 32 tokens on the tensor-core projections (Qwen3 only)
-    prompt_info = None
-    if world == 1 and work.key == "qwen3_1_7b":
-        walk = sess.generate(prompt, 4)
-        sess.generate(prompt, 4, prefill=True)                                  # warm-up: buffers, tensor maps
-        chunked = sess.generate(prompt, 4, prefill=True)
-        prompt_info = {"tokens": PROMPT_TOKENS, "walk_ms": walk.prompt_seconds * 1e3,
-                       "chunked_prefill_ms": chunked.prompt_seconds * 1e3,
-                       "same_continuation": walk.tokens == chunked.tokens}
-
-    batch32 = None
-    if world == 1 and work.key == "qwen3_1_7b":
+    # ---- the other configurations, bounded, so that their numbers come from the same run ----------------------------
+    def guarded(fn, *a):
         try:
-            batch32 = batch32_summary(work, dev, sess, min(K, 2048))
-        except Exception as exc:                      # a side measurement: it must not cost the headline line
-            batch32 = {"error": f"{type(exc).__name__}: {exc}"}
+            return fn(*a)
+        except Exception as exc:                          # side measurements must not cost the headline line
+            return {"error": f"{type(exc).__name__}: {exc}"}
 
-    base = None
-    if world == 1 and not args.no_cpu:
-        base = cpu_baseline(work, 32 if work.cpu_layers is None else 8, PROMPT_TOKENS if work.cpu_layers is None else 8)
-
-    line = {
-        "metric": METRIC, "value": units * K / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K,
-        "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong" if sharded else "weak",
-        "vs_baseline": None,
-        "dtype": work.dtype, "data": "synthetic",
-        "config": {"workload": work.describe, "name": work.key, "timed_positions": [W, W + K],
-                   "parallelism": (f"ep{world} routed experts + tp{world} shared expert + vocabulary-parallel head, mixers "
-                                   f"replicated, one exchange per MoE block ({getattr(sess, 'collectives', 'nccl')} collectives)" if sharded else
-                                   "replicas only" if world > 1 else "1 gpu"),
-                   "l2": f"inputs larger than L2: {w_bytes / 1e9:.2f} GB of weights are streamed every step",
-                   "first_tokens": tokens_out[:8]},
-        "e2e": {"value": units * K / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 8,
-                "d2h_bytes_per_step": 8},
-        "gpu_launches": sess.launches_per_step * K,
-        "clocks": clocks, "roofline": roofline, "cpu_baseline": base, "prompt": prompt_info,
-        "batch32": batch32,
-    }
-    print(json.dumps(line), flush=True)
+    if world == 1 and work.key == "qwen3_1_7b" and not args.no_sides:
+        Ks = min(K, 256)
+        line["configs"] = {key: guarded(side_config, key, dev, Ks, W, not args.no_cpu)
+                           for key in ("minicpm3_4b", "granite_4_0_h_small", "qwen3_5_35b_a3b")}
+    if world > 1 and work.key == "qwen3_1_7b" and not args.no_sides:
+        # The sharded MoE steps wait on one another across ranks inside kernels (bounded) and in barriers (not): a
+        # watchdog prints the headline line and ends the process if this part does not finish in time.
+        def give_up():
+            if rank == 0:
+                line["sharded"] = {"error": "the sharded measurements did not finish within 420 s"}
+                print(json.dumps(line), flush=True)
+            os._exit(0)
+        dog = threading.Timer(420.0, give_up)
+        dog.daemon = True
+        dog.start()
+        Ks = min(K, 256)
+        res = {key: guarded(sharded_config, key, dev, Ks, W, rank, world)
+               for key in ("granite_4_0_h_small", "qwen3_5_35b_a3b")}
+        dog.cancel()
+        if rank == 0:
+            line["sharded"] = res
+    if rank == 0:
+        print(json.dumps(line), flush=True)
     if world > 1:
-        sys.stdout.flush()
-        os._exit(0)
+        # every rank stays until all of them are done, then they leave together (no captured graph is alive any more)
+        from tilefoundry_b200.engine.peer import leave_together
+        leave_together()
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2048)
-    ap.add_argument("--warmup", type=int, default=PROMPT_TOKENS - 1)
+    ap.add_argument("--warmup", type=int, default=3,
+                    help="untimed decode steps after the (always untimed) 64-token prompt walk")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="qwen3_1_7b",
                     choices=["qwen3_1_7b", "minicpm3_4b", "granite_4_0_h_small", "qwen3_5_35b_a3b"],
                     help="which configuration to run (default: the one the metric is quoted on)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-sides", action="store_true",
+                    help="only the headline configuration: no prompt / batch-32 / other-configuration / sharded side entries")
     ap.add_argument("--batch32-projection", action="store_true",
                     help="time the batch-32 tensor-core projection (tcgen05) on this configuration's projection shapes, "
                          "print one JSON line and exit")

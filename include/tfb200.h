@@ -841,7 +841,7 @@ TFB_API int tfb_qwen35_step_part(const tfb_qwen35_step_args* args, int32_t part,
  * flags u32 [world][ceil(hidden/256)], pick inbox f32 [2][world][2], pick flags u32 [world]; all zeroed once before
  * the first call.  epoch: local u32 [ceil(hidden/256)] (reduce) / [1] (pick), zeroed once.  Every rank must make the
  * same sequence of calls.  Waits are bounded: on a timeout *status becomes non-zero and the outputs are invalid.
- * No reference counterpart (the reference's sharded examples call NCCL). */
+ * No reference counterpart: the reference runs on one GPU and has no collective of any kind. */
 typedef struct {
     const float* partial; float* inbox[8]; uint32_t* flags[8]; uint32_t* epoch; uint32_t* status;
     const void* residual; void* out;

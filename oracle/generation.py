@@ -33,16 +33,20 @@ def _forward_traced(loaded, trace, token_ids, cos, sin, pos_ids, *rest):
     return loaded.lm_head(normed), tuple(entries)
 
 
-def decode_ids(loaded, prompt_ids, max_new, device="cpu", keep_logits=False, keep_hidden=False):
+def decode_ids(loaded, prompt_ids, max_new, device="cpu", keep_logits=False, keep_hidden=False, caches=None,
+               logits=None):
+    """*caches* / *logits*: continue a run whose ``prompt_ids`` have all been walked already (the ``caches`` and
+    ``last_logits`` an earlier call returned for exactly these ids); the prompt loop is then skipped."""
     prompt_ids = torch.as_tensor(prompt_ids, dtype=torch.int64)
     n_prompt = prompt_ids.numel()
     input_ids = torch.empty(n_prompt + max_new, dtype=torch.int64)
     input_ids[:n_prompt] = prompt_ids
-    caches = loaded.init_caches(device=device)
+    resumed = caches is not None
+    if not resumed:
+        caches = loaded.init_caches(device=device)
     kept, trace = [], []
-    logits = None
     t_prompt = perf_counter()
-    for step in range(n_prompt):
+    for step in range(0 if resumed else n_prompt):
         args = loaded.prepare_inputs_for_generation(input_ids[: step + 1], step, caches, device=device)
         logits, fresh = _forward_traced(loaded, trace, *args) if keep_hidden else loaded.forward(*args)
         caches = loaded.append_cache(caches, fresh)
@@ -63,4 +67,4 @@ def decode_ids(loaded, prompt_ids, max_new, device="cpu", keep_logits=False, kee
             kept.append(logits)
     seconds = perf_counter() - started
     return {"tokens": out, "seconds": seconds, "prompt_seconds": t_prompt, "logits": kept,
-            "caches": caches, "hidden": trace}
+            "caches": caches, "hidden": trace, "last_logits": logits}

@@ -20,7 +20,8 @@ def say(*a):
 
 
 def main():
-    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")                     # plain peer stores only: no NVLink multicast binding
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device(f"cuda:{local}")
@@ -73,10 +74,9 @@ def main():
     dist.barrier()
     if rank == 0:
         print(f"MULTI_GPU_OK world={world} modes={modes} tokens_equal={same}/{n_new} logit_err={err:.4g}", flush=True)
-    # Tearing the process group down while captured graphs still hold its collectives did not return on
-    # the 2-GPU box; the work is done and synchronised, so leave without the teardown.
-    sys.stdout.flush()
-    os._exit(0)
+    # graphs that recorded NCCL kernels keep the communicator alive: they are dropped before the teardown
+    from tilefoundry_b200.engine.peer import leave_together
+    leave_together([single, sharded])
 
 
 if __name__ == "__main__":

@@ -312,7 +312,7 @@ def test_session_matches_evaluator_tiny(dev, use_graph, kernel):
         assert_close_at_scale(v_got, v_ref[:, :total], f"layer {li} V cache")
 
 
-def test_config0_full_model_first_32_tokens(dev):
+def test_full_model_64_prompt_32_new_tokens(dev):
     """The CPU-runnable configuration: Qwen3-1.7B architecture, N(0, 0.02) weights, 64 random prompt
     ids, 32 greedy tokens.
 

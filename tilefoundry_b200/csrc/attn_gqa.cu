@@ -743,12 +743,11 @@ cudaError_t attn_gqa_dispatch(const AttnParams& p, cudaStream_t stream, bool pdl
 #define TFB_ATTN_BATCH(DD, GG)                                                                                 \
         if (p.d == DD && G == GG) {                                                                            \
             const size_t smem = size_t(4) * kSplitLen * DD * sizeof(uint16_t);                                 \
-            static bool once = false;                                                                          \
-            if (!once) {                                                                                       \
+            static PerDeviceOnce once;                                                                          \
+            if (once.first()) {                                                                                       \
                 cudaError_t e = cudaFuncSetAttribute(attn_gqa_batch_kernel<DD, GG>,                            \
                                                      cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); \
                 if (e != cudaSuccess) return e;                                                                \
-                once = true;                                                                                   \
             }                                                                                                  \
             return launch_kernel(attn_gqa_batch_kernel<DD, GG>, bgrid, bblock, smem, stream, pdl, p);         \
         }
@@ -759,11 +758,10 @@ cudaError_t attn_gqa_dispatch(const AttnParams& p, cudaStream_t stream, bool pdl
     const dim3 grid(p.hkv, p.nsplit), block(kAttnThreads);
 #define TFB_ATTN(DD, GG)                                                                                  \
     if (p.d == DD && G == GG) {                                                                           \
-        static bool once = false;                                                                         \
-        if (!once) {                                                                                      \
+        static PerDeviceOnce once;                                                                         \
+        if (once.first()) {                                                                                      \
             cudaFuncSetAttribute(attn_gqa_kernel<DD, GG>, cudaFuncAttributePreferredSharedMemoryCarveout, \
                                  cudaSharedmemCarveoutMaxShared);                                         \
-            once = true;                                                                                  \
         }                                                                                                 \
         return launch_kernel(attn_gqa_kernel<DD, GG>, grid, block, 0, stream, pdl, p);                    \
     }

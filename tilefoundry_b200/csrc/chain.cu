@@ -268,7 +268,8 @@ cudaError_t gemv_chain_launch(ChainParams& p, cudaStream_t stream, bool pdl, siz
     const size_t smem = (size_t(kmax) + 32 + p.part_floats) * sizeof(float) + size_t(kChainWarps) * kChainRing;
     if (smem_out) *smem_out = smem;
     if (smem > 227 * 1024) return cudaErrorInvalidValue;
-    static size_t set_smem = 0;
+    static size_t set_smem_dev[kMaxDevices] = {};          // the opt-in is per device
+    size_t& set_smem = set_smem_dev[dev >= 0 && dev < kMaxDevices ? dev : 0];
     if (smem > set_smem) {
         e = cudaFuncSetAttribute(gemv_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;

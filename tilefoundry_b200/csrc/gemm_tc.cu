@@ -342,8 +342,7 @@ int gemm_tc_splits_swiglu(int n, int k) { return splits_for_tiles((n + 63) / 64,
 // K splits = CTAs of one cluster: the largest power of two (at most 8, the portable cluster size) that keeps the
 // grid within the two CTAs an SM holds.
 static int splits_for_tiles(int tiles, int k) {
-    int sms = 148, dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int sms = sm_count();
     const int ksteps = k / TC_BK;
     int splits = 1;
     while (splits < 8 && tiles * splits * 2 <= 2 * sms && ksteps % (splits * 2) == 0) splits *= 2;
@@ -358,12 +357,10 @@ cudaError_t gemm_tc_launch(const void* w, const void* x, TcParams p, cudaStream_
     p.ksteps = p.K / TC_BK;
     const int tiles = p.swiglu ? (p.N + 63) / 64 : (p.N + TC_BM - 1) / TC_BM;
     const size_t smem = 1024 + size_t(TC_STAGES) * (TC_A_BYTES + TC_B_BYTES) + sizeof(TcSmemTail);
-    static bool once = false;
-    if (!once) {
+    static PerDeviceOnce once;
+    if (once.first()) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-        if (e != cudaSuccess) return e;
-        once = true;
-    }
+        if (e != cudaSuccess) return e;}
     const dim3 grid(tiles, p.splits), block(TC_THREADS);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;

@@ -156,16 +156,7 @@ __global__ void __launch_bounds__(kAsyncWarps * 32) gemv_async_kernel(const Gemv
     trace_end(p.trace);
 }
 
-static int async_sm_count() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-        if (n <= 0) n = 148;
-    }
-    return n;
-}
+static int async_sm_count() { return sm_count(); }
 
 template <int NMAT, int SI, int NORM_MODE, int EPI>
 static cudaError_t launch_async(const GemvParams& p, cudaStream_t stream, bool pdl) {

@@ -137,17 +137,6 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_persist_kernel(const GemvPara
     trace_end(p.trace);
 }
 
-static int sm_count() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-        if (n <= 0) n = 148;
-    }
-    return n;
-}
-
 template <int ROWS, int KSPLIT, int WARPS, int UNROLL, int NORM_MODE, int EPI>
 static cudaError_t launch_cfg(const GemvParams& p, cudaStream_t stream, bool pdl) {
     constexpr int GROUPS = WARPS / KSPLIT;
@@ -155,8 +144,12 @@ static cudaError_t launch_cfg(const GemvParams& p, cudaStream_t stream, bool pdl
     const int tiles = (p.n + rows_per_tile - 1) / rows_per_tile;
     const size_t smem = (size_t(p.k) + 32 + 2 * WARPS * ROWS * 2) * sizeof(float) + (NORM_MODE ? size_t(p.k) * 2 : 0);
     auto kern = gemv_persist_kernel<ROWS, KSPLIT, WARPS, UNROLL, NORM_MODE, EPI>;
-    static int occ = 0;
-    static size_t occ_smem = 0;
+    static int occ_dev[kMaxDevices] = {};                 // occupancy and the opt-in it follows from are per device
+    static size_t occ_smem_dev[kMaxDevices] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+    int& occ = occ_dev[dev];
+    size_t& occ_smem = occ_smem_dev[dev];
     if (occ == 0 || smem > occ_smem) {
         if (smem > 48 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));

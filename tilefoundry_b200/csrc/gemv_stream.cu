@@ -331,18 +331,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const Ge
 }
 
 // ---- host side ---------------------------------------------------------------------------------
-static int sm_count() {
-    static int cached = 0;
-    if (cached == 0) {
-        int dev = 0, n = 0;
-        if (cudaGetDevice(&dev) == cudaSuccess &&
-            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
-            cached = n;
-        else
-            cached = 148;
-    }
-    return cached;
-}
 
 // Largest multiple of 256 (up to 1024) that divides k; 0 if k is not a multiple of 256.
 static int pick_kc(int k) {

@@ -241,12 +241,10 @@ cudaError_t pick_finalize_launch(const float* pairs, int world, long long* token
 cudaError_t moe_down_launch(const MoeDownParams& p, cudaStream_t stream, bool pdl) {
     const size_t smem = (size_t(p.top_k) * p.inter + p.shared_inter) * sizeof(float);
     if (smem > 48 * 1024) {
-        static bool once = false;
-        if (!once) {
+        static PerDeviceOnce once;
+        if (once.first()) {
             cudaError_t e = cudaFuncSetAttribute(moe_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-            if (e != cudaSuccess) return e;
-            once = true;
-        }
+            if (e != cudaSuccess) return e;}
     }
     const dim3 grid((p.hidden + kDownWarps * kDownRows - 1) / (kDownWarps * kDownRows)), block(kDownWarps * 32);
     return launch_kernel(moe_down_kernel, grid, block, smem, stream, pdl, p);
@@ -367,12 +365,10 @@ __global__ void __launch_bounds__(kDownWarps * 32) moe_down_f32_kernel(const Moe
 cudaError_t moe_down_f32_launch(const MoeDownF32Params& p, cudaStream_t stream, bool pdl) {
     const size_t smem = (size_t(p.top_k) * p.inter + p.shared_inter) * sizeof(float);
     if (smem > 48 * 1024) {
-        static bool once = false;
-        if (!once) {
+        static PerDeviceOnce once;
+        if (once.first()) {
             cudaError_t e = cudaFuncSetAttribute(moe_down_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-            if (e != cudaSuccess) return e;
-            once = true;
-        }
+            if (e != cudaSuccess) return e;}
     }
     const dim3 grid((p.hidden + kDownWarps - 1) / kDownWarps), block(kDownWarps * 32);
     return launch_kernel(moe_down_f32_kernel, grid, block, smem, stream, pdl, p);

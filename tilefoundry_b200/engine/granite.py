@@ -161,15 +161,8 @@ class GraniteSession(DecodeSession):
                 layer["conv_state"].zero_()
                 layer["ssm_state"].zero_()
 
-    def capture(self) -> None:
-        # the warm-up steps of a capture advance the recurrent state: save and restore it with the tokens
-        saved = [(l["conv_state"].clone(), l["ssm_state"].clone()) for l in self.layers if l["kind"] == "linear_attention"]
-        super().capture()
-        it = iter(saved)
-        for layer in self.layers:
-            if layer["kind"] == "linear_attention":
-                c, s = next(it)
-                layer["conv_state"].copy_(c); layer["ssm_state"].copy_(s)
+    def state_tensors(self) -> list:
+        return [l[n] for l in self.layers if l["kind"] == "linear_attention" for n in ("conv_state", "ssm_state")]
 
     def weight_bytes(self) -> int:
         """Bytes of weights one token reads: every mixer, router and shared expert, top-k experts, the head."""

@@ -20,6 +20,9 @@ class PeerBuffers:
         words = [(w + 63) // 64 * 64 for w in words]                             # keep every region 256-byte aligned
         ok = torch.ones(1, device=device)
         try:
+            import os
+            # the exchange kernels use plain peer loads and stores; keep the buffer off any NVLink multicast object
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
             import torch.distributed._symmetric_memory as symm
             self._sym = symm.empty(sum(words), dtype=torch.float32, device=device)
             self._sym.zero_()
@@ -44,3 +47,33 @@ class PeerBuffers:
         z = lambda n: torch.zeros(n, device=device, dtype=torch.int32)
         self.reduce_epoch, self.pick_epoch, self.status = z(n_cta), z(1), z(1)
         self.mode = "peer"
+
+
+def leave_together(sessions=(), bound_s: float = 30.0) -> None:
+    """End of a multi-rank run: every rank drops its captured graphs, finishes its GPU work, meets the others at a
+    barrier and only then tears the process group down, so no rank is gone while a peer still pushes into its
+    buffers.  A CUDA graph that recorded NCCL kernels holds a reference on the communicator, and the
+    communicator's teardown waits until that reference is released -- destroying the process group while such a
+    graph is alive therefore never returns; the graphs go first.  The teardown is bounded all the same: if it has
+    not returned after *bound_s* seconds the process exits (its work is done and synchronised by then)."""
+    import gc
+    import os
+    import sys
+    import threading
+
+    import torch.distributed as dist
+
+    for s in sessions:
+        s.graph = None
+    gc.collect()
+    torch.cuda.synchronize()
+    if not dist.is_initialized():
+        return
+    dist.barrier()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    bound = threading.Timer(bound_s, lambda: os._exit(0))
+    bound.daemon = True
+    bound.start()
+    dist.destroy_process_group()
+    bound.cancel()

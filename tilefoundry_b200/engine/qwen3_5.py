@@ -185,12 +185,8 @@ class Qwen35Session(DecodeSession):
             layer["conv_state"].zero_()
             layer["state"].zero_()
 
-    def capture(self) -> None:
-        # the warm-up steps of a capture advance the recurrent state: save and restore it with the tokens
-        saved = [(l["conv_state"].clone(), l["state"].clone()) for l in self._recurrent()]
-        super().capture()
-        for layer, (c, s) in zip(self._recurrent(), saved):
-            layer["conv_state"].copy_(c); layer["state"].copy_(s)
+    def state_tensors(self) -> list:
+        return [l[n] for l in self._recurrent() for n in ("conv_state", "state")]
 
     def conv_window(self, layer: dict) -> torch.Tensor:
         """The convolution window the NEXT step will read, ``[channels, width-1]``."""

@@ -46,10 +46,25 @@ class DecodeSession:
             self.graph = None                         # the prompt length is baked into the capture
         self.n_prompt = int(prompt.numel())
 
+    def state_tensors(self) -> list:
+        """Device tensors, besides the token history and the position, that a step updates in place and a later
+        step reads again (recurrent state, convolution windows).  Cache rows are not listed: a step only reads
+        rows below its own position, so rows written by later steps need no rolling back."""
+        return []
+
+    def snapshot(self) -> dict:
+        """Copy of everything needed to return to the current position later with ``restore``."""
+        return {"tokens": self.tokens.clone(), "pos": self.pos.clone(), "state": [t.clone() for t in self.state_tensors()]}
+
+    def restore(self, snap: dict) -> None:
+        self.tokens.copy_(snap["tokens"]); self.pos.copy_(snap["pos"])
+        for dst, src in zip(self.state_tensors(), snap["state"]):
+            dst.copy_(src)
+
     def capture(self) -> None:
         """Record one step into a CUDA graph (positions and tokens live on the device, so the same
         graph serves every step).  Three eager warm-up steps run first and are rolled back."""
-        saved = (self.tokens.clone(), self.pos.clone())
+        saved = self.snapshot()                       # the warm-up steps advance position and recurrent state
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -57,13 +72,13 @@ class DecodeSession:
                 self.step()
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
-        self.tokens.copy_(saved[0]); self.pos.copy_(saved[1])
+        self.restore(saved)
         graph = torch.cuda.CUDAGraph()
         # thread-local capture mode: a process group's watchdog thread may query CUDA events meanwhile
         with torch.cuda.graph(graph, capture_error_mode="thread_local"):
             self.step()
         torch.cuda.synchronize()
-        self.tokens.copy_(saved[0]); self.pos.copy_(saved[1])
+        self.restore(saved)
         self.graph = graph
 
     def run(self, steps: int, use_graph: bool = True) -> None:
