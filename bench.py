@@ -618,6 +618,8 @@ def run_ours(args):
     first, mid = windows(K, W)
     max_ctx = (mid if mid is not None else first) + K + 8
     extra = {"group": dist.group.WORLD} if sharded else {}
+    if work.key == "qwen3_1_7b":
+        extra["kernel"] = args.kernel
     sess = work.session_cls(cfg, DictResource(work.device_weights(dev, seed=0)), max_ctx=max_ctx, device=dev, **extra)
     units = 1 if sharded else world                           # sequences decoded per step over all ranks
     sess.reset(prompt)
@@ -654,13 +656,14 @@ def run_ours(args):
             "warmup": W, "ms_per_step": m["ms_per_step"], "higher_is_better": True,
             "scaling": "strong" if sharded else "weak", "vs_baseline": None,
             "dtype": work.dtype, "data": "synthetic",
+            # (the reference arm prints the very same `config`)
             "config": {"workload": work.describe, "positions": describe_positions(K, W), "name": work.key,
-                       "timed_positions": m["timed_positions"],
-                       "parallelism": (f"ep{world} routed experts + tp{world} shared expert + vocabulary-parallel head, mixers "
-                                       f"replicated, one exchange per MoE block ({getattr(sess, 'collectives', 'nccl')} collectives)"
-                                       if sharded else "replicas only" if world > 1 else "1 gpu"),
-                       "l2": f"inputs larger than L2: {whole['weights_bytes'] / 1e9:.2f} GB of weights are streamed every step",
-                       "first_tokens": m["first_tokens"]},
+                       "timed_positions": m["timed_positions"]},
+            "parallelism": (f"ep{world} routed experts + tp{world} shared expert + vocabulary-parallel head, mixers "
+                            f"replicated, one exchange per MoE block ({getattr(sess, 'collectives', 'nccl')} collectives)"
+                            if sharded else "replicas only" if world > 1 else "1 gpu"),
+            "l2": f"inputs larger than L2: {whole['weights_bytes'] / 1e9:.2f} GB of weights are streamed every step",
+            "first_tokens": m["first_tokens"],
             "e2e": m["e2e"], "gpu_launches": m["gpu_launches"], "clocks": m["clocks"], "roofline": roofline,
             "cpu_baseline": base, "after_prompt": m.get("after_prompt"), "prompt": prompt_info, "batch32": batch32,
         }
@@ -714,6 +717,9 @@ def main():
     ap.add_argument("--config", default="qwen3_1_7b",
                     choices=["qwen3_1_7b", "minicpm3_4b", "granite_4_0_h_small", "qwen3_5_35b_a3b"],
                     help="which configuration to run (default: the one the metric is quoted on)")
+    ap.add_argument("--kernel", type=int, default=0,
+                    help="Qwen3 only: TFB_KERNEL_* of the step (0 = one launch per kernel, 6 = the whole step as one "
+                         "cooperative launch)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-sides", action="store_true",
                     help="only the headline configuration: no prompt / batch-32 / other-configuration / sharded side entries")

@@ -103,7 +103,8 @@ enum { TFB_EPI_STORE = 0, TFB_EPI_RESIDUAL = 1, TFB_EPI_SWIGLU = 2, TFB_EPI_STOR
 enum { TFB_KERNEL_AUTO = 0, TFB_KERNEL_ROWS = 1, TFB_KERNEL_RING = 2,
        TFB_KERNEL_PERSIST = 3, /* grid sized to residency, grid-stride tiles, two weight batches in flight */
        TFB_KERNEL_ASYNC = 4,   /* one CTA per SM, weights land in a shared-memory ring through cp.async */
-       TFB_KERNEL_CHAIN = 5    /* decode steps only: o / gate+up / down (/ next q|k|v) of a layer as ONE persistent launch */ };
+       TFB_KERNEL_CHAIN = 5,   /* decode steps only: o / gate+up / down (/ next q|k|v) of a layer as ONE persistent launch */
+       TFB_KERNEL_FUSED = 6    /* tfb_qwen3_decode_step only: the WHOLE step as one cooperative launch (step_* fields) */ };
 typedef struct {
     const void* w;
     const void* w2;
@@ -304,8 +305,23 @@ typedef struct {
     uint32_t* chain_sync;   /* TFB_KERNEL_CHAIN: u32[4] zeroed once ([0..1] grid barrier, [2] status: non-zero if a wait gave up) */
     float temperature;      /* > 0: sample each token from softmax(logits / temperature) (see tfb_lm_head_args); else greedy */
     uint64_t seed;
+    /* TFB_KERNEL_FUSED: the step as ONE cooperative launch, one CTA per multiprocessor; the weight stream runs
+     * through a shared-memory ring across all phases and layers, phases hand over through counters in global
+     * memory (every wait bounded).  Needs d = 128, hq = 2 hkv, hidden / hq*d / inter multiples of 1024 that divide
+     * 12288, hidden in {1024, 2048, 3072, 6144}, temperature <= 0; other shapes get TFB_EINVAL.
+     *   step_layers: DEVICE copy of the layer table, n_layers x 11 pointers in tfb_qwen3_layer's field order
+     *   step_sync:   uint32 [tfb_qwen3_step_sync_words(n_layers, hkv)], zeroed once (the kernel leaves it zero)
+     *   step_status: uint32 [1], zeroed once; non-zero after a wait gave up (the step's results are then void)
+     * and part_o / part_ml sized for tfb_qwen3_step_splits(hkv) splits, head_val / head_idx for one entry per
+     * multiprocessor.  No reference counterpart: the reference's fast driver replays about 280 launches per
+     * step (examples/qwen3_1_7b-tilelang/fast/engine.py:189-230). */
+    const void* step_layers;
+    uint32_t* step_sync;
+    uint32_t* step_status;
 } tfb_qwen3_step_args;
 TFB_API int tfb_qwen3_decode_step(const tfb_qwen3_step_args* args, tfb_stream_t stream);
+TFB_API int32_t tfb_qwen3_step_sync_words(int32_t n_layers, int32_t hkv);
+TFB_API int32_t tfb_qwen3_step_splits(int32_t hkv);   /* splits of the context the fused step may use (needs a CUDA device) */
 
 /* ---- multi-head latent attention decode (MiniCPM3) ------------------------------
  * One launch: RoPE on the rotary slice of q and on the shared rotary key slice,

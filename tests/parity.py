@@ -126,3 +126,18 @@ def routing_on_evaluator_inputs(twin, walk_step, where):
         got = got.reshape(-1).cpu()
         if sorted(got.tolist()) != sorted(want.tolist()):
             assert margin == 0.0, f"{where} layer {li}: experts {got.tolist()} != {want.tolist()}, margin {margin:.4g}"
+
+
+def assert_same_routing(got_idx, want_idx, router_logits, where=""):
+    """Routing indices, position by position.  Where the two sides name different experts their router logits must
+    be EQUAL: an exact tie, inside the selection (the order of equal values is not determined) or at its edge
+    (which of two equal experts is the last one taken is not determined either).  Anything else is an error."""
+    got, want = got_idx.reshape(-1).cpu(), want_idx.reshape(-1).cpu()
+    logits = router_logits.reshape(-1).float().cpu()
+    assert got.numel() == want.numel() and len(set(got.tolist())) == got.numel(), f"{where}: {got.tolist()}"
+    diff = (got != want).nonzero().flatten().tolist()
+    for i in diff:
+        assert float(logits[got[i]]) == float(logits[want[i]]), (
+            f"{where}: slot {i} holds expert {int(got[i])} (logit {float(logits[got[i]]):.6g}), the evaluator's holds "
+            f"{int(want[i])} (logit {float(logits[want[i]]):.6g})")
+    return len(diff)

@@ -312,7 +312,50 @@ def test_session_matches_evaluator_tiny(dev, use_graph, kernel):
         assert_close_at_scale(v_got, v_ref[:, :total], f"layer {li} V cache")
 
 
-def test_full_model_64_prompt_32_new_tokens(dev):
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_one_launch_step_matches_evaluator_small(dev, use_graph):
+    """The whole step as one cooperative launch (TFB_KERNEL_FUSED) against the evaluator: logits, every layer's
+    hidden state, greedy picks, caches and page table, over contexts that cross the 16-position split granularity
+    and the 64-slot page boundaries; no bounded wait may have given up."""
+    from tilefoundry_b200.engine import paged_kv
+    from tilefoundry_b200.engine.qwen3 import KERNEL_FUSED
+    cfg = q.QWEN3_SMALL
+    n_prompt, n_new = 24, 140
+    want, sess, got = _session_vs_oracle(cfg, dev, n_prompt, n_new, 11, 0.05, use_graph, KERNEL_FUSED)
+    sess.check_status()
+    assert sess.launches_per_step == 1
+    excused = _compare_run(cfg, want, sess, got, n_prompt, n_new)
+    assert excused <= 8, f"{excused} near-tie picks out of {n_prompt + n_new - 1}"
+    total = n_prompt + n_new - 1
+    assert torch.equal(sess.table.cpu(), paged_kv.block_table(1, sess.max_ctx))
+    for li, (k_ref, v_ref) in enumerate(want["caches"]):
+        k_got = paged_kv.logical_view(sess.layers[li]["k_pool"], sess.table[0], total)
+        v_got = paged_kv.logical_view(sess.layers[li]["v_pool"], sess.table[0], total)
+        assert_close_at_scale(k_got, k_ref[:, :total], f"layer {li} K cache")
+        assert_close_at_scale(v_got, v_ref[:, :total], f"layer {li} V cache")
+    assert int(sess.step_sync.abs().sum()) == 0                      # the last CTA left every counter at zero
+
+
+def test_one_launch_step_equals_the_launch_per_kernel_step(dev):
+    """Same session arguments, both forms of the step: the one-launch step must pick the tokens the step of
+    separate launches picks (same rounding points; only summation orders differ), and replaying its graph for a
+    second sequence must give the first run's tokens again."""
+    from tilefoundry_b200.engine.qwen3 import KERNEL_FUSED, Qwen3Session
+    cfg = q.QWEN3_SMALL
+    weights = _cuda(q.tie_head(random_weights(q.build(cfg), seed=2, std=0.05)), dev)
+    prompt = torch.arange(7, 40)
+    a = Qwen3Session(cfg, DictResource(weights), max_ctx=260, device=dev).generate(prompt, 200).tokens
+    fused = Qwen3Session(cfg, DictResource(weights), max_ctx=260, device=dev, kernel=KERNEL_FUSED)
+    b = fused.generate(prompt, 200).tokens
+    c = fused.generate(prompt, 200, use_graph=False).tokens
+    d = fused.generate(prompt, 200).tokens
+    fused.check_status()
+    assert b == c == d
+    assert sum(x == y for x, y in zip(a, b)) >= 190, (a, b)          # near-ties of random-weight logits may differ
+
+
+@pytest.mark.parametrize("kernel", [0, 6])
+def test_full_model_64_prompt_32_new_tokens(dev, kernel):
     """The CPU-runnable configuration: Qwen3-1.7B architecture, N(0, 0.02) weights, 64 random prompt
     ids, 32 greedy tokens.
 
@@ -328,7 +371,8 @@ def test_full_model_64_prompt_32_new_tokens(dev):
       6e-2 / cosine 0.998 (a sanity bound; 4.1e-2 was seen at step 62) of the evaluator itself."""
     cfg = q.QWEN3_1_7B
     n_prompt, n_new = 64, 32
-    want, sess, got = _session_vs_oracle(cfg, dev, n_prompt, n_new, 0, 0.02, True)
+    want, sess, got = _session_vs_oracle(cfg, dev, n_prompt, n_new, 0, 0.02, True, kernel)
+    sess.check_status()
     total = n_prompt + n_new - 1
     # arbiter: the same function bodies at f32, walking the same token sequence
     import dataclasses

@@ -51,6 +51,11 @@ QWEN3_1_7B = Qwen3Config()
 QWEN3_TINY = Qwen3Config(hidden_size=256, num_attention_heads=4, num_key_value_heads=2,
                          head_dim=64, intermediate_size=512, vocab_size=1024,
                          num_hidden_layers=3, max_position_embeddings=512)
+#: A mid-sized instance with the published head geometry (head_dim 128, two query heads per KV head) and widths
+#: that are multiples of 1024, the shapes the one-launch step is built for; small enough for the CPU evaluator.
+QWEN3_SMALL = Qwen3Config(hidden_size=1024, num_attention_heads=8, num_key_value_heads=4, head_dim=128,
+                          intermediate_size=3072, vocab_size=2048, num_hidden_layers=3,
+                          max_position_embeddings=512)
 
 
 @lru_cache(maxsize=None)

@@ -338,6 +338,44 @@ int tfb_attn_gqa_decode_noalloc(const tfb_attn_gqa_args* a, tfb_stream_t stream)
     return attn_gqa_run(&b, stream);
 }
 
+int32_t tfb_qwen3_step_sync_words(int32_t n_layers, int32_t hkv) {
+    return n_layers > 0 && hkv > 0 ? tfb::fused_step_sync_words(n_layers, hkv) : 0;
+}
+int32_t tfb_qwen3_step_splits(int32_t hkv) { return hkv > 0 ? tfb::fused_step_splits(hkv) : 0; }
+
+// TFB_KERNEL_FUSED: the whole step as one cooperative launch.
+static int qwen3_fused_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a->step_layers && a->step_sync && a->step_status, TFB_EINVAL);
+    TFB_REQUIRE(a->temperature <= 0.f, TFB_EINVAL);                        // greedy only
+    TFB_REQUIRE(a->vocab > 0 && a->vocab < (1ll << 31), TFB_EINVAL);
+    tfb::FusedParams p;
+    std::memset(&p, 0, sizeof p);
+    p.layers = static_cast<const tfb::FusedLayer*>(a->step_layers);
+    p.n_layers = a->n_layers; p.hidden = a->hidden; p.hq = a->hq; p.hkv = a->hkv; p.d = a->d; p.inter = a->inter;
+    p.vocab = int(a->vocab); p.eps = a->eps; p.scale = a->scale;
+    p.w_embed = static_cast<const uint16_t*>(a->w_embed);
+    p.gamma_final = static_cast<const uint16_t*>(a->gamma_final);
+    p.w_head = static_cast<const uint16_t*>(a->w_head);
+    p.cos_table = static_cast<const uint16_t*>(a->cos_table);
+    p.sin_table = static_cast<const uint16_t*>(a->sin_table);
+    p.page_size = a->page_size; p.max_ctx = a->max_ctx; p.block_table = a->block_table;
+    p.tokens = reinterpret_cast<long long*>(a->tokens); p.pos = a->pos;
+    p.n_prompt = a->n_prompt; p.max_tokens = a->max_tokens;
+    p.hidden_buf = static_cast<uint16_t*>(a->hidden_buf); p.qkv_buf = static_cast<uint16_t*>(a->qkv_buf);
+    p.attn_buf = static_cast<uint16_t*>(a->attn_buf); p.act_buf = static_cast<uint16_t*>(a->act_buf);
+    p.logits = static_cast<uint16_t*>(a->logits);
+    p.part_o = a->part_o; p.part_ml = a->part_ml;
+    p.sync = a->step_sync; p.status = a->step_status;
+    p.head_val = a->head_val; p.head_idx = a->head_idx;
+    p.picked = reinterpret_cast<long long*>(a->picked);
+    p.hidden_trace = static_cast<uint16_t*>(a->hidden_trace);
+    p.timeline = g_trace_buf;                                              // tfb_debug_trace, else nullptr
+    p.timeline_slots = g_trace_cap;
+    TFB_REQUIRE(a->cos_table && a->sin_table && a->block_table, TFB_EINVAL);
+    TFB_REQUIRE(tfb::fused_step_supported(p), TFB_EINVAL);
+    return done(tfb::fused_step_launch(p, S(stream)));
+}
+
 int tfb_qwen3_decode_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->layers && a->n_layers > 0, TFB_EINVAL);
     TFB_REQUIRE(a->w_embed && a->gamma_final && a->w_head && a->tokens && a->pos, TFB_EINVAL);
@@ -346,6 +384,7 @@ int tfb_qwen3_decode_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a->hidden % 256 == 0 && a->inter % 256 == 0 && (a->hq * a->d) % 256 == 0, TFB_EINVAL);
     TFB_REQUIRE((long long)a->page_size * a->table_len >= a->max_ctx, TFB_ECAPACITY);
     TFB_REQUIRE(a->max_pos >= a->max_ctx && a->max_tokens <= a->max_ctx + 1, TFB_ECAPACITY);
+    if (a->kernel == TFB_KERNEL_FUSED) return qwen3_fused_step(a, stream);
     const bool pdl = a->pdl != 0;
     const bool pf = (a->l2_prefetch & 2) != 0;
     const int spf = a->l2_prefetch & 1;

@@ -364,4 +364,38 @@ struct PeerPickParams {
 };
 cudaError_t pick_allgather_launch(const PeerPickParams& p, cudaStream_t stream, bool pdl);
 
+// ---- the whole Qwen3-architecture decode step as one cooperative launch (step_fused.cu) ------------------------
+constexpr int kFusedMaxLayers = 128;
+struct FusedLayer {                      // device-resident table, one entry per layer
+    const uint16_t *gamma_in, *w_qkv, *gamma_q, *gamma_k, *w_o, *gamma_post, *w_gate, *w_up, *w_down;
+    uint16_t *k_pool, *v_pool;
+};
+struct FusedParams {
+    const FusedLayer* layers;            // device pointer
+    int n_layers, hidden, hq, hkv, d, inter, vocab;
+    float eps, scale;
+    const uint16_t *w_embed, *gamma_final, *w_head, *cos_table, *sin_table;
+    int page_size, max_ctx;
+    const int* block_table;
+    long long* tokens;
+    int* pos;
+    int n_prompt, max_tokens;
+    uint16_t *hidden_buf, *qkv_buf, *attn_buf, *act_buf, *logits;
+    float *part_o, *part_ml;             // [hq][fused_step_splits][d], [hq][fused_step_splits][2]
+    unsigned* sync;                      // fused_step_sync_words() words, zero before the first launch
+    unsigned* status;                    // [1]: non-zero after a wait gave up
+    float* head_val;                     // [multiprocessors]
+    int* head_idx;
+    long long* picked;
+    uint16_t* hidden_trace;
+    // debug timeline (nullptr normally): 8 words per phase -- earliest entry, earliest / latest end of the wait,
+    // latest end of the phase over all CTAs (%globaltimer); phase 0 = embedding, 1 + 5*layer + {0..4}, then the head
+    unsigned long long* timeline;
+    int timeline_slots;
+};
+int fused_step_sync_words(int n_layers, int hkv);
+int fused_step_splits(int hkv);
+bool fused_step_supported(const FusedParams& p);
+cudaError_t fused_step_launch(const FusedParams& p, cudaStream_t stream);
+
 }  // namespace tfb

@@ -1,0 +1,681 @@
+// One decode step of the Qwen3 architecture as ONE cooperative launch (one CTA per SM):
+//   embed -> layers x [norm + q|k|v, q/k norm + RoPE + KV append + split-KV attention + merge, o + residual,
+//   norm + gate/up + SwiGLU, down + residual] -> final norm + head + greedy pick + position advance.
+//
+// Why one launch: as separate launches the step is bound by the chain of dependent launches (about 4 us of
+// release + activation staging + first-byte latency + tail per kernel, five per layer), not by bytes.  Here the
+// weight stream never stops at a dependency: weights do not depend on activations, so one producer thread per
+// CTA walks a STATIC schedule of 24 KB tiles (contiguous rows of the [out, in] matrices) through all phases of
+// all layers and lands them in a 192 KB shared-memory ring with bulk asynchronous copies (cp.async.bulk,
+// mbarrier transaction counts), as far ahead of the arithmetic as the ring allows.  While the consumer warps
+// wait for an activation vector, the ring -- nearly empty in steady state, because shared memory is read several
+// times faster than HBM fills it -- takes up to 4 us of HBM traffic.
+//
+// Data layout: matrix rows are dealt to the CTAs in contiguous blocks (CTA c owns rows [c*n/G, (c+1)*n/G));
+// a tile is 12 K-slices of 1024 elements: 12/KS rows of a k = KS*1024 wide matrix (gate/up: half gate rows, half
+// the matching up rows).  Each of the 12 consumer warps owns one (row, K-slice) of every tile and keeps its
+// slice of the activation vector in registers for the whole phase, so a tile costs it four 16-byte shared
+// loads per lane.  Slice sums meet in shared memory in fixed order (deterministic); rounding points are those
+// of gemv_kernel / attn_gqa_kernel / lm_head_kernel.
+//
+// Dependencies between phases are counters in global memory: a CTA adds one when its rows of a phase are
+// written (release), consumers poll until every producer CTA has arrived (acquire) and then read the vector
+// through L2.  Attention: KV head h, split s of the context on CTA s*hkv + h (the context is cut into at most
+// G/hkv splits, so no CTA has two); cached K/V rows are requested before the q|k|v counter is waited on; the
+// last split of a KV head to finish (a ticket) merges the partials.  Every wait is bounded: a timeout sets
+// *status, and every later wait of that CTA returns at once, so the launch always ends.
+//
+// HBM-bound: algorithmic bytes per launch = all weights once + the KV rows of positions [0, pos].
+#include "common.cuh"
+#include "kernels.h"
+#include "launch.h"
+
+namespace tfb {
+namespace {
+
+constexpr int kCW = 12;                          // consumer warps
+constexpr int kCT = kCW * 32;                    // consumer threads
+constexpr int kFusedThreads = kCT + 32;          // + the producer warp (warp 0)
+constexpr int kSliceLen = 1024;                  // K elements one warp keeps in registers
+constexpr int kTileBytes = kCW * kSliceLen * 2;  // 24 KB
+constexpr int kStages = 8;
+constexpr unsigned long long kWaitNs = 200ull * 1000 * 1000;   // every wait gives up after 0.2 s
+constexpr int kD = 128, kGQ = 2;                 // head dim and query heads per KV head of this build
+constexpr int kBatchRows = 8;                    // cache rows one warp holds in registers at a time
+
+struct FusedSmem {
+    alignas(128) unsigned char ring[kStages][kTileBytes];
+    alignas(8) unsigned long long full[kStages];
+    unsigned long long empty[kStages];
+    float part[2][kCW];
+    float red[16];
+    alignas(16) float q[kGQ][kD];
+    alignas(16) float knew[kD];
+    alignas(16) float vnew[kD];
+    float wm[kCW][kGQ], wl[kCW][kGQ];
+    alignas(16) float wo[kCW][kGQ][kD];
+    int flag;
+    volatile int abort;
+};
+
+__device__ __forceinline__ uint32_t s_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mb_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(s_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mb_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(s_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mb_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(s_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mb_try(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(s_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(s_u32(dst)), "l"(src), "r"(bytes), "r"(s_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" :: "n"(kCT) : "memory"); }
+__device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 lds16(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+// Bounded waits.  After the first timeout of a CTA every wait returns at once (the results are void, *status says so).
+__device__ __forceinline__ void wait_bar(FusedSmem& s, unsigned long long* bar, unsigned parity, unsigned* status, unsigned code) {
+    if (s.abort) return;
+    if (mb_try(bar, parity)) return;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        for (int i = 0; i < 64; ++i)
+            if (mb_try(bar, parity)) return;
+        if (s.abort) return;
+        if (global_ns() - t0 > kWaitNs) break;
+    }
+    s.abort = 1;
+    atomicOr(status, code);
+}
+// One thread of the CTA polls; the consumer barrier that follows hands the acquired view to the others.
+__device__ __forceinline__ void wait_count(FusedSmem& s, const unsigned* ctr, unsigned target, unsigned* status, unsigned code) {
+    if (s.abort) return;
+    if (ld_acquire(ctr) >= target) return;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        for (int i = 0; i < 16; ++i)
+            if (ld_acquire(ctr) >= target) return;
+        if (global_ns() - t0 > kWaitNs) break;
+    }
+    s.abort = 1;
+    atomicOr(status, code);
+}
+// A CTA's outputs of a phase are written (by the threads of one warp, or before a consumer_sync): publish them.
+__device__ __forceinline__ void arrive(unsigned* ctr) {
+    __threadfence();
+    atomicAdd(ctr, 1u);
+}
+
+// debug timeline of phase `ph` (one thread per CTA calls these)
+__device__ __forceinline__ void tl_enter(const FusedParams& p, int ph) {
+    if (p.timeline && ph < p.timeline_slots) atomicMin(p.timeline + 8 * ph, global_ns());
+}
+__device__ __forceinline__ void tl_waited(const FusedParams& p, int ph) {
+    if (p.timeline && ph < p.timeline_slots) {
+        const unsigned long long t = global_ns();
+        atomicMin(p.timeline + 8 * ph + 1, t);
+        atomicMax(p.timeline + 8 * ph + 2, t);
+    }
+}
+__device__ __forceinline__ void tl_done(const FusedParams& p, int ph) {
+    if (p.timeline && ph < p.timeline_slots) atomicMax(p.timeline + 8 * ph + 3, global_ns());
+}
+
+__device__ __forceinline__ void span(int n, int c, int G, int& u0, int& u1) {
+    u0 = int((long long)n * c / G);
+    u1 = int((long long)n * (c + 1) / G);
+}
+
+struct RingPos {
+    int stage;
+    unsigned parity;
+    __device__ __forceinline__ void next() {
+        if (++stage == kStages) { stage = 0; parity ^= 1u; }
+    }
+};
+
+// ---- producer: the tiles of one matrix phase, in the order the consumers take them ------------------------------
+__device__ __forceinline__ void produce(FusedSmem& s, RingPos& rp, const uint16_t* w, const uint16_t* w2, int n, int k,
+                                        int c, int G, unsigned* status) {
+    const int KS = k / kSliceLen, R = kCW / KS;
+    const int U = w2 ? R / 2 : R;                            // output units (rows, or gate/up row pairs) per tile
+    int u0, u1;
+    span(n, c, G, u0, u1);
+    for (int u = u0; u < u1; u += U) {
+        const int nu = min(U, u1 - u);
+        wait_bar(s, &s.empty[rp.stage], rp.parity ^ 1u, status, 0x10000u);
+        const unsigned bytes = unsigned(nu) * unsigned(k) * 2u;
+        mb_expect_tx(&s.full[rp.stage], w2 ? 2u * bytes : bytes);
+        bulk_load(s.ring[rp.stage], w + size_t(u) * k, bytes, &s.full[rp.stage]);
+        if (w2) bulk_load(s.ring[rp.stage] + size_t(U) * k * 2, w2 + size_t(u) * k, bytes, &s.full[rp.stage]);
+        rp.next();
+    }
+}
+
+enum { kStore = 0, kResidual = 1, kSwiglu = 2, kHead = 3 };
+
+struct HeadBest {
+    float v;
+    int i;
+};
+
+// ---- consumers: one matrix phase --------------------------------------------------------------------------------
+// y = epilogue(W . prologue(x)) for this CTA's rows.  `wait_ctr`/`wait_target`: the counter that says x is complete.
+template <int KIND, bool NORM>
+__device__ __forceinline__ void consume(FusedSmem& s, RingPos& rp, const FusedParams& p, int n, int k,
+                                        const uint16_t* x, const uint16_t* gamma, uint16_t* y, uint16_t* trace_row,
+                                        const unsigned* wait_ctr, unsigned wait_target, unsigned* arrive_ctr,
+                                        int c, int G, int cw, int lane, HeadBest* best, int ph) {
+    const int KS = k / kSliceLen, R = kCW / KS;
+    const int U = KIND == kSwiglu ? R / 2 : R;
+    const int r = cw / KS, j = cw % KS;
+    int u0, u1;
+    span(n, c, G, u0, u1);
+
+    // norm gains are weights: ask for them before the wait
+    uint4 gv[4];
+    if (NORM) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) gv[q] = *reinterpret_cast<const uint4*>(gamma + j * kSliceLen + q * 256 + lane * 8);
+    }
+    if (cw == 0 && lane == 0) {
+        tl_enter(p, ph);
+        wait_count(s, wait_ctr, wait_target, p.status, 0x100u);
+        tl_waited(p, ph);
+    }
+    consumer_sync();
+
+    // this warp's K-slice of the activation vector, in registers for the whole phase
+    float xf[32];
+    {
+        uint4 xv[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) xv[q] = __ldcg(reinterpret_cast<const uint4*>(x + j * kSliceLen + q * 256 + lane * 8));
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint32_t u[4] = {xv[q].x, xv[q].y, xv[q].z, xv[q].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { xf[q * 8 + 2 * i] = bf16_lo(u[i]); xf[q * 8 + 2 * i + 1] = bf16_hi(u[i]); }
+        }
+    }
+    // the residual of this CTA's rows (at most 32), one per lane of the finishing warp, ahead of the tile loop
+    float res = 0.f;
+    if (KIND == kResidual && cw == 0 && u0 + lane < u1) res = bf16_bits_to_f32(__ldcg(y + u0 + lane));
+    if (NORM) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) ss = fmaf(xf[i], xf[i], ss);
+        ss = warp_sum(ss);
+        if (r == 0 && lane == 0) s.red[j] = ss;
+        consumer_sync();
+        float tot = 0.f;
+        for (int q = 0; q < KS; ++q) tot += s.red[q];
+        const float rstd = rsqrtf(tot / float(k) + p.eps);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint32_t g[4] = {gv[q].x, gv[q].y, gv[q].z, gv[q].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {                     // Qwen3RMSNorm: round, then gain (a bf16 multiply)
+                xf[q * 8 + 2 * i] = round_bf16(round_bf16(xf[q * 8 + 2 * i] * rstd) * bf16_lo(g[i]));
+                xf[q * 8 + 2 * i + 1] = round_bf16(round_bf16(xf[q * 8 + 2 * i + 1] * rstd) * bf16_hi(g[i]));
+            }
+        }
+        if (trace_row && c == 0 && r == 0) {                  // the final-normed hidden state, for the trace
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) trace_row[j * kSliceLen + q * 256 + lane * 8 + i] = f32_to_bf16_bits(xf[q * 8 + i]);
+        }
+    }
+
+    int buf = 0;
+    for (int u = u0; u < u1; u += U) {
+        const int nu = min(U, u1 - u);
+        wait_bar(s, &s.full[rp.stage], rp.parity, p.status, 0x20000u);
+        const bool valid = KIND == kSwiglu ? (r % U) < nu : r < nu;
+        float acc0 = 0.f, acc1 = 0.f;
+        if (valid) {
+            const uint32_t base = s_u32(s.ring[rp.stage]) + uint32_t(r) * uint32_t(k) * 2u + uint32_t(j) * (kSliceLen * 2) + lane * 16;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint4 w = lds16(base + q * 512);
+                const float4 xa = make_float4(xf[q * 8], xf[q * 8 + 1], xf[q * 8 + 2], xf[q * 8 + 3]);
+                const float4 xb = make_float4(xf[q * 8 + 4], xf[q * 8 + 5], xf[q * 8 + 6], xf[q * 8 + 7]);
+                if (q & 1) acc1 = dot8(w, xa, xb, acc1); else acc0 = dot8(w, xa, xb, acc0);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mb_arrive(&s.empty[rp.stage]);          // this warp has read its part of the stage
+        rp.next();
+        const float sum = warp_sum(acc0 + acc1);
+        if (lane == 0) s.part[buf][cw] = sum;
+        consumer_sync();
+        if (cw == 0 && lane < nu) {                            // K-slices added in fixed order, epilogue
+            float v = 0.f, v2 = 0.f;
+            for (int q = 0; q < KS; ++q) {
+                v += s.part[buf][lane * KS + q];
+                if (KIND == kSwiglu) v2 += s.part[buf][(lane + U) * KS + q];
+            }
+            const int row = u + lane;
+            if (KIND == kStore) {
+                y[row] = f32_to_bf16_bits(v);
+            } else if (KIND == kSwiglu) {
+                const float g = round_bf16(v), up = round_bf16(v2);
+                y[row] = f32_to_bf16_bits(round_bf16(silu_f32(g)) * up);
+            } else if (KIND == kHead) {
+                const float sc = round_bf16(v);
+                if (y) y[row] = f32_to_bf16_bits(sc);
+                if (sc > best->v || (sc == best->v && row < best->i)) { best->v = sc; best->i = row; }
+            }
+        }
+        if (KIND == kResidual && cw == 0) {                    // (all lanes: the residual comes from another lane)
+            float v = 0.f;
+            if (lane < nu)
+                for (int q = 0; q < KS; ++q) v += s.part[buf][lane * KS + q];
+            const float mine = __shfl_sync(0xffffffffu, res, (u - u0 + lane) & 31);
+            if (lane < nu) {
+                const uint16_t out = f32_to_bf16_bits(mine + round_bf16(v));
+                y[u + lane] = out;
+                if (trace_row) trace_row[u + lane] = out;
+            }
+        }
+        buf ^= 1;
+    }
+    consumer_sync();                                            // (also protects s.red / s.part against the next phase)
+    if (cw == 0 && lane == 0) {
+        if (arrive_ctr) arrive(arrive_ctr);
+        tl_done(p, ph);
+    }
+}
+
+__device__ __forceinline__ size_t kv_offset(const FusedParams& p, int pos, int h) {
+    const int page = p.block_table[pos / p.page_size];
+    return ((size_t(page) * p.page_size + (pos % p.page_size)) * p.hkv + h) * kD;
+}
+
+// ---- consumers: attention of one layer ------------------------------------------------------------------------
+__device__ __forceinline__ void attend(FusedSmem& s, const FusedParams& p, const FusedLayer& L, const unsigned* qkv_ctr,
+                                       unsigned* tickets, unsigned* done_ctr, int pos, int c, int G, int cw, int lane,
+                                       int ph) {
+    const int total = pos + 1;
+    const int ns_max = min(G / p.hkv, 64);
+    const int SL = max(16, ((total + ns_max - 1) / ns_max + 15) & ~15);
+    const int NS = (total + SL - 1) / SL;
+    const int h = c % p.hkv, sp = c / p.hkv;
+    if (sp >= NS || c >= p.hkv * ns_max) return;
+    const int p0 = sp * SL, p1 = min(p0 + SL, total), n = p1 - p0;
+    const bool owner = sp == NS - 1;
+    const uint16_t* kpool = L.k_pool;
+    const uint16_t* vpool = L.v_pool;
+
+    // cached rows do not depend on this token: the first batch is requested before the q|k|v counter is waited on
+    uint2 kreg[kBatchRows], vreg[kBatchRows];
+#pragma unroll
+    for (int t = 0; t < kBatchRows; ++t) {
+        const int pp = p0 + cw + kCW * t;
+        kreg[t] = make_uint2(0, 0);
+        vreg[t] = make_uint2(0, 0);
+        if (pp < p1 && pp < pos) {
+            const size_t off = kv_offset(p, pp, h) + lane * 4;
+            kreg[t] = __ldg(reinterpret_cast<const uint2*>(kpool + off));
+            vreg[t] = __ldg(reinterpret_cast<const uint2*>(vpool + off));
+        }
+    }
+    // norm gains and the rotary row of this position are known too
+    const int nvec = kGQ + 2;
+    float gm[4], rc[4], rs[4];
+    if (cw <= kGQ) {
+        const uint16_t* gsrc = cw < kGQ ? L.gamma_q : L.gamma_k;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            gm[i] = bf16_bits_to_f32(gsrc[lane + 32 * i]);
+            rc[i] = bf16_bits_to_f32(p.cos_table[size_t(pos) * kD + lane + 32 * i]);
+            rs[i] = bf16_bits_to_f32(p.sin_table[size_t(pos) * kD + lane + 32 * i]);
+        }
+    }
+    if (cw == 0 && lane == 0) {
+        tl_enter(p, ph);
+        wait_count(s, qkv_ctr, unsigned(G), p.status, 0x200u);
+        tl_waited(p, ph);
+    }
+    consumer_sync();
+
+    // this token's q (2 heads), k, v of KV head h: one warp per vector, lane l holds elements l, l+32, l+64, l+96,
+    // so the rotate-half partner (64 away) sits in the same lane
+    if (cw < nvec) {
+        const uint16_t* src = cw < kGQ ? p.qkv_buf + size_t(h * kGQ + cw) * kD
+                              : cw == kGQ ? p.qkv_buf + size_t(p.hq) * kD + size_t(h) * kD
+                                          : p.qkv_buf + size_t(p.hq + p.hkv) * kD + size_t(h) * kD;
+        float xv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) xv[i] = bf16_bits_to_f32(__ldcg(src + lane + 32 * i));
+        if (cw == kGQ + 1) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s.vnew[lane + 32 * i] = xv[i];
+        } else {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) ss = fmaf(xv[i], xv[i], ss);
+            ss = warp_sum(ss);
+            const float rstd = rsqrtf(ss / float(kD) + p.eps);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) xv[i] = round_bf16(round_bf16(xv[i] * rstd) * gm[i]);
+            float out[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float partner = i < 2 ? -xv[i + 2] : xv[i - 2];
+                out[i] = round_bf16(__fadd_rn(__fmul_rn(xv[i], rc[i]), __fmul_rn(partner, rs[i])));
+                if (cw < kGQ) out[i] = round_bf16(out[i] * p.scale);
+            }
+            float* dst = cw < kGQ ? s.q[cw] : s.knew;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[lane + 32 * i] = out[i];
+        }
+    }
+    consumer_sync();
+    if (owner && (cw == kGQ || cw == kGQ + 1)) {                // append this token's row to the cache
+        uint16_t* dst = (cw == kGQ ? L.k_pool : L.v_pool) + kv_offset(p, pos, h);
+        const float* src = cw == kGQ ? s.knew : s.vnew;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dst[lane + 32 * i] = f32_to_bf16_bits(src[lane + 32 * i]);
+    }
+
+    float qv[kGQ][4];
+#pragma unroll
+    for (int jh = 0; jh < kGQ; ++jh) {
+        const float4 t4 = *reinterpret_cast<const float4*>(&s.q[jh][lane * 4]);
+        qv[jh][0] = t4.x; qv[jh][1] = t4.y; qv[jh][2] = t4.z; qv[jh][3] = t4.w;
+    }
+    float m[kGQ], l[kGQ], o[kGQ][4];
+#pragma unroll
+    for (int jh = 0; jh < kGQ; ++jh) { m[jh] = -INFINITY; l[jh] = 0.f; o[jh][0] = o[jh][1] = o[jh][2] = o[jh][3] = 0.f; }
+
+    for (int b0 = 0; b0 < n; b0 += kCW * kBatchRows) {
+        if (b0 > 0) {                                           // later batches of a long split: request them now
+#pragma unroll
+            for (int t = 0; t < kBatchRows; ++t) {
+                const int pp = p0 + b0 + cw + kCW * t;
+                kreg[t] = make_uint2(0, 0);
+                vreg[t] = make_uint2(0, 0);
+                if (pp < p1 && pp < pos) {
+                    const size_t off = kv_offset(p, pp, h) + lane * 4;
+                    kreg[t] = __ldg(reinterpret_cast<const uint2*>(kpool + off));
+                    vreg[t] = __ldg(reinterpret_cast<const uint2*>(vpool + off));
+                }
+            }
+        }
+        float sc[kGQ][kBatchRows], vf[kBatchRows][4];
+        float bm[kGQ];
+#pragma unroll
+        for (int jh = 0; jh < kGQ; ++jh) bm[jh] = -INFINITY;
+#pragma unroll
+        for (int t = 0; t < kBatchRows; ++t) {
+            const int pp = p0 + b0 + cw + kCW * t;
+            const bool valid = pp < p1;
+            float kf[4];
+            if (valid && pp == pos) {                            // this token's own row comes from shared memory
+                const float4 k4 = *reinterpret_cast<const float4*>(&s.knew[lane * 4]);
+                const float4 v4 = *reinterpret_cast<const float4*>(&s.vnew[lane * 4]);
+                kf[0] = k4.x; kf[1] = k4.y; kf[2] = k4.z; kf[3] = k4.w;
+                vf[t][0] = v4.x; vf[t][1] = v4.y; vf[t][2] = v4.z; vf[t][3] = v4.w;
+            } else {
+                kf[0] = bf16_lo(kreg[t].x); kf[1] = bf16_hi(kreg[t].x); kf[2] = bf16_lo(kreg[t].y); kf[3] = bf16_hi(kreg[t].y);
+                vf[t][0] = bf16_lo(vreg[t].x); vf[t][1] = bf16_hi(vreg[t].x); vf[t][2] = bf16_lo(vreg[t].y); vf[t][3] = bf16_hi(vreg[t].y);
+            }
+#pragma unroll
+            for (int jh = 0; jh < kGQ; ++jh) {
+                float d = qv[jh][0] * kf[0];
+                d = fmaf(qv[jh][1], kf[1], d);
+                d = fmaf(qv[jh][2], kf[2], d);
+                d = fmaf(qv[jh][3], kf[3], d);
+                d = warp_sum(d);
+                sc[jh][t] = valid ? d : -INFINITY;
+                bm[jh] = fmaxf(bm[jh], sc[jh][t]);
+            }
+        }
+#pragma unroll
+        for (int jh = 0; jh < kGQ; ++jh) {
+            if (bm[jh] == -INFINITY) continue;                   // no row of this warp in the batch
+            const float nm = fmaxf(m[jh], bm[jh]);
+            const float resc = m[jh] == -INFINITY ? 0.f : __expf(m[jh] - nm);
+            l[jh] *= resc;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[jh][e] *= resc;
+#pragma unroll
+            for (int t = 0; t < kBatchRows; ++t) {
+                const float pr = sc[jh][t] == -INFINITY ? 0.f : __expf(sc[jh][t] - nm);
+                l[jh] += pr;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) o[jh][e] = fmaf(pr, vf[t][e], o[jh][e]);
+            }
+            m[jh] = nm;
+        }
+    }
+#pragma unroll
+    for (int jh = 0; jh < kGQ; ++jh) {
+        if (lane == 0) { s.wm[cw][jh] = m[jh]; s.wl[cw][jh] = l[jh]; }
+        *reinterpret_cast<float4*>(&s.wo[cw][jh][lane * 4]) = make_float4(o[jh][0], o[jh][1], o[jh][2], o[jh][3]);
+    }
+    consumer_sync();
+
+    // the warps' partial (max, sum, weighted V) of this split, folded in warp order
+    const int tid = cw * 32 + lane;
+    const int jh = tid / kD, d = tid % kD;                       // threads 0..255: one output element each
+    if (tid < kGQ * kD) {
+        float M = -INFINITY;
+        for (int w = 0; w < kCW; ++w) M = fmaxf(M, s.wm[w][jh]);
+        float num = 0.f, den = 0.f;
+        for (int w = 0; w < kCW; ++w) {
+            const float wgt = s.wm[w][jh] == -INFINITY ? 0.f : __expf(s.wm[w][jh] - M);
+            num = fmaf(wgt, s.wo[w][jh][d], num);
+            den = fmaf(wgt, s.wl[w][jh], den);
+        }
+        const int head = h * kGQ + jh;
+        if (NS == 1) {
+            p.attn_buf[size_t(head) * kD + d] = f32_to_bf16_bits(num / den);
+        } else {
+            p.part_o[(size_t(head) * ns_max + sp) * kD + d] = num;
+            if (d == 0) {
+                p.part_ml[(size_t(head) * ns_max + sp) * 2] = M;
+                p.part_ml[(size_t(head) * ns_max + sp) * 2 + 1] = den;
+            }
+        }
+    }
+    if (NS > 1) {
+        __threadfence();                                         // every writer publishes its own partials
+        consumer_sync();
+        if (tid == 0) s.flag = atomicAdd(&tickets[h], 1u) == unsigned(NS - 1);
+        consumer_sync();
+        if (!s.flag) return;                                     // another split of this KV head merges
+        __threadfence();
+        if (tid < kGQ * kD) {
+            const int head = h * kGQ + jh;
+            const float* ml = p.part_ml + size_t(head) * ns_max * 2;
+            float M = -INFINITY;
+            for (int q = 0; q < NS; ++q) M = fmaxf(M, __ldcg(ml + 2 * q));
+            float num = 0.f, den = 0.f;
+            for (int q = 0; q < NS; ++q) {
+                const float wgt = __expf(__ldcg(ml + 2 * q) - M);
+                num = fmaf(wgt, __ldcg(p.part_o + (size_t(head) * ns_max + q) * kD + d), num);
+                den = fmaf(wgt, __ldcg(ml + 2 * q + 1), den);
+            }
+            p.attn_buf[size_t(head) * kD + d] = f32_to_bf16_bits(num / den);
+        }
+    }
+    __threadfence();
+    consumer_sync();
+    if (tid == 0) {
+        atomicAdd(done_ctr, 1u);                                 // one arrival per KV head
+        tl_done(p, ph);
+    }
+}
+
+__global__ void __launch_bounds__(kFusedThreads, 1) qwen3_step_kernel(const FusedParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    FusedSmem& s = *reinterpret_cast<FusedSmem*>(smem_raw);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = blockIdx.x, G = gridDim.x;
+    const int pos = *p.pos;
+    if (pos < 0 || pos >= p.max_ctx) return;                      // (uniform over the grid: nothing waits on anything)
+    const int H = p.hidden, L = p.n_layers, QP = p.hq * kD, NQKV = (p.hq + 2 * p.hkv) * kD;
+    const int per_layer = 5 + p.hkv;
+    unsigned* const glob = p.sync + L * per_layer;                 // [0] embedding copied, [1] head pairs written, [2] exit tickets
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kStages; ++i) { mb_init(&s.full[i], 1); mb_init(&s.empty[i], kCW); }
+        s.abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == 0) {
+        // ---- producer: every weight tile of the step, in consumption order ----
+        if (lane != 0) return;
+        RingPos rp{0, 0};
+        for (int l = 0; l < L; ++l) {
+            const FusedLayer Ly = p.layers[l];
+            produce(s, rp, Ly.w_qkv, nullptr, NQKV, H, c, G, p.status);
+            produce(s, rp, Ly.w_o, nullptr, H, QP, c, G, p.status);
+            produce(s, rp, Ly.w_gate, Ly.w_up, p.inter, H, c, G, p.status);
+            produce(s, rp, Ly.w_down, nullptr, H, p.inter, c, G, p.status);
+        }
+        produce(s, rp, p.w_head, nullptr, p.vocab, H, c, G, p.status);
+        return;
+    }
+
+    // ---- consumers ----
+    const int cw = warp - 1;
+    const int tid = cw * 32 + lane;
+    RingPos rp{0, 0};
+    {   // the embedding row of this step's token, dealt like the rows of the projections that update it
+        long long id = p.tokens[pos];
+        id = id < 0 ? 0 : (id >= p.vocab ? p.vocab - 1 : id);
+        int u0, u1;
+        span(H, c, G, u0, u1);
+        for (int i = u0 + tid; i < u1; i += kCT) p.hidden_buf[i] = p.w_embed[size_t(id) * H + i];
+        consumer_sync();
+        if (tid == 0) {
+            arrive(&glob[0]);
+            tl_done(p, 0);
+        }
+    }
+    const unsigned* hidden_ready = &glob[0];
+    for (int l = 0; l < L; ++l) {
+        const FusedLayer& Ly = p.layers[l];
+        unsigned* ctr = p.sync + l * per_layer;                    // [0] q|k|v, [1] attention, [2] o, [3] gate/up, [4] down, [5..] tickets
+        consume<kStore, true>(s, rp, p, NQKV, H, p.hidden_buf, Ly.gamma_in, p.qkv_buf, nullptr, hidden_ready, unsigned(G),
+                              &ctr[0], c, G, cw, lane, nullptr, 1 + 5 * l);
+        attend(s, p, Ly, &ctr[0], &ctr[5], &ctr[1], pos, c, G, cw, lane, 2 + 5 * l);
+        consume<kResidual, false>(s, rp, p, H, QP, p.attn_buf, nullptr, p.hidden_buf, nullptr, &ctr[1], unsigned(p.hkv),
+                                  &ctr[2], c, G, cw, lane, nullptr, 3 + 5 * l);
+        consume<kSwiglu, true>(s, rp, p, p.inter, H, p.hidden_buf, Ly.gamma_post, p.act_buf, nullptr, &ctr[2], unsigned(G),
+                               &ctr[3], c, G, cw, lane, nullptr, 4 + 5 * l);
+        consume<kResidual, false>(s, rp, p, H, p.inter, p.act_buf, nullptr, p.hidden_buf,
+                                  p.hidden_trace ? p.hidden_trace + size_t(l) * H : nullptr, &ctr[3], unsigned(G), &ctr[4],
+                                  c, G, cw, lane, nullptr, 5 + 5 * l);
+        hidden_ready = &ctr[4];
+    }
+    HeadBest best{-INFINITY, 0x7fffffff};
+    consume<kHead, true>(s, rp, p, p.vocab, H, p.hidden_buf, p.gamma_final, p.logits,
+                         p.hidden_trace ? p.hidden_trace + size_t(L) * H : nullptr, hidden_ready, unsigned(G), nullptr,
+                         c, G, cw, lane, &best, 1 + 5 * L);
+    if (cw == 0) {
+        // this CTA's (best logit, lowest index), then the pick over all CTAs by CTA 0
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best.v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best.i, o);
+            if (ov > best.v || (ov == best.v && oi < best.i)) { best.v = ov; best.i = oi; }
+        }
+        if (lane == 0) {
+            p.head_val[c] = best.v;
+            p.head_idx[c] = best.i;
+            arrive(&glob[1]);
+        }
+        if (c == 0) {
+            if (lane == 0) wait_count(s, &glob[1], unsigned(G), p.status, 0x400u);
+            __syncwarp();
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+            for (int q = lane; q < G; q += 32) {
+                const float ov = __ldcg(p.head_val + q);
+                const int oi = __ldcg(p.head_idx + q);
+                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            }
+            if (lane == 0) {
+                if (p.picked) *p.picked = bi;
+                if (pos + 1 < p.max_tokens) {
+                    if (pos + 1 >= p.n_prompt) p.tokens[pos + 1] = bi;
+                    *p.pos = pos + 1;
+                }
+            }
+        }
+        // the last CTA to leave puts every counter back to zero for the next launch
+        if (lane == 0) s.flag = atomicAdd(&glob[2], 1u) == unsigned(G - 1);
+        __syncwarp();
+        if (s.flag) {
+            __threadfence();
+            for (int i = lane; i < L * per_layer + 3; i += 32) p.sync[i] = 0u;
+        }
+    }
+}
+
+}  // namespace
+
+int fused_step_sync_words(int n_layers, int hkv) { return n_layers * (5 + hkv) + 3; }
+int fused_step_splits(int hkv) { const int s = sm_count() / (hkv > 0 ? hkv : 1); return s < 64 ? s : 64; }
+
+bool fused_step_supported(const FusedParams& p) {
+    const int QP = p.hq * kD;
+    auto ok_k = [](int k) { return k >= kSliceLen && k % kSliceLen == 0 && kCW % (k / kSliceLen) == 0; };
+    const int G = sm_count();
+    return p.n_layers >= 1 && p.n_layers <= kFusedMaxLayers && p.d == kD && p.hkv >= 1 && p.hq == kGQ * p.hkv &&
+           ok_k(p.hidden) && ok_k(QP) && ok_k(p.inter) && (kCW / (p.hidden / kSliceLen)) % 2 == 0 &&
+           p.hidden <= 32 * G && p.hkv <= G && p.inter >= 1 && p.vocab >= 1;
+}
+
+cudaError_t fused_step_launch(const FusedParams& p, cudaStream_t stream) {
+    if (!fused_step_supported(p)) return cudaErrorInvalidValue;
+    const size_t smem = sizeof(FusedSmem);
+    static PerDeviceOnce once;
+    if (once.first()) {
+        cudaError_t e = cudaFuncSetAttribute(qwen3_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return e;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sm_count());
+    cfg.blockDim = dim3(kFusedThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;               // every CTA resident: they wait on one another
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, qwen3_step_kernel, p);
+}
+
+}  // namespace tfb

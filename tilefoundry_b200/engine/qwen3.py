@@ -18,6 +18,16 @@ from ..authored.qwen3_1_7b import Qwen3Config, rope_tables
 from . import paged_kv
 from .session import DecodeSession, Generated  # noqa: F401
 
+KERNEL_FUSED = 6          # TFB_KERNEL_FUSED: the whole step as one cooperative launch
+
+
+def fused_step_supported(cfg: Qwen3Config) -> bool:
+    """Shapes the one-launch step is built for (the C ABI refuses the others with TFB_EINVAL)."""
+    ok_k = lambda k: k >= 1024 and k % 1024 == 0 and 12 % (k // 1024) == 0
+    return (cfg.head_dim == 128 and cfg.num_attention_heads == 2 * cfg.num_key_value_heads
+            and ok_k(cfg.hidden_size) and ok_k(cfg.num_attention_heads * cfg.head_dim) and ok_k(cfg.intermediate_size)
+            and cfg.hidden_size in (1024, 2048, 3072, 6144))
+
 
 def pack_layer(w: dict) -> dict:
     """Authored ``(1, in, out)`` projections -> kernel layout ``[out, in]`` with q|k|v fused."""
@@ -69,6 +79,9 @@ class Qwen3Session(DecodeSession):
         bf, f32 = torch.bfloat16, torch.float32
         z = lambda *s, dtype=bf: torch.zeros(*s, device=dev, dtype=dtype)
         nsplit = lib.attn_splits(self.max_ctx)
+        self.fused = int(kernel) == KERNEL_FUSED
+        if self.fused:                    # the one-launch step cuts the context into up to (multiprocessors / hkv) splits
+            nsplit = max(nsplit, lib.load().tfb_qwen3_step_splits(HKV))
         self.tokens = z(self.max_ctx + 1, dtype=torch.int64)
         self.pos = z(1, dtype=torch.int32)
         self.hidden = z(H)
@@ -79,7 +92,7 @@ class Qwen3Session(DecodeSession):
         self.part_o = z(HQ * nsplit * D, dtype=f32)
         self.part_ml = z(HQ * nsplit * 2, dtype=f32)
         self.counters = z(HKV + 1, dtype=torch.int32)
-        n_head = lib.lm_head_scratch_entries(V)
+        n_head = max(lib.lm_head_scratch_entries(V), 1024)         # (the one-launch step: one entry per multiprocessor)
         self.head_val = z(n_head, dtype=f32)
         self.head_idx = z(n_head, dtype=torch.int32)
         self.trace = z(cfg.num_hidden_layers + 1, H) if trace_hidden else None
@@ -91,6 +104,12 @@ class Qwen3Session(DecodeSession):
                 setattr(s, name, lib.ptr(layer[name]))
         scale = float(torch.tensor(D ** -0.5, dtype=bf))   # the authored step holds it as a bf16 tensor
         self.chain_sync = torch.zeros(4, device=self.device, dtype=torch.int32)   # grid barrier + status of the chained launch
+        # the one-launch step: the layer table on the device (11 pointers per layer, the C struct's field order),
+        # its phase counters and its status word
+        self.step_layers = torch.tensor([[layer[name].data_ptr() for name, _ in lib.Qwen3Layer._fields_]
+                                         for layer in self.layers], dtype=torch.int64, device=dev)
+        self.step_sync = z(max(lib.load().tfb_qwen3_step_sync_words(len(self.layers), HKV), 1), dtype=torch.int32)
+        self.step_status = z(1, dtype=torch.int32)
         self.args = lib.Qwen3StepArgs(
             layers=self._layer_structs, n_layers=len(self.layers), hidden=H, hq=HQ, hkv=HKV, d=D, inter=I,
             vocab=V, eps=cfg.rms_norm_eps, scale=scale,
@@ -104,11 +123,13 @@ class Qwen3Session(DecodeSession):
             part_ml=lib.ptr(self.part_ml), counters=lib.ptr(self.counters), head_val=lib.ptr(self.head_val),
             head_idx=lib.ptr(self.head_idx), hidden_trace=lib.ptr(self.trace),
             pdl=int(pdl), l2_prefetch=int(l2_prefetch), kernel=int(kernel), picked=lib.ptr(self.picked),
-            chain_sync=lib.ptr(self.chain_sync), temperature=float(temperature), seed=int(seed) & (2 ** 64 - 1))
+            chain_sync=lib.ptr(self.chain_sync), temperature=float(temperature), seed=int(seed) & (2 ** 64 - 1),
+            step_layers=lib.ptr(self.step_layers), step_sync=lib.ptr(self.step_sync),
+            step_status=lib.ptr(self.step_status))
         self.graph = None
         self._graph_prompt = None
         #: kernels one step enqueues (embed + 5 per layer + lm_head [+ trace copies and final norm])
-        self.launches_per_step = 2 + 5 * len(self.layers) + (
+        self.launches_per_step = 1 if self.fused else 2 + 5 * len(self.layers) + (
             len(self.layers) + 1 if trace_hidden else 0)
 
     # weights read once per token, for roofline arithmetic
@@ -123,6 +144,14 @@ class Qwen3Session(DecodeSession):
     def step(self) -> None:
         """Enqueue one decode step on the current stream."""
         lib.check(lib.load().tfb_qwen3_decode_step(C.byref(self.args), lib.stream()), "tfb_qwen3_decode_step")
+
+    def check_status(self) -> None:
+        """Raise if a bounded wait of the one-launch step gave up (its results are void then)."""
+        code = int(self.step_status)
+        if code:
+            self.step_status.zero_()
+            self.step_sync.zero_()
+            raise RuntimeError(f"tfb_qwen3_decode_step (one launch): a bounded wait gave up (status {code:#x})")
 
     def prefill(self, n_tokens: int) -> None:
         """Process positions ``pos .. pos + n_tokens - 1`` of the token history in chunks of up to 32 tokens

@@ -63,7 +63,8 @@ class Qwen3StepArgs(C.Structure):
                 ("hidden_buf", _vp), ("qkv_buf", _vp), ("attn_buf", _vp), ("act_buf", _vp), ("logits", _vp),
                 ("part_o", _vp), ("part_ml", _vp), ("counters", _vp), ("head_val", _vp), ("head_idx", _vp),
                 ("hidden_trace", _vp), ("pdl", _i32), ("l2_prefetch", _i32), ("kernel", _i32), ("picked", _vp),
-                ("chain_sync", _vp), ("temperature", _f32), ("seed", _u64)]
+                ("chain_sync", _vp), ("temperature", _f32), ("seed", _u64),
+                ("step_layers", _vp), ("step_sync", _vp), ("step_status", _vp)]
 
 
 class GemvChainArgs(C.Structure):
@@ -257,6 +258,8 @@ SYMBOLS = {
     "tfb_attn_gqa_decode": (_i32, [C.POINTER(AttnGqaArgs), _vp]),
     "tfb_attn_gqa_decode_noalloc": (_i32, [C.POINTER(AttnGqaArgs), _vp]),
     "tfb_qwen3_decode_step": (_i32, [C.POINTER(Qwen3StepArgs), _vp]),
+    "tfb_qwen3_step_sync_words": (_i32, [_i32, _i32]),
+    "tfb_qwen3_step_splits": (_i32, [_i32]),
     "tfb_attn_mla_decode": (_i32, [C.POINTER(AttnMlaArgs), _vp]),
     "tfb_minicpm3_decode_step": (_i32, [C.POINTER(MiniCPM3StepArgs), _vp]),
     "tfb_residual_add": (_i32, [_vp, _vp, _vp, _i32, _f32, _vp]),
