@@ -114,11 +114,13 @@ def test_moe_functions_and_routing_indices(dev, sides):
         tokens = rm.post_norm(hidden.cpu())
         # routing: an integer output -- the experts bit-exact, slot by slot, except where two router logits are
         # exactly equal (their order is not determined); weights within tolerance
-        _check(tm.router.routing, rm.router.routing, (tokens.to(dev),), {"output[0]": CLOSE})
+        got_w, got_idx = tm.router.routing(tokens.to(dev))
+        want_w, want_idx = rm.router.routing(tokens)
         w_r = rm.router.constants["w_router"]
         w_r = w_r if w_r.shape[0] == tokens.shape[-1] else w_r.t()
-        parity.assert_same_routing(tm.router.routing(tokens.to(dev))[1], rm.router.routing(tokens)[1],
-                                   torch.matmul(tokens.to(w_r.dtype), w_r), f"trial {trial}")
+        parity.assert_same_routing(got_idx, want_idx, torch.matmul(tokens.to(w_r.dtype), w_r), f"trial {trial}")
+        assert got_idx.dtype == want_idx.dtype and got_w.dtype == want_w.dtype and got_w.shape == want_w.shape
+        assert_close_at_scale(got_w, want_w, f"routing weights, trial {trial}")
     weights, indices = rm.router.routing(tokens)
     args = tuple(t.to(dev) for t in (tokens, weights, indices))
     _check(tm.routed_experts, rm.routed_experts, args, {"output": CLOSE})

@@ -312,8 +312,8 @@ def test_session_matches_evaluator_tiny(dev, use_graph, kernel):
         assert_close_at_scale(v_got, v_ref[:, :total], f"layer {li} V cache")
 
 
-@pytest.mark.parametrize("use_graph", [False, True])
-def test_one_launch_step_matches_evaluator_small(dev, use_graph):
+@pytest.mark.parametrize("use_graph,kernel", [(False, 6), (True, 6), (True, 0)])
+def test_one_launch_step_matches_evaluator_small(dev, use_graph, kernel):
     """The whole step as one cooperative launch (TFB_KERNEL_FUSED) against the evaluator: logits, every layer's
     hidden state, greedy picks, caches and page table, over contexts that cross the 16-position split granularity
     and the 64-slot page boundaries; no bounded wait may have given up."""
@@ -321,9 +321,10 @@ def test_one_launch_step_matches_evaluator_small(dev, use_graph):
     from tilefoundry_b200.engine.qwen3 import KERNEL_FUSED
     cfg = q.QWEN3_SMALL
     n_prompt, n_new = 24, 140
-    want, sess, got = _session_vs_oracle(cfg, dev, n_prompt, n_new, 11, 0.05, use_graph, KERNEL_FUSED)
+    assert KERNEL_FUSED == 6
+    want, sess, got = _session_vs_oracle(cfg, dev, n_prompt, n_new, 11, 0.02, use_graph, kernel)   # (0: the same bars for the step of separate launches)
     sess.check_status()
-    assert sess.launches_per_step == 1
+    assert sess.launches_per_step == (1 if kernel == KERNEL_FUSED else 2 + 5 * cfg.num_hidden_layers + cfg.num_hidden_layers + 1)
     excused = _compare_run(cfg, want, sess, got, n_prompt, n_new)
     assert excused <= 8, f"{excused} near-tie picks out of {n_prompt + n_new - 1}"
     total = n_prompt + n_new - 1
@@ -351,7 +352,10 @@ def test_one_launch_step_equals_the_launch_per_kernel_step(dev):
     d = fused.generate(prompt, 200).tokens
     fused.check_status()
     assert b == c == d
-    assert sum(x == y for x, y in zip(a, b)) >= 190, (a, b)          # near-ties of random-weight logits may differ
+    # free-running sequences of random-weight models part ways for good at the first near-tie (the two forms add
+    # in different orders): a common prefix, not equality; parity proper is judged against the evaluator above
+    prefix = next((i for i, (x, y) in enumerate(zip(a, b)) if x != y), len(a))
+    assert prefix >= 8, (prefix, a[:prefix + 2], b[:prefix + 2])
 
 
 @pytest.mark.parametrize("kernel", [0, 6])
