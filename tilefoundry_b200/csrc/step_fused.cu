@@ -106,7 +106,10 @@ __device__ __forceinline__ void wait_bar(FusedSmem& s, unsigned long long* bar, 
     if (mb_try(bar, parity)) return;
     if (s.abort) return;
     const unsigned long long t0 = global_ns();
-    while (!mb_try(bar, parity)) {
+    for (;;) {                                   // (the timer is slow to read: one look per 32 tests)
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (mb_try(bar, parity)) return;
         if (s.abort) return;
         if (global_ns() - t0 > kWaitNs) { wait_failed(s, status, code); return; }
     }
@@ -117,7 +120,10 @@ __device__ __forceinline__ void wait_count(FusedSmem& s, const unsigned* ctr, un
     if (ld_acquire(ctr) >= target) return;
     if (s.abort) return;
     const unsigned long long t0 = global_ns();
-    while (ld_acquire(ctr) < target) {
+    for (;;) {                                   // (the timer is slow to read: one look per 32 polls)
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (ld_acquire(ctr) >= target) return;
         if (global_ns() - t0 > kWaitNs) { wait_failed(s, status, code); return; }
     }
 }
