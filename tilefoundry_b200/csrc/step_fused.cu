@@ -43,17 +43,13 @@ constexpr unsigned long long kWaitNs = 200ull * 1000 * 1000;   // every wait giv
 constexpr int kD = 128, kGQ = 2;                 // head dim and query heads per KV head of this build
 constexpr int kBatchRows = 8;                    // cache rows one warp holds in registers at a time
 constexpr int kMergeLoads = 20;                  // split partials one merging thread requests at once
-constexpr int kBatchTiles = 8;                   // weight tiles between two meetings of the consumer warps
 
 struct FusedSmem {
     alignas(128) unsigned char ring[kStages][kTileBytes];
     alignas(8) unsigned long long full[kStages];
     unsigned long long empty[kStages];
-    float part[2][kBatchTiles][kCW];
+    float part[2][kCW];
     float red[16];
-    float res[32];
-    float bestv[kBatchTiles * kCW];
-    int besti[kBatchTiles * kCW];
     alignas(16) float q[kGQ][kD];
     alignas(16) float knew[kD];
     alignas(16) float vnew[kD];
@@ -61,7 +57,8 @@ struct FusedSmem {
     alignas(16) float wo[kCW][kGQ][kD];
     int flag;
     volatile int abort;
-    FusedParams p;                               // the launch parameters, where the out-of-line phase bodies read them
+    unsigned koff[kCW][kBatchRows];              // element offset of warp w's cached row t of its first batch, or ~0u
+    unsigned new_off;                            // where this token's own row goes (the owner split)
 };
 
 __device__ __forceinline__ uint32_t s_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -97,35 +94,31 @@ __device__ __forceinline__ uint4 lds16(uint32_t addr) {
 }
 
 // Bounded waits.  After the first timeout of a CTA every wait returns at once (the results are void, *status says so).
-__device__ __noinline__ void wait_failed(FusedSmem& s, unsigned* status, unsigned code) {
+__device__ __forceinline__ void wait_bar(FusedSmem& s, unsigned long long* bar, unsigned parity, unsigned* status, unsigned code) {
+    if (s.abort) return;
+    if (mb_try(bar, parity)) return;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        for (int i = 0; i < 64; ++i)
+            if (mb_try(bar, parity)) return;
+        if (s.abort) return;
+        if (global_ns() - t0 > kWaitNs) break;
+    }
     s.abort = 1;
     atomicOr(status, code);
 }
-// (inline: a call in the tile loop would make the compiler park the loop's live registers in local memory around it)
-__device__ __forceinline__ void wait_bar(FusedSmem& s, unsigned long long* bar, unsigned parity, unsigned* status, unsigned code) {
-    if (mb_try(bar, parity)) return;
-    if (s.abort) return;
-    const unsigned long long t0 = global_ns();
-    for (;;) {                                   // (the timer is slow to read: one look per 32 tests)
-#pragma unroll 1
-        for (int i = 0; i < 32; ++i)
-            if (mb_try(bar, parity)) return;
-        if (s.abort) return;
-        if (global_ns() - t0 > kWaitNs) { wait_failed(s, status, code); return; }
-    }
-}
-// One thread of the CTA polls; the consumer barrier that follows hands the acquired view to the others.  (Inline
-// for the same reason: loads already in flight around the wait would have to land to be parked.)
+// One thread of the CTA polls; the consumer barrier that follows hands the acquired view to the others.
 __device__ __forceinline__ void wait_count(FusedSmem& s, const unsigned* ctr, unsigned target, unsigned* status, unsigned code) {
-    if (ld_acquire(ctr) >= target) return;
     if (s.abort) return;
+    if (ld_acquire(ctr) >= target) return;
     const unsigned long long t0 = global_ns();
-    for (;;) {                                   // (the timer is slow to read: one look per 32 polls)
-#pragma unroll 1
-        for (int i = 0; i < 32; ++i)
+    for (;;) {
+        for (int i = 0; i < 16; ++i)
             if (ld_acquire(ctr) >= target) return;
-        if (global_ns() - t0 > kWaitNs) { wait_failed(s, status, code); return; }
+        if (global_ns() - t0 > kWaitNs) break;
     }
+    s.abort = 1;
+    atomicOr(status, code);
 }
 // A CTA's outputs of a phase are written (by the threads of one warp, or before a consumer_sync): publish them.
 __device__ __forceinline__ void arrive(unsigned* ctr) {
@@ -148,14 +141,6 @@ __device__ __forceinline__ void tl_done(const FusedParams& p, int ph) {
     if (p.timeline && ph < p.timeline_slots) atomicMax(p.timeline + 8 * ph + 3, global_ns());
 }
 
-// debug tile log (CTA 0 only), after the phase slots: word 2*t = when tile t was requested, 2*t + 1 = when it was ready
-__device__ __forceinline__ void tl_tile(const FusedParams& p, int first_slot, int tile, int which) {
-    if (p.timeline && blockIdx.x == 0) {
-        const long long w = 8ll * first_slot + 2ll * tile + which;
-        if (w < 8ll * p.timeline_slots) p.timeline[w] = global_ns();
-    }
-}
-
 __device__ __forceinline__ void span(int n, int c, int G, int& u0, int& u1) {
     u0 = int((long long)n * c / G);
     u1 = int((long long)n * (c + 1) / G);
@@ -164,24 +149,18 @@ __device__ __forceinline__ void span(int n, int c, int G, int& u0, int& u1) {
 struct RingPos {
     int stage;
     unsigned parity;
-    int tile;                                    // running tile number (debug log)
     __device__ __forceinline__ void next() {
-        ++tile;
         if (++stage == kStages) { stage = 0; parity ^= 1u; }
     }
 };
 
 // ---- producer: the tiles of one matrix phase, in the order the consumers take them ------------------------------
-__device__ __noinline__ void produce(FusedSmem& s, RingPos& rp_io, const uint16_t* w, const uint16_t* w2, int n, int k,
-                                     int c, int G) {
-    const FusedParams& p = s.p;
-    unsigned* const status = p.status;
+__device__ __forceinline__ void produce(FusedSmem& s, RingPos& rp, const uint16_t* w, const uint16_t* w2, int n, int k,
+                                        int c, int G, unsigned* status) {
     const int KS = k / kSliceLen, R = kCW / KS;
     const int U = w2 ? R / 2 : R;                            // output units (rows, or gate/up row pairs) per tile
     int u0, u1;
     span(n, c, G, u0, u1);
-    RingPos rp = rp_io;                                      // in registers for the loop (the caller's copy is in memory)
-    const int log_slot = 2 + 5 * p.n_layers;
     for (int u = u0; u < u1; u += U) {
         const int nu = min(U, u1 - u);
         wait_bar(s, &s.empty[rp.stage], rp.parity ^ 1u, status, 0x10000u);
@@ -189,10 +168,8 @@ __device__ __noinline__ void produce(FusedSmem& s, RingPos& rp_io, const uint16_
         mb_expect_tx(&s.full[rp.stage], w2 ? 2u * bytes : bytes);
         bulk_load(s.ring[rp.stage], w + size_t(u) * k, bytes, &s.full[rp.stage]);
         if (w2) bulk_load(s.ring[rp.stage] + size_t(U) * k * 2, w2 + size_t(u) * k, bytes, &s.full[rp.stage]);
-        tl_tile(p, log_slot, rp.tile, 0);
         rp.next();
     }
-    rp_io = rp;
 }
 
 enum { kStore = 0, kResidual = 1, kSwiglu = 2, kHead = 3 };
@@ -202,74 +179,52 @@ struct HeadBest {
     int i;
 };
 
-struct PhaseArgs {
-    int kind;                    // kStore / kResidual / kSwiglu / kHead
-    bool norm;                   // Qwen3RMSNorm of x (gains `gamma`) in the prologue
-    int n, k;                    // output units (rows; gate/up row pairs) and row length
-    const uint16_t* x;
-    const uint16_t* gamma;
-    uint16_t* y;
-    uint16_t* trace_row;
-    const unsigned* wait_ctr;    // the counter that says x is complete, and its target
-    unsigned wait_target;
-    unsigned* arrive_ctr;
-    int ph;                      // phase number for the debug timeline
-};
-
 // ---- consumers: one matrix phase --------------------------------------------------------------------------------
-// y = epilogue(W . prologue(x)) for this CTA's rows.  ONE body for every phase of every layer (not inlined, no
-// unrolling over tiles): the step runs through a few thousand tiles, and code that does not fit the instruction
-// cache costs more than the arithmetic.
-__device__ __noinline__ void consume(FusedSmem& s, RingPos& rp_io, const PhaseArgs a, int c, int G, int cw, int lane,
-                                     HeadBest& best_io) {
-    const FusedParams& p = s.p;
-    RingPos rp = rp_io;                                      // in registers for the loop (the caller's copies are in memory)
-    HeadBest best = best_io;
-    const int log_slot = 2 + 5 * p.n_layers;
-    unsigned* const status = p.status;
-    uint16_t* const y = a.y;
-    uint16_t* const trace_row = a.trace_row;
-    const int kind = a.kind, k = a.k;
+// y = epilogue(W . prologue(x)) for this CTA's rows.  `wait_ctr`/`wait_target`: the counter that says x is complete.
+template <int KIND, bool NORM>
+__device__ __forceinline__ void consume(FusedSmem& s, RingPos& rp, const FusedParams& p, int n, int k,
+                                        const uint16_t* x, const uint16_t* gamma, uint16_t* y, uint16_t* trace_row,
+                                        const unsigned* wait_ctr, unsigned wait_target, unsigned* arrive_ctr,
+                                        int c, int G, int cw, int lane, HeadBest* best, int ph) {
     const int KS = k / kSliceLen, R = kCW / KS;
-    const int U = kind == kSwiglu ? R / 2 : R;
+    const int U = KIND == kSwiglu ? R / 2 : R;
     const int r = cw / KS, j = cw % KS;
-    const int tid = cw * 32 + lane;
     int u0, u1;
-    span(a.n, c, G, u0, u1);
+    span(n, c, G, u0, u1);
 
-    if (tid == 0) {
-        tl_enter(p, a.ph);
-        wait_count(s, a.wait_ctr, a.wait_target, p.status, 0x100u);
-        tl_waited(p, a.ph);
+    // norm gains are weights: ask for them before the wait
+    uint4 gv[4];
+    if (NORM) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) gv[q] = *reinterpret_cast<const uint4*>(gamma + j * kSliceLen + q * 256 + lane * 8);
+    }
+    if (cw == 0 && lane == 0) {
+        tl_enter(p, ph);
+        wait_count(s, wait_ctr, wait_target, p.status, 0x100u);
+        tl_waited(p, ph);
     }
     consumer_sync();
 
-    // this warp's K-slice of the activation vector, in registers for the whole phase: 32 values, kept as bf16 pairs
-    // (they are bf16 numbers) so that the tile loop fits the register budget without spilling; the norm gains come
-    // in the same round trip
-    uint32_t xp[16];
-    uint4 gv[4];
+    // this warp's K-slice of the activation vector, in registers for the whole phase
+    float xf[32];
     {
         uint4 xv[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) xv[q] = __ldcg(reinterpret_cast<const uint4*>(a.x + j * kSliceLen + q * 256 + lane * 8));
-        if (a.norm) {
+        for (int q = 0; q < 4; ++q) xv[q] = __ldcg(reinterpret_cast<const uint4*>(x + j * kSliceLen + q * 256 + lane * 8));
 #pragma unroll
-            for (int q = 0; q < 4; ++q) gv[q] = *reinterpret_cast<const uint4*>(a.gamma + j * kSliceLen + q * 256 + lane * 8);
+        for (int q = 0; q < 4; ++q) {
+            const uint32_t u[4] = {xv[q].x, xv[q].y, xv[q].z, xv[q].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { xf[q * 8 + 2 * i] = bf16_lo(u[i]); xf[q * 8 + 2 * i + 1] = bf16_hi(u[i]); }
         }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) { xp[q * 4] = xv[q].x; xp[q * 4 + 1] = xv[q].y; xp[q * 4 + 2] = xv[q].z; xp[q * 4 + 3] = xv[q].w; }
     }
-    // the residual of this CTA's rows (at most 32), parked in shared memory ahead of the tile loop
-    if (kind == kResidual && cw == 0 && u0 + lane < u1) s.res[lane] = bf16_bits_to_f32(__ldcg(a.y + u0 + lane));
-    if (a.norm) {
+    // the residual of this CTA's rows (at most 32), one per lane of the finishing warp, ahead of the tile loop
+    float res = 0.f;
+    if (KIND == kResidual && cw == 0 && u0 + lane < u1) res = bf16_bits_to_f32(__ldcg(y + u0 + lane));
+    if (NORM) {
         float ss = 0.f;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const float lo = bf16_lo(xp[i]), hi = bf16_hi(xp[i]);
-            ss = fmaf(lo, lo, ss);
-            ss = fmaf(hi, hi, ss);
-        }
+        for (int i = 0; i < 32; ++i) ss = fmaf(xf[i], xf[i], ss);
         ss = warp_sum(ss);
         if (r == 0 && lane == 0) s.red[j] = ss;
         consumer_sync();
@@ -281,84 +236,76 @@ __device__ __noinline__ void consume(FusedSmem& s, RingPos& rp_io, const PhaseAr
             const uint32_t g[4] = {gv[q].x, gv[q].y, gv[q].z, gv[q].w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {                     // Qwen3RMSNorm: round, then gain (a bf16 multiply)
-                const float lo = round_bf16(round_bf16(bf16_lo(xp[q * 4 + i]) * rstd) * bf16_lo(g[i]));
-                const float hi = round_bf16(round_bf16(bf16_hi(xp[q * 4 + i]) * rstd) * bf16_hi(g[i]));
-                xp[q * 4 + i] = (__float_as_uint(hi) & 0xffff0000u) | (__float_as_uint(lo) >> 16);
+                xf[q * 8 + 2 * i] = round_bf16(round_bf16(xf[q * 8 + 2 * i] * rstd) * bf16_lo(g[i]));
+                xf[q * 8 + 2 * i + 1] = round_bf16(round_bf16(xf[q * 8 + 2 * i + 1] * rstd) * bf16_hi(g[i]));
             }
         }
-        if (kind == kHead && a.trace_row && c == 0 && r == 0) {   // the final-normed hidden state, for the trace
+        if (trace_row && c == 0 && r == 0) {                  // the final-normed hidden state, for the trace
 #pragma unroll
             for (int q = 0; q < 4; ++q)
-                *reinterpret_cast<uint4*>(a.trace_row + j * kSliceLen + q * 256 + lane * 8) =
-                    make_uint4(xp[q * 4], xp[q * 4 + 1], xp[q * 4 + 2], xp[q * 4 + 3]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) trace_row[j * kSliceLen + q * 256 + lane * 8 + i] = f32_to_bf16_bits(xf[q * 8 + i]);
         }
     }
 
-    // Tiles are taken in batches of kBatchTiles: every warp runs its (row, K-slice) of each tile of the batch with
-    // nothing but the ring's own barriers in between; the slice sums meet in shared memory and one thread per
-    // output row adds them in fixed order and applies the epilogue.
-    const uint32_t my_off = uint32_t(r) * uint32_t(k) * 2u + uint32_t(j) * (kSliceLen * 2) + lane * 16;
-    int pb = 0;
-    for (int ub = u0; ub < u1; ub += kBatchTiles * U) {
-        const int nb = min(kBatchTiles, (u1 - ub + U - 1) / U);             // tiles in this batch
-#pragma unroll 1
-        for (int t = 0; t < nb; ++t) {
-            const int nu = min(U, u1 - (ub + t * U));
-            wait_bar(s, &s.full[rp.stage], rp.parity, status, 0x20000u);
-            if (tid == 0) tl_tile(p, log_slot, rp.tile, 1);
-            const bool valid = kind == kSwiglu ? (r % U) < nu : r < nu;
-            float acc = 0.f;
-            if (valid) {
-                const uint32_t base = s_u32(s.ring[rp.stage]) + my_off;
-                float a4[4];
+    int buf = 0;
+    for (int u = u0; u < u1; u += U) {
+        const int nu = min(U, u1 - u);
+        wait_bar(s, &s.full[rp.stage], rp.parity, p.status, 0x20000u);
+        const bool valid = KIND == kSwiglu ? (r % U) < nu : r < nu;
+        float acc0 = 0.f, acc1 = 0.f;
+        if (valid) {
+            const uint32_t base = s_u32(s.ring[rp.stage]) + uint32_t(r) * uint32_t(k) * 2u + uint32_t(j) * (kSliceLen * 2) + lane * 16;
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const uint4 w = lds16(base + q * 512);
-                    const float4 xa = make_float4(bf16_lo(xp[q * 4]), bf16_hi(xp[q * 4]), bf16_lo(xp[q * 4 + 1]), bf16_hi(xp[q * 4 + 1]));
-                    const float4 xb = make_float4(bf16_lo(xp[q * 4 + 2]), bf16_hi(xp[q * 4 + 2]), bf16_lo(xp[q * 4 + 3]), bf16_hi(xp[q * 4 + 3]));
-                    a4[q] = dot8(w, xa, xb, 0.f);
-                }
-                acc = (a4[0] + a4[1]) + (a4[2] + a4[3]);
+            for (int q = 0; q < 4; ++q) {
+                const uint4 w = lds16(base + q * 512);
+                const float4 xa = make_float4(xf[q * 8], xf[q * 8 + 1], xf[q * 8 + 2], xf[q * 8 + 3]);
+                const float4 xb = make_float4(xf[q * 8 + 4], xf[q * 8 + 5], xf[q * 8 + 6], xf[q * 8 + 7]);
+                if (q & 1) acc1 = dot8(w, xa, xb, acc1); else acc0 = dot8(w, xa, xb, acc0);
             }
-            __syncwarp();
-            if (lane == 0) mb_arrive(&s.empty[rp.stage]);          // this warp has read its part of the stage
-            rp.next();
-            acc = warp_sum(acc);
-            if (lane == 0) s.part[pb][t][cw] = acc;
         }
+        __syncwarp();
+        if (lane == 0) mb_arrive(&s.empty[rp.stage]);          // this warp has read its part of the stage
+        rp.next();
+        const float sum = warp_sum(acc0 + acc1);
+        if (lane == 0) s.part[buf][cw] = sum;
         consumer_sync();
-        if (tid < nb * U && ub + tid < u1) {                       // K-slices added in fixed order, epilogue
-            const int tb = tid / U, ru = tid % U;
-            const int row = ub + tid;
+        if (cw == 0 && lane < nu) {                            // K-slices added in fixed order, epilogue
             float v = 0.f, v2 = 0.f;
             for (int q = 0; q < KS; ++q) {
-                v += s.part[pb][tb][ru * KS + q];
-                if (kind == kSwiglu) v2 += s.part[pb][tb][(ru + U) * KS + q];
+                v += s.part[buf][lane * KS + q];
+                if (KIND == kSwiglu) v2 += s.part[buf][(lane + U) * KS + q];
             }
-            if (kind == kStore) {
+            const int row = u + lane;
+            if (KIND == kStore) {
                 y[row] = f32_to_bf16_bits(v);
-            } else if (kind == kSwiglu) {
+            } else if (KIND == kSwiglu) {
                 const float g = round_bf16(v), up = round_bf16(v2);
                 y[row] = f32_to_bf16_bits(round_bf16(silu_f32(g)) * up);
-            } else if (kind == kResidual) {
-                const uint16_t out = f32_to_bf16_bits(s.res[row - u0] + round_bf16(v));
-                y[row] = out;
-                if (trace_row) trace_row[row] = out;
-            } else {
+            } else if (KIND == kHead) {
                 const float sc = round_bf16(v);
                 if (y) y[row] = f32_to_bf16_bits(sc);
-                if (sc > best.v || (sc == best.v && row < best.i)) { best.v = sc; best.i = row; }
+                if (sc > best->v || (sc == best->v && row < best->i)) { best->v = sc; best->i = row; }
             }
         }
-        pb ^= 1;
+        if (KIND == kResidual && cw == 0) {                    // (all lanes: the residual comes from another lane)
+            float v = 0.f;
+            if (lane < nu)
+                for (int q = 0; q < KS; ++q) v += s.part[buf][lane * KS + q];
+            const float mine = __shfl_sync(0xffffffffu, res, (u - u0 + lane) & 31);
+            if (lane < nu) {
+                const uint16_t out = f32_to_bf16_bits(mine + round_bf16(v));
+                y[u + lane] = out;
+                if (trace_row) trace_row[u + lane] = out;
+            }
+        }
+        buf ^= 1;
     }
-    consumer_sync();                                            // (also protects s.red / s.part / s.res against the next phase)
-    if (tid == 0) {
-        if (a.arrive_ctr) arrive(a.arrive_ctr);
-        tl_done(p, a.ph);
+    consumer_sync();                                            // (also protects s.red / s.part against the next phase)
+    if (cw == 0 && lane == 0) {
+        if (arrive_ctr) arrive(arrive_ctr);
+        tl_done(p, ph);
     }
-    rp_io = rp;
-    best_io = best;
 }
 
 __device__ __forceinline__ size_t kv_offset(const FusedParams& p, int pos, int h) {
@@ -366,56 +313,32 @@ __device__ __forceinline__ size_t kv_offset(const FusedParams& p, int pos, int h
     return ((size_t(page) * p.page_size + (pos % p.page_size)) * p.hkv + h) * kD;
 }
 
-// What a CTA does in every layer's attention, worked out once per launch: the page table belongs to the
-// sequence, not to a layer, so the cache rows a warp reads sit at the same offsets in every layer's pools.
-struct AttnPlan {
-    bool active, owner;
-    int h, sp, NS, ns_max, p0, p1, n;
-    unsigned off[kBatchRows];                    // element offset of this warp's row t of the first batch, or ~0u
-    unsigned new_off;                            // where this token's own row goes (the owner split)
-};
-__device__ __forceinline__ AttnPlan plan_attention(const FusedParams& p, int pos, int c, int G, int cw) {
-    AttnPlan a;
-    const int total = pos + 1;
-    a.ns_max = min(G / p.hkv, 64);
-    const int SL = max(16, ((total + a.ns_max - 1) / a.ns_max + 15) & ~15);
-    a.NS = (total + SL - 1) / SL;
-    a.h = c % p.hkv;
-    a.sp = c / p.hkv;
-    a.active = a.sp < a.NS && c < p.hkv * a.ns_max;
-    a.p0 = a.sp * SL;
-    a.p1 = min(a.p0 + SL, total);
-    a.n = a.p1 - a.p0;
-    a.owner = a.sp == a.NS - 1;
-    a.new_off = (a.active && a.owner) ? unsigned(kv_offset(p, pos, a.h)) : 0u;
-#pragma unroll
-    for (int t = 0; t < kBatchRows; ++t) {
-        const int pp = a.p0 + cw + kCW * t;
-        a.off[t] = (a.active && pp < a.p1 && pp < pos) ? unsigned(kv_offset(p, pp, a.h)) : ~0u;
-    }
-    return a;
-}
-
 // ---- consumers: attention of one layer ------------------------------------------------------------------------
-__device__ __noinline__ void attend(FusedSmem& s, const FusedLayer& L, const AttnPlan& a, const unsigned* qkv_ctr,
-                                    unsigned* tickets, unsigned* done_ctr, int pos, int c, int G, int cw, int lane,
-                                    int ph) {
-    if (!a.active) return;
-    const FusedParams& p = s.p;
-    const int NS = a.NS, ns_max = a.ns_max, h = a.h, sp = a.sp, p0 = a.p0, p1 = a.p1, n = a.n;
-    const bool owner = a.owner;
+__device__ __forceinline__ void attend(FusedSmem& s, const FusedParams& p, const FusedLayer& L, const unsigned* qkv_ctr,
+                                       unsigned* tickets, unsigned* done_ctr, int pos, int c, int G, int cw, int lane,
+                                       int ph) {
+    const int total = pos + 1;
+    const int ns_max = min(G / p.hkv, 64);
+    const int SL = max(16, ((total + ns_max - 1) / ns_max + 15) & ~15);
+    const int NS = (total + SL - 1) / SL;
+    const int h = c % p.hkv, sp = c / p.hkv;
+    if (sp >= NS || c >= p.hkv * ns_max) return;
+    const int p0 = sp * SL, p1 = min(p0 + SL, total), n = p1 - p0;
+    const bool owner = sp == NS - 1;
     const uint16_t* kpool = L.k_pool;
     const uint16_t* vpool = L.v_pool;
 
     // cached rows do not depend on this token: the first batch is requested before the q|k|v counter is waited on
     uint2 kreg[kBatchRows], vreg[kBatchRows];
+    // (the page table belongs to the sequence, not to a layer: the offsets were worked out once, at the start)
 #pragma unroll
     for (int t = 0; t < kBatchRows; ++t) {
+        const unsigned off = s.koff[cw][t];
         kreg[t] = make_uint2(0, 0);
         vreg[t] = make_uint2(0, 0);
-        if (a.off[t] != ~0u) {
-            kreg[t] = __ldg(reinterpret_cast<const uint2*>(kpool + a.off[t] + lane * 4));
-            vreg[t] = __ldg(reinterpret_cast<const uint2*>(vpool + a.off[t] + lane * 4));
+        if (off != ~0u) {
+            kreg[t] = __ldg(reinterpret_cast<const uint2*>(kpool + off + lane * 4));
+            vreg[t] = __ldg(reinterpret_cast<const uint2*>(vpool + off + lane * 4));
         }
     }
     // norm gains and the rotary row of this position are known too
@@ -471,7 +394,7 @@ __device__ __noinline__ void attend(FusedSmem& s, const FusedLayer& L, const Att
     }
     consumer_sync();
     if (owner && (cw == kGQ || cw == kGQ + 1)) {                // append this token's row to the cache
-        uint16_t* dst = (cw == kGQ ? L.k_pool : L.v_pool) + a.new_off;
+        uint16_t* dst = (cw == kGQ ? L.k_pool : L.v_pool) + s.new_off;
         const float* src = cw == kGQ ? s.knew : s.vnew;
 #pragma unroll
         for (int i = 0; i < 4; ++i) dst[lane + 32 * i] = f32_to_bf16_bits(src[lane + 32 * i]);
@@ -638,7 +561,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) qwen3_step_kernel(const Fuse
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStages; ++i) { mb_init(&s.full[i], 1); mb_init(&s.empty[i], kCW); }
         s.abort = 0;
-        s.p = p;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -646,23 +568,34 @@ __global__ void __launch_bounds__(kFusedThreads, 1) qwen3_step_kernel(const Fuse
     if (warp == 0) {
         // ---- producer: every weight tile of the step, in consumption order ----
         if (lane != 0) return;
-        RingPos rp{0, 0, 0};
-#pragma unroll 1
+        RingPos rp{0, 0};
         for (int l = 0; l < L; ++l) {
             const FusedLayer Ly = p.layers[l];
-            produce(s, rp, Ly.w_qkv, nullptr, NQKV, H, c, G);
-            produce(s, rp, Ly.w_o, nullptr, H, QP, c, G);
-            produce(s, rp, Ly.w_gate, Ly.w_up, p.inter, H, c, G);
-            produce(s, rp, Ly.w_down, nullptr, H, p.inter, c, G);
+            produce(s, rp, Ly.w_qkv, nullptr, NQKV, H, c, G, p.status);
+            produce(s, rp, Ly.w_o, nullptr, H, QP, c, G, p.status);
+            produce(s, rp, Ly.w_gate, Ly.w_up, p.inter, H, c, G, p.status);
+            produce(s, rp, Ly.w_down, nullptr, H, p.inter, c, G, p.status);
         }
-        produce(s, rp, p.w_head, nullptr, p.vocab, H, c, G);
+        produce(s, rp, p.w_head, nullptr, p.vocab, H, c, G, p.status);
         return;
     }
 
     // ---- consumers ----
     const int cw = warp - 1;
     const int tid = cw * 32 + lane;
-    RingPos rp{0, 0, 0};
+    RingPos rp{0, 0};
+    {   // where this CTA's attention rows sit in every layer's pools (same split arithmetic as attend())
+        const int total = pos + 1, ns_max = min(G / p.hkv, 64);
+        const int SL = max(16, ((total + ns_max - 1) / ns_max + 15) & ~15), NS = (total + SL - 1) / SL;
+        const int h = c % p.hkv, sp = c / p.hkv;
+        const bool active = sp < NS && c < p.hkv * ns_max;
+        const int p0 = sp * SL, p1 = min(p0 + SL, total);
+        if (lane < kBatchRows) {
+            const int pp = p0 + cw + kCW * lane;
+            s.koff[cw][lane] = (active && pp < p1 && pp < pos) ? unsigned(kv_offset(p, pp, h)) : ~0u;
+        }
+        if (tid == 0) s.new_off = (active && sp == NS - 1) ? unsigned(kv_offset(p, pos, h)) : 0u;
+    }
     {   // the embedding row of this step's token, dealt like the rows of the projections that update it
         long long id = p.tokens[pos];
         id = id < 0 ? 0 : (id >= p.vocab ? p.vocab - 1 : id);
@@ -675,38 +608,28 @@ __global__ void __launch_bounds__(kFusedThreads, 1) qwen3_step_kernel(const Fuse
             tl_done(p, 0);
         }
     }
-    const AttnPlan plan = plan_attention(p, pos, c, G, cw);
-    HeadBest best{-INFINITY, 0x7fffffff};
     const unsigned* hidden_ready = &glob[0];
-#pragma unroll 1
     for (int l = 0; l < L; ++l) {
-        const FusedLayer Ly = p.layers[l];
+        const FusedLayer& Ly = p.layers[l];
         unsigned* ctr = p.sync + l * per_layer;                    // [0] q|k|v, [1] attention, [2] o, [3] gate/up, [4] down, [5..] tickets
-        uint16_t* tr = p.hidden_trace ? p.hidden_trace + size_t(l) * H : nullptr;
-        consume(s, rp, PhaseArgs{kStore, true, NQKV, H, p.hidden_buf, Ly.gamma_in, p.qkv_buf, nullptr, hidden_ready,
-                                    unsigned(G), &ctr[0], 1 + 5 * l}, c, G, cw, lane, best);
-        attend(s, Ly, plan, &ctr[0], &ctr[5], &ctr[1], pos, c, G, cw, lane, 2 + 5 * l);
-        consume(s, rp, PhaseArgs{kResidual, false, H, QP, p.attn_buf, nullptr, p.hidden_buf, nullptr, &ctr[1],
-                                    unsigned(p.hkv), &ctr[2], 3 + 5 * l}, c, G, cw, lane, best);
-        consume(s, rp, PhaseArgs{kSwiglu, true, p.inter, H, p.hidden_buf, Ly.gamma_post, p.act_buf, nullptr, &ctr[2],
-                                    unsigned(G), &ctr[3], 4 + 5 * l}, c, G, cw, lane, best);
-        consume(s, rp, PhaseArgs{kResidual, false, H, p.inter, p.act_buf, nullptr, p.hidden_buf, tr, &ctr[3],
-                                    unsigned(G), &ctr[4], 5 + 5 * l}, c, G, cw, lane, best);
+        consume<kStore, true>(s, rp, p, NQKV, H, p.hidden_buf, Ly.gamma_in, p.qkv_buf, nullptr, hidden_ready, unsigned(G),
+                              &ctr[0], c, G, cw, lane, nullptr, 1 + 5 * l);
+        attend(s, p, Ly, &ctr[0], &ctr[5], &ctr[1], pos, c, G, cw, lane, 2 + 5 * l);
+        consume<kResidual, false>(s, rp, p, H, QP, p.attn_buf, nullptr, p.hidden_buf, nullptr, &ctr[1], unsigned(p.hkv),
+                                  &ctr[2], c, G, cw, lane, nullptr, 3 + 5 * l);
+        consume<kSwiglu, true>(s, rp, p, p.inter, H, p.hidden_buf, Ly.gamma_post, p.act_buf, nullptr, &ctr[2], unsigned(G),
+                               &ctr[3], c, G, cw, lane, nullptr, 4 + 5 * l);
+        consume<kResidual, false>(s, rp, p, H, p.inter, p.act_buf, nullptr, p.hidden_buf,
+                                  p.hidden_trace ? p.hidden_trace + size_t(l) * H : nullptr, &ctr[3], unsigned(G), &ctr[4],
+                                  c, G, cw, lane, nullptr, 5 + 5 * l);
         hidden_ready = &ctr[4];
     }
-    consume(s, rp, PhaseArgs{kHead, true, p.vocab, H, p.hidden_buf, p.gamma_final, p.logits,
-                                p.hidden_trace ? p.hidden_trace + size_t(L) * H : nullptr, hidden_ready, unsigned(G), nullptr,
-                                1 + 5 * L}, c, G, cw, lane, best);
-    // this CTA's (best logit, lowest index) over the threads that finished rows, then the pick over all CTAs by CTA 0
-    if (tid < kBatchTiles * kCW) { s.bestv[tid] = best.v; s.besti[tid] = best.i; }
-    consumer_sync();
+    HeadBest best{-INFINITY, 0x7fffffff};
+    consume<kHead, true>(s, rp, p, p.vocab, H, p.hidden_buf, p.gamma_final, p.logits,
+                         p.hidden_trace ? p.hidden_trace + size_t(L) * H : nullptr, hidden_ready, unsigned(G), nullptr,
+                         c, G, cw, lane, &best, 1 + 5 * L);
     if (cw == 0) {
-        best = HeadBest{-INFINITY, 0x7fffffff};
-        for (int q = lane; q < kBatchTiles * kCW; q += 32) {
-            const float ov = s.bestv[q];
-            const int oi = s.besti[q];
-            if (ov > best.v || (ov == best.v && oi < best.i)) { best.v = ov; best.i = oi; }
-        }
+        // this CTA's (best logit, lowest index), then the pick over all CTAs by CTA 0
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, best.v, o);

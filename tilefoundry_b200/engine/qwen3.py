@@ -46,7 +46,9 @@ def pack_layer(w: dict) -> dict:
 class Qwen3Session(DecodeSession):
     def __init__(self, cfg: Qwen3Config, resource, *, max_ctx: int = 2176, device="cuda:0",
                  keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True,
-                 l2_prefetch: int = 0, kernel: int = 0, temperature: float = 0.0, seed: int = 0):
+                 l2_prefetch: int = 0, kernel: int | None = None, temperature: float = 0.0, seed: int = 0):
+        """*kernel*: ``TFB_KERNEL_*`` of the step; ``None`` picks the one-launch step (``KERNEL_FUSED``) where the
+        shapes allow it and the pick is greedy, else the step of one launch per kernel (0)."""
         if not torch.cuda.is_available():
             raise RuntimeError("Qwen3Session needs a CUDA device; there is no CPU path")
         lib.load()
@@ -54,6 +56,8 @@ class Qwen3Session(DecodeSession):
         self.max_ctx = int(max_ctx)
         dev = self.device
         to = lambda t: t.to(dev)
+        if kernel is None:
+            kernel = KERNEL_FUSED if fused_step_supported(cfg) and temperature <= 0.0 else 0
 
         from .packed import PackedQwen3, pack
         # a resource speaks the authored names and is packed here; a PackedQwen3 (engine/packed.py) is already in
