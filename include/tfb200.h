@@ -175,6 +175,15 @@ typedef struct {
      * (own generator: the draw is keyed by the vocabulary index, not by a launch geometry). */
     float temperature;
     uint64_t seed;
+    /* end-of-sequence latch, optional (eos_ids may be NULL): when the token this step picks is a NEW token (its slot
+     * is past the prompt) and is one of eos_ids[0..n_eos), *stop_at becomes that slot's index in `tokens`; while
+     * *stop_at != 0 a step leaves tokens and *pos untouched, so a caller may replay a fixed number of steps and
+     * read where the sequence ended once, afterwards.  stop_at: int32[1], zeroed before a sequence starts.
+     * Stands in for the `if token in eos: break` of tests/models/orchestrator/causal_lm/generation.py:70-72. */
+    const int64_t* eos_ids;
+    int32_t* stop_at;
+    int32_t n_eos;
+    int32_t reserved_eos;
 } tfb_lm_head_args;
 TFB_API int32_t tfb_lm_head_scratch_entries(int32_t n);
 TFB_API int tfb_lm_head_argmax(const tfb_lm_head_args* args, tfb_stream_t stream);
@@ -318,6 +327,10 @@ typedef struct {
     const void* step_layers;
     uint32_t* step_sync;
     uint32_t* step_status;
+    const int64_t* eos_ids;   /* end-of-sequence latch: see tfb_lm_head_args (NULL: none) */
+    int32_t* stop_at;
+    int32_t n_eos;
+    int32_t reserved_eos;
 } tfb_qwen3_step_args;
 TFB_API int tfb_qwen3_decode_step(const tfb_qwen3_step_args* args, tfb_stream_t stream);
 TFB_API int32_t tfb_qwen3_step_sync_words(int32_t n_layers, int32_t hkv);
@@ -409,6 +422,10 @@ typedef struct {
     int32_t pdl;
     float temperature;        /* > 0: sample each token from softmax(logits / temperature) (see tfb_lm_head_args); else greedy */
     uint64_t seed;
+    const int64_t* eos_ids;   /* end-of-sequence latch: see tfb_lm_head_args (NULL: none) */
+    int32_t* stop_at;
+    int32_t n_eos;
+    int32_t reserved_eos;
 } tfb_minicpm3_step_args;
 TFB_API int tfb_minicpm3_decode_step(const tfb_minicpm3_step_args* args, tfb_stream_t stream);
 
@@ -555,6 +572,10 @@ typedef struct {
     float* gathered;          /* f32 [ep_world][2] */
     float temperature;        /* > 0: sample each token from softmax(logits / temperature) (see tfb_lm_head_args); else greedy */
     uint64_t seed;
+    const int64_t* eos_ids;   /* end-of-sequence latch: see tfb_lm_head_args (NULL: none) */
+    int32_t* stop_at;
+    int32_t n_eos;
+    int32_t reserved_eos;
 } tfb_granite_step_args;
 TFB_API int tfb_granite_decode_step(const tfb_granite_step_args* args, tfb_stream_t stream);
 /* One piece of the step, so a sharded caller can interleave its collectives: part 0 embed; 1 layer `layer` up to
@@ -841,6 +862,10 @@ typedef struct {
     int32_t reserved;
     float temperature;        /* > 0: sample each token from softmax(logits / temperature) (see tfb_lm_head_args); else greedy */
     uint64_t seed;
+    const int64_t* eos_ids;   /* end-of-sequence latch: see tfb_lm_head_args (NULL: none) */
+    int32_t* stop_at;
+    int32_t n_eos;
+    int32_t reserved_eos;
 } tfb_qwen35_step_args;
 TFB_API int tfb_qwen35_decode_step(const tfb_qwen35_step_args* args, tfb_stream_t stream);
 /* One piece of the step, so a sharded caller can put its exchange kernels between them: part 0 embed; part 1 layer

@@ -245,6 +245,10 @@ int tfb_lm_head_argmax(const tfb_lm_head_args* a, tfb_stream_t stream) {
     p.index_offset = a->index_offset;
     p.temperature = a->temperature > 0.f ? a->temperature : 0.f;
     p.seed = a->seed;
+    TFB_REQUIRE(a->n_eos >= 0 && a->n_eos <= 16 && (a->eos_ids == nullptr || (a->stop_at && a->n_eos > 0)), TFB_EINVAL);
+    p.eos_ids = reinterpret_cast<const long long*>(a->eos_ids);
+    p.n_eos = a->eos_ids ? a->n_eos : 0;
+    p.stop_at = a->stop_at;
     return done(tfb::lm_head_dispatch(p, a->prologue, S(stream), a->pdl != 0));
 }
 
@@ -369,6 +373,10 @@ static int qwen3_fused_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
     p.head_val = a->head_val; p.head_idx = a->head_idx;
     p.picked = reinterpret_cast<long long*>(a->picked);
     p.hidden_trace = static_cast<uint16_t*>(a->hidden_trace);
+    TFB_REQUIRE(a->n_eos >= 0 && a->n_eos <= 16 && (a->eos_ids == nullptr || (a->stop_at && a->n_eos > 0)), TFB_EINVAL);
+    p.eos_ids = reinterpret_cast<const long long*>(a->eos_ids);
+    p.n_eos = a->eos_ids ? a->n_eos : 0;
+    p.stop_at = a->stop_at;
     p.timeline = g_trace_buf;                                              // tfb_debug_trace, else nullptr
     p.timeline_slots = g_trace_cap;
     TFB_REQUIRE(a->cos_table && a->sin_table && a->block_table, TFB_EINVAL);
@@ -492,6 +500,7 @@ int tfb_qwen3_decode_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
     h.token_out = a->picked;
     h.tokens = a->tokens; h.pos = a->pos; h.n_prompt = a->n_prompt; h.max_tokens = a->max_tokens;
     h.temperature = a->temperature; h.seed = a->seed;
+    h.eos_ids = a->eos_ids; h.n_eos = a->n_eos; h.stop_at = a->stop_at;
     return tfb_lm_head_argmax(&h, stream);
 }
 

@@ -132,6 +132,7 @@ int tfb_minicpm3_decode_step(const tfb_minicpm3_step_args* a, tfb_stream_t strea
     h.token_out = a->picked;
     h.tokens = a->tokens; h.pos = a->pos; h.n_prompt = a->n_prompt; h.max_tokens = a->max_tokens;
     h.temperature = a->temperature; h.seed = a->seed;
+    h.eos_ids = a->eos_ids; h.n_eos = a->n_eos; h.stop_at = a->stop_at;
     return tfb_lm_head_argmax(&h, stream);
 }
 

@@ -282,6 +282,7 @@ static int qwen35_part(const tfb_qwen35_step_args* a, int part, int layer, tfb_s
     h.x_scale = 1.f; h.out_scale = 1.f; h.pdl = pdl; h.token_out = a->picked;
     h.tokens = a->tokens; h.pos = a->pos; h.n_prompt = a->n_prompt; h.max_tokens = a->max_tokens;
     h.temperature = a->temperature; h.seed = a->seed;
+    h.eos_ids = a->eos_ids; h.n_eos = a->n_eos; h.stop_at = a->stop_at;
     return tfb_lm_head_argmax(&h, stream);
 }
 

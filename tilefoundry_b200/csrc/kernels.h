@@ -97,6 +97,9 @@ struct HeadParams {
     int index_offset;
     float temperature;          // > 0: Gumbel-max sample from softmax(logits / temperature); else greedy
     unsigned long long seed;
+    const long long* eos_ids;   // end-of-sequence latch (nullptr: none): see tfb_lm_head_args
+    int n_eos;
+    int* stop_at;
 };
 int lm_head_ctas(int n);
 cudaError_t lm_head_dispatch(const HeadParams& p, int norm_mode, cudaStream_t stream, bool pdl);
@@ -388,6 +391,9 @@ struct FusedParams {
     int* head_idx;
     long long* picked;
     uint16_t* hidden_trace;
+    const long long* eos_ids;            // end-of-sequence latch (nullptr: none): see tfb_lm_head_args
+    int n_eos;
+    int* stop_at;
     // debug timeline (nullptr normally): 8 words per phase -- earliest entry, earliest / latest end of the wait,
     // latest end of the phase over all CTAs (%globaltimer); phase 0 = embedding, 1 + 5*layer + {0..4}, then the head
     unsigned long long* timeline;

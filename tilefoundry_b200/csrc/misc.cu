@@ -264,8 +264,13 @@ __global__ void __launch_bounds__(kHeadWarps * 32, 4) lm_head_kernel(const HeadP
         if (p.token_out) *p.token_out = best_i + p.index_offset;
         if (!p.pair_out && p.tokens && p.pos) {
             const int cur = *p.pos;
-            if (cur + 1 < p.max_tokens) {
-                if (cur + 1 >= p.n_prompt) p.tokens[cur + 1] = best_i;
+            const bool ended = p.stop_at != nullptr && *p.stop_at != 0;   // the sequence met an end token: nothing moves
+            if (!ended && cur + 1 < p.max_tokens) {
+                if (cur + 1 >= p.n_prompt) {
+                    p.tokens[cur + 1] = best_i;
+                    for (int e = 0; e < p.n_eos; ++e)
+                        if (p.eos_ids[e] == (long long)(best_i + p.index_offset)) *p.stop_at = cur + 1;
+                }
                 *p.pos = cur + 1;
             }
         }

@@ -554,6 +554,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) qwen3_step_kernel(const Fuse
     const int c = blockIdx.x, G = gridDim.x;
     const int pos = *p.pos;
     if (pos < 0 || pos >= p.max_ctx) return;                      // (uniform over the grid: nothing waits on anything)
+    if (p.stop_at != nullptr && *p.stop_at != 0) return;          // the sequence met an end token: the step is a no-op
     const int H = p.hidden, L = p.n_layers, QP = p.hq * kD, NQKV = (p.hq + 2 * p.hkv) * kD;
     const int per_layer = 5 + p.hkv;
     unsigned* const glob = p.sync + L * per_layer;                 // [0] embedding copied, [1] head pairs written, [2] exit tickets
@@ -660,7 +661,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) qwen3_step_kernel(const Fuse
             if (lane == 0) {
                 if (p.picked) *p.picked = bi;
                 if (pos + 1 < p.max_tokens) {
-                    if (pos + 1 >= p.n_prompt) p.tokens[pos + 1] = bi;
+                    if (pos + 1 >= p.n_prompt) {
+                        p.tokens[pos + 1] = bi;
+                        for (int e = 0; e < p.n_eos; ++e)
+                            if (p.eos_ids[e] == (long long)bi) *p.stop_at = pos + 1;
+                    }
                     *p.pos = pos + 1;
                 }
             }

@@ -166,10 +166,12 @@ class Qwen3Session(DecodeSession):
             self._prefill = Qwen3Prefill(self)
         self._prefill.run(n_tokens)
 
-    def generate(self, prompt_ids, max_new: int, use_graph: bool = True, prefill: bool = False):
+    def generate(self, prompt_ids, max_new: int, use_graph: bool = True, prefill: bool = False, eos=None):
         """As DecodeSession.generate; with ``prefill`` the prompt (all but its last token) is processed in chunks."""
         if not prefill:
-            return super().generate(prompt_ids, max_new, use_graph)
+            return super().generate(prompt_ids, max_new, use_graph, eos)
+        if eos is not None:
+            self.set_eos(eos)
         self.reset(prompt_ids)
         if self.n_prompt + max_new > self.max_ctx + 1:
             raise ValueError(f"{self.n_prompt}+{max_new} tokens exceed capacity {self.max_ctx}")
@@ -183,5 +185,5 @@ class Qwen3Session(DecodeSession):
         end.record()
         torch.cuda.synchronize()
         self._prefill.check_status()
-        out = self.tokens[self.n_prompt: self.n_prompt + max_new].tolist()
+        out = self.tokens[self.n_prompt: self.generated_end(self.n_prompt + max_new)].tolist()
         return Generated(out, mid.elapsed_time(end) / 1e3, start.elapsed_time(mid) / 1e3, self.n_prompt)

@@ -25,6 +25,8 @@ class DecodeSession:
 
     graph = None
     n_prompt = 0
+    eos_ids = None
+    stop_at = None
 
     def step(self) -> None:
         raise NotImplementedError
@@ -41,10 +43,34 @@ class DecodeSession:
         self.tokens[: prompt.numel()] = prompt.to(self.device)
         self.pos.zero_()
         self.counters.zero_()
+        if self.stop_at is not None:
+            self.stop_at.zero_()
         if self.args.n_prompt != prompt.numel():
             self.args.n_prompt = int(prompt.numel())
             self.graph = None                         # the prompt length is baked into the capture
         self.n_prompt = int(prompt.numel())
+
+    def set_eos(self, eos_ids) -> None:
+        """End-of-sequence token ids (at most 16; empty: none).  Once a step picks one of them as a NEW token the
+        sequence is over: the head kernel latches the slot in ``stop_at`` on the device and every later step leaves
+        the token history and the position alone, so ``generate`` can replay its fixed number of steps without a
+        host round trip and read where the sequence ended once, at the end (the reference loop asks the host every
+        token: ``tests/models/orchestrator/causal_lm/generation.py:70-72``)."""
+        from .. import lib
+        ids = [int(t) for t in eos_ids]
+        if len(ids) > 16:
+            raise ValueError("at most 16 end-of-sequence ids")
+        if not hasattr(self.args, "eos_ids"):
+            raise NotImplementedError(f"{type(self).__name__} has no end-of-sequence latch")
+        if getattr(self, "world", 1) > 1 and ids:
+            raise NotImplementedError("the sharded step's pick exchange has no end-of-sequence latch")
+        self.eos_ids = torch.tensor(ids, dtype=torch.int64, device=self.device) if ids else None
+        if self.stop_at is None:
+            self.stop_at = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.args.eos_ids = lib.ptr(self.eos_ids)
+        self.args.n_eos = len(ids)
+        self.args.stop_at = lib.ptr(self.stop_at) if ids else None
+        self.graph = None                             # the pointers are baked into a capture
 
     def state_tensors(self) -> list:
         """Device tensors, besides the token history and the position, that a step updates in place and a later
@@ -54,10 +80,13 @@ class DecodeSession:
 
     def snapshot(self) -> dict:
         """Copy of everything needed to return to the current position later with ``restore``."""
-        return {"tokens": self.tokens.clone(), "pos": self.pos.clone(), "state": [t.clone() for t in self.state_tensors()]}
+        return {"tokens": self.tokens.clone(), "pos": self.pos.clone(), "state": [t.clone() for t in self.state_tensors()],
+                "stop_at": None if self.stop_at is None else self.stop_at.clone()}
 
     def restore(self, snap: dict) -> None:
         self.tokens.copy_(snap["tokens"]); self.pos.copy_(snap["pos"])
+        if self.stop_at is not None and snap.get("stop_at") is not None:
+            self.stop_at.copy_(snap["stop_at"])
         for dst, src in zip(self.state_tensors(), snap["state"]):
             dst.copy_(src)
 
@@ -87,8 +116,11 @@ class DecodeSession:
         for _ in range(steps):
             self.graph.replay() if use_graph else self.step()
 
-    def generate(self, prompt_ids, max_new: int, use_graph: bool = True) -> Generated:
-        """Walk the prompt, then continue greedily for *max_new* tokens; one sync at each end."""
+    def generate(self, prompt_ids, max_new: int, use_graph: bool = True, eos=None) -> Generated:
+        """Walk the prompt, then continue greedily for *max_new* tokens; one sync at each end.  *eos*: token ids
+        that end the sequence; the tokens before the first of them are returned (``set_eos``)."""
+        if eos is not None:
+            self.set_eos(eos)
         self.reset(prompt_ids)
         n_prompt = self.n_prompt
         if n_prompt + max_new > self.max_ctx + 1:
@@ -102,5 +134,11 @@ class DecodeSession:
         self.run(max_new, use_graph)               # step at position p writes token p+1
         end.record()
         torch.cuda.synchronize()
-        out = self.tokens[n_prompt: n_prompt + max_new].tolist()
+        out = self.tokens[n_prompt: self.generated_end(n_prompt + max_new)].tolist()
         return Generated(out, mid.elapsed_time(end) / 1e3, start.elapsed_time(mid) / 1e3, n_prompt)
+
+    def generated_end(self, limit: int) -> int:
+        """Index in the token history one past the last generated token that counts: the slot of the end-of-sequence
+        token if one was picked (it is not part of the output), else *limit*."""
+        stop = int(self.stop_at) if self.stop_at is not None and self.eos_ids is not None else 0
+        return min(stop, limit) if stop else limit

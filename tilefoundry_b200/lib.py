@@ -35,7 +35,8 @@ class LmHeadArgs(C.Structure):
                 ("n", _i32), ("k", _i32), ("prologue", _i32),
                 ("eps", _f32), ("x_scale", _f32), ("out_scale", _f32), ("pdl", _i32),
                 ("tokens", _vp), ("pos", _vp), ("n_prompt", _i32), ("max_tokens", _i32), ("kernel", _i32), ("self_prefetch", _i32), ("index_offset", _i32), ("pair_out", _vp),
-                ("temperature", _f32), ("seed", _u64)]
+                ("temperature", _f32), ("seed", _u64),
+                ("eos_ids", _vp), ("stop_at", _vp), ("n_eos", _i32), ("reserved_eos", _i32)]
 
 
 class AttnGqaArgs(C.Structure):
@@ -64,7 +65,8 @@ class Qwen3StepArgs(C.Structure):
                 ("part_o", _vp), ("part_ml", _vp), ("counters", _vp), ("head_val", _vp), ("head_idx", _vp),
                 ("hidden_trace", _vp), ("pdl", _i32), ("l2_prefetch", _i32), ("kernel", _i32), ("picked", _vp),
                 ("chain_sync", _vp), ("temperature", _f32), ("seed", _u64),
-                ("step_layers", _vp), ("step_sync", _vp), ("step_status", _vp)]
+                ("step_layers", _vp), ("step_sync", _vp), ("step_status", _vp),
+                ("eos_ids", _vp), ("stop_at", _vp), ("n_eos", _i32), ("reserved_eos", _i32)]
 
 
 class GemvChainArgs(C.Structure):
@@ -143,7 +145,8 @@ class MiniCPM3StepArgs(C.Structure):
                 ("hidden_buf", _vp), ("qkv_a_buf", _vp), ("q_up_buf", _vp), ("kv_up_buf", _vp), ("attn_buf", _vp),
                 ("act_buf", _vp), ("logits", _vp), ("part_o", _vp), ("part_ml", _vp), ("counters", _vp),
                 ("head_val", _vp), ("head_idx", _vp), ("hidden_trace", _vp), ("picked", _vp), ("pdl", _i32),
-                ("temperature", _f32), ("seed", _u64)]
+                ("temperature", _f32), ("seed", _u64),
+                ("eos_ids", _vp), ("stop_at", _vp), ("n_eos", _i32), ("reserved_eos", _i32)]
 
 
 class MoeDownArgs(C.Structure):
@@ -173,7 +176,8 @@ class GraniteStepArgs(C.Structure):
                 ("part_o", _vp), ("part_ml", _vp), ("counters", _vp), ("head_val", _vp), ("head_idx", _vp),
                 ("hidden_trace", _vp), ("idx_trace", _vp), ("picked", _vp), ("pdl", _i32),
                 ("ep_rank", _i32), ("ep_world", _i32), ("partial", _vp), ("pair", _vp), ("gathered", _vp),
-                ("temperature", _f32), ("seed", _u64)]
+                ("temperature", _f32), ("seed", _u64),
+                ("eos_ids", _vp), ("stop_at", _vp), ("n_eos", _i32), ("reserved_eos", _i32)]
 
 
 #: every symbol ``include/tfb200.h`` declares: name -> (restype, argtypes)
@@ -228,7 +232,8 @@ class Qwen35StepArgs(C.Structure):
                 ("part_ml", _vp), ("counters", _vp), ("head_val", _vp), ("head_idx", _vp), ("logits", _vp),
                 ("picked", _vp), ("hidden_trace", _vp), ("idx_trace", _vp), ("ep_rank", _i32), ("ep_world", _i32),
                 ("partial", _vp), ("pair", _vp), ("expert_prefetch", _i32), ("reserved", _i32),
-                ("temperature", _f32), ("seed", _u64)]
+                ("temperature", _f32), ("seed", _u64),
+                ("eos_ids", _vp), ("stop_at", _vp), ("n_eos", _i32), ("reserved_eos", _i32)]
 
 
 class RouterSelectArgs(C.Structure):
