@@ -190,3 +190,66 @@ def test_granite_matches_hf_granitemoehybrid(golden_dir):
     ours = max((logits[0].float() - want["logits"][step].float()).abs().max().item()
                for step, _, logits, _, _, _, _ in parity.nested_walk(ref, cfg.layer_types, ids, ids.numel()))
     assert ours <= 1.25 * hf_gap + 1e-3, f"evaluator {ours:.4g} vs HF bf16 {hf_gap:.4g} from the f32 run"
+
+
+# ---- Qwen3 against the reference's OWN torch statements (tests/golden/make_qwen3_refstmt_golden.py) ----------------
+
+def _refstmt_inputs(cfg, ctx, seed):
+    g = torch.Generator().manual_seed(seed)
+    hidden = torch.randn(1, 1, cfg.hidden_size, generator=g).to(torch.bfloat16)
+    kc = torch.randn(1, ctx, cfg.num_key_value_heads, cfg.head_dim, generator=g).to(torch.bfloat16)
+    vc = torch.randn(1, ctx, cfg.num_key_value_heads, cfg.head_dim, generator=g).to(torch.bfloat16)
+    return hidden, kc, vc
+
+
+def test_qwen3_attention_body_equals_the_reference_f64_statement(golden_dir):
+    """``examples/qwen3_1_7b-tilelang/fast/arbitrate.py:22-56`` states the authored attention in float64.  The
+    restated function body evaluated at float64 over the same seeded inputs must agree with it to f32 accuracy
+    (two handlers compute in f32 whatever they are given) -- the two can then only differ in where they round --
+    and the bf16 evaluation must sit within bf16 noise of it."""
+    import dataclasses
+    fx = torch.load(golden_dir / "qwen3_refstmt.pt")
+    cfg = q.QWEN3_TINY
+    mod = q.build(cfg)
+    weights = q.tie_head(random_weights(mod, seed=fx["seed_w"], std=0.05))
+    exact = evaluator.load_as(mod, DictResource(weights), oq.make(dataclasses.replace(cfg, dtype="f64")), torch.float64)
+    rounded = evaluator.load(mod, DictResource(weights), oq.make(cfg))
+    cos, sin = q.rope_tables(cfg)
+    for ctx in fx["f64_contexts"]:
+        hidden, kc, vc = _refstmt_inputs(cfg, ctx, fx["seed_x"] + ctx)
+        pos = torch.tensor([ctx], dtype=torch.int32)
+        want = fx[f"f64_attention_ctx{ctx}"].reshape(-1)
+        f64 = lambda t: t.to(torch.float64)
+        scale64 = torch.full((1, 1, 1, 1), float(torch.tensor(cfg.head_dim ** -0.5, dtype=torch.bfloat16)), dtype=torch.float64)
+        out64, _, _ = exact.layer0.self_attention(f64(hidden), f64(cos), f64(sin), pos, f64(kc), f64(vc), scale64)
+        rel = float((out64.reshape(-1) - want).norm() / want.norm())
+        # (1e-6, not 1e-12: the RMSNorm and softmax handlers compute in f32 by definition, whatever the operand type)
+        assert rel < 1e-6, f"ctx {ctx}: the function body at f64 is {rel:.3g} from the reference's f64 statement"
+        scale = torch.full((1, 1, 1, 1), cfg.head_dim ** -0.5, dtype=torch.bfloat16)
+        out16, _, _ = rounded.layer0.self_attention(hidden, cos, sin, pos, kc, vc, scale)
+        rel16 = float((out16.reshape(-1).double() - want).norm() / want.norm())
+        assert rel16 < 3e-2, f"ctx {ctx}: the bf16 evaluation is {rel16:.3g} from the f64 statement"
+
+
+def test_qwen3_layer_matches_the_reference_kernel_statements_at_published_widths(golden_dir):
+    """The reference judges its own Qwen3 kernels by torch statements at the published widths
+    (``examples/qwen3_1_7b-tilelang/fast/test_kernels.py:32-172``) under max-error-at-scale < 2e-2 and cosine
+    > 1 - 2e-2 (``:18-29``).  The restated ``self_attention`` / ``mlp`` / ``input_rms_norm`` are held to those
+    statements under the same bound."""
+    import dataclasses
+    from tests.helpers import assert_close_at_scale
+    fx = torch.load(golden_dir / "qwen3_refstmt.pt")
+    cfg = dataclasses.replace(q.QWEN3_1_7B, num_hidden_layers=1, vocab_size=1024)
+    mod = q.build(cfg)
+    weights = q.tie_head(random_weights(mod, seed=fx["seed_w"], std=0.02))
+    loaded = evaluator.load(mod, DictResource(weights), oq.make(cfg))
+    ctx = fx["wide_ctx"]
+    hidden, kc, vc = _refstmt_inputs(cfg, ctx, fx["seed_x"])
+    cos, sin = q.rope_tables(cfg)
+    scale = torch.full((1, 1, 1, 1), cfg.head_dim ** -0.5, dtype=torch.bfloat16)
+    out, k_new, v_new = loaded.layer0.self_attention(hidden, cos, sin, torch.tensor([ctx], dtype=torch.int32), kc, vc, scale)
+    assert_close_at_scale(out, fx["wide_attention_out"], "self_attention out")
+    assert_close_at_scale(k_new, fx["wide_k_new"], "k_new")
+    assert torch.equal(v_new, fx["wide_v_new"])                       # a projection output, rounded once on both sides
+    assert_close_at_scale(loaded.layer0.mlp(hidden), fx["wide_mlp_out"], "mlp")
+    assert_ulps(loaded.layer0.input_rms_norm(hidden).reshape(-1), fx["wide_input_norm"], 1, "input_rms_norm")
