@@ -19,7 +19,10 @@
 
 namespace tfb {
 
-constexpr unsigned kPeerSpinLimit = 1u << 22;
+// A peer's flag is waited for at most this long (a healthy exchange takes microseconds); the clock is read every
+// 64th poll, and a poll count bounds the loop as well should the clock not advance.
+constexpr unsigned long long kPeerWaitNs = 1000ull * 1000 * 1000;
+constexpr unsigned kPeerSpinLimit = 1u << 24;
 
 __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
@@ -31,9 +34,16 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
 }
 // wait until *flag has reached epoch (epochs only grow; the comparison is wrap-safe)
 __device__ __forceinline__ bool wait_epoch(const unsigned* flag, unsigned epoch) {
+    unsigned long long t0 = 0;
     for (unsigned spin = 0; spin < kPeerSpinLimit; ++spin) {
         if (int(ld_acquire_sys(flag) - epoch) >= 0) return true;
         __nanosleep(40);
+        if ((spin & 63u) == 63u) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kPeerWaitNs) return false;
+        }
     }
     return false;
 }
