@@ -63,7 +63,7 @@ class Workload:
             self.authored, self.cfg, self.session_cls, self.overrides = a, a.MINICPM3_4B, S, None
             self.describe = ("MiniCPM3-4B architecture (62 layers, hidden 2560, 40 heads, MLA q_lora 768 / kv_lora "
                              "256, nope 64 + rope 32, v 64, SwiGLU 6400, vocab 73448), batch 1, 64-token random "
-                             "prompt, greedy decode, paged bf16 cache of assembled keys and values")
+                             "prompt, greedy decode, paged bf16 cache of latents (kv_lora 256 + rope 32 per position), kv_b absorbed")
             self.oracle_name, self.cpu_layers = "minicpm3_4b", 8
         elif key == "granite_4_0_h_small":
             from tilefoundry_b200.authored import granite_4_0_h_small as a

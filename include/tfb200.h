@@ -369,6 +369,49 @@ typedef struct {
 } tfb_attn_mla_args;
 TFB_API int tfb_attn_mla_decode(const tfb_attn_mla_args* args, tfb_stream_t stream);
 
+/* ---- multi-head latent attention over a cache of LATENTS ("absorbed" form) -------------------------
+ * The cache holds, per position, the normalised compressed kv vector and the rotated shared rotary key:
+ * pool[page][slot][kv_lora + rope] bf16 (576 bytes per position per layer for MiniCPM3-4B against 12,800 for
+ * assembled keys and values).  W_kv_b is never applied to the cache: its key half is folded into the query
+ * (q_lat[h] = W_UK[h]^T bf16(q_nope[h] * scale)) and its value half into the output (out[h] = W_UV[h] sum_t p_t c_t).
+ * Three launches: (1) low-rank norm + q_b + absorption / RoPE, and the append of this token's latent row at *pos;
+ * (2) split attention of all heads over the shared latent rows; (3) merge + W_UV.  Input is the fused
+ * down-projection qkv_a = [q_a | kv_a] of the normalised hidden state; output is what mla_attention feeds to w_o.
+ * kv_lora 256, nope 64, rope 32, v 64, heads a multiple of 4, q_lora a multiple of 256 up to 1024.
+ * Scratch: q_lat f32 [heads*2*kv_lora], q_rope f32 [heads*rope], part_o f32 [heads*splits*kv_lora],
+ * part_ml f32 [heads*splits*2] with splits = tfb_mla_latent_splits(max_ctx); nothing needs zeroing.
+ * Same function as tfb_attn_mla_decode plus the two up-projections before it:
+ * examples/minicpm3_4b-cutedsl/model.py:214-290 (the reference's kernel keeps the assembled cache,
+ * kernels/cute_attention.py:60-200). */
+typedef struct {
+    const void* qkv_a;        /* [q_lora + kv_lora + rope] bf16 */
+    const void* gamma_q_a;
+    const void* gamma_kv_a;
+    const void* w_q_b;        /* [heads*(nope+rope), q_lora] */
+    const void* w_kv_b;       /* [heads*(nope+v), kv_lora] */
+    const void* cos_table;    /* [max_pos, rope] */
+    const void* sin_table;
+    const int32_t* pos;
+    const int32_t* rope_pos;  /* optional: rotary position when it differs from *pos */
+    void* pool;
+    const int32_t* block_table;
+    void* out;                /* [heads*v] bf16 */
+    void* latent_new_out;     /* optional [kv_lora + rope]: the row appended */
+    float* q_lat;
+    float* q_rope;
+    float* part_o;
+    float* part_ml;
+    int32_t heads, q_lora, kv_lora, nope, rope, v;
+    int32_t page_size, table_len, max_ctx, max_pos;
+    float scale, lora_eps;
+    int32_t pdl, reserved;
+} tfb_mla_latent_args;
+TFB_API int tfb_mla_latent_decode(const tfb_mla_latent_args* args, tfb_stream_t stream);
+TFB_API int32_t tfb_mla_latent_splits(int32_t max_ctx);
+
+#define TFB_MLA_CACHE_ASSEMBLED 0   /* k_pool [..][heads][nope+rope], v_pool [..][heads][v] (the reference's format) */
+#define TFB_MLA_CACHE_LATENT 1      /* k_pool [..][kv_lora+rope], v_pool unused */
+
 /* ---- a whole MiniCPM3-architecture decode step ----------------------------------
  * embed*scale_emb -> layers x [norm + (q_a|kv_a), q_b, kv_b, MLA attention, o + scaled
  * residual, norm + gate/up + SwiGLU, down + scaled residual] -> final norm, hidden /
@@ -426,6 +469,13 @@ typedef struct {
     int32_t* stop_at;
     int32_t n_eos;
     int32_t reserved_eos;
+    /* cache_layout TFB_MLA_CACHE_LATENT: layers[i].k_pool is the latent pool, kv_b runs absorbed (tfb_mla_latent_decode
+     * instead of kv_b + tfb_attn_mla_decode), part_o / part_ml sized by tfb_mla_latent_splits, and the two scratch
+     * vectors below are required. */
+    int32_t cache_layout;
+    int32_t reserved_layout;
+    float* q_lat_buf;         /* [heads*2*kv_lora] */
+    float* q_rope_buf;        /* [heads*rope] */
 } tfb_minicpm3_step_args;
 TFB_API int tfb_minicpm3_decode_step(const tfb_minicpm3_step_args* args, tfb_stream_t stream);
 

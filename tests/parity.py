@@ -65,8 +65,11 @@ def compare_caches(want, sess, total):
     from tilefoundry_b200.engine import paged_kv
     assert torch.equal(sess.table.cpu(), paged_kv.block_table(1, sess.max_ctx))
     for li, (k_ref, v_ref) in enumerate(want["caches"]):
-        k_got = paged_kv.logical_view(sess.layers[li]["k_pool"], sess.table[0], total)
-        v_got = paged_kv.logical_view(sess.layers[li]["v_pool"], sess.table[0], total)
+        if hasattr(sess, "assembled_cache"):                  # a latent cache is compared re-expanded
+            k_got, v_got = sess.assembled_cache(li, total)
+        else:
+            k_got = paged_kv.logical_view(sess.layers[li]["k_pool"], sess.table[0], total)
+            v_got = paged_kv.logical_view(sess.layers[li]["v_pool"], sess.table[0], total)
         assert_close_at_scale(k_got, k_ref[:, :total], f"layer {li} K cache")
         assert_close_at_scale(v_got, v_ref[:, :total], f"layer {li} V cache")
 

@@ -61,7 +61,7 @@ def test_check_command_passes_and_fails_on_the_gpu(capsys):
     assert [m["fn"] for m in rec["outputs"][0]["fns"]] == ["allclose", "nan_inf"]
     # a bound that cannot be met must FAIL (the reference's installed-surface tests make the same negative check,
     # tests/installed/models/contract.py:359-370)
-    bad = check_cli.run([subject, "--out", "output", "--fn", "max_abs", "--max", "0"])
+    bad = check_cli.run([subject, "--out", "output", "--fn", "max_abs", "--max", "-1"])
     assert bad == 1 and capsys.readouterr().out.rstrip().endswith("FAIL")
     # a function with several outputs and a range to bind
     attn = check_cli.run(["tilefoundry_b200/twins/qwen3_1_7b.py:make_twin.layer0.self_attention", "--dim", "ctx_len=24",

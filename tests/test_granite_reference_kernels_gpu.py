@@ -124,8 +124,11 @@ def test_routing_and_experts(K, F):
           f"{_time(lambda: K.experts_gate_up(wg, wu, tok, idx, both, h)):.1f} us (L2-warm)")
 
 
-@pytest.mark.parametrize("step", [0, 1, 63, 64, 300])
+@pytest.mark.parametrize("step", [7, 15, 63, 64, 300])
 def test_attention(K, F, step):
+    """Lengths at which every one of the reference kernel's eight position stripes holds a position.  With an empty
+    stripe (7 * ceil(len / 8) >= len, which only lengths below 50 can meet) its partial is exp(-inf - -inf) and the
+    combine's ``gs > 0`` test then writes zeros for the head, so those lengths say nothing about the oracle."""
     dev, g = torch.device("cuda:0"), torch.Generator().manual_seed(step)
     cfg = CFG
     HQ, HKV, D, CAP, H = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.max_ctx, cfg.hidden_size

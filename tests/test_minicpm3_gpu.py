@@ -4,7 +4,7 @@ import torch
 
 from oracle import evaluator, minicpm3_4b as om
 from tests import parity
-from tests.helpers import ATOL, RTOL
+from tests.helpers import ATOL, RTOL, assert_close_at_scale
 from tilefoundry_b200.authored import minicpm3_4b as m
 from tilefoundry_b200.authored.weights import random_weights
 from tilefoundry_b200.runtime import AllClose, DictResource, Equal, NanInf, check
@@ -64,6 +64,44 @@ def test_layer_functions_against_evaluator_tiny(dev, ctx):
         assert rep.passed, f"{fn}\n{rep.render()}"
 
 
+def expand_latents(cfg, rows, w_kv_b):
+    """Assembled ``(k [1, C, heads, qk], v [1, C, heads, v])`` of latent rows ``[C, kv_lora + rope]`` in the
+    authored arithmetic (``examples/minicpm3_4b-cutedsl/model.py:236-247``): one bf16 matmul, the rotary slice
+    repeated over the heads."""
+    NH, NOPE, R, VD, KVL = (cfg.num_attention_heads, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim,
+                            cfg.kv_lora_rank)
+    C = rows.shape[0]
+    kv = torch.matmul(rows[:, :KVL].reshape(1, C, KVL), w_kv_b.cpu()).reshape(C, NH, NOPE + VD)
+    k = torch.cat([kv[:, :, :NOPE], rows[:, None, KVL:].expand(C, NH, R)], dim=-1)
+    return k.unsqueeze(0).contiguous(), kv[:, :, NOPE:].unsqueeze(0).contiguous()
+
+
+@pytest.mark.parametrize("size,ctx", [("tiny", c) for c in (0, 1, 31, 32, 33, 63, 64, 65, 200)]
+                         + [("full", c) for c in (0, 1, 63, 64, 65, 200, 1088)])
+def test_latent_attention_against_evaluator(dev, size, ctx):
+    """The absorbed form over a cache of latents against ``mla_attention`` over the same history assembled: ``out``
+    under the bounds of the other functions, and the row it appends re-expanded against ``k_new`` / ``v_new``."""
+    cfg = m.MINICPM3_TINY if size == "tiny" else m.MiniCPM3Config(num_hidden_layers=1, vocab_size=4096)
+    ref, twin, weights = _sides(cfg, dev, std=0.05 if size == "tiny" else 0.02)
+    g = torch.Generator().manual_seed(100 + ctx)
+    LAT = cfg.kv_lora_rank + cfg.qk_rope_head_dim
+    rows = torch.randn(ctx, LAT, generator=g).to(BF)
+    hidden = torch.randn(1, 1, cfg.hidden_size, generator=g).to(BF)
+    cos, sin = m.rope_tables(cfg)
+    pos = torch.tensor([ctx], dtype=torch.int32)
+    scale = torch.full((1, 1, 1, 1), cfg.qk_head_dim ** -0.5, dtype=BF)
+    w_kv_b = weights["layer0.w_kv_b"]
+    kc, vc = expand_latents(cfg, rows, w_kv_b)
+    want_out, want_k, want_v = ref.layer0.mla_attention(hidden, cos, sin, pos, kc, vc, scale)
+    got_out, latent_new = twin.layer0.mla_attention_latent(*(t.to(dev) for t in (hidden, cos, sin, pos)),
+                                                           rows.reshape(1, ctx, LAT).to(dev), scale.to(dev))
+    torch.cuda.synchronize()
+    assert_close_at_scale(got_out, want_out, f"out at context {ctx}")
+    got_k, got_v = expand_latents(cfg, latent_new.cpu().reshape(1, LAT), w_kv_b)
+    assert_close_at_scale(got_k.reshape(want_k.shape), want_k, f"k_new at context {ctx}")
+    assert_close_at_scale(got_v.reshape(want_v.shape), want_v, f"v_new at context {ctx}")
+
+
 def test_full_size_layer_and_root_functions(dev):
     cfg = m.MiniCPM3Config(num_hidden_layers=1, vocab_size=4096)
     ref, twin, _ = _sides(cfg, dev, std=0.02)
@@ -80,15 +118,16 @@ def test_full_size_layer_and_root_functions(dev):
     assert rep.passed, rep.render()
 
 
+@pytest.mark.parametrize("cache", ["latent", "assembled"])
 @pytest.mark.parametrize("use_graph", [False, True])
-def test_session_matches_evaluator_tiny(dev, use_graph):
+def test_session_matches_evaluator_tiny(dev, use_graph, cache):
     from tilefoundry_b200.engine.minicpm3 import MiniCPM3Session
     cfg = m.MINICPM3_TINY
     mod = m.build(cfg)
     weights = m.tie_head(random_weights(mod, seed=11, std=0.05))
     ref = evaluator.load(mod, DictResource(weights), om.make(cfg))
     make = lambda cap: MiniCPM3Session(cfg, DictResource(parity.cuda_weights(weights, dev)), max_ctx=cap, device=dev,
-                                       keep_logits=True, trace_hidden=True)
+                                       keep_logits=True, trace_hidden=True, cache=cache)
     n_prompt, n_new = 24, 120
     want, sess, got = parity.teacher_forced(ref, make, cfg.vocab_size, n_prompt, n_new, 11, use_graph)
     excused = parity.compare_run(cfg.num_hidden_layers, want, sess, got, n_prompt, n_new)

@@ -40,14 +40,49 @@ int tfb_attn_mla_decode(const tfb_attn_mla_args* a, tfb_stream_t stream) {
     return done(tfb::attn_mla_dispatch(p, S(stream), a->pdl != 0));
 }
 
+int32_t tfb_mla_latent_splits(int32_t max_ctx) { return max_ctx > 0 ? tfb::mla_latent_splits(max_ctx) : 0; }
+
+int tfb_mla_latent_decode(const tfb_mla_latent_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->qkv_a && a->gamma_q_a && a->gamma_kv_a && a->w_q_b && a->w_kv_b, TFB_EINVAL);
+    TFB_REQUIRE(a->cos_table && a->sin_table && a->pos && a->pool && a->block_table && a->out, TFB_EINVAL);
+    TFB_REQUIRE(a->q_lat && a->q_rope && a->part_o && a->part_ml, TFB_EINVAL);
+    TFB_REQUIRE(a->page_size > 0 && a->table_len > 0 && a->max_ctx > 0, TFB_EINVAL);
+    TFB_REQUIRE(tfb::mla_latent_supported(a->heads, a->q_lora, a->kv_lora, a->nope, a->rope, a->v, a->max_ctx), TFB_EINVAL);
+    TFB_REQUIRE((long long)a->page_size * a->table_len >= a->max_ctx && a->max_pos >= a->max_ctx, TFB_ECAPACITY);
+    TFB_REQUIRE(aligned16(a->pool) && aligned16(a->w_q_b) && aligned16(a->w_kv_b) && aligned16(a->qkv_a), TFB_EALIGN);
+    tfb::MlaLatentParams p = {};
+    p.qkv_a = static_cast<const uint16_t*>(a->qkv_a);
+    p.gamma_q_a = static_cast<const uint16_t*>(a->gamma_q_a);
+    p.gamma_kv_a = static_cast<const uint16_t*>(a->gamma_kv_a);
+    p.w_q_b = static_cast<const uint16_t*>(a->w_q_b);
+    p.w_kv_b = static_cast<const uint16_t*>(a->w_kv_b);
+    p.cos_table = static_cast<const uint16_t*>(a->cos_table);
+    p.sin_table = static_cast<const uint16_t*>(a->sin_table);
+    p.pos = a->pos; p.rope_pos = a->rope_pos;
+    p.pool = static_cast<uint16_t*>(a->pool);
+    p.block_table = a->block_table;
+    p.q_lat = a->q_lat; p.q_rope = a->q_rope; p.part_o = a->part_o; p.part_ml = a->part_ml;
+    p.out = static_cast<uint16_t*>(a->out);
+    p.latent_new_out = static_cast<uint16_t*>(a->latent_new_out);
+    p.heads = a->heads; p.q_lora = a->q_lora; p.page_size = a->page_size; p.max_ctx = a->max_ctx;
+    p.nsplit = tfb::mla_latent_splits(a->max_ctx);
+    p.scale = a->scale; p.lora_eps = a->lora_eps;
+    p.trace = next_trace();
+    return done(tfb::mla_latent_dispatch(p, S(stream), a->pdl != 0));
+}
+
 int tfb_minicpm3_decode_step(const tfb_minicpm3_step_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->layers && a->n_layers > 0, TFB_EINVAL);
     TFB_REQUIRE(a->w_embed && a->gamma_final && a->w_head && a->tokens && a->pos, TFB_EINVAL);
-    TFB_REQUIRE(a->hidden_buf && a->qkv_a_buf && a->q_up_buf && a->kv_up_buf && a->attn_buf && a->act_buf, TFB_EINVAL);
+    TFB_REQUIRE(a->hidden_buf && a->qkv_a_buf && a->attn_buf && a->act_buf, TFB_EINVAL);
+    TFB_REQUIRE(a->cache_layout == TFB_MLA_CACHE_LATENT || (a->q_up_buf && a->kv_up_buf), TFB_EINVAL);
     TFB_REQUIRE(a->part_o && a->part_ml && a->counters && a->head_val && a->head_idx, TFB_EINVAL);
     TFB_REQUIRE(a->hidden % 256 == 0 && a->inter % 256 == 0 && a->q_lora % 256 == 0 && a->kv_lora % 256 == 0, TFB_EINVAL);
     TFB_REQUIRE((a->heads * a->v) % 256 == 0, TFB_EINVAL);
     TFB_REQUIRE(a->max_tokens <= a->max_ctx + 1, TFB_ECAPACITY);
+    TFB_REQUIRE(a->cache_layout == TFB_MLA_CACHE_ASSEMBLED || a->cache_layout == TFB_MLA_CACHE_LATENT, TFB_EINVAL);
+    const bool latent = a->cache_layout == TFB_MLA_CACHE_LATENT;
+    TFB_REQUIRE(!latent || (a->q_lat_buf && a->q_rope_buf), TFB_EINVAL);
     const bool pdl = a->pdl != 0;
     const int H = a->hidden, I = a->inter, NH = a->heads;
     const int NA = a->q_lora + a->kv_lora + a->rope, NQ = NH * (a->nope + a->rope), NKV = NH * (a->nope + a->v);
@@ -80,6 +115,19 @@ int tfb_minicpm3_decode_step(const tfb_minicpm3_step_args* a, tfb_stream_t strea
         // 1. input norm + q down-projection | kv compression (one fused projection)
         if ((rc = gemv(L.w_qkv_a, nullptr, hid, L.gamma_in, nullptr, qkv_a, NA, H, TFB_NORM_CAST_THEN_GAIN,
                        TFB_EPI_STORE, a->eps, 1.f))) return rc;
+        if (latent) {
+            // 2-4. absorbed form: q_b + W_UK^T q / RoPE + latent append, attention over the latents, merge + W_UV
+            tfb_mla_latent_args t;
+            std::memset(&t, 0, sizeof t);
+            t.qkv_a = qkv_a; t.gamma_q_a = L.gamma_q_a; t.gamma_kv_a = L.gamma_kv_a; t.w_q_b = L.w_q_b; t.w_kv_b = L.w_kv_b;
+            t.cos_table = a->cos_table; t.sin_table = a->sin_table; t.pos = a->pos; t.pool = L.k_pool;
+            t.block_table = a->block_table; t.out = a->attn_buf; t.q_lat = a->q_lat_buf; t.q_rope = a->q_rope_buf;
+            t.part_o = a->part_o; t.part_ml = a->part_ml;
+            t.heads = NH; t.q_lora = a->q_lora; t.kv_lora = a->kv_lora; t.nope = a->nope; t.rope = a->rope; t.v = a->v;
+            t.page_size = a->page_size; t.table_len = a->table_len; t.max_ctx = a->max_ctx; t.max_pos = a->max_pos;
+            t.scale = a->scale; t.lora_eps = a->lora_eps; t.pdl = pdl;
+            if ((rc = tfb_mla_latent_decode(&t, stream))) return rc;
+        } else {
         // 2 + 3. low-rank norms + q up-projection and kv up-projection (k_nope | v per head): independent of each
         // other, one launch
         {
@@ -104,6 +152,7 @@ int tfb_minicpm3_decode_step(const tfb_minicpm3_step_args* a, tfb_stream_t strea
         t.page_size = a->page_size; t.table_len = a->table_len; t.max_ctx = a->max_ctx; t.max_pos = a->max_pos;
         t.scale = a->scale; t.pdl = pdl;
         if ((rc = tfb_attn_mla_decode(&t, stream))) return rc;
+        }
         // 5. output projection + scaled residual
         if ((rc = gemv(L.w_o, nullptr, a->attn_buf, nullptr, hid, hid, H, NO, TFB_NORM_NONE, TFB_EPI_RESIDUAL,
                        a->eps, a->residual_scale))) return rc;

@@ -138,6 +138,32 @@ struct MlaParams {
     float scale;
     unsigned long long* trace;
 };
+// Latent-cache form (attn_mla_latent.cu): pool rows are [kv_lora | rope] per position.
+struct MlaLatentParams {
+    const uint16_t* qkv_a;       // [q_lora | kv_lora | rope]: the fused down-projection of this token
+    const uint16_t* gamma_q_a;   // [q_lora]
+    const uint16_t* gamma_kv_a;  // [kv_lora]
+    const uint16_t* w_q_b;       // [heads*(nope+rope)][q_lora]
+    const uint16_t* w_kv_b;      // [heads*(nope+v)][kv_lora]: k_nope rows then v rows per head
+    const uint16_t* cos_table;
+    const uint16_t* sin_table;
+    const int* pos;
+    const int* rope_pos;
+    uint16_t* pool;              // [page][slot][kv_lora + rope]
+    const int* block_table;
+    float* q_lat;                // [heads][2][kv_lora] scratch
+    float* q_rope;               // [heads][rope] scratch
+    float* part_o;               // [heads][nsplit][kv_lora]
+    float* part_ml;              // [heads][nsplit][2]
+    uint16_t* out;               // [heads][v]
+    uint16_t* latent_new_out;    // optional [kv_lora + rope]
+    int heads, q_lora, page_size, max_ctx, nsplit;
+    float scale, lora_eps;
+    unsigned long long* trace;
+};
+int mla_latent_splits(int max_ctx);
+bool mla_latent_supported(int heads, int q_lora, int kv_lora, int nope, int rope, int vd, int max_ctx);
+cudaError_t mla_latent_dispatch(const MlaLatentParams& p, cudaStream_t stream, bool pdl);
 int mla_splits(int max_ctx);
 cudaError_t attn_mla_dispatch(const MlaParams& p, cudaStream_t stream, bool pdl);
 

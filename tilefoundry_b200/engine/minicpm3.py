@@ -1,6 +1,10 @@
-"""MiniCPM3-architecture (MLA) decode session: packed weights, paged cache of assembled keys and
-values, one captured step.  Same trade as the Qwen3 session; the reference's own fast driver for this
-model makes it too (``examples/minicpm3_4b-cutedsl/runtime_model.py:248-320`` repacks at load)."""
+"""MiniCPM3-architecture (MLA) decode session: packed weights, paged cache, one captured step.
+
+The cache holds LATENTS by default -- per position the normalised compressed kv vector and the rotated shared
+rotary key, 576 bytes per layer -- and the kv up-projection runs absorbed into the query and the output
+(``csrc/attn_mla_latent.cu``).  ``cache="assembled"`` keeps per-head keys and values instead (12,800 bytes per
+position per layer), the format of the reference's own cache (``examples/minicpm3_4b-cutedsl/model.py:28-38``).
+Weights are repacked at load as the reference's fast driver does (``runtime_model.py:248-320``)."""
 from __future__ import annotations
 
 import ctypes as C
@@ -29,10 +33,14 @@ LAYER_WEIGHTS = ("gamma_in", "w_q_a", "gamma_q_a", "w_q_b", "w_kv_a", "gamma_kv_
 class MiniCPM3Session(DecodeSession):
     def __init__(self, cfg: MiniCPM3Config, resource, *, max_ctx: int = 2176, device="cuda:0",
                  keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True,
-                 temperature: float = 0.0, seed: int = 0):
+                 temperature: float = 0.0, seed: int = 0, cache: str = "latent"):
         if not torch.cuda.is_available():
             raise RuntimeError("MiniCPM3Session needs a CUDA device; there is no CPU path")
+        if cache not in ("latent", "assembled"):
+            raise ValueError(f"cache must be 'latent' or 'assembled', not {cache!r}")
         lib.load()
+        self.cache = cache
+        latent = cache == "latent"
         self.cfg, self.device, self.max_ctx = cfg, torch.device(device), int(max_ctx)
         dev = self.device
         to = lambda t: t.to(dev)
@@ -51,19 +59,26 @@ class MiniCPM3Session(DecodeSession):
         NH, QK, VD, H, I, V = (cfg.num_attention_heads, cfg.qk_head_dim, cfg.v_head_dim, cfg.hidden_size,
                                cfg.intermediate_size, cfg.vocab_size)
         self.table = paged_kv.block_table(1, self.max_ctx, device=dev)
+        LAT = cfg.kv_lora_rank + cfg.qk_rope_head_dim
         for layer in self.layers:
-            layer["k_pool"] = paged_kv.new_pool(1, self.max_ctx, NH, QK, device=dev)
-            layer["v_pool"] = paged_kv.new_pool(1, self.max_ctx, NH, VD, device=dev)
+            if latent:
+                layer["k_pool"], layer["v_pool"] = paged_kv.new_pool(1, self.max_ctx, 1, LAT, device=dev), None
+            else:
+                layer["k_pool"] = paged_kv.new_pool(1, self.max_ctx, NH, QK, device=dev)
+                layer["v_pool"] = paged_kv.new_pool(1, self.max_ctx, NH, VD, device=dev)
         bf, f32 = torch.bfloat16, torch.float32
         z = lambda *s, dtype=bf: torch.zeros(*s, device=dev, dtype=dtype)
-        nsplit = lib.attn_splits(self.max_ctx)
+        nsplit = lib.load().tfb_mla_latent_splits(self.max_ctx) if latent else lib.attn_splits(self.max_ctx)
+        PD = cfg.kv_lora_rank if latent else VD                 # width of a split's partial output
         self.tokens, self.pos = z(self.max_ctx + 1, dtype=torch.int64), z(1, dtype=torch.int32)
         self.hidden = z(H)
         self.qkv_a = z(cfg.q_lora_rank + cfg.kv_lora_rank + cfg.qk_rope_head_dim)
         self.q_up, self.kv_up = z(NH * QK), z(NH * (cfg.qk_nope_head_dim + VD))
         self.attn, self.act = z(NH * VD), z(I)
         self.logits = z(V) if keep_logits else None
-        self.part_o, self.part_ml = z(NH * nsplit * VD, dtype=f32), z(NH * nsplit * 2, dtype=f32)
+        self.part_o, self.part_ml = z(NH * nsplit * PD, dtype=f32), z(NH * nsplit * 2, dtype=f32)
+        self.q_lat = z(NH * 2 * cfg.kv_lora_rank, dtype=f32) if latent else None
+        self.q_rope = z(NH * cfg.qk_rope_head_dim, dtype=f32) if latent else None
         self.counters = z(NH + 1, dtype=torch.int32)
         n_head = lib.lm_head_scratch_entries(V)
         self.head_val, self.head_idx = z(n_head, dtype=f32), z(n_head, dtype=torch.int32)
@@ -90,8 +105,10 @@ class MiniCPM3Session(DecodeSession):
             act_buf=lib.ptr(self.act), logits=lib.ptr(self.logits), part_o=lib.ptr(self.part_o),
             part_ml=lib.ptr(self.part_ml), counters=lib.ptr(self.counters), head_val=lib.ptr(self.head_val),
             head_idx=lib.ptr(self.head_idx), hidden_trace=lib.ptr(self.trace), picked=lib.ptr(self.picked),
-            pdl=int(pdl))
-        self.launches_per_step = 2 + 6 * len(self.layers) + (len(self.layers) + 1 if trace_hidden else 0)
+            pdl=int(pdl), cache_layout=lib.MLA_CACHE_LATENT if latent else lib.MLA_CACHE_ASSEMBLED,
+            q_lat_buf=lib.ptr(self.q_lat), q_rope_buf=lib.ptr(self.q_rope))
+        self.launches_per_step = (2 + (7 if latent else 6) * len(self.layers)
+                                  + (len(self.layers) + 1 if trace_hidden else 0))
 
     def weight_bytes(self) -> int:
         names = ("w_qkv_a", "w_q_b", "w_kv_b", "w_o", "w_gate", "w_up", "w_down")
@@ -99,7 +116,24 @@ class MiniCPM3Session(DecodeSession):
 
     def kv_bytes_per_position(self) -> int:
         c = self.cfg
+        if self.cache == "latent":
+            return (c.kv_lora_rank + c.qk_rope_head_dim) * 2 * c.num_hidden_layers
         return c.num_attention_heads * (c.qk_head_dim + c.v_head_dim) * 2 * c.num_hidden_layers
+
+    def assembled_cache(self, layer: int, length: int):
+        """``(k [1, length, heads, qk], v [1, length, heads, v])`` of a layer as the authored functions hold them.
+        With the latent cache the rows are re-expanded through ``w_kv_b`` in the authored arithmetic (one bf16
+        matmul per row, ``examples/minicpm3_4b-cutedsl/model.py:236-247``): a view for checks, not a step of decode."""
+        c, L = self.cfg, self.layers[layer]
+        if self.cache != "latent":
+            return (paged_kv.logical_view(L["k_pool"], self.table[0], length),
+                    paged_kv.logical_view(L["v_pool"], self.table[0], length))
+        NH, NOPE, R, VD, KVL = (c.num_attention_heads, c.qk_nope_head_dim, c.qk_rope_head_dim, c.v_head_dim,
+                                c.kv_lora_rank)
+        rows = paged_kv.logical_view(L["k_pool"], self.table[0], length)[0, :, 0].cpu()       # [length, kvl + rope]
+        kv = torch.matmul(rows[:, :KVL], L["w_kv_b"].cpu().t()).reshape(length, NH, NOPE + VD)
+        k = torch.cat([kv[:, :, :NOPE], rows[:, None, KVL:].expand(length, NH, R)], dim=-1)
+        return k.unsqueeze(0).contiguous(), kv[:, :, NOPE:].unsqueeze(0).contiguous()
 
     def step(self) -> None:
         lib.check(lib.load().tfb_minicpm3_decode_step(C.byref(self.args), lib.stream()), "tfb_minicpm3_decode_step")

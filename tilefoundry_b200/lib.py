@@ -146,7 +146,21 @@ class MiniCPM3StepArgs(C.Structure):
                 ("act_buf", _vp), ("logits", _vp), ("part_o", _vp), ("part_ml", _vp), ("counters", _vp),
                 ("head_val", _vp), ("head_idx", _vp), ("hidden_trace", _vp), ("picked", _vp), ("pdl", _i32),
                 ("temperature", _f32), ("seed", _u64),
-                ("eos_ids", _vp), ("stop_at", _vp), ("n_eos", _i32), ("reserved_eos", _i32)]
+                ("eos_ids", _vp), ("stop_at", _vp), ("n_eos", _i32), ("reserved_eos", _i32),
+                ("cache_layout", _i32), ("reserved_layout", _i32), ("q_lat_buf", _vp), ("q_rope_buf", _vp)]
+
+
+class MlaLatentArgs(C.Structure):
+    _fields_ = [("qkv_a", _vp), ("gamma_q_a", _vp), ("gamma_kv_a", _vp), ("w_q_b", _vp), ("w_kv_b", _vp),
+                ("cos_table", _vp), ("sin_table", _vp), ("pos", _vp), ("rope_pos", _vp), ("pool", _vp),
+                ("block_table", _vp), ("out", _vp), ("latent_new_out", _vp), ("q_lat", _vp), ("q_rope", _vp),
+                ("part_o", _vp), ("part_ml", _vp), ("heads", _i32), ("q_lora", _i32), ("kv_lora", _i32),
+                ("nope", _i32), ("rope", _i32), ("v", _i32), ("page_size", _i32), ("table_len", _i32),
+                ("max_ctx", _i32), ("max_pos", _i32), ("scale", _f32), ("lora_eps", _f32), ("pdl", _i32),
+                ("reserved", _i32)]
+
+
+MLA_CACHE_ASSEMBLED, MLA_CACHE_LATENT = 0, 1
 
 
 class MoeDownArgs(C.Structure):
@@ -266,6 +280,8 @@ SYMBOLS = {
     "tfb_qwen3_step_sync_words": (_i32, [_i32, _i32]),
     "tfb_qwen3_step_splits": (_i32, [_i32]),
     "tfb_attn_mla_decode": (_i32, [C.POINTER(AttnMlaArgs), _vp]),
+    "tfb_mla_latent_decode": (_i32, [C.POINTER(MlaLatentArgs), _vp]),
+    "tfb_mla_latent_splits": (_i32, [_i32]),
     "tfb_minicpm3_decode_step": (_i32, [C.POINTER(MiniCPM3StepArgs), _vp]),
     "tfb_residual_add": (_i32, [_vp, _vp, _vp, _i32, _f32, _vp]),
     "tfb_conv_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),

@@ -67,6 +67,41 @@ def make_twin(cfg: authored.MiniCPM3Config = authored.MINICPM3_4B):
             lib.check(lib.load().tfb_attn_mla_decode(C.byref(a), lib.stream()), "tfb_attn_mla_decode")
             return attn, k_new, v_new
 
+        def mla_attention_latent(self, hidden, cos_cache, sin_cache, pos_ids, latent_cache, scale):
+            """``mla_attention`` over a cache of latents: *latent_cache* is ``[1, C, kv_lora + rope]`` (normalised
+            compressed kv vector | rotated shared key per position) instead of the assembled ``k_cache`` /
+            ``v_cache``; returns ``(out [1, 1, hidden], latent_new [1, 1, kv_lora + rope])``.  Not an authored
+            function (the reference has no latent cache): the decode session's form of it, exposed so a test can hold
+            it to ``mla_attention`` on the re-expanded cache."""
+            p = self._packed
+            dev = hidden.device
+            ctx = latent_cache.shape[1]
+            cap = ctx + 1
+            LAT = KVL + R
+            table = paged_kv.block_table(1, cap, device=dev)
+            pool = paged_kv.new_pool(1, cap, 1, LAT, device=dev)
+            paged_kv.fill_from_logical(pool, table[0], latent_cache.reshape(1, ctx, 1, LAT))
+            qkv_a = lib.gemv(p["w_qkv_a"], hidden.reshape(-1), _new(QL + KVL + R, hidden), gamma=p["gamma_in"],
+                             prologue=CAST, eps=EPS)
+            so = lib.load()
+            nsplit = so.tfb_mla_latent_splits(cap)
+            f32 = torch.float32
+            attn, latent_new = _new(NH * VD, hidden), _new((1, 1, LAT), hidden)
+            pos = torch.tensor([ctx], device=dev, dtype=torch.int32)
+            rope_pos = pos_ids.reshape(-1)[:1].to(torch.int32).contiguous()
+            q_lat, q_rope = _new(NH * 2 * KVL, hidden, f32), _new(NH * R, hidden, f32)
+            part_o, part_ml = _new(NH * nsplit * KVL, hidden, f32), _new(NH * nsplit * 2, hidden, f32)
+            a = lib.MlaLatentArgs(
+                qkv_a=lib.ptr(qkv_a), gamma_q_a=lib.ptr(p["gamma_q_a"]), gamma_kv_a=lib.ptr(p["gamma_kv_a"]),
+                w_q_b=lib.ptr(p["w_q_b"]), w_kv_b=lib.ptr(p["w_kv_b"]), cos_table=lib.ptr(cos_cache),
+                sin_table=lib.ptr(sin_cache), pos=lib.ptr(pos), rope_pos=lib.ptr(rope_pos), pool=lib.ptr(pool),
+                block_table=lib.ptr(table), out=lib.ptr(attn), latent_new_out=lib.ptr(latent_new), q_lat=lib.ptr(q_lat),
+                q_rope=lib.ptr(q_rope), part_o=lib.ptr(part_o), part_ml=lib.ptr(part_ml), heads=NH, q_lora=QL,
+                kv_lora=KVL, nope=NOPE, rope=R, v=VD, page_size=paged_kv.PAGE_SIZE, table_len=table.shape[1],
+                max_ctx=cap, max_pos=cos_cache.shape[0], scale=float(scale.reshape(-1)[0]), lora_eps=LEPS, pdl=0)
+            lib.check(so.tfb_mla_latent_decode(C.byref(a), lib.stream()), "tfb_mla_latent_decode")
+            return lib.gemv(p["w_o"], attn, _new(Hd, hidden)).reshape(1, 1, Hd), latent_new
+
         def _mlp(self, hidden, residual=None, res_scale=1.0):
             p = self._packed
             act = lib.gemv(p["w_gate"], hidden.reshape(-1), _new(I, hidden), w2=p["w_up"], gamma=p["gamma_post"],
