@@ -67,7 +67,7 @@ int tfb_mla_latent_decode(const tfb_mla_latent_args* a, tfb_stream_t stream) {
     p.heads = a->heads; p.q_lora = a->q_lora; p.page_size = a->page_size; p.max_ctx = a->max_ctx;
     p.nsplit = tfb::mla_latent_splits(a->max_ctx);
     p.scale = a->scale; p.lora_eps = a->lora_eps;
-    p.trace = next_trace();
+    for (int i = 0; i < 3; ++i) p.trace3[i] = next_trace();
     return done(tfb::mla_latent_dispatch(p, S(stream), a->pdl != 0));
 }
 

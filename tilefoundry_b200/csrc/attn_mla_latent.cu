@@ -11,12 +11,15 @@
 //                         (two CTAs per head, 32 nope rows each) or RoPE on the rotary query slice.  CTA (2, 0)
 //                         also norms the compressed kv vector, rotates the shared key slice and APPENDS the
 //                         latent row at *pos.
-//   mla_latent_attn_kernel grid (heads / HG, splits of 32 positions): the 32 latent rows stream into shared
-//                         memory once (cp.async, cached rows before the dependency wait) and serve HG heads;
-//                         thread (head, position) takes one 288-long dot product, a warp owns a head's softmax,
-//                         then the probabilities weight the 256 latent columns.  Partials (f32) go to part_o/ml.
-//   mla_v_absorb_kernel   grid (heads): merges the split partials of a head, applies W_UV[h] (64 rows x 256,
-//                         in registers before the wait) and rounds the 64 outputs to bf16.
+//   mla_latent_attn_kernel grid (heads / 4, splits of 32 positions): the 32 latent rows stream into shared
+//                         memory once (cp.async, cached rows before the dependency wait) and serve 4 heads;
+//                         warp (head, half of the 288 columns) x lane (position) takes half a dot product, a warp
+//                         owns a head's softmax, then the probabilities weight the 256 latent columns.  Partials
+//                         (f32) go to part_o / part_ml.  Many small CTAs (340 at context 1088) spread evenly
+//                         over the multiprocessors; with 8 heads per CTA 170 CTAs left 22 of 148 with double work.
+//   mla_v_absorb_kernel   grid (heads), 512 threads: merges the split partials of a head (every (max, sum) pair in
+//                         one load per thread, up to 32 partial columns per thread in flight), applies W_UV[h]
+//                         (64 rows x 256, in registers before the wait) and rounds the 64 outputs to bf16.
 //
 // Algorithmic bytes per layer: (ctx+1) * 576 (cache) + heads*(96*q_lora + 128*256)*2 (q_b and W_kv_b).
 #include "common.cuh"
@@ -65,12 +68,21 @@ __global__ void __launch_bounds__(kLatThreads) mla_q_absorb_kernel(const MlaLate
 #pragma unroll
         for (int r = 0; r < 16; ++r) wk[r] = __ldg(reinterpret_cast<const uint32_t*>(base + size_t(r) * kKvl));
     }
+    // The position does not change inside a step (the head kernel advances it, and a step's first launch waits for
+    // the whole previous step), so it and the rotary row it selects are read ahead of the wait as well.
+    const int pos = *reinterpret_cast<const volatile int*>(p.pos);
+    const bool pos_ok = pos >= 0 && pos < p.max_ctx;
+    constexpr int HALF = kRope / 2;
+    float rc = 0.f, rs = 0.f;
+    if (pos_ok && j == 2 && tid < kRope) {
+        const int rpos = p.rope_pos ? *reinterpret_cast<const volatile int*>(p.rope_pos) : pos;
+        rc = bf16_bits_to_f32(p.cos_table[size_t(rpos) * kRope + tid]);
+        rs = bf16_bits_to_f32(p.sin_table[size_t(rpos) * kRope + tid]);
+    }
     pdl_trigger();
     pdl_wait();
     trace_waited(p.trace);
-
-    const int pos = *p.pos;
-    if (pos < 0 || pos >= p.max_ctx) return;
+    if (!pos_ok) return;
 
     // low-rank norm of the compressed query: cast, then gain
     {
@@ -113,13 +125,9 @@ __global__ void __launch_bounds__(kLatThreads) mla_q_absorb_kernel(const MlaLate
         return;
     }
 
-    const int rpos = p.rope_pos ? *p.rope_pos : pos;
-    constexpr int HALF = kRope / 2;
     if (tid < kRope) {
-        const float c = bf16_bits_to_f32(p.cos_table[size_t(rpos) * kRope + tid]);
-        const float s = bf16_bits_to_f32(p.sin_table[size_t(rpos) * kRope + tid]);
         const float qp = (tid < HALF) ? -qv[tid + HALF] : qv[tid - HALF];
-        const float q = round_bf16(__fadd_rn(__fmul_rn(qv[tid], c), __fmul_rn(qp, s)));
+        const float q = round_bf16(__fadd_rn(__fmul_rn(qv[tid], rc), __fmul_rn(qp, rs)));
         p.q_rope[size_t(h) * kRope + tid] = round_bf16(q * p.scale);
     }
     if (h != 0) { trace_end(p.trace); return; }
@@ -135,23 +143,23 @@ __global__ void __launch_bounds__(kLatThreads) mla_q_absorb_kernel(const MlaLate
     if (p.latent_new_out) p.latent_new_out[tid] = lat;
     if (tid < kRope) {
         const uint16_t* kr = kv_c + kKvl;
-        const float c = bf16_bits_to_f32(p.cos_table[size_t(rpos) * kRope + tid]);
-        const float s = bf16_bits_to_f32(p.sin_table[size_t(rpos) * kRope + tid]);
         const float k0 = bf16_bits_to_f32(kr[tid]);
         const float kp = (tid < HALF) ? -bf16_bits_to_f32(kr[tid + HALF]) : bf16_bits_to_f32(kr[tid - HALF]);
-        const uint16_t rot = f32_to_bf16_bits(__fadd_rn(__fmul_rn(k0, c), __fmul_rn(kp, s)));
+        const uint16_t rot = f32_to_bf16_bits(__fadd_rn(__fmul_rn(k0, rc), __fmul_rn(kp, rs)));
         dst[kKvl + tid] = rot;
         if (p.latent_new_out) p.latent_new_out[kKvl + tid] = rot;
     }
     trace_end(p.trace);
 }
 
-// ---- 2. attention of HG heads over 32 latent rows ---------------------------------------------------------------
-template <int HG>
+// ---- 2. attention of 4 heads over 32 latent rows ----------------------------------------------------------------
+constexpr int kLatHG = 4;
+
 __global__ void __launch_bounds__(kLatThreads) mla_latent_attn_kernel(const MlaLatentParams p) {
-    static_assert(HG == 8 || HG == 4, "head group");
+    constexpr int HG = kLatHG;
     __shared__ __align__(16) uint16_t kv[kLatSplit][kLatPad];
     __shared__ __align__(16) float qf[HG][kLatRow];
+    __shared__ float sp[2 * HG][kLatSplit];        // partial scores of a (head, column half) warp
     __shared__ float sc[HG][kLatSplit];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -159,63 +167,70 @@ __global__ void __launch_bounds__(kLatThreads) mla_latent_attn_kernel(const MlaL
     constexpr int PIECES = kLatRow / 8;            // 16-byte pieces per row
 
     trace_start(p.trace);
-    int pre_end = p0;
-    {
-        const int pos_early = *reinterpret_cast<const volatile int*>(p.pos);
-        if (pos_early >= 0 && pos_early < p.max_ctx) {
-            pre_end = max(p0, min(p0 + kLatSplit, pos_early));          // rows below *pos are final already
-            for (int c = tid; c < (pre_end - p0) * PIECES; c += kLatThreads) {
-                const int r = c / PIECES, piece = c % PIECES, pp = p0 + r;
-                const size_t row = size_t(p.block_table[pp / p.page_size]) * p.page_size + (pp % p.page_size);
-                lat_cp16(&kv[r][piece * 8], p.pool + row * kLatRow + piece * 8);
-            }
-        }
+    // the position is fixed for the whole step (see mla_q_absorb_kernel): rows below it are final already
+    const int pos = *reinterpret_cast<const volatile int*>(p.pos);
+    const int total = pos + 1;
+    const int n_active = (total + kLatSplit - 1) / kLatSplit;
+    const bool active = pos >= 0 && pos < p.max_ctx && split < n_active;
+    const int n = active ? min(p0 + kLatSplit, total) - p0 : 0;
+    const int n_cached = active ? min(p0 + kLatSplit, pos) - p0 : 0;      // all but this token's own row
+    for (int c = tid; c < n_cached * PIECES; c += kLatThreads) {
+        const int r = c / PIECES, piece = c % PIECES, pp = p0 + r;
+        const size_t row = size_t(p.block_table[pp / p.page_size]) * p.page_size + (pp % p.page_size);
+        lat_cp16(&kv[r][piece * 8], p.pool + row * kLatRow + piece * 8);
     }
     pdl_trigger();
     pdl_wait();
     trace_waited(p.trace);
+    if (!active) { lat_cp_wait(); return; }
 
-    const int pos = *p.pos, total = pos + 1;
-    const int n_active = (total + kLatSplit - 1) / kLatSplit;
-    if (pos < 0 || pos >= p.max_ctx || split >= n_active) { lat_cp_wait(); return; }
-    const int n = min(p0 + kLatSplit, total) - p0;
-    for (int c = tid; c < (n - (pre_end - p0)) * PIECES; c += kLatThreads) {      // includes the row just appended
-        const int r = (pre_end - p0) + c / PIECES, piece = c % PIECES, pp = p0 + r;
-        const size_t row = size_t(p.block_table[pp / p.page_size]) * p.page_size + (pp % p.page_size);
-        lat_cp16(&kv[r][piece * 8], p.pool + row * kLatRow + piece * 8);
+    if (n > n_cached && tid < PIECES) {            // the row appended by the kernel before this one
+        const size_t row = size_t(p.block_table[pos / p.page_size]) * p.page_size + (pos % p.page_size);
+        lat_cp16(&kv[n_cached][tid * 8], p.pool + row * kLatRow + tid * 8);
     }
-    for (int c = tid; c < HG * kLatRow; c += kLatThreads) {
-        const int hh = c / kLatRow, e = c % kLatRow;
+    if (warp >= HG) {                              // warp 4 + i fetches head i's query: both partial absorbed queries and
+        const int hh = warp - HG;                  // the rotary slice, every load issued before the first is used
         const size_t h = size_t(h0 + hh);
-        qf[hh][e] = e < kKvl ? __ldcg(p.q_lat + (h * 2) * kKvl + e) + __ldcg(p.q_lat + (h * 2 + 1) * kKvl + e)
-                             : __ldcg(p.q_rope + h * kRope + (e - kKvl));
+        const float4* a = reinterpret_cast<const float4*>(p.q_lat + h * 2 * kKvl);
+        const float4* b = a + kKvl / 4;
+        const float4 a0 = __ldcg(a + lane), a1 = __ldcg(a + lane + 32), b0 = __ldcg(b + lane), b1 = __ldcg(b + lane + 32);
+        const float r = __ldcg(p.q_rope + h * kRope + lane);
+        float4* q4 = reinterpret_cast<float4*>(&qf[hh][0]);
+        q4[lane] = make_float4(a0.x + b0.x, a0.y + b0.y, a0.z + b0.z, a0.w + b0.w);
+        q4[lane + 32] = make_float4(a1.x + b1.x, a1.y + b1.y, a1.z + b1.z, a1.w + b1.w);
+        qf[hh][kKvl + lane] = r;
     }
     lat_cp_wait();
     __syncthreads();
     trace_mark(p.trace, 0);
 
-    // scores: warp = head, lane = position
-    if (warp < HG) {
-        float s = -INFINITY;
+    // scores: warp = (column half, head), lane = position; 18 pieces of 8 columns each
+    {
+        const int hh = warp & (HG - 1), kh = warp / HG;
+        float acc = 0.f;
         if (lane < n) {
-            const uint4* krow = reinterpret_cast<const uint4*>(&kv[lane][0]);
-            const float4* q4 = reinterpret_cast<const float4*>(&qf[warp][0]);
-            float a0 = 0.f, a1 = 0.f;
-#pragma unroll 6
-            for (int c = 0; c < PIECES; c += 2) {
+            const uint4* krow = reinterpret_cast<const uint4*>(&kv[lane][0]) + kh * (PIECES / 2);
+            const float4* q4 = reinterpret_cast<const float4*>(&qf[hh][0]) + kh * PIECES;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f;
+#pragma unroll
+            for (int c = 0; c < PIECES / 2; c += 3) {
                 a0 = dot8(krow[c], q4[2 * c], q4[2 * c + 1], a0);
                 a1 = dot8(krow[c + 1], q4[2 * c + 2], q4[2 * c + 3], a1);
+                a2 = dot8(krow[c + 2], q4[2 * c + 4], q4[2 * c + 5], a2);
             }
-            s = a0 + a1;
+            acc = a0 + a1 + a2;
         }
+        sp[warp][lane] = acc;
+    }
+    __syncthreads();
+    if (warp < HG) {
+        const float s = lane < n ? sp[warp][lane] + sp[warp + HG][lane] : -INFINITY;
         const float m = warp_max(s);
         const float e = lane < n ? __expf(s - m) : 0.f;
         const float l = warp_sum(e);
         sc[warp][lane] = e;
-        if (lane == 0) {
-            p.part_ml[(size_t(h0 + warp) * p.nsplit + split) * 2] = m;
-            p.part_ml[(size_t(h0 + warp) * p.nsplit + split) * 2 + 1] = l;
-        }
+        if (lane == 0)
+            *reinterpret_cast<float2*>(p.part_ml + (size_t(h0 + warp) * p.nsplit + split) * 2) = make_float2(m, l);
     }
     __syncthreads();
     trace_mark(p.trace, 1);
@@ -227,6 +242,7 @@ __global__ void __launch_bounds__(kLatThreads) mla_latent_attn_kernel(const MlaL
         float acc[HH][2];
 #pragma unroll
         for (int i = 0; i < HH; ++i) acc[i][0] = acc[i][1] = 0.f;
+#pragma unroll 4
         for (int r = 0; r < n; ++r) {
             const uint32_t u = *reinterpret_cast<const uint32_t*>(&kv[r][pair * 2]);
             const float c0 = bf16_lo(u), c1 = bf16_hi(u);
@@ -247,62 +263,90 @@ __global__ void __launch_bounds__(kLatThreads) mla_latent_attn_kernel(const MlaL
 
 // ---- 3. merge of the splits + W_UV -------------------------------------------------------------------------------
 constexpr int kLatMaxSplits = 1024;                // 32,768 positions
+constexpr int kVaThreads = 512;
 
-__global__ void __launch_bounds__(kLatThreads) mla_v_absorb_kernel(const MlaLatentParams p) {
+__global__ void __launch_bounds__(kVaThreads) mla_v_absorb_kernel(const MlaLatentParams p) {
     __shared__ float w[kLatMaxSplits];
-    __shared__ __align__(16) float ol[kKvl];
+    __shared__ __align__(16) float ol[2][kKvl];
     __shared__ float red[32];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, h = blockIdx.x;
     trace_start(p.trace);
-    // W_UV[h]: 64 rows x 256; a warp takes 8 rows, a lane 8 columns of each
-    uint4 wv[8];
-    const uint16_t* base = p.w_kv_b + (size_t(h) * (kNope + kVd) + kNope + size_t(warp) * 8) * kKvl + lane * 8;
+    // W_UV[h]: 64 rows x 256; a warp takes 4 rows, a lane 8 columns of each
+    uint4 wv[4];
+    const uint16_t* base = p.w_kv_b + (size_t(h) * (kNope + kVd) + kNope + size_t(warp) * 4) * kKvl + lane * 8;
 #pragma unroll
-    for (int r = 0; r < 8; ++r) wv[r] = ld_stream16(base + size_t(r) * kKvl);
+    for (int r = 0; r < 4; ++r) wv[r] = ld_stream16(base + size_t(r) * kKvl);
+    const int pos = *reinterpret_cast<const volatile int*>(p.pos);      // fixed for the whole step
     pdl_trigger();
     pdl_wait();
     trace_waited(p.trace);
-
-    const int pos = *p.pos;
     if (pos < 0 || pos >= p.max_ctx) return;
     const int n_active = (pos + kLatSplit) / kLatSplit;
-    const float* ml = p.part_ml + size_t(h) * p.nsplit * 2;
+    // the first 64 splits' partial columns of this thread are requested together with the (max, sum) pairs below:
+    // one round trip to L2 for everything the merge needs
+    const int mc = tid & (kKvl - 1), mhalf = tid >> 8;
+    const float* po = p.part_o + size_t(h) * p.nsplit * kKvl + mc;
+    float v0[32];
+#pragma unroll
+    for (int q = 0; q < 32; ++q) v0[q] = __ldcg(po + size_t(min(mhalf + 2 * q, n_active - 1)) * kKvl);
+    // (max, sum) of every split: one load per thread (two beyond 512 splits), kept in registers
+    const float2* ml = reinterpret_cast<const float2*>(p.part_ml + size_t(h) * p.nsplit * 2);
+    float2 st[kLatMaxSplits / kVaThreads];
     float m = -INFINITY;
-    for (int s = tid; s < n_active; s += kLatThreads) m = fmaxf(m, __ldcg(ml + 2 * s));
+#pragma unroll
+    for (int i = 0; i < kLatMaxSplits / kVaThreads; ++i) {
+        const int sidx = tid + i * kVaThreads;
+        st[i] = sidx < n_active ? __ldcg(ml + sidx) : make_float2(-INFINITY, 0.f);
+        m = fmaxf(m, st[i].x);
+    }
     m = warp_max(m);
     if (lane == 0) red[warp] = m;
     __syncthreads();
     m = red[0];
 #pragma unroll
-    for (int i = 1; i < kLatThreads / 32; ++i) m = fmaxf(m, red[i]);
+    for (int i = 1; i < kVaThreads / 32; ++i) m = fmaxf(m, red[i]);
     float den = 0.f;
-    for (int s = tid; s < n_active; s += kLatThreads) {
-        const float ws = __expf(__ldcg(ml + 2 * s) - m);
-        w[s] = ws;
-        den = fmaf(ws, __ldcg(ml + 2 * s + 1), den);
+#pragma unroll
+    for (int i = 0; i < kLatMaxSplits / kVaThreads; ++i) {
+        const int sidx = tid + i * kVaThreads;
+        if (sidx < n_active) {
+            const float ws = __expf(st[i].x - m);
+            w[sidx] = ws;
+            den = fmaf(ws, st[i].y, den);
+        }
     }
-    __syncthreads();                               // red read by everyone before block_sum reuses it; w complete
+    __syncthreads();                               // everyone has read red; w is complete
     den = block_sum(den, red);
     {
-        const float* po = p.part_o + size_t(h) * p.nsplit * kKvl + tid;
+        // thread (column, parity of the split)
         float a = 0.f, b = 0.f;
-        int s = 0;
-        for (; s + 4 <= n_active; s += 4) {        // four independent loads in flight
-            const float v0 = __ldcg(po + size_t(s) * kKvl), v1 = __ldcg(po + size_t(s + 1) * kKvl);
-            const float v2 = __ldcg(po + size_t(s + 2) * kKvl), v3 = __ldcg(po + size_t(s + 3) * kKvl);
-            a = fmaf(w[s], v0, a); b = fmaf(w[s + 1], v1, b); a = fmaf(w[s + 2], v2, a); b = fmaf(w[s + 3], v3, b);
+#pragma unroll
+        for (int q = 0; q < 32; q += 2) {
+            a = fmaf(mhalf + 2 * q < n_active ? w[mhalf + 2 * q] : 0.f, v0[q], a);
+            b = fmaf(mhalf + 2 * q + 2 < n_active ? w[mhalf + 2 * q + 2] : 0.f, v0[q + 1], b);
         }
-        for (; s < n_active; ++s) a = fmaf(w[s], __ldcg(po + size_t(s) * kKvl), a);
-        ol[tid] = (a + b) / den;
+        for (int s0 = mhalf + 64; s0 < n_active; s0 += 64) {   // contexts beyond 2048 positions
+            float v[32];
+#pragma unroll
+            for (int q = 0; q < 32; ++q) v[q] = __ldcg(po + size_t(min(s0 + 2 * q, n_active - 1)) * kKvl);
+#pragma unroll
+            for (int q = 0; q < 32; q += 2) {
+                a = fmaf(s0 + 2 * q < n_active ? w[s0 + 2 * q] : 0.f, v[q], a);
+                b = fmaf(s0 + 2 * q + 2 < n_active ? w[s0 + 2 * q + 2] : 0.f, v[q + 1], b);
+            }
+        }
+        ol[mhalf][mc] = a + b;
     }
     __syncthreads();
-    const float4* x4 = reinterpret_cast<const float4*>(ol + lane * 8);
+    if (tid < kKvl) ol[0][tid] = (ol[0][tid] + ol[1][tid]) / den;
+    __syncthreads();
+    const float4* x4 = reinterpret_cast<const float4*>(&ol[0][lane * 8]);
     const float4 xa = x4[0], xb = x4[1];
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
+    for (int r = 0; r < 4; ++r) {
         const float acc = warp_sum(dot8(wv[r], xa, xb, 0.f));
-        if (lane == 0) p.out[size_t(h) * kVd + warp * 8 + r] = f32_to_bf16_bits(acc);
+        if (lane == 0) p.out[size_t(h) * kVd + warp * 4 + r] = f32_to_bf16_bits(acc);
     }
     trace_end(p.trace);
 }
@@ -315,7 +359,9 @@ bool mla_latent_supported(int heads, int q_lora, int kv_lora, int nope, int rope
            mla_latent_splits(max_ctx) <= kLatMaxSplits;
 }
 
-cudaError_t mla_latent_dispatch(const MlaLatentParams& p, cudaStream_t stream, bool pdl) {
+cudaError_t mla_latent_dispatch(const MlaLatentParams& params, cudaStream_t stream, bool pdl) {
+    MlaLatentParams p = params;
+    p.trace = p.trace3[0];
     cudaError_t e;
     const dim3 block(kLatThreads), g1(3, p.heads);
     switch (p.q_lora / 256) {
@@ -326,12 +372,11 @@ cudaError_t mla_latent_dispatch(const MlaLatentParams& p, cudaStream_t stream, b
         default: return cudaErrorInvalidValue;
     }
     if (e != cudaSuccess) return e;
-    if (p.heads % 8 == 0)
-        e = launch_kernel(mla_latent_attn_kernel<8>, dim3(p.heads / 8, p.nsplit), block, 0, stream, pdl, p);
-    else
-        e = launch_kernel(mla_latent_attn_kernel<4>, dim3(p.heads / 4, p.nsplit), block, 0, stream, pdl, p);
+    p.trace = p.trace3[1];
+    e = launch_kernel(mla_latent_attn_kernel, dim3(p.heads / kLatHG, p.nsplit), block, 0, stream, pdl, p);
     if (e != cudaSuccess) return e;
-    return launch_kernel(mla_v_absorb_kernel, dim3(p.heads), block, 0, stream, pdl, p);
+    p.trace = p.trace3[2];
+    return launch_kernel(mla_v_absorb_kernel, dim3(p.heads), dim3(kVaThreads), 0, stream, pdl, p);
 }
 
 }  // namespace tfb

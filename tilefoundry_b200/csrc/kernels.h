@@ -159,7 +159,8 @@ struct MlaLatentParams {
     uint16_t* latent_new_out;    // optional [kv_lora + rope]
     int heads, q_lora, page_size, max_ctx, nsplit;
     float scale, lora_eps;
-    unsigned long long* trace;
+    unsigned long long* trace;   // debug timeline record of the launch this copy of the parameters goes to
+    unsigned long long* trace3[3];
 };
 int mla_latent_splits(int max_ctx);
 bool mla_latent_supported(int heads, int q_lora, int kv_lora, int nope, int rope, int vd, int max_ctx);
