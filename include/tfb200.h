@@ -315,11 +315,15 @@ typedef struct {
     float temperature;      /* > 0: sample each token from softmax(logits / temperature) (see tfb_lm_head_args); else greedy */
     uint64_t seed;
     /* TFB_KERNEL_FUSED: the step as ONE cooperative launch, one CTA per multiprocessor; the weight stream runs
-     * through a shared-memory ring across all phases and layers, phases hand over through counters in global
-     * memory (every wait bounded).  Needs d = 128, hq = 2 hkv, hidden / hq*d / inter multiples of 1024 that divide
-     * 12288, hidden in {1024, 2048, 3072, 6144}, temperature <= 0; other shapes get TFB_EINVAL.
+     * through a shared-memory ring across all phases and layers; phases hand activations over as tagged 32-bit
+     * words (bf16 value + 16-bit tag of launch and phase) that the consumer polls, every wait bounded.  Needs
+     * d = 128, hq = 2 hkv, hidden / hq*d / inter in {1024, 2048, 3072, 4096, 6144}, hidden in {1024, 2048, 3072,
+     * 6144}, temperature <= 0; other shapes get TFB_EINVAL.
      *   step_layers: DEVICE copy of the layer table, n_layers x 11 pointers in tfb_qwen3_layer's field order
-     *   step_sync:   uint32 [tfb_qwen3_step_sync_words(n_layers, hkv)], zeroed once (the kernel leaves it zero)
+     *   step_sync:   uint32 [tfb_qwen3_step_sync_words(n_layers, hkv)], zeroed once (merge tickets, which the kernel
+     *                leaves zero, and a launch counter, which it advances)
+     *   step_xbuf:   uint32 [tfb_qwen3_step_xbuf_words(hidden, hq, hkv, d, inter)], zeroed once and again whenever
+     *                step_sync is zeroed (the tagged activations: hidden | q|k|v | attention | MLP inner)
      *   step_status: uint32 [1], zeroed once; non-zero after a wait gave up (the step's results are then void)
      * and part_o / part_ml sized for tfb_qwen3_step_splits(hkv) splits, head_val / head_idx for one entry per
      * multiprocessor.  No reference counterpart: the reference's fast driver replays about 280 launches per
@@ -331,9 +335,11 @@ typedef struct {
     int32_t* stop_at;
     int32_t n_eos;
     int32_t reserved_eos;
+    uint32_t* step_xbuf;
 } tfb_qwen3_step_args;
 TFB_API int tfb_qwen3_decode_step(const tfb_qwen3_step_args* args, tfb_stream_t stream);
 TFB_API int32_t tfb_qwen3_step_sync_words(int32_t n_layers, int32_t hkv);
+TFB_API int64_t tfb_qwen3_step_xbuf_words(int32_t hidden, int32_t hq, int32_t hkv, int32_t d, int32_t inter);
 TFB_API int32_t tfb_qwen3_step_splits(int32_t hkv);   /* splits of the context the fused step may use (needs a CUDA device) */
 
 /* ---- multi-head latent attention decode (MiniCPM3) ------------------------------

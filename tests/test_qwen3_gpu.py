@@ -334,7 +334,7 @@ def test_one_launch_step_matches_evaluator_small(dev, use_graph, kernel):
         v_got = paged_kv.logical_view(sess.layers[li]["v_pool"], sess.table[0], total)
         assert_close_at_scale(k_got, k_ref[:, :total], f"layer {li} K cache")
         assert_close_at_scale(v_got, v_ref[:, :total], f"layer {li} V cache")
-    assert int(sess.step_sync.abs().sum()) == 0                      # the last CTA left every counter at zero
+    assert int(sess.step_sync[:-1].abs().sum()) == 0                 # the last CTA left every ticket at zero (the last word counts launches)
 
 
 def test_one_launch_step_equals_the_launch_per_kernel_step(dev):

@@ -345,11 +345,14 @@ int tfb_attn_gqa_decode_noalloc(const tfb_attn_gqa_args* a, tfb_stream_t stream)
 int32_t tfb_qwen3_step_sync_words(int32_t n_layers, int32_t hkv) {
     return n_layers > 0 && hkv > 0 ? tfb::fused_step_sync_words(n_layers, hkv) : 0;
 }
+int64_t tfb_qwen3_step_xbuf_words(int32_t hidden, int32_t hq, int32_t hkv, int32_t d, int32_t inter) {
+    return hidden > 0 && hq > 0 && hkv > 0 && d > 0 && inter > 0 ? tfb::fused_step_xbuf_words(hidden, hq, hkv, d, inter) : 0;
+}
 int32_t tfb_qwen3_step_splits(int32_t hkv) { return hkv > 0 ? tfb::fused_step_splits(hkv) : 0; }
 
 // TFB_KERNEL_FUSED: the whole step as one cooperative launch.
 static int qwen3_fused_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
-    TFB_REQUIRE(a->step_layers && a->step_sync && a->step_status, TFB_EINVAL);
+    TFB_REQUIRE(a->step_layers && a->step_sync && a->step_status && a->step_xbuf, TFB_EINVAL);
     TFB_REQUIRE(a->temperature <= 0.f, TFB_EINVAL);                        // greedy only
     TFB_REQUIRE(a->vocab > 0 && a->vocab < (1ll << 31), TFB_EINVAL);
     tfb::FusedParams p;
@@ -365,9 +368,8 @@ static int qwen3_fused_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
     p.page_size = a->page_size; p.max_ctx = a->max_ctx; p.block_table = a->block_table;
     p.tokens = reinterpret_cast<long long*>(a->tokens); p.pos = a->pos;
     p.n_prompt = a->n_prompt; p.max_tokens = a->max_tokens;
-    p.hidden_buf = static_cast<uint16_t*>(a->hidden_buf); p.qkv_buf = static_cast<uint16_t*>(a->qkv_buf);
-    p.attn_buf = static_cast<uint16_t*>(a->attn_buf); p.act_buf = static_cast<uint16_t*>(a->act_buf);
     p.logits = static_cast<uint16_t*>(a->logits);
+    p.xbuf = a->step_xbuf;
     p.part_o = a->part_o; p.part_ml = a->part_ml;
     p.sync = a->step_sync; p.status = a->step_status;
     p.head_val = a->head_val; p.head_idx = a->head_idx;

@@ -410,7 +410,8 @@ struct FusedParams {
     long long* tokens;
     int* pos;
     int n_prompt, max_tokens;
-    uint16_t *hidden_buf, *qkv_buf, *attn_buf, *act_buf, *logits;
+    uint16_t* logits;
+    unsigned* xbuf;                      // fused_step_xbuf_words() tagged activation words, zero before the first launch
     float *part_o, *part_ml;             // [hq][fused_step_splits][d], [hq][fused_step_splits][2]
     unsigned* sync;                      // fused_step_sync_words() words, zero before the first launch
     unsigned* status;                    // [1]: non-zero after a wait gave up
@@ -427,6 +428,7 @@ struct FusedParams {
     int timeline_slots;
 };
 int fused_step_sync_words(int n_layers, int hkv);
+long long fused_step_xbuf_words(int hidden, int hq, int hkv, int d, int inter);
 int fused_step_splits(int hkv);
 bool fused_step_supported(const FusedParams& p);
 cudaError_t fused_step_launch(const FusedParams& p, cudaStream_t stream);

@@ -18,11 +18,18 @@
 // loads per lane.  Slice sums meet in shared memory in fixed order (deterministic); rounding points are those
 // of gemv_kernel / attn_gqa_kernel / lm_head_kernel.
 //
-// Dependencies between phases are counters in global memory: a CTA adds one when its rows of a phase are
-// written (release), consumers poll until every producer CTA has arrived (acquire) and then read the vector
-// through L2.  Attention: KV head h, split s of the context on CTA s*hkv + h (the context is cut into at most
-// G/hkv splits, so no CTA has two); cached K/V rows are requested before the q|k|v counter is waited on; the
-// last split of a KV head to finish (a ticket) merges the partials.  Every wait is bounded: a timeout sets
+// Dependencies between phases travel WITH the data: every activation element is a 32-bit word, bf16 value in
+// the low half and a 16-bit tag in the high half that names the launch and the phase that wrote it.  A consumer
+// polls the words themselves (relaxed gpu-scope loads; each word of a vector is fetched by exactly one thread
+// of the CTA and shared through shared memory) and proceeds when every tag matches, so a hand-over costs one
+// trip through L2 -- no fence, no counter, no second read.  (With counters it cost fence + atomic + counter poll
+// + vector read, about 3.5 us per phase, five phases per layer.)  A word is single-copy atomic, the tag of a
+// phase differs from the tag of whatever the word held before (launch counter * phases + phase, mod 65535, +1;
+// zero is never a tag), and a word is rewritten only after every reader of its old value has produced something
+// that the writer has already consumed (the data dependences of the step guarantee it).
+// Attention: KV head h, split s of the context on CTA s*hkv + h (the context is cut into at most G/hkv splits,
+// so no CTA has two); cached K/V rows are requested before this token's q|k|v is waited on; the last split of
+// a KV head to finish (a ticket, with fences) merges the partials.  Every wait is bounded: a timeout sets
 // *status, and every later wait of that CTA returns at once, so the launch always ends.
 //
 // HBM-bound: algorithmic bytes per launch = all weights once + the KV rows of positions [0, pos].
@@ -39,16 +46,17 @@ constexpr int kFusedThreads = kCT + 32;          // + the producer warp (warp 0)
 constexpr int kSliceLen = 1024;                  // K elements one warp keeps in registers
 constexpr int kTileBytes = kCW * kSliceLen * 2;  // 24 KB
 constexpr int kStages = 8;
+constexpr int kTileBatch = 4;                     // tiles a consumer warp takes between two barriers
 constexpr unsigned long long kWaitNs = 200ull * 1000 * 1000;   // every wait gives up after 0.2 s
 constexpr int kD = 128, kGQ = 2;                 // head dim and query heads per KV head of this build
 constexpr int kBatchRows = 8;                    // cache rows one warp holds in registers at a time
-constexpr int kMergeLoads = 20;                  // split partials one merging thread requests at once
+constexpr int kMergeLoads = 6;                   // 16-byte pieces of split partials one merging thread requests at once
 
 struct FusedSmem {
     alignas(128) unsigned char ring[kStages][kTileBytes];
     alignas(8) unsigned long long full[kStages];
     unsigned long long empty[kStages];
-    float part[2][kCW];
+    float part[2][kTileBatch][kCW];
     float red[16];
     alignas(16) float q[kGQ][kD];
     alignas(16) float knew[kD];
@@ -57,6 +65,7 @@ struct FusedSmem {
     alignas(16) float wo[kCW][kGQ][kD];
     int flag;
     volatile int abort;
+    float mrg_m[kGQ][64], mrg_l[kGQ][64];        // (max, sum) of every split of this KV head's query heads, for the merge
     unsigned koff[kCW][kBatchRows];              // element offset of warp w's cached row t of its first batch, or ~0u
     unsigned new_off;                            // where this token's own row goes (the owner split)
 };
@@ -93,6 +102,39 @@ __device__ __forceinline__ uint4 lds16(uint32_t addr) {
     return v;
 }
 
+__device__ __forceinline__ uint4 ld_relaxed16(const unsigned* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned ld_relaxed32(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_tagged(unsigned* p, unsigned tag, uint16_t bits) {
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" :: "l"(p), "r"((tag << 16) | unsigned(bits)) : "memory");
+}
+// f32 partials travel the same way in 64-bit words: value in the low half, tag in the high half.
+__device__ __forceinline__ void st_tagged64(unsigned long long* p, unsigned tag, float v) {
+    const unsigned long long w = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" :: "l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_relaxed64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ ulonglong2 ld_relaxed64x2(const unsigned long long* p) {
+    ulonglong2 v;
+    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(v.x), "=l"(v.y) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ bool tags_ok(const uint4& w, unsigned tag) {
+    return (w.x >> 16) == tag && (w.y >> 16) == tag && (w.z >> 16) == tag && (w.w >> 16) == tag;
+}
+
 // Bounded waits.  After the first timeout of a CTA every wait returns at once (the results are void, *status says so).
 __device__ __forceinline__ void wait_bar(FusedSmem& s, unsigned long long* bar, unsigned parity, unsigned* status, unsigned code) {
     if (s.abort) return;
@@ -119,6 +161,16 @@ __device__ __forceinline__ void wait_count(FusedSmem& s, const unsigned* ctr, un
     }
     s.abort = 1;
     atomicOr(status, code);
+}
+// Inside a polling loop: true when the loop has to give up (another wait of the CTA already did, or this one has
+// made kPollLimit trips to L2: a trip takes 0.3 us at the least, so the bound is a tenth of a second or more).
+constexpr int kPollLimit = 1 << 19;
+__device__ __forceinline__ bool poll_expired(FusedSmem& s, int& spins, unsigned* status, unsigned code) {
+    if (s.abort) return true;
+    if (++spins < kPollLimit) return false;
+    s.abort = 1;
+    atomicOr(status, code);
+    return true;
 }
 // A CTA's outputs of a phase are written (by the threads of one warp, or before a consumer_sync): publish them.
 __device__ __forceinline__ void arrive(unsigned* ctr) {
@@ -180,11 +232,12 @@ struct HeadBest {
 };
 
 // ---- consumers: one matrix phase --------------------------------------------------------------------------------
-// y = epilogue(W . prologue(x)) for this CTA's rows.  `wait_ctr`/`wait_target`: the counter that says x is complete.
+// y = epilogue(W . prologue(x)) for this CTA's rows.  x: tagged words, complete when every tag is in_tag; y: tagged
+// words written with out_tag (the head writes plain bf16 logits to y_plain instead).
 template <int KIND, bool NORM>
 __device__ __forceinline__ void consume(FusedSmem& s, RingPos& rp, const FusedParams& p, int n, int k,
-                                        const uint16_t* x, const uint16_t* gamma, uint16_t* y, uint16_t* trace_row,
-                                        const unsigned* wait_ctr, unsigned wait_target, unsigned* arrive_ctr,
+                                        const unsigned* x, unsigned in_tag, const uint16_t* gamma, unsigned* y,
+                                        unsigned out_tag, uint16_t* y_plain, uint16_t* trace_row,
                                         int c, int G, int cw, int lane, HeadBest* best, int ph) {
     const int KS = k / kSliceLen, R = kCW / KS;
     const int U = KIND == kSwiglu ? R / 2 : R;
@@ -198,38 +251,60 @@ __device__ __forceinline__ void consume(FusedSmem& s, RingPos& rp, const FusedPa
 #pragma unroll
         for (int q = 0; q < 4; ++q) gv[q] = *reinterpret_cast<const uint4*>(gamma + j * kSliceLen + q * 256 + lane * 8);
     }
-    if (cw == 0 && lane == 0) {
-        tl_enter(p, ph);
-        wait_count(s, wait_ctr, wait_target, p.status, 0x100u);
-        tl_waited(p, ph);
+    const int tid = cw * 32 + lane;
+    if (tid == 0) tl_enter(p, ph);
+    // The activation vector: each tagged word is fetched by exactly one thread of the CTA, polled until its tag says
+    // this phase's input has landed, and parked as bf16 in shared memory (the attention scratch, idle here).
+    uint16_t* xs = reinterpret_cast<uint16_t*>(&s.wo[0][0][0]);
+    {
+        const int nvec = k >> 2;                              // <= 4 * kCT (k <= 6144)
+        uint4 w[4];
+        int spins = 0;
+        for (;;) {                                            // (a thread without an i-th piece re-reads its first)
+            bool ok = true;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) w[i] = ld_relaxed16(x + 4 * (tid + i * kCT < nvec ? tid + i * kCT : tid % nvec));
+#pragma unroll
+            for (int i = 0; i < 4; ++i) ok = ok && tags_ok(w[i], in_tag);
+            if (ok || poll_expired(s, spins, p.status, 0x100u)) break;
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (tid + i * kCT < nvec) {
+                *reinterpret_cast<uint2*>(xs + 4 * (tid + i * kCT)) =
+                    make_uint2((w[i].x & 0xffffu) | (w[i].y << 16), (w[i].z & 0xffffu) | (w[i].w << 16));
+                if (NORM) {
+                    const float a = bf16_lo(w[i].x), b = bf16_lo(w[i].y), cc = bf16_lo(w[i].z), d = bf16_lo(w[i].w);
+                    ss = fmaf(a, a, ss); ss = fmaf(b, b, ss); ss = fmaf(cc, cc, ss); ss = fmaf(d, d, ss);
+                }
+            }
+        }
+        if (NORM) {
+            ss = warp_sum(ss);
+            if (lane == 0) s.red[cw] = ss;
+        }
     }
     consumer_sync();
+    if (tid == 0) tl_waited(p, ph);
 
     // this warp's K-slice of the activation vector, in registers for the whole phase
     float xf[32];
-    {
-        uint4 xv[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) xv[q] = __ldcg(reinterpret_cast<const uint4*>(x + j * kSliceLen + q * 256 + lane * 8));
+    for (int q = 0; q < 4; ++q) {
+        const uint4 xv = *reinterpret_cast<const uint4*>(xs + j * kSliceLen + q * 256 + lane * 8);
+        const uint32_t u[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const uint32_t u[4] = {xv[q].x, xv[q].y, xv[q].z, xv[q].w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) { xf[q * 8 + 2 * i] = bf16_lo(u[i]); xf[q * 8 + 2 * i + 1] = bf16_hi(u[i]); }
-        }
+        for (int i = 0; i < 4; ++i) { xf[q * 8 + 2 * i] = bf16_lo(u[i]); xf[q * 8 + 2 * i + 1] = bf16_hi(u[i]); }
     }
     // the residual of this CTA's rows (at most 32), one per lane of the finishing warp, ahead of the tile loop
+    // (written by this CTA itself in an earlier phase; whatever tag it carries)
     float res = 0.f;
-    if (KIND == kResidual && cw == 0 && u0 + lane < u1) res = bf16_bits_to_f32(__ldcg(y + u0 + lane));
+    if (KIND == kResidual && cw == 0 && u0 + lane < u1) res = bf16_lo(ld_relaxed32(y + u0 + lane));
     if (NORM) {
-        float ss = 0.f;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) ss = fmaf(xf[i], xf[i], ss);
-        ss = warp_sum(ss);
-        if (r == 0 && lane == 0) s.red[j] = ss;
-        consumer_sync();
         float tot = 0.f;
-        for (int q = 0; q < KS; ++q) tot += s.red[q];
+#pragma unroll
+        for (int q = 0; q < kCW; ++q) tot += s.red[q];
         const float rstd = rsqrtf(tot / float(k) + p.eps);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -248,64 +323,71 @@ __device__ __forceinline__ void consume(FusedSmem& s, RingPos& rp, const FusedPa
         }
     }
 
+    // Tiles are taken kTileBatch at a time: the chain wait -> shared loads -> multiply-adds -> warp reduction ->
+    // barrier -> epilogue is latency, not work (the step ran no faster with the weight loads taken out), so one
+    // barrier and one epilogue serve several tiles.  A batch never holds more rows than a warp has lanes.
+    const int NB = min(kTileBatch, 32 / U);
     int buf = 0;
-    for (int u = u0; u < u1; u += U) {
-        const int nu = min(U, u1 - u);
-        wait_bar(s, &s.full[rp.stage], rp.parity, p.status, 0x20000u);
-        const bool valid = KIND == kSwiglu ? (r % U) < nu : r < nu;
-        float acc0 = 0.f, acc1 = 0.f;
-        if (valid) {
-            const uint32_t base = s_u32(s.ring[rp.stage]) + uint32_t(r) * uint32_t(k) * 2u + uint32_t(j) * (kSliceLen * 2) + lane * 16;
+    for (int u = u0; u < u1; u += NB * U) {
+#pragma unroll 1
+        for (int b = 0; b < NB; ++b) {                             // (not unrolled: the kernel's code has to stay small)
+            const int ub = u + b * U;
+            if (ub >= u1) break;                                   // (the same for every thread of the CTA)
+            const int nu = min(U, u1 - ub);
+            wait_bar(s, &s.full[rp.stage], rp.parity, p.status, 0x20000u);
+            const bool valid = KIND == kSwiglu ? (r % U) < nu : r < nu;
+            float acc0 = 0.f, acc1 = 0.f;
+            if (valid) {
+                const uint32_t base = s_u32(s.ring[rp.stage]) + uint32_t(r) * uint32_t(k) * 2u + uint32_t(j) * (kSliceLen * 2) + lane * 16;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const uint4 w = lds16(base + q * 512);
-                const float4 xa = make_float4(xf[q * 8], xf[q * 8 + 1], xf[q * 8 + 2], xf[q * 8 + 3]);
-                const float4 xb = make_float4(xf[q * 8 + 4], xf[q * 8 + 5], xf[q * 8 + 6], xf[q * 8 + 7]);
-                if (q & 1) acc1 = dot8(w, xa, xb, acc1); else acc0 = dot8(w, xa, xb, acc0);
+                for (int q = 0; q < 4; ++q) {
+                    const uint4 w = lds16(base + q * 512);
+                    const float4 xa = make_float4(xf[q * 8], xf[q * 8 + 1], xf[q * 8 + 2], xf[q * 8 + 3]);
+                    const float4 xb = make_float4(xf[q * 8 + 4], xf[q * 8 + 5], xf[q * 8 + 6], xf[q * 8 + 7]);
+                    if (q & 1) acc1 = dot8(w, xa, xb, acc1); else acc0 = dot8(w, xa, xb, acc0);
+                }
             }
+            __syncwarp();
+            if (lane == 0) mb_arrive(&s.empty[rp.stage]);          // this warp has read its part of the stage
+            rp.next();
+            const float sum = warp_sum(acc0 + acc1);
+            if (lane == 0) s.part[buf][b][cw] = sum;
         }
-        __syncwarp();
-        if (lane == 0) mb_arrive(&s.empty[rp.stage]);          // this warp has read its part of the stage
-        rp.next();
-        const float sum = warp_sum(acc0 + acc1);
-        if (lane == 0) s.part[buf][cw] = sum;
         consumer_sync();
-        if (cw == 0 && lane < nu) {                            // K-slices added in fixed order, epilogue
+        if (cw == 0) {                                             // K-slices added in fixed order, epilogue: lane = (tile, row)
+            const int b = lane / U, rr = lane % U, row = u + b * U + rr;
+            const bool live = b < NB && row < u1;
             float v = 0.f, v2 = 0.f;
-            for (int q = 0; q < KS; ++q) {
-                v += s.part[buf][lane * KS + q];
-                if (KIND == kSwiglu) v2 += s.part[buf][(lane + U) * KS + q];
+            if (live) {
+                for (int q = 0; q < KS; ++q) {
+                    v += s.part[buf][b][rr * KS + q];
+                    if (KIND == kSwiglu) v2 += s.part[buf][b][(rr + U) * KS + q];
+                }
             }
-            const int row = u + lane;
             if (KIND == kStore) {
-                y[row] = f32_to_bf16_bits(v);
+                if (live) st_tagged(y + row, out_tag, f32_to_bf16_bits(v));
             } else if (KIND == kSwiglu) {
                 const float g = round_bf16(v), up = round_bf16(v2);
-                y[row] = f32_to_bf16_bits(round_bf16(silu_f32(g)) * up);
+                if (live) st_tagged(y + row, out_tag, f32_to_bf16_bits(round_bf16(silu_f32(g)) * up));
             } else if (KIND == kHead) {
                 const float sc = round_bf16(v);
-                if (y) y[row] = f32_to_bf16_bits(sc);
-                if (sc > best->v || (sc == best->v && row < best->i)) { best->v = sc; best->i = row; }
-            }
-        }
-        if (KIND == kResidual && cw == 0) {                    // (all lanes: the residual comes from another lane)
-            float v = 0.f;
-            if (lane < nu)
-                for (int q = 0; q < KS; ++q) v += s.part[buf][lane * KS + q];
-            const float mine = __shfl_sync(0xffffffffu, res, (u - u0 + lane) & 31);
-            if (lane < nu) {
-                const uint16_t out = f32_to_bf16_bits(mine + round_bf16(v));
-                y[u + lane] = out;
-                if (trace_row) trace_row[u + lane] = out;
+                if (live) {
+                    if (y_plain) y_plain[row] = f32_to_bf16_bits(sc);
+                    if (sc > best->v || (sc == best->v && row < best->i)) { best->v = sc; best->i = row; }
+                }
+            } else {                                               // residual (all lanes shuffle: it sits in another lane)
+                const float mine = __shfl_sync(0xffffffffu, res, (row - u0) & 31);
+                if (live) {
+                    const uint16_t out = f32_to_bf16_bits(mine + round_bf16(v));
+                    st_tagged(y + row, out_tag, out);
+                    if (trace_row) trace_row[row] = out;
+                }
             }
         }
         buf ^= 1;
     }
-    consumer_sync();                                            // (also protects s.red / s.part against the next phase)
-    if (cw == 0 && lane == 0) {
-        if (arrive_ctr) arrive(arrive_ctr);
-        tl_done(p, ph);
-    }
+    consumer_sync();                                            // (protects s.red / s.part / xs against the next phase)
+    if (tid == 0) tl_done(p, ph);
 }
 
 __device__ __forceinline__ size_t kv_offset(const FusedParams& p, int pos, int h) {
@@ -314,9 +396,9 @@ __device__ __forceinline__ size_t kv_offset(const FusedParams& p, int pos, int h
 }
 
 // ---- consumers: attention of one layer ------------------------------------------------------------------------
-__device__ __forceinline__ void attend(FusedSmem& s, const FusedParams& p, const FusedLayer& L, const unsigned* qkv_ctr,
-                                       unsigned* tickets, unsigned* done_ctr, int pos, int c, int G, int cw, int lane,
-                                       int ph) {
+__device__ __forceinline__ void attend(FusedSmem& s, const FusedParams& p, const FusedLayer& L, const unsigned* xqkv,
+                                       unsigned in_tag, unsigned* xattn, unsigned out_tag, unsigned long long* xpart, int pos,
+                                       int c, int G, int cw, int lane, int ph) {
     const int total = pos + 1;
     const int ns_max = min(G / p.hkv, 64);
     const int SL = max(16, ((total + ns_max - 1) / ns_max + 15) & ~15);
@@ -353,22 +435,28 @@ __device__ __forceinline__ void attend(FusedSmem& s, const FusedParams& p, const
             rs[i] = bf16_bits_to_f32(p.sin_table[size_t(pos) * kD + lane + 32 * i]);
         }
     }
-    if (cw == 0 && lane == 0) {
-        tl_enter(p, ph);
-        wait_count(s, qkv_ctr, unsigned(G), p.status, 0x200u);
-        tl_waited(p, ph);
-    }
-    consumer_sync();
+    if (cw == 0 && lane == 0) tl_enter(p, ph);
 
     // this token's q (2 heads), k, v of KV head h: one warp per vector, lane l holds elements l, l+32, l+64, l+96,
-    // so the rotate-half partner (64 away) sits in the same lane
+    // so the rotate-half partner (64 away) sits in the same lane; the tagged words are polled until they are this
+    // layer's
     if (cw < nvec) {
-        const uint16_t* src = cw < kGQ ? p.qkv_buf + size_t(h * kGQ + cw) * kD
-                              : cw == kGQ ? p.qkv_buf + size_t(p.hq) * kD + size_t(h) * kD
-                                          : p.qkv_buf + size_t(p.hq + p.hkv) * kD + size_t(h) * kD;
+        const unsigned* src = cw < kGQ ? xqkv + size_t(h * kGQ + cw) * kD
+                              : cw == kGQ ? xqkv + size_t(p.hq) * kD + size_t(h) * kD
+                                          : xqkv + size_t(p.hq + p.hkv) * kD + size_t(h) * kD;
+        unsigned wd[4];
+        int spins = 0;
+        for (;;) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) wd[i] = ld_relaxed32(src + lane + 32 * i);
+            const bool ok = (wd[0] >> 16) == in_tag && (wd[1] >> 16) == in_tag && (wd[2] >> 16) == in_tag && (wd[3] >> 16) == in_tag;
+            if (__all_sync(0xffffffffu, ok)) break;
+            if (poll_expired(s, spins, p.status, 0x200u)) break;
+        }
+        if (cw == 0 && lane == 0) tl_waited(p, ph);
         float xv[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) xv[i] = bf16_bits_to_f32(__ldcg(src + lane + 32 * i));
+        for (int i = 0; i < 4; ++i) xv[i] = bf16_lo(wd[i]);
         if (cw == kGQ + 1) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) s.vnew[lane + 32 * i] = xv[i];
@@ -481,70 +569,95 @@ __device__ __forceinline__ void attend(FusedSmem& s, const FusedParams& p, const
     // the warps' partial (max, sum, weighted V) of this split, folded in warp order
     const int tid = cw * 32 + lane;
     const int jh = tid / kD, d = tid % kD;                       // threads 0..255: one output element each
-    if (tid < kGQ * kD) {
-        float M = -INFINITY;
+    const bool col = tid < kGQ * kD;
+    const int head = h * kGQ + (col ? jh : 0);
+    constexpr int PW = kD + 2;                                   // words of a partial: kD weighted sums, max, sum
+    float M = -INFINITY, num = 0.f, den = 0.f;
+    if (col) {
         for (int w = 0; w < kCW; ++w) M = fmaxf(M, s.wm[w][jh]);
-        float num = 0.f, den = 0.f;
         for (int w = 0; w < kCW; ++w) {
             const float wgt = s.wm[w][jh] == -INFINITY ? 0.f : __expf(s.wm[w][jh] - M);
             num = fmaf(wgt, s.wo[w][jh][d], num);
             den = fmaf(wgt, s.wl[w][jh], den);
         }
-        const int head = h * kGQ + jh;
         if (NS == 1) {
-            p.attn_buf[size_t(head) * kD + d] = f32_to_bf16_bits(num / den);
-        } else {
-            p.part_o[(size_t(head) * ns_max + sp) * kD + d] = num;
+            st_tagged(xattn + size_t(head) * kD + d, out_tag, f32_to_bf16_bits(num / den));
+        } else if (sp != 0) {                                    // handed to split 0 of this KV head as tagged words
+            unsigned long long* dst = xpart + (size_t(head) * ns_max + sp) * PW;
+            st_tagged64(dst + d, out_tag, num);
             if (d == 0) {
-                p.part_ml[(size_t(head) * ns_max + sp) * 2] = M;
-                p.part_ml[(size_t(head) * ns_max + sp) * 2 + 1] = den;
+                st_tagged64(dst + kD, out_tag, M);
+                st_tagged64(dst + kD + 1, out_tag, den);
             }
         }
     }
-    if (NS > 1) {
-        __threadfence();                                         // every writer publishes its own partials
-        consumer_sync();
-        if (tid == 0) s.flag = atomicAdd(&tickets[h], 1u) == unsigned(NS - 1);
-        consumer_sync();
-        if (!s.flag) return;                                     // another split of this KV head merges
-        __threadfence();
-        if (tid < kGQ * kD) {
-            const int head = h * kGQ + jh;
-            const float2* ml = reinterpret_cast<const float2*>(p.part_ml + size_t(head) * ns_max * 2);
-            const float* po = p.part_o + size_t(head) * ns_max * kD + d;
-            float M = -INFINITY, num = 0.f, den = 0.f;
-            for (int q0 = 0; q0 < NS; q0 += kMergeLoads) {          // every partial of a pass requested at once
-                float2 st[kMergeLoads];
-                float ov[kMergeLoads];
+    if (NS > 1 && sp == 0) {
+        // Split 0 merges.  Every word it needs is requested at once and polled until its tag is this phase's: one
+        // trip through L2 after the last split has written, with no fence and no ticket on the way.  The other
+        // splits' columns are dealt over all 384 threads -- thread (pair of columns, third of the splits) -- so
+        // that a thread holds at most kMergeLoads 16-byte loads in registers.
+        const int others = NS - 1;
+        const int pr = tid & 127, g = tid >> 7;                  // pr: head pr / 64, columns 2 * (pr % 64) and the next
+        const int pj = pr >> 6, pd = (pr & 63) * 2;
+        const unsigned long long* src = xpart + (size_t(h * kGQ + pj) * ns_max) * PW + pd;
+        ulonglong2 nv[kMergeLoads];
+        auto split_of = [others, g](int i) { return min(1 + g + 3 * i, others); };      // (clamped: re-reads the last one)
 #pragma unroll
-                for (int q = 0; q < kMergeLoads; ++q) {
-                    const bool in = q0 + q < NS;
-                    st[q] = in ? __ldcg(ml + q0 + q) : make_float2(-INFINITY, 0.f);
-                    ov[q] = in ? __ldcg(po + size_t(q0 + q) * kD) : 0.f;
-                }
-                float pm = M;
-#pragma unroll
-                for (int q = 0; q < kMergeLoads; ++q) pm = fmaxf(pm, st[q].x);
-                const float resc = M == -INFINITY ? 0.f : __expf(M - pm);
-                num *= resc;
-                den *= resc;
-#pragma unroll
-                for (int q = 0; q < kMergeLoads; ++q) {
-                    const float wgt = st[q].x == -INFINITY ? 0.f : __expf(st[q].x - pm);
-                    num = fmaf(wgt, ov[q], num);
-                    den = fmaf(wgt, st[q].y, den);
-                }
-                M = pm;
+        for (int i = 0; i < kMergeLoads; ++i) nv[i] = ld_relaxed64x2(src + size_t(split_of(i)) * PW);
+        if (tid < kGQ * others * 2) {                            // (max, sum) of the other splits: one word per thread
+            const int j2 = tid / (others * 2), rem = tid % (others * 2), q = 1 + (rem >> 1), which = rem & 1;
+            const unsigned long long* a = xpart + (size_t(h * kGQ + j2) * ns_max + q) * PW + kD + which;
+            unsigned long long w;
+            int spins = 0;
+            for (;;) {
+                w = ld_relaxed64(a);
+                if (unsigned(w >> 32) == out_tag || poll_expired(s, spins, p.status, 0x800u)) break;
             }
-            p.attn_buf[size_t(head) * kD + d] = f32_to_bf16_bits(num / den);
+            (which ? s.mrg_l : s.mrg_m)[j2][q] = __uint_as_float(unsigned(w));
+        }
+        if (col && d == 0) { s.mrg_m[jh][0] = M; s.mrg_l[jh][0] = den; }
+        consumer_sync();                                         // (also: every thread is done with s.wo)
+        float gm = -INFINITY;
+        for (int q = 0; q < NS; ++q) gm = fmaxf(gm, s.mrg_m[pj][q]);
+        float t0 = 0.f, t1 = 0.f;
+        for (int i0 = 0; 1 + g + 3 * i0 <= others; i0 += kMergeLoads) {
+            if (i0 > 0) {                                        // more splits than one batch holds
+#pragma unroll
+                for (int i = 0; i < kMergeLoads; ++i) nv[i] = ld_relaxed64x2(src + size_t(split_of(i0 + i)) * PW);
+            }
+            int spins = 0;
+            for (;;) {                                           // until the whole batch carries this phase's tag
+                bool ok = true;
+#pragma unroll
+                for (int i = 0; i < kMergeLoads; ++i)
+                    ok = ok && unsigned(nv[i].x >> 32) == out_tag && unsigned(nv[i].y >> 32) == out_tag;
+                if (ok || poll_expired(s, spins, p.status, 0x800u)) break;
+#pragma unroll
+                for (int i = 0; i < kMergeLoads; ++i) nv[i] = ld_relaxed64x2(src + size_t(split_of(i0 + i)) * PW);
+            }
+#pragma unroll
+            for (int i = 0; i < kMergeLoads; ++i) {
+                const int q = 1 + g + 3 * (i0 + i);
+                if (q <= others) {
+                    const float wq = __expf(s.mrg_m[pj][q] - gm);
+                    t0 = fmaf(wq, __uint_as_float(unsigned(nv[i].x)), t0);
+                    t1 = fmaf(wq, __uint_as_float(unsigned(nv[i].y)), t1);
+                }
+            }
+        }
+        float* acc = &s.wo[0][0][0];                             // [3][kGQ][kD]
+        *reinterpret_cast<float2*>(acc + (g * kGQ + pj) * kD + pd) = make_float2(t0, t1);
+        consumer_sync();
+        if (col) {
+            float gmc = -INFINITY, td = 0.f;
+            for (int q = 0; q < NS; ++q) gmc = fmaxf(gmc, s.mrg_m[jh][q]);
+            for (int q = 0; q < NS; ++q) td = fmaf(__expf(s.mrg_m[jh][q] - gmc), s.mrg_l[jh][q], td);
+            const float tn = fmaf(__expf(M - gmc), num, acc[(0 * kGQ + jh) * kD + d] + acc[(1 * kGQ + jh) * kD + d] + acc[(2 * kGQ + jh) * kD + d]);
+            st_tagged(xattn + size_t(head) * kD + d, out_tag, f32_to_bf16_bits(tn / td));
         }
     }
-    __threadfence();
-    consumer_sync();
-    if (tid == 0) {
-        atomicAdd(done_ctr, 1u);                                 // one arrival per KV head
-        tl_done(p, ph);
-    }
+    consumer_sync();                                             // (s.wo is the next phase's activation staging)
+    if (tid == 0) tl_done(p, ph);
 }
 
 __global__ void __launch_bounds__(kFusedThreads, 1) qwen3_step_kernel(const FusedParams p) {
@@ -556,8 +669,17 @@ __global__ void __launch_bounds__(kFusedThreads, 1) qwen3_step_kernel(const Fuse
     if (pos < 0 || pos >= p.max_ctx) return;                      // (uniform over the grid: nothing waits on anything)
     if (p.stop_at != nullptr && *p.stop_at != 0) return;          // the sequence met an end token: the step is a no-op
     const int H = p.hidden, L = p.n_layers, QP = p.hq * kD, NQKV = (p.hq + 2 * p.hkv) * kD;
-    const int per_layer = 5 + p.hkv;
-    unsigned* const glob = p.sync + L * per_layer;                 // [0] embedding copied, [1] head pairs written, [2] exit tickets
+    const int per_layer = 5 + p.hkv;                               // [5..] of a layer's words: its KV heads' merge tickets
+    unsigned* const glob = p.sync + L * per_layer;                 // [1] head pairs written, [2] exit tickets, [3] launch counter
+    // tags: launch counter * phases + phase, mod 65535, + 1 (phase 0 embedding, 1 + 5*layer + {0..4}, then the head)
+    const unsigned epoch = glob[3];                                // written by the previous launch's last CTA
+    const unsigned tag_base = unsigned((unsigned long long)epoch * unsigned(5 * L + 2) % 65535ull);
+    auto tag = [tag_base](int ph) { return (tag_base + unsigned(ph)) % 65535u + 1u; };
+    unsigned* const xh = p.xbuf;                                   // tagged activations: hidden | q|k|v | attention | MLP inner
+    unsigned* const xqkv = xh + H;
+    unsigned* const xattn = xqkv + NQKV;
+    unsigned* const xact = xattn + QP;
+    unsigned long long* const xpart = reinterpret_cast<unsigned long long*>(xact + ((p.inter + 1) & ~1));   // split partials
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStages; ++i) { mb_init(&s.full[i], 1); mb_init(&s.empty[i], kCW); }
@@ -602,33 +724,27 @@ __global__ void __launch_bounds__(kFusedThreads, 1) qwen3_step_kernel(const Fuse
         id = id < 0 ? 0 : (id >= p.vocab ? p.vocab - 1 : id);
         int u0, u1;
         span(H, c, G, u0, u1);
-        for (int i = u0 + tid; i < u1; i += kCT) p.hidden_buf[i] = p.w_embed[size_t(id) * H + i];
-        consumer_sync();
-        if (tid == 0) {
-            arrive(&glob[0]);
-            tl_done(p, 0);
-        }
+        for (int i = u0 + tid; i < u1; i += kCT) st_tagged(xh + i, tag(0), p.w_embed[size_t(id) * H + i]);
+        if (tid == 0) tl_done(p, 0);
     }
-    const unsigned* hidden_ready = &glob[0];
+    int hidden_ph = 0;                                             // the phase that wrote the current hidden state
     for (int l = 0; l < L; ++l) {
         const FusedLayer& Ly = p.layers[l];
-        unsigned* ctr = p.sync + l * per_layer;                    // [0] q|k|v, [1] attention, [2] o, [3] gate/up, [4] down, [5..] tickets
-        consume<kStore, true>(s, rp, p, NQKV, H, p.hidden_buf, Ly.gamma_in, p.qkv_buf, nullptr, hidden_ready, unsigned(G),
-                              &ctr[0], c, G, cw, lane, nullptr, 1 + 5 * l);
-        attend(s, p, Ly, &ctr[0], &ctr[5], &ctr[1], pos, c, G, cw, lane, 2 + 5 * l);
-        consume<kResidual, false>(s, rp, p, H, QP, p.attn_buf, nullptr, p.hidden_buf, nullptr, &ctr[1], unsigned(p.hkv),
-                                  &ctr[2], c, G, cw, lane, nullptr, 3 + 5 * l);
-        consume<kSwiglu, true>(s, rp, p, p.inter, H, p.hidden_buf, Ly.gamma_post, p.act_buf, nullptr, &ctr[2], unsigned(G),
-                               &ctr[3], c, G, cw, lane, nullptr, 4 + 5 * l);
-        consume<kResidual, false>(s, rp, p, H, p.inter, p.act_buf, nullptr, p.hidden_buf,
-                                  p.hidden_trace ? p.hidden_trace + size_t(l) * H : nullptr, &ctr[3], unsigned(G), &ctr[4],
-                                  c, G, cw, lane, nullptr, 5 + 5 * l);
-        hidden_ready = &ctr[4];
+        const int ph = 1 + 5 * l;
+        consume<kStore, true>(s, rp, p, NQKV, H, xh, tag(hidden_ph), Ly.gamma_in, xqkv, tag(ph), nullptr, nullptr,
+                              c, G, cw, lane, nullptr, ph);
+        attend(s, p, Ly, xqkv, tag(ph), xattn, tag(ph + 1), xpart, pos, c, G, cw, lane, ph + 1);
+        consume<kResidual, false>(s, rp, p, H, QP, xattn, tag(ph + 1), nullptr, xh, tag(ph + 2), nullptr, nullptr,
+                                  c, G, cw, lane, nullptr, ph + 2);
+        consume<kSwiglu, true>(s, rp, p, p.inter, H, xh, tag(ph + 2), Ly.gamma_post, xact, tag(ph + 3), nullptr, nullptr,
+                               c, G, cw, lane, nullptr, ph + 3);
+        consume<kResidual, false>(s, rp, p, H, p.inter, xact, tag(ph + 3), nullptr, xh, tag(ph + 4), nullptr,
+                                  p.hidden_trace ? p.hidden_trace + size_t(l) * H : nullptr, c, G, cw, lane, nullptr, ph + 4);
+        hidden_ph = ph + 4;
     }
     HeadBest best{-INFINITY, 0x7fffffff};
-    consume<kHead, true>(s, rp, p, p.vocab, H, p.hidden_buf, p.gamma_final, p.logits,
-                         p.hidden_trace ? p.hidden_trace + size_t(L) * H : nullptr, hidden_ready, unsigned(G), nullptr,
-                         c, G, cw, lane, &best, 1 + 5 * L);
+    consume<kHead, true>(s, rp, p, p.vocab, H, xh, tag(hidden_ph), p.gamma_final, nullptr, 0u, p.logits,
+                         p.hidden_trace ? p.hidden_trace + size_t(L) * H : nullptr, c, G, cw, lane, &best, 1 + 5 * L);
     if (cw == 0) {
         // this CTA's (best logit, lowest index), then the pick over all CTAs by CTA 0
 #pragma unroll
@@ -676,22 +792,28 @@ __global__ void __launch_bounds__(kFusedThreads, 1) qwen3_step_kernel(const Fuse
         if (s.flag) {
             __threadfence();
             for (int i = lane; i < L * per_layer + 3; i += 32) p.sync[i] = 0u;
+            if (lane == 0) glob[3] = epoch + 1u;
         }
     }
 }
 
 }  // namespace
 
-int fused_step_sync_words(int n_layers, int hkv) { return n_layers * (5 + hkv) + 3; }
+int fused_step_sync_words(int n_layers, int hkv) { return n_layers * (5 + hkv) + 4; }
+long long fused_step_xbuf_words(int hidden, int hq, int hkv, int d, int inter) {
+    const long long vectors = (long long)hidden + (long long)(hq + 2 * hkv) * d + (long long)hq * d + ((inter + 1) & ~1);
+    return vectors + 2ll * hq * fused_step_splits(hkv) * (d + 2);       // + the split partials as 64-bit words
+}
 int fused_step_splits(int hkv) { const int s = sm_count() / (hkv > 0 ? hkv : 1); return s < 64 ? s : 64; }
 
 bool fused_step_supported(const FusedParams& p) {
     const int QP = p.hq * kD;
-    auto ok_k = [](int k) { return k >= kSliceLen && k % kSliceLen == 0 && kCW % (k / kSliceLen) == 0; };
+    // (k <= 6144: an activation vector is staged as bf16 in the 12 KB attention scratch, four 16-byte pieces per thread)
+    auto ok_k = [](int k) { return k >= kSliceLen && k % kSliceLen == 0 && kCW % (k / kSliceLen) == 0 && k <= 4 * 4 * kCT; };
     const int G = sm_count();
     return p.n_layers >= 1 && p.n_layers <= kFusedMaxLayers && p.d == kD && p.hkv >= 1 && p.hq == kGQ * p.hkv &&
            ok_k(p.hidden) && ok_k(QP) && ok_k(p.inter) && (kCW / (p.hidden / kSliceLen)) % 2 == 0 &&
-           p.hidden <= 32 * G && p.hkv <= G && p.inter >= 1 && p.vocab >= 1;
+           p.hidden <= 32 * G && p.hkv <= G && p.inter >= 1 && p.vocab >= 1 && p.xbuf != nullptr;
 }
 
 cudaError_t fused_step_launch(const FusedParams& p, cudaStream_t stream) {

@@ -114,6 +114,7 @@ class Qwen3Session(DecodeSession):
                                          for layer in self.layers], dtype=torch.int64, device=dev)
         self.step_sync = z(max(lib.load().tfb_qwen3_step_sync_words(len(self.layers), HKV), 1), dtype=torch.int32)
         self.step_status = z(1, dtype=torch.int32)
+        self.step_xbuf = z(max(int(lib.load().tfb_qwen3_step_xbuf_words(H, HQ, HKV, D, I)), 1), dtype=torch.int32)
         self.args = lib.Qwen3StepArgs(
             layers=self._layer_structs, n_layers=len(self.layers), hidden=H, hq=HQ, hkv=HKV, d=D, inter=I,
             vocab=V, eps=cfg.rms_norm_eps, scale=scale,
@@ -129,7 +130,7 @@ class Qwen3Session(DecodeSession):
             pdl=int(pdl), l2_prefetch=int(l2_prefetch), kernel=int(kernel), picked=lib.ptr(self.picked),
             chain_sync=lib.ptr(self.chain_sync), temperature=float(temperature), seed=int(seed) & (2 ** 64 - 1),
             step_layers=lib.ptr(self.step_layers), step_sync=lib.ptr(self.step_sync),
-            step_status=lib.ptr(self.step_status))
+            step_status=lib.ptr(self.step_status), step_xbuf=lib.ptr(self.step_xbuf))
         self.graph = None
         self._graph_prompt = None
         #: kernels one step enqueues (embed + 5 per layer + lm_head [+ trace copies and final norm])
@@ -155,6 +156,7 @@ class Qwen3Session(DecodeSession):
         if code:
             self.step_status.zero_()
             self.step_sync.zero_()
+            self.step_xbuf.zero_()                       # the launch counter restarts: no stale tag may match
             raise RuntimeError(f"tfb_qwen3_decode_step (one launch): a bounded wait gave up (status {code:#x})")
 
     def prefill(self, n_tokens: int) -> None:

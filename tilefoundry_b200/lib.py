@@ -66,7 +66,7 @@ class Qwen3StepArgs(C.Structure):
                 ("hidden_trace", _vp), ("pdl", _i32), ("l2_prefetch", _i32), ("kernel", _i32), ("picked", _vp),
                 ("chain_sync", _vp), ("temperature", _f32), ("seed", _u64),
                 ("step_layers", _vp), ("step_sync", _vp), ("step_status", _vp),
-                ("eos_ids", _vp), ("stop_at", _vp), ("n_eos", _i32), ("reserved_eos", _i32)]
+                ("eos_ids", _vp), ("stop_at", _vp), ("n_eos", _i32), ("reserved_eos", _i32), ("step_xbuf", _vp)]
 
 
 class GemvChainArgs(C.Structure):
@@ -279,6 +279,7 @@ SYMBOLS = {
     "tfb_qwen3_decode_step": (_i32, [C.POINTER(Qwen3StepArgs), _vp]),
     "tfb_qwen3_step_sync_words": (_i32, [_i32, _i32]),
     "tfb_qwen3_step_splits": (_i32, [_i32]),
+    "tfb_qwen3_step_xbuf_words": (_i64, [_i32, _i32, _i32, _i32, _i32]),
     "tfb_attn_mla_decode": (_i32, [C.POINTER(AttnMlaArgs), _vp]),
     "tfb_mla_latent_decode": (_i32, [C.POINTER(MlaLatentArgs), _vp]),
     "tfb_mla_latent_splits": (_i32, [_i32]),
