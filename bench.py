@@ -721,6 +721,41 @@ def run_ours(args):
         leave_together()
 
 
+def run_profile_case(args):
+    """A few eager decode steps of a configuration cut to --profile-layers layers, the position parked at the mean
+    context of the benchmark: small enough (a few GB) for a profiler to replay single launches of any kernel of the
+    step.  Prints what it ran; not a benchmark line."""
+    import dataclasses
+
+    import torch
+
+    from tilefoundry_b200.runtime import DictResource
+
+    work = Workload(args.config)
+    n = args.profile_layers
+    kw = {"n_layers": n} if work.key == "qwen3_5_35b_a3b" else {"num_hidden_layers": n}
+    if work.key == "granite_4_0_h_small":
+        kw["attention_layers"] = (n - 1,)
+    work.cfg = dataclasses.replace(work.cfg, **kw)
+    dev = torch.device("cuda:0")
+    extra = {"kernel": args.kernel} if work.key == "qwen3_1_7b" and args.kernel >= 0 else {}
+    sess = work.session_cls(work.cfg, DictResource(work.device_weights(dev, seed=0)), max_ctx=PROMPT_TOKENS + NEW_TOKENS,
+                            device=dev, **extra)
+    sess.reset(prompt_ids(work.cfg, 0))
+    steps = min(max(args.steps, 1), 16)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(steps + 1):
+        sess.pos.fill_(PROMPT_TOKENS - 1 + NEW_TOKENS // 2)
+        if i == 1:
+            t0.record()
+        sess.step()
+    t1.record()
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": True, "config": work.key, "layers": n, "eager_steps": steps,
+                      "context": PROMPT_TOKENS - 1 + NEW_TOKENS // 2, "launches_per_step": sess.launches_per_step,
+                      "ms_per_eager_step": t0.elapsed_time(t1) / steps}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -749,11 +784,17 @@ def main():
     ap.add_argument("--skip-prompt-walk", action="store_true",
                     help="with --batch: start at the end of the prompt without walking it and launch eagerly (for profiler "
                          "captures; the number includes host launch time)")
+    ap.add_argument("--profile-layers", type=int, default=0,
+                    help="the small case a profiler capture runs: the configuration cut to this many layers (same widths, one "
+                         "attention layer among them where the model mixes layer kinds), --steps eager decode steps at "
+                         "the run's mean context, one JSON line that is NOT the metric")
     ap.add_argument("--dominant-only", action="store_true",
                     help="build the session, time only the dominant kernel over every layer's weights, print it and exit "
                          "(the small case a profiler capture of that kernel runs)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile_layers > 0:
+        run_profile_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     elif args.batch32_projection:
         run_batch32_projection(args)

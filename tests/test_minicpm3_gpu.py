@@ -133,3 +133,22 @@ def test_session_matches_evaluator_tiny(dev, use_graph, cache):
     excused = parity.compare_run(cfg.num_hidden_layers, want, sess, got, n_prompt, n_new)
     assert excused <= 8
     parity.compare_caches(want, sess, n_prompt + n_new - 1)
+
+
+@pytest.mark.parametrize("cache", ["latent", "assembled"])
+def test_session_matches_evaluator_published_widths(dev, cache):
+    """The session walk at the published widths (hidden 2560, 40 heads, q_lora 768 / kv_lora 256, SwiGLU 6400) on a
+    stack of two layers and a 4096-token vocabulary: hidden state after every layer, logits, picks and caches of every
+    teacher-forced step against the evaluator, graph replay."""
+    from tilefoundry_b200.engine.minicpm3 import MiniCPM3Session
+    cfg = m.MiniCPM3Config(num_hidden_layers=2, vocab_size=4096, max_position_embeddings=512)
+    mod = m.build(cfg)
+    weights = m.tie_head(random_weights(mod, seed=13, std=0.02))
+    ref = evaluator.load(mod, DictResource(weights), om.make(cfg))
+    make = lambda cap: MiniCPM3Session(cfg, DictResource(parity.cuda_weights(weights, dev)), max_ctx=cap, device=dev,
+                                       keep_logits=True, trace_hidden=True, cache=cache)
+    n_prompt, n_new = 8, 40
+    want, sess, got = parity.teacher_forced(ref, make, cfg.vocab_size, n_prompt, n_new, 13, True)
+    excused = parity.compare_run(cfg.num_hidden_layers, want, sess, got, n_prompt, n_new)
+    assert excused <= 4
+    parity.compare_caches(want, sess, n_prompt + n_new - 1)

@@ -137,8 +137,8 @@ __device__ __forceinline__ bool tags_ok(const uint4& w, unsigned tag) {
 
 // Bounded waits.  After the first timeout of a CTA every wait returns at once (the results are void, *status says so).
 __device__ __forceinline__ void wait_bar(FusedSmem& s, unsigned long long* bar, unsigned parity, unsigned* status, unsigned code) {
-    if (s.abort) return;
     if (mb_try(bar, parity)) return;
+    if (s.abort) return;
     const unsigned long long t0 = global_ns();
     for (;;) {
         for (int i = 0; i < 64; ++i)
@@ -336,7 +336,7 @@ __device__ __forceinline__ void consume(FusedSmem& s, RingPos& rp, const FusedPa
             const int nu = min(U, u1 - ub);
             wait_bar(s, &s.full[rp.stage], rp.parity, p.status, 0x20000u);
             const bool valid = KIND == kSwiglu ? (r % U) < nu : r < nu;
-            float acc0 = 0.f, acc1 = 0.f;
+            float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
             if (valid) {
                 const uint32_t base = s_u32(s.ring[rp.stage]) + uint32_t(r) * uint32_t(k) * 2u + uint32_t(j) * (kSliceLen * 2) + lane * 16;
 #pragma unroll
@@ -344,13 +344,16 @@ __device__ __forceinline__ void consume(FusedSmem& s, RingPos& rp, const FusedPa
                     const uint4 w = lds16(base + q * 512);
                     const float4 xa = make_float4(xf[q * 8], xf[q * 8 + 1], xf[q * 8 + 2], xf[q * 8 + 3]);
                     const float4 xb = make_float4(xf[q * 8 + 4], xf[q * 8 + 5], xf[q * 8 + 6], xf[q * 8 + 7]);
-                    if (q & 1) acc1 = dot8(w, xa, xb, acc1); else acc0 = dot8(w, xa, xb, acc0);
+                    if (q == 0) acc0 = dot8(w, xa, xb, acc0);
+                    else if (q == 1) acc1 = dot8(w, xa, xb, acc1);
+                    else if (q == 2) acc2 = dot8(w, xa, xb, acc2);
+                    else acc3 = dot8(w, xa, xb, acc3);
                 }
             }
             __syncwarp();
             if (lane == 0) mb_arrive(&s.empty[rp.stage]);          // this warp has read its part of the stage
             rp.next();
-            const float sum = warp_sum(acc0 + acc1);
+            const float sum = warp_sum((acc0 + acc1) + (acc2 + acc3));
             if (lane == 0) s.part[buf][b][cw] = sum;
         }
         consumer_sync();
