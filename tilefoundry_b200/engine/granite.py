@@ -24,6 +24,33 @@ def pack_mixer(kind: str, w: dict) -> dict:
             "w_out": w["w_o"].contiguous()}
 
 
+def pack_model(cfg: GraniteConfig, resource, device=None):
+    """Authored names -> kernel layout of the whole model, unsharded (``engine/packed_models.py`` ``PackedModel``)."""
+    from .packed_models import PackedModel
+    to = (lambda t: t) if device is None else (lambda t: t.to(device))
+    root = {"table": to(resource.load("table")).contiguous(), "gamma_final": to(resource.load("gamma_final")).contiguous()}
+    layers = []
+    for i, kind in enumerate(cfg.layer_types):
+        sub = resource.subtree(f"layer{i}")
+        mix, moe = sub.subtree("mixer"), sub.subtree("moe")
+        names = MAMBA_W if kind == "linear_attention" else ATTN_W
+        layer = pack_mixer(kind, {n: to(mix.load(n)) for n in names})
+        layer.update({n: to(moe.load(n)).contiguous() for n in MOE_W})
+        layer["w_router"] = to(moe.subtree("router").load("w_router")).contiguous()
+        layers.append(layer)
+    return PackedModel("granite_4_0_h_small", root, layers)
+
+
+def shard_layer(layer: dict, rank: int, world: int) -> dict:
+    """This rank's part of a packed layer: its experts (``e % world == rank``), its slice of the shared expert; the
+    mixer, the norms and the router stay whole."""
+    out = dict(layer)
+    for n in ("w_gate", "w_up", "w_down"):
+        out[n] = sharding.local_experts(layer[n], rank, world)
+    out["w_shared_in"], out["w_shared_out"] = sharding.shared_slices(layer["w_shared_in"], layer["w_shared_out"], rank, world)
+    return out
+
+
 class GraniteSession(DecodeSession):
     def __init__(self, cfg: GraniteConfig, resource, *, max_ctx: int = 2176, device="cuda:0",
                  keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True, group=None,
@@ -44,8 +71,13 @@ class GraniteSession(DecodeSession):
         self.cfg, self.device, self.max_ctx = cfg, torch.device(device), int(max_ctx)
         dev = self.device
         to = lambda t: t.to(dev)
-        self.table_w = to(resource.load("table")).contiguous()
-        self.gamma_final = to(resource.load("gamma_final")).contiguous()
+        from .packed_models import PackedModel
+        # a resource speaks the authored names and is packed here (on this device when one rank holds everything,
+        # where the tensors lie when the model is sharded, so that only this rank's shard travels); a PackedModel is
+        # already in the kernels' layout
+        packed = resource if isinstance(resource, PackedModel) else pack_model(cfg, resource, dev if self.world == 1 else None)
+        self.table_w = to(packed.root["table"]).contiguous()
+        self.gamma_final = to(packed.root["gamma_final"]).contiguous()
         bf, f32 = torch.bfloat16, torch.float32
         z = lambda *s, dtype=bf: torch.zeros(*s, device=dev, dtype=dtype)
         HQ, HKV, D, H = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.hidden_size
@@ -54,19 +86,8 @@ class GraniteSession(DecodeSession):
         self.table = paged_kv.block_table(1, self.max_ctx, device=dev)
         self.layers = []
         for i, kind in enumerate(cfg.layer_types):
-            sub = resource.subtree(f"layer{i}")
-            mix, moe = sub.subtree("mixer"), sub.subtree("moe")
-            names = MAMBA_W if kind == "linear_attention" else ATTN_W
-            layer = pack_mixer(kind, {n: to(mix.load(n)) for n in names})
-            if self.world == 1:
-                layer.update({n: to(moe.load(n)).contiguous() for n in MOE_W})
-            else:                                     # keep only this rank's shard on the device
-                layer["gamma_post"] = to(moe.load("gamma_post")).contiguous()
-                for n in ("w_gate", "w_up", "w_down"):
-                    layer[n] = to(sharding.local_experts(moe.load(n), self.rank, self.world))
-                w_in, w_out = sharding.shared_slices(moe.load("w_shared_in"), moe.load("w_shared_out"), self.rank, self.world)
-                layer["w_shared_in"], layer["w_shared_out"] = to(w_in), to(w_out)
-            layer["w_router"] = to(moe.subtree("router").load("w_router")).contiguous()
+            layer = packed.layers[i] if self.world == 1 else shard_layer(packed.layers[i], self.rank, self.world)
+            layer = {n: to(t).contiguous() for n, t in layer.items()}
             layer["kind"] = kind
             if kind == "linear_attention":
                 layer["conv_state"] = z(cfg.conv_dim, cfg.mamba_d_conv - 1)

@@ -30,6 +30,22 @@ LAYER_WEIGHTS = ("gamma_in", "w_q_a", "gamma_q_a", "w_q_b", "w_kv_a", "gamma_kv_
                  "gamma_post", "w_gate", "w_up", "w_down")
 
 
+def pack_model(cfg: MiniCPM3Config, resource, device=None):
+    """Authored names -> kernel layout (``engine/packed_models.py`` ``PackedModel``): the head is stored only when it
+    is not the embedding table."""
+    from .packed_models import PackedModel
+    to = (lambda t: t) if device is None else (lambda t: t.to(device))
+    embed = to(resource.load("w_embed")).contiguous()
+    head = to(resource.load("w_head")).t().contiguous()
+    root = {"w_embed": embed, "w_head": None if torch.equal(head, embed) else head,
+            "gamma_final": to(resource.load("gamma_final")).contiguous()}
+    layers = []
+    for i in range(cfg.num_hidden_layers):
+        sub = resource.subtree(f"layer{i}")
+        layers.append(pack_layer({n: to(sub.load(n)) for n in LAYER_WEIGHTS}))
+    return PackedModel("minicpm3_4b", root, layers)
+
+
 class MiniCPM3Session(DecodeSession):
     def __init__(self, cfg: MiniCPM3Config, resource, *, max_ctx: int = 2176, device="cuda:0",
                  keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True,
@@ -43,15 +59,14 @@ class MiniCPM3Session(DecodeSession):
         latent = cache == "latent"
         self.cfg, self.device, self.max_ctx = cfg, torch.device(device), int(max_ctx)
         dev = self.device
-        to = lambda t: t.to(dev)
-        self.w_embed = to(resource.load("w_embed")).contiguous()
-        head = to(resource.load("w_head")).t().contiguous()
-        self.w_head = self.w_embed if torch.equal(head, self.w_embed) else head
-        self.gamma_final = to(resource.load("gamma_final")).contiguous()
-        self.layers = []
-        for i in range(cfg.num_hidden_layers):
-            sub = resource.subtree(f"layer{i}")
-            self.layers.append(pack_layer({n: to(sub.load(n)) for n in LAYER_WEIGHTS}))
+        from .packed_models import PackedModel
+        # a resource speaks the authored names and is packed here; a PackedModel is already in the kernels' layout
+        # (e.g. read from a file written by engine/packed_models.py save_packed)
+        packed = (resource if isinstance(resource, PackedModel) else pack_model(cfg, resource, dev)).to(dev)
+        self.w_embed = packed.root["w_embed"]
+        self.w_head = self.w_embed if packed.root["w_head"] is None else packed.root["w_head"]
+        self.gamma_final = packed.root["gamma_final"]
+        self.layers = [dict(layer) for layer in packed.layers]
 
         cos, sin = rope_tables(cfg, "cpu")
         self.max_pos = min(cfg.max_position_embeddings, self.max_ctx)

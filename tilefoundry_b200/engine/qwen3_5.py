@@ -43,6 +43,36 @@ ATTN_W = ("gamma_in", "w_qg", "w_k", "w_v", "gamma_q", "gamma_k", "w_o")
 MOE_W = ("gamma_post", "w_gate", "w_up", "w_down", "w_shared_gate", "w_shared_up", "w_shared_down", "w_shared_scale")
 
 
+def pack_model(cfg: Qwen35Config, resource, device=None):
+    """Authored names -> kernel layout of the whole model, unsharded (``engine/packed_models.py`` ``PackedModel``)."""
+    from .packed_models import PackedModel
+    to = (lambda t: t) if device is None else (lambda t: t.to(device))
+    root = {"table": to(resource.load("table")).contiguous(), "gamma_final": to(resource.load("gamma_final")).contiguous(),
+            "w_head": _rows(to(resource.load("w_head")))}                  # authored (hidden, vocab) -> [vocab, hidden]
+    layers = []
+    for i, kind in enumerate(cfg.layer_types):
+        sub = resource.subtree(f"layer{i}")
+        mix, moe = sub.subtree("mixer"), sub.subtree("moe")
+        names = GDN_W if kind == "linear_attention" else ATTN_W
+        layer = pack_mixer(kind, {n: to(mix.load(n)) for n in names})
+        layer.update(pack_moe({n: to(moe.load(n)) for n in MOE_W}, to(moe.subtree("router").load("w_router"))))
+        layers.append(layer)
+    return PackedModel("qwen3_5_35b_a3b", root, layers)
+
+
+def shard_layer(cfg: Qwen35Config, layer: dict, rank: int, world: int) -> dict:
+    """This rank's part of a packed layer: its experts (``e % world == rank``) and its rows of the shared expert's
+    gate / up projections with the matching columns of its down projection."""
+    out = dict(layer)
+    for n in ("w_gate", "w_up", "w_down"):
+        out[n] = sharding.local_experts(layer[n], rank, world)
+    per = cfg.shared_intermediate // world
+    lo, hi = rank * per, (rank + 1) * per
+    out["w_shared_gate"], out["w_shared_up"] = layer["w_shared_gate"][lo:hi].contiguous(), layer["w_shared_up"][lo:hi].contiguous()
+    out["w_shared_down"] = layer["w_shared_down"][:, lo:hi].contiguous()
+    return out
+
+
 class Qwen35Session(DecodeSession):
     def __init__(self, cfg: Qwen35Config, resource, *, max_ctx: int | None = None, device="cuda:0",
                  keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True, group=None,
@@ -73,32 +103,26 @@ class Qwen35Session(DecodeSession):
         H, V = cfg.hidden, cfg.vocab
         HQ, HKV, D = cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim
         E, K, I, IS = cfg.n_experts, cfg.top_k, cfg.moe_intermediate, cfg.shared_intermediate
-        self.table_w = to(resource.load("table")).contiguous()
-        self.gamma_final = to(resource.load("gamma_final")).contiguous()
-        head = resource.load("w_head")                                   # authored (hidden, vocab)
+        from .packed_models import PackedModel
+        # a resource speaks the authored names and is packed here (on this device when one rank holds everything,
+        # where the tensors lie when the model is sharded, so that only this rank's shard travels); a PackedModel is
+        # already in the kernels' layout
+        packed = resource if isinstance(resource, PackedModel) else pack_model(cfg, resource, dev if self.world == 1 else None)
+        self.table_w = to(packed.root["table"]).contiguous()
+        self.gamma_final = to(packed.root["gamma_final"]).contiguous()
+        head = packed.root["w_head"]                                     # [vocab, hidden]
         if self.world > 1:
             lo, hi = sharding.vocab_slice(V, self.rank, self.world)
-            head = head[:, lo:hi]
-        self.w_head = _rows(to(head))
+            head = head[lo:hi]
+        self.w_head = to(head).contiguous()
         cos, sin = rope_tables(cfg, "cpu")
         self.cos, self.sin = to(cos).contiguous(), to(sin).contiguous()
         self.table = paged_kv.block_table(1, self.max_ctx, device=dev)
         self.conv_stride = cfg.conv_dim * (cfg.gdn_conv_kernel - 1)
         self.layers = []
         for i, kind in enumerate(cfg.layer_types):
-            sub = resource.subtree(f"layer{i}")
-            mix, moe = sub.subtree("mixer"), sub.subtree("moe")
-            names = GDN_W if kind == "linear_attention" else ATTN_W
-            layer = pack_mixer(kind, {n: to(mix.load(n)) for n in names})
-            moe_w = {n: moe.load(n) for n in MOE_W}
-            if self.world > 1:                                           # keep only this rank's shard on the device
-                for n in ("w_gate", "w_up", "w_down"):
-                    moe_w[n] = sharding.local_experts(moe_w[n], self.rank, self.world)
-                per = IS // self.world
-                lo, hi = self.rank * per, (self.rank + 1) * per
-                moe_w["w_shared_gate"], moe_w["w_shared_up"] = moe_w["w_shared_gate"][:, lo:hi], moe_w["w_shared_up"][:, lo:hi]
-                moe_w["w_shared_down"] = moe_w["w_shared_down"][lo:hi, :]
-            layer.update(pack_moe({n: to(t) for n, t in moe_w.items()}, to(moe.subtree("router").load("w_router"))))
+            layer = packed.layers[i] if self.world == 1 else shard_layer(cfg, packed.layers[i], self.rank, self.world)
+            layer = {n: to(t).contiguous() for n, t in layer.items()}
             layer["kind"] = kind
             if kind == "linear_attention":
                 layer["conv_state"] = z(2, cfg.conv_dim, cfg.gdn_conv_kernel - 1)
