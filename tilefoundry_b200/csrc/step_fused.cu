@@ -327,6 +327,7 @@ __device__ __forceinline__ void consume(FusedSmem& s, RingPos& rp, const FusedPa
     // barrier -> epilogue is latency, not work (the step ran no faster with the weight loads taken out), so one
     // barrier and one epilogue serve several tiles.  A batch never holds more rows than a warp has lanes.
     const int NB = min(kTileBatch, 32 / U);
+    const int fb = lane / U, frr = lane % U;                      // the epilogue's lane = (tile of the batch, row of the tile)
     int buf = 0;
     for (int u = u0; u < u1; u += NB * U) {
 #pragma unroll 1
@@ -358,7 +359,7 @@ __device__ __forceinline__ void consume(FusedSmem& s, RingPos& rp, const FusedPa
         }
         consumer_sync();
         if (cw == 0) {                                             // K-slices added in fixed order, epilogue: lane = (tile, row)
-            const int b = lane / U, rr = lane % U, row = u + b * U + rr;
+            const int b = fb, rr = frr, row = u + b * U + rr;
             const bool live = b < NB && row < u1;
             float v = 0.f, v2 = 0.f;
             if (live) {
