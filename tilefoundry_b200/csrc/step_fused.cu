@@ -41,7 +41,6 @@ namespace tfb {
 namespace {
 
 constexpr int kCW = 12;                          // consumer warps
-constexpr int kGW = kCW / 2;                     // ... in two groups that take alternate tiles
 constexpr int kCT = kCW * 32;                    // consumer threads
 constexpr int kFusedThreads = kCT + 32;          // + the producer warp (warp 0)
 constexpr int kSliceLen = 1024;                  // K elements one warp keeps in registers
@@ -57,7 +56,7 @@ struct FusedSmem {
     alignas(128) unsigned char ring[kStages][kTileBytes];
     alignas(8) unsigned long long full[kStages];
     unsigned long long empty[kStages];
-    float part[2][2][kTileBatch][kCW];           // [group][buffer][tile of the batch][unit]
+    float part[2][kTileBatch][kCW];
     float red[16];
     alignas(16) float q[kGQ][kD];
     alignas(16) float knew[kD];
@@ -92,10 +91,6 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, unsigned b
                  :: "r"(s_u32(dst)), "l"(src), "r"(bytes), "r"(s_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" :: "n"(kCT) : "memory"); }
-__device__ __forceinline__ void group_sync(int grp) {           // the six warps of one group
-    if (grp) asm volatile("bar.sync 3, %0;" :: "n"(kGW * 32) : "memory");
-    else asm volatile("bar.sync 2, %0;" :: "n"(kGW * 32) : "memory");
-}
 __device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
     unsigned v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -206,10 +201,8 @@ __device__ __forceinline__ void span(int n, int c, int G, int& u0, int& u1) {
 struct RingPos {
     int stage;
     unsigned parity;
-    int odd;                                       // parity of the tile's place in the launch-wide sequence of tiles
     __device__ __forceinline__ void next() {
         if (++stage == kStages) { stage = 0; parity ^= 1u; }
-        odd ^= 1;
     }
 };
 
@@ -248,11 +241,7 @@ __device__ __forceinline__ void consume(FusedSmem& s, RingPos& rp, const FusedPa
                                         int c, int G, int cw, int lane, HeadBest* best, int ph) {
     const int KS = k / kSliceLen, R = kCW / KS;
     const int U = KIND == kSwiglu ? R / 2 : R;
-    // Two groups of six warps take alternate tiles, so that one group's fixed latencies (barrier test, reduction,
-    // group barrier, epilogue) overlap the other group's arithmetic.  A warp owns two (row, K-slice) units of its
-    // group's tiles -- rows r and r + R / 2, the same K-slice j, whose part of x it keeps in registers.
-    const int grp = cw / kGW, w6 = cw % kGW;
-    const int r = w6 / KS, j = w6 % KS;
+    const int r = cw / KS, j = cw % KS;
     int u0, u1;
     span(n, c, G, u0, u1);
 
@@ -311,7 +300,7 @@ __device__ __forceinline__ void consume(FusedSmem& s, RingPos& rp, const FusedPa
     // the residual of this CTA's rows (at most 32), one per lane of the finishing warp, ahead of the tile loop
     // (written by this CTA itself in an earlier phase; whatever tag it carries)
     float res = 0.f;
-    if (KIND == kResidual && w6 == 0 && u0 + lane < u1) res = bf16_lo(ld_relaxed32(y + u0 + lane));
+    if (KIND == kResidual && cw == 0 && u0 + lane < u1) res = bf16_lo(ld_relaxed32(y + u0 + lane));
     if (NORM) {
         float tot = 0.f;
 #pragma unroll
@@ -334,68 +323,49 @@ __device__ __forceinline__ void consume(FusedSmem& s, RingPos& rp, const FusedPa
         }
     }
 
-    // A group takes up to kTileBatch of its tiles between two group barriers: the chain wait -> shared loads ->
-    // multiply-adds -> warp reduction -> barrier -> epilogue is latency, not work (the step ran no faster with the
-    // weight loads taken out), so one barrier and one epilogue serve several tiles.  A batch never holds more rows
-    // than a warp has lanes; the group's first warp applies the epilogue, lane = (tile of the batch, row of the tile).
+    // Tiles are taken kTileBatch at a time: the chain wait -> shared loads -> multiply-adds -> warp reduction ->
+    // barrier -> epilogue is latency, not work (the step ran no faster with the weight loads taken out), so one
+    // barrier and one epilogue serve several tiles.  A batch never holds more rows than a warp has lanes.
     const int NB = min(kTileBatch, 32 / U);
-    const int fb = lane / U, frr = lane % U;
-    const int r2 = r + R / 2;                                     // (SwiGLU: the up row that belongs to gate row r)
-    int buf = 0, nb = 0, u_first = 0;
-    for (int u = u0; u < u1 || nb > 0; u += U) {
-        const bool more = u < u1;
-        if (more) {
-            if (rp.odd == grp) {
-                const int nu = min(U, u1 - u);
-                if (nb == 0) u_first = u;
-                wait_bar(s, &s.full[rp.stage], rp.parity, p.status, 0x20000u);
-                const bool valid = r < nu, valid2 = KIND == kSwiglu ? r < nu : r2 < nu;
-                float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+    const int fb = lane / U, frr = lane % U;                      // the epilogue's lane = (tile of the batch, row of the tile)
+    int buf = 0;
+    for (int u = u0; u < u1; u += NB * U) {
+#pragma unroll 1
+        for (int b = 0; b < NB; ++b) {                             // (not unrolled: the kernel's code has to stay small)
+            const int ub = u + b * U;
+            if (ub >= u1) break;                                   // (the same for every thread of the CTA)
+            const int nu = min(U, u1 - ub);
+            wait_bar(s, &s.full[rp.stage], rp.parity, p.status, 0x20000u);
+            const bool valid = KIND == kSwiglu ? (r % U) < nu : r < nu;
+            float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+            if (valid) {
                 const uint32_t base = s_u32(s.ring[rp.stage]) + uint32_t(r) * uint32_t(k) * 2u + uint32_t(j) * (kSliceLen * 2) + lane * 16;
-                const uint32_t base2 = base + uint32_t(R / 2) * uint32_t(k) * 2u;
-                if (valid) {
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const uint4 w = lds16(base + q * 512);
-                        const float4 xa = make_float4(xf[q * 8], xf[q * 8 + 1], xf[q * 8 + 2], xf[q * 8 + 3]);
-                        const float4 xb = make_float4(xf[q * 8 + 4], xf[q * 8 + 5], xf[q * 8 + 6], xf[q * 8 + 7]);
-                        if (q & 1) acc1 = dot8(w, xa, xb, acc1); else acc0 = dot8(w, xa, xb, acc0);
-                    }
+                for (int q = 0; q < 4; ++q) {
+                    const uint4 w = lds16(base + q * 512);
+                    const float4 xa = make_float4(xf[q * 8], xf[q * 8 + 1], xf[q * 8 + 2], xf[q * 8 + 3]);
+                    const float4 xb = make_float4(xf[q * 8 + 4], xf[q * 8 + 5], xf[q * 8 + 6], xf[q * 8 + 7]);
+                    if (q == 0) acc0 = dot8(w, xa, xb, acc0);
+                    else if (q == 1) acc1 = dot8(w, xa, xb, acc1);
+                    else if (q == 2) acc2 = dot8(w, xa, xb, acc2);
+                    else acc3 = dot8(w, xa, xb, acc3);
                 }
-                if (valid2) {
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const uint4 w = lds16(base2 + q * 512);
-                        const float4 xa = make_float4(xf[q * 8], xf[q * 8 + 1], xf[q * 8 + 2], xf[q * 8 + 3]);
-                        const float4 xb = make_float4(xf[q * 8 + 4], xf[q * 8 + 5], xf[q * 8 + 6], xf[q * 8 + 7]);
-                        if (q & 1) acc3 = dot8(w, xa, xb, acc3); else acc2 = dot8(w, xa, xb, acc2);
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) mb_arrive(&s.empty[rp.stage]);      // this warp has read its part of the stage
-                float sum = acc0 + acc1, sum2 = acc2 + acc3;       // two reductions, interleaved
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) {
-                    sum += __shfl_xor_sync(0xffffffffu, sum, o);
-                    sum2 += __shfl_xor_sync(0xffffffffu, sum2, o);
-                }
-                if (lane == 0) { s.part[grp][buf][nb][w6] = sum; s.part[grp][buf][nb][w6 + kGW] = sum2; }
-                ++nb;
             }
+            __syncwarp();
+            if (lane == 0) mb_arrive(&s.empty[rp.stage]);          // this warp has read its part of the stage
             rp.next();
+            const float sum = warp_sum((acc0 + acc1) + (acc2 + acc3));
+            if (lane == 0) s.part[buf][b][cw] = sum;
         }
-        // the group's batch is full, or the phase has no more tiles for it
-        const bool flush = nb > 0 && (nb == NB || !more || u + U >= u1);
-        if (!flush) continue;
-        group_sync(grp);
-        if (w6 == 0) {                                             // K-slices added in fixed order, epilogue
-            const int b = fb, rr = frr, row = u_first + b * 2 * U + rr;       // (the group's tiles are 2 U rows apart)
-            const bool live = b < nb && row < u1;
+        consumer_sync();
+        if (cw == 0) {                                             // K-slices added in fixed order, epilogue: lane = (tile, row)
+            const int b = fb, rr = frr, row = u + b * U + rr;
+            const bool live = b < NB && row < u1;
             float v = 0.f, v2 = 0.f;
             if (live) {
                 for (int q = 0; q < KS; ++q) {
-                    v += s.part[grp][buf][b][rr * KS + q];
-                    if (KIND == kSwiglu) v2 += s.part[grp][buf][b][(rr + U) * KS + q];
+                    v += s.part[buf][b][rr * KS + q];
+                    if (KIND == kSwiglu) v2 += s.part[buf][b][(rr + U) * KS + q];
                 }
             }
             if (KIND == kStore) {
@@ -419,7 +389,6 @@ __device__ __forceinline__ void consume(FusedSmem& s, RingPos& rp, const FusedPa
             }
         }
         buf ^= 1;
-        nb = 0;
     }
     consumer_sync();                                            // (protects s.red / s.part / xs against the next phase)
     if (tid == 0) tl_done(p, ph);
@@ -717,7 +686,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) qwen3_step_kernel(const Fuse
     unsigned long long* const xpart = reinterpret_cast<unsigned long long*>(xact + ((p.inter + 1) & ~1));   // split partials
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kStages; ++i) { mb_init(&s.full[i], 1); mb_init(&s.empty[i], kGW); }
+        for (int i = 0; i < kStages; ++i) { mb_init(&s.full[i], 1); mb_init(&s.empty[i], kCW); }
         s.abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -726,7 +695,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) qwen3_step_kernel(const Fuse
     if (warp == 0) {
         // ---- producer: every weight tile of the step, in consumption order ----
         if (lane != 0) return;
-        RingPos rp{0, 0, 0};
+        RingPos rp{0, 0};
         for (int l = 0; l < L; ++l) {
             const FusedLayer Ly = p.layers[l];
             produce(s, rp, Ly.w_qkv, nullptr, NQKV, H, c, G, p.status);
@@ -741,7 +710,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) qwen3_step_kernel(const Fuse
     // ---- consumers ----
     const int cw = warp - 1;
     const int tid = cw * 32 + lane;
-    RingPos rp{0, 0, 0};
+    RingPos rp{0, 0};
     {   // where this CTA's attention rows sit in every layer's pools (same split arithmetic as attend())
         const int total = pos + 1, ns_max = min(G / p.hkv, 64);
         const int SL = max(16, ((total + ns_max - 1) / ns_max + 15) & ~15), NS = (total + SL - 1) / SL;
@@ -780,21 +749,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) qwen3_step_kernel(const Fuse
     HeadBest best{-INFINITY, 0x7fffffff};
     consume<kHead, true>(s, rp, p, p.vocab, H, xh, tag(hidden_ph), p.gamma_final, nullptr, 0u, p.logits,
                          p.hidden_trace ? p.hidden_trace + size_t(L) * H : nullptr, c, G, cw, lane, &best, 1 + 5 * L);
-    if (cw == 0 || cw == kGW) {                                    // the two groups' finishing warps hold the candidates
+    if (cw == 0) {
+        // this CTA's (best logit, lowest index), then the pick over all CTAs by CTA 0
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, best.v, o);
             const int oi = __shfl_xor_sync(0xffffffffu, best.i, o);
-            if (ov > best.v || (ov == best.v && oi < best.i)) { best.v = ov; best.i = oi; }
-        }
-        if (cw == kGW && lane == 0) { s.red[0] = best.v; s.red[1] = __int_as_float(best.i); }
-    }
-    consumer_sync();
-    if (cw == 0) {
-        // this CTA's (best logit, lowest index), then the pick over all CTAs by CTA 0
-        {
-            const float ov = s.red[0];
-            const int oi = __float_as_int(s.red[1]);
             if (ov > best.v || (ov == best.v && oi < best.i)) { best.v = ov; best.i = oi; }
         }
         if (lane == 0) {
