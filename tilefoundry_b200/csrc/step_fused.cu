@@ -46,7 +46,7 @@ constexpr int kFusedThreads = kCT + 32;          // + the producer warp (warp 0)
 constexpr int kSliceLen = 1024;                  // K elements one warp keeps in registers
 constexpr int kTileBytes = kCW * kSliceLen * 2;  // 24 KB
 constexpr int kStages = 8;
-constexpr int kTileBatch = 4;                     // tiles a consumer warp takes between two barriers
+constexpr int kTileBatch = 8;                     // tiles a consumer warp takes between two barriers
 constexpr unsigned long long kWaitNs = 200ull * 1000 * 1000;   // every wait gives up after 0.2 s
 constexpr int kD = 128, kGQ = 2;                 // head dim and query heads per KV head of this build
 constexpr int kBatchRows = 8;                    // cache rows one warp holds in registers at a time
