@@ -320,8 +320,8 @@ typedef struct {
      * d = 128, hq = 2 hkv, hidden / hq*d / inter in {1024, 2048, 3072, 4096, 6144}, hidden in {1024, 2048, 3072,
      * 6144}, temperature <= 0; other shapes get TFB_EINVAL.
      *   step_layers: DEVICE copy of the layer table, n_layers x 11 pointers in tfb_qwen3_layer's field order
-     *   step_sync:   uint32 [tfb_qwen3_step_sync_words(n_layers, hkv)], zeroed once (merge tickets, which the kernel
-     *                leaves zero, and a launch counter, which it advances)
+     *   step_sync:   uint32 [tfb_qwen3_step_sync_words(n_layers, hkv)], zeroed once (words the kernel leaves zero, the
+     *                head's arrival count and a launch counter, which it advances)
      *   step_xbuf:   uint32 [tfb_qwen3_step_xbuf_words(hidden, hq, hkv, d, inter)], zeroed once and again whenever
      *                step_sync is zeroed (the tagged activations: hidden | q|k|v | attention | MLP inner)
      *   step_status: uint32 [1], zeroed once; non-zero after a wait gave up (the step's results are then void)

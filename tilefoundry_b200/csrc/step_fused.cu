@@ -673,7 +673,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) qwen3_step_kernel(const Fuse
     if (pos < 0 || pos >= p.max_ctx) return;                      // (uniform over the grid: nothing waits on anything)
     if (p.stop_at != nullptr && *p.stop_at != 0) return;          // the sequence met an end token: the step is a no-op
     const int H = p.hidden, L = p.n_layers, QP = p.hq * kD, NQKV = (p.hq + 2 * p.hkv) * kD;
-    const int per_layer = 5 + p.hkv;                               // [5..] of a layer's words: its KV heads' merge tickets
+    const int per_layer = 5 + p.hkv;                               // (a layer's words: unused since hand-overs travel with the data)
     unsigned* const glob = p.sync + L * per_layer;                 // [1] head pairs written, [2] exit tickets, [3] launch counter
     // tags: launch counter * phases + phase, mod 65535, + 1 (phase 0 embedding, 1 + 5*layer + {0..4}, then the head)
     const unsigned epoch = glob[3];                                // written by the previous launch's last CTA

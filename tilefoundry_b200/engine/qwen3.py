@@ -109,7 +109,7 @@ class Qwen3Session(DecodeSession):
         scale = float(torch.tensor(D ** -0.5, dtype=bf))   # the authored step holds it as a bf16 tensor
         self.chain_sync = torch.zeros(4, device=self.device, dtype=torch.int32)   # grid barrier + status of the chained launch
         # the one-launch step: the layer table on the device (11 pointers per layer, the C struct's field order),
-        # its phase counters and its status word
+        # its scratch words (merge tickets, launch counter), its tagged activation words and its status word
         self.step_layers = torch.tensor([[layer[name].data_ptr() for name, _ in lib.Qwen3Layer._fields_]
                                          for layer in self.layers], dtype=torch.int64, device=dev)
         self.step_sync = z(max(lib.load().tfb_qwen3_step_sync_words(len(self.layers), HKV), 1), dtype=torch.int32)
