@@ -565,6 +565,19 @@ def side_config(key, dev, K, W, with_cpu):
     m = measure(work, sess, prompt_ids(work.cfg, 0), K, W, dev, 0, 1, 1, False)
     whole = m.pop("whole_step")
     out = {"workload": work.describe, "dtype": work.dtype, "unit": "tok/s", **m, "roofline": roofline_of(work, sess, whole)}
+    if hasattr(sess, "prefill"):
+        # prompt processing, outside the metric: the 64-token prompt walked one decode step per token against the
+        # same prompt in chunks of 32 tokens (tensor-core projections)
+        try:
+            prompt = prompt_ids(work.cfg, 0)
+            walk = sess.generate(prompt, 4)
+            sess.generate(prompt, 4, prefill=True)                                  # warm-up: buffers, tensor maps
+            chunked = sess.generate(prompt, 4, prefill=True)
+            out["prompt"] = {"tokens": PROMPT_TOKENS, "walk_ms": walk.prompt_seconds * 1e3,
+                             "chunked_prefill_ms": chunked.prompt_seconds * 1e3,
+                             "same_continuation": walk.tokens == chunked.tokens}
+        except Exception as exc:                      # a side measurement: it must not cost the entry
+            out["prompt"] = {"error": f"{type(exc).__name__}: {exc}"}
     del sess
     torch.cuda.empty_cache()
     if with_cpu:

@@ -410,7 +410,9 @@ typedef struct {
     int32_t heads, q_lora, kv_lora, nope, rope, v;
     int32_t page_size, table_len, max_ctx, max_pos;
     float scale, lora_eps;
-    int32_t pdl, reserved;
+    int32_t pdl;
+    int32_t no_early_rows;    /* 1: fetch no cache row before the dependency wait (set when rows below *pos may have been
+                               * written by a launch that is still in the same dependency chain, as in a prompt chunk) */
 } tfb_mla_latent_args;
 TFB_API int tfb_mla_latent_decode(const tfb_mla_latent_args* args, tfb_stream_t stream);
 TFB_API int32_t tfb_mla_latent_splits(int32_t max_ctx);
@@ -484,6 +486,40 @@ typedef struct {
     float* q_rope_buf;        /* [heads*rope] */
 } tfb_minicpm3_step_args;
 TFB_API int tfb_minicpm3_decode_step(const tfb_minicpm3_step_args* args, tfb_stream_t stream);
+
+/* ---- a chunk of up to 32 consecutive prompt tokens through the MiniCPM3 stack (latent cache) ----------------
+ * Every projection streams its weights once per chunk on the tensor cores (tfb_gemm_small_m); the attention of the
+ * chunk's tokens runs token by token (tfb_mla_latent_decode with pos = pos_rows + t: each token appends its latent
+ * row, then attends to the rows up to its own).  Nothing is picked.  Needs the gate and up projections of a layer
+ * as one [2*inter, hidden] block (layers[i].w_up == layers[i].w_gate + inter*hidden elements) and
+ * layers[i].k_pool = the latent pool.  Scratch as for the decode step with cache_layout TFB_MLA_CACHE_LATENT, the
+ * row buffers m times as long.  Replaces the prompt loop of tests/models/orchestrator/causal_lm/generation.py:56-61
+ * for this model. */
+typedef struct {
+    const tfb_minicpm3_layer* layers;
+    int32_t n_layers, m, hidden, heads, q_lora, kv_lora, nope, rope, v, inter;
+    int64_t vocab;
+    float eps, lora_eps, scale, embed_scale, residual_scale;
+    int32_t pdl;
+    const void* w_embed;
+    const void* cos_table;
+    const void* sin_table;
+    int32_t max_pos, page_size, table_len, max_ctx;
+    const int32_t* block_table;
+    const int64_t* ids;       /* [m] token ids of the chunk */
+    const int32_t* pos_rows;  /* [m] on the device: the chunk's positions (consecutive) */
+    void* hidden_buf;         /* [m][hidden] */
+    void* norm_buf;           /* [m][hidden] */
+    void* qkv_a_buf;          /* [m][q_lora + kv_lora + rope] */
+    void* attn_buf;           /* [m][heads*v] */
+    void* act_buf;            /* [m][inter] */
+    float* q_lat_buf;
+    float* q_rope_buf;
+    float* part_o;
+    float* part_ml;
+    uint32_t* status;         /* [1]: non-zero after a bounded wait of a projection gave up */
+} tfb_minicpm3_prefill_args;
+TFB_API int tfb_minicpm3_prefill_chunk(const tfb_minicpm3_prefill_args* args, tfb_stream_t stream);
 
 /* out[i] = bf16(a[i] + bf16(b[i] * scale)).  Stands in for residual_add:
  * examples/granite_4_0_h_small-cuda/model.py:502-508; reference kernel granite.cu:159. */
@@ -669,6 +705,8 @@ typedef struct {
     /* swiglu != 0: w is [2n, k] = n gate rows then n up rows, y[M, n] = bf16(silu(bf16(x.gate^T)) * bf16(x.up^T))
      * (TFB_EPI_SWIGLU's rounding); n a multiple of 64, no residual. */
     int32_t swiglu;
+    /* with residual: y = bf16(residual + bf16(bf16(acc) * res_scale)), as tfb_gemv's res_scale; 0 means 1 */
+    float res_scale;
 } tfb_gemm_small_m_args;
 TFB_API int32_t tfb_gemm_small_m_splits(int32_t n, int32_t k);
 TFB_API int32_t tfb_gemm_small_m_swiglu_splits(int32_t n, int32_t k);

@@ -152,3 +152,42 @@ def test_session_matches_evaluator_published_widths(dev, cache):
     excused = parity.compare_run(cfg.num_hidden_layers, want, sess, got, n_prompt, n_new)
     assert excused <= 4
     parity.compare_caches(want, sess, n_prompt + n_new - 1)
+
+
+@pytest.mark.parametrize("size,n_prompt", [("tiny", 100), ("tiny", 34), ("tiny", 3), ("wide", 40)])
+def test_prefill_matches_walk_and_evaluator(dev, size, n_prompt):
+    """The prompt in chunks of up to 32 tokens (tensor-core projections, token-by-token latent attention) against the
+    token-by-token walk of the same session class and against the evaluator: position, latent cache rows, the first
+    new token's logits, and the continuation."""
+    from oracle import generation
+    from tilefoundry_b200.engine import paged_kv
+    from tilefoundry_b200.engine.minicpm3 import MiniCPM3Session
+    cfg = m.MINICPM3_TINY if size == "tiny" else m.MiniCPM3Config(num_hidden_layers=2, vocab_size=4096,
+                                                                  max_position_embeddings=512)
+    mod = m.build(cfg)
+    weights = m.tie_head(random_weights(mod, seed=31, std=0.05 if size == "tiny" else 0.02))
+    res = DictResource(parity.cuda_weights(weights, dev))
+    prompt = torch.randint(0, cfg.vocab_size, (n_prompt,), generator=torch.Generator().manual_seed(n_prompt))
+    walk = MiniCPM3Session(cfg, res, max_ctx=160, device=dev, keep_logits=True)
+    tok_walk = walk.generate(prompt, 1).tokens
+    logits_walk = walk.logits.clone()
+    pre = MiniCPM3Session(cfg, res, max_ctx=160, device=dev, keep_logits=True)
+    tok_pre = pre.generate(prompt, 1, prefill=True).tokens
+    assert int(pre.pos) == int(walk.pos) == n_prompt
+    assert_close_at_scale(pre.logits, logits_walk, "first new token's logits: prefill vs walk")
+    for li in range(cfg.num_hidden_layers):
+        a = paged_kv.logical_view(pre.layers[li]["k_pool"], pre.table[0], n_prompt)
+        b = paged_kv.logical_view(walk.layers[li]["k_pool"], walk.table[0], n_prompt)
+        assert_close_at_scale(a, b, f"layer {li} latent rows")
+    ref = evaluator.load(mod, DictResource(weights), om.make(cfg))
+    want = generation.decode_ids(ref, prompt, 1, keep_logits=True)
+    ref_logits = want["logits"][n_prompt - 1][0]
+    assert_close_at_scale(pre.logits, ref_logits, "first new token's logits: prefill vs evaluator")
+    if tok_pre != tok_walk:
+        top = torch.topk(ref_logits.float(), 2).values
+        assert float(top[0] - top[1]) < 2e-2
+    more_a = pre.generate(prompt, 24, prefill=True).tokens
+    more_b = pre.generate(prompt, 24, prefill=True, use_graph=False).tokens
+    assert more_a == more_b and len(more_a) == 24
+    with pytest.raises(ValueError, match="latent"):
+        MiniCPM3Session(cfg, res, max_ctx=160, device=dev, cache="assembled").prefill(4)

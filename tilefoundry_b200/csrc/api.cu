@@ -192,6 +192,7 @@ int tfb_gemm_small_m(const tfb_gemm_small_m_args* a, tfb_stream_t stream) {
     p.splits = p.swiglu ? tfb::gemm_tc_splits_swiglu(a->n, a->k) : tfb::gemm_tc_splits(a->n, a->k);
     p.status = a->status;
     p.y = static_cast<uint16_t*>(a->y); p.residual = static_cast<const uint16_t*>(a->residual);
+    p.res_scale = a->res_scale == 0.f ? 1.f : a->res_scale;
     return done(tfb::gemm_tc_launch(a->w, a->x, p, S(stream), a->pdl != 0));
 }
 

@@ -66,9 +66,66 @@ int tfb_mla_latent_decode(const tfb_mla_latent_args* a, tfb_stream_t stream) {
     p.latent_new_out = static_cast<uint16_t*>(a->latent_new_out);
     p.heads = a->heads; p.q_lora = a->q_lora; p.page_size = a->page_size; p.max_ctx = a->max_ctx;
     p.nsplit = tfb::mla_latent_splits(a->max_ctx);
-    p.scale = a->scale; p.lora_eps = a->lora_eps;
+    p.scale = a->scale; p.lora_eps = a->lora_eps; p.no_early_rows = a->no_early_rows != 0;
     for (int i = 0; i < 3; ++i) p.trace3[i] = next_trace();
     return done(tfb::mla_latent_dispatch(p, S(stream), a->pdl != 0));
+}
+
+int tfb_minicpm3_prefill_chunk(const tfb_minicpm3_prefill_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->layers && a->n_layers > 0 && a->m >= 2 && a->m <= 32, TFB_EINVAL);
+    TFB_REQUIRE(a->w_embed && a->ids && a->pos_rows && a->block_table && a->cos_table && a->sin_table, TFB_EINVAL);
+    TFB_REQUIRE(a->hidden_buf && a->norm_buf && a->qkv_a_buf && a->attn_buf && a->act_buf, TFB_EINVAL);
+    TFB_REQUIRE(a->q_lat_buf && a->q_rope_buf && a->part_o && a->part_ml && a->status, TFB_EINVAL);
+    TFB_REQUIRE(a->hidden % 64 == 0 && a->inter % 64 == 0 && (a->heads * a->v) % 64 == 0, TFB_EINVAL);
+    TFB_REQUIRE(tfb::mla_latent_supported(a->heads, a->q_lora, a->kv_lora, a->nope, a->rope, a->v, a->max_ctx), TFB_EINVAL);
+    const bool pdl = a->pdl != 0;
+    const int M = a->m, H = a->hidden, I = a->inter, NH = a->heads;
+    const int NA = a->q_lora + a->kv_lora + a->rope, NO = NH * a->v;
+    cudaStream_t st = S(stream);
+    uint16_t* hid = static_cast<uint16_t*>(a->hidden_buf);
+    uint16_t* nrm = static_cast<uint16_t*>(a->norm_buf);
+    uint16_t* qkv_a = static_cast<uint16_t*>(a->qkv_a_buf);
+    uint16_t* attn = static_cast<uint16_t*>(a->attn_buf);
+
+    auto project = [&](const void* w, const void* x, const void* residual, void* y, int n, int k, bool swiglu) -> int {
+        tfb_gemm_small_m_args g;
+        std::memset(&g, 0, sizeof g);
+        g.w = w; g.x = x; g.residual = residual; g.y = y; g.status = a->status;
+        g.m = M; g.n = n; g.k = k; g.pdl = pdl; g.swiglu = swiglu; g.res_scale = a->residual_scale;
+        return tfb_gemm_small_m(&g, stream);
+    };
+    auto norm = [&](const void* gamma) -> int {
+        return done(tfb::rmsnorm_launch(hid, static_cast<const uint16_t*>(gamma), nrm, M, H, a->eps,
+                                        TFB_NORM_CAST_THEN_GAIN, st, pdl));
+    };
+    // first launch without a programmatic dependency, as in the decode steps
+    cudaError_t e = tfb::embed_launch(static_cast<const uint16_t*>(a->w_embed), reinterpret_cast<const long long*>(a->ids),
+                                      nullptr, nullptr, hid, M, H, a->vocab, a->embed_scale, st, false);
+    if (e != cudaSuccess) return fail_launch(e);
+    for (int l = 0; l < a->n_layers; ++l) {
+        const tfb_minicpm3_layer& L = a->layers[l];
+        TFB_REQUIRE(static_cast<const uint16_t*>(L.w_up) == static_cast<const uint16_t*>(L.w_gate) + size_t(I) * H, TFB_EINVAL);
+        int rc = norm(L.gamma_in);
+        if (rc) return rc;
+        if ((rc = project(L.w_qkv_a, nrm, nullptr, qkv_a, NA, H, false))) return rc;
+        for (int t = 0; t < M; ++t) {                        // token t appends its latent row, then attends to rows <= its own
+            tfb_mla_latent_args m;
+            std::memset(&m, 0, sizeof m);
+            m.qkv_a = qkv_a + size_t(t) * NA; m.gamma_q_a = L.gamma_q_a; m.gamma_kv_a = L.gamma_kv_a;
+            m.w_q_b = L.w_q_b; m.w_kv_b = L.w_kv_b; m.cos_table = a->cos_table; m.sin_table = a->sin_table;
+            m.pos = a->pos_rows + t; m.pool = L.k_pool; m.block_table = a->block_table; m.out = attn + size_t(t) * NO;
+            m.q_lat = a->q_lat_buf; m.q_rope = a->q_rope_buf; m.part_o = a->part_o; m.part_ml = a->part_ml;
+            m.heads = NH; m.q_lora = a->q_lora; m.kv_lora = a->kv_lora; m.nope = a->nope; m.rope = a->rope; m.v = a->v;
+            m.page_size = a->page_size; m.table_len = a->table_len; m.max_ctx = a->max_ctx; m.max_pos = a->max_pos;
+            m.scale = a->scale; m.lora_eps = a->lora_eps; m.pdl = pdl; m.no_early_rows = 1;
+            if ((rc = tfb_mla_latent_decode(&m, stream))) return rc;
+        }
+        if ((rc = project(L.w_o, attn, hid, hid, H, NO, false))) return rc;
+        if ((rc = norm(L.gamma_post))) return rc;
+        if ((rc = project(L.w_gate, nrm, nullptr, a->act_buf, I, H, true))) return rc;
+        if ((rc = project(L.w_down, a->act_buf, hid, hid, H, I, false))) return rc;
+    }
+    return TFB_OK;
 }
 
 int tfb_minicpm3_decode_step(const tfb_minicpm3_step_args* a, tfb_stream_t stream) {

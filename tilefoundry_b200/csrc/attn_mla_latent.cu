@@ -174,7 +174,10 @@ __global__ void __launch_bounds__(kLatThreads) mla_latent_attn_kernel(const MlaL
     const bool active = pos >= 0 && pos < p.max_ctx && split < n_active;
     const int n = active ? min(p0 + kLatSplit, total) - p0 : 0;
     const int n_cached = active ? min(p0 + kLatSplit, pos) - p0 : 0;      // all but this token's own row
-    for (int c = tid; c < n_cached * PIECES; c += kLatThreads) {
+    // (a chunk of prompt tokens runs this kernel once per token in one dependency chain: rows of the chunk's earlier
+    // tokens may still be on their way then, so nothing is fetched ahead of the wait)
+    const int n_early = p.no_early_rows ? 0 : n_cached;
+    for (int c = tid; c < n_early * PIECES; c += kLatThreads) {
         const int r = c / PIECES, piece = c % PIECES, pp = p0 + r;
         const size_t row = size_t(p.block_table[pp / p.page_size]) * p.page_size + (pp % p.page_size);
         lat_cp16(&kv[r][piece * 8], p.pool + row * kLatRow + piece * 8);
@@ -184,6 +187,11 @@ __global__ void __launch_bounds__(kLatThreads) mla_latent_attn_kernel(const MlaL
     trace_waited(p.trace);
     if (!active) { lat_cp_wait(); return; }
 
+    for (int c = tid; c < (n_cached - n_early) * PIECES; c += kLatThreads) {
+        const int r = n_early + c / PIECES, piece = c % PIECES, pp = p0 + r;
+        const size_t row = size_t(p.block_table[pp / p.page_size]) * p.page_size + (pp % p.page_size);
+        lat_cp16(&kv[r][piece * 8], p.pool + row * kLatRow + piece * 8);
+    }
     if (n > n_cached && tid < PIECES) {            // the row appended by the kernel before this one
         const size_t row = size_t(p.block_table[pos / p.page_size]) * p.page_size + (pos % p.page_size);
         lat_cp16(&kv[n_cached][tid * 8], p.pool + row * kLatRow + tid * 8);

@@ -129,7 +129,11 @@ __device__ __forceinline__ void tc_finish_row(const TcParams& p, TcSmemTail* t, 
     for (int m = 0; m < 32; ++m)
         if (m < p.M) {
             float o = acc[m];
-            if (p.residual) o = bf16_bits_to_f32(p.residual[size_t(m) * p.N + n]) + round_bf16(acc[m]);
+            if (p.residual) {                              // TFB_EPI_RESIDUAL's rounding: bf16(acc), bf16(. * scale), then the add
+                float t = round_bf16(acc[m]);
+                if (p.res_scale != 1.f) t = round_bf16(t * p.res_scale);
+                o = bf16_bits_to_f32(p.residual[size_t(m) * p.N + n]) + t;
+            }
             p.y[size_t(m) * p.N + n] = f32_to_bf16_bits(o);
         }
 }
@@ -159,7 +163,11 @@ __device__ __forceinline__ void tc_finish_quad(const TcParams& p, int tile, int 
         const int n = tile * TC_BM + 4 * q + i;
         if (n < p.N) {
             float o = a[i];
-            if (p.residual) o = bf16_bits_to_f32(p.residual[size_t(m) * p.N + n]) + round_bf16(a[i]);
+            if (p.residual) {
+                float t = round_bf16(a[i]);
+                if (p.res_scale != 1.f) t = round_bf16(t * p.res_scale);
+                o = bf16_bits_to_f32(p.residual[size_t(m) * p.N + n]) + t;
+            }
             p.y[size_t(m) * p.N + n] = f32_to_bf16_bits(o);
         }
     }

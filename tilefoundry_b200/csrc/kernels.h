@@ -158,6 +158,7 @@ struct MlaLatentParams {
     uint16_t* out;               // [heads][v]
     uint16_t* latent_new_out;    // optional [kv_lora + rope]
     int heads, q_lora, page_size, max_ctx, nsplit;
+    int no_early_rows;           // 1: fetch no cache row ahead of the dependency wait (rows may still be in flight)
     float scale, lora_eps;
     unsigned long long* trace;   // debug timeline record of the launch this copy of the parameters goes to
     unsigned long long* trace3[3];
@@ -350,6 +351,7 @@ struct TcParams {
     unsigned* status;            // u32, set non-zero if a bounded wait gave up
     int M, N, K, ksteps, splits;
     int swiglu;                  // 1: w holds [gate rows; up rows] (2N rows), y[M][N] = bf16(silu(bf16 g)) * bf16 u
+    float res_scale;             // with residual: y = residual + bf16(bf16(acc) * res_scale) (1: no multiply)
 };
 int gemm_tc_splits(int n, int k);
 int gemm_tc_splits_swiglu(int n, int k);

@@ -17,13 +17,23 @@ from . import paged_kv
 from .session import DecodeSession
 
 
+def split_gate_up(layer: dict) -> dict:
+    """``w_gate`` / ``w_up`` as views of the layer's ``w_gate_up`` block (gate rows, then up rows)."""
+    inter = layer["w_gate_up"].shape[0] // 2
+    layer["w_gate"], layer["w_up"] = layer["w_gate_up"][:inter], layer["w_gate_up"][inter:]
+    return layer
+
+
 def pack_layer(w: dict) -> dict:
-    """Authored ``(1, in, out)`` -> ``[out, in]``; q_a and kv_a fused along the output axis."""
+    """Authored ``(1, in, out)`` -> ``[out, in]``; q_a and kv_a fused along the output axis, gate and up rows in
+    one block (the chunked prompt path runs them as one tensor-core projection; the decode step reads the two
+    halves through the ``w_gate`` / ``w_up`` views)."""
     t = lambda name: w[name][0].t().contiguous()
     out = {n: w[n].contiguous() for n in ("gamma_in", "gamma_q_a", "gamma_kv_a", "gamma_post")}
     out.update(w_qkv_a=torch.cat([t("w_q_a"), t("w_kv_a")], dim=0).contiguous(), w_q_b=t("w_q_b"),
-               w_kv_b=t("w_kv_b"), w_o=t("w_o"), w_gate=t("w_gate"), w_up=t("w_up"), w_down=t("w_down"))
-    return out
+               w_kv_b=t("w_kv_b"), w_o=t("w_o"), w_gate_up=torch.cat([t("w_gate"), t("w_up")], dim=0).contiguous(),
+               w_down=t("w_down"))
+    return split_gate_up(out)
 
 
 LAYER_WEIGHTS = ("gamma_in", "w_q_a", "gamma_q_a", "w_q_b", "w_kv_a", "gamma_kv_a", "w_kv_b", "w_o",
@@ -42,7 +52,9 @@ def pack_model(cfg: MiniCPM3Config, resource, device=None):
     layers = []
     for i in range(cfg.num_hidden_layers):
         sub = resource.subtree(f"layer{i}")
-        layers.append(pack_layer({n: to(sub.load(n)) for n in LAYER_WEIGHTS}))
+        layer = pack_layer({n: to(sub.load(n)) for n in LAYER_WEIGHTS})
+        del layer["w_gate"], layer["w_up"]                      # views of w_gate_up: re-made where the block lands
+        layers.append(layer)
     return PackedModel("minicpm3_4b", root, layers)
 
 
@@ -66,7 +78,7 @@ class MiniCPM3Session(DecodeSession):
         self.w_embed = packed.root["w_embed"]
         self.w_head = self.w_embed if packed.root["w_head"] is None else packed.root["w_head"]
         self.gamma_final = packed.root["gamma_final"]
-        self.layers = [dict(layer) for layer in packed.layers]
+        self.layers = [split_gate_up(dict(layer)) for layer in packed.layers]
 
         cos, sin = rope_tables(cfg, "cpu")
         self.max_pos = min(cfg.max_position_embeddings, self.max_ctx)
@@ -152,3 +164,37 @@ class MiniCPM3Session(DecodeSession):
 
     def step(self) -> None:
         lib.check(lib.load().tfb_minicpm3_decode_step(C.byref(self.args), lib.stream()), "tfb_minicpm3_decode_step")
+
+    def prefill(self, n_tokens: int) -> None:
+        """Process positions ``pos .. pos + n_tokens - 1`` of the token history in chunks of up to 32 tokens
+        (projections once per chunk on the tensor cores, attention token by token over the latent cache) instead of
+        one decode step each, and advance the position.  Nothing is picked.  Latent cache only."""
+        from .minicpm3_prefill import MiniCPM3Prefill
+        if self.cache != "latent":
+            raise ValueError("chunked prompt processing is built for the latent cache")
+        if getattr(self, "_prefill", None) is None:
+            self._prefill = MiniCPM3Prefill(self)
+        self._prefill.run(n_tokens)
+
+    def generate(self, prompt_ids, max_new: int, use_graph: bool = True, prefill: bool = False, eos=None):
+        """As DecodeSession.generate; with ``prefill`` the prompt (all but its last token) is processed in chunks."""
+        if not prefill:
+            return super().generate(prompt_ids, max_new, use_graph, eos)
+        from .session import Generated
+        if eos is not None:
+            self.set_eos(eos)
+        self.reset(prompt_ids)
+        if self.n_prompt + max_new > self.max_ctx + 1:
+            raise ValueError(f"{self.n_prompt}+{max_new} tokens exceed capacity {self.max_ctx}")
+        if use_graph and self.graph is None:
+            self.capture()
+        start, mid, end = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        start.record()
+        self.prefill(self.n_prompt - 1)
+        mid.record()
+        self.run(max_new, use_graph)
+        end.record()
+        torch.cuda.synchronize()
+        self._prefill.check_status()
+        out = self.tokens[self.n_prompt: self.generated_end(self.n_prompt + max_new)].tolist()
+        return Generated(out, mid.elapsed_time(end) / 1e3, start.elapsed_time(mid) / 1e3, self.n_prompt)

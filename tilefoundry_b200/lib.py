@@ -75,7 +75,7 @@ class GemvChainArgs(C.Structure):
 
 class GemmSmallMArgs(C.Structure):
     _fields_ = [("w", _vp), ("x", _vp), ("residual", _vp), ("y", _vp), ("partial", _vp), ("tickets", _vp), ("status", _vp),
-                ("m", _i32), ("n", _i32), ("k", _i32), ("pdl", _i32), ("swiglu", _i32)]
+                ("m", _i32), ("n", _i32), ("k", _i32), ("pdl", _i32), ("swiglu", _i32), ("res_scale", _f32)]
 
 
 class Qwen3BatchLayer(C.Structure):
@@ -150,6 +150,18 @@ class MiniCPM3StepArgs(C.Structure):
                 ("cache_layout", _i32), ("reserved_layout", _i32), ("q_lat_buf", _vp), ("q_rope_buf", _vp)]
 
 
+class MiniCPM3PrefillArgs(C.Structure):
+    _fields_ = [("layers", C.POINTER(MiniCPM3Layer)),
+                ("n_layers", _i32), ("m", _i32), ("hidden", _i32), ("heads", _i32), ("q_lora", _i32), ("kv_lora", _i32),
+                ("nope", _i32), ("rope", _i32), ("v", _i32), ("inter", _i32), ("vocab", _i64),
+                ("eps", _f32), ("lora_eps", _f32), ("scale", _f32), ("embed_scale", _f32), ("residual_scale", _f32),
+                ("pdl", _i32), ("w_embed", _vp), ("cos_table", _vp), ("sin_table", _vp),
+                ("max_pos", _i32), ("page_size", _i32), ("table_len", _i32), ("max_ctx", _i32),
+                ("block_table", _vp), ("ids", _vp), ("pos_rows", _vp),
+                ("hidden_buf", _vp), ("norm_buf", _vp), ("qkv_a_buf", _vp), ("attn_buf", _vp), ("act_buf", _vp),
+                ("q_lat_buf", _vp), ("q_rope_buf", _vp), ("part_o", _vp), ("part_ml", _vp), ("status", _vp)]
+
+
 class MlaLatentArgs(C.Structure):
     _fields_ = [("qkv_a", _vp), ("gamma_q_a", _vp), ("gamma_kv_a", _vp), ("w_q_b", _vp), ("w_kv_b", _vp),
                 ("cos_table", _vp), ("sin_table", _vp), ("pos", _vp), ("rope_pos", _vp), ("pool", _vp),
@@ -157,7 +169,7 @@ class MlaLatentArgs(C.Structure):
                 ("part_o", _vp), ("part_ml", _vp), ("heads", _i32), ("q_lora", _i32), ("kv_lora", _i32),
                 ("nope", _i32), ("rope", _i32), ("v", _i32), ("page_size", _i32), ("table_len", _i32),
                 ("max_ctx", _i32), ("max_pos", _i32), ("scale", _f32), ("lora_eps", _f32), ("pdl", _i32),
-                ("reserved", _i32)]
+                ("no_early_rows", _i32)]
 
 
 MLA_CACHE_ASSEMBLED, MLA_CACHE_LATENT = 0, 1
@@ -282,6 +294,7 @@ SYMBOLS = {
     "tfb_qwen3_step_xbuf_words": (_i64, [_i32, _i32, _i32, _i32, _i32]),
     "tfb_attn_mla_decode": (_i32, [C.POINTER(AttnMlaArgs), _vp]),
     "tfb_mla_latent_decode": (_i32, [C.POINTER(MlaLatentArgs), _vp]),
+    "tfb_minicpm3_prefill_chunk": (_i32, [C.POINTER(MiniCPM3PrefillArgs), _vp]),
     "tfb_mla_latent_splits": (_i32, [_i32]),
     "tfb_minicpm3_decode_step": (_i32, [C.POINTER(MiniCPM3StepArgs), _vp]),
     "tfb_residual_add": (_i32, [_vp, _vp, _vp, _i32, _f32, _vp]),
