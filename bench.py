@@ -664,13 +664,14 @@ def run_ours(args):
         # prompt processing, outside the metric: the 64-token prompt walked one decode step per token against the same
         # prompt in chunks of 32 tokens on the tensor-core projections (Qwen3 only)
         prompt_info = batch32 = None
-        if world == 1 and work.key == "qwen3_1_7b" and not args.no_sides:
+        if world == 1 and hasattr(sess, "prefill") and not args.no_sides:
             walk = sess.generate(prompt, 4)
             sess.generate(prompt, 4, prefill=True)                                  # warm-up: buffers, tensor maps
             chunked = sess.generate(prompt, 4, prefill=True)
             prompt_info = {"tokens": PROMPT_TOKENS, "walk_ms": walk.prompt_seconds * 1e3,
                            "chunked_prefill_ms": chunked.prompt_seconds * 1e3,
                            "same_continuation": walk.tokens == chunked.tokens}
+        if world == 1 and work.key == "qwen3_1_7b" and not args.no_sides:
             try:
                 batch32 = batch32_summary(work, dev, sess, min(K, 2048))
             except Exception as exc:                      # a side measurement: it must not cost the headline line

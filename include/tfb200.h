@@ -413,6 +413,11 @@ typedef struct {
     int32_t pdl;
     int32_t no_early_rows;    /* 1: fetch no cache row before the dependency wait (set when rows below *pos may have been
                                * written by a launch that is still in the same dependency chain, as in a prompt chunk) */
+    /* tokens > 1: a chunk of consecutive tokens of one sequence in the same three launches.  qkv_a is then
+     * [tokens][q_lora+kv_lora+rope], pos (and rope_pos) [tokens], out [tokens][heads*v], latent_new_out
+     * [tokens][kv_lora+rope], and every scratch buffer tokens times as long; all rows are appended by the first launch,
+     * then token t attends to the rows up to pos[t].  no_early_rows must be set.  0 or 1: one token. */
+    int32_t tokens, reserved;
 } tfb_mla_latent_args;
 TFB_API int tfb_mla_latent_decode(const tfb_mla_latent_args* args, tfb_stream_t stream);
 TFB_API int32_t tfb_mla_latent_splits(int32_t max_ctx);
@@ -489,11 +494,11 @@ TFB_API int tfb_minicpm3_decode_step(const tfb_minicpm3_step_args* args, tfb_str
 
 /* ---- a chunk of up to 32 consecutive prompt tokens through the MiniCPM3 stack (latent cache) ----------------
  * Every projection streams its weights once per chunk on the tensor cores (tfb_gemm_small_m); the attention of the
- * chunk's tokens runs token by token (tfb_mla_latent_decode with pos = pos_rows + t: each token appends its latent
- * row, then attends to the rows up to its own).  Nothing is picked.  Needs the gate and up projections of a layer
+ * chunk runs as one tfb_mla_latent_decode with tokens = m (every token appends its latent row, then token t attends
+ * to the rows up to its own).  Nothing is picked.  Needs the gate and up projections of a layer
  * as one [2*inter, hidden] block (layers[i].w_up == layers[i].w_gate + inter*hidden elements) and
- * layers[i].k_pool = the latent pool.  Scratch as for the decode step with cache_layout TFB_MLA_CACHE_LATENT, the
- * row buffers m times as long.  Replaces the prompt loop of tests/models/orchestrator/causal_lm/generation.py:56-61
+ * layers[i].k_pool = the latent pool.  Scratch as for the decode step with cache_layout TFB_MLA_CACHE_LATENT, every
+ * buffer m times as long.  Replaces the prompt loop of tests/models/orchestrator/causal_lm/generation.py:56-61
  * for this model. */
 typedef struct {
     const tfb_minicpm3_layer* layers;

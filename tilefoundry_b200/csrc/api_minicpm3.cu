@@ -46,6 +46,7 @@ int tfb_mla_latent_decode(const tfb_mla_latent_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->qkv_a && a->gamma_q_a && a->gamma_kv_a && a->w_q_b && a->w_kv_b, TFB_EINVAL);
     TFB_REQUIRE(a->cos_table && a->sin_table && a->pos && a->pool && a->block_table && a->out, TFB_EINVAL);
     TFB_REQUIRE(a->q_lat && a->q_rope && a->part_o && a->part_ml, TFB_EINVAL);
+    TFB_REQUIRE(a->tokens >= 0 && a->tokens <= 32 && (a->tokens <= 1 || a->no_early_rows), TFB_EINVAL);
     TFB_REQUIRE(a->page_size > 0 && a->table_len > 0 && a->max_ctx > 0, TFB_EINVAL);
     TFB_REQUIRE(tfb::mla_latent_supported(a->heads, a->q_lora, a->kv_lora, a->nope, a->rope, a->v, a->max_ctx), TFB_EINVAL);
     TFB_REQUIRE((long long)a->page_size * a->table_len >= a->max_ctx && a->max_pos >= a->max_ctx, TFB_ECAPACITY);
@@ -67,6 +68,8 @@ int tfb_mla_latent_decode(const tfb_mla_latent_args* a, tfb_stream_t stream) {
     p.heads = a->heads; p.q_lora = a->q_lora; p.page_size = a->page_size; p.max_ctx = a->max_ctx;
     p.nsplit = tfb::mla_latent_splits(a->max_ctx);
     p.scale = a->scale; p.lora_eps = a->lora_eps; p.no_early_rows = a->no_early_rows != 0;
+    p.tokens = a->tokens > 1 ? a->tokens : 1;
+    p.qkv_stride = a->q_lora + a->kv_lora + a->rope;
     for (int i = 0; i < 3; ++i) p.trace3[i] = next_trace();
     return done(tfb::mla_latent_dispatch(p, S(stream), a->pdl != 0));
 }
@@ -108,16 +111,16 @@ int tfb_minicpm3_prefill_chunk(const tfb_minicpm3_prefill_args* a, tfb_stream_t 
         int rc = norm(L.gamma_in);
         if (rc) return rc;
         if ((rc = project(L.w_qkv_a, nrm, nullptr, qkv_a, NA, H, false))) return rc;
-        for (int t = 0; t < M; ++t) {                        // token t appends its latent row, then attends to rows <= its own
+        {                                                    // every token appends its latent row, then token t attends to rows <= its own
             tfb_mla_latent_args m;
             std::memset(&m, 0, sizeof m);
-            m.qkv_a = qkv_a + size_t(t) * NA; m.gamma_q_a = L.gamma_q_a; m.gamma_kv_a = L.gamma_kv_a;
+            m.qkv_a = qkv_a; m.gamma_q_a = L.gamma_q_a; m.gamma_kv_a = L.gamma_kv_a;
             m.w_q_b = L.w_q_b; m.w_kv_b = L.w_kv_b; m.cos_table = a->cos_table; m.sin_table = a->sin_table;
-            m.pos = a->pos_rows + t; m.pool = L.k_pool; m.block_table = a->block_table; m.out = attn + size_t(t) * NO;
+            m.pos = a->pos_rows; m.pool = L.k_pool; m.block_table = a->block_table; m.out = attn;
             m.q_lat = a->q_lat_buf; m.q_rope = a->q_rope_buf; m.part_o = a->part_o; m.part_ml = a->part_ml;
             m.heads = NH; m.q_lora = a->q_lora; m.kv_lora = a->kv_lora; m.nope = a->nope; m.rope = a->rope; m.v = a->v;
             m.page_size = a->page_size; m.table_len = a->table_len; m.max_ctx = a->max_ctx; m.max_pos = a->max_pos;
-            m.scale = a->scale; m.lora_eps = a->lora_eps; m.pdl = pdl; m.no_early_rows = 1;
+            m.scale = a->scale; m.lora_eps = a->lora_eps; m.pdl = pdl; m.no_early_rows = 1; m.tokens = M;
             if ((rc = tfb_mla_latent_decode(&m, stream))) return rc;
         }
         if ((rc = project(L.w_o, attn, hid, hid, H, NO, false))) return rc;

@@ -41,8 +41,25 @@ __device__ __forceinline__ void lat_cp16(void* smem_dst, const void* gsrc) {
 __device__ __forceinline__ void lat_cp_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // ---- 1. q_b rows + absorption of W_UK / RoPE / latent append --------------------------------------------------
+// A launch may carry several tokens of one sequence (a prompt chunk): the last grid axis is the token, each with its
+// own position word, input row and scratch; one token (decode) is the same code with that axis 1 long.
+__device__ __forceinline__ MlaLatentParams for_token(const MlaLatentParams& q, int tok) {
+    MlaLatentParams p = q;
+    p.qkv_a += size_t(tok) * q.qkv_stride;
+    p.pos += tok;
+    if (p.rope_pos) p.rope_pos += tok;
+    p.q_lat += size_t(tok) * q.heads * 2 * kKvl;
+    p.q_rope += size_t(tok) * q.heads * kRope;
+    p.part_o += size_t(tok) * q.heads * q.nsplit * kKvl;
+    p.part_ml += size_t(tok) * q.heads * q.nsplit * 2;
+    p.out += size_t(tok) * q.heads * kVd;
+    if (p.latent_new_out) p.latent_new_out += size_t(tok) * kLatRow;
+    return p;
+}
+
 template <int QC>                                  // q_lora = 256 * QC
-__global__ void __launch_bounds__(kLatThreads) mla_q_absorb_kernel(const MlaLatentParams p) {
+__global__ void __launch_bounds__(kLatThreads) mla_q_absorb_kernel(const MlaLatentParams pq) {
+    const MlaLatentParams p = for_token(pq, blockIdx.z);
     constexpr int QL = 256 * QC;
     __shared__ float xs[QL];
     __shared__ float red[32];
@@ -155,7 +172,8 @@ __global__ void __launch_bounds__(kLatThreads) mla_q_absorb_kernel(const MlaLate
 // ---- 2. attention of 4 heads over 32 latent rows ----------------------------------------------------------------
 constexpr int kLatHG = 4;
 
-__global__ void __launch_bounds__(kLatThreads) mla_latent_attn_kernel(const MlaLatentParams p) {
+__global__ void __launch_bounds__(kLatThreads) mla_latent_attn_kernel(const MlaLatentParams pq) {
+    const MlaLatentParams p = for_token(pq, blockIdx.z);
     constexpr int HG = kLatHG;
     __shared__ __align__(16) uint16_t kv[kLatSplit][kLatPad];
     __shared__ __align__(16) float qf[HG][kLatRow];
@@ -273,7 +291,8 @@ __global__ void __launch_bounds__(kLatThreads) mla_latent_attn_kernel(const MlaL
 constexpr int kLatMaxSplits = 1024;                // 32,768 positions
 constexpr int kVaThreads = 512;
 
-__global__ void __launch_bounds__(kVaThreads) mla_v_absorb_kernel(const MlaLatentParams p) {
+__global__ void __launch_bounds__(kVaThreads) mla_v_absorb_kernel(const MlaLatentParams pq) {
+    const MlaLatentParams p = for_token(pq, blockIdx.y);
     __shared__ float w[kLatMaxSplits];
     __shared__ __align__(16) float ol[2][kKvl];
     __shared__ float red[32];
@@ -371,7 +390,8 @@ cudaError_t mla_latent_dispatch(const MlaLatentParams& params, cudaStream_t stre
     MlaLatentParams p = params;
     p.trace = p.trace3[0];
     cudaError_t e;
-    const dim3 block(kLatThreads), g1(3, p.heads);
+    const int T = p.tokens > 0 ? p.tokens : 1;
+    const dim3 block(kLatThreads), g1(3, p.heads, T);
     switch (p.q_lora / 256) {
         case 1: e = launch_kernel(mla_q_absorb_kernel<1>, g1, block, 0, stream, pdl, p); break;
         case 2: e = launch_kernel(mla_q_absorb_kernel<2>, g1, block, 0, stream, pdl, p); break;
@@ -381,10 +401,10 @@ cudaError_t mla_latent_dispatch(const MlaLatentParams& params, cudaStream_t stre
     }
     if (e != cudaSuccess) return e;
     p.trace = p.trace3[1];
-    e = launch_kernel(mla_latent_attn_kernel, dim3(p.heads / kLatHG, p.nsplit), block, 0, stream, pdl, p);
+    e = launch_kernel(mla_latent_attn_kernel, dim3(p.heads / kLatHG, p.nsplit, T), block, 0, stream, pdl, p);
     if (e != cudaSuccess) return e;
     p.trace = p.trace3[2];
-    return launch_kernel(mla_v_absorb_kernel, dim3(p.heads), dim3(kVaThreads), 0, stream, pdl, p);
+    return launch_kernel(mla_v_absorb_kernel, dim3(p.heads, T), dim3(kVaThreads), 0, stream, pdl, p);
 }
 
 }  // namespace tfb

@@ -159,6 +159,7 @@ struct MlaLatentParams {
     uint16_t* latent_new_out;    // optional [kv_lora + rope]
     int heads, q_lora, page_size, max_ctx, nsplit;
     int no_early_rows;           // 1: fetch no cache row ahead of the dependency wait (rows may still be in flight)
+    int tokens, qkv_stride;      // tokens of one sequence in this launch (prompt chunk; 0 or 1: one) and elements between their qkv_a rows
     float scale, lora_eps;
     unsigned long long* trace;   // debug timeline record of the launch this copy of the parameters goes to
     unsigned long long* trace3[3];

@@ -2,8 +2,8 @@
 
 The reference walks a prompt one token at a time (``tests/models/orchestrator/causal_lm/generation.py:56-61``).
 Here up to 32 consecutive prompt tokens go through the layer stack together: every projection streams its weights
-once per chunk on the tensor cores; the attention of the chunk's tokens runs token by token over the latent cache
-(each token appends its latent row and attends to the rows up to its own).  The cache rows and the position the
+once per chunk on the tensor cores; the chunk's attention is one launch of each latent-attention kernel with the
+token as a grid axis (every token appends its latent row, then each attends to the rows up to its own).  The cache rows and the position the
 session ends with are those of the token-by-token walk.
 """
 from __future__ import annotations
@@ -30,6 +30,12 @@ class MiniCPM3Prefill:
         self.qkv_a, self.attn, self.act = z(CHUNK, NA), z(CHUNK, NH * VD), z(CHUNK, I)
         self.status = z(1, dtype=i32)
         self.pos_rows = z(CHUNK, dtype=i32)
+        f32 = torch.float32
+        nsplit = lib.load().tfb_mla_latent_splits(sess.max_ctx)
+        KVL, R = cfg.kv_lora_rank, cfg.qk_rope_head_dim
+        # the chunk's tokens attend in ONE launch of each latent-attention kernel: scratch per token
+        self.q_lat, self.q_rope = z(CHUNK, NH * 2 * KVL, dtype=f32), z(CHUNK, NH * R, dtype=f32)
+        self.part_o, self.part_ml = z(CHUNK, NH * nsplit * KVL, dtype=f32), z(CHUNK, NH * nsplit * 2, dtype=f32)
         a = sess.args
         self.args = lib.MiniCPM3PrefillArgs(
             layers=sess._layer_structs, n_layers=len(sess.layers), m=CHUNK, hidden=H, heads=NH, q_lora=cfg.q_lora_rank,
@@ -40,12 +46,12 @@ class MiniCPM3Prefill:
             table_len=sess.table.shape[1], max_ctx=sess.max_ctx, block_table=lib.ptr(sess.table), ids=None,
             pos_rows=lib.ptr(self.pos_rows), hidden_buf=lib.ptr(self.hidden), norm_buf=lib.ptr(self.norm),
             qkv_a_buf=lib.ptr(self.qkv_a), attn_buf=lib.ptr(self.attn), act_buf=lib.ptr(self.act),
-            q_lat_buf=lib.ptr(sess.q_lat), q_rope_buf=lib.ptr(sess.q_rope), part_o=lib.ptr(sess.part_o),
-            part_ml=lib.ptr(sess.part_ml), status=lib.ptr(self.status))
+            q_lat_buf=lib.ptr(self.q_lat), q_rope_buf=lib.ptr(self.q_rope), part_o=lib.ptr(self.part_o),
+            part_ml=lib.ptr(self.part_ml), status=lib.ptr(self.status))
 
     def launches(self, m: int) -> int:
-        """Kernels one chunk of *m* tokens enqueues: embed + per layer 2 norms, 4 projections, 3 per token."""
-        return 1 + (6 + 3 * m) * len(self.sess.layers)
+        """Kernels one chunk enqueues: embed + per layer 2 norms, 4 projections, 3 of the latent attention."""
+        return 1 + 9 * len(self.sess.layers)
 
     def run(self, n_tokens: int) -> None:
         """Positions ``pos .. pos + n_tokens - 1`` of the session's token history; one host read of the position."""

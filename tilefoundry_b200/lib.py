@@ -169,7 +169,7 @@ class MlaLatentArgs(C.Structure):
                 ("part_o", _vp), ("part_ml", _vp), ("heads", _i32), ("q_lora", _i32), ("kv_lora", _i32),
                 ("nope", _i32), ("rope", _i32), ("v", _i32), ("page_size", _i32), ("table_len", _i32),
                 ("max_ctx", _i32), ("max_pos", _i32), ("scale", _f32), ("lora_eps", _f32), ("pdl", _i32),
-                ("no_early_rows", _i32)]
+                ("no_early_rows", _i32), ("tokens", _i32), ("reserved", _i32)]
 
 
 MLA_CACHE_ASSEMBLED, MLA_CACHE_LATENT = 0, 1
