@@ -43,10 +43,18 @@ namespace {
 constexpr int kCW = 12;                          // consumer warps
 constexpr int kCT = kCW * 32;                    // consumer threads
 constexpr int kFusedThreads = kCT + 32;          // + the producer warp (warp 0)
-constexpr int kSliceLen = 1024;                  // K elements one warp keeps in registers
-constexpr int kTileBytes = kCW * kSliceLen * 2;  // 24 KB
-constexpr int kStages = 8;
-constexpr int kTileBatch = 8;                     // tiles a consumer warp takes between two barriers
+constexpr int kSliceLen = 1024;                  // K elements of a weight row in one tile
+constexpr int kGroupRows = 16;                   // weight rows of a tile, and of one accumulator (8 tensor-memory lanes each)
+constexpr int kRowBytes = kSliceLen * 2;         // a tile row: 2 KB, one bulk copy
+constexpr int kTileBytes = kGroupRows * kRowBytes;   // 32 KB
+constexpr int kStages = 6;
+constexpr int kChunkBytes = 256;                 // of every tile row, what one MMA consumes (128 elements)
+constexpr int kAccBufs = 4;                      // accumulators in flight between the MMA thread and the epilogue warps
+constexpr int kAccCols = 32;                     // tensor-memory columns per hand-over: 16 per issuing thread
+constexpr int kTmemCols = kAccBufs * kAccCols;
+constexpr int kEpiWarps = 4;                     // consumer warps 0..3 read tensor memory (one lane quadrant each)
+constexpr int kMmaWarp = 4;                      // first of the consumer warps whose lane 0 issues MMAs
+constexpr int kMmaThreads = 2;                   // ... each takes its share of every tile's chunks, into its own accumulator
 constexpr unsigned long long kWaitNs = 200ull * 1000 * 1000;   // every wait gives up after 0.2 s
 constexpr int kD = 128, kGQ = 2;                 // head dim and query heads per KV head of this build
 constexpr int kBatchRows = 8;                    // cache rows one warp holds in registers at a time
@@ -56,7 +64,10 @@ struct FusedSmem {
     alignas(128) unsigned char ring[kStages][kTileBytes];
     alignas(8) unsigned long long full[kStages];
     unsigned long long empty[kStages];
-    float part[2][kTileBatch][kCW];
+    unsigned long long acc_full[kAccBufs], acc_empty[kAccBufs], mma_done;
+    uint32_t tmem_base;
+    float head_v[kEpiWarps];                     // the epilogue warps' best logit and its row, for the pick
+    int head_i[kEpiWarps];
     float red[16];
     alignas(16) float q[kGQ][kD];
     alignas(16) float knew[kD];
@@ -94,11 +105,6 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;"
 __device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
     unsigned v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ uint4 lds16(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
 
@@ -204,23 +210,43 @@ struct RingPos {
     __device__ __forceinline__ void next() {
         if (++stage == kStages) { stage = 0; parity ^= 1u; }
     }
+    __device__ __forceinline__ void advance(int n) {
+        const int t = stage + n;
+        stage = t % kStages;
+        parity ^= unsigned(t / kStages) & 1u;
+    }
 };
 
+// A CTA's rows of a matrix are taken in groups of at most `cap` units (rows, or gate/up pairs), evenly sized.
+__device__ __forceinline__ void groups_of(int units, int cap, int& ng, int& per) {
+    ng = (units + cap - 1) / cap;
+    per = ng > 0 ? (units + ng - 1) / ng : 0;
+}
+
 // ---- producer: the tiles of one matrix phase, in the order the consumers take them ------------------------------
+// A tile is kSliceLen consecutive K elements of up to kGroupRows rows, one 2 KB bulk copy per row (lane r copies
+// tile row r); gate/up phases interleave the rows: tile row 2i is gate row i of the group, 2i + 1 its up row.
 __device__ __forceinline__ void produce(FusedSmem& s, RingPos& rp, const uint16_t* w, const uint16_t* w2, int n, int k,
-                                        int c, int G, unsigned* status) {
-    const int KS = k / kSliceLen, R = kCW / KS;
-    const int U = w2 ? R / 2 : R;                            // output units (rows, or gate/up row pairs) per tile
-    int u0, u1;
+                                        int c, int G, int lane, unsigned* status) {
+    const int KT = k / kSliceLen;
+    int u0, u1, ng, per;
     span(n, c, G, u0, u1);
-    for (int u = u0; u < u1; u += U) {
-        const int nu = min(U, u1 - u);
-        wait_bar(s, &s.empty[rp.stage], rp.parity ^ 1u, status, 0x10000u);
-        const unsigned bytes = unsigned(nu) * unsigned(k) * 2u;
-        mb_expect_tx(&s.full[rp.stage], w2 ? 2u * bytes : bytes);
-        bulk_load(s.ring[rp.stage], w + size_t(u) * k, bytes, &s.full[rp.stage]);
-        if (w2) bulk_load(s.ring[rp.stage] + size_t(U) * k * 2, w2 + size_t(u) * k, bytes, &s.full[rp.stage]);
-        rp.next();
+    groups_of(u1 - u0, w2 ? kGroupRows / 2 : kGroupRows, ng, per);
+    for (int g = 0; g < ng; ++g) {
+        const int u = u0 + g * per, nu = min(per, u1 - u);
+        const int nrows = w2 ? 2 * nu : nu;
+        const uint16_t* src = w;
+        if (lane < nrows) src = w2 ? ((lane & 1) ? w2 : w) + size_t(u + (lane >> 1)) * k : w + size_t(u + lane) * k;
+        for (int kt = 0; kt < KT; ++kt) {
+            if (lane == 0) {
+                wait_bar(s, &s.empty[rp.stage], rp.parity ^ 1u, status, 0x10000u);
+                mb_expect_tx(&s.full[rp.stage], unsigned(nrows) * kRowBytes);
+            }
+            __syncwarp();
+            if (lane < nrows)
+                bulk_load(s.ring[rp.stage] + lane * kRowBytes, src + kt * kSliceLen, kRowBytes, &s.full[rp.stage]);
+            rp.next();
+        }
     }
 }
 
@@ -231,33 +257,106 @@ struct HeadBest {
     int i;
 };
 
+// ---- tensor-core pieces of the matrix phases ---------------------------------------------------------------------
+// Batch 1 has no N dimension to give the MMA, so K is FOLDED into it.  A K-major operand without swizzle is made of core
+// matrices of 8 rows x 16 bytes, each 128 contiguous bytes.  Read 256 contiguous bytes of a weight row (128 elements)
+// as ONE 8 x 16 block -- "row" r, column 8h + c is element h * 64 + r * 8 + c (two core matrices, 128 bytes apart along
+// K) -- and let the stride between 8-row groups be the pitch of the tile's rows: the A operand of an M = 128 MMA is then
+// the same 128-element chunk of 16 weight rows, straight from the row-major tile.  The B operand is the matching chunk
+// of the activation vector, folded the same way (8 x 16; N = 16 is the least M = 128 takes, the second eight are never
+// read).  D[8g + r][r'] = sum over (h, c) of W[g][(r, h, c)] * x[(r', h, c)]: the diagonal r = r' of each 8 x 8 block
+// carries the products that belong together, and successive chunks ACCUMULATE in tensor memory, so after k / 128 MMAs
+// row g's dot product is D[8g][0] + D[8g + 1][1] + ... + D[8g + 7][7].  Seven of eight products are thrown away, and
+// the tensor core still takes 4 KB of weights every ~50 cycles, four times what HBM delivers to one SM: the CUDA cores
+// (64 unpack + multiply-add instructions per 2 KB per warp, and a barrier per handful of rows) did not keep up.
+__device__ __forceinline__ uint64_t folded_desc(uint32_t smem_addr, uint32_t group_pitch) {
+    uint64_t d = 0;
+    d |= uint64_t((smem_addr & 0x3FFFF) >> 4);               // start address, 16-byte units
+    d |= uint64_t(128 >> 4) << 16;                            // byte offset between core matrices along K
+    d |= uint64_t(group_pitch >> 4) << 32;                    // byte offset between 8-row groups
+    d |= uint64_t(1) << 46;                                   // descriptor version of this architecture
+    return d;                                                  // (layout type 0: no swizzle)
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_arrive(unsigned long long* bar) {     // arrives when every MMA issued so far is done
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(s_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+// D f32, A and B bf16, both K-major, N = 16, M = 128
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(16 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+
+struct AccPos {                                   // which accumulator a hand-over uses, and its barrier parity
+    int buf;
+    unsigned parity;
+    __device__ __forceinline__ void next() {
+        if (++buf == kAccBufs) { buf = 0; parity ^= 1u; }
+    }
+    __device__ __forceinline__ void advance(int n) {
+        const int t = buf + n;
+        buf = t % kAccBufs;
+        parity ^= unsigned(t / kAccBufs) & 1u;
+    }
+};
+
+// The dot product of the weight row that this lane's team of eight lanes holds in the accumulators of hand-over `buf`
+// (row i of an M = 128 accumulator sits in tensor-memory lane i; lane l of the quadrant wants column l % 8 of each).  Every lane of a team
+// returns the row's sum (a fixed shuffle tree: deterministic).  `release` is arrived on as soon as the load has landed.
+__device__ __forceinline__ float team_dot(uint32_t tmem, int buf, int quad, int lane, unsigned long long* release) {
+    uint32_t v[8], w[8];
+    const uint32_t taddr = tmem + (uint32_t(quad * 32) << 16) + uint32_t(buf * kAccCols);
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+                 : "r"(taddr + uint32_t(kAccCols / kMmaThreads)) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mb_arrive(release);                        // this warp has read the accumulators
+    const bool b4 = lane & 4, b2 = lane & 2, b1 = lane & 1;
+    const uint32_t t0 = b4 ? v[4] : v[0], t1 = b4 ? v[5] : v[1], t2 = b4 ? v[6] : v[2], t3 = b4 ? v[7] : v[3];
+    const uint32_t s0 = b4 ? w[4] : w[0], s1 = b4 ? w[5] : w[1], s2 = b4 ? w[6] : w[2], s3 = b4 ? w[7] : w[3];
+    const uint32_t q0 = b2 ? t2 : t0, q1 = b2 ? t3 : t1, r0 = b2 ? s2 : s0, r1 = b2 ? s3 : s1;
+    float d = __uint_as_float(b1 ? q1 : q0) + __uint_as_float(b1 ? r1 : r0);      // the two issuing threads' halves
+    d += __shfl_xor_sync(0xffffffffu, d, 1);
+    d += __shfl_xor_sync(0xffffffffu, d, 2);
+    d += __shfl_xor_sync(0xffffffffu, d, 4);
+    return d;
+}
+
 // ---- consumers: one matrix phase --------------------------------------------------------------------------------
 // y = epilogue(W . prologue(x)) for this CTA's rows.  x: tagged words, complete when every tag is in_tag; y: tagged
 // words written with out_tag (the head writes plain bf16 logits to y_plain instead).
 template <int KIND, bool NORM>
-__device__ __forceinline__ void consume(FusedSmem& s, RingPos& rp, const FusedParams& p, int n, int k,
+__device__ __forceinline__ void consume(FusedSmem& s, RingPos& rp, AccPos& ap, const FusedParams& p, int n, int k,
                                         const unsigned* x, unsigned in_tag, const uint16_t* gamma, unsigned* y,
                                         unsigned out_tag, uint16_t* y_plain, uint16_t* trace_row,
                                         int c, int G, int cw, int lane, HeadBest* best, int ph) {
-    const int KS = k / kSliceLen, R = kCW / KS;
-    const int U = KIND == kSwiglu ? R / 2 : R;
-    const int r = cw / KS, j = cw % KS;
-    int u0, u1;
+    const int KT = k / kSliceLen;
+    int u0, u1, ng, per;
     span(n, c, G, u0, u1);
+    groups_of(u1 - u0, KIND == kSwiglu ? kGroupRows / 2 : kGroupRows, ng, per);
+    const int tid = cw * 32 + lane;
+    const int nvec = k >> 2;                                  // <= 4 * kCT (k <= 6144)
 
-    // norm gains are weights: ask for them before the wait
-    uint4 gv[4];
+    // norm gains are weights: ask for the ones of this thread's pieces before the wait
+    uint2 gv[4];
     if (NORM) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) gv[q] = *reinterpret_cast<const uint4*>(gamma + j * kSliceLen + q * 256 + lane * 8);
+        for (int i = 0; i < 4; ++i)
+            gv[i] = tid + i * kCT < nvec ? *reinterpret_cast<const uint2*>(gamma + 4 * (tid + i * kCT)) : make_uint2(0u, 0u);
     }
-    const int tid = cw * 32 + lane;
     if (tid == 0) tl_enter(p, ph);
     // The activation vector: each tagged word is fetched by exactly one thread of the CTA, polled until its tag says
-    // this phase's input has landed, and parked as bf16 in shared memory (the attention scratch, idle here).
+    // this phase's input has landed, normalised where the phase asks for it, and parked as bf16 in shared memory (the
+    // attention scratch, idle here) in natural order: the MMAs' other operand.
     uint16_t* xs = reinterpret_cast<uint16_t*>(&s.wo[0][0][0]);
     {
-        const int nvec = k >> 2;                              // <= 4 * kCT (k <= 6144)
         uint4 w[4];
         int spins = 0;
         for (;;) {                                            // (a thread without an i-th piece re-reads its first)
@@ -268,129 +367,118 @@ __device__ __forceinline__ void consume(FusedSmem& s, RingPos& rp, const FusedPa
             for (int i = 0; i < 4; ++i) ok = ok && tags_ok(w[i], in_tag);
             if (ok || poll_expired(s, spins, p.status, 0x100u)) break;
         }
-        float ss = 0.f;
+        float rstd = 1.f;
+        if (NORM) {
+            float ss = 0.f;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            if (tid + i * kCT < nvec) {
-                *reinterpret_cast<uint2*>(xs + 4 * (tid + i * kCT)) =
-                    make_uint2((w[i].x & 0xffffu) | (w[i].y << 16), (w[i].z & 0xffffu) | (w[i].w << 16));
-                if (NORM) {
+            for (int i = 0; i < 4; ++i) {
+                if (tid + i * kCT < nvec) {
                     const float a = bf16_lo(w[i].x), b = bf16_lo(w[i].y), cc = bf16_lo(w[i].z), d = bf16_lo(w[i].w);
                     ss = fmaf(a, a, ss); ss = fmaf(b, b, ss); ss = fmaf(cc, cc, ss); ss = fmaf(d, d, ss);
                 }
             }
-        }
-        if (NORM) {
             ss = warp_sum(ss);
             if (lane == 0) s.red[cw] = ss;
+            consumer_sync();
+            float tot = 0.f;
+#pragma unroll
+            for (int q = 0; q < kCW; ++q) tot += s.red[q];
+            rstd = rsqrtf(tot / float(k) + p.eps);
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (tid + i * kCT < nvec) {
+                uint32_t lo = (w[i].x & 0xffffu) | (w[i].y << 16), hi = (w[i].z & 0xffffu) | (w[i].w << 16);
+                if (NORM) {                                   // Qwen3RMSNorm: round, then gain (a bf16 multiply)
+                    const float a = round_bf16(round_bf16(bf16_lo(w[i].x) * rstd) * bf16_lo(gv[i].x));
+                    const float b = round_bf16(round_bf16(bf16_lo(w[i].y) * rstd) * bf16_hi(gv[i].x));
+                    const float cc = round_bf16(round_bf16(bf16_lo(w[i].z) * rstd) * bf16_lo(gv[i].y));
+                    const float d = round_bf16(round_bf16(bf16_lo(w[i].w) * rstd) * bf16_hi(gv[i].y));
+                    lo = uint32_t(f32_to_bf16_bits(a)) | (uint32_t(f32_to_bf16_bits(b)) << 16);
+                    hi = uint32_t(f32_to_bf16_bits(cc)) | (uint32_t(f32_to_bf16_bits(d)) << 16);
+                    if (trace_row && KIND == kHead && c == 0)  // the final-normed hidden state, for the trace
+                        *reinterpret_cast<uint2*>(trace_row + 4 * (tid + i * kCT)) = make_uint2(lo, hi);
+                }
+                *reinterpret_cast<uint2*>(xs + 4 * (tid + i * kCT)) = make_uint2(lo, hi);
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // these writes are read by the MMAs (async proxy)
     }
     consumer_sync();
     if (tid == 0) tl_waited(p, ph);
 
-    // this warp's K-slice of the activation vector, in registers for the whole phase
-    float xf[32];
+    const uint32_t tmem = s.tmem_base;
+    RingPos r = rp;
+    AccPos a = ap;
+    if (cw >= kMmaWarp && cw < kMmaWarp + kMmaThreads) {
+        // ---- the MMA issuers (lane 0 of two warps): a tensor-core instruction of this size occupies the pipe for ~45
+        // cycles however it is shaped, and the waits and commits around a tile cost the issuing thread as much again;
+        // two threads, each with half of every tile's chunks and an accumulator of its own, keep the pipe busy ----
+        if (lane == 0) {
+            const int j = cw - kMmaWarp;
+            constexpr int CPT = kRowBytes / kChunkBytes / kMmaThreads;          // chunks of a tile per thread
+            const uint64_t xdesc = folded_desc(s_u32(xs) + uint32_t(j * CPT * kChunkBytes), kChunkBytes);
+            for (int g = 0; g < ng; ++g) {
+                wait_bar(s, &s.acc_empty[a.buf], a.parity ^ 1u, p.status, 0x40000u);
+                tc_fence_after();
+                const uint32_t d_tmem = tmem + uint32_t(a.buf * kAccCols + j * (kAccCols / kMmaThreads));
+                for (int kt = 0; kt < KT; ++kt) {
+                    wait_bar(s, &s.full[r.stage], r.parity, p.status, 0x20000u);
+                    const uint64_t da = folded_desc(s_u32(s.ring[r.stage]) + uint32_t(j * CPT * kChunkBytes), kRowBytes);
+                    const uint64_t db = xdesc + uint64_t((kt * kRowBytes) >> 4);
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        const uint4 xv = *reinterpret_cast<const uint4*>(xs + j * kSliceLen + q * 256 + lane * 8);
-        const uint32_t u[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { xf[q * 8 + 2 * i] = bf16_lo(u[i]); xf[q * 8 + 2 * i + 1] = bf16_hi(u[i]); }
-    }
-    // the residual of this CTA's rows (at most 32), one per lane of the finishing warp, ahead of the tile loop
-    // (written by this CTA itself in an earlier phase; whatever tag it carries)
-    float res = 0.f;
-    if (KIND == kResidual && cw == 0 && u0 + lane < u1) res = bf16_lo(ld_relaxed32(y + u0 + lane));
-    if (NORM) {
-        float tot = 0.f;
-#pragma unroll
-        for (int q = 0; q < kCW; ++q) tot += s.red[q];
-        const float rstd = rsqrtf(tot / float(k) + p.eps);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const uint32_t g[4] = {gv[q].x, gv[q].y, gv[q].z, gv[q].w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {                     // Qwen3RMSNorm: round, then gain (a bf16 multiply)
-                xf[q * 8 + 2 * i] = round_bf16(round_bf16(xf[q * 8 + 2 * i] * rstd) * bf16_lo(g[i]));
-                xf[q * 8 + 2 * i + 1] = round_bf16(round_bf16(xf[q * 8 + 2 * i + 1] * rstd) * bf16_hi(g[i]));
-            }
-        }
-        if (trace_row && c == 0 && r == 0) {                  // the final-normed hidden state, for the trace
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-#pragma unroll
-                for (int i = 0; i < 8; ++i) trace_row[j * kSliceLen + q * 256 + lane * 8 + i] = f32_to_bf16_bits(xf[q * 8 + i]);
-        }
-    }
-
-    // Tiles are taken kTileBatch at a time: the chain wait -> shared loads -> multiply-adds -> warp reduction ->
-    // barrier -> epilogue is latency, not work (the step ran no faster with the weight loads taken out), so one
-    // barrier and one epilogue serve several tiles.  A batch never holds more rows than a warp has lanes.
-    const int NB = min(kTileBatch, 32 / U);
-    const int fb = lane / U, frr = lane % U;                      // the epilogue's lane = (tile of the batch, row of the tile)
-    int buf = 0;
-    for (int u = u0; u < u1; u += NB * U) {
-#pragma unroll 1
-        for (int b = 0; b < NB; ++b) {                             // (not unrolled: the kernel's code has to stay small)
-            const int ub = u + b * U;
-            if (ub >= u1) break;                                   // (the same for every thread of the CTA)
-            const int nu = min(U, u1 - ub);
-            wait_bar(s, &s.full[rp.stage], rp.parity, p.status, 0x20000u);
-            const bool valid = KIND == kSwiglu ? (r % U) < nu : r < nu;
-            float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
-            if (valid) {
-                const uint32_t base = s_u32(s.ring[rp.stage]) + uint32_t(r) * uint32_t(k) * 2u + uint32_t(j) * (kSliceLen * 2) + lane * 16;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const uint4 w = lds16(base + q * 512);
-                    const float4 xa = make_float4(xf[q * 8], xf[q * 8 + 1], xf[q * 8 + 2], xf[q * 8 + 3]);
-                    const float4 xb = make_float4(xf[q * 8 + 4], xf[q * 8 + 5], xf[q * 8 + 6], xf[q * 8 + 7]);
-                    if (q == 0) acc0 = dot8(w, xa, xb, acc0);
-                    else if (q == 1) acc1 = dot8(w, xa, xb, acc1);
-                    else if (q == 2) acc2 = dot8(w, xa, xb, acc2);
-                    else acc3 = dot8(w, xa, xb, acc3);
+                    for (int t = 0; t < CPT; ++t)
+                        umma_f16(d_tmem, da + uint64_t((t * kChunkBytes) >> 4), db + uint64_t((t * kChunkBytes) >> 4), kIdesc,
+                                 (kt | t) != 0 ? 1u : 0u);
+                    umma_arrive(&s.empty[r.stage]);               // the stage is free when the MMAs that read it are done
+                    r.next();
                 }
+                umma_arrive(&s.acc_full[a.buf]);
+                a.next();
             }
-            __syncwarp();
-            if (lane == 0) mb_arrive(&s.empty[rp.stage]);          // this warp has read its part of the stage
-            rp.next();
-            const float sum = warp_sum((acc0 + acc1) + (acc2 + acc3));
-            if (lane == 0) s.part[buf][b][cw] = sum;
         }
-        consumer_sync();
-        if (cw == 0) {                                             // K-slices added in fixed order, epilogue: lane = (tile, row)
-            const int b = fb, rr = frr, row = u + b * U + rr;
-            const bool live = b < NB && row < u1;
-            float v = 0.f, v2 = 0.f;
-            if (live) {
-                for (int q = 0; q < KS; ++q) {
-                    v += s.part[buf][b][rr * KS + q];
-                    if (KIND == kSwiglu) v2 += s.part[buf][b][(rr + U) * KS + q];
-                }
-            }
+        __syncwarp();
+    } else if (cw < kEpiWarps) {
+        // ---- the epilogue warps: a team of eight lanes per weight row, four rows per warp, no step across warps ----
+        const int quad = (cw + 1) & 3;                        // the tensor-memory lane quadrant this warp may read
+        const int trow = quad * 4 + (lane >> 3);              // the tile row of this lane's team
+        const int unit = KIND == kSwiglu ? trow >> 1 : trow;  // (gate/up: tile rows 2i and 2i + 1 make unit i)
+        const bool writer = KIND == kSwiglu ? (lane & 15) == 0 : (lane & 7) == 0;
+        for (int g = 0; g < ng; ++g) {
+            const int u = u0 + g * per, nu = min(per, u1 - u);
+            const int row = u + unit;
+            const bool live = writer && unit < nu;
+            float res = 0.f;                                   // (written by this CTA itself in an earlier phase)
+            if (KIND == kResidual && live) res = bf16_lo(ld_relaxed32(y + row));
+            wait_bar(s, &s.acc_full[a.buf], a.parity, p.status, 0x80000u);
+            tc_fence_after();
+            const float v = team_dot(tmem, a.buf, quad, lane, &s.acc_empty[a.buf]);
             if (KIND == kStore) {
                 if (live) st_tagged(y + row, out_tag, f32_to_bf16_bits(v));
             } else if (KIND == kSwiglu) {
-                const float g = round_bf16(v), up = round_bf16(v2);
-                if (live) st_tagged(y + row, out_tag, f32_to_bf16_bits(round_bf16(silu_f32(g)) * up));
+                const float up = round_bf16(__shfl_xor_sync(0xffffffffu, v, 8));
+                if (live) st_tagged(y + row, out_tag, f32_to_bf16_bits(round_bf16(silu_f32(round_bf16(v))) * up));
             } else if (KIND == kHead) {
                 const float sc = round_bf16(v);
                 if (live) {
                     if (y_plain) y_plain[row] = f32_to_bf16_bits(sc);
                     if (sc > best->v || (sc == best->v && row < best->i)) { best->v = sc; best->i = row; }
                 }
-            } else {                                               // residual (all lanes shuffle: it sits in another lane)
-                const float mine = __shfl_sync(0xffffffffu, res, (row - u0) & 31);
+            } else {
                 if (live) {
-                    const uint16_t out = f32_to_bf16_bits(mine + round_bf16(v));
+                    const uint16_t out = f32_to_bf16_bits(res + round_bf16(v));
                     st_tagged(y + row, out_tag, out);
                     if (trace_row) trace_row[row] = out;
                 }
             }
+            a.next();
         }
-        buf ^= 1;
     }
-    consumer_sync();                                            // (protects s.red / s.part / xs against the next phase)
+    // every thread tracks the ring and the accumulators, whatever its role in this phase
+    rp.advance(ng * KT);
+    ap.advance(ng);
+    consumer_sync();                                            // (every MMA of the phase is complete: its accumulator was
+                                                                //  waited for; s.red / xs may be reused)
     if (tid == 0) tl_done(p, ph);
 }
 
@@ -686,24 +774,31 @@ __global__ void __launch_bounds__(kFusedThreads, 1) qwen3_step_kernel(const Fuse
     unsigned long long* const xpart = reinterpret_cast<unsigned long long*>(xact + ((p.inter + 1) & ~1));   // split partials
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kStages; ++i) { mb_init(&s.full[i], 1); mb_init(&s.empty[i], kCW); }
+        for (int i = 0; i < kStages; ++i) { mb_init(&s.full[i], 1); mb_init(&s.empty[i], kMmaThreads); }
+        for (int i = 0; i < kAccBufs; ++i) { mb_init(&s.acc_full[i], kMmaThreads); mb_init(&s.acc_empty[i], kEpiWarps); }
+        mb_init(&s.mma_done, kMmaThreads);
         s.abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (warp == 1 + kMmaWarp) {                                     // tensor memory for the accumulators
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(s_u32(&s.tmem_base)), "n"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
     __syncthreads();
+    tc_fence_after();
 
     if (warp == 0) {
-        // ---- producer: every weight tile of the step, in consumption order ----
-        if (lane != 0) return;
+        // ---- producer: every weight tile of the step, in consumption order (lane r: row r of every tile) ----
         RingPos rp{0, 0};
         for (int l = 0; l < L; ++l) {
             const FusedLayer Ly = p.layers[l];
-            produce(s, rp, Ly.w_qkv, nullptr, NQKV, H, c, G, p.status);
-            produce(s, rp, Ly.w_o, nullptr, H, QP, c, G, p.status);
-            produce(s, rp, Ly.w_gate, Ly.w_up, p.inter, H, c, G, p.status);
-            produce(s, rp, Ly.w_down, nullptr, H, p.inter, c, G, p.status);
+            produce(s, rp, Ly.w_qkv, nullptr, NQKV, H, c, G, lane, p.status);
+            produce(s, rp, Ly.w_o, nullptr, H, QP, c, G, lane, p.status);
+            produce(s, rp, Ly.w_gate, Ly.w_up, p.inter, H, c, G, lane, p.status);
+            produce(s, rp, Ly.w_down, nullptr, H, p.inter, c, G, lane, p.status);
         }
-        produce(s, rp, p.w_head, nullptr, p.vocab, H, c, G, p.status);
+        produce(s, rp, p.w_head, nullptr, p.vocab, H, c, G, lane, p.status);
         return;
     }
 
@@ -711,6 +806,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) qwen3_step_kernel(const Fuse
     const int cw = warp - 1;
     const int tid = cw * 32 + lane;
     RingPos rp{0, 0};
+    AccPos ap{0, 0};
     {   // where this CTA's attention rows sit in every layer's pools (same split arithmetic as attend())
         const int total = pos + 1, ns_max = min(G / p.hkv, 64);
         const int SL = max(16, ((total + ns_max - 1) / ns_max + 15) & ~15), NS = (total + SL - 1) / SL;
@@ -735,26 +831,51 @@ __global__ void __launch_bounds__(kFusedThreads, 1) qwen3_step_kernel(const Fuse
     for (int l = 0; l < L; ++l) {
         const FusedLayer& Ly = p.layers[l];
         const int ph = 1 + 5 * l;
-        consume<kStore, true>(s, rp, p, NQKV, H, xh, tag(hidden_ph), Ly.gamma_in, xqkv, tag(ph), nullptr, nullptr,
+        consume<kStore, true>(s, rp, ap, p, NQKV, H, xh, tag(hidden_ph), Ly.gamma_in, xqkv, tag(ph), nullptr, nullptr,
                               c, G, cw, lane, nullptr, ph);
         attend(s, p, Ly, xqkv, tag(ph), xattn, tag(ph + 1), xpart, pos, c, G, cw, lane, ph + 1);
-        consume<kResidual, false>(s, rp, p, H, QP, xattn, tag(ph + 1), nullptr, xh, tag(ph + 2), nullptr, nullptr,
+        consume<kResidual, false>(s, rp, ap, p, H, QP, xattn, tag(ph + 1), nullptr, xh, tag(ph + 2), nullptr, nullptr,
                                   c, G, cw, lane, nullptr, ph + 2);
-        consume<kSwiglu, true>(s, rp, p, p.inter, H, xh, tag(ph + 2), Ly.gamma_post, xact, tag(ph + 3), nullptr, nullptr,
+        consume<kSwiglu, true>(s, rp, ap, p, p.inter, H, xh, tag(ph + 2), Ly.gamma_post, xact, tag(ph + 3), nullptr, nullptr,
                                c, G, cw, lane, nullptr, ph + 3);
-        consume<kResidual, false>(s, rp, p, H, p.inter, xact, tag(ph + 3), nullptr, xh, tag(ph + 4), nullptr,
+        consume<kResidual, false>(s, rp, ap, p, H, p.inter, xact, tag(ph + 3), nullptr, xh, tag(ph + 4), nullptr,
                                   p.hidden_trace ? p.hidden_trace + size_t(l) * H : nullptr, c, G, cw, lane, nullptr, ph + 4);
         hidden_ph = ph + 4;
     }
     HeadBest best{-INFINITY, 0x7fffffff};
-    consume<kHead, true>(s, rp, p, p.vocab, H, xh, tag(hidden_ph), p.gamma_final, nullptr, 0u, p.logits,
+    consume<kHead, true>(s, rp, ap, p, p.vocab, H, xh, tag(hidden_ph), p.gamma_final, nullptr, 0u, p.logits,
                          p.hidden_trace ? p.hidden_trace + size_t(L) * H : nullptr, c, G, cw, lane, &best, 1 + 5 * L);
-    if (cw == 0) {
-        // this CTA's (best logit, lowest index), then the pick over all CTAs by CTA 0
+    if (cw > kMmaWarp && cw < kMmaWarp + kMmaThreads && lane == 0) umma_arrive(&s.mma_done);
+    if (cw == kMmaWarp) {
+        // Tensor memory goes back once nothing can touch it: the head phase's last barrier is behind every consumer, and
+        // every MMA this CTA issued has completed (after a timeout some may still be in flight: wait for them, bounded).
+        if (lane == 0) {
+            umma_arrive(&s.mma_done);
+            const unsigned long long t0 = global_ns();
+            while (!mb_try(&s.mma_done, 0u) && global_ns() - t0 < kWaitNs) {}
+        }
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(s.tmem_base), "n"(kTmemCols) : "memory");
+    }
+    if (cw < kEpiWarps) {                                           // each epilogue warp's (best logit, lowest index)
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, best.v, o);
             const int oi = __shfl_xor_sync(0xffffffffu, best.i, o);
+            if (ov > best.v || (ov == best.v && oi < best.i)) { best.v = ov; best.i = oi; }
+        }
+        if (lane == 0) { s.head_v[cw] = best.v; s.head_i[cw] = best.i; }
+    }
+    consumer_sync();
+    if (cw == 0) {
+        // this CTA's best, then the pick over all CTAs by CTA 0
+        best.v = s.head_v[0];
+        best.i = s.head_i[0];
+#pragma unroll
+        for (int q = 1; q < kEpiWarps; ++q) {
+            const float ov = s.head_v[q];
+            const int oi = s.head_i[q];
             if (ov > best.v || (ov == best.v && oi < best.i)) { best.v = ov; best.i = oi; }
         }
         if (lane == 0) {
@@ -813,10 +934,10 @@ int fused_step_splits(int hkv) { const int s = sm_count() / (hkv > 0 ? hkv : 1);
 bool fused_step_supported(const FusedParams& p) {
     const int QP = p.hq * kD;
     // (k <= 6144: an activation vector is staged as bf16 in the 12 KB attention scratch, four 16-byte pieces per thread)
-    auto ok_k = [](int k) { return k >= kSliceLen && k % kSliceLen == 0 && kCW % (k / kSliceLen) == 0 && k <= 4 * 4 * kCT; };
+    auto ok_k = [](int k) { return k >= kSliceLen && k % kSliceLen == 0 && k <= 4 * 4 * kCT; };
     const int G = sm_count();
     return p.n_layers >= 1 && p.n_layers <= kFusedMaxLayers && p.d == kD && p.hkv >= 1 && p.hq == kGQ * p.hkv &&
-           ok_k(p.hidden) && ok_k(QP) && ok_k(p.inter) && (kCW / (p.hidden / kSliceLen)) % 2 == 0 &&
+           ok_k(p.hidden) && ok_k(QP) && ok_k(p.inter) &&
            p.hidden <= 32 * G && p.hkv <= G && p.inter >= 1 && p.vocab >= 1 && p.xbuf != nullptr;
 }
 
