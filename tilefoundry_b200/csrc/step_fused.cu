@@ -44,10 +44,14 @@ constexpr int kCW = 12;                          // consumer warps
 constexpr int kCT = kCW * 32;                    // consumer threads
 constexpr int kFusedThreads = kCT + 32;          // + the producer warp (warp 0)
 constexpr int kSliceLen = 1024;                  // K elements of a weight row in one tile
-constexpr int kGroupRows = 16;                   // weight rows of a tile, and of one accumulator (8 tensor-memory lanes each)
+constexpr int kGroupRows = 16;                   // weight rows one accumulator has room for (8 tensor-memory lanes each)
+#ifndef TFB_GROUP_CAP
+#define TFB_GROUP_CAP 14
+#endif
+constexpr int kGroupCap = TFB_GROUP_CAP;         // ... and how many a tile takes (even; 2048 / 148 = 13.8 rows fit one tile)
 constexpr int kRowBytes = kSliceLen * 2;         // a tile row: 2 KB, one bulk copy
-constexpr int kTileBytes = kGroupRows * kRowBytes;   // 32 KB
-constexpr int kStages = 6;
+constexpr int kTileBytes = kGroupCap * kRowBytes;
+constexpr int kStages = (210 * 1024) / kTileBytes;   // seven 28 KB stages
 constexpr int kChunkBytes = 256;                 // of every tile row, what one MMA consumes (128 elements)
 constexpr int kAccBufs = 4;                      // accumulators in flight between the MMA thread and the epilogue warps
 constexpr int kAccCols = 32;                     // tensor-memory columns per hand-over: 16 per issuing thread
@@ -224,14 +228,14 @@ __device__ __forceinline__ void groups_of(int units, int cap, int& ng, int& per)
 }
 
 // ---- producer: the tiles of one matrix phase, in the order the consumers take them ------------------------------
-// A tile is kSliceLen consecutive K elements of up to kGroupRows rows, one 2 KB bulk copy per row (lane r copies
+// A tile is kSliceLen consecutive K elements of up to kGroupCap rows, one 2 KB bulk copy per row (lane r copies
 // tile row r); gate/up phases interleave the rows: tile row 2i is gate row i of the group, 2i + 1 its up row.
 __device__ __forceinline__ void produce(FusedSmem& s, RingPos& rp, const uint16_t* w, const uint16_t* w2, int n, int k,
                                         int c, int G, int lane, unsigned* status) {
     const int KT = k / kSliceLen;
     int u0, u1, ng, per;
     span(n, c, G, u0, u1);
-    groups_of(u1 - u0, w2 ? kGroupRows / 2 : kGroupRows, ng, per);
+    groups_of(u1 - u0, w2 ? kGroupCap / 2 : kGroupCap, ng, per);
     for (int g = 0; g < ng; ++g) {
         const int u = u0 + g * per, nu = min(per, u1 - u);
         const int nrows = w2 ? 2 * nu : nu;
@@ -340,7 +344,7 @@ __device__ __forceinline__ void consume(FusedSmem& s, RingPos& rp, AccPos& ap, c
     const int KT = k / kSliceLen;
     int u0, u1, ng, per;
     span(n, c, G, u0, u1);
-    groups_of(u1 - u0, KIND == kSwiglu ? kGroupRows / 2 : kGroupRows, ng, per);
+    groups_of(u1 - u0, KIND == kSwiglu ? kGroupCap / 2 : kGroupCap, ng, per);
     const int tid = cw * 32 + lane;
     const int nvec = k >> 2;                                  // <= 4 * kCT (k <= 6144)
 
