@@ -199,9 +199,9 @@ def _graph_time(launches, n_launches, reps=10):
 
 
 #: dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from one ncu capture
-#: (profiles/qwen3_step_kernel_qwen3_1_7b.md: the one-launch step at context 1087: 3.56695 GB read + 21.15 MB written);
+#: (profiles/qwen3_step_kernel_qwen3_1_7b.md: the one-launch step at context 1087: 3.569 GB read + 20.1 MB written);
 #: None where no capture was taken for that configuration.
-NCU_TRAFFIC = {"qwen3_1_7b": 3566950000 + 21147648}
+NCU_TRAFFIC = {"qwen3_1_7b": 3569151000 + 20059392}
 
 
 def dominant_kernel(work, sess):

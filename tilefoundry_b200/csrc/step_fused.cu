@@ -4,19 +4,19 @@
 //
 // Why one launch: as separate launches the step is bound by the chain of dependent launches (about 4 us of
 // release + activation staging + first-byte latency + tail per kernel, five per layer), not by bytes.  Here the
-// weight stream never stops at a dependency: weights do not depend on activations, so one producer thread per
-// CTA walks a STATIC schedule of 24 KB tiles (contiguous rows of the [out, in] matrices) through all phases of
-// all layers and lands them in a 192 KB shared-memory ring with bulk asynchronous copies (cp.async.bulk,
-// mbarrier transaction counts), as far ahead of the arithmetic as the ring allows.  While the consumer warps
-// wait for an activation vector, the ring -- nearly empty in steady state, because shared memory is read several
-// times faster than HBM fills it -- takes up to 4 us of HBM traffic.
+// weight stream never stops at a dependency: weights do not depend on activations, so the producer warp of a CTA
+// walks a STATIC schedule of tiles through all phases of all layers and lands them in a 196 KB shared-memory ring
+// with bulk asynchronous copies (cp.async.bulk, mbarrier transaction counts), as far ahead of the arithmetic as
+// the ring allows.  While the consumer warps wait for an activation vector, the ring takes up to 4.5 us of HBM
+// traffic.
 //
-// Data layout: matrix rows are dealt to the CTAs in contiguous blocks (CTA c owns rows [c*n/G, (c+1)*n/G));
-// a tile is 12 K-slices of 1024 elements: 12/KS rows of a k = KS*1024 wide matrix (gate/up: half gate rows, half
-// the matching up rows).  Each of the 12 consumer warps owns one (row, K-slice) of every tile and keeps its
-// slice of the activation vector in registers for the whole phase, so a tile costs it four 16-byte shared
-// loads per lane.  Slice sums meet in shared memory in fixed order (deterministic); rounding points are those
-// of gemv_kernel / attn_gqa_kernel / lm_head_kernel.
+// Data layout: matrix rows are dealt to the CTAs in contiguous blocks (CTA c owns rows [c*n/G, (c+1)*n/G)), taken
+// in groups of at most 14 rows (gate/up: 7 row pairs, interleaved); a tile is 1024 consecutive K elements of a
+// group's rows, 2 KB per row.  The dot products run on the tensor cores although the batch is one: K is folded
+// into the MMA's N (see "tensor-core pieces" below), one tcgen05.mma per 16 rows x 128 elements, accumulating over
+// a group's tiles in tensor memory; four epilogue warps read the accumulators back, a team of eight lanes per
+// row.  Everything is summed in a fixed order (deterministic); rounding points are those of gemv_kernel /
+// attn_gqa_kernel / lm_head_kernel.
 //
 // Dependencies between phases travel WITH the data: every activation element is a 32-bit word, bf16 value in
 // the low half and a 16-bit tag in the high half that names the launch and the phase that wrote it.  A consumer
@@ -28,8 +28,8 @@
 // zero is never a tag), and a word is rewritten only after every reader of its old value has produced something
 // that the writer has already consumed (the data dependences of the step guarantee it).
 // Attention: KV head h, split s of the context on CTA s*hkv + h (the context is cut into at most G/hkv splits,
-// so no CTA has two); cached K/V rows are requested before this token's q|k|v is waited on; the last split of
-// a KV head to finish (a ticket, with fences) merges the partials.  Every wait is bounded: a timeout sets
+// so no CTA has two); cached K/V rows are requested before this token's q|k|v is waited on; split 0 of a KV
+// head merges the partials, which reach it as tagged 64-bit words.  Every wait is bounded: a timeout sets
 // *status, and every later wait of that CTA returns at once, so the launch always ends.
 //
 // HBM-bound: algorithmic bytes per launch = all weights once + the KV rows of positions [0, pos].
