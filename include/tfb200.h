@@ -317,8 +317,8 @@ typedef struct {
     /* TFB_KERNEL_FUSED: the step as ONE cooperative launch, one CTA per multiprocessor; the weight stream runs
      * through a shared-memory ring across all phases and layers; phases hand activations over as tagged 32-bit
      * words (bf16 value + 16-bit tag of launch and phase) that the consumer polls, every wait bounded.  Needs
-     * d = 128, hq = 2 hkv, hidden / hq*d / inter in {1024, 2048, 3072, 4096, 6144}, hidden in {1024, 2048, 3072,
-     * 6144}, temperature <= 0; other shapes get TFB_EINVAL.
+     * d = 128, hq = 2 hkv, hidden / hq*d / inter multiples of 1024 up to 6144; other shapes get TFB_EINVAL.  The matrix
+     * phases run on the tcgen05 tensor cores (K folded into the MMA's N); temperature > 0 samples as the head kernel does.
      *   step_layers: DEVICE copy of the layer table, n_layers x 11 pointers in tfb_qwen3_layer's field order
      *   step_sync:   uint32 [tfb_qwen3_step_sync_words(n_layers, hkv)], zeroed once (words the kernel leaves zero, the
      *                head's arrival count and a launch counter, which it advances)

@@ -345,7 +345,7 @@ def test_one_launch_step_equals_the_launch_per_kernel_step(dev):
     cfg = q.QWEN3_SMALL
     weights = _cuda(q.tie_head(random_weights(q.build(cfg), seed=2, std=0.05)), dev)
     prompt = torch.arange(7, 40)
-    a = Qwen3Session(cfg, DictResource(weights), max_ctx=260, device=dev).generate(prompt, 200).tokens
+    a = Qwen3Session(cfg, DictResource(weights), max_ctx=260, device=dev, kernel=0).generate(prompt, 200).tokens
     fused = Qwen3Session(cfg, DictResource(weights), max_ctx=260, device=dev, kernel=KERNEL_FUSED)
     b = fused.generate(prompt, 200).tokens
     c = fused.generate(prompt, 200, use_graph=False).tokens

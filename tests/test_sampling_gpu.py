@@ -133,6 +133,31 @@ def test_session_sampling_is_reproducible_and_seeded(dev):
     _expect(logits, 1.0, 42, step, one[-1])
 
 
+def test_one_launch_step_samples_with_the_same_rule(dev):
+    """The one-launch Qwen3 step draws inside its head phase: reproducible (graph or eager), keyed by the seed, and
+    every checked draw equals the CPU restatement applied to the logits the step itself wrote."""
+    from tilefoundry_b200.engine.qwen3 import KERNEL_FUSED, Qwen3Session
+    cfg = q.QWEN3_SMALL
+    weights = q.tie_head(random_weights(q.build(cfg), seed=5, std=0.05))
+    res = DictResource({k: v.to(dev) for k, v in weights.items()})
+    prompt = torch.randint(0, cfg.vocab_size, (12,), generator=torch.Generator().manual_seed(2))
+    a = Qwen3Session(cfg, res, max_ctx=128, device=dev, keep_logits=True, temperature=0.8, seed=42, kernel=KERNEL_FUSED)
+    assert a.launches_per_step == 1
+    one = a.generate(prompt, 60, use_graph=True).tokens
+    two = a.generate(prompt, 60, use_graph=False).tokens
+    a.check_status()
+    assert one == two
+    step = int(a.pos) - 1
+    _expect(a.logits.float().cpu().numpy(), 0.8, 42, step, one[-1])
+    for n_new in (1, 7, 23):                                     # a few more draws, each against the step's own logits
+        t = a.generate(prompt, n_new, use_graph=False).tokens
+        assert t == one[:len(t)]
+        _expect(a.logits.float().cpu().numpy(), 0.8, 42, int(a.pos) - 1, t[-1])
+    other = Qwen3Session(cfg, res, max_ctx=128, device=dev, temperature=0.8, seed=43, kernel=KERNEL_FUSED).generate(prompt, 60).tokens
+    greedy = Qwen3Session(cfg, res, max_ctx=128, device=dev, kernel=KERNEL_FUSED).generate(prompt, 60).tokens
+    assert other != one and greedy != one
+
+
 @pytest.mark.parametrize("model", ["minicpm3", "granite", "qwen3_5"])
 def test_other_sessions_sample_too(dev, model):
     """The other three decode steps hand temperature and seed to the same head kernel."""

@@ -354,7 +354,6 @@ int32_t tfb_qwen3_step_splits(int32_t hkv) { return hkv > 0 ? tfb::fused_step_sp
 // TFB_KERNEL_FUSED: the whole step as one cooperative launch.
 static int qwen3_fused_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a->step_layers && a->step_sync && a->step_status && a->step_xbuf, TFB_EINVAL);
-    TFB_REQUIRE(a->temperature <= 0.f, TFB_EINVAL);                        // greedy only
     TFB_REQUIRE(a->vocab > 0 && a->vocab < (1ll << 31), TFB_EINVAL);
     tfb::FusedParams p;
     std::memset(&p, 0, sizeof p);
@@ -375,6 +374,8 @@ static int qwen3_fused_step(const tfb_qwen3_step_args* a, tfb_stream_t stream) {
     p.sync = a->step_sync; p.status = a->step_status;
     p.head_val = a->head_val; p.head_idx = a->head_idx;
     p.picked = reinterpret_cast<long long*>(a->picked);
+    p.temperature = a->temperature > 0.f ? a->temperature : 0.f;
+    p.seed = a->seed;
     p.hidden_trace = static_cast<uint16_t*>(a->hidden_trace);
     TFB_REQUIRE(a->n_eos >= 0 && a->n_eos <= 16 && (a->eos_ids == nullptr || (a->stop_at && a->n_eos > 0)), TFB_EINVAL);
     p.eos_ids = reinterpret_cast<const long long*>(a->eos_ids);

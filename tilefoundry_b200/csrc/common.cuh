@@ -124,4 +124,20 @@ __device__ __forceinline__ float apply_scale(float x, float s) {
 
 __device__ __forceinline__ float silu_f32(float x) { return x / (1.f + __expf(-x)); }
 
+// Gumbel-max sampling: argmax_i(logit_i / T + G_i) with G_i = -log(-log(u_i)) is a draw from softmax(logits / T),
+// so sampling is the greedy pick over perturbed scores -- no normalisation pass.  u_i comes from a counter-based
+// generator (the splitmix64 finaliser over seed, step and the GLOBAL vocabulary index), so a vocabulary-parallel
+// head draws the same token as one GPU.  u = (k + 0.5) / 2^23 with k the top 23 bits: never 0 or 1.  The two
+// logarithms run in double precision (one lane per row, so their cost does not matter): the fast single-precision
+// log loses the tail u -> 1 where the winning variates live.
+static __device__ __noinline__ float gumbel_variate(unsigned long long seed, int step, int index) {
+    unsigned long long z = seed + 0x9E3779B97F4A7C15ull * (unsigned long long)(unsigned(index) + 1u) +
+                           0xD1B54A32D192ED03ull * (unsigned long long)(unsigned(step) + 1u);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    const double u = (double(unsigned(z >> 41)) + 0.5) * (1.0 / 8388608.0);
+    return float(-log(-log(u)));
+}
+
 }  // namespace tfb

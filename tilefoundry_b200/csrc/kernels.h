@@ -421,6 +421,8 @@ struct FusedParams {
     float* head_val;                     // [multiprocessors]
     int* head_idx;
     long long* picked;
+    float temperature;                   // > 0: Gumbel-max sample from softmax(logits / temperature); else greedy
+    unsigned long long seed;
     uint16_t* hidden_trace;
     const long long* eos_ids;            // end-of-sequence latch (nullptr: none): see tfb_lm_head_args
     int n_eos;

@@ -411,6 +411,7 @@ __device__ __forceinline__ void consume(FusedSmem& s, RingPos& rp, AccPos& ap, c
     consumer_sync();
     if (tid == 0) tl_waited(p, ph);
 
+    const int sample_step = (KIND == kHead && p.temperature > 0.f) ? *p.pos : 0;   // (the draw is keyed by the position)
     const uint32_t tmem = s.tmem_base;
     RingPos r = rp;
     AccPos a = ap;
@@ -463,9 +464,11 @@ __device__ __forceinline__ void consume(FusedSmem& s, RingPos& rp, AccPos& ap, c
                 const float up = round_bf16(__shfl_xor_sync(0xffffffffu, v, 8));
                 if (live) st_tagged(y + row, out_tag, f32_to_bf16_bits(round_bf16(silu_f32(round_bf16(v))) * up));
             } else if (KIND == kHead) {
-                const float sc = round_bf16(v);
+                float sc = round_bf16(v);
                 if (live) {
                     if (y_plain) y_plain[row] = f32_to_bf16_bits(sc);
+                    // sampling: the greedy pick over logit / T + Gumbel noise (the rule of lm_head_kernel, same variates)
+                    if (p.temperature > 0.f) sc = __fdiv_rn(sc, p.temperature) + gumbel_variate(p.seed, sample_step, row);
                     if (sc > best->v || (sc == best->v && row < best->i)) { best->v = sc; best->i = row; }
                 }
             } else {

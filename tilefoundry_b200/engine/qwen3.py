@@ -23,10 +23,9 @@ KERNEL_FUSED = 6          # TFB_KERNEL_FUSED: the whole step as one cooperative 
 
 def fused_step_supported(cfg: Qwen3Config) -> bool:
     """Shapes the one-launch step is built for (the C ABI refuses the others with TFB_EINVAL)."""
-    ok_k = lambda k: k >= 1024 and k % 1024 == 0 and 12 % (k // 1024) == 0
+    ok_k = lambda k: k >= 1024 and k % 1024 == 0 and k <= 6144
     return (cfg.head_dim == 128 and cfg.num_attention_heads == 2 * cfg.num_key_value_heads
-            and ok_k(cfg.hidden_size) and ok_k(cfg.num_attention_heads * cfg.head_dim) and ok_k(cfg.intermediate_size)
-            and cfg.hidden_size in (1024, 2048, 3072, 6144))
+            and ok_k(cfg.hidden_size) and ok_k(cfg.num_attention_heads * cfg.head_dim) and ok_k(cfg.intermediate_size))
 
 
 def pack_layer(w: dict) -> dict:
@@ -57,7 +56,7 @@ class Qwen3Session(DecodeSession):
         dev = self.device
         to = lambda t: t.to(dev)
         if kernel is None:
-            kernel = KERNEL_FUSED if fused_step_supported(cfg) and temperature <= 0.0 else 0
+            kernel = KERNEL_FUSED if fused_step_supported(cfg) else 0
 
         from .packed import PackedQwen3, pack
         # a resource speaks the authored names and is packed here; a PackedQwen3 (engine/packed.py) is already in
