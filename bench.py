@@ -502,19 +502,12 @@ def measure(work, sess, prompt, K, W, dev, rank, world, units, sample_clocks):
     # ---- end to end over the same positions: token in from pinned host memory, picked token back, every step ----
     sess.restore(snap)
     pin_in = torch.empty(1, dtype=torch.int64).pin_memory()
-    pin_out = torch.empty(1, dtype=torch.int64).pin_memory()
     pin_in[0] = int(sess.tokens[at])
     barrier()
     t0 = time.perf_counter()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
-    for i in range(K):
-        pos = at + i
-        sess.tokens[pos: pos + 1].copy_(pin_in, non_blocking=True)         # H2D: this step's input
-        sess.graph.replay()
-        pin_out.copy_(sess.tokens[pos + 1: pos + 2], non_blocking=True)    # D2H: this step's result
-        stream.synchronize()
-        pin_in[0] = pin_out[0]
+    sess.generate_host(at, K, pin_in)                   # every step: H2D its input token, the step, D2H its pick, wait
     e1.record(stream)
     barrier()
     e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3))

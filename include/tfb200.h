@@ -50,6 +50,23 @@ TFB_API const char* tfb_last_error(void);
  * (~0, ~0, 0, 0, 0, 0, 0, 0).  Pass NULL to stop.  Not for production use. */
 TFB_API int tfb_debug_trace(void* device_buffer, int32_t capacity);
 
+/* ---- one decode step with the token crossing the host -----------------------
+ * What a host-driven generation loop does around the device step, in one call: copy this step's token id from
+ * (pinned) host memory into its slot of the device token history, launch a captured step (a cudaGraphExec_t of any of
+ * the four decode steps), copy the picked token back to (pinned) host memory and wait for the stream.
+ * Stands in for one iteration of the reference's loop, which feeds `input_ids` from the host and reads the argmax
+ * back every step: tests/models/orchestrator/causal_lm/generation.py:56-77.
+ *   graph_exec: cudaGraphExec_t of the captured step        token_slot: device address of tokens[pos] (int64)
+ *   picked:     device address the step writes its pick to (tokens[pos + 1], or the step's `picked` scalar)
+ * Returns TFB_ELAUNCH with tfb_last_error() set if a CUDA call fails. */
+TFB_API int tfb_graph_step_host(void* graph_exec, void* token_slot, const int64_t* token_in_host, const void* picked,
+                                int64_t* token_out_host, tfb_stream_t stream);
+/* `steps` such iterations from position `pos`: every step feeds *token_io_host (pinned) into tokens[pos + i], launches
+ * the step, reads tokens[pos + i + 1] back into *token_io_host and waits -- the token crosses the host both ways every
+ * step, as in the reference's loop -- and appends it to out_host[i] (plain host memory, may be NULL). */
+TFB_API int tfb_graph_generate_host(void* graph_exec, void* tokens, int64_t pos, int32_t steps, int64_t* token_io_host,
+                                    int64_t* out_host, tfb_stream_t stream);
+
 /* ---- embedding row gather -------------------------------------------------
  * out[r, :] = table[ids[r], :] * scale (scale == 1 copies bits).
  * Stands in for `embed`: tests/models/qwen3_1_7b/model.py:311-318 (scale 1),

@@ -358,6 +358,38 @@ def test_one_launch_step_equals_the_launch_per_kernel_step(dev):
     assert prefix >= 8, (prefix, a[:prefix + 2], b[:prefix + 2])
 
 
+def test_host_driven_loop_gives_the_same_tokens(dev):
+    """``step_host`` -- token id in from pinned host memory, picked token back, every step, one C call -- walks the
+    prompt and continues exactly as the device-resident loop does."""
+    from tilefoundry_b200.engine.qwen3 import Qwen3Session
+    cfg = q.QWEN3_SMALL
+    weights = _cuda(q.tie_head(random_weights(q.build(cfg), seed=2, std=0.05)), dev)
+    prompt = torch.arange(7, 40)
+    sess = Qwen3Session(cfg, DictResource(weights), max_ctx=260, device=dev)
+    want = sess.generate(prompt, 50).tokens
+    sess.reset(prompt)
+    pin_in, pin_out = (torch.empty(1, dtype=torch.int64).pin_memory() for _ in range(2))
+    history = prompt.tolist()
+    pin_in[0] = history[0]
+    for pos in range(len(prompt) + 50 - 1):
+        sess.step_host(pos, pin_in, pin_out)
+        nxt = int(pin_out[0])
+        if pos + 1 < len(prompt):
+            assert nxt == history[pos + 1]                    # inside the prompt the history is left alone
+        else:
+            history.append(nxt)
+        pin_in[0] = nxt
+    sess.check_status()
+    assert history[len(prompt):] == want
+    # the same loop inside one C call, from the end of the prompt
+    sess.reset(prompt)
+    sess.run(len(prompt) - 1)
+    pin_in[0] = history[len(prompt) - 1]
+    assert sess.generate_host(len(prompt) - 1, 50, pin_in) == want
+    with pytest.raises(ValueError):
+        sess.step_host(0, torch.empty(1, dtype=torch.int64), pin_out)      # not pinned
+
+
 @pytest.mark.parametrize("kernel", [0, 6])
 def test_full_model_64_prompt_32_new_tokens(dev, kernel):
     """The CPU-runnable configuration: Qwen3-1.7B architecture, N(0, 0.02) weights, 64 random prompt

@@ -40,6 +40,29 @@ int tfb_debug_trace(void* device_buffer, int32_t capacity) {
     return TFB_OK;
 }
 
+int tfb_graph_step_host(void* graph_exec, void* token_slot, const int64_t* token_in_host, const void* picked,
+                        int64_t* token_out_host, tfb_stream_t stream) {
+    TFB_REQUIRE(graph_exec && token_slot && token_in_host && picked && token_out_host, TFB_EINVAL);
+    cudaStream_t st = S(stream);
+    cudaError_t e = cudaMemcpyAsync(token_slot, token_in_host, sizeof(int64_t), cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaGraphLaunch(static_cast<cudaGraphExec_t>(graph_exec), st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(token_out_host, picked, sizeof(int64_t), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    return done(e);
+}
+
+int tfb_graph_generate_host(void* graph_exec, void* tokens, int64_t pos, int32_t steps, int64_t* token_io_host,
+                            int64_t* out_host, tfb_stream_t stream) {
+    TFB_REQUIRE(graph_exec && tokens && token_io_host && pos >= 0 && steps >= 0, TFB_EINVAL);
+    int64_t* hist = static_cast<int64_t*>(tokens);
+    for (int32_t i = 0; i < steps; ++i) {
+        const int rc = tfb_graph_step_host(graph_exec, hist + pos + i, token_io_host, hist + pos + i + 1, token_io_host, stream);
+        if (rc != TFB_OK) return rc;
+        if (out_host) out_host[i] = *token_io_host;
+    }
+    return TFB_OK;
+}
+
 const char* tfb_status_string(int status) {
     switch (status) {
         case TFB_OK: return "ok";

@@ -6,6 +6,8 @@ from dataclasses import dataclass
 
 import torch
 
+from .. import lib
+
 
 @dataclass
 class Generated:
@@ -109,6 +111,38 @@ class DecodeSession:
         torch.cuda.synchronize()
         self.restore(saved)
         self.graph = graph
+
+    def step_host(self, pos: int, token_in: torch.Tensor, token_out: torch.Tensor) -> None:
+        """One iteration of a host-driven generation loop (the reference's ``generation.decode``): the token id in
+        ``token_in`` (pinned int64[1]) goes to ``tokens[pos]``, the captured step runs, its pick comes back in
+        ``token_out`` (pinned int64[1]); returns when the stream has finished.  One C call: two 8-byte copies, one
+        graph launch, one wait."""
+        if self.graph is None:
+            self.capture()
+        if not (0 <= pos and pos + 1 < self.tokens.numel()):
+            raise ValueError(f"position {pos} has no successor slot in a history of {self.tokens.numel()}")
+        for t in (token_in, token_out):
+            if t.is_cuda or not t.is_pinned() or t.dtype != torch.int64 or t.numel() != 1:
+                raise ValueError("token_in / token_out must be pinned host int64 tensors of one element")
+        base = self.tokens.data_ptr()
+        lib.check(lib.load().tfb_graph_step_host(int(self.graph.raw_cuda_graph_exec()), base + 8 * pos, token_in.data_ptr(),
+                                                 base + 8 * (pos + 1), token_out.data_ptr(), lib.stream()),
+                  "tfb_graph_step_host")
+
+    def generate_host(self, pos: int, steps: int, token_io: torch.Tensor) -> list:
+        """*steps* iterations of ``step_host`` from position *pos* in one C call: ``token_io`` (pinned int64[1]) holds the
+        token fed to the next step and receives each pick; the picks are returned."""
+        if self.graph is None:
+            self.capture()
+        if not (0 <= pos and pos + steps < self.tokens.numel()):
+            raise ValueError(f"positions {pos}..{pos + steps} exceed a history of {self.tokens.numel()}")
+        if token_io.is_cuda or not token_io.is_pinned() or token_io.dtype != torch.int64 or token_io.numel() != 1:
+            raise ValueError("token_io must be a pinned host int64 tensor of one element")
+        out = torch.empty(max(steps, 1), dtype=torch.int64)
+        lib.check(lib.load().tfb_graph_generate_host(int(self.graph.raw_cuda_graph_exec()), self.tokens.data_ptr(), pos, steps,
+                                                     token_io.data_ptr(), out.data_ptr(), lib.stream()),
+                  "tfb_graph_generate_host")
+        return out[:steps].tolist()
 
     def run(self, steps: int, use_graph: bool = True) -> None:
         if use_graph and self.graph is None:

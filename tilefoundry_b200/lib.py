@@ -273,6 +273,8 @@ SYMBOLS = {
     "tfb_status_string": (C.c_char_p, [_i32]),
     "tfb_last_error": (C.c_char_p, []),
     "tfb_debug_trace": (_i32, [_vp, _i32]),
+    "tfb_graph_step_host": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp]),
+    "tfb_graph_generate_host": (_i32, [_vp, _vp, _i64, _i32, _vp, _vp, _vp]),
     "tfb_embed": (_i32, [_vp, _vp, _vp, _i32, _i32, _i64, _f32, _vp]),
     "tfb_rmsnorm": (_i32, [_vp, _vp, _vp, _i32, _i32, _f32, _i32, _vp]),
     "tfb_gemv": (_i32, [C.POINTER(GemvArgs), _vp]),
