@@ -494,6 +494,19 @@ __device__ __forceinline__ size_t kv_offset(const FusedParams& p, int pos, int h
     return ((size_t(page) * p.page_size + (pos % p.page_size)) * p.hkv + h) * kD;
 }
 
+// A layer's cached K/V rows of this CTA's split (first batch: the rows of s.koff) asked into L2 well before attention
+// wants them.  A DRAM read issued when attention starts queues behind the weight stream -- every CTA keeps up to 196 KB
+// of tile copies in flight, 29 MB over the GPU, 4 us of HBM time -- and attention then sat waiting for its rows.
+// The warps that have nothing to do in the matrix phases issue the hints, one row half (128 bytes) of K and of V each.
+__device__ __forceinline__ void ask_cache_rows(const FusedSmem& s, const FusedLayer& L, int cw, int lane) {
+    if (cw < kCW / 2) return;
+    const int i = (cw - kCW / 2) * 32 + lane;                   // 0 .. 191 = kCW * kBatchRows * 2 row halves
+    const unsigned off = s.koff[i >> 4][(i >> 1) & (kBatchRows - 1)];
+    if (off == ~0u) return;
+    asm volatile("prefetch.global.L2 [%0];" :: "l"(L.k_pool + off + (i & 1) * (kD / 2)));
+    asm volatile("prefetch.global.L2 [%0];" :: "l"(L.v_pool + off + (i & 1) * (kD / 2)));
+}
+
 // ---- consumers: attention of one layer ------------------------------------------------------------------------
 __device__ __forceinline__ void attend(FusedSmem& s, const FusedParams& p, const FusedLayer& L, const unsigned* xqkv,
                                        unsigned in_tag, unsigned* xattn, unsigned out_tag, unsigned long long* xpart, int pos,
@@ -835,6 +848,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) qwen3_step_kernel(const Fuse
         if (tid == 0) tl_done(p, 0);
     }
     int hidden_ph = 0;                                             // the phase that wrote the current hidden state
+    consumer_sync();                                               // (s.koff is read across warps below)
+    ask_cache_rows(s, p.layers[0], cw, lane);
     for (int l = 0; l < L; ++l) {
         const FusedLayer& Ly = p.layers[l];
         const int ph = 1 + 5 * l;
@@ -845,6 +860,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) qwen3_step_kernel(const Fuse
                                   c, G, cw, lane, nullptr, ph + 2);
         consume<kSwiglu, true>(s, rp, ap, p, p.inter, H, xh, tag(ph + 2), Ly.gamma_post, xact, tag(ph + 3), nullptr, nullptr,
                                c, G, cw, lane, nullptr, ph + 3);
+        if (l + 1 < L) ask_cache_rows(s, p.layers[l + 1], cw, lane);   // (two phases and two hand-overs ahead of its use)
         consume<kResidual, false>(s, rp, ap, p, H, p.inter, xact, tag(ph + 3), nullptr, xh, tag(ph + 4), nullptr,
                                   p.hidden_trace ? p.hidden_trace + size_t(l) * H : nullptr, c, G, cw, lane, nullptr, ph + 4);
         hidden_ph = ph + 4;
