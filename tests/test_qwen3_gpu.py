@@ -337,6 +337,23 @@ def test_one_launch_step_matches_evaluator_small(dev, use_graph, kernel):
     assert int(sess.step_sync[:-1].abs().sum()) == 0                 # the last CTA left every ticket at zero (the last word counts launches)
 
 
+def test_one_launch_step_long_context_second_row_batch(dev):
+    """Sixteen KV heads leave nine splits of the context, so past 864 positions a split holds more rows than its
+    twelve warps take in one batch of eight: the later-batch path of the attention phase (rows located through the
+    page table, not the offsets found at launch), against the evaluator up to context 960; widths 4096 (o) and 2048
+    exercise four- and two-tile row groups."""
+    from tilefoundry_b200.engine.qwen3 import KERNEL_FUSED, fused_step_supported
+    cfg = q.Qwen3Config(hidden_size=1024, num_attention_heads=32, num_key_value_heads=16, head_dim=128,
+                        intermediate_size=2048, vocab_size=1024, num_hidden_layers=2, max_position_embeddings=1024)
+    assert fused_step_supported(cfg)
+    n_prompt, n_new = 900, 61
+    want, sess, got = _session_vs_oracle(cfg, dev, n_prompt, n_new, 13, 0.02, True, KERNEL_FUSED)
+    sess.check_status()
+    assert sess.launches_per_step == 1
+    excused = _compare_run(cfg, want, sess, got, n_prompt, n_new)
+    assert excused <= 30, f"{excused} near-tie picks out of {n_prompt + n_new - 1}"      # (same share as 8 of 163 above)
+
+
 def test_one_launch_step_equals_the_launch_per_kernel_step(dev):
     """Same session arguments, both forms of the step: the one-launch step must pick the tokens the step of
     separate launches picks (same rounding points; only summation orders differ), and replaying its graph for a
