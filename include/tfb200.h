@@ -782,6 +782,10 @@ typedef struct {
     int32_t* pick_idx;      /* i32 [batch * 8] */
     int64_t* picked;        /* optional [batch]: the token each sequence picked, whatever its prompt says */
     void* hidden_trace;     /* optional [n_layers+1][batch][hidden] bf16 */
+    float temperature;      /* > 0: every sequence samples from softmax(logits / temperature) by the Gumbel-max rule of
+                             * tfb_lm_head_args, sequence b keyed by (seed + b, its position, vocabulary index); else greedy */
+    int32_t reserved;
+    uint64_t seed;
 } tfb_qwen3_batch_step_args;
 TFB_API int tfb_qwen3_batch_decode_step(const tfb_qwen3_batch_step_args* args, tfb_stream_t stream);
 

@@ -197,6 +197,34 @@ def test_batch_generate_graph_equals_eager_and_is_idempotent(dev):
     assert [d.tokens[i] for i in range(8)] == [a.tokens[int(perm[i])] for i in range(8)]
 
 
+def test_batch_step_samples_per_sequence(dev):
+    """With a temperature the batch step's pick is the Gumbel-max rule of the head kernel, sequence b keyed by
+    seed + b: reproducible (graph or eager), different per sequence and per seed, and the last draw of every sequence
+    equals the CPU restatement applied to that sequence's logits."""
+    import numpy as np
+    from oracle import sampling
+    from tilefoundry_b200.engine.qwen3_batch import Qwen3BatchSession
+    cfg = q.QWEN3_TINY
+    weights = q.tie_head(random_weights(q.build(cfg), seed=23, std=0.05))
+    res = DictResource(_cuda(weights, dev))
+    prompts = torch.randint(0, cfg.vocab_size, (1, 16), generator=torch.Generator().manual_seed(1)).repeat(4, 1)
+    sess = Qwen3BatchSession(cfg, res, batch=4, max_ctx=200, device=dev, temperature=0.9, seed=77)
+    a = sess.generate(prompts, 40, use_graph=True).tokens
+    b = sess.generate(prompts, 40, use_graph=False).tokens
+    assert a == b
+    assert len({tuple(t) for t in a}) == 4                        # the same prompt four times: four different samples
+    step = int(sess.pos[0]) - 1
+    logits = sess.logits.float().cpu().numpy()
+    for i in range(4):
+        scores = sampling.gumbel_scores(logits[i], 0.9, 77 + i, step)
+        order = np.argsort(-scores, kind="stable")
+        assert a[i][-1] == int(order[0]) or (a[i][-1] == int(order[1]) and scores[order[0]] - scores[order[1]] < 1e-4)
+    other = Qwen3BatchSession(cfg, res, batch=4, max_ctx=200, device=dev, temperature=0.9, seed=78).generate(prompts, 40).tokens
+    greedy = Qwen3BatchSession(cfg, res, batch=4, max_ctx=200, device=dev).generate(prompts, 40).tokens
+    assert other != a and greedy != a
+    assert other[0] == a[1]                                      # seed 78 sequence 0 draws as seed 77 sequence 1 did
+
+
 def test_batch_session_rejects_bad_arguments(dev):
     from tilefoundry_b200.engine.qwen3_batch import Qwen3BatchSession
     cfg = q.QWEN3_TINY

@@ -87,7 +87,7 @@ int tfb_qwen3_batch_decode_step(const tfb_qwen3_batch_step_args* a, tfb_stream_t
     e = tfb::pick_rows_launch(static_cast<const uint16_t*>(a->logits), B, int(a->vocab),
                               reinterpret_cast<long long*>(a->tokens), a->pos, a->n_prompt, a->max_tokens,
                               reinterpret_cast<long long*>(a->picked), a->pick_val, a->pick_idx,
-                              a->counters + size_t(B) * a->hkv, st, pdl);
+                              a->counters + size_t(B) * a->hkv, a->temperature > 0.f ? a->temperature : 0.f, a->seed, st, pdl);
     return e == cudaSuccess ? TFB_OK : fail_launch(e);
 }
 

@@ -42,7 +42,8 @@ __global__ void __launch_bounds__(kPickThreads) pick_rows_kernel(const uint16_t*
                                                                  long long* __restrict__ tokens, int* __restrict__ pos,
                                                                  int n_prompt, int max_tokens, long long* __restrict__ picked,
                                                                  float* __restrict__ part_val, int* __restrict__ part_idx,
-                                                                 unsigned* __restrict__ tickets) {
+                                                                 unsigned* __restrict__ tickets, float temperature,
+                                                                 unsigned long long seed) {
     __shared__ float wv[kPickThreads / 32];
     __shared__ int wi[kPickThreads / 32];
     __shared__ int s_last;
@@ -54,8 +55,13 @@ __global__ void __launch_bounds__(kPickThreads) pick_rows_kernel(const uint16_t*
     const int begin = part * per, end = min(vocab, begin + per);
     float best = -INFINITY;
     int best_i = 0x7fffffff;
-    // 16-byte loads where the row allows it (vocab a multiple of 8 keeps every row aligned)
-    if ((vocab & 7) == 0) {
+    if (temperature > 0.f) {
+        // Gumbel-max sample of sequence b: the greedy pick over logit / T + noise (the rule and the generator of
+        // lm_head_kernel); the draw is keyed by (seed + b, the sequence's position, vocabulary index)
+        const int step = pos[b];
+        for (int c = begin + threadIdx.x; c < end; c += kPickThreads)
+            pick_merge(best, best_i, __fdiv_rn(bf16_bits_to_f32(row[c]), temperature) + gumbel_variate(seed + (unsigned long long)b, step, c), c);
+    } else if ((vocab & 7) == 0) {     // 16-byte loads where the row allows it (vocab a multiple of 8 keeps every row aligned)
         for (int c = begin + threadIdx.x * 8; c < end; c += kPickThreads * 8) {
             const uint4 v = __ldcg(reinterpret_cast<const uint4*>(row + c));
             const uint32_t u[4] = {v.x, v.y, v.z, v.w};
@@ -103,9 +109,9 @@ int pick_rows_parts() { return kPickParts; }
 
 cudaError_t pick_rows_launch(const uint16_t* logits, int rows, int vocab, long long* tokens, int* pos, int n_prompt,
                              int max_tokens, long long* picked, float* part_val, int* part_idx, unsigned* tickets,
-                             cudaStream_t stream, bool pdl) {
+                             float temperature, unsigned long long seed, cudaStream_t stream, bool pdl) {
     return launch_kernel(pick_rows_kernel, dim3(rows, kPickParts), dim3(kPickThreads), 0, stream, pdl, logits, vocab,
-                         tokens, pos, n_prompt, max_tokens, picked, part_val, part_idx, tickets);
+                         tokens, pos, n_prompt, max_tokens, picked, part_val, part_idx, tickets, temperature, seed);
 }
 
 }  // namespace tfb

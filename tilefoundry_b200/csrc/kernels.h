@@ -364,7 +364,7 @@ cudaError_t embed_rows_launch(const uint16_t* table, const long long* tokens, co
 int pick_rows_parts();
 cudaError_t pick_rows_launch(const uint16_t* logits, int rows, int vocab, long long* tokens, int* pos, int n_prompt,
                              int max_tokens, long long* picked, float* part_val, int* part_idx, unsigned* tickets,
-                             cudaStream_t stream, bool pdl);
+                             float temperature, unsigned long long seed, cudaStream_t stream, bool pdl);
 
 // ---- exchange steps over NVLink peer memory (collective.cu) ----
 constexpr int kMaxPeers = 8;

@@ -23,7 +23,7 @@ MAX_BATCH = 32
 
 class Qwen3BatchSession:
     def __init__(self, cfg: Qwen3Config, resource, *, batch: int, max_ctx: int = 2176, device="cuda:0",
-                 trace_hidden: bool = False, pdl: bool = True):
+                 trace_hidden: bool = False, pdl: bool = True, temperature: float = 0.0, seed: int = 0):
         if not torch.cuda.is_available():
             raise RuntimeError("Qwen3BatchSession needs a CUDA device; there is no CPU path")
         if not 1 <= batch <= MAX_BATCH:
@@ -91,7 +91,8 @@ class Qwen3BatchSession:
             attn_buf=lib.ptr(self.attn), act_buf=lib.ptr(self.act), logits=lib.ptr(self.logits),
             part_o=lib.ptr(self.part_o), part_ml=lib.ptr(self.part_ml), counters=lib.ptr(self.counters),
             status=lib.ptr(self.status), pick_val=lib.ptr(self.pick_val), pick_idx=lib.ptr(self.pick_idx),
-            picked=lib.ptr(self.picked), hidden_trace=lib.ptr(self.trace))
+            picked=lib.ptr(self.picked), hidden_trace=lib.ptr(self.trace),
+            temperature=float(temperature), seed=int(seed) & (2 ** 64 - 1))
         self.graph = None
         self.n_prompt = 0
         #: kernels one step enqueues (embed + 7 per layer + final norm + head + pick [+ trace copies])

@@ -93,7 +93,7 @@ class Qwen3BatchStepArgs(C.Structure):
                 ("hidden_buf", _vp), ("norm_buf", _vp), ("qkv_buf", _vp), ("attn_buf", _vp), ("act_buf", _vp),
                 ("logits", _vp), ("part_o", _vp), ("part_ml", _vp), ("counters", _vp),
                 ("status", _vp), ("pick_val", _vp), ("pick_idx", _vp), ("picked", _vp),
-                ("hidden_trace", _vp)]
+                ("hidden_trace", _vp), ("temperature", _f32), ("reserved", _i32), ("seed", C.c_uint64)]
 
 
 class Qwen3PrefillArgs(C.Structure):
