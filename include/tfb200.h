@@ -734,6 +734,40 @@ TFB_API int32_t tfb_gemm_small_m_splits(int32_t n, int32_t k);
 TFB_API int32_t tfb_gemm_small_m_swiglu_splits(int32_t n, int32_t k);
 TFB_API int tfb_gemm_small_m(const tfb_gemm_small_m_args* args, tfb_stream_t stream);
 
+/* ---- mixture-of-experts block for a batch of tokens -----------------------------------------------------------
+ * out[t] = residual[t] + sum_s weights[t,s] * bf16(W_down[e] . bf16(silu(bf16(W_gate[e] . bf16 x[t])) * bf16(W_up[e] . bf16 x[t])))
+ *          + (the same through the shared expert) * sigmoid(shared_gate[t]),            e = indices[t,s]
+ * for `tokens` tokens at once: every expert that a token selected is read once and meets all of its tokens on the
+ * tensor cores (K folded into the MMA's N, eight tokens per tcgen05.mma; tilefoundry_b200/csrc/moe_grouped.cu).  The
+ * batch form of `experts` of the authored Qwen3.5 block (examples/qwen3_5_35b_a3b-tilelang/model.py: routed_experts +
+ * shared_expert; the reference's kernels, kernels/moe.py:368 `_h_kernel` and :527 `_down_kernel`, take one token).
+ * Routing (indices, weights, the shared gate's logit) is the caller's: tfb_router_select per token.
+ * Scratch (device, any contents): x_bf16 [tokens][hidden] bf16, inner [tokens][top_k+1][inter] bf16,
+ * y [tokens][top_k+1][hidden] bf16, counts i32 [experts+1], lists i32 [experts+1][tokens]; status u32 zeroed once.
+ * hidden and inter multiples of 128 (inter of 8, hidden of 16), (16 + 8) * max(hidden, inter) * 2 <= 200 KB. */
+typedef struct {
+    const float* x;             /* [tokens][hidden] f32 */
+    const int64_t* indices;     /* [tokens][top_k] */
+    const float* weights;       /* [tokens][top_k] f32 */
+    const float* shared_gate;   /* optional [tokens] f32 */
+    const float* residual;      /* optional [tokens][hidden] f32 */
+    const void* w_gate;         /* bf16 [experts][inter][hidden] */
+    const void* w_up;
+    const void* w_down;         /* bf16 [experts][hidden][inter] */
+    const void* w_shared_gate;  /* optional: bf16 [inter][hidden] */
+    const void* w_shared_up;
+    const void* w_shared_down;  /* bf16 [hidden][inter] */
+    float* out;                 /* [tokens][hidden] f32 */
+    void* x_bf16;
+    void* inner;
+    void* y;
+    int32_t* counts;
+    int32_t* lists;
+    uint32_t* status;
+    int32_t tokens, hidden, inter, experts, top_k, pdl;
+} tfb_moe_batch_args;
+TFB_API int tfb_moe_batch(const tfb_moe_batch_args* args, tfb_stream_t stream);
+
 /* ---- Qwen3-architecture decode step for several sequences (batch <= 32) ------------------------------------
  * One token for each of `batch` independent sequences: every projection runs once on the tensor cores for the
  * whole batch (tfb_gemm_small_m), attention once per layer with one CTA set per sequence (tfb_attn_gqa_decode

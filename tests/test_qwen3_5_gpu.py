@@ -121,6 +121,28 @@ def test_moe_functions_and_routing_indices(dev, sides):
     _check(twin.layer0.residual_add, ref.layer0.residual_add, (hidden, b), {"output": F32})
 
 
+@pytest.mark.parametrize("n_tokens", [1, 5, 64])
+def test_experts_for_a_batch_of_tokens(dev, sides, n_tokens):
+    """``tfb_moe_batch``: the block's ``experts`` for several tokens at once -- every selected expert read once, its rows
+    against all of its tokens on the tensor cores -- equals the evaluator's ``experts`` token by token (the evaluator's
+    own routing is handed to both sides, so no near-tie can make them differ).  64 tokens with 8 of 256 experts each is
+    the batch the grouped form is for; 1 and 5 tokens leave most experts without a token."""
+    cfg, ref, twin = sides[:3]
+    g = torch.Generator().manual_seed(40 + n_tokens)
+    rm, tm = ref.layer0.moe, twin.layer0.moe
+    hidden = torch.randn(n_tokens, 1, 1, cfg.hidden, generator=g)
+    tokens = torch.cat([rm.post_norm(h) for h in hidden])                       # [T, H] f32
+    routed = [rm.router.routing(tokens[t:t + 1]) for t in range(n_tokens)]
+    weights = torch.cat([w.reshape(1, -1) for w, _ in routed])
+    indices = torch.cat([i.reshape(1, -1) for _, i in routed])
+    want = torch.cat([rm.experts(tokens[t:t + 1], *routed[t]).reshape(1, -1) for t in range(n_tokens)])
+    got = tm.experts_batch(tokens.to(dev), weights.to(dev), indices.to(dev)).cpu()
+    assert_close_at_scale(got, want, f"experts of {n_tokens} tokens")
+    # and the one-token path of the twin agrees with it on its own routing inputs
+    one = tm.experts(tokens[:1].to(dev), weights[:1].to(dev), indices[:1].to(dev)).reshape(1, -1).cpu()
+    assert_close_at_scale(got[:1], one, "batch form against the one-token kernels")
+
+
 def test_root_functions(dev, sides):
     cfg, ref, twin = sides[:3]
     g = torch.Generator().manual_seed(2)

@@ -14,7 +14,7 @@ CSRC = Path(__file__).resolve().parent / "csrc"
 LIB = CSRC / "libtfb200.so"
 SOURCES = ("api.cu", "api_minicpm3.cu", "gemv.cu", "gemv_stream.cu", "attn_gqa.cu", "attn_mla.cu", "attn_mla_latent.cu", "mamba2.cu", "moe.cu", "api_granite.cu", "misc.cu",
            "gemv_persist.cu", "gemv_async.cu", "chain.cu", "gemm_tc.cu", "collective.cu", "gemv_f32.cu", "gdn.cu", "attn_gated.cu", "api_qwen35.cu",
-           "batch.cu", "api_batch.cu", "step_fused.cu")
+           "batch.cu", "api_batch.cu", "step_fused.cu", "moe_grouped.cu")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-Xcudafe", "--diag_suppress=177"]
 # Approximate exp / division / rsqrt only where every output is a bf16-rounded activation.  The files that decide

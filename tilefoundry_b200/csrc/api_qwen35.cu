@@ -94,6 +94,25 @@ int tfb_attn_gated_decode(const tfb_attn_gated_args* a, tfb_stream_t stream) {
     return done(tfb::attn_gated_dispatch(p, S(stream), a->pdl != 0));
 }
 
+int tfb_moe_batch(const tfb_moe_batch_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->x && a->indices && a->weights && a->w_gate && a->w_up && a->w_down && a->out, TFB_EINVAL);
+    TFB_REQUIRE(a->x_bf16 && a->inner && a->y && a->counts && a->lists && a->status, TFB_EINVAL);
+    TFB_REQUIRE(aligned16(a->w_gate) && aligned16(a->w_up) && aligned16(a->w_down) && aligned16(a->x_bf16) && aligned16(a->inner) &&
+                    (!a->w_shared_gate || (aligned16(a->w_shared_gate) && aligned16(a->w_shared_up) && aligned16(a->w_shared_down))), TFB_EALIGN);
+    tfb::MoeBatchParams p;
+    std::memset(&p, 0, sizeof p);
+    p.x = a->x; p.indices = reinterpret_cast<const long long*>(a->indices); p.weights = a->weights;
+    p.shared_gate = a->shared_gate; p.residual = a->residual;
+    auto c16 = [](const void* q) { return static_cast<const uint16_t*>(q); };
+    p.w_gate = c16(a->w_gate); p.w_up = c16(a->w_up); p.w_down = c16(a->w_down);
+    p.w_shared_gate = c16(a->w_shared_gate); p.w_shared_up = c16(a->w_shared_up); p.w_shared_down = c16(a->w_shared_down);
+    p.out = a->out; p.x_bf16 = static_cast<uint16_t*>(a->x_bf16); p.inner = static_cast<uint16_t*>(a->inner);
+    p.y = static_cast<uint16_t*>(a->y); p.counts = a->counts; p.lists = a->lists; p.status = a->status;
+    p.tokens = a->tokens; p.hidden = a->hidden; p.inter = a->inter; p.experts = a->experts; p.top_k = a->top_k;
+    TFB_REQUIRE(tfb::moe_batch_supported(p), TFB_EINVAL);
+    return done(tfb::moe_batch_launch(p, S(stream), a->pdl != 0));
+}
+
 int tfb_moe_down_f32(const tfb_moe_down_f32_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->inner && a->out && a->top_k >= 0 && a->top_k <= 32, TFB_EINVAL);
     TFB_REQUIRE(a->top_k == 0 || (a->w_down && a->indices && a->weights), TFB_EINVAL);

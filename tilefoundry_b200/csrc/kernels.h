@@ -366,6 +366,31 @@ cudaError_t pick_rows_launch(const uint16_t* logits, int rows, int vocab, long l
                              int max_tokens, long long* picked, float* part_val, int* part_idx, unsigned* tickets,
                              float temperature, unsigned long long seed, cudaStream_t stream, bool pdl);
 
+// ---- mixture-of-experts block for a batch of tokens (moe_grouped.cu) ----
+struct MoeBatchParams {
+    const float* x;                  // f32 [tokens][hidden]: the block's input (post-attention norm applied)
+    const long long* indices;        // [tokens][top_k]
+    const float* weights;            // f32 [tokens][top_k]
+    const float* shared_gate;        // optional f32 [tokens]: logit of the shared expert's sigmoid gate
+    const float* residual;           // optional f32 [tokens][hidden], added to the result
+    const uint16_t* w_gate;          // bf16 [experts][inter][hidden]
+    const uint16_t* w_up;
+    const uint16_t* w_down;          // bf16 [experts][hidden][inter]
+    const uint16_t* w_shared_gate;   // optional shared expert, bf16 [inter][hidden] / [hidden][inter]
+    const uint16_t* w_shared_up;
+    const uint16_t* w_shared_down;
+    float* out;                      // f32 [tokens][hidden]
+    uint16_t* x_bf16;                // scratch bf16 [tokens][hidden]
+    uint16_t* inner;                 // scratch bf16 [tokens][top_k + 1][inter]
+    uint16_t* y;                     // scratch bf16 [tokens][top_k + 1][hidden]
+    int* counts;                     // scratch i32 [experts + 1]
+    int* lists;                      // scratch i32 [experts + 1][tokens]
+    unsigned* status;                // u32, set non-zero if a bounded wait gave up
+    int tokens, hidden, inter, experts, top_k;
+};
+bool moe_batch_supported(const MoeBatchParams& p);
+cudaError_t moe_batch_launch(const MoeBatchParams& p, cudaStream_t stream, bool pdl);
+
 // ---- exchange steps over NVLink peer memory (collective.cu) ----
 constexpr int kMaxPeers = 8;
 struct PeerReduceParams {

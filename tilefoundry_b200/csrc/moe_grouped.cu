@@ -1,0 +1,295 @@
+// Mixture-of-experts block for a batch of tokens: every expert that at least one token selected is read ONCE, and its
+// rows meet all of its tokens on the tensor cores.
+//
+//   inner[t, s, :] = bf16( silu(bf16(W_gate[e] . x_t)) * bf16(W_up[e] . x_t) )        e = indices[t, s]  (x_t rounded to bf16)
+//   y[t, s, :]     = bf16( W_down[e] . inner[t, s, :] )
+//   out[t, :]      = sum_s weights[t, s] * y[t, s, :]  +  y[t, K, :] * sigmoid(shared_gate[t])      (slot K: the shared expert)
+//
+// the rounding points of Qwen3_5SparseMoeBlock as authored (every matmul takes bf16 operands and returns bf16).
+//
+// A batch of 64 tokens with 8 of 256 experts each touches ~222 experts with two or three tokens apiece: a GEMM per
+// expert has no M to speak of and a GEMV per (token, expert) reads every expert several times.  Here a CTA owns 16 rows
+// of one expert and up to eight of its tokens at a time: K is folded into the MMA's N as in the one-launch Qwen3 step
+// (256 contiguous bytes of a weight row are an 8 x 16 K-major block; the stride between 8-row groups is the row pitch;
+// the B operand is the same fold of each token's activation chunk, one 8-row group per token, so N = 8 x tokens), one
+// tcgen05.mma (M 128, N 64, K 16) per 128 elements of K whatever the number of tokens, accumulating in tensor memory;
+// token b's dot product with row g is the diagonal sum D[8g + r][8b + r].  HBM-bound: the touched experts' bytes once.
+#include "common.cuh"
+#include "kernels.h"
+#include "launch.h"
+
+namespace tfb {
+namespace {
+
+constexpr int kGRows = 16;                       // weight rows of a CTA (M = 128: eight tensor-memory lanes per row)
+constexpr int kGTok = 8;                         // tokens per pass (N = 64)
+constexpr int kGThreads = 128;
+constexpr int kGCols = 64;                       // tensor-memory columns of the accumulator
+constexpr unsigned kSpinLimit = 1u << 22;        // bound of every barrier wait (each try may suspend for a while)
+
+__device__ __forceinline__ uint32_t s_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mb_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(s_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mb_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(s_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mb_try(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(s_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// false: the wait gave up (the caller records it; the results of the CTA are void)
+__device__ __forceinline__ bool mb_wait(unsigned long long* bar, unsigned parity) {
+    for (unsigned i = 0; i < kSpinLimit; ++i)
+        if (mb_try(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(s_u32(dst)), "l"(src), "r"(bytes), "r"(s_u32(bar)) : "memory");
+}
+__device__ __forceinline__ uint64_t folded_desc(uint32_t smem_addr, uint32_t group_pitch) {
+    uint64_t d = 0;
+    d |= uint64_t((smem_addr & 0x3FFFF) >> 4);               // start address, 16-byte units
+    d |= uint64_t(128 >> 4) << 16;                            // byte offset between core matrices along K
+    d |= uint64_t(group_pitch >> 4) << 32;                    // byte offset between 8-row groups
+    d |= uint64_t(1) << 46;                                   // descriptor version of this architecture
+    return d;                                                  // (layout type 0: no swizzle)
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_arrive(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(s_u32(bar)) : "memory");
+}
+// D f32, A and B bf16, both K-major, N = 64, M = 128
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(kGTok * 8 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+
+// one expert list entry: token in the high bits, slot (0 .. K) in the low eight
+__device__ __forceinline__ int entry_token(int e) { return e >> 8; }
+__device__ __forceinline__ int entry_slot(int e) { return e & 255; }
+
+// ---- tokens f32 -> bf16 rows, and the experts' token lists ------------------------------------------------------
+__global__ void __launch_bounds__(256) moe_batch_prepare_kernel(const MoeBatchParams p) {
+    pdl_trigger();
+    pdl_wait();
+    if (blockIdx.x > 0) {                                      // CTAs 1..: the rounding of the activations
+        const size_t n = size_t(p.tokens) * p.hidden;
+        for (size_t i = size_t(blockIdx.x - 1) * blockDim.x + threadIdx.x; i < n; i += size_t(gridDim.x - 1) * blockDim.x)
+            p.x_bf16[i] = f32_to_bf16_bits(p.x[i]);
+        return;
+    }
+    // CTA 0: lists in token order (deterministic), by one thread per expert
+    const int T = p.tokens, K = p.top_k, E = p.experts;
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+        int n = 0;
+        int* lst = p.lists + size_t(e) * T;
+        if (e == E) {
+            if (p.w_shared_gate) for (int t = 0; t < T; ++t) lst[n++] = (t << 8) | K;
+        } else {
+            for (int t = 0; t < T; ++t)
+                for (int s = 0; s < K; ++s)
+                    if (p.indices[size_t(t) * K + s] == (long long)e) lst[n++] = (t << 8) | s;
+        }
+        p.counts[e] = n;
+    }
+}
+
+// ---- the grouped products -----------------------------------------------------------------------------------------
+// STAGE 0: gate/up + SwiGLU -- grid (inter / 8, experts + 1), tile rows 2i / 2i + 1 = gate / up row r0 + i, k = hidden,
+//          activations x_bf16[token], result inner[token, slot, r0 + i].
+// STAGE 1: down -- grid (hidden / 16, experts + 1), tile rows = rows j0 .. j0 + 15 of W_down[e], k = inter,
+//          activations inner[token, slot], result y[token, slot, j0 + g].
+template <int STAGE>
+__global__ void __launch_bounds__(kGThreads) moe_grouped_kernel(const MoeBatchParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ __align__(8) unsigned long long bar_w, bar_x, bar_mma;
+    __shared__ uint32_t tmem_base;
+    __shared__ int s_fail;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int e = blockIdx.y, E = p.experts, K = p.top_k, T = p.tokens;
+    const int k = STAGE == 0 ? p.hidden : p.inter;              // reduction length
+    const int row_bytes = k * 2;
+    pdl_trigger();
+    pdl_wait();
+    const int n = p.counts[e];
+    if (n == 0) return;                                        // (uniform over the CTA, before anything is allocated)
+    const int* lst = p.lists + size_t(e) * T;
+    unsigned char* tile = smem;                                // [16 rows][k] bf16
+    unsigned char* xs = smem + kGRows * row_bytes;             // [8 tokens][k] bf16
+
+    if (tid == 0) {
+        mb_init(&bar_w, 1); mb_init(&bar_x, 1); mb_init(&bar_mma, 1);
+        s_fail = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(s_u32(&tmem_base)), "n"(kGCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmem_base;
+
+    // the weight rows of this CTA: lane r of warp 0 copies tile row r
+    if (warp == 0) {
+        if (lane == 0) mb_expect_tx(&bar_w, unsigned(kGRows) * row_bytes);
+        __syncwarp();
+        if (lane < kGRows) {
+            const uint16_t* src;
+            if (STAGE == 0) {
+                const int r = blockIdx.x * (kGRows / 2) + (lane >> 1);
+                const uint16_t* base = e < E ? ((lane & 1) ? p.w_up : p.w_gate) + size_t(e) * p.inter * p.hidden
+                                             : ((lane & 1) ? p.w_shared_up : p.w_shared_gate);
+                src = base + size_t(r) * p.hidden;
+            } else {
+                const int j = blockIdx.x * kGRows + lane;
+                src = (e < E ? p.w_down + size_t(e) * p.hidden * p.inter : p.w_shared_down) + size_t(j) * p.inter;
+            }
+            bulk_load(tile + lane * row_bytes, src, row_bytes, &bar_w);
+        }
+    }
+
+    const int team = lane >> 3;                                 // the tile row of this lane's team: 4 * warp + team
+    const int trow = warp * 4 + team;
+    unsigned xpar = 0, mpar = 0;
+    bool ok = true;
+    for (int p0 = 0; p0 < n; p0 += kGTok) {
+        const int nb = min(kGTok, n - p0);
+        // this pass's activations: lane b of warp 1 copies token b's row
+        if (warp == 1) {
+            if (lane == 0) mb_expect_tx(&bar_x, unsigned(nb) * row_bytes);
+            __syncwarp();
+            if (lane < nb) {
+                const int ent = lst[p0 + lane];
+                const uint16_t* src = STAGE == 0 ? p.x_bf16 + size_t(entry_token(ent)) * p.hidden
+                                                 : p.inner + (size_t(entry_token(ent)) * (K + 1) + entry_slot(ent)) * p.inter;
+                bulk_load(xs + lane * row_bytes, src, row_bytes, &bar_x);
+            }
+        }
+        if (tid == 0) {
+            // the MMAs of the pass: one per 128 elements of K, all tokens at once
+            ok = (p0 > 0 || mb_wait(&bar_w, 0)) && mb_wait(&bar_x, xpar);
+            if (ok) {
+                const uint64_t da = folded_desc(s_u32(tile), row_bytes), db = folded_desc(s_u32(xs), row_bytes);
+                for (int t = 0; t < k / 128; ++t)
+                    umma_f16(tmem, da + uint64_t((t * 256) >> 4), db + uint64_t((t * 256) >> 4), kIdesc, t ? 1u : 0u);
+            } else {
+                s_fail = 1;
+            }
+            umma_arrive(&bar_mma);
+        }
+        xpar ^= 1u;
+        // everyone waits for the accumulator
+        if (!mb_wait(&bar_mma, mpar)) { s_fail = 1; }
+        mpar ^= 1u;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (s_fail) break;                                      // (uniform after the barrier)
+
+        // epilogue: lane 8g + r of the quadrant wants, for token b, column 8b + r; a team of eight lanes sums the diagonal
+        uint32_t v[kGCols];
+        const uint32_t taddr = tmem + (uint32_t(warp * 32) << 16);
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+                     "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                       "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31]),
+                       "=r"(v[32]), "=r"(v[33]), "=r"(v[34]), "=r"(v[35]), "=r"(v[36]), "=r"(v[37]), "=r"(v[38]), "=r"(v[39]), "=r"(v[40]), "=r"(v[41]), "=r"(v[42]), "=r"(v[43]), "=r"(v[44]), "=r"(v[45]), "=r"(v[46]), "=r"(v[47]),
+                       "=r"(v[48]), "=r"(v[49]), "=r"(v[50]), "=r"(v[51]), "=r"(v[52]), "=r"(v[53]), "=r"(v[54]), "=r"(v[55]), "=r"(v[56]), "=r"(v[57]), "=r"(v[58]), "=r"(v[59]), "=r"(v[60]), "=r"(v[61]), "=r"(v[62]), "=r"(v[63])
+                     : "r"(taddr) : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const bool b4 = lane & 4, b2 = lane & 2, b1 = lane & 1;
+#pragma unroll
+        for (int b = 0; b < kGTok; ++b) {
+            const uint32_t t0 = b4 ? v[8 * b + 4] : v[8 * b], t1 = b4 ? v[8 * b + 5] : v[8 * b + 1];
+            const uint32_t t2 = b4 ? v[8 * b + 6] : v[8 * b + 2], t3 = b4 ? v[8 * b + 7] : v[8 * b + 3];
+            const uint32_t q0 = b2 ? t2 : t0, q1 = b2 ? t3 : t1;
+            float d = __uint_as_float(b1 ? q1 : q0);
+            d += __shfl_xor_sync(0xffffffffu, d, 1);
+            d += __shfl_xor_sync(0xffffffffu, d, 2);
+            d += __shfl_xor_sync(0xffffffffu, d, 4);
+            if (STAGE == 0) {
+                const float up = round_bf16(__shfl_xor_sync(0xffffffffu, d, 8));     // (the team next door holds the up row)
+                if (b < nb && (lane & 15) == 0) {
+                    const int ent = lst[p0 + b];
+                    const int col = blockIdx.x * (kGRows / 2) + (trow >> 1);
+                    p.inner[(size_t(entry_token(ent)) * (K + 1) + entry_slot(ent)) * p.inter + col] =
+                        f32_to_bf16_bits(silu_f32(round_bf16(d)) * up);
+                }
+            } else {
+                if (b < nb && (lane & 7) == 0) {
+                    const int ent = lst[p0 + b];
+                    p.y[(size_t(entry_token(ent)) * (K + 1) + entry_slot(ent)) * p.hidden + blockIdx.x * kGRows + trow] = f32_to_bf16_bits(d);
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();                                        // (the next pass overwrites the activations and the accumulator)
+    }
+    if (s_fail && tid == 0) atomicOr(p.status, 0x1000u);
+    if (s_fail && tid == 0) {                                   // MMAs may still be in flight: they end by themselves
+        umma_arrive(&bar_w);                                    // (a fresh completion to wait for, bounded)
+        mb_wait(&bar_w, 1);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "n"(kGCols) : "memory");
+    }
+}
+
+// ---- out[t] = residual[t] + sum of the routed slots by weight + shared slot by its gate --------------------------
+__global__ void __launch_bounds__(256) moe_batch_finalize_kernel(const MoeBatchParams p) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.y, K = p.top_k;
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= p.hidden) return;
+    const uint16_t* y = p.y + size_t(t) * (K + 1) * p.hidden + j;
+    float routed = 0.f;
+    for (int s = 0; s < K; ++s) routed = fmaf(bf16_bits_to_f32(y[size_t(s) * p.hidden]), p.weights[size_t(t) * K + s], routed);
+    float out = routed;
+    if (p.w_shared_gate) {
+        float sh = bf16_bits_to_f32(y[size_t(K) * p.hidden]);
+        if (p.shared_gate) sh *= 1.f / (1.f + expf(-p.shared_gate[t]));
+        out += sh;
+    }
+    if (p.residual) out += p.residual[size_t(t) * p.hidden + j];
+    p.out[size_t(t) * p.hidden + j] = out;
+}
+
+}  // namespace
+
+size_t moe_grouped_smem(int k) { return size_t(kGRows + kGTok) * k * 2; }
+
+bool moe_batch_supported(const MoeBatchParams& p) {
+    auto ok_k = [](int k) { return k >= 128 && k % 128 == 0 && moe_grouped_smem(k) <= 200 * 1024; };
+    return p.tokens >= 1 && p.tokens <= 4096 && p.top_k >= 1 && p.top_k < 255 && p.experts >= 1 && ok_k(p.hidden) &&
+           ok_k(p.inter) && p.inter % (kGRows / 2) == 0 && p.hidden % kGRows == 0 &&
+           (!p.w_shared_gate || (p.w_shared_up && p.w_shared_down));
+}
+
+cudaError_t moe_batch_launch(const MoeBatchParams& p, cudaStream_t stream, bool pdl) {
+    if (!moe_batch_supported(p)) return cudaErrorInvalidValue;
+    static PerDeviceOnce once;
+    if (once.first()) {
+        cudaError_t e = cudaFuncSetAttribute(moe_grouped_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(moe_grouped_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return e;
+    }
+    cudaError_t e = launch_kernel(moe_batch_prepare_kernel, dim3(1 + 64), dim3(256), 0, stream, pdl, p);
+    if (e != cudaSuccess) return e;
+    e = launch_kernel(moe_grouped_kernel<0>, dim3(p.inter / (kGRows / 2), p.experts + 1), dim3(kGThreads), moe_grouped_smem(p.hidden), stream, pdl, p);
+    if (e != cudaSuccess) return e;
+    e = launch_kernel(moe_grouped_kernel<1>, dim3(p.hidden / kGRows, p.experts + 1), dim3(kGThreads), moe_grouped_smem(p.inter), stream, pdl, p);
+    if (e != cudaSuccess) return e;
+    return launch_kernel(moe_batch_finalize_kernel, dim3((p.hidden + 255) / 256, p.tokens), dim3(256), 0, stream, pdl, p);
+}
+
+}  // namespace tfb

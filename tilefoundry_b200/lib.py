@@ -107,6 +107,14 @@ class Qwen3PrefillArgs(C.Structure):
                 ("part_o", _vp), ("part_ml", _vp), ("counters", _vp), ("status", _vp)]
 
 
+class MoeBatchArgs(C.Structure):
+    _fields_ = [("x", _vp), ("indices", _vp), ("weights", _vp), ("shared_gate", _vp), ("residual", _vp),
+                ("w_gate", _vp), ("w_up", _vp), ("w_down", _vp), ("w_shared_gate", _vp), ("w_shared_up", _vp),
+                ("w_shared_down", _vp), ("out", _vp), ("x_bf16", _vp), ("inner", _vp), ("y", _vp), ("counts", _vp),
+                ("lists", _vp), ("status", _vp), ("tokens", _i32), ("hidden", _i32), ("inter", _i32), ("experts", _i32),
+                ("top_k", _i32), ("pdl", _i32)]
+
+
 class MoeAllreduceArgs(C.Structure):
     _fields_ = [("partial", _vp), ("inbox", _vp * 8), ("flags", _vp * 8), ("epoch", _vp), ("status", _vp),
                 ("residual", _vp), ("out", _vp), ("hidden", _i32), ("rank", _i32), ("world", _i32), ("has_shared", _i32),
@@ -273,6 +281,7 @@ SYMBOLS = {
     "tfb_status_string": (C.c_char_p, [_i32]),
     "tfb_last_error": (C.c_char_p, []),
     "tfb_debug_trace": (_i32, [_vp, _i32]),
+    "tfb_moe_batch": (_i32, [C.POINTER(MoeBatchArgs), _vp]),
     "tfb_graph_step_host": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "tfb_graph_generate_host": (_i32, [_vp, _vp, _i64, _i32, _vp, _vp, _vp]),
     "tfb_embed": (_i32, [_vp, _vp, _vp, _i32, _i32, _i64, _f32, _vp]),

@@ -204,6 +204,33 @@ def make_twin(cfg: authored.Qwen35Config = authored.QWEN3_5_35B_A3B):
             logit = gemv(self._scale, x, 1, H, like=tokens)
             return self._down(tokens, inner, K, _flat(weights), idx, w_down, shared=True, gate_logit=logit).reshape(1, 1, H)
 
+        def experts_batch(self, tokens, weights, indices):
+            """``experts`` for a batch: tokens f32 [T, H], routing weights f32 [T, K] and indices int64 [T, K] -> f32 [T, H].
+            Every selected expert is read once for all of its tokens (``tfb_moe_batch``)."""
+            b = self._bound
+            T = tokens.shape[0]
+            x = tokens.contiguous()
+            dev = x.device
+            logits = torch.cat([gemv(self._scale, x[t], 1, H, like=x[t]) for t in range(T)]).contiguous()
+            out = torch.empty(T, H, device=dev, dtype=torch.float32)
+            scratch = dict(x_bf16=torch.empty(T, H, device=dev, dtype=torch.bfloat16),
+                           inner=torch.empty(T, K + 1, I, device=dev, dtype=torch.bfloat16),
+                           y=torch.empty(T, K + 1, H, device=dev, dtype=torch.bfloat16),
+                           counts=torch.empty(E + 1, device=dev, dtype=torch.int32),
+                           lists=torch.empty(E + 1, T, device=dev, dtype=torch.int32))
+            status = torch.zeros(1, device=dev, dtype=torch.int32)
+            if IS != I:
+                raise ValueError("tfb_moe_batch takes a shared expert as wide as the routed ones")
+            a = lib.MoeBatchArgs(x=lib.ptr(x), indices=lib.ptr(indices.contiguous()), weights=lib.ptr(weights.contiguous()),
+                                 shared_gate=lib.ptr(logits), residual=None, w_gate=lib.ptr(b["w_gate"]), w_up=lib.ptr(b["w_up"]),
+                                 w_down=lib.ptr(b["w_down"]), w_shared_gate=lib.ptr(self._sg), w_shared_up=lib.ptr(self._su),
+                                 w_shared_down=lib.ptr(self._sd), out=lib.ptr(out), status=lib.ptr(status), tokens=T, hidden=H,
+                                 inter=I, experts=E, top_k=K, pdl=0, **{k: lib.ptr(v) for k, v in scratch.items()})
+            lib.check(L().tfb_moe_batch(C.byref(a), lib.stream()), "tfb_moe_batch")
+            if int(status):
+                raise RuntimeError(f"tfb_moe_batch: a bounded wait gave up (status {int(status):#x})")
+            return out
+
     def layer_cls(layer_sem, mixer_cls):
         @runtime_func
         def residual_add(self, a, b):
