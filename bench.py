@@ -311,6 +311,87 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_moe_batch(args):
+    """The Qwen3.5-35B-A3B expert block for a batch of tokens (`tfb_moe_batch`): 256 experts of 512, top-8, the shared
+    expert, hidden 2048; random tokens routed by a random router, so ~222 experts are touched by 64 tokens.  Timed over
+    several layers' expert sets (1.6 GB each, far more than L2) in one CUDA graph; bytes = the touched experts' three
+    matrices once, plus the shared expert's.  For scale, the same tokens one at a time through the one-token kernels
+    (gathered gate/up GEMV + down), which read an expert once per token that selected it."""
+    import ctypes as C
+
+    from tilefoundry_b200 import lib
+
+    lib.load()
+    dev = torch.device("cuda:0")
+    T = args.moe_batch
+    E, K, H, I = 256, 8, 2048, 512
+    g = torch.Generator(device=dev).manual_seed(0)
+    bf = torch.bfloat16
+    rnd = lambda *shape, std=0.02: (torch.randn(*shape, device=dev, generator=g) * std).to(bf)
+    n_layers = 3
+    layers = [dict(w_gate=rnd(E, I, H), w_up=rnd(E, I, H), w_down=rnd(E, H, I), sg=rnd(I, H), su=rnd(I, H), sd=rnd(H, I),
+                   router=rnd(E, H, std=0.05)) for _ in range(n_layers)]
+    x = torch.randn(T, H, device=dev, generator=g)
+    status = torch.zeros(1, device=dev, dtype=torch.int32)
+    out = torch.empty(T, H, device=dev)
+    scratch = dict(x_bf16=torch.empty(T, H, device=dev, dtype=bf), inner=torch.empty(T, K + 1, I, device=dev, dtype=bf),
+                   y=torch.empty(T, K + 1, H, device=dev, dtype=bf), counts=torch.empty(2 * (E + 1) + 1, device=dev, dtype=torch.int32),
+                   lists=torch.empty(E + 1, T, device=dev, dtype=torch.int32))
+    calls, touched = [], []
+    for L in layers:
+        probs = torch.softmax((x.to(bf) @ L["router"].t()).float(), dim=-1)
+        top, idx = torch.topk(probs, K, dim=-1)
+        L["idx"], L["w"] = idx.contiguous(), (top / top.sum(-1, keepdim=True)).contiguous()
+        L["gate"] = torch.zeros(T, device=dev)
+        touched.append(int(torch.unique(idx).numel()))
+        calls.append(lib.MoeBatchArgs(x=lib.ptr(x), indices=lib.ptr(L["idx"]), weights=lib.ptr(L["w"]), shared_gate=lib.ptr(L["gate"]),
+                                      residual=None, w_gate=lib.ptr(L["w_gate"]), w_up=lib.ptr(L["w_up"]), w_down=lib.ptr(L["w_down"]),
+                                      w_shared_gate=lib.ptr(L["sg"]), w_shared_up=lib.ptr(L["su"]), w_shared_down=lib.ptr(L["sd"]),
+                                      out=lib.ptr(out), status=lib.ptr(status), tokens=T, hidden=H, inter=I, experts=E, top_k=K,
+                                      pdl=0, **{k: lib.ptr(v) for k, v in scratch.items()}))
+
+    def grouped():
+        for a in calls:
+            lib.check(lib.load().tfb_moe_batch(C.byref(a), lib.stream()), "tfb_moe_batch")
+    ms = _graph_time(grouped, n_layers)
+    if int(status):
+        raise RuntimeError(f"tfb_moe_batch: a bounded wait gave up (status {int(status):#x})")
+    expert_bytes = 3 * I * H * 2
+    bytes_grouped = (sum(touched) / n_layers + 1) * expert_bytes
+    peak, kind = peaks()
+
+    # the same work token by token through the one-token kernels (gathered gate/up + SwiGLU, then down + combine)
+    inner1 = torch.empty((K + 1) * I, device=dev)
+    out1 = torch.empty(H, device=dev)
+    one = []
+    for L in layers:
+        for t in range(T):
+            one.append((lib.GemvF32Args(w=lib.ptr(L["w_gate"]), w2=lib.ptr(L["w_up"]), w_extra=lib.ptr(L["sg"]), w2_extra=lib.ptr(L["su"]),
+                                        x=lib.ptr(x[t]), y=lib.ptr(inner1), n=K * I + I, k=H, eps=1e-6, pdl=1, epilogue=lib.EPI_SWIGLU,
+                                        expert_idx=lib.ptr(L["idx"][t]), rows_per_expert=I, routed_slots=K),
+                        lib.MoeDownF32Args(w_down=lib.ptr(L["w_down"]), w_shared=lib.ptr(L["sd"]), inner=lib.ptr(inner1),
+                                           indices=lib.ptr(L["idx"][t]), weights=lib.ptr(L["w"][t]),
+                                           shared_gate_logit=lib.ptr(L["gate"][t:t + 1]), out=lib.ptr(out1), hidden=H, inter=I,
+                                           shared_inter=I, top_k=K, pdl=1)))
+
+    def token_by_token():
+        for ga, da in one:
+            lib.check(lib.load().tfb_gemv_f32(C.byref(ga), lib.stream()), "tfb_gemv_f32")
+            lib.check(lib.load().tfb_moe_down_f32(C.byref(da), lib.stream()), "tfb_moe_down_f32")
+    try:
+        per_token_ms = _graph_time(token_by_token, n_layers, reps=3)
+    except Exception as exc:                                    # the comparison is a courtesy, not the measurement
+        per_token_ms = f"{type(exc).__name__}: {exc}"
+    line = {"mode": "moe_batch", "kernel": "moe_grouped_kernel (tcgen05.mma, K folded into N: 16 rows x 128 elements x 8 tokens per MMA)",
+            "config": {"workload": "Qwen3.5-35B-A3B expert block: 256 experts of 512 + shared expert, top-8, hidden 2048", "tokens": T},
+            "experts_touched_mean": sum(touched) / n_layers, "us_per_block": ms * 1e3,
+            "algorithmic_bytes": bytes_grouped, "GBs": bytes_grouped / (ms * 1e-3) / 1e9,
+            "frac_of_hbm_peak": bytes_grouped / (ms * 1e-3) / 1e9 / peak, "peak_GBs": peak, "peak_kind": kind,
+            "tokens_per_s_block_only": T / (ms * 1e-3),
+            "one_token_kernels_us_for_the_same_tokens": per_token_ms * 1e3 if isinstance(per_token_ms, float) else per_token_ms}
+    print(json.dumps(line))
+
+
 def run_batch32_projection(args):
     """The batch-32 form of the projections of the Qwen3-1.7B architecture: y[32, n] = x[32, k] . w[n, k]^T on the
     tensor cores, timed over distinct weight matrices (far more than L2) in one CUDA graph, as HBM GB/s of weight
@@ -782,6 +863,9 @@ def main():
     ap.add_argument("--batch32-projection", action="store_true",
                     help="time the batch-32 tensor-core projection (tcgen05) on this configuration's projection shapes, "
                          "print one JSON line and exit")
+    ap.add_argument("--moe-batch", type=int, default=0,
+                    help="time the Qwen3.5 expert block for this many tokens at once (tfb_moe_batch, e.g. 64), print one JSON "
+                         "line and exit")
     ap.add_argument("--batch", type=int, default=1,
                     help="decode this many independent Qwen3-1.7B sequences per step (2..32) on the tensor-core "
                          "projections, print one JSON line and exit")
@@ -803,6 +887,8 @@ def main():
         run_profile_case(args)
     elif args.impl == "reference":
         run_reference(args)
+    elif args.moe_batch > 0:
+        run_moe_batch(args)
     elif args.batch32_projection:
         run_batch32_projection(args)
     elif args.batch > 1:

@@ -743,7 +743,7 @@ TFB_API int tfb_gemm_small_m(const tfb_gemm_small_m_args* args, tfb_stream_t str
  * shared_expert; the reference's kernels, kernels/moe.py:368 `_h_kernel` and :527 `_down_kernel`, take one token).
  * Routing (indices, weights, the shared gate's logit) is the caller's: tfb_router_select per token.
  * Scratch (device, any contents): x_bf16 [tokens][hidden] bf16, inner [tokens][top_k+1][inter] bf16,
- * y [tokens][top_k+1][hidden] bf16, counts i32 [experts+1], lists i32 [experts+1][tokens]; status u32 zeroed once.
+ * y [tokens][top_k+1][hidden] bf16, counts i32 [2*(experts+1)+1], lists i32 [experts+1][tokens]; status u32 zeroed once.
  * hidden and inter multiples of 128 (inter of 8, hidden of 16), (16 + 8) * max(hidden, inter) * 2 <= 200 KB. */
 typedef struct {
     const float* x;             /* [tokens][hidden] f32 */

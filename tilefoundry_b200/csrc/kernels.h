@@ -383,7 +383,7 @@ struct MoeBatchParams {
     uint16_t* x_bf16;                // scratch bf16 [tokens][hidden]
     uint16_t* inner;                 // scratch bf16 [tokens][top_k + 1][inter]
     uint16_t* y;                     // scratch bf16 [tokens][top_k + 1][hidden]
-    int* counts;                     // scratch i32 [experts + 1]
+    int* counts;                     // scratch i32 [2 * (experts + 1) + 1]: tokens per expert, number of experts with tokens, their ids
     int* lists;                      // scratch i32 [experts + 1][tokens]
     unsigned* status;                // u32, set non-zero if a bounded wait gave up
     int tokens, hidden, inter, experts, top_k;

@@ -18,6 +18,8 @@
 #include "kernels.h"
 #include "launch.h"
 
+#include <algorithm>
+
 namespace tfb {
 namespace {
 
@@ -82,26 +84,45 @@ __global__ void __launch_bounds__(256) moe_batch_prepare_kernel(const MoeBatchPa
             p.x_bf16[i] = f32_to_bf16_bits(p.x[i]);
         return;
     }
-    // CTA 0: lists in token order (deterministic), by one thread per expert
+    // CTA 0: lists in token order (deterministic), one thread per expert; the routing table passes through shared
+    // memory in pieces (read straight from global memory, 512 dependent loads per thread took 70 us)
+    __shared__ short ids[1024];
     const int T = p.tokens, K = p.top_k, E = p.experts;
-    for (int e = threadIdx.x; e <= E; e += blockDim.x) {
-        int n = 0;
-        int* lst = p.lists + size_t(e) * T;
-        if (e == E) {
-            if (p.w_shared_gate) for (int t = 0; t < T; ++t) lst[n++] = (t << 8) | K;
-        } else {
-            for (int t = 0; t < T; ++t)
-                for (int s = 0; s < K; ++s)
-                    if (p.indices[size_t(t) * K + s] == (long long)e) lst[n++] = (t << 8) | s;
+    int n_mine[2] = {0, 0};                                    // (a thread has at most two experts: 257 <= 2 * 256)
+    for (int a0 = 0; a0 < T * K; a0 += 1024) {
+        const int na = min(1024, T * K - a0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < na; i += blockDim.x) ids[i] = short(p.indices[a0 + i]);
+        __syncthreads();
+        for (int q = 0, e = threadIdx.x; q < 2 && e < E; ++q, e += blockDim.x) {
+            int* lst = p.lists + size_t(e) * T;
+            int n = n_mine[q];
+            for (int i = 0; i < na; ++i)
+                if (ids[i] == short(e)) { const int a = a0 + i; lst[n++] = ((a / K) << 8) | (a % K); }
+            n_mine[q] = n;
         }
-        p.counts[e] = n;
+    }
+    for (int q = 0, e = threadIdx.x; q < 2 && e < E; ++q, e += blockDim.x) p.counts[e] = n_mine[q];
+    if (threadIdx.x == 0) {                                    // the shared expert takes every token, in slot K
+        int n = 0;
+        if (p.w_shared_gate) for (int t = 0; t < T; ++t) p.lists[size_t(E) * T + n++] = (t << 8) | K;
+        p.counts[E] = n;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {                                    // the experts that have tokens, in index order
+        int* active = p.counts + E + 2;
+        int na = 0;
+        for (int e = 0; e <= E; ++e)
+            if (p.counts[e] > 0) active[na++] = e;
+        p.counts[E + 1] = na;
     }
 }
 
 // ---- the grouped products -----------------------------------------------------------------------------------------
-// STAGE 0: gate/up + SwiGLU -- grid (inter / 8, experts + 1), tile rows 2i / 2i + 1 = gate / up row r0 + i, k = hidden,
+// STAGE 0: gate/up + SwiGLU -- inter / 8 row groups per expert, tile rows 2i / 2i + 1 = gate / up row r0 + i, k = hidden,
 //          activations x_bf16[token], result inner[token, slot, r0 + i].
-// STAGE 1: down -- grid (hidden / 16, experts + 1), tile rows = rows j0 .. j0 + 15 of W_down[e], k = inter,
+// Persistent: a CTA allocates its accumulator once and takes every gridDim.x-th (expert with tokens, row group).
+// STAGE 1: down -- hidden / 16 row groups per expert, tile rows = rows j0 .. j0 + 15 of W_down[e], k = inter,
 //          activations inner[token, slot], result y[token, slot, j0 + g].
 template <int STAGE>
 __global__ void __launch_bounds__(kGThreads) moe_grouped_kernel(const MoeBatchParams p) {
@@ -110,14 +131,15 @@ __global__ void __launch_bounds__(kGThreads) moe_grouped_kernel(const MoeBatchPa
     __shared__ uint32_t tmem_base;
     __shared__ int s_fail;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int e = blockIdx.y, E = p.experts, K = p.top_k, T = p.tokens;
+    const int E = p.experts, K = p.top_k, T = p.tokens;
     const int k = STAGE == 0 ? p.hidden : p.inter;              // reduction length
     const int row_bytes = k * 2;
+    const int RG = STAGE == 0 ? p.inter / (kGRows / 2) : p.hidden / kGRows;      // row groups of an expert
     pdl_trigger();
     pdl_wait();
-    const int n = p.counts[e];
-    if (n == 0) return;                                        // (uniform over the CTA, before anything is allocated)
-    const int* lst = p.lists + size_t(e) * T;
+    const int n_items = p.counts[E + 1] * RG;                  // (experts with tokens) x (row groups): a CTA takes every
+    if (int(blockIdx.x) >= n_items) return;                    //  gridDim.x-th item (uniform over the CTA, nothing allocated yet)
+    const int* active = p.counts + E + 2;
     unsigned char* tile = smem;                                // [16 rows][k] bf16
     unsigned char* xs = smem + kGRows * row_bytes;             // [8 tokens][k] bf16
 
@@ -134,107 +156,110 @@ __global__ void __launch_bounds__(kGThreads) moe_grouped_kernel(const MoeBatchPa
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = tmem_base;
+    const int trow = warp * 4 + (lane >> 3);                    // the tile row of this lane's team of eight
+    unsigned wpar = 0, xpar = 0, mpar = 0;
 
-    // the weight rows of this CTA: lane r of warp 0 copies tile row r
-    if (warp == 0) {
-        if (lane == 0) mb_expect_tx(&bar_w, unsigned(kGRows) * row_bytes);
-        __syncwarp();
-        if (lane < kGRows) {
-            const uint16_t* src;
-            if (STAGE == 0) {
-                const int r = blockIdx.x * (kGRows / 2) + (lane >> 1);
-                const uint16_t* base = e < E ? ((lane & 1) ? p.w_up : p.w_gate) + size_t(e) * p.inter * p.hidden
-                                             : ((lane & 1) ? p.w_shared_up : p.w_shared_gate);
-                src = base + size_t(r) * p.hidden;
-            } else {
-                const int j = blockIdx.x * kGRows + lane;
-                src = (e < E ? p.w_down + size_t(e) * p.hidden * p.inter : p.w_shared_down) + size_t(j) * p.inter;
-            }
-            bulk_load(tile + lane * row_bytes, src, row_bytes, &bar_w);
-        }
-    }
-
-    const int team = lane >> 3;                                 // the tile row of this lane's team: 4 * warp + team
-    const int trow = warp * 4 + team;
-    unsigned xpar = 0, mpar = 0;
-    bool ok = true;
-    for (int p0 = 0; p0 < n; p0 += kGTok) {
-        const int nb = min(kGTok, n - p0);
-        // this pass's activations: lane b of warp 1 copies token b's row
-        if (warp == 1) {
-            if (lane == 0) mb_expect_tx(&bar_x, unsigned(nb) * row_bytes);
+    for (int item = blockIdx.x; item < n_items && !s_fail; item += gridDim.x) {
+        const int e = active[item / RG], rg = item % RG;
+        const int n = p.counts[e];
+        const int* lst = p.lists + size_t(e) * T;
+        // the weight rows of this item: lane r of warp 0 copies tile row r (the MMAs that read the tile's last
+        // occupant have completed: every pass ends behind their barrier)
+        if (warp == 0) {
+            if (lane == 0) mb_expect_tx(&bar_w, unsigned(kGRows) * row_bytes);
             __syncwarp();
-            if (lane < nb) {
-                const int ent = lst[p0 + lane];
-                const uint16_t* src = STAGE == 0 ? p.x_bf16 + size_t(entry_token(ent)) * p.hidden
-                                                 : p.inner + (size_t(entry_token(ent)) * (K + 1) + entry_slot(ent)) * p.inter;
-                bulk_load(xs + lane * row_bytes, src, row_bytes, &bar_x);
+            if (lane < kGRows) {
+                const uint16_t* src;
+                if (STAGE == 0) {
+                    const int r = rg * (kGRows / 2) + (lane >> 1);
+                    const uint16_t* base = e < E ? ((lane & 1) ? p.w_up : p.w_gate) + size_t(e) * p.inter * p.hidden
+                                                 : ((lane & 1) ? p.w_shared_up : p.w_shared_gate);
+                    src = base + size_t(r) * p.hidden;
+                } else {
+                    const int j = rg * kGRows + lane;
+                    src = (e < E ? p.w_down + size_t(e) * p.hidden * p.inter : p.w_shared_down) + size_t(j) * p.inter;
+                }
+                bulk_load(tile + lane * row_bytes, src, row_bytes, &bar_w);
             }
         }
-        if (tid == 0) {
-            // the MMAs of the pass: one per 128 elements of K, all tokens at once
-            ok = (p0 > 0 || mb_wait(&bar_w, 0)) && mb_wait(&bar_x, xpar);
-            if (ok) {
-                const uint64_t da = folded_desc(s_u32(tile), row_bytes), db = folded_desc(s_u32(xs), row_bytes);
-                for (int t = 0; t < k / 128; ++t)
-                    umma_f16(tmem, da + uint64_t((t * 256) >> 4), db + uint64_t((t * 256) >> 4), kIdesc, t ? 1u : 0u);
-            } else {
-                s_fail = 1;
+        for (int p0 = 0; p0 < n; p0 += kGTok) {
+            const int nb = min(kGTok, n - p0);
+            // this pass's activations: lane b of warp 1 copies token b's row
+            if (warp == 1) {
+                if (lane == 0) mb_expect_tx(&bar_x, unsigned(nb) * row_bytes);
+                __syncwarp();
+                if (lane < nb) {
+                    const int ent = lst[p0 + lane];
+                    const uint16_t* src = STAGE == 0 ? p.x_bf16 + size_t(entry_token(ent)) * p.hidden
+                                                     : p.inner + (size_t(entry_token(ent)) * (K + 1) + entry_slot(ent)) * p.inter;
+                    bulk_load(xs + lane * row_bytes, src, row_bytes, &bar_x);
+                }
             }
-            umma_arrive(&bar_mma);
-        }
-        xpar ^= 1u;
-        // everyone waits for the accumulator
-        if (!mb_wait(&bar_mma, mpar)) { s_fail = 1; }
-        mpar ^= 1u;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        __syncthreads();
-        if (s_fail) break;                                      // (uniform after the barrier)
+            if (tid == 0) {
+                // the MMAs of the pass: one per 128 elements of K, all tokens at once
+                const bool ok = (p0 > 0 || mb_wait(&bar_w, wpar)) && mb_wait(&bar_x, xpar);
+                if (ok) {
+                    const uint64_t da = folded_desc(s_u32(tile), row_bytes), db = folded_desc(s_u32(xs), row_bytes);
+                    for (int t = 0; t < k / 128; ++t)
+                        umma_f16(tmem, da + uint64_t((t * 256) >> 4), db + uint64_t((t * 256) >> 4), kIdesc, t ? 1u : 0u);
+                } else {
+                    s_fail = 1;
+                }
+                umma_arrive(&bar_mma);
+            }
+            xpar ^= 1u;
+            if (!mb_wait(&bar_mma, mpar)) s_fail = 1;          // everyone waits for the accumulator
+            mpar ^= 1u;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            __syncthreads();
+            if (s_fail) break;                                  // (uniform after the barrier)
 
-        // epilogue: lane 8g + r of the quadrant wants, for token b, column 8b + r; a team of eight lanes sums the diagonal
-        uint32_t v[kGCols];
-        const uint32_t taddr = tmem + (uint32_t(warp * 32) << 16);
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x64.b32 "
-                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
-                     "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
-                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                       "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31]),
-                       "=r"(v[32]), "=r"(v[33]), "=r"(v[34]), "=r"(v[35]), "=r"(v[36]), "=r"(v[37]), "=r"(v[38]), "=r"(v[39]), "=r"(v[40]), "=r"(v[41]), "=r"(v[42]), "=r"(v[43]), "=r"(v[44]), "=r"(v[45]), "=r"(v[46]), "=r"(v[47]),
-                       "=r"(v[48]), "=r"(v[49]), "=r"(v[50]), "=r"(v[51]), "=r"(v[52]), "=r"(v[53]), "=r"(v[54]), "=r"(v[55]), "=r"(v[56]), "=r"(v[57]), "=r"(v[58]), "=r"(v[59]), "=r"(v[60]), "=r"(v[61]), "=r"(v[62]), "=r"(v[63])
-                     : "r"(taddr) : "memory");
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const bool b4 = lane & 4, b2 = lane & 2, b1 = lane & 1;
+            // epilogue: lane 8g + r of the quadrant wants, for token b, column 8b + r; a team of eight lanes sums the diagonal
+            uint32_t v[kGCols];
+            const uint32_t taddr = tmem + (uint32_t(warp * 32) << 16);
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+                         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+                         "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+                         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                           "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31]),
+                           "=r"(v[32]), "=r"(v[33]), "=r"(v[34]), "=r"(v[35]), "=r"(v[36]), "=r"(v[37]), "=r"(v[38]), "=r"(v[39]), "=r"(v[40]), "=r"(v[41]), "=r"(v[42]), "=r"(v[43]), "=r"(v[44]), "=r"(v[45]), "=r"(v[46]), "=r"(v[47]),
+                           "=r"(v[48]), "=r"(v[49]), "=r"(v[50]), "=r"(v[51]), "=r"(v[52]), "=r"(v[53]), "=r"(v[54]), "=r"(v[55]), "=r"(v[56]), "=r"(v[57]), "=r"(v[58]), "=r"(v[59]), "=r"(v[60]), "=r"(v[61]), "=r"(v[62]), "=r"(v[63])
+                         : "r"(taddr) : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            const bool b4 = lane & 4, b2 = lane & 2, b1 = lane & 1;
 #pragma unroll
-        for (int b = 0; b < kGTok; ++b) {
-            const uint32_t t0 = b4 ? v[8 * b + 4] : v[8 * b], t1 = b4 ? v[8 * b + 5] : v[8 * b + 1];
-            const uint32_t t2 = b4 ? v[8 * b + 6] : v[8 * b + 2], t3 = b4 ? v[8 * b + 7] : v[8 * b + 3];
-            const uint32_t q0 = b2 ? t2 : t0, q1 = b2 ? t3 : t1;
-            float d = __uint_as_float(b1 ? q1 : q0);
-            d += __shfl_xor_sync(0xffffffffu, d, 1);
-            d += __shfl_xor_sync(0xffffffffu, d, 2);
-            d += __shfl_xor_sync(0xffffffffu, d, 4);
-            if (STAGE == 0) {
-                const float up = round_bf16(__shfl_xor_sync(0xffffffffu, d, 8));     // (the team next door holds the up row)
-                if (b < nb && (lane & 15) == 0) {
-                    const int ent = lst[p0 + b];
-                    const int col = blockIdx.x * (kGRows / 2) + (trow >> 1);
-                    p.inner[(size_t(entry_token(ent)) * (K + 1) + entry_slot(ent)) * p.inter + col] =
-                        f32_to_bf16_bits(silu_f32(round_bf16(d)) * up);
-                }
-            } else {
-                if (b < nb && (lane & 7) == 0) {
-                    const int ent = lst[p0 + b];
-                    p.y[(size_t(entry_token(ent)) * (K + 1) + entry_slot(ent)) * p.hidden + blockIdx.x * kGRows + trow] = f32_to_bf16_bits(d);
+            for (int b = 0; b < kGTok; ++b) {
+                const uint32_t t0 = b4 ? v[8 * b + 4] : v[8 * b], t1 = b4 ? v[8 * b + 5] : v[8 * b + 1];
+                const uint32_t t2 = b4 ? v[8 * b + 6] : v[8 * b + 2], t3 = b4 ? v[8 * b + 7] : v[8 * b + 3];
+                const uint32_t q0 = b2 ? t2 : t0, q1 = b2 ? t3 : t1;
+                float d = __uint_as_float(b1 ? q1 : q0);
+                d += __shfl_xor_sync(0xffffffffu, d, 1);
+                d += __shfl_xor_sync(0xffffffffu, d, 2);
+                d += __shfl_xor_sync(0xffffffffu, d, 4);
+                if (STAGE == 0) {
+                    const float up = round_bf16(__shfl_xor_sync(0xffffffffu, d, 8));     // (the team next door holds the up row)
+                    if (b < nb && (lane & 15) == 0) {
+                        const int ent = lst[p0 + b];
+                        const int col = rg * (kGRows / 2) + (trow >> 1);
+                        p.inner[(size_t(entry_token(ent)) * (K + 1) + entry_slot(ent)) * p.inter + col] =
+                            f32_to_bf16_bits(silu_f32(round_bf16(d)) * up);
+                    }
+                } else {
+                    if (b < nb && (lane & 7) == 0) {
+                        const int ent = lst[p0 + b];
+                        p.y[(size_t(entry_token(ent)) * (K + 1) + entry_slot(ent)) * p.hidden + rg * kGRows + trow] = f32_to_bf16_bits(d);
+                    }
                 }
             }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncthreads();                                    // (the next pass overwrites the activations and the accumulator)
         }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();                                        // (the next pass overwrites the activations and the accumulator)
+        wpar ^= 1u;
     }
-    if (s_fail && tid == 0) atomicOr(p.status, 0x1000u);
-    if (s_fail && tid == 0) {                                   // MMAs may still be in flight: they end by themselves
-        umma_arrive(&bar_w);                                    // (a fresh completion to wait for, bounded)
-        mb_wait(&bar_w, 1);
+    if (s_fail && tid == 0) {
+        atomicOr(p.status, 0x1000u);
+        umma_arrive(&bar_mma);                                  // MMAs may still be in flight: they end by themselves, and this
+        mb_wait(&bar_mma, mpar);                                //  fresh completion is waited for (bounded) before the release
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -270,7 +295,7 @@ size_t moe_grouped_smem(int k) { return size_t(kGRows + kGTok) * k * 2; }
 
 bool moe_batch_supported(const MoeBatchParams& p) {
     auto ok_k = [](int k) { return k >= 128 && k % 128 == 0 && moe_grouped_smem(k) <= 200 * 1024; };
-    return p.tokens >= 1 && p.tokens <= 4096 && p.top_k >= 1 && p.top_k < 255 && p.experts >= 1 && ok_k(p.hidden) &&
+    return p.tokens >= 1 && p.tokens <= 4096 && p.top_k >= 1 && p.top_k < 255 && p.experts >= 1 && p.experts <= 512 && ok_k(p.hidden) &&
            ok_k(p.inter) && p.inter % (kGRows / 2) == 0 && p.hidden % kGRows == 0 &&
            (!p.w_shared_gate || (p.w_shared_up && p.w_shared_down));
 }
@@ -278,16 +303,33 @@ bool moe_batch_supported(const MoeBatchParams& p) {
 cudaError_t moe_batch_launch(const MoeBatchParams& p, cudaStream_t stream, bool pdl) {
     if (!moe_batch_supported(p)) return cudaErrorInvalidValue;
     static PerDeviceOnce once;
+    static int s_regs[2] = {96, 96};                           // registers per thread of the two stages (the same on every device)
     if (once.first()) {
         cudaError_t e = cudaFuncSetAttribute(moe_grouped_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(moe_grouped_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncAttributes fa;
+        if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, moe_grouped_kernel<0>);
+        if (e == cudaSuccess) s_regs[0] = fa.numRegs;
+        if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, moe_grouped_kernel<1>);
+        if (e == cudaSuccess) s_regs[1] = fa.numRegs;
         if (e != cudaSuccess) return e;
     }
     cudaError_t e = launch_kernel(moe_batch_prepare_kernel, dim3(1 + 64), dim3(256), 0, stream, pdl, p);
     if (e != cudaSuccess) return e;
-    e = launch_kernel(moe_grouped_kernel<0>, dim3(p.inter / (kGRows / 2), p.experts + 1), dim3(kGThreads), moe_grouped_smem(p.hidden), stream, pdl, p);
+    // persistent grids: as many CTAs as stay resident (two per multiprocessor by the 96 KB of the gate/up stage, eight by
+    // the 64 tensor-memory columns of the down stage), each taking every gridDim.x-th (expert, row group)
+    const int sms = sm_count();
+    const int max0 = p.inter / (kGRows / 2) * (p.experts + 1), max1 = p.hidden / kGRows * (p.experts + 1);
+    // CTAs that stay resident on a multiprocessor: by registers, shared memory and the 512 columns of tensor memory
+    auto resident = [](int regs, size_t smem) {
+        const int by_regs = 65536 / (((regs + 7) / 8 * 8) * kGThreads);
+        const int by_smem = int((227 * 1024) / (smem + 1024));
+        return std::max(1, std::min({by_regs, by_smem, 512 / kGCols}));
+    };
+    const int per0 = resident(s_regs[0], moe_grouped_smem(p.hidden)), per1 = resident(s_regs[1], moe_grouped_smem(p.inter));
+    e = launch_kernel(moe_grouped_kernel<0>, dim3(std::min(max0, sms * per0)), dim3(kGThreads), moe_grouped_smem(p.hidden), stream, pdl, p);
     if (e != cudaSuccess) return e;
-    e = launch_kernel(moe_grouped_kernel<1>, dim3(p.hidden / kGRows, p.experts + 1), dim3(kGThreads), moe_grouped_smem(p.inter), stream, pdl, p);
+    e = launch_kernel(moe_grouped_kernel<1>, dim3(std::min(max1, sms * per1)), dim3(kGThreads), moe_grouped_smem(p.inter), stream, pdl, p);
     if (e != cudaSuccess) return e;
     return launch_kernel(moe_batch_finalize_kernel, dim3((p.hidden + 255) / 256, p.tokens), dim3(256), 0, stream, pdl, p);
 }

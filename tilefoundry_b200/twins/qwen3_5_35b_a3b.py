@@ -216,7 +216,7 @@ def make_twin(cfg: authored.Qwen35Config = authored.QWEN3_5_35B_A3B):
             scratch = dict(x_bf16=torch.empty(T, H, device=dev, dtype=torch.bfloat16),
                            inner=torch.empty(T, K + 1, I, device=dev, dtype=torch.bfloat16),
                            y=torch.empty(T, K + 1, H, device=dev, dtype=torch.bfloat16),
-                           counts=torch.empty(E + 1, device=dev, dtype=torch.int32),
+                           counts=torch.empty(2 * (E + 1) + 1, device=dev, dtype=torch.int32),
                            lists=torch.empty(E + 1, T, device=dev, dtype=torch.int32))
             status = torch.zeros(1, device=dev, dtype=torch.int32)
             if IS != I:
