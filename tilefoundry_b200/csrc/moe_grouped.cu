@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(256) moe_batch_prepare_kernel(const MoeBatchPa
     // memory in pieces (read straight from global memory, 512 dependent loads per thread took 70 us)
     __shared__ short ids[1024];
     const int T = p.tokens, K = p.top_k, E = p.experts;
-    int n_mine[2] = {0, 0};                                    // (a thread has at most two experts: 257 <= 2 * 256)
+    int n_mine[2] = {0, 0};                                    // (a thread has at most two experts: experts <= 512)
     for (int a0 = 0; a0 < T * K; a0 += 1024) {
         const int na = min(1024, T * K - a0);
         __syncthreads();
@@ -102,18 +102,18 @@ __global__ void __launch_bounds__(256) moe_batch_prepare_kernel(const MoeBatchPa
             n_mine[q] = n;
         }
     }
-    for (int q = 0, e = threadIdx.x; q < 2 && e < E; ++q, e += blockDim.x) p.counts[e] = n_mine[q];
-    if (threadIdx.x == 0) {                                    // the shared expert takes every token, in slot K
-        int n = 0;
-        if (p.w_shared_gate) for (int t = 0; t < T; ++t) p.lists[size_t(E) * T + n++] = (t << 8) | K;
-        p.counts[E] = n;
-    }
+    __shared__ int s_cnt[513];
+    for (int q = 0, e = threadIdx.x; q < 2 && e < E; ++q, e += blockDim.x) { p.counts[e] = n_mine[q]; s_cnt[e] = n_mine[q]; }
+    // the shared expert takes every token, in slot K
+    const int n_shared = p.w_shared_gate ? T : 0;
+    for (int t = threadIdx.x; t < n_shared; t += blockDim.x) p.lists[size_t(E) * T + t] = (t << 8) | K;
+    if (threadIdx.x == 0) { p.counts[E] = n_shared; s_cnt[E] = n_shared; }
     __syncthreads();
     if (threadIdx.x == 0) {                                    // the experts that have tokens, in index order
         int* active = p.counts + E + 2;
         int na = 0;
         for (int e = 0; e <= E; ++e)
-            if (p.counts[e] > 0) active[na++] = e;
+            if (s_cnt[e] > 0) active[na++] = e;
         p.counts[E + 1] = na;
     }
 }
