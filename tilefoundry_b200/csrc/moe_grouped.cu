@@ -159,42 +159,50 @@ __global__ void __launch_bounds__(kGThreads) moe_grouped_kernel(const MoeBatchPa
     const int trow = warp * 4 + (lane >> 3);                    // the tile row of this lane's team of eight
     unsigned wpar = 0, xpar = 0, mpar = 0;
 
+    // the weight rows of an item: lane r of warp 0 copies tile row r
+    auto issue_tile = [&](int item) {
+        if (warp != 0) return;
+        const int e = active[item / RG], rg = item % RG;
+        if (lane == 0) mb_expect_tx(&bar_w, unsigned(kGRows) * row_bytes);
+        __syncwarp();
+        if (lane < kGRows) {
+            const uint16_t* src;
+            if (STAGE == 0) {
+                const int r = rg * (kGRows / 2) + (lane >> 1);
+                const uint16_t* base = e < E ? ((lane & 1) ? p.w_up : p.w_gate) + size_t(e) * p.inter * p.hidden
+                                             : ((lane & 1) ? p.w_shared_up : p.w_shared_gate);
+                src = base + size_t(r) * p.hidden;
+            } else {
+                const int j = rg * kGRows + lane;
+                src = (e < E ? p.w_down + size_t(e) * p.hidden * p.inter : p.w_shared_down) + size_t(j) * p.inter;
+            }
+            bulk_load(tile + lane * row_bytes, src, row_bytes, &bar_w);
+        }
+    };
+    // the activations of one pass over an item's tokens: lane b of warp 1 copies token b's row
+    auto issue_x = [&](int item, int p0) {
+        if (warp != 1) return;
+        const int e = active[item / RG];
+        const int nb = min(kGTok, p.counts[e] - p0);
+        const int* lst = p.lists + size_t(e) * T;
+        if (lane == 0) mb_expect_tx(&bar_x, unsigned(nb) * row_bytes);
+        __syncwarp();
+        if (lane < nb) {
+            const int ent = lst[p0 + lane];
+            const uint16_t* src = STAGE == 0 ? p.x_bf16 + size_t(entry_token(ent)) * p.hidden
+                                             : p.inner + (size_t(entry_token(ent)) * (K + 1) + entry_slot(ent)) * p.inter;
+            bulk_load(xs + lane * row_bytes, src, row_bytes, &bar_x);
+        }
+    };
+    issue_tile(blockIdx.x);
+    issue_x(blockIdx.x, 0);
     for (int item = blockIdx.x; item < n_items && !s_fail; item += gridDim.x) {
         const int e = active[item / RG], rg = item % RG;
         const int n = p.counts[e];
         const int* lst = p.lists + size_t(e) * T;
-        // the weight rows of this item: lane r of warp 0 copies tile row r (the MMAs that read the tile's last
-        // occupant have completed: every pass ends behind their barrier)
-        if (warp == 0) {
-            if (lane == 0) mb_expect_tx(&bar_w, unsigned(kGRows) * row_bytes);
-            __syncwarp();
-            if (lane < kGRows) {
-                const uint16_t* src;
-                if (STAGE == 0) {
-                    const int r = rg * (kGRows / 2) + (lane >> 1);
-                    const uint16_t* base = e < E ? ((lane & 1) ? p.w_up : p.w_gate) + size_t(e) * p.inter * p.hidden
-                                                 : ((lane & 1) ? p.w_shared_up : p.w_shared_gate);
-                    src = base + size_t(r) * p.hidden;
-                } else {
-                    const int j = rg * kGRows + lane;
-                    src = (e < E ? p.w_down + size_t(e) * p.hidden * p.inter : p.w_shared_down) + size_t(j) * p.inter;
-                }
-                bulk_load(tile + lane * row_bytes, src, row_bytes, &bar_w);
-            }
-        }
         for (int p0 = 0; p0 < n; p0 += kGTok) {
             const int nb = min(kGTok, n - p0);
-            // this pass's activations: lane b of warp 1 copies token b's row
-            if (warp == 1) {
-                if (lane == 0) mb_expect_tx(&bar_x, unsigned(nb) * row_bytes);
-                __syncwarp();
-                if (lane < nb) {
-                    const int ent = lst[p0 + lane];
-                    const uint16_t* src = STAGE == 0 ? p.x_bf16 + size_t(entry_token(ent)) * p.hidden
-                                                     : p.inner + (size_t(entry_token(ent)) * (K + 1) + entry_slot(ent)) * p.inter;
-                    bulk_load(xs + lane * row_bytes, src, row_bytes, &bar_x);
-                }
-            }
+            if (p0 > 0) issue_x(item, p0);                      // (the first pass's were asked for while the last item finished)
             if (tid == 0) {
                 // the MMAs of the pass: one per 128 elements of K, all tokens at once
                 const bool ok = (p0 > 0 || mb_wait(&bar_w, wpar)) && mb_wait(&bar_x, xpar);
@@ -213,6 +221,12 @@ __global__ void __launch_bounds__(kGThreads) moe_grouped_kernel(const MoeBatchPa
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             __syncthreads();
             if (s_fail) break;                                  // (uniform after the barrier)
+            // The rows and the activations have been read: the next item's can land while this pass's results are
+            // taken out of tensor memory.
+            if (p0 + kGTok >= n && item + int(gridDim.x) < n_items) {
+                issue_tile(item + gridDim.x);
+                issue_x(item + gridDim.x, 0);
+            }
 
             // epilogue: lane 8g + r of the quadrant wants, for token b, column 8b + r; a team of eight lanes sums the diagonal
             uint32_t v[kGCols];
@@ -259,7 +273,9 @@ __global__ void __launch_bounds__(kGThreads) moe_grouped_kernel(const MoeBatchPa
     if (s_fail && tid == 0) {
         atomicOr(p.status, 0x1000u);
         umma_arrive(&bar_mma);                                  // MMAs may still be in flight: they end by themselves, and this
-        mb_wait(&bar_mma, mpar);                                //  fresh completion is waited for (bounded) before the release
+        mb_wait(&bar_mma, mpar);                                //  fresh completion is waited for (bounded) before the release;
+        mb_wait(&bar_w, wpar);                                  //  so are copies that were asked for ahead (bounded: if none
+        mb_wait(&bar_x, xpar);                                  //  is in flight these give up after their limit)
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
