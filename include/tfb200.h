@@ -767,6 +767,22 @@ typedef struct {
     int32_t tokens, hidden, inter, experts, top_k, pdl;
 } tfb_moe_batch_args;
 TFB_API int tfb_moe_batch(const tfb_moe_batch_args* args, tfb_stream_t stream);
+/* Routing for the same batch: logits[t][e] = bf16(W_router[e] . bf16 x[t]) (row `experts`: the shared expert's scale row),
+ * then the selection of tfb_router_select (mode 0: top-k then softmax over the k; mode 1: softmax over all, top-k,
+ * renormalise) for every token, one CTA per token.  `routing` + the gate logit of `shared_expert` of the authored
+ * block for a batch (examples/qwen3_5_35b_a3b-tilelang/model.py: routing, shared_expert); weights are f32.
+ * hidden a multiple of 256 up to 8192, experts <= 256, top_k <= 32. */
+typedef struct {
+    const float* x;              /* [tokens][hidden] f32 */
+    const void* w_router;        /* bf16 [experts][hidden] */
+    const void* w_shared_scale;  /* optional bf16 [hidden] */
+    float* logits;               /* scratch [tokens][experts + 1] f32 */
+    int64_t* indices;            /* [tokens][top_k] */
+    float* weights;              /* [tokens][top_k] f32 */
+    float* shared_gate;          /* optional [tokens] f32 */
+    int32_t tokens, hidden, experts, top_k, mode, pdl;
+} tfb_moe_route_args;
+TFB_API int tfb_moe_batch_route(const tfb_moe_route_args* args, tfb_stream_t stream);
 
 /* ---- Qwen3-architecture decode step for several sequences (batch <= 32) ------------------------------------
  * One token for each of `batch` independent sequences: every projection runs once on the tensor cores for the

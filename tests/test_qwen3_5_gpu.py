@@ -143,6 +143,38 @@ def test_experts_for_a_batch_of_tokens(dev, sides, n_tokens):
     assert_close_at_scale(got[:1], one, "batch form against the one-token kernels")
 
 
+def test_block_forward_for_a_batch_of_tokens(dev, sides):
+    """Post-norm, routing and experts for 48 tokens in eight launches: the routing of every token equals the evaluator's
+    (experts bit-exact except across exactly equal or near-equal probabilities), the gate logits and weights are
+    close, and the block's output equals the evaluator's forward for every token whose routing agrees."""
+    cfg, ref, twin = sides[:3]
+    T = 48
+    g = torch.Generator().manual_seed(77)
+    rm, tm = ref.layer0.moe, twin.layer0.moe
+    hidden = torch.randn(T, 1, 1, cfg.hidden, generator=g)
+    tokens = torch.cat([rm.post_norm(h) for h in hidden])
+    got_w, got_idx, got_gate = (v.cpu() for v in tm.route_batch(tokens.to(dev)))
+    w_r = rm.router.constants["w_router"]
+    w_r = w_r if w_r.shape[0] == tokens.shape[-1] else w_r.t()
+    same, flips = [], []
+    for t in range(T):
+        want_w, want_idx = rm.router.routing(tokens[t:t + 1])
+        same.append(torch.equal(got_idx[t], want_idx.reshape(-1)))
+        if same[-1]:
+            assert_close_at_scale(got_w[t], want_w.reshape(-1), f"routing weights, token {t}")
+            continue
+        try:                                                   # an exact tie of bf16 logits may be taken in either order
+            parity.assert_same_routing(got_idx[t:t + 1], want_idx.reshape(1, -1), torch.matmul(tokens[t:t + 1].to(w_r.dtype), w_r), f"token {t}")
+        except AssertionError:                                 # a logit one bf16 step apart (the sums run in another order)
+            flips.append(t)
+    assert len(flips) <= 2, f"routing differs beyond exact ties on tokens {flips}"
+    assert sum(same) >= T // 2, f"routing differs on {T - sum(same)} of {T} tokens"      # (exact ties of bf16 logits are common)
+    got = tm.forward_batch(hidden.reshape(T, cfg.hidden).to(dev)).cpu()
+    for t in range(T):
+        if same[t]:
+            assert_close_at_scale(got[t], rm(hidden[t]).reshape(-1), f"block forward, token {t}")
+
+
 def test_root_functions(dev, sides):
     cfg, ref, twin = sides[:3]
     g = torch.Generator().manual_seed(2)

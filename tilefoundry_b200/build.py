@@ -19,7 +19,7 @@ FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-Xcudafe", "--diag_suppress=177"]
 # Approximate exp / division / rsqrt only where every output is a bf16-rounded activation.  The files that decide
 # integers (expert selection, its softmax) or carry f32 recurrent state across tokens keep IEEE arithmetic.
-PRECISE = frozenset({"moe.cu", "gemv_f32.cu", "mamba2.cu", "gdn.cu", "collective.cu"})
+PRECISE = frozenset({"moe.cu", "moe_grouped.cu", "gemv_f32.cu", "mamba2.cu", "gdn.cu", "collective.cu"})
 
 
 def flags_for(src: str) -> list:

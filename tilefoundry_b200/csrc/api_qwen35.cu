@@ -94,6 +94,20 @@ int tfb_attn_gated_decode(const tfb_attn_gated_args* a, tfb_stream_t stream) {
     return done(tfb::attn_gated_dispatch(p, S(stream), a->pdl != 0));
 }
 
+int tfb_moe_batch_route(const tfb_moe_route_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->x && a->w_router && a->logits && a->indices && a->weights, TFB_EINVAL);
+    TFB_REQUIRE(aligned16(a->x) && aligned16(a->w_router) && (!a->w_shared_scale || aligned16(a->w_shared_scale)), TFB_EALIGN);
+    TFB_REQUIRE(a->mode == 0 || a->mode == 1, TFB_EINVAL);
+    tfb::MoeRouteParams p;
+    std::memset(&p, 0, sizeof p);
+    p.x = a->x; p.w_router = static_cast<const uint16_t*>(a->w_router);
+    p.w_shared_scale = static_cast<const uint16_t*>(a->w_shared_scale);
+    p.logits = a->logits; p.indices = reinterpret_cast<long long*>(a->indices); p.weights = a->weights; p.shared_gate = a->shared_gate;
+    p.tokens = a->tokens; p.hidden = a->hidden; p.experts = a->experts; p.top_k = a->top_k; p.mode = a->mode;
+    const cudaError_t e = tfb::moe_batch_route_launch(p, S(stream), a->pdl != 0);
+    return e == cudaErrorInvalidValue ? TFB_EINVAL : done(e);
+}
+
 int tfb_moe_batch(const tfb_moe_batch_args* a, tfb_stream_t stream) {
     TFB_REQUIRE(a && a->x && a->indices && a->weights && a->w_gate && a->w_up && a->w_down && a->out, TFB_EINVAL);
     TFB_REQUIRE(a->x_bf16 && a->inner && a->y && a->counts && a->lists && a->status, TFB_EINVAL);

@@ -388,6 +388,17 @@ struct MoeBatchParams {
     unsigned* status;                // u32, set non-zero if a bounded wait gave up
     int tokens, hidden, inter, experts, top_k;
 };
+struct MoeRouteParams {
+    const float* x;                  // f32 [tokens][hidden]
+    const uint16_t* w_router;        // bf16 [experts][hidden]
+    const uint16_t* w_shared_scale;  // optional bf16 [hidden]: the row of the shared expert's gate
+    float* logits;                   // scratch f32 [tokens][experts + 1]
+    long long* indices;              // [tokens][top_k]
+    float* weights;                  // f32 [tokens][top_k]
+    float* shared_gate;              // optional f32 [tokens]
+    int tokens, hidden, experts, top_k, mode;
+};
+cudaError_t moe_batch_route_launch(const MoeRouteParams& p, cudaStream_t stream, bool pdl);
 bool moe_batch_supported(const MoeBatchParams& p);
 cudaError_t moe_batch_launch(const MoeBatchParams& p, cudaStream_t stream, bool pdl);
 

@@ -15,6 +15,7 @@
 // tcgen05.mma (M 128, N 64, K 16) per 128 elements of K whatever the number of tokens, accumulating in tensor memory;
 // token b's dot product with row g is the diagonal sum D[8g + r][8b + r].  HBM-bound: the touched experts' bytes once.
 #include "common.cuh"
+#include "route.cuh"
 #include "kernels.h"
 #include "launch.h"
 
@@ -73,6 +74,57 @@ constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(kGTok
 // one expert list entry: token in the high bits, slot (0 .. K) in the low eight
 __device__ __forceinline__ int entry_token(int e) { return e >> 8; }
 __device__ __forceinline__ int entry_slot(int e) { return e & 255; }
+
+// ---- routing of a batch: router logits, top-k, the shared expert's gate logit -- one CTA per token ----------------
+// logits[t][e] = bf16(W_router[e] . bf16 x_t) (the authored matmul: bf16 in, bf16 out), row `experts` = the shared
+// expert's scale row; then the selection of route_select (the rule of the one-token router kernel).
+template <int MAXE>
+__global__ void __launch_bounds__(256) moe_batch_route_kernel(const MoeRouteParams p) {
+    extern __shared__ __align__(16) float xr[];                // x_t rounded to bf16, as f32
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int H = p.hidden, E = p.experts;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) xr[i] = round_bf16(p.x[size_t(t) * H + i]);
+    __syncthreads();
+    float* logits = p.logits + size_t(t) * (E + 1);
+    const int rows = E + (p.w_shared_scale ? 1 : 0);
+    // a warp takes four rows at a time (rows r, r + 8, r + 16, r + 24): four independent chains of loads in flight
+    for (int r0 = warp; r0 < rows; r0 += 32) {
+        const uint4* w[4];
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int r = min(r0 + 8 * q, rows - 1);            // (a row past the end repeats the last one; not stored)
+            w[q] = reinterpret_cast<const uint4*>(r < E ? p.w_router + size_t(r) * H : p.w_shared_scale);
+        }
+#pragma unroll 8
+        for (int c = lane; c < (H >> 3); c += 32) {            // (unrolled: the loads of eight steps are requested together)
+            uint4 wv[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) wv[q] = __ldg(w[q] + c);
+            const float4 xa = *reinterpret_cast<const float4*>(xr + c * 8), xb = *reinterpret_cast<const float4*>(xr + c * 8 + 4);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) acc[q] = dot8(wv[q], xa, xb, acc[q]);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float sum = warp_sum(acc[q]);
+            if (lane == 0 && r0 + 8 * q < rows) logits[r0 + 8 * q] = round_bf16(sum);
+        }
+    }
+    __syncthreads();                                           // (the logits were written by this CTA: visible to it in L2)
+    if (warp == 0) {
+        float w;
+        int e;
+        route_select<MAXE>(logits, nullptr, E, p.top_k, p.mode, lane, w, e);
+        if (lane < p.top_k) {
+            p.indices[size_t(t) * p.top_k + lane] = e;
+            p.weights[size_t(t) * p.top_k + lane] = w;
+        }
+        if (lane == 0 && p.shared_gate) p.shared_gate[t] = p.w_shared_scale ? __ldcg(logits + E) : 0.f;
+    }
+}
 
 // ---- tokens f32 -> bf16 rows, and the experts' token lists ------------------------------------------------------
 __global__ void __launch_bounds__(256) moe_batch_prepare_kernel(const MoeBatchParams p) {
@@ -306,6 +358,15 @@ __global__ void __launch_bounds__(256) moe_batch_finalize_kernel(const MoeBatchP
 }
 
 }  // namespace
+
+cudaError_t moe_batch_route_launch(const MoeRouteParams& p, cudaStream_t stream, bool pdl) {
+    if (p.tokens < 1 || p.hidden < 256 || p.hidden % 256 != 0 || p.hidden > 8192 || p.experts < 1 || p.experts > 256 ||
+        p.top_k < 1 || p.top_k > 32 || p.top_k > p.experts)
+        return cudaErrorInvalidValue;
+    const size_t smem = size_t(p.hidden) * 4;
+    if (p.experts <= 128) return launch_kernel(moe_batch_route_kernel<128>, dim3(p.tokens), dim3(256), smem, stream, pdl, p);
+    return launch_kernel(moe_batch_route_kernel<256>, dim3(p.tokens), dim3(256), smem, stream, pdl, p);
+}
 
 size_t moe_grouped_smem(int k) { return size_t(kGRows + kGTok) * k * 2; }
 

@@ -107,6 +107,12 @@ class Qwen3PrefillArgs(C.Structure):
                 ("part_o", _vp), ("part_ml", _vp), ("counters", _vp), ("status", _vp)]
 
 
+class MoeRouteArgs(C.Structure):
+    _fields_ = [("x", _vp), ("w_router", _vp), ("w_shared_scale", _vp), ("logits", _vp), ("indices", _vp), ("weights", _vp),
+                ("shared_gate", _vp), ("tokens", _i32), ("hidden", _i32), ("experts", _i32), ("top_k", _i32), ("mode", _i32),
+                ("pdl", _i32)]
+
+
 class MoeBatchArgs(C.Structure):
     _fields_ = [("x", _vp), ("indices", _vp), ("weights", _vp), ("shared_gate", _vp), ("residual", _vp),
                 ("w_gate", _vp), ("w_up", _vp), ("w_down", _vp), ("w_shared_gate", _vp), ("w_shared_up", _vp),
@@ -282,6 +288,7 @@ SYMBOLS = {
     "tfb_last_error": (C.c_char_p, []),
     "tfb_debug_trace": (_i32, [_vp, _i32]),
     "tfb_moe_batch": (_i32, [C.POINTER(MoeBatchArgs), _vp]),
+    "tfb_moe_batch_route": (_i32, [C.POINTER(MoeRouteArgs), _vp]),
     "tfb_graph_step_host": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "tfb_graph_generate_host": (_i32, [_vp, _vp, _i64, _i32, _vp, _vp, _vp]),
     "tfb_embed": (_i32, [_vp, _vp, _vp, _i32, _i32, _i64, _f32, _vp]),

@@ -204,14 +204,42 @@ def make_twin(cfg: authored.Qwen35Config = authored.QWEN3_5_35B_A3B):
             logit = gemv(self._scale, x, 1, H, like=tokens)
             return self._down(tokens, inner, K, _flat(weights), idx, w_down, shared=True, gate_logit=logit).reshape(1, 1, H)
 
-        def experts_batch(self, tokens, weights, indices):
+        def route_batch(self, tokens):
+            """``routing`` and the shared expert's gate logit for a batch: tokens f32 [T, H] (post-norm) -> routing
+            weights f32 [T, K], indices int64 [T, K], gate logits f32 [T] (``tfb_moe_batch_route``)."""
+            T = tokens.shape[0]
+            x = tokens.contiguous()
+            dev = x.device
+            weights = torch.empty(T, K, device=dev, dtype=torch.float32)
+            indices = torch.empty(T, K, device=dev, dtype=torch.int64)
+            gate = torch.empty(T, device=dev, dtype=torch.float32)
+            logits = torch.empty(T, E + 1, device=dev, dtype=torch.float32)
+            a = lib.MoeRouteArgs(x=lib.ptr(x), w_router=lib.ptr(self.router._w), w_shared_scale=lib.ptr(self._scale),
+                                 logits=lib.ptr(logits), indices=lib.ptr(indices), weights=lib.ptr(weights),
+                                 shared_gate=lib.ptr(gate), tokens=T, hidden=H, experts=E, top_k=K, mode=1, pdl=0)
+            lib.check(L().tfb_moe_batch_route(C.byref(a), lib.stream()), "tfb_moe_batch_route")
+            return weights, indices, gate
+
+        def forward_batch(self, hidden):
+            """The block's forward for a batch: hidden f32 [T, H] -> f32 [T, H] (post-norm, routing, experts), four kernels
+            for the routing and the norm plus the four of ``tfb_moe_batch`` whatever the number of tokens."""
+            T = hidden.shape[0]
+            x = hidden.contiguous()
+            tokens = torch.empty_like(x)
+            lib.check(L().tfb_rmsnorm_f32(lib.ptr(x), lib.ptr(self._bound["gamma_post"]), lib.ptr(tokens), T, H, 1e-6, 0, lib.stream()),
+                      "tfb_rmsnorm_f32")
+            weights, indices, gate = self.route_batch(tokens)
+            return self.experts_batch(tokens, weights, indices, gate)
+
+        def experts_batch(self, tokens, weights, indices, gate_logits=None):
             """``experts`` for a batch: tokens f32 [T, H], routing weights f32 [T, K] and indices int64 [T, K] -> f32 [T, H].
             Every selected expert is read once for all of its tokens (``tfb_moe_batch``)."""
             b = self._bound
             T = tokens.shape[0]
             x = tokens.contiguous()
             dev = x.device
-            logits = torch.cat([gemv(self._scale, x[t], 1, H, like=x[t]) for t in range(T)]).contiguous()
+            logits = gate_logits if gate_logits is not None else \
+                torch.cat([gemv(self._scale, x[t], 1, H, like=x[t]) for t in range(T)]).contiguous()
             out = torch.empty(T, H, device=dev, dtype=torch.float32)
             scratch = dict(x_bf16=torch.empty(T, H, device=dev, dtype=torch.bfloat16),
                            inner=torch.empty(T, K + 1, I, device=dev, dtype=torch.bfloat16),
