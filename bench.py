@@ -312,6 +312,10 @@ def run_reference(args):
 
 
 def run_moe_batch(args):
+    print(json.dumps(moe_batch_summary(args.moe_batch)))
+
+
+def moe_batch_summary(T, dev=None, compare=True):
     """The Qwen3.5-35B-A3B expert block for a batch of tokens (`tfb_moe_batch`): 256 experts of 512, top-8, the shared
     expert, hidden 2048; random tokens routed by a random router, so ~222 experts are touched by 64 tokens.  Timed over
     several layers' expert sets (1.6 GB each, far more than L2) in one CUDA graph; bytes = the touched experts' three
@@ -322,8 +326,7 @@ def run_moe_batch(args):
     from tilefoundry_b200 import lib
 
     lib.load()
-    dev = torch.device("cuda:0")
-    T = args.moe_batch
+    dev = dev or torch.device("cuda:0")
     E, K, H, I = 256, 8, 2048, 512
     g = torch.Generator(device=dev).manual_seed(0)
     bf = torch.bfloat16
@@ -405,7 +408,7 @@ def run_moe_batch(args):
             lib.check(lib.load().tfb_gemv_f32(C.byref(ga), lib.stream()), "tfb_gemv_f32")
             lib.check(lib.load().tfb_moe_down_f32(C.byref(da), lib.stream()), "tfb_moe_down_f32")
     try:
-        per_token_ms = _graph_time(token_by_token, n_layers, reps=3)
+        per_token_ms = _graph_time(token_by_token, n_layers, reps=3) if compare else None
     except Exception as exc:                                    # the comparison is a courtesy, not the measurement
         per_token_ms = f"{type(exc).__name__}: {exc}"
     line = {"mode": "moe_batch", "kernel": "moe_grouped_kernel (tcgen05.mma, K folded into N: 16 rows x 128 elements x 8 tokens per MMA)",
@@ -415,7 +418,7 @@ def run_moe_batch(args):
             "frac_of_hbm_peak": bytes_grouped / (ms * 1e-3) / 1e9 / peak, "peak_GBs": peak, "peak_kind": kind,
             "us_per_block_with_norm_and_routing": ms_whole * 1e3,
             "one_token_kernels_us_for_the_same_tokens": per_token_ms * 1e3 if isinstance(per_token_ms, float) else per_token_ms}
-    print(json.dumps(line))
+    return line
 
 
 def run_batch32_projection(args):
@@ -810,6 +813,8 @@ def run_ours(args):
         Ks = min(K, 256)
         line["configs"] = {key: guarded(side_config, key, dev, Ks, W, not args.no_cpu)
                            for key in ("minicpm3_4b", "granite_4_0_h_small", "qwen3_5_35b_a3b")}
+        torch.cuda.empty_cache()
+        line["moe_batch64"] = guarded(moe_batch_summary, 64, dev, False)     # the Qwen3.5 expert block for 64 tokens at once
     if world > 1 and work.key == "qwen3_1_7b" and not args.no_sides:
         # The sharded MoE steps wait on one another across ranks inside kernels (bounded) and in barriers (not): a
         # watchdog prints the headline line and ends the process if this part does not finish in time.
