@@ -156,3 +156,37 @@ def test_several_sequence_step_rejects_bad_arguments(so):
     assert scall(table_len=8) == ECAPACITY                               # the block table does not cover max_ctx
     assert scall(max_tokens=4000) == ECAPACITY
     assert so.tfb_qwen3_batch_decode_step(None, None) == EINVAL
+
+
+def test_moe_batch_and_its_routing_reject_bad_arguments(so):
+    def a(**kw):
+        base = dict(x=P, indices=P, weights=P, w_gate=P, w_up=P, w_down=P, out=P, x_bf16=P, inner=P, y=P, counts=P, lists=P,
+                    status=P, tokens=64, hidden=2048, inter=512, experts=256, top_k=8)
+        base.update(kw)
+        return lib.MoeBatchArgs(**base)
+    call = lambda x: so.tfb_moe_batch(C.byref(x), None)
+    assert so.tfb_moe_batch(None, None) == EINVAL
+    assert call(a(x=None)) == EINVAL and call(a(out=None)) == EINVAL and call(a(counts=None)) == EINVAL
+    assert call(a(w_gate=ODD)) == EALIGN and call(a(inner=ODD)) == EALIGN
+    assert call(a(tokens=0)) == EINVAL and call(a(top_k=0)) == EINVAL and call(a(experts=600)) == EINVAL
+    assert call(a(hidden=2000)) == EINVAL                  # the reduction lengths are multiples of 128
+    assert call(a(inter=100)) == EINVAL
+    assert call(a(hidden=8192)) == EINVAL                  # 24 rows of it do not fit a CTA's shared memory
+    assert call(a(w_shared_gate=P)) == EINVAL              # a shared expert comes with all three matrices
+
+    def r(**kw):
+        base = dict(x=P, w_router=P, logits=P, indices=P, weights=P, tokens=64, hidden=2048, experts=256, top_k=8, mode=1)
+        base.update(kw)
+        return lib.MoeRouteArgs(**base)
+    route = lambda x: so.tfb_moe_batch_route(C.byref(x), None)
+    assert so.tfb_moe_batch_route(None, None) == EINVAL
+    assert route(r(logits=None)) == EINVAL and route(r(mode=2)) == EINVAL and route(r(w_router=ODD)) == EALIGN
+    assert route(r(experts=300)) == EINVAL and route(r(top_k=40)) == EINVAL and route(r(hidden=1000)) == EINVAL
+
+
+def test_host_driven_step_rejects_null_arguments(so):
+    assert so.tfb_graph_step_host(None, P, P, P, P, None) == EINVAL
+    assert so.tfb_graph_step_host(P, None, P, P, P, None) == EINVAL
+    assert so.tfb_graph_generate_host(P, P, -1, 4, P, None, None) == EINVAL
+    assert so.tfb_graph_generate_host(None, P, 0, 4, P, None, None) == EINVAL
+    assert so.tfb_graph_generate_host(P, P, 0, 0, P, None, None) == 0          # no steps: nothing is touched
