@@ -169,10 +169,13 @@ __global__ void __launch_bounds__(1024) moe_batch_prepare_kernel(const MoeBatchP
     for (int t = threadIdx.x; t < n_shared; t += blockDim.x) p.lists[size_t(E) * T + t] = (t << 8) | K;
     if (threadIdx.x == 0) { p.counts[E] = n_shared; s_cnt[E] = n_shared; }
     __syncthreads();
-    if (threadIdx.x == 0) {                                    // the experts that have tokens, in index order
+    if (threadIdx.x == 0) {
+        // the experts that have tokens: the shared expert first (every token is its: its items take the most passes, and
+        // items are dealt round-robin, so the longest go out first), then the routed ones in index order
         int* active = p.counts + E + 2;
         int na = 0;
-        for (int e = 0; e <= E; ++e)
+        if (s_cnt[E] > 0) active[na++] = E;
+        for (int e = 0; e < E; ++e)
             if (s_cnt[e] > 0) active[na++] = e;
         p.counts[E + 1] = na;
     }
