@@ -4,7 +4,7 @@ where they lie in the reference tree, for sm_100a:
     python -m oracle.build_ref [--force]
 
 Source: ``examples/granite_4_0_h_small-cuda/kernels/granite.cu`` of the reference checkout (path in
-``TILEFOUNDRY_REFERENCE``, default ``/root/reference``); recipe: the flags of the reference's own
+``TILEFOUNDRY_REFERENCE``, default: a ``reference`` directory beside this repository); recipe: the flags of the reference's own
 ``kernels/__init__.py:24-41`` with the architecture switched the way its ``GRANITE_CUDA_ARCH`` switch does
 (``:14``).  Output: ``oracle/_ref/granite/granite_ref_kernels.so`` only -- no reference source is copied.
 The library is used by ``tests/test_granite_reference_kernels_gpu.py`` to hold the evaluator restatement
@@ -22,7 +22,7 @@ NAME = "granite_ref_kernels"
 
 
 def reference_source() -> Path:
-    root = Path(os.environ.get("TILEFOUNDRY_REFERENCE", "/root/reference"))
+    root = Path(os.environ.get("TILEFOUNDRY_REFERENCE") or HERE.parents[1] / "reference")
     return root / "examples" / "granite_4_0_h_small-cuda" / "kernels" / "granite.cu"
 
 
