@@ -291,40 +291,44 @@ __global__ void __launch_bounds__(kGThreads) moe_grouped_kernel(const MoeBatchPa
                 issue_x(item + gridDim.x, 0);
             }
 
-            // epilogue: lane 8g + r of the quadrant wants, for token b, column 8b + r; a team of eight lanes sums the diagonal
-            uint32_t v[kGCols];
-            const uint32_t taddr = tmem + (uint32_t(warp * 32) << 16);
-            asm volatile("tcgen05.ld.sync.aligned.32x32b.x64.b32 "
-                         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
-                         "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
-                         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                           "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31]),
-                           "=r"(v[32]), "=r"(v[33]), "=r"(v[34]), "=r"(v[35]), "=r"(v[36]), "=r"(v[37]), "=r"(v[38]), "=r"(v[39]), "=r"(v[40]), "=r"(v[41]), "=r"(v[42]), "=r"(v[43]), "=r"(v[44]), "=r"(v[45]), "=r"(v[46]), "=r"(v[47]),
-                           "=r"(v[48]), "=r"(v[49]), "=r"(v[50]), "=r"(v[51]), "=r"(v[52]), "=r"(v[53]), "=r"(v[54]), "=r"(v[55]), "=r"(v[56]), "=r"(v[57]), "=r"(v[58]), "=r"(v[59]), "=r"(v[60]), "=r"(v[61]), "=r"(v[62]), "=r"(v[63])
-                         : "r"(taddr) : "memory");
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            // epilogue: lane 8g + r of the quadrant wants, for token b, column 8b + r; a team of eight lanes sums the
+            // diagonal.  Four tokens (32 columns) at a time: 64 values in registers cost the down stage three of its
+            // eight resident CTAs.
             const bool b4 = lane & 4, b2 = lane & 2, b1 = lane & 1;
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+                if (half * 4 >= nb) break;                      // (uniform: no token in the second half)
+                uint32_t v[32];
+                const uint32_t taddr = tmem + (uint32_t(warp * 32) << 16) + uint32_t(half * 32);
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                               "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                             : "r"(taddr) : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int b = 0; b < kGTok; ++b) {
-                const uint32_t t0 = b4 ? v[8 * b + 4] : v[8 * b], t1 = b4 ? v[8 * b + 5] : v[8 * b + 1];
-                const uint32_t t2 = b4 ? v[8 * b + 6] : v[8 * b + 2], t3 = b4 ? v[8 * b + 7] : v[8 * b + 3];
-                const uint32_t q0 = b2 ? t2 : t0, q1 = b2 ? t3 : t1;
-                float d = __uint_as_float(b1 ? q1 : q0);
-                d += __shfl_xor_sync(0xffffffffu, d, 1);
-                d += __shfl_xor_sync(0xffffffffu, d, 2);
-                d += __shfl_xor_sync(0xffffffffu, d, 4);
-                if (STAGE == 0) {
-                    const float up = round_bf16(__shfl_xor_sync(0xffffffffu, d, 8));     // (the team next door holds the up row)
-                    if (b < nb && (lane & 15) == 0) {
-                        const int ent = lst[p0 + b];
-                        const int col = rg * (kGRows / 2) + (trow >> 1);
-                        p.inner[(size_t(entry_token(ent)) * (K + 1) + entry_slot(ent)) * p.inter + col] =
-                            f32_to_bf16_bits(silu_f32(round_bf16(d)) * up);
-                    }
-                } else {
-                    if (b < nb && (lane & 7) == 0) {
-                        const int ent = lst[p0 + b];
-                        p.y[(size_t(entry_token(ent)) * (K + 1) + entry_slot(ent)) * p.hidden + rg * kGRows + trow] = f32_to_bf16_bits(d);
+                for (int bb = 0; bb < 4; ++bb) {
+                    const int b = half * 4 + bb;
+                    const uint32_t t0 = b4 ? v[8 * bb + 4] : v[8 * bb], t1 = b4 ? v[8 * bb + 5] : v[8 * bb + 1];
+                    const uint32_t t2 = b4 ? v[8 * bb + 6] : v[8 * bb + 2], t3 = b4 ? v[8 * bb + 7] : v[8 * bb + 3];
+                    const uint32_t q0 = b2 ? t2 : t0, q1 = b2 ? t3 : t1;
+                    float d = __uint_as_float(b1 ? q1 : q0);
+                    d += __shfl_xor_sync(0xffffffffu, d, 1);
+                    d += __shfl_xor_sync(0xffffffffu, d, 2);
+                    d += __shfl_xor_sync(0xffffffffu, d, 4);
+                    if (STAGE == 0) {
+                        const float up = round_bf16(__shfl_xor_sync(0xffffffffu, d, 8));     // (the team next door holds the up row)
+                        if (b < nb && (lane & 15) == 0) {
+                            const int ent = lst[p0 + b];
+                            const int col = rg * (kGRows / 2) + (trow >> 1);
+                            p.inner[(size_t(entry_token(ent)) * (K + 1) + entry_slot(ent)) * p.inter + col] =
+                                f32_to_bf16_bits(silu_f32(round_bf16(d)) * up);
+                        }
+                    } else {
+                        if (b < nb && (lane & 7) == 0) {
+                            const int ent = lst[p0 + b];
+                            p.y[(size_t(entry_token(ent)) * (K + 1) + entry_slot(ent)) * p.hidden + rg * kGRows + trow] = f32_to_bf16_bits(d);
+                        }
                     }
                 }
             }
