@@ -734,6 +734,36 @@ TFB_API int32_t tfb_gemm_small_m_splits(int32_t n, int32_t k);
 TFB_API int32_t tfb_gemm_small_m_swiglu_splits(int32_t n, int32_t k);
 TFB_API int tfb_gemm_small_m(const tfb_gemm_small_m_args* args, tfb_stream_t stream);
 
+/* ---- nucleus (top-p) sampling after a decode step ------------------------------------------------------------
+ * Replaces the token a decode step has just written by a draw from the nucleus of softmax(logits / temperature): the
+ * distinct logit values are walked from the largest down, adding count(value) * exp((value - max) / temperature) in
+ * f64; the first value at which the running mass reaches top_p * total is the threshold, and every token whose logit
+ * is at least that value belongs (ties included).  Inside the nucleus the pick is the Gumbel-max rule of
+ * tfb_lm_head_args (same variates: top_p = 1 draws what the head kernel draws).  The reference's sampler has
+ * temperature only (examples/granite_4_0_h_small-cuda/kernels/granite.cu:712-797); this is the filter its
+ * generation loop would apply on the host.
+ *   logits:   bf16 [vocab], kept by the step (its `logits` argument)
+ *   pos:      the step's position scalar, after the step; prev_pos: a copy taken before the step
+ *   tokens:   the history; tokens[*pos] is rewritten when *pos != *prev_pos and *pos >= n_prompt
+ *   eos_ids / n_eos / stop_at: the end-of-sequence latch of tfb_lm_head_args, applied to the new token (give the step
+ *             itself no end ids then); a latched sequence is left alone
+ *   hist:     scratch int32 [65536]                threshold_out: optional, the smallest logit value inside the nucleus */
+typedef struct {
+    const void* logits;
+    const int32_t* pos;
+    const int32_t* prev_pos;
+    int64_t* tokens;
+    int64_t* picked;            /* optional */
+    float* threshold_out;       /* optional */
+    const int64_t* eos_ids;
+    int32_t* stop_at;
+    int32_t* hist;
+    int32_t vocab, n_prompt, n_eos, pdl;
+    float temperature, top_p;
+    uint64_t seed;
+} tfb_sample_top_p_args;
+TFB_API int tfb_sample_top_p(const tfb_sample_top_p_args* args, tfb_stream_t stream);
+
 /* ---- mixture-of-experts block for a batch of tokens -----------------------------------------------------------
  * out[t] = residual[t] + sum_s weights[t,s] * bf16(W_down[e] . bf16(silu(bf16(W_gate[e] . bf16 x[t])) * bf16(W_up[e] . bf16 x[t])))
  *          + (the same through the shared expert) * sigmoid(shared_gate[t]),            e = indices[t,s]

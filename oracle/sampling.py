@@ -35,3 +35,32 @@ def gumbel_scores(logits: np.ndarray, temperature: float, seed: int, step: int, 
 def sample(logits: np.ndarray, temperature: float, seed: int, step: int, index_offset: int = 0) -> int:
     """Lowest index of the largest perturbed score."""
     return int(np.argmax(gumbel_scores(logits, temperature, seed, step, index_offset)))
+
+
+def _bf16_keys(logits: np.ndarray) -> np.ndarray:
+    """Order-preserving 16-bit keys of bf16 values given as f32 (the kernel's histogram index)."""
+    bits = (logits.astype(np.float32).view(np.uint32) >> np.uint32(16)).astype(np.uint32)
+    neg = (bits & np.uint32(0x8000)) != 0
+    return np.where(neg, ~bits & np.uint32(0xFFFF), bits | np.uint32(0x8000)).astype(np.int64)
+
+
+def nucleus_threshold(logits: np.ndarray, temperature: float, top_p: float) -> float:
+    """The smallest logit value inside the nucleus: distinct values from the largest down, mass count * exp((value - max)
+    / T) in f64, the first value at which the running mass reaches top_p * total."""
+    keys = _bf16_keys(logits)
+    counts = np.bincount(keys, minlength=65536)
+    present = np.nonzero(counts)[0][::-1]                          # descending keys
+    bits = np.where(present & 0x8000, present & 0x7FFF, ~present & 0xFFFF).astype(np.uint32) << np.uint32(16)
+    values = bits.view(np.float32).astype(np.float64)
+    mass = counts[present] * np.exp((values - values[0]) / np.float64(np.float32(temperature)))
+    run = np.cumsum(mass)
+    k = int(np.searchsorted(run, np.float64(np.float32(top_p)) * run[-1], side="left"))
+    return float(values[min(k, len(values) - 1)])
+
+
+def sample_top_p(logits: np.ndarray, temperature: float, top_p: float, seed: int, step: int) -> int:
+    """Gumbel-max pick among the tokens whose logit is at least the nucleus threshold (lowest index on ties)."""
+    tau = nucleus_threshold(logits, temperature, top_p)
+    scores = gumbel_scores(logits, temperature, seed, step)
+    scores = np.where(logits.astype(np.float32) >= np.float32(tau), scores, -np.inf)
+    return int(np.argmax(scores))

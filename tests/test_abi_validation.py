@@ -190,3 +190,17 @@ def test_host_driven_step_rejects_null_arguments(so):
     assert so.tfb_graph_generate_host(P, P, -1, 4, P, None, None) == EINVAL
     assert so.tfb_graph_generate_host(None, P, 0, 4, P, None, None) == EINVAL
     assert so.tfb_graph_generate_host(P, P, 0, 0, P, None, None) == 0          # no steps: nothing is touched
+
+
+def test_nucleus_sampling_rejects_bad_arguments(so):
+    def a(**kw):
+        base = dict(logits=P, pos=P, prev_pos=P, tokens=P, hist=P, vocab=1024, temperature=0.8, top_p=0.9)
+        base.update(kw)
+        return lib.SampleTopPArgs(**base)
+    call = lambda x: so.tfb_sample_top_p(C.byref(x), None)
+    assert so.tfb_sample_top_p(None, None) == EINVAL
+    assert call(a(logits=None)) == EINVAL and call(a(prev_pos=None)) == EINVAL and call(a(hist=None)) == EINVAL
+    assert call(a(temperature=0.0)) == EINVAL and call(a(top_p=0.0)) == EINVAL and call(a(top_p=1.5)) == EINVAL
+    assert call(a(vocab=0)) == EINVAL
+    assert call(a(n_eos=2)) == EINVAL and call(a(n_eos=2, eos_ids=P)) == EINVAL      # end ids come with their latch
+    assert call(a(n_eos=17, eos_ids=P, stop_at=P)) == EINVAL

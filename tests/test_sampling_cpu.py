@@ -32,3 +32,24 @@ def test_gumbel_max_draws_from_softmax():
         assert 0.5 * np.abs(counts / counts.sum() - want).sum() < 0.02
     # temperature -> 0 approaches the greedy pick
     assert all(sampling.sample(logits, 1e-3, 5, s) == 0 for s in range(50))
+
+
+def test_nucleus_threshold_and_pick():
+    rng = np.random.default_rng(3)
+    import torch
+    logits = (torch.from_numpy(rng.standard_normal(4000).astype(np.float32)) * 2).to(torch.bfloat16).float().numpy()
+    for temperature in (0.7, 1.0):
+        p = np.exp((logits.astype(np.float64) - logits.max()) / temperature)
+        p /= p.sum()
+        for top_p in (0.05, 0.5, 0.9):
+            tau = sampling.nucleus_threshold(logits, temperature, top_p)
+            assert p[logits >= tau].sum() >= top_p - 1e-12           # the nucleus holds the mass asked for ...
+            assert p[logits > tau].sum() < top_p + 1e-12             # ... and would not without the threshold's own tokens
+            picks = {sampling.sample_top_p(logits, temperature, top_p, 5, s) for s in range(300)}
+            assert all(logits[i] >= tau for i in picks) and (len(picks) > 1 or (logits >= tau).sum() == 1)
+        # the whole distribution: the plain draw
+        assert all(sampling.sample_top_p(logits, temperature, 1.0, 5, s) == sampling.sample(logits, temperature, 5, s) for s in range(50))
+    # a nucleus of one value: always the (lowest-index) maximum when it alone carries the mass
+    spike = np.full(100, -20.0, dtype=np.float32)
+    spike[17] = 10.0
+    assert all(sampling.sample_top_p(spike, 1.0, 0.9, 1, s) == 17 for s in range(20))

@@ -158,6 +158,38 @@ def test_one_launch_step_samples_with_the_same_rule(dev):
     assert other != one and greedy != one
 
 
+def test_nucleus_sampling_after_the_step(dev):
+    """``top_p`` < 1: every new token is the nucleus draw of the CPU restatement on the step's own logits, for the
+    one-launch step and the step of separate launches; reproducible; ``top_p`` close to 0 draws among the top value's tokens; an end
+    id picked by the nucleus draw latches the sequence."""
+    from tilefoundry_b200.engine.qwen3 import KERNEL_FUSED, Qwen3Session
+    cfg = q.QWEN3_SMALL
+    weights = q.tie_head(random_weights(q.build(cfg), seed=5, std=0.05))
+    res = DictResource({k: v.to(dev) for k, v in weights.items()})
+    prompt = torch.randint(0, cfg.vocab_size, (12,), generator=torch.Generator().manual_seed(2))
+    for kernel in (KERNEL_FUSED, 0):
+        a = Qwen3Session(cfg, res, max_ctx=128, device=dev, temperature=0.8, seed=42, top_p=0.6, kernel=kernel)
+        one = a.generate(prompt, 40, use_graph=True).tokens
+        two = a.generate(prompt, 40, use_graph=False).tokens
+        if kernel == KERNEL_FUSED:
+            a.check_status()
+        assert one == two
+        for n_new in (1, 9, 40):                                   # draws against the step's own logits
+            t = a.generate(prompt, n_new, use_graph=False).tokens
+            assert t == one[:n_new]
+            want = sampling.sample_top_p(a.logits.float().cpu().numpy(), 0.8, 0.6, 42, int(a.pos) - 1)
+            assert t[-1] == want, (kernel, n_new, t[-1], want)
+        plain = Qwen3Session(cfg, res, max_ctx=128, device=dev, temperature=0.8, seed=42, kernel=kernel).generate(prompt, 40).tokens
+        assert plain != one                                        # the filter changes the draws
+        tight = Qwen3Session(cfg, res, max_ctx=128, device=dev, temperature=0.8, seed=42, top_p=1e-6, kernel=kernel)
+        for n_new in (1, 7, 25):                                   # a nucleus of the top VALUE alone (several tokens may share it)
+            last = tight.generate(prompt, n_new, use_graph=False).tokens[-1]
+            assert float(tight.logits[last]) == float(tight.logits.max())
+        stop = one[5]
+        cut = a.generate(prompt, 40, eos=[stop]).tokens
+        assert cut == one[:one.index(stop)]
+
+
 @pytest.mark.parametrize("model", ["minicpm3", "granite", "qwen3_5"])
 def test_other_sessions_sample_too(dev, model):
     """The other three decode steps hand temperature and seed to the same head kernel."""

@@ -40,6 +40,21 @@ int tfb_debug_trace(void* device_buffer, int32_t capacity) {
     return TFB_OK;
 }
 
+int tfb_sample_top_p(const tfb_sample_top_p_args* a, tfb_stream_t stream) {
+    TFB_REQUIRE(a && a->logits && a->pos && a->prev_pos && a->tokens && a->hist, TFB_EINVAL);
+    TFB_REQUIRE(a->vocab > 0 && a->temperature > 0.f && a->top_p > 0.f && a->top_p <= 1.f, TFB_EINVAL);
+    TFB_REQUIRE(a->n_eos >= 0 && a->n_eos <= 16 && (a->n_eos == 0 || (a->eos_ids && a->stop_at)), TFB_EINVAL);
+    tfb::TopPParams p;
+    std::memset(&p, 0, sizeof p);
+    p.logits = static_cast<const uint16_t*>(a->logits); p.vocab = a->vocab;
+    p.temperature = a->temperature; p.top_p = a->top_p; p.seed = a->seed;
+    p.pos = a->pos; p.prev_pos = a->prev_pos; p.tokens = reinterpret_cast<long long*>(a->tokens); p.n_prompt = a->n_prompt;
+    p.picked = reinterpret_cast<long long*>(a->picked); p.threshold_out = a->threshold_out;
+    p.eos_ids = reinterpret_cast<const long long*>(a->eos_ids); p.n_eos = a->eos_ids ? a->n_eos : 0; p.stop_at = a->stop_at;
+    p.hist = a->hist;
+    return done(tfb::sample_top_p_launch(p, S(stream), a->pdl != 0));
+}
+
 int tfb_graph_step_host(void* graph_exec, void* token_slot, const int64_t* token_in_host, const void* picked,
                         int64_t* token_out_host, tfb_stream_t stream) {
     TFB_REQUIRE(graph_exec && token_slot && token_in_host && picked && token_out_host, TFB_EINVAL);

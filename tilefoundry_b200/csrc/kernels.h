@@ -101,6 +101,23 @@ struct HeadParams {
     int n_eos;
     int* stop_at;
 };
+struct TopPParams {
+    const uint16_t* logits;     // bf16 [vocab]: the logits the step before kept
+    int vocab;
+    float temperature, top_p;
+    unsigned long long seed;
+    const int* pos;             // the position after that step
+    const int* prev_pos;        // ... and before it
+    long long* tokens;
+    int n_prompt;
+    long long* picked;          // optional
+    float* threshold_out;       // optional: the smallest logit value inside the nucleus
+    const long long* eos_ids;
+    int n_eos;
+    int* stop_at;
+    int* hist;                  // scratch i32 [65536]
+};
+cudaError_t sample_top_p_launch(const TopPParams& p, cudaStream_t stream, bool pdl);
 int lm_head_ctas(int n);
 cudaError_t lm_head_dispatch(const HeadParams& p, int norm_mode, cudaStream_t stream, bool pdl);
 

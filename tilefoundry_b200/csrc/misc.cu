@@ -319,4 +319,104 @@ cudaError_t residual_add_f32_launch(const float* a, const float* b, float* out, 
     return launch_kernel(residual_add_f32_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, pdl, a, b, out, n);
 }
 
+// ---- nucleus (top-p) sampling over a row of bf16 logits -----------------------------------------------------------
+// The nucleus: walk the distinct logit VALUES from the largest down, adding count(value) * exp((value - max) / T); the
+// first value at which the running mass reaches top_p * (total mass) is the threshold, and every token whose logit is
+// at least that value belongs (ties included).  bf16 logits have at most 65536 distinct values, so the walk is over a
+// histogram of integer counts (exact, whatever the order of the atomics) and the masses are f64: the threshold does not
+// depend on summation order beyond the last bit of a double.  Inside the nucleus the pick is the Gumbel-max rule of the
+// head kernel (same variates), so top_p = 1 draws what the head kernel draws.
+// One CTA: the kernel follows a decode step that kept its logits; it replaces the token that step wrote.
+__device__ __forceinline__ unsigned bf16_key(uint16_t b) { return (b & 0x8000u) ? (~unsigned(b) & 0xffffu) : (unsigned(b) | 0x8000u); }
+__device__ __forceinline__ float bf16_of_key(unsigned key) {
+    return bf16_bits_to_f32(uint16_t((key & 0x8000u) ? (key & 0x7fffu) : (~key & 0xffffu)));
+}
+constexpr int kTopPThreads = 1024;
+
+__global__ void __launch_bounds__(kTopPThreads) sample_top_p_kernel(const TopPParams p) {
+    __shared__ double s_part[kTopPThreads];
+    __shared__ float s_val[kTopPThreads / 32];
+    __shared__ int s_idx[kTopPThreads / 32];
+    __shared__ unsigned s_maxkey, s_tau;
+    pdl_trigger();
+    pdl_wait();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (p.stop_at && *p.stop_at != 0) return;                  // the sequence has ended
+    const int slot = *p.pos, step = *p.prev_pos;               // the step before this kernel moved pos from `step` to `slot`
+    if (slot == step || slot < p.n_prompt) return;             // it did not advance, or the slot belongs to the prompt
+    if (tid == 0) s_maxkey = 0u;
+    for (int k = tid; k < 65536; k += kTopPThreads) p.hist[k] = 0;
+    __syncthreads();
+    unsigned mk = 0u;
+    for (int i = tid; i < p.vocab; i += kTopPThreads) {
+        const unsigned key = bf16_key(p.logits[i]);
+        atomicAdd(p.hist + key, 1);
+        mk = max(mk, key);
+    }
+    atomicMax(&s_maxkey, mk);
+    __syncthreads();
+    const double m = double(bf16_of_key(s_maxkey)), inv_t = 1.0 / double(p.temperature);
+    // thread t owns keys 65535 - 64 t down to 65535 - 64 t - 63
+    constexpr int PER = 65536 / kTopPThreads;
+    double mine = 0.0;
+    for (int q = 0; q < PER; ++q) {
+        const unsigned key = 65535u - unsigned(tid * PER + q);
+        const int c = p.hist[key];
+        if (c) mine += double(c) * exp((double(bf16_of_key(key)) - m) * inv_t);
+    }
+    s_part[tid] = mine;
+    __syncthreads();
+    if (tid == 0) {                                            // the walk over the threads' masses, in key order
+        double total = 0.0;
+        for (int t = 0; t < kTopPThreads; ++t) total += s_part[t];
+        const double target = double(p.top_p) * total;
+        double run = 0.0;
+        unsigned tau = 0u;
+        bool found = false;
+        for (int t = 0; t < kTopPThreads && !found; ++t) {
+            if (run + s_part[t] < target) { run += s_part[t]; continue; }
+            for (int q = 0; q < PER && !found; ++q) {          // the crossing lies among this thread's keys
+                const unsigned key = 65535u - unsigned(t * PER + q);
+                const int c = p.hist[key];
+                if (c == 0) continue;
+                run += double(c) * exp((double(bf16_of_key(key)) - m) * inv_t);
+                if (run >= target) { tau = key; found = true; }
+            }
+            // (if rounding left the crossing to the next thread's keys, the walk goes on there)
+        }
+        s_tau = tau;                                           // (0 if never reached: every token belongs)
+    }
+    __syncthreads();
+    const unsigned tau = s_tau;
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int i = tid; i < p.vocab; i += kTopPThreads) {
+        const uint16_t b = p.logits[i];
+        if (bf16_key(b) < tau) continue;
+        const float sc = __fdiv_rn(bf16_bits_to_f32(b), p.temperature) + gumbel_variate(p.seed, step, i);
+        if (sc > best || (sc == best && i < best_i)) { best = sc; best_i = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    if (lane == 0) { s_val[warp] = best; s_idx[warp] = best_i; }
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < kTopPThreads / 32; ++w)
+            if (s_val[w] > best || (s_val[w] == best && s_idx[w] < best_i)) { best = s_val[w]; best_i = s_idx[w]; }
+        p.tokens[slot] = best_i;
+        if (p.picked) *p.picked = best_i;
+        if (p.threshold_out) *p.threshold_out = bf16_of_key(tau);
+        for (int e = 0; e < p.n_eos; ++e)
+            if (p.eos_ids[e] == (long long)best_i) *p.stop_at = slot;
+    }
+}
+
+cudaError_t sample_top_p_launch(const TopPParams& p, cudaStream_t stream, bool pdl) {
+    return launch_kernel(sample_top_p_kernel, dim3(1), dim3(kTopPThreads), 0, stream, pdl, p);
+}
+
 }  // namespace tfb

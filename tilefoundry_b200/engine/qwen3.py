@@ -45,7 +45,8 @@ def pack_layer(w: dict) -> dict:
 class Qwen3Session(DecodeSession):
     def __init__(self, cfg: Qwen3Config, resource, *, max_ctx: int = 2176, device="cuda:0",
                  keep_logits: bool = False, trace_hidden: bool = False, pdl: bool = True,
-                 l2_prefetch: int = 0, kernel: int | None = None, temperature: float = 0.0, seed: int = 0):
+                 l2_prefetch: int = 0, kernel: int | None = None, temperature: float = 0.0, seed: int = 0,
+                 top_p: float = 1.0):
         """*kernel*: ``TFB_KERNEL_*`` of the step; ``None`` picks the one-launch step (``KERNEL_FUSED``) where the
         shapes allow it and the pick is greedy, else the step of one launch per kernel (0)."""
         if not torch.cuda.is_available():
@@ -91,7 +92,11 @@ class Qwen3Session(DecodeSession):
         self.qkv = z((HQ + 2 * HKV) * D)
         self.attn = z(HQ * D)
         self.act = z(I)
-        self.logits = z(V) if keep_logits else None
+        self.top_p = float(top_p)
+        if not 0.0 < self.top_p <= 1.0:
+            raise ValueError(f"top_p must be in (0, 1], got {top_p}")
+        nucleus = temperature > 0.0 and self.top_p < 1.0        # a second kernel filters the step's own draw
+        self.logits = z(V) if keep_logits or nucleus else None
         self.part_o = z(HQ * nsplit * D, dtype=f32)
         self.part_ml = z(HQ * nsplit * 2, dtype=f32)
         self.counters = z(HKV + 1, dtype=torch.int32)
@@ -135,6 +140,15 @@ class Qwen3Session(DecodeSession):
         #: kernels one step enqueues (embed + 5 per layer + lm_head [+ trace copies and final norm])
         self.launches_per_step = 1 if self.fused else 2 + 5 * len(self.layers) + (
             len(self.layers) + 1 if trace_hidden else 0)
+        self.nucleus = None
+        if nucleus:                                   # top-p: tfb_sample_top_p after every step, on the step's own logits
+            self.prev_pos = z(1, dtype=torch.int32)
+            self.nucleus_hist = z(65536, dtype=torch.int32)
+            self.nucleus = lib.SampleTopPArgs(
+                logits=lib.ptr(self.logits), pos=lib.ptr(self.pos), prev_pos=lib.ptr(self.prev_pos), tokens=lib.ptr(self.tokens),
+                picked=lib.ptr(self.picked), hist=lib.ptr(self.nucleus_hist), vocab=V, n_prompt=0, n_eos=0, pdl=0,
+                temperature=float(temperature), top_p=self.top_p, seed=int(seed) & (2 ** 64 - 1))
+            self.launches_per_step += 1
 
     # weights read once per token, for roofline arithmetic
     def weight_bytes(self) -> int:
@@ -146,8 +160,20 @@ class Qwen3Session(DecodeSession):
         return 2 * c.num_key_value_heads * c.head_dim * 2 * c.num_hidden_layers
 
     def step(self) -> None:
-        """Enqueue one decode step on the current stream."""
+        """Enqueue one decode step on the current stream (with ``top_p`` < 1: the step, then the nucleus draw that replaces
+        the token it wrote)."""
+        if self.nucleus is not None:
+            self.prev_pos.copy_(self.pos)
         lib.check(lib.load().tfb_qwen3_decode_step(C.byref(self.args), lib.stream()), "tfb_qwen3_decode_step")
+        if self.nucleus is not None:
+            self.nucleus.n_prompt = self.args.n_prompt
+            lib.check(lib.load().tfb_sample_top_p(C.byref(self.nucleus), lib.stream()), "tfb_sample_top_p")
+
+    def set_eos(self, eos_ids) -> None:
+        super().set_eos(eos_ids)
+        if self.nucleus is not None:                  # the latch belongs to the kernel that decides the token
+            self.nucleus.eos_ids, self.nucleus.n_eos, self.nucleus.stop_at = self.args.eos_ids, self.args.n_eos, self.args.stop_at
+            self.args.eos_ids, self.args.n_eos = None, 0      # (the step keeps stop_at: a latched sequence is a no-op)
 
     def check_status(self) -> None:
         """Raise if a bounded wait of the one-launch step gave up (its results are void then)."""

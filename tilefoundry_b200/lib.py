@@ -107,6 +107,12 @@ class Qwen3PrefillArgs(C.Structure):
                 ("part_o", _vp), ("part_ml", _vp), ("counters", _vp), ("status", _vp)]
 
 
+class SampleTopPArgs(C.Structure):
+    _fields_ = [("logits", _vp), ("pos", _vp), ("prev_pos", _vp), ("tokens", _vp), ("picked", _vp), ("threshold_out", _vp),
+                ("eos_ids", _vp), ("stop_at", _vp), ("hist", _vp), ("vocab", _i32), ("n_prompt", _i32), ("n_eos", _i32),
+                ("pdl", _i32), ("temperature", _f32), ("top_p", _f32), ("seed", C.c_uint64)]
+
+
 class MoeRouteArgs(C.Structure):
     _fields_ = [("x", _vp), ("w_router", _vp), ("w_shared_scale", _vp), ("logits", _vp), ("indices", _vp), ("weights", _vp),
                 ("shared_gate", _vp), ("tokens", _i32), ("hidden", _i32), ("experts", _i32), ("top_k", _i32), ("mode", _i32),
@@ -287,6 +293,7 @@ SYMBOLS = {
     "tfb_status_string": (C.c_char_p, [_i32]),
     "tfb_last_error": (C.c_char_p, []),
     "tfb_debug_trace": (_i32, [_vp, _i32]),
+    "tfb_sample_top_p": (_i32, [C.POINTER(SampleTopPArgs), _vp]),
     "tfb_moe_batch": (_i32, [C.POINTER(MoeBatchArgs), _vp]),
     "tfb_moe_batch_route": (_i32, [C.POINTER(MoeRouteArgs), _vp]),
     "tfb_graph_step_host": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp]),
