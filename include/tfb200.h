@@ -747,7 +747,8 @@ TFB_API int tfb_gemm_small_m(const tfb_gemm_small_m_args* args, tfb_stream_t str
  *   tokens:   the history; tokens[*pos] is rewritten when *pos != *prev_pos and *pos >= n_prompt
  *   eos_ids / n_eos / stop_at: the end-of-sequence latch of tfb_lm_head_args, applied to the new token (give the step
  *             itself no end ids then); a latched sequence is left alone
- *   hist:     scratch int32 [65536]                threshold_out: optional, the smallest logit value inside the nucleus */
+ *   hist:     scratch int32 [65664], zeroed once (the two kernels of the call leave it zeroed)
+ *   threshold_out: optional, the smallest logit value inside the nucleus */
 typedef struct {
     const void* logits;
     const int32_t* pos;

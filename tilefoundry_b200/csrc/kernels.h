@@ -115,7 +115,7 @@ struct TopPParams {
     const long long* eos_ids;
     int n_eos;
     int* stop_at;
-    int* hist;                  // scratch i32 [65536]
+    int* hist;                  // scratch i32 [65664], zero between calls: value histogram, tickets, largest / threshold key, CTA picks
 };
 cudaError_t sample_top_p_launch(const TopPParams& p, cudaStream_t stream, bool pdl);
 int lm_head_ctas(int n);

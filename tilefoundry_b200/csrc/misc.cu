@@ -326,42 +326,57 @@ cudaError_t residual_add_f32_launch(const float* a, const float* b, float* out, 
 // histogram of integer counts (exact, whatever the order of the atomics) and the masses are f64: the threshold does not
 // depend on summation order beyond the last bit of a double.  Inside the nucleus the pick is the Gumbel-max rule of the
 // head kernel (same variates), so top_p = 1 draws what the head kernel draws.
-// One CTA: the kernel follows a decode step that kept its logits; it replaces the token that step wrote.
+// The kernel follows a decode step that kept its logits; it replaces the token that step wrote.
 __device__ __forceinline__ unsigned bf16_key(uint16_t b) { return (b & 0x8000u) ? (~unsigned(b) & 0xffffu) : (unsigned(b) | 0x8000u); }
 __device__ __forceinline__ float bf16_of_key(unsigned key) {
     return bf16_bits_to_f32(uint16_t((key & 0x8000u) ? (key & 0x7fffu) : (~key & 0xffffu)));
 }
 constexpr int kTopPThreads = 1024;
+constexpr int kTopPCtas = 32;
 
-__global__ void __launch_bounds__(kTopPThreads) sample_top_p_kernel(const TopPParams p) {
+// Scratch words after the 65536 counts: [0] ticket of the first kernel, [1] largest key, [2] threshold key, [3] ticket of
+// the second kernel, [4 ..] the CTAs' best (score bits, index) pairs.
+constexpr int kTopPScratch = 65536;
+
+// First kernel: every CTA counts its slice of the logits into the histogram (atomics from 32 multiprocessors at once);
+// the last CTA to finish walks the values and leaves the threshold key.
+__global__ void __launch_bounds__(kTopPThreads) top_p_threshold_kernel(const TopPParams p) {
     __shared__ double s_part[kTopPThreads];
-    __shared__ float s_val[kTopPThreads / 32];
-    __shared__ int s_idx[kTopPThreads / 32];
-    __shared__ unsigned s_maxkey, s_tau;
+    __shared__ unsigned s_maxkey;
+    __shared__ int s_last;
     pdl_trigger();
     pdl_wait();
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (p.stop_at && *p.stop_at != 0) return;                  // the sequence has ended
-    const int slot = *p.pos, step = *p.prev_pos;               // the step before this kernel moved pos from `step` to `slot`
+    const int tid = threadIdx.x;
+    if (p.stop_at && *p.stop_at != 0) return;                  // the sequence has ended (the same for every CTA)
+    const int slot = *p.pos, step = *p.prev_pos;               // the step before moved pos from `step` to `slot`
     if (slot == step || slot < p.n_prompt) return;             // it did not advance, or the slot belongs to the prompt
+    int* const ticket = p.hist + kTopPScratch;
+    unsigned* const gmax = reinterpret_cast<unsigned*>(p.hist + kTopPScratch + 1);
     if (tid == 0) s_maxkey = 0u;
-    for (int k = tid; k < 65536; k += kTopPThreads) p.hist[k] = 0;
     __syncthreads();
     unsigned mk = 0u;
-    for (int i = tid; i < p.vocab; i += kTopPThreads) {
+    for (int i = blockIdx.x * kTopPThreads + tid; i < p.vocab; i += gridDim.x * kTopPThreads) {
         const unsigned key = bf16_key(p.logits[i]);
         atomicAdd(p.hist + key, 1);
         mk = max(mk, key);
     }
     atomicMax(&s_maxkey, mk);
     __syncthreads();
-    const double m = double(bf16_of_key(s_maxkey)), inv_t = 1.0 / double(p.temperature);
+    if (tid == 0) {
+        atomicMax(gmax, s_maxkey);
+        __threadfence();
+        s_last = atomicAdd(ticket, 1) == int(gridDim.x) - 1;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const double m = double(bf16_of_key(__ldcg(gmax))), inv_t = 1.0 / double(p.temperature);
     // thread t owns keys 65535 - 64 t down to 65535 - 64 t - 63
     constexpr int PER = 65536 / kTopPThreads;
     double mine = 0.0;
     for (int q = 0; q < PER; ++q) {
         const unsigned key = 65535u - unsigned(tid * PER + q);
-        const int c = p.hist[key];
+        const int c = __ldcg(p.hist + key);
         if (c) mine += double(c) * exp((double(bf16_of_key(key)) - m) * inv_t);
     }
     s_part[tid] = mine;
@@ -377,20 +392,38 @@ __global__ void __launch_bounds__(kTopPThreads) sample_top_p_kernel(const TopPPa
             if (run + s_part[t] < target) { run += s_part[t]; continue; }
             for (int q = 0; q < PER && !found; ++q) {          // the crossing lies among this thread's keys
                 const unsigned key = 65535u - unsigned(t * PER + q);
-                const int c = p.hist[key];
+                const int c = __ldcg(p.hist + key);
                 if (c == 0) continue;
                 run += double(c) * exp((double(bf16_of_key(key)) - m) * inv_t);
                 if (run >= target) { tau = key; found = true; }
             }
             // (if rounding left the crossing to the next thread's keys, the walk goes on there)
         }
-        s_tau = tau;                                           // (0 if never reached: every token belongs)
+        p.hist[kTopPScratch + 2] = int(tau);                   // (0 if never reached: every token belongs)
+        *ticket = 0;
+        *gmax = 0u;
     }
-    __syncthreads();
-    const unsigned tau = s_tau;
+}
+
+// Second kernel: the Gumbel-max pick inside the nucleus, every CTA over its slice (two double-precision logarithms per
+// token of the nucleus: too many for one multiprocessor); the last CTA to finish merges, writes the token, applies the
+// end-of-sequence latch and zeroes the histogram for the next call.
+__global__ void __launch_bounds__(kTopPThreads) top_p_pick_kernel(const TopPParams p) {
+    __shared__ float s_val[kTopPThreads / 32];
+    __shared__ int s_idx[kTopPThreads / 32];
+    __shared__ int s_last;
+    pdl_trigger();
+    pdl_wait();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (p.stop_at && *p.stop_at != 0) return;
+    const int slot = *p.pos, step = *p.prev_pos;
+    if (slot == step || slot < p.n_prompt) return;
+    const unsigned tau = unsigned(__ldcg(p.hist + kTopPScratch + 2));
+    int* const ticket = p.hist + kTopPScratch + 3;
+    int* const pairs = p.hist + kTopPScratch + 4;
     float best = -INFINITY;
     int best_i = 0x7fffffff;
-    for (int i = tid; i < p.vocab; i += kTopPThreads) {
+    for (int i = blockIdx.x * kTopPThreads + tid; i < p.vocab; i += gridDim.x * kTopPThreads) {
         const uint16_t b = p.logits[i];
         if (bf16_key(b) < tau) continue;
         const float sc = __fdiv_rn(bf16_bits_to_f32(b), p.temperature) + gumbel_variate(p.seed, step, i);
@@ -407,16 +440,36 @@ __global__ void __launch_bounds__(kTopPThreads) sample_top_p_kernel(const TopPPa
     if (tid == 0) {
         for (int w = 1; w < kTopPThreads / 32; ++w)
             if (s_val[w] > best || (s_val[w] == best && s_idx[w] < best_i)) { best = s_val[w]; best_i = s_idx[w]; }
+        pairs[2 * blockIdx.x] = __float_as_int(best);
+        pairs[2 * blockIdx.x + 1] = best_i;
+        __threadfence();
+        s_last = atomicAdd(ticket, 1) == int(gridDim.x) - 1;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int k = tid; k < 65536; k += kTopPThreads) p.hist[k] = 0;      // clean for the next call
+    if (tid == 0) {
+        best = -INFINITY;
+        best_i = 0x7fffffff;
+        for (int c = 0; c < int(gridDim.x); ++c) {
+            const float ov = __int_as_float(__ldcg(pairs + 2 * c));
+            const int oi = __ldcg(pairs + 2 * c + 1);
+            if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+        }
         p.tokens[slot] = best_i;
         if (p.picked) *p.picked = best_i;
         if (p.threshold_out) *p.threshold_out = bf16_of_key(tau);
         for (int e = 0; e < p.n_eos; ++e)
             if (p.eos_ids[e] == (long long)best_i) *p.stop_at = slot;
+        *ticket = 0;
     }
 }
 
 cudaError_t sample_top_p_launch(const TopPParams& p, cudaStream_t stream, bool pdl) {
-    return launch_kernel(sample_top_p_kernel, dim3(1), dim3(kTopPThreads), 0, stream, pdl, p);
+    const cudaError_t e = launch_kernel(top_p_threshold_kernel, dim3(kTopPCtas), dim3(kTopPThreads), 0, stream, pdl, p);
+    if (e != cudaSuccess) return e;
+    return launch_kernel(top_p_pick_kernel, dim3(kTopPCtas), dim3(kTopPThreads), 0, stream, pdl, p);
 }
 
 }  // namespace tfb

@@ -143,12 +143,12 @@ class Qwen3Session(DecodeSession):
         self.nucleus = None
         if nucleus:                                   # top-p: tfb_sample_top_p after every step, on the step's own logits
             self.prev_pos = z(1, dtype=torch.int32)
-            self.nucleus_hist = z(65536, dtype=torch.int32)
+            self.nucleus_hist = z(65664, dtype=torch.int32)
             self.nucleus = lib.SampleTopPArgs(
                 logits=lib.ptr(self.logits), pos=lib.ptr(self.pos), prev_pos=lib.ptr(self.prev_pos), tokens=lib.ptr(self.tokens),
                 picked=lib.ptr(self.picked), hist=lib.ptr(self.nucleus_hist), vocab=V, n_prompt=0, n_eos=0, pdl=0,
                 temperature=float(temperature), top_p=self.top_p, seed=int(seed) & (2 ** 64 - 1))
-            self.launches_per_step += 1
+            self.launches_per_step += 2
 
     # weights read once per token, for roofline arithmetic
     def weight_bytes(self) -> int:
