@@ -101,6 +101,62 @@ def test_alias_tables_read_a_checkpoint_as_the_authored_weights():
     _same_packed(pm.pack("granite_4_0_h_small", cfg, res), pm.pack("granite_4_0_h_small", cfg, DictResource(w)))
 
 
+def _qwen35_state_dict(cfg, w, pre="model.language_model"):
+    """A Hugging Face Qwen3.5-MoE checkpoint's keys and layouts holding the seeded weights: ``nn.Linear`` is (out, in),
+    the experts' gate and up halves are one tensor, the norms store ``w`` of ``x * (1 + w)``.  Returns the state dict and
+    the authored weights it stands for (the gains are what reading ``1 + w`` back gives)."""
+    want = dict(w)
+    lin = lambda t: t[0].t().contiguous()
+    sd = {f"{pre}.embed_tokens.weight": w["table"], "lm_head.weight": w["w_head"].t().contiguous()}
+
+    def gain(key, name):
+        sd[key] = (w[name] - 1.0).to(BF)
+        want[name] = sd[key].float() + 1.0
+    gain(f"{pre}.norm.weight", "gamma_final")
+    for i, kind in enumerate(cfg.layer_types):
+        L, g = f"{pre}.layers.{i}", lambda n: w[f"layer{i}.{n}"]
+        gain(f"{L}.input_layernorm.weight", f"layer{i}.mixer.gamma_in")
+        gain(f"{L}.post_attention_layernorm.weight", f"layer{i}.moe.gamma_post")
+        if kind == "linear_attention":
+            for ours, theirs in (("w_in_qkv", "in_proj_qkv"), ("w_in_z", "in_proj_z"), ("w_in_b", "in_proj_b"),
+                                 ("w_in_a", "in_proj_a"), ("w_out", "out_proj")):
+                sd[f"{L}.linear_attn.{theirs}.weight"] = lin(g(f"mixer.{ours}"))
+            sd[f"{L}.linear_attn.conv1d.weight"] = g("mixer.conv_w").unsqueeze(1)
+            sd[f"{L}.linear_attn.A_log"], sd[f"{L}.linear_attn.dt_bias"] = g("mixer.a_log"), g("mixer.dt_bias")
+            sd[f"{L}.linear_attn.norm.weight"] = g("mixer.gamma_gdn")
+        else:
+            for ours, theirs in (("w_qg", "q_proj"), ("w_k", "k_proj"), ("w_v", "v_proj"), ("w_o", "o_proj")):
+                sd[f"{L}.self_attn.{theirs}.weight"] = lin(g(f"mixer.{ours}"))
+            gain(f"{L}.self_attn.q_norm.weight", f"layer{i}.mixer.gamma_q")
+            gain(f"{L}.self_attn.k_norm.weight", f"layer{i}.mixer.gamma_k")
+        sd[f"{L}.mlp.experts.gate_up_proj"] = torch.cat([g("moe.w_gate"), g("moe.w_up")], dim=1)
+        sd[f"{L}.mlp.experts.down_proj"] = g("moe.w_down")
+        for ours, theirs in (("w_shared_gate", "shared_expert.gate_proj"), ("w_shared_up", "shared_expert.up_proj"),
+                             ("w_shared_down", "shared_expert.down_proj"), ("w_shared_scale", "shared_expert_gate")):
+            sd[f"{L}.mlp.{theirs}.weight"] = g(f"moe.{ours}").t().contiguous()
+        sd[f"{L}.mlp.gate.weight"] = g("moe.router.w_router").t().contiguous()
+    return sd, want
+
+
+def test_qwen35_alias_table_applies_the_checkpoint_conversions():
+    cfg, w = _qwen35()
+    sd, want = _qwen35_state_dict(cfg, w)
+    res = DictResource(sd, alias=pm.hf_alias_qwen3_5(cfg))
+    for name, value in want.items():                             # name by name: value, shape and dtype as authored
+        *path, leaf = name.split(".")
+        sub = res
+        for seg in path:
+            sub = sub.subtree(seg)
+        got = sub.load(leaf)
+        assert got.dtype == value.dtype and got.shape == value.shape and torch.equal(got, value), name
+    assert torch.equal(res.subtree("layer0").subtree("mixer").load("gamma_in"),
+                       sd["model.language_model.layers.0.input_layernorm.weight"].float() + 1.0)
+    _same_packed(pm.pack("qwen3_5_35b_a3b", cfg, res), pm.pack("qwen3_5_35b_a3b", cfg, DictResource(want)))
+    # a tied head reads the embedding table
+    tied = DictResource(sd, alias=pm.hf_alias_qwen3_5(cfg, head="model.language_model.embed_tokens.weight"))
+    assert torch.equal(tied.load("w_head"), w["table"].t())
+
+
 @pytest.mark.parametrize("key", sorted(MODELS))
 def test_pack_save_load_round_trip(tmp_path, key):
     cfg, w = MODELS[key]()

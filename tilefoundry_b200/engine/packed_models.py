@@ -8,9 +8,10 @@ converters that fold and repack them (``src/tilefoundry/ir/core/module.py:505-58
 layout the kernels read (each engine module's ``pack_model``: projections ``[out, in]`` row-major bf16, the ones
 that share an input concatenated, expert slabs as declared), written as ONE safetensors file per model with the
 dimensions in its metadata.  A session takes the loaded ``PackedModel`` in place of a resource; for several GPUs it
-cuts its shard out of the packed tensors.  The Qwen3.5 alias table is not restated here: that checkpoint needs the
-converters of its ``model.py`` (``1 + w`` gains, fused expert tensors), so its file is packed from a resource that
-already speaks the authored names.
+cuts its shard out of the packed tensors.  The Qwen3.5 checkpoint differs from its authored weights by more than
+names (``1 + w`` gains, ``nn.Linear`` layouts, one fused gate/up tensor per layer's experts:
+``examples/qwen3_5_35b_a3b-tilelang/model.py:232-287,421-476,501-505,607-652,809-820``); every one of those converters
+takes a single raw tensor, so they are read-side transforms of the alias table here (``hf_alias_qwen3_5``).
 """
 from __future__ import annotations
 
@@ -139,4 +140,50 @@ def hf_alias_granite(cfg) -> dict:
         alias[f"{layer}.block_sparse_moe.gamma_post"] = Absolute(f"{layer}.post_attention_layernorm.weight")
         alias[f"{layer}.block_sparse_moe.w_shared_in"] = Absolute(f"{layer}.shared_mlp.input_linear.weight")
         alias[f"{layer}.block_sparse_moe.w_shared_out"] = Absolute(f"{layer}.shared_mlp.output_linear.weight")
+    return alias
+
+
+def hf_alias_qwen3_5(cfg, text_prefix: str = "model.language_model", head: str = "lm_head.weight") -> dict:
+    """Authored name -> key of a Hugging Face ``Qwen3_5MoeForConditionalGeneration`` checkpoint, with the read-side
+    transform each weight needs (raw names: ``examples/qwen3_5_35b_a3b-tilelang/model.py:931-965``).  What differs:
+    the norms of this family multiply by ``1 + w`` where the authored ``rms_norm`` multiplies by ``w`` (all but the
+    gated norm of the linear-attention read-out); every ``nn.Linear`` is ``(out, in)`` where the authored matmuls
+    take ``(in, out)``; the experts' gate and up projections are the two halves of one ``(experts, 2 * inter,
+    hidden)`` tensor, gate first; the depthwise convolution keeps a singleton axis.  Gains, ``A_log``, ``dt_bias`` and
+    the convolution kernel are read as f32 (they are added to and exponentiated, not contracted over), the matmul
+    weights stay bf16.  A tied head is ``head=`` the embedding's key."""
+    inter = cfg.moe_intermediate
+    gain = lambda t: t.float() + 1.0
+    f32 = lambda t: t.float().contiguous()
+    linear = lambda t: t.t().unsqueeze(0).contiguous()            # (out, in) -> (1, in, out)
+    flip = lambda t: t.t().contiguous()                            # (a, b) -> (b, a)
+    pre = text_prefix
+    alias = {"table": Absolute(f"{pre}.embed_tokens.weight"),
+             "gamma_final": Preprocessed(Absolute(f"{pre}.norm.weight"), gain),
+             "w_head": Preprocessed(Absolute(head), flip)}
+    gdn = {"gamma_in": ("input_layernorm.weight", gain), "w_in_qkv": ("linear_attn.in_proj_qkv.weight", linear),
+           "w_in_z": ("linear_attn.in_proj_z.weight", linear), "w_in_b": ("linear_attn.in_proj_b.weight", linear),
+           "w_in_a": ("linear_attn.in_proj_a.weight", linear),
+           "conv_w": ("linear_attn.conv1d.weight", lambda t: t.float().squeeze(1).contiguous()),
+           "a_log": ("linear_attn.A_log", f32), "dt_bias": ("linear_attn.dt_bias", f32),
+           "gamma_gdn": ("linear_attn.norm.weight", f32), "w_out": ("linear_attn.out_proj.weight", linear)}
+    attn = {"gamma_in": ("input_layernorm.weight", gain), "w_qg": ("self_attn.q_proj.weight", linear),
+            "w_k": ("self_attn.k_proj.weight", linear), "w_v": ("self_attn.v_proj.weight", linear),
+            "gamma_q": ("self_attn.q_norm.weight", gain), "gamma_k": ("self_attn.k_norm.weight", gain),
+            "w_o": ("self_attn.o_proj.weight", linear)}
+    moe = {"gamma_post": ("post_attention_layernorm.weight", gain),
+           "w_gate": ("mlp.experts.gate_up_proj", lambda t: t[:, :inter, :].contiguous()),
+           "w_up": ("mlp.experts.gate_up_proj", lambda t: t[:, inter:, :].contiguous()),
+           "w_down": ("mlp.experts.down_proj", lambda t: t.contiguous()),
+           "w_shared_gate": ("mlp.shared_expert.gate_proj.weight", flip),
+           "w_shared_up": ("mlp.shared_expert.up_proj.weight", flip),
+           "w_shared_down": ("mlp.shared_expert.down_proj.weight", flip),
+           "w_shared_scale": ("mlp.shared_expert_gate.weight", flip)}
+    for i, kind in enumerate(cfg.layer_types):
+        layer = f"{pre}.layers.{i}"
+        for ours, (theirs, read) in (gdn if kind == "linear_attention" else attn).items():
+            alias[f"layer{i}.mixer.{ours}"] = Preprocessed(Absolute(f"{layer}.{theirs}"), read)
+        for ours, (theirs, read) in moe.items():
+            alias[f"layer{i}.moe.{ours}"] = Preprocessed(Absolute(f"{layer}.{theirs}"), read)
+        alias[f"layer{i}.moe.router.w_router"] = Preprocessed(Absolute(f"{layer}.mlp.gate.weight"), flip)
     return alias
