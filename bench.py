@@ -4,9 +4,9 @@
 
 A "step" is one decode step: one token through embed -> 28 layers -> lm_head ->
 greedy pick.  The sequence is a 64-token uniform-random prompt followed by greedy
-continuation; the first W steps (default 63, the prompt walk) are untimed warm-up
-and the next K steps (default 2048) are timed, so the defaults time exactly the
-2048 new tokens the metric names.  Weights are seeded bf16 N(0, 0.02) (norm gains
+continuation; the prompt walk (63 steps) and W further decode steps (default 3) are
+untimed warm-up and the next K steps (default 2048) are timed, so the defaults time
+the 2048 new tokens the metric names.  Weights are seeded bf16 N(0, 0.02) (norm gains
 1 + N(0, 0.02)); nothing is read from disk.
 
 One JSON line is printed by rank 0.  `value` is measured with the whole state
@@ -15,6 +15,11 @@ the same captured step the way the reference's generation loop drives a model --
 token id in from pinned host memory, picked token back to the host, every step.
 The dense Qwen3 path does not shard ("replicas only"): with --gpus N each rank
 decodes its own sequence and `value` is the sum over ranks.
+
+Side modes, each printing one JSON line that is not the metric: --config (the other
+three architectures), --batch B (B sequences per step), --batch32-projection,
+--moe-batch T (the Qwen3.5 expert block for T tokens at once), --profile-layers /
+--dominant-only (the small cases profiler captures run).
 """
 from __future__ import annotations
 
