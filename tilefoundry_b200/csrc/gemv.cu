@@ -190,7 +190,6 @@ cudaError_t gemv_pair_dispatch(const GemvParams& a, const GemvParams& b, int nor
 template <int ROWS, int KSPLIT, int WARPS, int UNROLL, int NORM_MODE, int EPI>
 static cudaError_t launch_cfg(const GemvParams& p, cudaStream_t stream, bool pdl) {
     constexpr int GROUPS = WARPS / KSPLIT;
-    constexpr int NMAT = (EPI == 2) ? 2 : 1;
     const int rows_per_cta = GROUPS * ROWS;
     const unsigned grid = (p.n + rows_per_cta - 1) / rows_per_cta;
     // x (f32) + reduce scratch + K-split partials (padded to WARPS*ROWS*2) + parked gains (bf16)

@@ -88,11 +88,12 @@ template <int MAXC>
 struct StagedGain {
     template <int NORM_MODE>
     static __device__ __forceinline__ void preload(const uint16_t* __restrict__ gamma, uint4* gs, int k) {
-        if (NORM_MODE == 0) return;
+        if constexpr (NORM_MODE != 0) {
 #pragma unroll
-        for (int m = 0; m < MAXC; ++m) {
-            const int c = threadIdx.x + m * blockDim.x;
-            if (c < (k >> 3)) gs[c] = *reinterpret_cast<const uint4*>(gamma + (c << 3));
+            for (int m = 0; m < MAXC; ++m) {
+                const int c = threadIdx.x + m * blockDim.x;
+                if (c < (k >> 3)) gs[c] = *reinterpret_cast<const uint4*>(gamma + (c << 3));
+            }
         }
     }
     template <int NORM_MODE>

@@ -51,6 +51,7 @@ constexpr int kGroupRows = 16;                   // weight rows one accumulator 
 constexpr int kGroupCap = TFB_GROUP_CAP;         // ... and how many a tile takes (even; 2048 / 148 = 13.8 rows fit one tile)
 constexpr int kRowBytes = kSliceLen * 2;         // a tile row: 2 KB, one bulk copy
 constexpr int kTileBytes = kGroupCap * kRowBytes;
+static_assert(kGroupCap % 2 == 0 && kGroupCap <= kGroupRows, "a tile's rows must fit one accumulator");
 constexpr int kStages = (210 * 1024) / kTileBytes;   // seven 28 KB stages
 constexpr int kChunkBytes = 256;                 // of every tile row, what one MMA consumes (128 elements)
 constexpr int kAccBufs = 4;                      // accumulators in flight between the MMA thread and the epilogue warps
